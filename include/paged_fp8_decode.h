@@ -1,0 +1,149 @@
+/*
+ * C ABI of the B200 (sm_100a) paged FP8-e4m3 KV-cache GQA decode-attention library
+ * (libpaged_fp8_decode.so).
+ *
+ * Plain pointers and sizes only: no torch types.  Every entry point is asynchronous on
+ * the CUDA stream it is given, allocates nothing unless stated, returns 0 on success or a
+ * negative PFD_ERR_* code, and records a message readable with pfd_last_error().
+ *
+ * File/line citations name the interface of the reference project
+ * (Kevin-Li-2025/single-gpu-inference-lab) that each entry point replaces.
+ */
+#ifndef PAGED_FP8_DECODE_H_
+#define PAGED_FP8_DECODE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PFD_ABI_VERSION 1
+
+/* element types of query / output / partial_output */
+#define PFD_DTYPE_F32 0
+#define PFD_DTYPE_F16 1
+#define PFD_DTYPE_BF16 2
+
+#define PFD_OK 0
+#define PFD_ERR_INVALID (-1)     /* bad argument; nothing was launched            */
+#define PFD_ERR_UNSUPPORTED (-2) /* geometry outside what the kernels implement   */
+#define PFD_ERR_CUDA (-3)        /* a CUDA runtime / driver call failed           */
+#define PFD_ERR_DEVICE (-4)      /* a kernel recorded an error status             */
+
+/* flags */
+#define PFD_FLAG_NO_TMA 1u        /* stream K/V with plain 16-byte global loads instead of TMA */
+#define PFD_FLAG_NO_DIRECT_OUT 2u /* always go through the partial workspace + merge kernel    */
+
+/*
+ * Operands of one decode-attention layer-step.
+ *
+ * Replaces the argument list of
+ *   l20_paged_decode_fp8_e4m3_split_out_cuda(query, key_cache, value_cache, block_table,
+ *       seq_lens, partial_output, partial_max, partial_sum, output, k_scale, v_scale,
+ *       max_seq_len, split_size)      integrations/vllm/cuda/l20_paged_decode.cu:651-664
+ * and of the Triton launcher l20_paged_split_kv_attention_fp8
+ *                                      integrations/vllm/l20_paged_split_kv.py:597-695
+ * (which, unlike the CUDA launcher, honours cache strides: :665-668).
+ *
+ * Layouts (all device pointers):
+ *   query, output   [batch, num_q_heads, head_dim]   f16 or bf16, innermost contiguous
+ *   key/value_cache [pages, page_size=16, num_kv_heads, head_dim] e4m3 bytes addressed by
+ *                   (page, token, head) byte strides; head_dim bytes contiguous.  NHD (the
+ *                   reference op's layout) and HND are both just strides.
+ *   block_table     [batch, >= ceil(max_seq_len/16)] int32 physical page ids
+ *   seq_lens        [batch] int32
+ *   partial_output  [batch, num_q_heads, workspace_splits, head_dim] (partial_dtype),
+ *   partial_max/sum [batch, num_q_heads, workspace_splits] f32; workspace_splits >=
+ *                   ceil((max_seq_len - kv_start) / split_size).  May be NULL when that
+ *                   quotient is 1.
+ * Split s of sequence b covers tokens [kv_start + s*split_size, kv_start + (s+1)*split_size)
+ * clipped to [0, seq_lens[b]).  partial_max is in natural-log units, partial_output is the
+ * un-normalised sum of p*v (v already scaled), as in the reference kernels.
+ */
+typedef struct pfd_decode_args {
+  uint32_t struct_size; /* sizeof(pfd_decode_args): lets the library reject a stale caller */
+  uint32_t flags;
+
+  int32_t batch;
+  int32_t num_q_heads;
+  int32_t num_kv_heads;
+  int32_t head_dim;  /* 64 or 128 */
+  int32_t page_size; /* 16 */
+  int32_t max_seq_len;
+  int32_t split_size; /* multiple of 16, >= 16 */
+  int32_t kv_start;   /* first token attended (0 for a normal decode step) */
+  int32_t query_dtype;   /* PFD_DTYPE_F16 | PFD_DTYPE_BF16; output uses the same */
+  int32_t partial_dtype; /* PFD_DTYPE_F32 | F16 | BF16 */
+  float sm_scale;        /* softmax scale; 0 selects head_dim^-0.5 */
+  float k_scale;         /* used when k_scale_per_head == NULL */
+  float v_scale;         /* used when v_scale_per_head == NULL */
+  int32_t workspace_splits;
+
+  const void* query;
+  int64_t q_stride_b, q_stride_h; /* elements */
+  const void* key_cache;
+  const void* value_cache;
+  int64_t num_pages;
+  int64_t k_stride_page, k_stride_token, k_stride_head; /* bytes */
+  int64_t v_stride_page, v_stride_token, v_stride_head; /* bytes */
+  const int32_t* block_table;
+  int64_t bt_stride_b; /* elements */
+  const int32_t* seq_lens;
+  const float* k_scale_per_head; /* [num_kv_heads] device floats, or NULL */
+  const float* v_scale_per_head;
+
+  void* partial_output;
+  float* partial_max;
+  float* partial_sum;
+  int64_t partial_stride_b, partial_stride_h, partial_stride_s; /* elements, of partial_max */
+
+  void* output; /* [batch, num_q_heads, head_dim], may be NULL if packed_output is set */
+  int64_t o_stride_b, o_stride_h; /* elements */
+  /* optional [batch, num_q_heads, head_dim + 2] f32: merged (o un-normalised, m, l) of the
+   * attended range, the exchange format for a KV range split across GPUs */
+  float* packed_output;
+
+  void* stream; /* cudaStream_t */
+} pfd_decode_args;
+
+/*
+ * One decode-attention layer-step: split-KV partial kernel + LSE merge kernel.
+ * Replaces l20_paged_decode_fp8_e4m3_split_out_cuda
+ * (integrations/vllm/cuda/l20_paged_decode.cu:651-725) and the two Triton launches of
+ * l20_paged_split_kv_attention_fp8 (integrations/vllm/l20_paged_split_kv.py:652-694).
+ */
+int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args);
+
+/*
+ * LSE merge of `num_parts` packed partials [num_parts, rows, head_dim + 2] f32
+ * (o un-normalised, m natural-log, l) into output [rows, head_dim] of `out_dtype`.
+ * Same maths as _paged_split_kv_reduce (integrations/vllm/l20_paged_split_kv.py:459-488)
+ * and paged_decode_merge_kernel (integrations/vllm/cuda/l20_paged_decode.cu:424-463), with
+ * no limit on the number of parts.  Used after the all-gather of a KV-range split.
+ */
+int pfd_merge_packed(const float* packed, int32_t num_parts, int64_t rows, int32_t head_dim,
+                     void* output, int32_t out_dtype, void* stream);
+
+/*
+ * Debug / parity entry: writes, for every (sequence, token < max_seq_len), the cache slot
+ * index page*16 + token%16 that the kernels' address function resolves (-1 beyond the
+ * sequence) into slots[batch, max_seq_len] (int64).  Counterpart of the gather
+ * `physical = table[b, t // 16]; offsets = t % 16`
+ * (scripts/smoke_cuda_paged_fp8_decode_op.py:29-33).
+ */
+int pfd_resolve_slots(const int32_t* block_table, int64_t bt_stride_b, const int32_t* seq_lens,
+                      int32_t batch, int32_t max_seq_len, int64_t* slots, void* stream);
+
+/* Number of kernels this library has launched in this process (for launch accounting). */
+int64_t pfd_launch_count(void);
+
+/* Message of the last failing call on this thread ("" if none). */
+const char* pfd_last_error(void);
+
+int pfd_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PAGED_FP8_DECODE_H_ */

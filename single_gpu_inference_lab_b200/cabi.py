@@ -1,0 +1,197 @@
+"""``ctypes`` binding of the C ABI in ``include/paged_fp8_decode.h``.
+
+This is the route a non-PyTorch host takes; torch tensors are used here only as device
+buffers whose ``data_ptr()`` / strides are handed over as plain integers.  The parity tests
+call the kernels through this module.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import torch
+
+LIB_NAME = "libpaged_fp8_decode.so"
+
+PFD_DTYPE_F32, PFD_DTYPE_F16, PFD_DTYPE_BF16 = 0, 1, 2
+PFD_FLAG_NO_TMA = 1
+PFD_FLAG_NO_DIRECT_OUT = 2
+
+EXPORTS = (
+    "pfd_paged_decode_fp8_e4m3_split_out",
+    "pfd_merge_packed",
+    "pfd_resolve_slots",
+    "pfd_launch_count",
+    "pfd_last_error",
+    "pfd_abi_version",
+)
+
+
+class DecodeArgs(C.Structure):
+    """Mirror of ``pfd_decode_args`` (field order and types must match the header)."""
+
+    _fields_ = [
+        ("struct_size", C.c_uint32),
+        ("flags", C.c_uint32),
+        ("batch", C.c_int32),
+        ("num_q_heads", C.c_int32),
+        ("num_kv_heads", C.c_int32),
+        ("head_dim", C.c_int32),
+        ("page_size", C.c_int32),
+        ("max_seq_len", C.c_int32),
+        ("split_size", C.c_int32),
+        ("kv_start", C.c_int32),
+        ("query_dtype", C.c_int32),
+        ("partial_dtype", C.c_int32),
+        ("sm_scale", C.c_float),
+        ("k_scale", C.c_float),
+        ("v_scale", C.c_float),
+        ("workspace_splits", C.c_int32),
+        ("query", C.c_void_p),
+        ("q_stride_b", C.c_int64),
+        ("q_stride_h", C.c_int64),
+        ("key_cache", C.c_void_p),
+        ("value_cache", C.c_void_p),
+        ("num_pages", C.c_int64),
+        ("k_stride_page", C.c_int64),
+        ("k_stride_token", C.c_int64),
+        ("k_stride_head", C.c_int64),
+        ("v_stride_page", C.c_int64),
+        ("v_stride_token", C.c_int64),
+        ("v_stride_head", C.c_int64),
+        ("block_table", C.c_void_p),
+        ("bt_stride_b", C.c_int64),
+        ("seq_lens", C.c_void_p),
+        ("k_scale_per_head", C.c_void_p),
+        ("v_scale_per_head", C.c_void_p),
+        ("partial_output", C.c_void_p),
+        ("partial_max", C.c_void_p),
+        ("partial_sum", C.c_void_p),
+        ("partial_stride_b", C.c_int64),
+        ("partial_stride_h", C.c_int64),
+        ("partial_stride_s", C.c_int64),
+        ("output", C.c_void_p),
+        ("o_stride_b", C.c_int64),
+        ("o_stride_h", C.c_int64),
+        ("packed_output", C.c_void_p),
+        ("stream", C.c_void_p),
+    ]
+
+
+_lib = None
+
+
+def library_path() -> Path:
+    return Path(__file__).with_name(LIB_NAME)
+
+
+def load() -> C.CDLL:
+    """Load the C-ABI library (built in-tree by ``build.py``).  Raises if it is missing."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not path.exists():
+            raise RuntimeError(
+                f"{path} is missing: build it with `python -m single_gpu_inference_lab_b200.build`; "
+                "there is no fallback implementation"
+            )
+        lib = C.CDLL(str(path))
+        lib.pfd_paged_decode_fp8_e4m3_split_out.argtypes = [C.POINTER(DecodeArgs)]
+        lib.pfd_paged_decode_fp8_e4m3_split_out.restype = C.c_int
+        lib.pfd_merge_packed.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]
+        lib.pfd_merge_packed.restype = C.c_int
+        lib.pfd_resolve_slots.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
+        lib.pfd_resolve_slots.restype = C.c_int
+        lib.pfd_launch_count.restype = C.c_int64
+        lib.pfd_last_error.restype = C.c_char_p
+        lib.pfd_abi_version.restype = C.c_int
+        _lib = lib
+    return _lib
+
+
+def _dtype_code(dtype: torch.dtype) -> int:
+    return {torch.float32: PFD_DTYPE_F32, torch.float16: PFD_DTYPE_F16, torch.bfloat16: PFD_DTYPE_BF16}[dtype]
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise RuntimeError(load().pfd_last_error().decode())
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def decode_args(
+    query, key_cache, value_cache, block_table, seq_lens, *, k_scale, v_scale, max_seq_len,
+    split_size, output=None, packed_output=None, workspace=None, kv_start=0, sm_scale=0.0, flags=0,
+) -> DecodeArgs:
+    """Fill ``pfd_decode_args`` from torch tensors (device buffers)."""
+    a = DecodeArgs()
+    a.struct_size = C.sizeof(DecodeArgs)
+    a.flags = flags
+    a.batch, a.num_q_heads, a.head_dim = query.shape
+    a.num_kv_heads = key_cache.shape[2]
+    a.page_size = key_cache.shape[1]
+    a.max_seq_len = int(max_seq_len)
+    a.split_size = int(split_size)
+    a.kv_start = int(kv_start)
+    a.query_dtype = _dtype_code(query.dtype)
+    a.sm_scale = float(sm_scale)
+    a.query = query.data_ptr()
+    a.q_stride_b, a.q_stride_h = query.stride(0), query.stride(1)
+    a.key_cache, a.value_cache = key_cache.data_ptr(), value_cache.data_ptr()
+    a.num_pages = key_cache.shape[0]
+    a.k_stride_page, a.k_stride_token, a.k_stride_head = key_cache.stride()[:3]
+    a.v_stride_page, a.v_stride_token, a.v_stride_head = value_cache.stride()[:3]
+    a.block_table = block_table.data_ptr()
+    a.bt_stride_b = block_table.stride(0)
+    a.seq_lens = seq_lens.data_ptr()
+    if isinstance(k_scale, torch.Tensor):
+        a.k_scale_per_head = k_scale.data_ptr()
+    else:
+        a.k_scale = float(k_scale)
+    if isinstance(v_scale, torch.Tensor):
+        a.v_scale_per_head = v_scale.data_ptr()
+    else:
+        a.v_scale = float(v_scale)
+    if workspace is not None:
+        po, pm, ps = workspace[:3]
+        a.partial_output, a.partial_max, a.partial_sum = po.data_ptr(), pm.data_ptr(), ps.data_ptr()
+        a.partial_dtype = _dtype_code(po.dtype)
+        a.partial_stride_b, a.partial_stride_h, a.partial_stride_s = pm.stride()
+        a.workspace_splits = po.shape[2]
+    if output is not None:
+        a.output = output.data_ptr()
+        a.o_stride_b, a.o_stride_h = output.stride(0), output.stride(1)
+    if packed_output is not None:
+        a.packed_output = packed_output.data_ptr()
+    a.stream = _stream(query)
+    return a
+
+
+def paged_decode_fp8_e4m3_split_out(query, key_cache, value_cache, block_table, seq_lens, **kw) -> None:
+    """One layer-step through ``pfd_paged_decode_fp8_e4m3_split_out``; see ``decode_args``."""
+    args = decode_args(query, key_cache, value_cache, block_table, seq_lens, **kw)
+    with torch.cuda.device(query.device):
+        _check(load().pfd_paged_decode_fp8_e4m3_split_out(C.byref(args)))
+
+
+def merge_packed(packed: torch.Tensor, output: torch.Tensor) -> None:
+    parts, batch, heads, dp2 = packed.shape
+    with torch.cuda.device(packed.device):
+        _check(load().pfd_merge_packed(packed.data_ptr(), parts, batch * heads, dp2 - 2, output.data_ptr(),
+                                       _dtype_code(output.dtype), _stream(packed)))
+
+
+def resolve_slots(block_table: torch.Tensor, seq_lens: torch.Tensor, max_seq_len: int) -> torch.Tensor:
+    slots = torch.empty(block_table.shape[0], max_seq_len, dtype=torch.int64, device=block_table.device)
+    with torch.cuda.device(block_table.device):
+        _check(load().pfd_resolve_slots(block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(),
+                                        block_table.shape[0], max_seq_len, slots.data_ptr(), _stream(block_table)))
+    return slots
+
+
+def launch_count() -> int:
+    return int(load().pfd_launch_count())

@@ -1,0 +1,526 @@
+// Device code of the paged FP8-e4m3 KV GQA decode-attention path for sm_100a.
+//
+// Work item = (KV split, kv head, sequence).  All g = Hq/Hkv query heads of the group are
+// rows of one 16-row MMA tile, so every K/V byte is fetched once per group (the reference
+// kernels launch one program per *query* head and re-read the cache g times:
+// integrations/vllm/cuda/l20_paged_decode.cu:308-311, l20_paged_split_kv.py:164-168).
+//
+// Per warp and per 16-token page:
+//   S = Q K^T   : mma.sync.m16n8k16 f16 -> f32.  e4m3 -> f16 is exact (cvt.rn.f16x2.e4m3x2);
+//                 a dot product does not care about the order of d, so Q's A-fragments are
+//                 permuted once such that every thread's natural 16-byte K load *is* its
+//                 B-fragment.  k_scale * sm_scale * log2(e) is applied to the 8 scores, not
+//                 to the bytes.
+//   online softmax in fp32 (exp2), row max over the quad with two shuffles.
+//   O += P V    : same MMA; the token-pair interleave V needs is two byte permutes per word.
+// Warps of a CTA take pages round-robin and never synchronise inside the loop; they merge
+// their (m, l, O) once at the end through shared memory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace pfd {
+
+constexpr int kPage = 16;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct KernelParams {
+  const void* __restrict__ query;
+  const uint8_t* __restrict__ key_cache;
+  const uint8_t* __restrict__ value_cache;
+  const int32_t* __restrict__ block_table;
+  const int32_t* __restrict__ seq_lens;
+  const float* __restrict__ k_scale_ph;
+  const float* __restrict__ v_scale_ph;
+  void* partial_output;
+  float* partial_max;
+  float* partial_sum;
+  void* output;
+  float* packed_output;
+  int64_t q_stride_b, q_stride_h;
+  int64_t k_stride_page, k_stride_token, k_stride_head;
+  int64_t v_stride_page, v_stride_token, v_stride_head;
+  int64_t bt_stride_b;
+  int64_t partial_stride_b, partial_stride_h, partial_stride_s;
+  int64_t o_stride_b, o_stride_h;
+  float k_scale, v_scale, sm_scale;
+  int32_t num_q_heads, num_kv_heads, group;
+  int32_t split_size, kv_start;
+  int32_t partial_dtype;
+  int32_t direct_out;  // 1: a sequence with a single split writes its final result itself
+};
+
+// The one address function every kernel uses for "which cache slot holds token t of
+// sequence b".  Returns the physical page; the slot is page * 16 + t % 16.
+__device__ __forceinline__ int32_t page_of(const int32_t* __restrict__ block_table,
+                                           int64_t bt_stride_b, int b, int logical_page) {
+  return __ldg(block_table + (int64_t)b * bt_stride_b + logical_page);
+}
+
+__device__ __forceinline__ uint32_t cvt_e4m3x2_to_f16x2(uint32_t two_bytes) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"((uint16_t)two_bytes));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
+__device__ __forceinline__ void mma_m16n8k16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                             uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ldg_nc_16(const uint8_t* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ldg_nc_8(const uint8_t* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
+// Register image of one (page, kv head) tile as the MMA fragments want it.
+//   K: thread (i = lane/4, j = lane%4) holds bytes [16*(j+4l), +16) of rows i and i+8.
+//   V: the same thread holds bytes [CB*i, +CB) (CB = D/8) of rows 2j, 2j+1, 2j+8, 2j+9.
+template <int D>
+struct TileRegs {
+  static constexpr int KL = D / 64;  // 16-byte K chunks per thread per row
+  static constexpr int VW = D / 32;  // 32-bit V words per thread per row
+  uint32_t k[2][KL][4];
+  uint32_t v[4][VW];
+};
+
+template <int D>
+__device__ __forceinline__ void load_tile_global(TileRegs<D>& t, const uint8_t* kpage,
+                                                 const uint8_t* vpage, int64_t kst, int64_t vst,
+                                                 int i, int j) {
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+    for (int l = 0; l < TileRegs<D>::KL; ++l) {
+      uint4 x = ldg_nc_16(kpage + (int64_t)(nt * 8 + i) * kst + 16 * (j + 4 * l));
+      t.k[nt][l][0] = x.x; t.k[nt][l][1] = x.y; t.k[nt][l][2] = x.z; t.k[nt][l][3] = x.w;
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int row = 2 * j + (r & 1) + 8 * (r >> 1);
+    const uint8_t* p = vpage + (int64_t)row * vst + (D / 8) * i;
+    if constexpr (D == 128) {
+      uint4 x = ldg_nc_16(p);
+      t.v[r][0] = x.x; t.v[r][1] = x.y; t.v[r][2] = x.z; t.v[r][3] = x.w;
+    } else {
+      uint2 x = ldg_nc_8(p);
+      t.v[r][0] = x.x; t.v[r][1] = x.y;
+    }
+  }
+}
+
+// Per-warp running state: rows i (index 0) and i+8 (index 1) of the 16-row head tile.
+template <int D>
+struct WarpState {
+  float o[D / 8][4];  // n-tile m covers d = 32j + 16e + m (D=128) / 16j + 8e + m (D=64)
+  float m[2];         // running max, log2 domain
+  float l[2];         // running sum, this thread's columns only (quad-reduced at the end)
+};
+
+// One 16-token tile.  tok0 = global token index of row 0; tokens outside [lo, hi) are masked.
+template <int D>
+__device__ __forceinline__ void consume_tile(WarpState<D>& st, TileRegs<D>& t,
+                                             const uint32_t (&qa)[D / 16][4], float scale_log2,
+                                             int tok0, int lo, int hi, int j) {
+  constexpr int KL = TileRegs<D>::KL;
+  constexpr int VW = TileRegs<D>::VW;
+  float s[2][4];
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int l = 0; l < KL; ++l) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t word = t.k[nt][l][w];
+        mma_m16n8k16(s[nt], qa[l * 4 + w], cvt_e4m3x2_to_f16x2(word),
+                     cvt_e4m3x2_to_f16x2(word >> 16));
+      }
+    }
+  }
+  const bool edge = (tok0 < lo) | (tok0 + kPage > hi);
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      float x = s[nt][c] * scale_log2;
+      if (edge) {
+        const int tok = tok0 + nt * 8 + 2 * j + (c & 1);
+        if (tok < lo || tok >= hi) x = -INFINITY;
+      }
+      s[nt][c] = x;
+    }
+  }
+  if (edge) {
+    // Bytes of tokens outside the range may be anything (NaN patterns included) and
+    // 0 * NaN would poison the accumulator: zero them, as the reference's masked loads do.
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int tok = tok0 + 2 * j + (r & 1) + 8 * (r >> 1);
+      if (tok < lo || tok >= hi) {
+#pragma unroll
+        for (int w = 0; w < VW; ++w) t.v[r][w] = 0u;
+      }
+    }
+  }
+  float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+  float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+  const float mn0 = fmaxf(st.m[0], mx0);
+  const float mn1 = fmaxf(st.m[1], mx1);
+  const float alpha0 = exp2f(st.m[0] - mn0);
+  const float alpha1 = exp2f(st.m[1] - mn1);
+  st.m[0] = mn0;
+  st.m[1] = mn1;
+  float p[2][4];
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt) {
+    p[nt][0] = exp2f(s[nt][0] - mn0);
+    p[nt][1] = exp2f(s[nt][1] - mn0);
+    p[nt][2] = exp2f(s[nt][2] - mn1);
+    p[nt][3] = exp2f(s[nt][3] - mn1);
+  }
+  st.l[0] = st.l[0] * alpha0 + ((p[0][0] + p[0][1]) + (p[1][0] + p[1][1]));
+  st.l[1] = st.l[1] * alpha1 + ((p[0][2] + p[0][3]) + (p[1][2] + p[1][3]));
+  uint32_t pa[4];
+  pa[0] = pack_f16x2(p[0][0], p[0][1]);
+  pa[1] = pack_f16x2(p[0][2], p[0][3]);
+  pa[2] = pack_f16x2(p[1][0], p[1][1]);
+  pa[3] = pack_f16x2(p[1][2], p[1][3]);
+#pragma unroll
+  for (int m = 0; m < D / 8; ++m) {
+    st.o[m][0] *= alpha0; st.o[m][1] *= alpha0;
+    st.o[m][2] *= alpha1; st.o[m][3] *= alpha1;
+  }
+#pragma unroll
+  for (int w = 0; w < VW; ++w) {
+    // rows (2j, 2j+1) and (2j+8, 2j+9): interleave token pairs byte-wise
+    const uint32_t x01 = prmt(t.v[0][w], t.v[1][w], 0x5140u);
+    const uint32_t y01 = prmt(t.v[0][w], t.v[1][w], 0x7362u);
+    const uint32_t x23 = prmt(t.v[2][w], t.v[3][w], 0x5140u);
+    const uint32_t y23 = prmt(t.v[2][w], t.v[3][w], 0x7362u);
+    mma_m16n8k16(st.o[4 * w + 0], pa, cvt_e4m3x2_to_f16x2(x01), cvt_e4m3x2_to_f16x2(x23));
+    mma_m16n8k16(st.o[4 * w + 1], pa, cvt_e4m3x2_to_f16x2(x01 >> 16), cvt_e4m3x2_to_f16x2(x23 >> 16));
+    mma_m16n8k16(st.o[4 * w + 2], pa, cvt_e4m3x2_to_f16x2(y01), cvt_e4m3x2_to_f16x2(y23));
+    mma_m16n8k16(st.o[4 * w + 3], pa, cvt_e4m3x2_to_f16x2(y01 >> 16), cvt_e4m3x2_to_f16x2(y23 >> 16));
+  }
+}
+
+// Q rows i and i+8 of the kv head's group as f16 A-fragments, d permuted to match the K loads:
+// k-step ks = 4l + w covers d = 16*(j+4l) + 4w + {0,1 | 2,3}.
+template <int D, bool QBF16>
+__device__ __forceinline__ void load_q_frags(uint32_t (&qa)[D / 16][4], const KernelParams& p, int b,
+                                             int kvh, int i, int j) {
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int row = i + 8 * half;
+    const bool live = row < p.group;
+    const uint16_t* q = reinterpret_cast<const uint16_t*>(p.query) + (int64_t)b * p.q_stride_b +
+                        (int64_t)(kvh * p.group + (live ? row : 0)) * p.q_stride_h;
+#pragma unroll
+    for (int l = 0; l < D / 64; ++l) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        uint2 raw = make_uint2(0u, 0u);
+        if (live) raw = *reinterpret_cast<const uint2*>(q + 16 * (j + 4 * l) + 4 * w);
+        uint32_t lo = raw.x, hi = raw.y;
+        if constexpr (QBF16) {
+          const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+          const __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+          lo = pack_f16x2(__bfloat162float(a.x), __bfloat162float(a.y));
+          hi = pack_f16x2(__bfloat162float(c.x), __bfloat162float(c.y));
+        }
+        qa[l * 4 + w][half] = lo;       // a0 / a1 : k = 2j, 2j+1
+        qa[l * 4 + w][2 + half] = hi;   // a2 / a3 : k = 2j+8, 2j+9
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void store_partial_elem4(void* base, int dtype, int64_t idx, float4 v) {
+  if (dtype == 0) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + idx) = v;
+  } else if (dtype == 1) {
+    __half2 a = __floats2half2_rn(v.x, v.y), c = __floats2half2_rn(v.z, v.w);
+    uint2 u = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&c));
+    *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(base) + idx) = u;
+  } else {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), c = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u = make_uint2(*reinterpret_cast<uint32_t*>(&a), *reinterpret_cast<uint32_t*>(&c));
+    *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(base) + idx) = u;
+  }
+}
+
+__device__ __forceinline__ float load_partial_elem(const void* base, int dtype, int64_t idx) {
+  if (dtype == 0) return reinterpret_cast<const float*>(base)[idx];
+  if (dtype == 1) return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+  return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+}
+
+template <bool BF16>
+__device__ __forceinline__ void store_out_elem4(void* base, int64_t idx, float4 v) {
+  store_partial_elem4(base, BF16 ? 2 : 1, idx, v);
+}
+
+// Cross-warp merge + store, shared by the global-load and the TMA kernels.
+//   sm_m/sm_l : [NWARPS][16], sm_o : [NWARPS][16][D] floats.
+template <int D, bool QBF16, int NWARPS>
+__device__ __forceinline__ void cta_merge_and_store(WarpState<D>& st, const KernelParams& p, int b,
+                                                    int kvh, int split, int nsplits_seq,
+                                                    float v_scale, float* sm_m, float* sm_l,
+                                                    float* sm_o) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 1);
+    st.l[h] += __shfl_xor_sync(0xffffffffu, st.l[h], 2);
+  }
+  if (j == 0) {
+    sm_m[warp * 16 + i] = st.m[0];
+    sm_m[warp * 16 + i + 8] = st.m[1];
+  }
+  __syncthreads();
+  float big[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int w = 0; w < NWARPS; ++w) {
+    big[0] = fmaxf(big[0], sm_m[w * 16 + i]);
+    big[1] = fmaxf(big[1], sm_m[w * 16 + i + 8]);
+  }
+  // a warp that saw no tile has m = -inf, l = 0, o = 0: factor 0
+  const float f0 = (st.m[0] == -INFINITY) ? 0.f : exp2f(st.m[0] - big[0]);
+  const float f1 = (st.m[1] == -INFINITY) ? 0.f : exp2f(st.m[1] - big[1]);
+  if (j == 0) {
+    sm_l[warp * 16 + i] = st.l[0] * f0;
+    sm_l[warp * 16 + i + 8] = st.l[1] * f1;
+  }
+  constexpr int CB = D / 8;
+#pragma unroll
+  for (int m = 0; m < CB; ++m) {
+    // c0,c1 -> cols 2j, 2j+1 of n-tile m -> d = CB*(2j+e) + m
+    sm_o[(warp * 16 + i) * D + CB * (2 * j) + m] = st.o[m][0] * f0;
+    sm_o[(warp * 16 + i) * D + CB * (2 * j + 1) + m] = st.o[m][1] * f0;
+    sm_o[(warp * 16 + i + 8) * D + CB * (2 * j) + m] = st.o[m][2] * f1;
+    sm_o[(warp * 16 + i + 8) * D + CB * (2 * j + 1) + m] = st.o[m][3] * f1;
+  }
+  __syncthreads();
+  const bool direct = p.direct_out && nsplits_seq == 1;
+  // g rows x D columns, 4 columns per thread-iteration
+  for (int e = threadIdx.x; e < p.group * (D / 4); e += NWARPS * 32) {
+    const int row = e / (D / 4), c4 = (e % (D / 4)) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) {
+      const float4 x = *reinterpret_cast<const float4*>(sm_o + (w * 16 + row) * D + c4);
+      acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+      lsum += sm_l[w * 16 + row];
+    }
+    float big_row = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NWARPS; ++w) big_row = fmaxf(big_row, sm_m[w * 16 + row]);
+    acc.x *= v_scale; acc.y *= v_scale; acc.z *= v_scale; acc.w *= v_scale;
+    const int hq = kvh * p.group + row;
+    if (direct) {
+      if (p.packed_output != nullptr) {
+        float* dst = p.packed_output + ((int64_t)b * p.num_q_heads + hq) * (D + 2);
+        dst[c4] = acc.x; dst[c4 + 1] = acc.y; dst[c4 + 2] = acc.z; dst[c4 + 3] = acc.w;
+        if (c4 == 0) { dst[D] = big_row * kLn2; dst[D + 1] = lsum; }
+      } else {
+        const float inv = 1.f / lsum;
+        acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+        store_out_elem4<QBF16>(p.output, (int64_t)b * p.o_stride_b + (int64_t)hq * p.o_stride_h + c4, acc);
+      }
+    } else {
+      const int64_t pidx = (int64_t)b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h +
+                           (int64_t)split * p.partial_stride_s;
+      store_partial_elem4(p.partial_output, p.partial_dtype, pidx * D + c4, acc);
+      if (c4 == 0) {
+        p.partial_max[pidx] = big_row * kLn2;
+        p.partial_sum[pidx] = lsum;
+      }
+    }
+  }
+}
+
+// Split-KV partial kernel, plain global loads (any 16-byte-aligned strides).
+// grid = (splits, kv heads, sequences), block = NWARPS * 32.
+template <int D, bool QBF16, int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32)
+paged_decode_fp8_partial_ldg_kernel(const KernelParams p) {
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int seq_len = p.seq_lens[b];
+  const int lo = p.kv_start + split * p.split_size;
+  const int hi = min(lo + p.split_size, seq_len);
+  if (lo >= hi) return;  // the merge kernel derives the live split count from seq_len
+  const int nsplits_seq = (seq_len - p.kv_start + p.split_size - 1) / p.split_size;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
+
+  __shared__ float sm_m[NWARPS * 16];
+  __shared__ float sm_l[NWARPS * 16];
+  __shared__ __align__(16) float sm_o[NWARPS * 16 * D];
+
+  uint32_t qa[D / 16][4];
+  load_q_frags<D, QBF16>(qa, p, b, kvh, i, j);
+  const float ks = p.k_scale_ph ? __ldg(p.k_scale_ph + kvh) : p.k_scale;
+  const float vs = p.v_scale_ph ? __ldg(p.v_scale_ph + kvh) : p.v_scale;
+  const float scale_log2 = ks * p.sm_scale * kLog2e;
+
+  WarpState<D> st;
+#pragma unroll
+  for (int m = 0; m < D / 8; ++m) st.o[m][0] = st.o[m][1] = st.o[m][2] = st.o[m][3] = 0.f;
+  st.m[0] = st.m[1] = -INFINITY;
+  st.l[0] = st.l[1] = 0.f;
+
+  const int page_first = lo / kPage, page_last = (hi - 1) / kPage;
+  const uint8_t* kbase = p.key_cache + (int64_t)kvh * p.k_stride_head;
+  const uint8_t* vbase = p.value_cache + (int64_t)kvh * p.v_stride_head;
+
+  TileRegs<D> cur, nxt;
+  int pg = page_first + warp;
+  if (pg <= page_last) {
+    const int64_t phys = page_of(p.block_table, p.bt_stride_b, b, pg);
+    load_tile_global<D>(cur, kbase + phys * p.k_stride_page, vbase + phys * p.v_stride_page,
+                        p.k_stride_token, p.v_stride_token, i, j);
+  }
+  for (; pg <= page_last; pg += NWARPS) {
+    const int pn = pg + NWARPS;
+    if (pn <= page_last) {
+      const int64_t phys = page_of(p.block_table, p.bt_stride_b, b, pn);
+      load_tile_global<D>(nxt, kbase + phys * p.k_stride_page, vbase + phys * p.v_stride_page,
+                          p.k_stride_token, p.v_stride_token, i, j);
+    }
+    consume_tile<D>(st, cur, qa, scale_log2, pg * kPage, lo, hi, j);
+    cur = nxt;
+  }
+  cta_merge_and_store<D, QBF16, NWARPS>(st, p, b, kvh, split, nsplits_seq, vs, sm_m, sm_l, sm_o);
+}
+
+// LSE merge over the live splits of each (sequence, q head); one warp per row.
+// Same maths as _paged_split_kv_reduce (integrations/vllm/l20_paged_split_kv.py:459-488).
+template <int D, bool QBF16>
+__global__ void __launch_bounds__(128)
+paged_decode_merge_kernel(const KernelParams p, int batch) {
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= batch * p.num_q_heads) return;
+  const int b = row / p.num_q_heads, hq = row % p.num_q_heads;
+  const int seq_len = p.seq_lens[b];
+  const int live = seq_len - p.kv_start;
+  const int ns = live > 0 ? (live + p.split_size - 1) / p.split_size : 0;
+  constexpr int E = D / 32;  // elements per lane
+  float acc[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) acc[e] = 0.f;
+  float big = -INFINITY, den = 0.f;
+  if (ns == 1 && p.direct_out) return;  // written by the partial kernel
+  if (ns > 0) {
+    const int64_t base = (int64_t)b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h;
+    for (int s = lane; s < ns; s += 32) big = fmaxf(big, p.partial_max[base + s * p.partial_stride_s]);
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
+    for (int s = 0; s < ns; ++s) {
+      const int64_t pidx = base + s * p.partial_stride_s;
+      const float c = expf(p.partial_max[pidx] - big);
+      den += p.partial_sum[pidx] * c;
+#pragma unroll
+      for (int e = 0; e < E; ++e)
+        acc[e] += c * load_partial_elem(p.partial_output, p.partial_dtype, pidx * D + lane * E + e);
+    }
+  }
+  if (p.packed_output != nullptr) {
+    float* dst = p.packed_output + (int64_t)row * (D + 2);
+#pragma unroll
+    for (int e = 0; e < E; ++e) dst[lane * E + e] = acc[e];
+    if (lane == 0) { dst[D] = big; dst[D + 1] = den; }
+    return;
+  }
+  const float inv = ns > 0 ? 1.f / den : 0.f;
+  const int64_t oidx = (int64_t)b * p.o_stride_b + (int64_t)hq * p.o_stride_h + lane * E;
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const float v = acc[e] * inv;
+    if constexpr (QBF16) reinterpret_cast<__nv_bfloat16*>(p.output)[oidx + e] = __float2bfloat16_rn(v);
+    else reinterpret_cast<__half*>(p.output)[oidx + e] = __float2half_rn(v);
+  }
+}
+
+// Merge of packed partials [parts, rows, D+2] (o, m, l) -> output [rows, D]; one warp per row.
+template <int D>
+__global__ void __launch_bounds__(128)
+merge_packed_kernel(const float* __restrict__ packed, int parts, int64_t rows, void* output,
+                    int out_dtype) {
+  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  constexpr int E = D / 32;
+  float big = -INFINITY;
+  for (int s = lane; s < parts; s += 32) big = fmaxf(big, packed[((int64_t)s * rows + row) * (D + 2) + D]);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
+  float acc[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) acc[e] = 0.f;
+  float den = 0.f;
+  for (int s = 0; s < parts; ++s) {
+    const float* src = packed + ((int64_t)s * rows + row) * (D + 2);
+    const float m = src[D];
+    const float c = (m == -INFINITY) ? 0.f : expf(m - big);
+    den += src[D + 1] * c;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] += c * src[lane * E + e];
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const float v = acc[e] * inv;
+    const int64_t idx = row * D + lane * E + e;
+    if (out_dtype == 0) reinterpret_cast<float*>(output)[idx] = v;
+    else if (out_dtype == 1) reinterpret_cast<__half*>(output)[idx] = __float2half_rn(v);
+    else reinterpret_cast<__nv_bfloat16*>(output)[idx] = __float2bfloat16_rn(v);
+  }
+}
+
+__global__ void resolve_slots_kernel(const int32_t* __restrict__ block_table, int64_t bt_stride_b,
+                                     const int32_t* __restrict__ seq_lens, int max_seq_len,
+                                     int64_t* __restrict__ slots) {
+  const int b = blockIdx.y;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= max_seq_len) return;
+  int64_t slot = -1;
+  if (t < seq_lens[b]) slot = (int64_t)page_of(block_table, bt_stride_b, b, t / kPage) * kPage + t % kPage;
+  slots[(int64_t)b * max_seq_len + t] = slot;
+}
+
+}  // namespace pfd

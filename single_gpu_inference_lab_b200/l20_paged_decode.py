@@ -1,0 +1,160 @@
+"""Dispatcher-backed entry points of the B200 paged-decode operator.
+
+Mirror of the reference wrapper module integrations/vllm/l20_paged_decode.py: the library
+sits next to this file as ``l20_paged_decode_ops.so`` and is loaded at import (:11-17,
+:116-117), the wrappers forward to ``torch.ops.l20_stack.*`` (:48-77) and fake (meta)
+implementations are registered for tracing (:80-113).  A missing library is an error: there
+is no eager or CPU fallback.
+"""
+
+from __future__ import annotations
+
+from pathlib import Path
+from typing import Optional, Union
+
+import torch
+
+_LOADED = False
+
+
+def load_library(path: Optional[Union[str, Path]] = None) -> None:
+    global _LOADED
+    library = (
+        Path(path)
+        if path is not None
+        else Path(__file__).with_name("l20_paged_decode_ops.so")
+    )
+    if not library.exists():
+        raise RuntimeError(
+            f"{library} is missing (build it with `python -m single_gpu_inference_lab_b200.build`); "
+            "the paged FP8 decode operator has no fallback implementation"
+        )
+    torch.ops.load_library(str(library))
+    _LOADED = True
+
+
+def paged_decode_fp8_e4m3_split_out(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    partial_output: torch.Tensor,
+    partial_max: torch.Tensor,
+    partial_sum: torch.Tensor,
+    output: torch.Tensor,
+    k_scale: float,
+    v_scale: float,
+    max_seq_len: int,
+    split_size: int,
+) -> torch.Tensor:
+    """Same call as the reference wrapper (l20_paged_decode.py:48-77); returns ``output``."""
+    return torch.ops.l20_stack.paged_decode_fp8_e4m3_split_out(
+        query,
+        key_cache,
+        value_cache,
+        block_table,
+        seq_lens,
+        partial_output,
+        partial_max,
+        partial_sum,
+        output,
+        float(k_scale),
+        float(v_scale),
+        max_seq_len,
+        split_size,
+    )
+
+
+def paged_decode_fp8_e4m3_split_out_v2(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    partial_output: Optional[torch.Tensor],
+    partial_max: Optional[torch.Tensor],
+    partial_sum: Optional[torch.Tensor],
+    output: Optional[torch.Tensor],
+    k_scale: torch.Tensor,
+    v_scale: torch.Tensor,
+    max_seq_len: int,
+    split_size: int,
+    *,
+    packed_output: Optional[torch.Tensor] = None,
+    sm_scale: float = 0.0,
+    kv_start: int = 0,
+    flags: int = 0,
+) -> Optional[torch.Tensor]:
+    """Superset op: ``[Hkv]`` scale tensors (per layer and kv head), explicit softmax scale
+    (0 = ``D**-0.5``), first attended token ``kv_start`` and, instead of or besides
+    ``output``, a packed fp32 ``[B, Hq, D + 2]`` ``(o, m, l)`` for cross-GPU merging."""
+    torch.ops.l20_stack.paged_decode_fp8_e4m3_split_out_v2(
+        query,
+        key_cache,
+        value_cache,
+        block_table,
+        seq_lens,
+        partial_output,
+        partial_max,
+        partial_sum,
+        output,
+        packed_output,
+        k_scale,
+        v_scale,
+        float(sm_scale),
+        max_seq_len,
+        split_size,
+        kv_start,
+        flags,
+    )
+    return output
+
+
+def merge_packed_partials(packed: torch.Tensor, output: torch.Tensor) -> torch.Tensor:
+    """LSE-merge ``[parts, B, Hq, D + 2]`` packed partials into ``output [B, Hq, D]``."""
+    torch.ops.l20_stack.merge_packed_partials(packed, output)
+    return output
+
+
+def resolve_slots(block_table: torch.Tensor, seq_lens: torch.Tensor, max_seq_len: int) -> torch.Tensor:
+    """Cache slot (``page * 16 + offset``) the kernels resolve per (sequence, token); -1 past the end."""
+    slots = torch.empty(block_table.shape[0], max_seq_len, dtype=torch.int64, device=block_table.device)
+    torch.ops.l20_stack.resolve_slots(block_table, seq_lens, slots)
+    return slots
+
+
+def _register_fake() -> None:
+    @torch.library.register_fake("l20_stack::paged_decode_fp8_e4m3_split_out")
+    def _paged_decode_fp8_e4m3_split_out_fake(
+        query,
+        key_cache,
+        value_cache,
+        block_table,
+        seq_lens,
+        partial_output,
+        partial_max,
+        partial_sum,
+        output,
+        k_scale,
+        v_scale,
+        max_seq_len,
+        split_size,
+    ):
+        return output
+
+    @torch.library.register_fake("l20_stack::paged_decode_fp8_e4m3_split_out_v2")
+    def _paged_decode_fp8_e4m3_split_out_v2_fake(*args):
+        return None
+
+    @torch.library.register_fake("l20_stack::merge_packed_partials")
+    def _merge_packed_partials_fake(packed, output):
+        return None
+
+    @torch.library.register_fake("l20_stack::resolve_slots")
+    def _resolve_slots_fake(block_table, seq_lens, slots):
+        return None
+
+
+load_library()
+_register_fake()

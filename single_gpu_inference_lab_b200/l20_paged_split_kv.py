@@ -1,0 +1,142 @@
+"""Paged split-KV GQA decode attention over an FP8-e4m3 KV cache, B200 build.
+
+Same public surface as the module the reference's vLLM hook copies into
+``vllm/v1/attention/ops/`` (integrations/vllm/l20_paged_split_kv.py):
+
+* ``allocate_l20_paged_split_kv_workspace(query, max_seq_len, *, split_size=512)``  (:14-30)
+* ``l20_paged_split_kv_attention_fp8(query, key_cache, value_cache, block_table, seq_lens, *,
+  k_scale, v_scale, max_seq_len=None, split_size=512, output=None, workspace=None)`` (:597-695)
+* ``should_use_l20_paged_fp8_split_kv(batch, max_seq_len)``                          (:705-709)
+
+with the same ``RuntimeError`` texts where the condition still exists.  Differences, all
+supersets: bf16 or fp16 queries, head_dim 64 or 128, any number of splits (the reference
+stops at 16, :635-636), ``k_scale`` / ``v_scale`` either floats or ``[Hkv]`` float32 tensors,
+fp32 partials (the reference keeps partial sums in the query dtype, :24-26), strided caches in
+any (page, token, head) order.  The two Triton launches are replaced by one call of the
+``l20_stack`` CUDA operator; there is no Triton, FlashInfer or CPU path behind it.
+"""
+
+from __future__ import annotations
+
+import torch
+
+REQUIRED_CAPABILITY = (10, 0)
+
+
+def _next_power_of_two(value: int) -> int:
+    return 1 << (max(int(value), 1) - 1).bit_length()
+
+
+def _cdiv(a: int, b: int) -> int:
+    return -(-int(a) // int(b))
+
+
+def _ops():
+    from . import l20_paged_decode  # loads l20_paged_decode_ops.so or raises
+
+    return l20_paged_decode
+
+
+def allocate_l20_paged_split_kv_workspace(
+    query: torch.Tensor,
+    max_seq_len: int,
+    *,
+    split_size: int = 512,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``(partial_output [B,Hq,S,D] f32, partial_max [B,Hq,S] f32, partial_sum, output)`` with
+    ``S = next_pow2(ceil(max_seq_len / split_size))`` as in the reference (:21-22)."""
+    batch, num_q_heads, head_dim = query.shape
+    num_splits = _next_power_of_two(_cdiv(max_seq_len, split_size))
+    partial_shape = (batch, num_q_heads, num_splits)
+    return (
+        torch.empty((*partial_shape, head_dim), device=query.device, dtype=torch.float32),
+        torch.empty(partial_shape, device=query.device, dtype=torch.float32),
+        torch.empty(partial_shape, device=query.device, dtype=torch.float32),
+        torch.empty_like(query),
+    )
+
+
+def choose_split_size(batch: int, num_kv_heads: int, max_seq_len: int, *, sm_count: int = 148,
+                      ctas_per_sm: int = 3, minimum: int = 128, maximum: int = 2048) -> int:
+    """Split size (multiple of 16) that yields roughly ``sm_count * ctas_per_sm`` CTAs for
+    ``batch * num_kv_heads`` (sequence, kv head) pairs of length ``max_seq_len``.  Host-only
+    arithmetic on values the caller already has; no device read."""
+    pairs = max(1, batch * num_kv_heads)
+    want_splits = max(1, _cdiv(sm_count * ctas_per_sm, pairs))
+    split = _cdiv(_cdiv(max(max_seq_len, 1), want_splits), 16) * 16
+    return int(min(max(split, minimum), maximum))
+
+
+def l20_paged_split_kv_attention_fp8(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    *,
+    k_scale: float | torch.Tensor,
+    v_scale: float | torch.Tensor,
+    max_seq_len: int | None = None,
+    split_size: int = 512,
+    output: torch.Tensor | None = None,
+    workspace: tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
+) -> torch.Tensor:
+    if not query.is_cuda or torch.cuda.get_device_capability(query.device) != REQUIRED_CAPABILITY:
+        raise RuntimeError("requires an SM100 GPU")
+    if query.ndim != 3 or key_cache.ndim != 4 or value_cache.shape != key_cache.shape:
+        raise RuntimeError("expected Q=[B,H,D], cache=[pages,page,Hkv,D]")
+    if key_cache.dtype != torch.float8_e4m3fn or value_cache.dtype != key_cache.dtype:
+        raise RuntimeError("key/value cache must use torch.float8_e4m3fn")
+    batch, num_q_heads, head_dim = query.shape
+    _, page_size, num_kv_heads, cache_dim = key_cache.shape
+    if (
+        head_dim not in (64, 128)
+        or cache_dim != head_dim
+        or page_size != 16
+        or num_q_heads % num_kv_heads
+        or num_q_heads // num_kv_heads > 16
+        or block_table.shape[0] != batch
+        or seq_lens.numel() != batch
+    ):
+        raise RuntimeError("requires compatible head_dim=64/128 GQA tensors")
+    if max_seq_len is None:
+        max_seq_len = int(seq_lens.max().item())
+    num_splits = _next_power_of_two(_cdiv(max_seq_len, split_size))
+    partial_shape = (batch, num_q_heads, num_splits)
+    if workspace is None:
+        workspace = allocate_l20_paged_split_kv_workspace(query, max_seq_len, split_size=split_size)
+    partial_output, partial_max, partial_sum, workspace_output = workspace
+    if output is None:
+        output = workspace_output
+    if (
+        partial_output.shape != (*partial_shape, head_dim)
+        or partial_max.shape != partial_shape
+        or partial_sum.shape != partial_shape
+        or output.shape != query.shape
+    ):
+        raise RuntimeError("paged split-KV workspace shape does not match the request")
+    ops = _ops()
+    if isinstance(k_scale, torch.Tensor) or isinstance(v_scale, torch.Tensor):
+        def as_vec(s):
+            if isinstance(s, torch.Tensor):
+                return s.to(device=query.device, dtype=torch.float32).reshape(-1).expand(num_kv_heads).contiguous()
+            return torch.full((num_kv_heads,), float(s), device=query.device, dtype=torch.float32)
+
+        ops.paged_decode_fp8_e4m3_split_out_v2(
+            query, key_cache, value_cache, block_table, seq_lens,
+            partial_output, partial_max, partial_sum, output,
+            as_vec(k_scale), as_vec(v_scale), max_seq_len, split_size,
+        )
+        return output
+    return ops.paged_decode_fp8_e4m3_split_out(
+        query, key_cache, value_cache, block_table, seq_lens,
+        partial_output, partial_max, partial_sum, output,
+        float(k_scale), float(v_scale), max_seq_len, split_size,
+    )
+
+
+def should_use_l20_paged_fp8_split_kv(batch: int, max_seq_len: int) -> bool:
+    # Same policy as the reference (:705-709): production dispatch stays off until a serving
+    # A/B on the target GPU says otherwise; VLLM_L20_FP8_PAGED_FORCE=1 bypasses this.
+    del batch, max_seq_len
+    return False

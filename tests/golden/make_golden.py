@@ -1,0 +1,133 @@
+#!/usr/bin/env python3
+"""Generate the golden vectors that pin ``oracle/paged_decode_oracle.py``.
+
+Runs the reference project's OWN torch implementation of the path --
+``reference()`` and ``quantize_fp8_e4m3()`` of
+``scripts/smoke_cuda_paged_fp8_decode_op.py`` (:13-41), imported from its source tree
+(default ``/root/reference``, override with ``--reference-root``) -- on seeded CPU inputs and
+stores inputs digests + outputs in ``tests/golden/paged_decode_golden.pt``.
+
+The reference function hard-codes ``device="cuda"`` in one ``torch.arange`` call (:29); the
+only change made here is to strip that keyword while the function runs, so everything stays
+on the CPU.  Nothing of this file or of the reference tree is needed at test time: the
+fixtures travel, the reference does not.
+
+    python tests/golden/make_golden.py
+"""
+
+from __future__ import annotations
+
+import argparse
+import contextlib
+import hashlib
+import importlib.util
+import sys
+from pathlib import Path
+
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parents[1]
+sys.path.insert(0, str(ROOT))
+
+from single_gpu_inference_lab_b200.workloads import make_inputs  # noqa: E402
+
+CASES = [
+    # (case name, workload, batch override, shrink)
+    ("cfg1-qwen0.5b-b8", "qwen2.5-0.5b-b8", None, 1.0),
+    ("cfg2-coder3b-b4", "qwen2.5-coder-3b-b64", 4, 0.25),
+    ("cfg3-qwen7b-b24", "qwen2.5-7b-b256", 24, 0.125),
+    ("cfg4-llama8b-b2", "llama3-8b-long-b4", 2, 1.0 / 64),
+    ("cfg5-prefix-b8", "shared-prefix-b64", 8, 0.125),
+]
+
+
+def digest(*tensors: torch.Tensor) -> str:
+    h = hashlib.sha256()
+    for t in tensors:
+        t = t.detach().cpu().contiguous()
+        if t.dtype in (torch.float8_e4m3fn,):
+            t = t.view(torch.uint8)
+        elif t.dtype in (torch.bfloat16, torch.float16):
+            t = t.view(torch.int16)
+        h.update(t.numpy().tobytes())
+    return h.hexdigest()
+
+
+@contextlib.contextmanager
+def arange_on_cpu():
+    real = torch.arange
+
+    def shim(*args, **kwargs):
+        kwargs.pop("device", None)
+        return real(*args, **kwargs)
+
+    torch.arange = shim
+    try:
+        yield
+    finally:
+        torch.arange = real
+
+
+def load_reference(root: Path):
+    path = root / "scripts/smoke_cuda_paged_fp8_decode_op.py"
+    spec = importlib.util.spec_from_file_location("ref_smoke", path)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module
+
+
+def smoke_recipe(ref, batch: int, context: int, q_heads: int, kv_heads: int):
+    """The reference smoke's own input recipe (:71-88) on the CPU: seed 29, uniform context,
+    fp16 query, bf16 K/V quantised per tensor."""
+    torch.manual_seed(29)
+    pages_per_request = (context + 15) // 16
+    pages = batch * pages_per_request
+    table = torch.randperm(pages).to(torch.int32).reshape(batch, pages_per_request)
+    seq_lens = torch.full((batch,), context, dtype=torch.int32)
+    query = torch.randn(batch, q_heads, 128, dtype=torch.float16)
+    key_bf16 = torch.randn(pages, 16, kv_heads, 128, dtype=torch.bfloat16)
+    value_bf16 = torch.randn_like(key_bf16)
+    key_cache, k_scale = ref.quantize_fp8_e4m3(key_bf16)
+    value_cache, v_scale = ref.quantize_fp8_e4m3(value_bf16)
+    return query, key_cache, value_cache, table, seq_lens, k_scale, v_scale
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--reference-root", default="/root/reference")
+    args = parser.parse_args()
+    ref = load_reference(Path(args.reference_root))
+    golden: dict = {"torch": torch.__version__, "cases": {}, "smoke": {}}
+
+    for name, workload, batch, shrink in CASES:
+        w = make_inputs(workload, seed=0, device="cpu", batch=batch, shrink=shrink)
+        with arange_on_cpu():
+            out = ref.reference(
+                w.query, w.key_cache, w.value_cache, w.block_table.long(), w.seq_lens,
+                w.k_scale.reshape(1, 1, -1, 1), w.v_scale.reshape(1, 1, -1, 1),
+            )
+        golden["cases"][name] = dict(
+            workload=workload, batch=batch, shrink=shrink,
+            inputs_sha256=digest(w.query, w.key_cache, w.value_cache, w.block_table, w.seq_lens, w.k_scale, w.v_scale),
+            output=out.clone(),
+        )
+        print(name, tuple(out.shape), out.dtype, "tokens", int(w.seq_lens.sum()))
+
+    for batch, context, hq, hkv in [(1, 257, 16, 8), (3, 100, 16, 2), (2, 513, 32, 8)]:
+        q, kc, vc, table, lens, ks, vs = smoke_recipe(ref, batch, context, hq, hkv)
+        with arange_on_cpu():
+            out = ref.reference(q, kc, vc, table.long(), lens, ks, vs)
+        golden["smoke"][f"b{batch}-c{context}-q{hq}-kv{hkv}"] = dict(
+            batch=batch, context=context, q_heads=hq, kv_heads=hkv,
+            k_scale=ks, v_scale=vs, cache_sha256=digest(kc, vc), output=out.clone(),
+        )
+        print("smoke", batch, context, hq, hkv, ks, vs)
+
+    torch.save(golden, HERE / "paged_decode_golden.pt")
+    print("wrote", HERE / "paged_decode_golden.pt")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
