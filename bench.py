@@ -1,0 +1,379 @@
+#!/usr/bin/env python3
+"""Benchmark of the paged FP8-KV GQA decode-attention step on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One *step* is one decode-attention layer-step over one synthetic batch (partial kernel +
+LSE merge kernel).  Metric: KV bytes read per second (``sum_b ctx_b * Hkv * D * 2`` bytes per
+step), with microseconds per layer-step beside it.  One JSON line is printed by rank 0.
+
+* ``value``        device-resident operands, CUDA events around K back-to-back steps; successive
+                   steps use different KV pools so that every step reads from HBM, not L2.
+* ``roofline``     the split-KV partial kernel alone (same pools, merge skipped), against the
+                   measured HBM copy peak.
+* ``e2e``          the call a serving hook makes (``l20_paged_split_kv_attention_fp8``) with the
+                   step's query / block table / sequence lengths copied from pinned host memory
+                   and the output copied back, every step.  The KV cache is the resident state of
+                   the serving engine and stays on the device.
+* ``cpu_baseline`` the CPU oracle (torch restatement of the reference's own torch path) timed
+                   on this host's cores on the same batch.
+* ``--impl reference`` times only that CPU path and prints its own line.
+
+With N > 1 every rank runs the same geometry on its own sequences (no data-path collective);
+``--workload llama3-8b-long-b4`` instead splits each sequence's KV range over the ranks and
+merges the partials after one NCCL all-gather.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+FALLBACK_HBM_GBS = 6650.0
+L2_BYTES = 126 * 1024 * 1024
+# dram__bytes_read.sum + dram__bytes_write.sum of one partial-kernel launch on the default
+# workload, from the ncu capture summarised under profiles/ (None until captured).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+DEFAULT_WORKLOAD = "qwen2.5-coder-3b-b64"
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=600)
+    p.add_argument("--warmup", type=int, default=30)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    p.add_argument("--split-size", type=int, default=0, help="0 = choose from the geometry")
+    p.add_argument("--pools", type=int, default=0, help="distinct KV pools rotated through (0 = enough to exceed L2 x3)")
+    p.add_argument("--flags", type=int, default=0)
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    return p.parse_args()
+
+
+def measured_peak() -> tuple[float, str]:
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+        return float(peaks["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed loops run."""
+
+    def __init__(self, index: int, period_s: float = 0.002):
+        self.samples: list[int] = []
+        self.reasons: set[str] = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._period = period_s
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(visible.split(",")[index]) if visible and visible.split(",")[index].isdigit() else index
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nvml = None
+
+    def _loop(self):
+        n = self._nvml
+        names = {
+            "hw_slowdown": getattr(n, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(n, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(n, "nvmlClocksEventReasonSwPowerCap", 0x4),
+            "hw_power_brake": getattr(n, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(n.nvmlDeviceGetClockInfo(self._h, n.NVML_CLOCK_SM))
+                get = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+                mask = get(self._h)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self._period)
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+def cpu_reference_run(w, sample_rows: int, repeats: int):
+    """Time the CPU oracle on the first ``sample_rows`` sequences (their pages compacted into
+    a cache of their own first, outside the timed region); returns (GB/s, seconds, bytes)."""
+    from oracle import paged_decode_oracle as oracle
+    from single_gpu_inference_lab_b200 import sharding
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    rows = torch.arange(sample_rows)
+    sub = sharding._compact(w, rows.to(w.query.device), 0, w.block_table.shape[1], w.seq_lens.cpu()[rows]).to("cpu")
+    table = sub.block_table.long()
+    hkv, d = sub.key_cache.shape[2], sub.key_cache.shape[3]
+    nbytes = int(sub.seq_lens.sum()) * hkv * d * 2
+    best = float("inf")
+    for attempt in range(repeats + 1):  # the first pass is the warm-up
+        t0 = time.perf_counter()
+        oracle.reference(sub.query, sub.key_cache, sub.value_cache, table, sub.seq_lens, sub.k_scale, sub.v_scale)
+        dt = time.perf_counter() - t0
+        if attempt > 0 or repeats == 0:
+            best = min(best, dt)
+    return nbytes / best / 1e9, best, nbytes
+
+
+def run_reference_arm(args, rank: int) -> int:
+    """The reference's own CPU torch path for this operator (its ``reference()`` restated in
+    oracle/), all host threads, on a bounded sample of the workload.  Rank 0 only."""
+    if rank != 0:
+        return 0
+    from single_gpu_inference_lab_b200.workloads import make_inputs
+
+    cores = os.cpu_count() or 1
+    shrink = 1.0 / 32 if args.workload == "llama3-8b-long-b4" else 1.0
+    w = make_inputs(args.workload, seed=0, device="cpu", shrink=shrink)
+    batch = w.query.shape[0]
+    sample_rows = batch
+    torch.set_num_threads(cores)
+    times = []
+    nbytes = 0
+    for i in range(args.warmup + args.steps):
+        gbs, dt, nbytes = cpu_reference_run(w, sample_rows, 0)
+        if i >= args.warmup:
+            times.append(dt)
+        if sum(times) > 150:  # bound the arm to a few minutes whatever K is
+            break
+    ms = 1e3 * sum(times) / len(times)
+    value = nbytes / (ms * 1e-3) / 1e9
+    sample = f"{sample_rows} of {batch} sequences of {args.workload}" + (f" with contexts scaled by {shrink}" if shrink != 1.0 else "")
+    line = {
+        "impl": "reference",
+        "metric": "decode_attn_kv_read_gbs", "value": round(value, 4), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "us_per_layer_step": round(ms * 1e3, 2),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp8_e4m3 KV, bf16 q, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": args.workload, "sample": sample, "kv_bytes_per_step": nbytes},
+        "cpu_baseline": {"value": round(value, 4), "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": round(value, 4), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def main() -> int:
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        return run_reference_arm(args, rank)
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the operator has no CPU path")
+    if world != args.gpus:
+        raise RuntimeError(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+
+    import torch.distributed as dist
+
+    from single_gpu_inference_lab_b200 import cabi, l20_paged_split_kv, sharding
+    from single_gpu_inference_lab_b200.workloads import make_inputs
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cabi.load()
+
+    kv_range_mode = args.workload == "llama3-8b-long-b4"
+    # -------- inputs: every rank builds its own batch directly on its GPU
+    if kv_range_mode:
+        full_len = 131072
+        lo, hi = sharding.kv_range_bounds(full_len, rank, world)
+        w = make_inputs(args.workload, seed=rank, device=dev, shrink=(hi - lo) / full_len)
+        scaling = "strong"
+    else:
+        w = make_inputs(args.workload, seed=rank, device=dev)
+        scaling = "weak"
+    q = w.query
+    batch, hq, d = q.shape
+    hkv = w.key_cache.shape[2]
+    kv_bytes = w.kv_bytes
+    split = args.split_size or l20_paged_split_kv.choose_split_size(batch, hkv, w.max_seq_len)
+    pool_bytes = 2 * w.key_cache.numel()
+    pools = args.pools or max(2, -(-3 * L2_BYTES // pool_bytes) + 1)
+    pools = min(pools, max(2, int(40e9 // pool_bytes)))
+    kcs = [w.key_cache] + [w.key_cache.clone() for _ in range(pools - 1)]
+    vcs = [w.value_cache] + [w.value_cache.clone() for _ in range(pools - 1)]
+    ws = l20_paged_split_kv.allocate_l20_paged_split_kv_workspace(q, w.max_seq_len, split_size=split)
+    out = ws[3]
+    packed = torch.empty(batch, hq, d + 2, device=dev) if kv_range_mode else None
+    gathered = torch.empty(world, batch, hq, d + 2, device=dev) if kv_range_mode else None
+
+    def step(i: int, flags: int = args.flags):
+        cabi.paged_decode_fp8_e4m3_split_out(
+            q, kcs[i % pools], vcs[i % pools], w.block_table, w.seq_lens, k_scale=w.k_scale, v_scale=w.v_scale,
+            max_seq_len=w.max_seq_len, split_size=split, output=None if kv_range_mode else out,
+            packed_output=packed, workspace=ws, flags=flags,
+        )
+        if kv_range_mode and not (flags & cabi.PFD_FLAG_PARTIAL_ONLY):
+            if world > 1:
+                dist.all_gather_into_tensor(gathered.view(-1, hq, d + 2), packed)
+            else:
+                gathered[0].copy_(packed)
+            cabi.merge_packed(gathered, out)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def timed(fn, steps: int) -> float:
+        """ms per step, CUDA events on the launching stream, max over ranks."""
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            fn(i)
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    # -------- e2e operands: pinned host copies of the per-step inputs
+    host_q = q.cpu().pin_memory()
+    host_table = w.block_table.cpu().pin_memory()
+    host_lens = w.seq_lens.cpu().pin_memory()
+    host_out = torch.empty_like(host_q).pin_memory()
+    dq, dtable, dlens = torch.empty_like(q), torch.empty_like(w.block_table), torch.empty_like(w.seq_lens)
+    h2d = host_q.numel() * host_q.element_size() + host_table.numel() * 4 + host_lens.numel() * 4
+    d2h = host_out.numel() * host_out.element_size()
+    stream = torch.cuda.current_stream()
+
+    def e2e_step(i: int):
+        dq.copy_(host_q, non_blocking=True)
+        dtable.copy_(host_table, non_blocking=True)
+        dlens.copy_(host_lens, non_blocking=True)
+        if kv_range_mode:
+            local = w.__class__(**{**w.__dict__, "query": dq, "block_table": dtable, "seq_lens": dlens,
+                                   "key_cache": kcs[i % pools], "value_cache": vcs[i % pools]})
+            if world > 1:
+                res = sharding.kv_range_decode(local, split_size=split, gather_buffer=gathered)
+            else:
+                res = l20_paged_split_kv.l20_paged_split_kv_attention_fp8(
+                    dq, kcs[i % pools], vcs[i % pools], dtable, dlens, k_scale=w.k_scale, v_scale=w.v_scale,
+                    max_seq_len=w.max_seq_len, split_size=split, workspace=ws)
+        else:
+            res = l20_paged_split_kv.l20_paged_split_kv_attention_fp8(
+                dq, kcs[i % pools], vcs[i % pools], dtable, dlens, k_scale=w.k_scale, v_scale=w.v_scale,
+                max_seq_len=w.max_seq_len, split_size=split, workspace=ws)
+        host_out.copy_(res, non_blocking=True)
+        stream.synchronize()  # the host consumes the step's result
+
+    # -------- warm-up, then the timed loops under clock sampling
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    for i in range(3):
+        e2e_step(i)
+    with ClockSampler(local_rank) as clocks:
+        launches_before = cabi.launch_count()
+        ms_step = timed(step, args.steps)
+        launches = cabi.launch_count() - launches_before
+        ms_kernel = timed(lambda i: step(i, args.flags | cabi.PFD_FLAG_PARTIAL_ONLY), args.steps)
+        ms_e2e = timed(e2e_step, args.steps)
+        ms_step2 = timed(step, args.steps)
+    ms_step = min(ms_step, ms_step2)
+
+    # -------- aggregate over ranks
+    total_bytes = torch.tensor([float(kv_bytes)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(total_bytes)
+    total_bytes = float(total_bytes.item())
+    peak, peak_kind = measured_peak()
+    value = total_bytes / (ms_step * 1e-3) / 1e9
+    e2e_value = total_bytes / (ms_e2e * 1e-3) / 1e9
+    achieved = kv_bytes / (ms_kernel * 1e-3) / 1e9  # one GPU's kernel, one GPU's peak
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        rows = batch if not kv_range_mode else 1
+        repeats = 3 if kv_bytes < 5e8 else 1
+        gbs, secs, nbytes = cpu_reference_run(w, rows, repeats)
+        cpu_baseline = {
+            "value": round(gbs, 4), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{rows} of {batch} sequences, best of {repeats}, {secs * 1e3:.0f} ms per pass",
+        }
+
+    if rank == 0:
+        line = {
+            "metric": "decode_attn_kv_read_gbs", "value": round(value, 2), "unit": "GB/s",
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms_step, 6), "us_per_layer_step": round(ms_step * 1e3, 3),
+            "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
+            "dtype": "fp8_e4m3 KV, bf16 q, fp32 accumulate", "data": "synthetic",
+            "config": {
+                "workload": args.workload, "batch_per_gpu": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
+                "page_size": 16, "split_size": split, "max_seq_len": w.max_seq_len,
+                "kv_bytes_per_step_per_gpu": kv_bytes,
+                "parallelism": ("kv-range split + all-gather" if kv_range_mode else "sequence-sharded, no collective") if world > 1 else "single GPU",
+                "l2": f"{pools} KV pools of {pool_bytes / 1e6:.0f} MB rotated ({pools * pool_bytes / 1e6:.0f} MB > L2): every step reads cold KV",
+            },
+            "pct_of_hbm_peak": round(100 * value / (peak * world), 2),
+            "roofline": {
+                "bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
+                "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "kernel": "paged_decode_fp8_partial", "us_per_launch": round(ms_kernel * 1e3, 3), "peak_source": peak_kind,
+                "algorithmic_bytes_per_launch": kv_bytes,
+            },
+            "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "us_per_layer_step": round(ms_e2e * 1e3, 3)},
+            "gpu_launches": int(launches),
+            "clocks": clocks.summary(),
+        }
+        if cpu_baseline is not None:
+            line["cpu_baseline"] = cpu_baseline
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

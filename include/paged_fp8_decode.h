@@ -34,6 +34,7 @@ extern "C" {
 /* flags */
 #define PFD_FLAG_NO_TMA 1u        /* stream K/V with plain 16-byte global loads instead of TMA */
 #define PFD_FLAG_NO_DIRECT_OUT 2u /* always go through the partial workspace + merge kernel    */
+#define PFD_FLAG_PARTIAL_ONLY 4u  /* launch the split-KV partial kernel only (kernel timing)   */
 
 /*
  * Operands of one decode-attention layer-step.

@@ -17,6 +17,7 @@ LIB_NAME = "libpaged_fp8_decode.so"
 PFD_DTYPE_F32, PFD_DTYPE_F16, PFD_DTYPE_BF16 = 0, 1, 2
 PFD_FLAG_NO_TMA = 1
 PFD_FLAG_NO_DIRECT_OUT = 2
+PFD_FLAG_PARTIAL_ONLY = 4
 
 EXPORTS = (
     "pfd_paged_decode_fp8_e4m3_split_out",

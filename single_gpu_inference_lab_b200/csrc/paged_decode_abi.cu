@@ -41,7 +41,7 @@ int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num
   const dim3 grid(num_splits, a.num_kv_heads, a.batch);
   pfd::paged_decode_fp8_partial_ldg_kernel<D, QBF16, kWarps><<<grid, kWarps * 32, 0, stream>>>(kp);
   if (int rc = check_launch("partial kernel")) return rc;
-  if (num_splits > 1 || !kp.direct_out) {
+  if ((num_splits > 1 || !kp.direct_out) && !(a.flags & PFD_FLAG_PARTIAL_ONLY)) {
     const int rows = a.batch * a.num_q_heads;
     pfd::paged_decode_merge_kernel<D, QBF16><<<(rows + 3) / 4, 128, 0, stream>>>(kp, a.batch);
     if (int rc = check_launch("merge kernel")) return rc;

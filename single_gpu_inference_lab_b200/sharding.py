@@ -1,0 +1,135 @@
+"""Multi-GPU forms of the paged FP8 decode step (one process per GPU).
+
+The reference project is single-GPU by design and has no collective anywhere; the two forms
+below are the natural shardings of its operator:
+
+* **sequence sharding** -- a batch is split by sequence, every rank owns the pages, block-table
+  rows, query rows and output rows of its sequences.  No data-path communication at all.
+  ``lpt_partition`` balances *tokens*, not sequence counts.
+* **KV-range sharding** -- every sequence's pages are dealt out in contiguous page ranges, one
+  range per rank; each rank runs the ordinary operator on its range with ``packed_output``
+  (``o`` un-normalised, ``m``, ``l``), the ranks exchange those ``[B, Hq, D + 2]`` fp32 records
+  with one ``all_gather_into_tensor`` and every rank applies the same LSE merge the single-GPU
+  split-KV path uses (reference maths: integrations/vllm/l20_paged_split_kv.py:459-488).
+
+Nothing here falls back to a CPU implementation: the default compute callbacks are the CUDA
+operator; tests on CPU ranks inject their own.
+"""
+
+from __future__ import annotations
+
+from dataclasses import replace
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from .workloads import PAGE_SIZE, PagedDecodeInputs
+
+
+def lpt_partition(lengths, world_size: int) -> list[list[int]]:
+    """Longest-processing-time-first assignment of sequences to ranks by context length.
+    Returns, per rank, the sorted list of sequence indices."""
+    lengths = [int(x) for x in lengths]
+    order = sorted(range(len(lengths)), key=lambda i: (-lengths[i], i))
+    loads = [0] * world_size
+    parts: list[list[int]] = [[] for _ in range(world_size)]
+    for i in order:
+        r = min(range(world_size), key=lambda k: (loads[k], k))
+        parts[r].append(i)
+        loads[r] += lengths[i]
+    return [sorted(p) for p in parts]
+
+
+def _compact(inputs: PagedDecodeInputs, rows, page_lo, page_hi, seq_lens) -> PagedDecodeInputs:
+    """Keep block-table columns [page_lo, page_hi) of ``rows`` and move the pages they name into
+    a dense local pool (local ids in order of first use)."""
+    table = inputs.block_table[rows][:, page_lo:page_hi].cpu().long()
+    lens = seq_lens.cpu().long()
+    used = []
+    local = torch.zeros_like(table)
+    remap: dict[int, int] = {}
+    for r in range(table.shape[0]):
+        n = -(-int(lens[r]) // PAGE_SIZE)
+        for c in range(n):
+            page = int(table[r, c])
+            if page not in remap:
+                remap[page] = len(used)
+                used.append(page)
+            local[r, c] = remap[page]
+    if not used:
+        used = [0]
+    index = torch.tensor(used, dtype=torch.long, device=inputs.key_cache.device)
+    return replace(
+        inputs,
+        query=inputs.query[rows],
+        key_cache=inputs.key_cache[index].contiguous(),
+        value_cache=inputs.value_cache[index].contiguous(),
+        block_table=local.to(torch.int32).to(inputs.block_table.device),
+        seq_lens=lens.to(torch.int32).to(inputs.seq_lens.device),
+        max_seq_len=int(lens.max()) if lens.numel() else 0,
+    )
+
+
+def shard_sequences(inputs: PagedDecodeInputs, rank: int, world_size: int) -> tuple[PagedDecodeInputs, list[int]]:
+    """This rank's sequences (token-balanced) with a compacted local page pool."""
+    rows = lpt_partition(inputs.seq_lens.tolist(), world_size)[rank]
+    idx = torch.tensor(rows, dtype=torch.long)
+    return _compact(inputs, idx, 0, inputs.block_table.shape[1], inputs.seq_lens.cpu()[idx]), rows
+
+
+def kv_range_bounds(max_seq_len: int, rank: int, world_size: int) -> tuple[int, int]:
+    """Token range [lo, hi) of rank ``rank``: whole pages, ceil(pages / world) pages per rank."""
+    pages = -(-max_seq_len // PAGE_SIZE)
+    per = -(-pages // world_size)
+    return rank * per * PAGE_SIZE, min((rank + 1) * per, pages) * PAGE_SIZE
+
+
+def shard_kv_range(inputs: PagedDecodeInputs, rank: int, world_size: int) -> PagedDecodeInputs:
+    """Every sequence's tokens [lo, hi) of this rank as a local cache, local block table and
+    local lengths (0 for sequences that end before ``lo``).  The query stays replicated."""
+    lo, hi = kv_range_bounds(inputs.max_seq_len, rank, world_size)
+    lens = (inputs.seq_lens.cpu().long() - lo).clamp(0, max(hi - lo, 0))
+    rows = torch.arange(inputs.query.shape[0])
+    hi_page = max(hi // PAGE_SIZE, lo // PAGE_SIZE + 1)
+    return _compact(inputs, rows, lo // PAGE_SIZE, hi_page, lens)
+
+
+def _cuda_partial(local: PagedDecodeInputs, split_size: int) -> torch.Tensor:
+    from . import l20_paged_decode as ops
+    from .l20_paged_split_kv import allocate_l20_paged_split_kv_workspace
+
+    q = local.query
+    packed = torch.empty(q.shape[0], q.shape[1], q.shape[2] + 2, device=q.device, dtype=torch.float32)
+    ws = allocate_l20_paged_split_kv_workspace(q, max(local.max_seq_len, 1), split_size=split_size)
+    ops.paged_decode_fp8_e4m3_split_out_v2(
+        q, local.key_cache, local.value_cache, local.block_table, local.seq_lens, ws[0], ws[1], ws[2], None,
+        local.k_scale, local.v_scale, local.max_seq_len, split_size, packed_output=packed,
+    )
+    return packed
+
+
+def _cuda_merge(gathered: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
+    from . import l20_paged_decode as ops
+
+    return ops.merge_packed_partials(gathered, torch.empty_like(like))
+
+
+def kv_range_decode(
+    local: PagedDecodeInputs,
+    *,
+    split_size: int = 2048,
+    group: Optional[dist.ProcessGroup] = None,
+    partial_fn: Callable[[PagedDecodeInputs, int], torch.Tensor] = _cuda_partial,
+    merge_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor] = _cuda_merge,
+    gather_buffer: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One decode step of a KV-range-sharded batch: local packed partial, one all-gather of
+    ``[B, Hq, D + 2]`` fp32 per rank, LSE merge on every rank.  Returns ``[B, Hq, D]``."""
+    packed = partial_fn(local, split_size).contiguous()
+    world = dist.get_world_size(group)
+    if gather_buffer is None:
+        gather_buffer = torch.empty((world, *packed.shape), device=packed.device, dtype=packed.dtype)
+    # concatenation along dim 0 is the layout every backend accepts; [world*B,...] == [world,B,...]
+    dist.all_gather_into_tensor(gather_buffer.view(-1, *packed.shape[1:]), packed, group=group)
+    return merge_fn(gather_buffer, local.query)
