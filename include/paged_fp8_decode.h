@@ -117,6 +117,32 @@ typedef struct pfd_decode_args {
 int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args);
 
 /*
+ * Allocation-free variant of pfd_paged_decode_fp8_e4m3_split_out.  It has no counterpart in
+ * the reference project, whose launcher always takes the partial workspace from its caller.
+ *
+ * Some hosts of this library cannot provide that workspace: an inference engine that measured
+ * free HBM at start-up and handed all of it to its KV-cache pool has nothing left for a later
+ * cudaMalloc (and cudaMalloc would stall the whole device while it runs), and a host written
+ * in C, Go or Rust has no tensor allocator to borrow from.  For them the split-KV partials
+ * (partial_output, partial_max, partial_sum of `args`, which are ignored here) live in a fixed
+ * array of PFD_NOALLOC_SCRATCH_BYTES inside the library image; every GPU that loads the
+ * library carries that array until the process exits.  Inputs and outputs are still the
+ * caller's.  The call is refused with PFD_ERR_UNSUPPORTED when
+ *   batch * num_q_heads * ceil((max_seq_len - kv_start) / split_size) * (head_dim + 2) * 4
+ * exceeds the array (a larger split_size shrinks the need).  No cudaMalloc, cudaFree or other
+ * allocating routine is called, on the first call or later.
+ *
+ * The first call on each device looks up the array's device address (cudaGetSymbolAddress)
+ * with the caller's current device, which must be the device of `args->stream`; make that
+ * first call before any stream capture begins.  All calls on a device share the one array and
+ * nothing in it needs clearing between calls (every live split is written before it is read),
+ * but two calls whose kernels overlap on the GPU (different streams, or different host threads
+ * on different streams) would overwrite each other's partials: serialise them.
+ */
+#define PFD_NOALLOC_SCRATCH_BYTES (8u * 1024u * 1024u)
+int pfd_paged_decode_fp8_e4m3_split_out_noalloc(const pfd_decode_args* args);
+
+/*
  * LSE merge of `num_parts` packed partials [num_parts, rows, head_dim + 2] f32
  * (o un-normalised, m natural-log, l) into output [rows, head_dim] of `out_dtype`.
  * Same maths as _paged_split_kv_reduce (integrations/vllm/l20_paged_split_kv.py:459-488)

@@ -21,6 +21,7 @@ PFD_FLAG_PARTIAL_ONLY = 4
 
 EXPORTS = (
     "pfd_paged_decode_fp8_e4m3_split_out",
+    "pfd_paged_decode_fp8_e4m3_split_out_noalloc",
     "pfd_merge_packed",
     "pfd_resolve_slots",
     "pfd_launch_count",
@@ -100,6 +101,8 @@ def load() -> C.CDLL:
         lib = C.CDLL(str(path))
         lib.pfd_paged_decode_fp8_e4m3_split_out.argtypes = [C.POINTER(DecodeArgs)]
         lib.pfd_paged_decode_fp8_e4m3_split_out.restype = C.c_int
+        lib.pfd_paged_decode_fp8_e4m3_split_out_noalloc.argtypes = [C.POINTER(DecodeArgs)]
+        lib.pfd_paged_decode_fp8_e4m3_split_out_noalloc.restype = C.c_int
         lib.pfd_merge_packed.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]
         lib.pfd_merge_packed.restype = C.c_int
         lib.pfd_resolve_slots.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p]
@@ -177,6 +180,21 @@ def paged_decode_fp8_e4m3_split_out(query, key_cache, value_cache, block_table, 
     args = decode_args(query, key_cache, value_cache, block_table, seq_lens, **kw)
     with torch.cuda.device(query.device):
         _check(load().pfd_paged_decode_fp8_e4m3_split_out(C.byref(args)))
+
+
+NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024
+
+
+def paged_decode_fp8_e4m3_split_out_noalloc(query, key_cache, value_cache, block_table, seq_lens, **kw) -> None:
+    """One layer-step through ``pfd_paged_decode_fp8_e4m3_split_out_noalloc``: no ``workspace``
+    argument, the split-KV partials live in the fixed array inside the library, for hosts that
+    have no memory left to allocate one (an engine that gave all free HBM to its KV cache) or no
+    allocator at all.  Raises when the request needs more than ``NOALLOC_SCRATCH_BYTES``.  Calls
+    that overlap on the GPU share that array and must be serialised by the caller."""
+    kw.pop("workspace", None)
+    args = decode_args(query, key_cache, value_cache, block_table, seq_lens, **kw)
+    with torch.cuda.device(query.device):
+        _check(load().pfd_paged_decode_fp8_e4m3_split_out_noalloc(C.byref(args)))
 
 
 def merge_packed(packed: torch.Tensor, output: torch.Tensor) -> None:

@@ -5,6 +5,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <mutex>
 #include <string>
 
 #include "paged_decode_kernels.cuh"
@@ -138,6 +139,66 @@ int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args) {
   if (a.head_dim == 128)
     return bf16 ? launch_decode<128, true>(a, kp, num_splits) : launch_decode<128, false>(a, kp, num_splits);
   return bf16 ? launch_decode<64, true>(a, kp, num_splits) : launch_decode<64, false>(a, kp, num_splits);
+}
+
+// ---- allocation-free entry point -------------------------------------------------------
+// The partial workspace of the split-KV path as a fixed array in the library image.  In host
+// code the name below is only a stand-in for the symbol, never a device address: the address
+// each device uses comes from cudaGetSymbolAddress, looked up once per device.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[PFD_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mutex;
+void* g_noalloc_ptr[kMaxDevices] = {nullptr};
+}  // namespace
+
+int pfd_paged_decode_fp8_e4m3_split_out_noalloc(const pfd_decode_args* args) {
+  if (args == nullptr) return fail(PFD_ERR_INVALID, "args is NULL");
+  if (args->struct_size != sizeof(pfd_decode_args))
+    return fail(PFD_ERR_INVALID, "pfd_decode_args size mismatch: caller %u, library %zu",
+                args->struct_size, sizeof(pfd_decode_args));
+  pfd_decode_args a = *args;
+  if (a.batch < 0 || a.num_q_heads <= 0 || a.head_dim <= 0 || a.split_size < 16 || a.kv_start < 0 ||
+      a.max_seq_len < 0)
+    return fail(PFD_ERR_INVALID, "invalid geometry");
+  const int64_t span = a.max_seq_len > a.kv_start ? a.max_seq_len - a.kv_start : 0;
+  int64_t splits = (span + a.split_size - 1) / a.split_size;
+  if (splits < 1) splits = 1;
+  const int64_t rows = (int64_t)a.batch * a.num_q_heads * splits;
+  const int64_t need = rows * (a.head_dim + 2) * (int64_t)sizeof(float);
+  if (need > (int64_t)PFD_NOALLOC_SCRATCH_BYTES)
+    return fail(PFD_ERR_UNSUPPORTED,
+                "request needs %lld bytes of split-KV scratch but the built-in array holds %u; "
+                "raise split_size or use the entry point that takes a workspace",
+                (long long)need, PFD_NOALLOC_SCRATCH_BYTES);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(PFD_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  void* base = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess || p == nullptr)
+        return fail(PFD_ERR_CUDA, "cudaGetSymbolAddress(scratch) failed on device %d: %s", dev,
+                    cudaGetErrorString(e));
+      g_noalloc_ptr[dev] = p;
+    }
+    base = g_noalloc_ptr[dev];
+  }
+  float* po = static_cast<float*>(base);
+  a.partial_output = po;
+  a.partial_max = po + rows * a.head_dim;
+  a.partial_sum = po + rows * a.head_dim + rows;
+  a.partial_dtype = PFD_DTYPE_F32;
+  a.workspace_splits = static_cast<int32_t>(splits);
+  a.partial_stride_b = (int64_t)a.num_q_heads * splits;
+  a.partial_stride_h = splits;
+  a.partial_stride_s = 1;
+  return pfd_paged_decode_fp8_e4m3_split_out(&a);
 }
 
 int pfd_merge_packed(const float* packed, int32_t num_parts, int64_t rows, int32_t head_dim,
