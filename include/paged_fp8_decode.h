@@ -162,6 +162,13 @@ int pfd_merge_packed(const float* packed, int32_t num_parts, int64_t rows, int32
 int pfd_resolve_slots(const int32_t* block_table, int64_t bt_stride_b, const int32_t* seq_lens,
                       int32_t batch, int32_t max_seq_len, int64_t* slots, void* stream);
 
+/*
+ * Synchronises with the current device and reads (then clears) the error word the kernels set
+ * when a bounded wait gave up: 0 = none, 1 = a TMA copy did not complete in time (the step's
+ * output is then undefined).  The kernels never trap and never spin without a limit.
+ */
+int pfd_device_status(int32_t* status);
+
 /* Number of kernels this library has launched in this process (for launch accounting). */
 int64_t pfd_launch_count(void);
 

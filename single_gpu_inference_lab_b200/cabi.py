@@ -24,6 +24,7 @@ EXPORTS = (
     "pfd_paged_decode_fp8_e4m3_split_out_noalloc",
     "pfd_merge_packed",
     "pfd_resolve_slots",
+    "pfd_device_status",
     "pfd_launch_count",
     "pfd_last_error",
     "pfd_abi_version",
@@ -210,6 +211,16 @@ def resolve_slots(block_table: torch.Tensor, seq_lens: torch.Tensor, max_seq_len
         _check(load().pfd_resolve_slots(block_table.data_ptr(), block_table.stride(0), seq_lens.data_ptr(),
                                         block_table.shape[0], max_seq_len, slots.data_ptr(), _stream(block_table)))
     return slots
+
+
+def device_status() -> int:
+    """Synchronise and return (then clear) the kernels' error word; 0 means no bounded wait gave up."""
+    value = C.c_int32(0)
+    lib = load()
+    lib.pfd_device_status.argtypes = [C.POINTER(C.c_int32)]
+    lib.pfd_device_status.restype = C.c_int
+    _check(lib.pfd_device_status(C.byref(value)))
+    return int(value.value)
 
 
 def launch_count() -> int:

@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <mutex>
 #include <string>
+#include <vector>
 
 #include "paged_decode_kernels.cuh"
 
@@ -35,13 +36,142 @@ int check_launch(const char* what) {
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 constexpr int kWarps = 4;
+constexpr int kStages = 4;
+constexpr int kMaxDevices = 64;
+
+// Error word the kernels write (bounded waits that gave up).  The name is a host-side stand-in
+// for the symbol; each device's address is looked up once with cudaGetSymbolAddress.
+static __device__ int g_device_status;
+std::mutex g_state_mutex;
+int32_t* g_status_ptr[kMaxDevices] = {nullptr};
+
+int status_pointer(int32_t** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(PFD_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_state_mutex);
+  if (g_status_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_device_status);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(PFD_ERR_CUDA, "cudaGetSymbolAddress(status) failed: %s", cudaGetErrorString(e));
+    g_status_ptr[dev] = static_cast<int32_t*>(p);
+  }
+  *out = g_status_ptr[dev];
+  return PFD_OK;
+}
+
+// ---- tensor maps (TMA descriptors) of the K and V caches, cached per distinct cache view ----
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+struct MapKey {
+  int dev;
+  const void* base;
+  int64_t stride_page, stride_token, stride_head, num_pages;
+  int32_t heads;
+  bool operator==(const MapKey& o) const {
+    return dev == o.dev && base == o.base && stride_page == o.stride_page && stride_token == o.stride_token &&
+           stride_head == o.stride_head && num_pages == o.num_pages && heads == o.heads;
+  }
+};
+struct MapEntry {
+  MapKey key;
+  CUtensorMap map;
+};
+std::vector<MapEntry> g_maps;
+EncodeTiledFn g_encode = nullptr;
+
+bool head_is_dim1(int64_t stride_token, int64_t stride_head) { return stride_head <= stride_token; }
+
+// [pages, 16, heads, 128] e4m3 bytes with arbitrary (page, token, head) strides as a rank-4 u8
+// tensor whose dimensions are listed by ascending stride; box = one (page, head) tile of
+// 16 x 128 bytes, 128-byte swizzle.
+int get_tensor_map(const void* base, int64_t stride_page, int64_t stride_token, int64_t stride_head,
+                   int64_t num_pages, int32_t heads, CUtensorMap* out) {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const MapKey key{dev, base, stride_page, stride_token, stride_head, num_pages, heads};
+  std::lock_guard<std::mutex> lock(g_state_mutex);
+  for (const MapEntry& e : g_maps)
+    if (e.key == key) {
+      *out = e.map;
+      return PFD_OK;
+    }
+  if (g_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || fn == nullptr)
+      return fail(PFD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  const bool h1 = head_is_dim1(stride_token, stride_head);
+  const cuuint64_t dims[4] = {128, (cuuint64_t)(h1 ? heads : 16), (cuuint64_t)(h1 ? 16 : heads),
+                              (cuuint64_t)num_pages};
+  const cuuint64_t strides[3] = {(cuuint64_t)(h1 ? stride_head : stride_token),
+                                 (cuuint64_t)(h1 ? stride_token : stride_head), (cuuint64_t)stride_page};
+  const cuuint32_t box[4] = {128, (cuuint32_t)(h1 ? 1 : 16), (cuuint32_t)(h1 ? 16 : 1), 1};
+  const cuuint32_t elem[4] = {1, 1, 1, 1};
+  MapEntry entry;
+  entry.key = key;
+  const CUresult r = g_encode(&entry.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides,
+                              box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(PFD_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  if (g_maps.size() >= 256) g_maps.erase(g_maps.begin());
+  g_maps.push_back(entry);
+  *out = entry.map;
+  return PFD_OK;
+}
+
+bool tma_eligible(const pfd_decode_args& a) {
+  if (a.head_dim != 128 || (a.flags & PFD_FLAG_NO_TMA)) return false;
+  // a size-1 dimension may carry any stride; everything else was checked to be 16-byte aligned
+  return a.k_stride_page > 0 && a.v_stride_page > 0 && a.k_stride_token > 0 && a.v_stride_token > 0 &&
+         a.k_stride_head > 0 && a.v_stride_head > 0 && a.num_pages > 0 &&
+         head_is_dim1(a.k_stride_token, a.k_stride_head) == head_is_dim1(a.v_stride_token, a.v_stride_head);
+}
+
+template <bool QBF16>
+int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, dim3 grid, cudaStream_t stream) {
+  CUtensorMap mk, mv;
+  if (int rc = get_tensor_map(a.key_cache, a.k_stride_page, a.k_stride_token, a.k_stride_head, a.num_pages,
+                              a.num_kv_heads, &mk))
+    return rc;
+  if (int rc = get_tensor_map(a.value_cache, a.v_stride_page, a.v_stride_token, a.v_stride_head, a.num_pages,
+                              a.num_kv_heads, &mv))
+    return rc;
+  pfd::TmaParams tp{};
+  tp.head_is_dim1 = head_is_dim1(a.k_stride_token, a.k_stride_head) ? 1 : 0;
+  if (int rc = status_pointer(&tp.status)) return rc;
+  auto kernel = pfd::paged_decode_fp8_partial_tma_kernel<QBF16, kWarps, kStages>;
+  constexpr int smem = 1024 + kWarps * kStages * 4096 + kWarps * kStages * 8 + 2 * kWarps * 16 * 4;
+  static bool configured[kMaxDevices] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev]) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    configured[dev] = true;
+  }
+  kernel<<<grid, kWarps * 32, smem, stream>>>(kp, tp, mk, mv);
+  return check_launch("partial kernel (TMA)");
+}
 
 template <int D, bool QBF16>
 int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num_splits) {
   cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
   const dim3 grid(num_splits, a.num_kv_heads, a.batch);
-  pfd::paged_decode_fp8_partial_ldg_kernel<D, QBF16, kWarps><<<grid, kWarps * 32, 0, stream>>>(kp);
-  if (int rc = check_launch("partial kernel")) return rc;
+  if (D == 128 && tma_eligible(a)) {
+    if (int rc = launch_partial_tma<QBF16>(a, kp, grid, stream)) return rc;
+  } else {
+    pfd::paged_decode_fp8_partial_ldg_kernel<D, QBF16, kWarps><<<grid, kWarps * 32, 0, stream>>>(kp);
+    if (int rc = check_launch("partial kernel")) return rc;
+  }
   if ((num_splits > 1 || !kp.direct_out) && !(a.flags & PFD_FLAG_PARTIAL_ONLY)) {
     const int rows = a.batch * a.num_q_heads;
     pfd::paged_decode_merge_kernel<D, QBF16><<<(rows + 3) / 4, 128, 0, stream>>>(kp, a.batch);
@@ -148,7 +278,6 @@ int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args) {
 static __device__ __align__(256) unsigned char g_noalloc_scratch[PFD_NOALLOC_SCRATCH_BYTES];
 
 namespace {
-constexpr int kMaxDevices = 64;
 std::mutex g_noalloc_mutex;
 void* g_noalloc_ptr[kMaxDevices] = {nullptr};
 }  // namespace
@@ -199,6 +328,20 @@ int pfd_paged_decode_fp8_e4m3_split_out_noalloc(const pfd_decode_args* args) {
   a.partial_stride_h = splits;
   a.partial_stride_s = 1;
   return pfd_paged_decode_fp8_e4m3_split_out(&a);
+}
+
+int pfd_device_status(int32_t* status) {
+  if (status == nullptr) return fail(PFD_ERR_INVALID, "status is NULL");
+  int32_t* p = nullptr;
+  if (int rc = status_pointer(&p)) return rc;
+  cudaError_t e = cudaMemcpy(status, p, sizeof(int32_t), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "reading the device status failed: %s", cudaGetErrorString(e));
+  if (*status != 0) {
+    const int32_t zero = 0;
+    e = cudaMemcpy(p, &zero, sizeof(int32_t), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "clearing the device status failed: %s", cudaGetErrorString(e));
+  }
+  return PFD_OK;
 }
 
 int pfd_merge_packed(const float* packed, int32_t num_parts, int64_t rows, int32_t head_dim,

@@ -19,6 +19,7 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -101,9 +102,18 @@ __device__ __forceinline__ uint2 ldg_nc_8(const uint8_t* p) {
   return v;
 }
 
+// Which token row of a page sits in column n of an 8-column score tile.  Any bijection works
+// for the maths (P's columns and V's rows follow it); this one makes both the K and the V
+// shared-memory reads of the TMA kernel bank-conflict free under the 128-byte swizzle:
+// columns 2q and 2q+1 land on rows that differ in bit 2, and the rows of the even (odd)
+// columns differ pairwise in bits 1..2.  rho = [0, 5, 2, 7, 4, 1, 6, 3].
+__device__ __forceinline__ int rho(int n) { return (n & 6) ^ ((n & 1) * 5); }
+
 // Register image of one (page, kv head) tile as the MMA fragments want it.
-//   K: thread (i = lane/4, j = lane%4) holds bytes [16*(j+4l), +16) of rows i and i+8.
-//   V: the same thread holds bytes [CB*i, +CB) (CB = D/8) of rows 2j, 2j+1, 2j+8, 2j+9.
+//   K: thread (i = lane/4, j = lane%4) holds bytes [16*(j+4l), +16) of rows rho(i), 8 + rho(i).
+//   V: the same thread holds bytes [CB*i, +CB) (CB = D/8) of rows 2j, 2j^5, 8+2j, 8+(2j^5),
+//      i.e. the rows of its own score columns 2j and 2j+1 in both column tiles.
+__device__ __forceinline__ int v_row(int j, int r) { return ((r & 1) ? ((2 * j) ^ 5) : 2 * j) + 8 * (r >> 1); }
 template <int D>
 struct TileRegs {
   static constexpr int KL = D / 64;  // 16-byte K chunks per thread per row
@@ -120,14 +130,13 @@ __device__ __forceinline__ void load_tile_global(TileRegs<D>& t, const uint8_t* 
   for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
     for (int l = 0; l < TileRegs<D>::KL; ++l) {
-      uint4 x = ldg_nc_16(kpage + (int64_t)(nt * 8 + i) * kst + 16 * (j + 4 * l));
+      uint4 x = ldg_nc_16(kpage + (int64_t)(nt * 8 + rho(i)) * kst + 16 * (j + 4 * l));
       t.k[nt][l][0] = x.x; t.k[nt][l][1] = x.y; t.k[nt][l][2] = x.z; t.k[nt][l][3] = x.w;
     }
   }
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
-    const int row = 2 * j + (r & 1) + 8 * (r >> 1);
-    const uint8_t* p = vpage + (int64_t)row * vst + (D / 8) * i;
+    const uint8_t* p = vpage + (int64_t)v_row(j, r) * vst + (D / 8) * i;
     if constexpr (D == 128) {
       uint4 x = ldg_nc_16(p);
       t.v[r][0] = x.x; t.v[r][1] = x.y; t.v[r][2] = x.z; t.v[r][3] = x.w;
@@ -146,50 +155,43 @@ struct WarpState {
   float l[2];         // running sum, this thread's columns only (quad-reduced at the end)
 };
 
-// One 16-token tile.  tok0 = global token index of row 0; tokens outside [lo, hi) are masked.
+// ---- the three phases of one 16-token tile ------------------------------------------------
+// tok0 = global token index of row 0 of the page; tokens outside [lo, hi) are masked.
+
+// S = Q K^T for both 8-column tiles (raw, unscaled).
 template <int D>
-__device__ __forceinline__ void consume_tile(WarpState<D>& st, TileRegs<D>& t,
-                                             const uint32_t (&qa)[D / 16][4], float scale_log2,
-                                             int tok0, int lo, int hi, int j) {
-  constexpr int KL = TileRegs<D>::KL;
-  constexpr int VW = TileRegs<D>::VW;
-  float s[2][4];
+__device__ __forceinline__ void qk_scores(float (&s)[2][4], const uint32_t (&k)[2][D / 64][4],
+                                          const uint32_t (&qa)[D / 16][4]) {
 #pragma unroll
   for (int nt = 0; nt < 2; ++nt) {
     s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
-    for (int l = 0; l < KL; ++l) {
+    for (int l = 0; l < D / 64; ++l) {
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        const uint32_t word = t.k[nt][l][w];
+        const uint32_t word = k[nt][l][w];
         mma_m16n8k16(s[nt], qa[l * 4 + w], cvt_e4m3x2_to_f16x2(word),
                      cvt_e4m3x2_to_f16x2(word >> 16));
       }
     }
   }
-  const bool edge = (tok0 < lo) | (tok0 + kPage > hi);
+}
+
+// Scale, mask, online softmax; rescales O and returns P as the f16 A-fragment of the PV MMA.
+template <int D>
+__device__ __forceinline__ void softmax_step(WarpState<D>& st, float (&s)[2][4], uint32_t (&pa)[4],
+                                             float scale_log2, bool edge, int tok0, int lo, int hi,
+                                             int j) {
 #pragma unroll
   for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       float x = s[nt][c] * scale_log2;
       if (edge) {
-        const int tok = tok0 + nt * 8 + 2 * j + (c & 1);
+        const int tok = tok0 + nt * 8 + rho(2 * j + (c & 1));
         if (tok < lo || tok >= hi) x = -INFINITY;
       }
       s[nt][c] = x;
-    }
-  }
-  if (edge) {
-    // Bytes of tokens outside the range may be anything (NaN patterns included) and
-    // 0 * NaN would poison the accumulator: zero them, as the reference's masked loads do.
-#pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const int tok = tok0 + 2 * j + (r & 1) + 8 * (r >> 1);
-      if (tok < lo || tok >= hi) {
-#pragma unroll
-        for (int w = 0; w < VW; ++w) t.v[r][w] = 0u;
-      }
     }
   }
   float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
@@ -214,28 +216,61 @@ __device__ __forceinline__ void consume_tile(WarpState<D>& st, TileRegs<D>& t,
   }
   st.l[0] = st.l[0] * alpha0 + ((p[0][0] + p[0][1]) + (p[1][0] + p[1][1]));
   st.l[1] = st.l[1] * alpha1 + ((p[0][2] + p[0][3]) + (p[1][2] + p[1][3]));
-  uint32_t pa[4];
   pa[0] = pack_f16x2(p[0][0], p[0][1]);
   pa[1] = pack_f16x2(p[0][2], p[0][3]);
   pa[2] = pack_f16x2(p[1][0], p[1][1]);
   pa[3] = pack_f16x2(p[1][2], p[1][3]);
+  // the running max rarely moves after the first tiles: skip the 4*D/8 multiplies then
+  if (__any_sync(0xffffffffu, (alpha0 != 1.f) | (alpha1 != 1.f))) {
 #pragma unroll
-  for (int m = 0; m < D / 8; ++m) {
-    st.o[m][0] *= alpha0; st.o[m][1] *= alpha0;
-    st.o[m][2] *= alpha1; st.o[m][3] *= alpha1;
+    for (int m = 0; m < D / 8; ++m) {
+      st.o[m][0] *= alpha0; st.o[m][1] *= alpha0;
+      st.o[m][2] *= alpha1; st.o[m][3] *= alpha1;
+    }
+  }
+}
+
+// O += P V.  On edge pages the rows of tokens outside the range are zeroed first: their bytes
+// may be anything (NaN patterns included) and 0 * NaN would poison the accumulator -- the
+// reference's masked loads (`other=0.0`) do the same.
+template <int D>
+__device__ __forceinline__ void pv_accumulate(WarpState<D>& st, uint32_t (&v)[4][D / 32],
+                                              const uint32_t (&pa)[4], bool edge, int tok0, int lo,
+                                              int hi, int j) {
+  if (edge) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int tok = tok0 + v_row(j, r);
+      if (tok < lo || tok >= hi) {
+#pragma unroll
+        for (int w = 0; w < D / 32; ++w) v[r][w] = 0u;
+      }
+    }
   }
 #pragma unroll
-  for (int w = 0; w < VW; ++w) {
-    // rows (2j, 2j+1) and (2j+8, 2j+9): interleave token pairs byte-wise
-    const uint32_t x01 = prmt(t.v[0][w], t.v[1][w], 0x5140u);
-    const uint32_t y01 = prmt(t.v[0][w], t.v[1][w], 0x7362u);
-    const uint32_t x23 = prmt(t.v[2][w], t.v[3][w], 0x5140u);
-    const uint32_t y23 = prmt(t.v[2][w], t.v[3][w], 0x7362u);
+  for (int w = 0; w < D / 32; ++w) {
+    // the two rows of each k-pair: interleave them byte-wise
+    const uint32_t x01 = prmt(v[0][w], v[1][w], 0x5140u);
+    const uint32_t y01 = prmt(v[0][w], v[1][w], 0x7362u);
+    const uint32_t x23 = prmt(v[2][w], v[3][w], 0x5140u);
+    const uint32_t y23 = prmt(v[2][w], v[3][w], 0x7362u);
     mma_m16n8k16(st.o[4 * w + 0], pa, cvt_e4m3x2_to_f16x2(x01), cvt_e4m3x2_to_f16x2(x23));
     mma_m16n8k16(st.o[4 * w + 1], pa, cvt_e4m3x2_to_f16x2(x01 >> 16), cvt_e4m3x2_to_f16x2(x23 >> 16));
     mma_m16n8k16(st.o[4 * w + 2], pa, cvt_e4m3x2_to_f16x2(y01), cvt_e4m3x2_to_f16x2(y23));
     mma_m16n8k16(st.o[4 * w + 3], pa, cvt_e4m3x2_to_f16x2(y01 >> 16), cvt_e4m3x2_to_f16x2(y23 >> 16));
   }
+}
+
+template <int D>
+__device__ __forceinline__ void consume_tile(WarpState<D>& st, TileRegs<D>& t,
+                                             const uint32_t (&qa)[D / 16][4], float scale_log2,
+                                             int tok0, int lo, int hi, int j) {
+  float s[2][4];
+  uint32_t pa[4];
+  const bool edge = (tok0 < lo) | (tok0 + kPage > hi);
+  qk_scores<D>(s, t.k, qa);
+  softmax_step<D>(st, s, pa, scale_log2, edge, tok0, lo, hi, j);
+  pv_accumulate<D>(st, t.v, pa, edge, tok0, lo, hi, j);
 }
 
 // Q rows i and i+8 of the kv head's group as f16 A-fragments, d permuted to match the K loads:
@@ -424,6 +459,213 @@ paged_decode_fp8_partial_ldg_kernel(const KernelParams p) {
     consume_tile<D>(st, cur, qa, scale_log2, pg * kPage, lo, hi, j);
     cur = nxt;
   }
+  cta_merge_and_store<D, QBF16, NWARPS>(st, p, b, kvh, split, nsplits_seq, vs, sm_m, sm_l, sm_o);
+}
+
+// ---- TMA pipeline ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after kSpinLimit polls (each poll itself suspends for a while in
+// hardware) so that a copy that never lands cannot hang the GPU; the caller records an error.
+constexpr uint32_t kSpinLimit = 1u << 22;
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  return false;
+}
+// 4-D tiled TMA load of one (page, kv head) tile: no multicast, CTA-local destination.
+__device__ __forceinline__ void tma_load_tile(uint32_t dst, const void* tmap, uint32_t bar, int c1,
+                                              int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ uint4 lds_16(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(addr));
+  return v;
+}
+
+struct TmaParams {
+  int32_t head_is_dim1;  // 1: tensor-map dims are (D, head, token, page); 0: (D, token, head, page)
+  int32_t* status;       // device error word (0 = ok)
+};
+
+constexpr int kErrTmaTimeout = 1;
+
+// Split-KV partial kernel for head_dim 128, K/V tiles staged by TMA.
+//
+// Every warp owns a private ring of NSTAGE stages of 4 KiB (K tile [16][128] + V tile
+// [16][128], 128-byte swizzled, 1 KiB aligned) and one mbarrier per stage; its lane 0 issues
+// the two tiled TMA loads of the warp's next page as soon as the warp has finished reading a
+// stage.  Warps never synchronise with each other inside the loop.  Up to NSTAGE * 4 KiB per
+// warp are in flight, independent of registers.
+template <bool QBF16, int NWARPS, int NSTAGE>
+__global__ void __launch_bounds__(NWARPS * 32)
+paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
+                                    const __grid_constant__ CUtensorMap tmap_k,
+                                    const __grid_constant__ CUtensorMap tmap_v) {
+  constexpr int D = 128;
+  constexpr uint32_t kTileBytes = kPage * D;      // 2 KiB
+  constexpr uint32_t kStageBytes = 2 * kTileBytes;
+  const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int seq_len = p.seq_lens[b];
+  const int lo = p.kv_start + split * p.split_size;
+  const int hi = min(lo + p.split_size, seq_len);
+  if (lo >= hi) return;
+  const int nsplits_seq = (seq_len - p.kv_start + p.split_size - 1) / p.split_size;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* ring_ptr = smem_raw + (ring - smem_u32(smem_raw));
+  // after the ring: mbarriers, then the small merge arrays; sm_o aliases the ring at the end
+  const uint32_t bars = ring + NWARPS * NSTAGE * kStageBytes;
+  float* sm_m = reinterpret_cast<float*>(ring_ptr + NWARPS * NSTAGE * kStageBytes + NWARPS * NSTAGE * 8);
+  float* sm_l = sm_m + NWARPS * 16;
+  float* sm_o = reinterpret_cast<float*>(ring_ptr);
+  static_assert(NSTAGE * kStageBytes >= 16 * D * 4, "merge buffer must fit in the ring");
+
+  const uint32_t my_ring = ring + warp * NSTAGE * kStageBytes;
+  const uint32_t my_bars = bars + warp * NSTAGE * 8;
+  if (lane == 0) {
+#pragma unroll
+    for (int s = 0; s < NSTAGE; ++s) mbar_init(my_bars + 8 * s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+
+  const int page_first = lo / kPage, page_last = (hi - 1) / kPage;
+  const int n_tiles = (page_last - page_first - warp + NWARPS) / NWARPS;  // pages warp, warp+NWARPS, ...
+  // page ids of this warp's next 32 tiles, one per lane
+  int ids_base = 0;
+  int32_t ids = 0;
+  if (lane < n_tiles) ids = page_of(p.block_table, p.bt_stride_b, b, page_first + warp + lane * NWARPS);
+
+  auto issue = [&](int t, int32_t phys) {  // lane 0 only
+    const int s = t % NSTAGE;
+    const uint32_t bar = my_bars + 8 * s;
+    const uint32_t dst = my_ring + s * kStageBytes;
+    mbar_expect_tx(bar, kStageBytes);
+    const int c1 = tp.head_is_dim1 ? kvh : 0;
+    const int c2 = tp.head_is_dim1 ? 0 : kvh;
+    tma_load_tile(dst, &tmap_k, bar, c1, c2, phys);
+    tma_load_tile(dst + kTileBytes, &tmap_v, bar, c1, c2, phys);
+  };
+#pragma unroll
+  for (int t = 0; t < NSTAGE; ++t) {
+    const int32_t phys = __shfl_sync(0xffffffffu, ids, t & 31);
+    if (lane == 0 && t < n_tiles) issue(t, phys);
+  }
+
+  uint32_t qa[D / 16][4];
+  load_q_frags<D, QBF16>(qa, p, b, kvh, i, j);
+  const float ks = p.k_scale_ph ? __ldg(p.k_scale_ph + kvh) : p.k_scale;
+  const float vs = p.v_scale_ph ? __ldg(p.v_scale_ph + kvh) : p.v_scale;
+  const float scale_log2 = ks * p.sm_scale * kLog2e;
+
+  WarpState<D> st;
+#pragma unroll
+  for (int m = 0; m < D / 8; ++m) st.o[m][0] = st.o[m][1] = st.o[m][2] = st.o[m][3] = 0.f;
+  st.m[0] = st.m[1] = -INFINITY;
+  st.l[0] = st.l[1] = 0.f;
+
+  // swizzled shared-memory offsets of this thread's fragments inside a stage
+  uint32_t k_off[2][2], v_off[4];
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int l = 0; l < 2; ++l)
+      k_off[nt][l] = (nt * 8 + rho(i)) * D + (((j + 4 * l) ^ rho(i)) << 4);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int row = v_row(j, r);
+    v_off[r] = kTileBytes + row * D + ((i ^ (row & 7)) << 4);
+  }
+
+  bool ok = true;
+  int t = 0;
+  for (; t < n_tiles; ++t) {
+    const int s = t % NSTAGE;
+    const uint32_t parity = (t / NSTAGE) & 1;
+    if (!mbar_wait_bounded(my_bars + 8 * s, parity)) { ok = false; break; }
+    const uint32_t stage = my_ring + s * kStageBytes;
+    const int tok0 = (page_first + warp + t * NWARPS) * kPage;
+    const bool edge = (tok0 < lo) | (tok0 + kPage > hi);
+    float sc[2][4];
+    uint32_t pa[4];
+    {
+      uint32_t k[2][2][4];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int l = 0; l < 2; ++l) {
+          const uint4 x = lds_16(stage + k_off[nt][l]);
+          k[nt][l][0] = x.x; k[nt][l][1] = x.y; k[nt][l][2] = x.z; k[nt][l][3] = x.w;
+        }
+      qk_scores<D>(sc, k, qa);
+    }
+    uint32_t v[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const uint4 x = lds_16(stage + v_off[r]);
+      v[r][0] = x.x; v[r][1] = x.y; v[r][2] = x.z; v[r][3] = x.w;
+    }
+    softmax_step<D>(st, sc, pa, scale_log2, edge, tok0, lo, hi, j);
+    pv_accumulate<D>(st, v, pa, edge, tok0, lo, hi, j);
+    // Every byte this warp read from the stage has been consumed by an MMA above, so the
+    // reads are complete: hand the stage back to TMA for the warp's tile t + NSTAGE.
+    __syncwarp();
+    const int tn = t + NSTAGE;
+    if (tn < n_tiles) {
+      if ((tn & 31) == 0) {  // next batch of 32 page ids
+        ids_base = tn;
+        ids = 0;
+        if (tn + lane < n_tiles)
+          ids = page_of(p.block_table, p.bt_stride_b, b, page_first + warp + (tn + lane) * NWARPS);
+      }
+      const int32_t phys = __shfl_sync(0xffffffffu, ids, (tn - ids_base) & 31);
+      if (lane == 0) {
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        issue(tn, phys);
+      }
+    }
+  }
+  if (!ok) {
+    // Record the failure, then give this warp's copies still in flight a bounded chance to
+    // land before the ring is reused by the merge below.
+    if (lane == 0) {
+      atomicExch(tp.status, kErrTmaTimeout);
+      const int issued = min(n_tiles, t + NSTAGE);
+      for (int u = t + 1; u < issued; ++u) mbar_wait_bounded(my_bars + 8 * (u % NSTAGE), (u / NSTAGE) & 1);
+    }
+    __syncwarp();
+  }
+  __syncthreads();  // every warp is done with its ring: sm_o may alias it
   cta_merge_and_store<D, QBF16, NWARPS>(st, p, b, kvh, split, nsplits_seq, vs, sm_m, sm_l, sm_o);
 }
 

@@ -54,6 +54,7 @@ def run(cabi, w, split_size, *, flags=0, kv_start=0, partial_dtype=torch.float32
         workspace=ws, kv_start=kv_start, flags=flags,
     )
     torch.cuda.synchronize()
+    assert cabi.device_status() == 0, "a bounded device-side wait gave up"
     return pk if packed else out
 
 
