@@ -18,7 +18,7 @@
 extern "C" {
 #endif
 
-#define PFD_ABI_VERSION 1
+#define PFD_ABI_VERSION 2
 
 /* element types of query / output / partial_output */
 #define PFD_DTYPE_F32 0
@@ -35,6 +35,8 @@ extern "C" {
 #define PFD_FLAG_NO_TMA 1u        /* stream K/V with plain 16-byte global loads instead of TMA */
 #define PFD_FLAG_NO_DIRECT_OUT 2u /* always go through the partial workspace + merge kernel    */
 #define PFD_FLAG_PARTIAL_ONLY 4u  /* launch the split-KV partial kernel only (kernel timing)   */
+#define PFD_FLAG_FIXED_SPLITS 8u  /* always use the fixed-split grid + merge kernel, even when
+                                     semaphores are given (partials then follow split_size)    */
 
 /*
  * Operands of one decode-attention layer-step.
@@ -106,6 +108,14 @@ typedef struct pfd_decode_args {
   float* packed_output;
 
   void* stream; /* cudaStream_t */
+
+  /* Optional [batch * num_kv_heads] int32, all zero on entry and left all zero on return.
+   * With it (and head_dim 128, f32 partials, workspace_splits >= 2) the step runs as ONE
+   * kernel: a persistent grid shares the KV bytes of all sequences in equal chunks and the
+   * CTA that retires the last piece of a (sequence, kv head) merges the pieces itself.  The
+   * partial workspace then holds those pieces, not split_size-sized splits. */
+  int32_t* semaphores;
+  int64_t num_semaphores;
 } pfd_decode_args;
 
 /*
@@ -168,6 +178,13 @@ int pfd_resolve_slots(const int32_t* block_table, int64_t bt_stride_b, const int
  * output is then undefined).  The kernels never trap and never spin without a limit.
  */
 int pfd_device_status(int32_t* status);
+
+/*
+ * Debug aid for tuning: while `device_buffer` (uint64 [grid][8], device memory owned by the
+ * caller) is set, thread 0 of every CTA of the balanced kernel stores nanosecond timestamps
+ * (%globaltimer) of its phases there.  NULL switches it off (the default).
+ */
+int pfd_debug_phase_times(void* device_buffer);
 
 /* Number of kernels this library has launched in this process (for launch accounting). */
 int64_t pfd_launch_count(void);

@@ -18,6 +18,7 @@ PFD_DTYPE_F32, PFD_DTYPE_F16, PFD_DTYPE_BF16 = 0, 1, 2
 PFD_FLAG_NO_TMA = 1
 PFD_FLAG_NO_DIRECT_OUT = 2
 PFD_FLAG_PARTIAL_ONLY = 4
+PFD_FLAG_FIXED_SPLITS = 8
 
 EXPORTS = (
     "pfd_paged_decode_fp8_e4m3_split_out",
@@ -25,6 +26,7 @@ EXPORTS = (
     "pfd_merge_packed",
     "pfd_resolve_slots",
     "pfd_device_status",
+    "pfd_debug_phase_times",
     "pfd_launch_count",
     "pfd_last_error",
     "pfd_abi_version",
@@ -79,6 +81,8 @@ class DecodeArgs(C.Structure):
         ("o_stride_h", C.c_int64),
         ("packed_output", C.c_void_p),
         ("stream", C.c_void_p),
+        ("semaphores", C.c_void_p),
+        ("num_semaphores", C.c_int64),
     ]
 
 
@@ -167,6 +171,9 @@ def decode_args(
         a.partial_dtype = _dtype_code(po.dtype)
         a.partial_stride_b, a.partial_stride_h, a.partial_stride_s = pm.stride()
         a.workspace_splits = po.shape[2]
+        if len(workspace) > 4 and workspace[4] is not None:
+            a.semaphores = workspace[4].data_ptr()
+            a.num_semaphores = workspace[4].numel()
     if output is not None:
         a.output = output.data_ptr()
         a.o_stride_b, a.o_stride_h = output.stride(0), output.stride(1)

@@ -5,7 +5,7 @@
 //       integrations/vllm/cuda/l20_paged_decode.cpp:128-135 (schema), :138-143 (CUDA impl),
 //       :153-155 (pybind export of the same launcher)
 // and adds "paged_decode_fp8_e4m3_split_out_v2" (per-kv-head scale tensors, explicit softmax
-// scale, kv_start, optional packed (o, m, l) output) plus "merge_packed_partials" and
+// scale, kv_start, optional packed (o, m, l) output, optional semaphores for the one-kernel path) plus "merge_packed_partials" and
 // "resolve_slots".  Every op only unpacks tensors into the C ABI of libpaged_fp8_decode.so
 // (include/paged_fp8_decode.h); there is no computation here and no fallback.
 #include <ATen/cuda/CUDAContext.h>
@@ -33,7 +33,7 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
                 const c10::optional<at::Tensor>& packed_output, double k_scale, double v_scale,
                 const c10::optional<at::Tensor>& k_scale_ph, const c10::optional<at::Tensor>& v_scale_ph,
                 double sm_scale, int64_t max_seq_len, int64_t split_size, int64_t kv_start,
-                int64_t flags) {
+                int64_t flags, const c10::optional<at::Tensor>& semaphores = c10::nullopt) {
   TORCH_CHECK(query.is_cuda(), "query must be CUDA");
   TORCH_CHECK(query.scalar_type() == at::kHalf || query.scalar_type() == at::kBFloat16,
               "query must be FP16 or BF16");
@@ -139,6 +139,12 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
                 "packed_output must be float32 [B, Hq, D + 2]");
     a.packed_output = packed_output->data_ptr<float>();
   }
+  if (semaphores.has_value()) {
+    TORCH_CHECK(semaphores->is_cuda() && semaphores->scalar_type() == at::kInt && semaphores->is_contiguous(),
+                "semaphores must be a contiguous int32 CUDA tensor");
+    a.semaphores = semaphores->data_ptr<int32_t>();
+    a.num_semaphores = semaphores->numel();
+  }
   const at::cuda::CUDAGuard guard(query.device());
   a.stream = at::cuda::getCurrentCUDAStream().stream();
   const int rc = pfd_paged_decode_fp8_e4m3_split_out(&a);
@@ -176,11 +182,12 @@ void paged_decode_fp8_e4m3_split_out_v2(at::Tensor query, at::Tensor key_cache, 
                                         c10::optional<at::Tensor> output,
                                         c10::optional<at::Tensor> packed_output, at::Tensor k_scale,
                                         at::Tensor v_scale, double sm_scale, int64_t max_seq_len,
-                                        int64_t split_size, int64_t kv_start, int64_t flags) {
+                                        int64_t split_size, int64_t kv_start, int64_t flags,
+                                        c10::optional<at::Tensor> semaphores) {
   TORCH_CHECK(output.has_value() || packed_output.has_value(), "no output given");
   run_decode(query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max,
              partial_sum, output, packed_output, 1.0, 1.0, k_scale, v_scale, sm_scale, max_seq_len,
-             split_size, kv_start, flags);
+             split_size, kv_start, flags, semaphores);
 }
 
 void merge_packed_partials(at::Tensor packed, at::Tensor output) {
@@ -236,7 +243,7 @@ TORCH_LIBRARY(l20_stack, module) {
       "Tensor(a!)? partial_output, Tensor(b!)? partial_max, "
       "Tensor(c!)? partial_sum, Tensor(d!)? output, Tensor(e!)? packed_output, "
       "Tensor k_scale, Tensor v_scale, float sm_scale, "
-      "int max_seq_len, int split_size, int kv_start, int flags) -> ()");
+      "int max_seq_len, int split_size, int kv_start, int flags, Tensor(f!)? semaphores) -> ()");
   module.def("merge_packed_partials(Tensor packed, Tensor(a!) output) -> ()");
   module.def("resolve_slots(Tensor block_table, Tensor seq_lens, Tensor(a!) slots) -> ()");
 }

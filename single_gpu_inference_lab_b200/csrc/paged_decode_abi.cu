@@ -2,6 +2,7 @@
 // Declarations and reference citations: include/paged_fp8_decode.h.
 #include "paged_fp8_decode.h"
 
+#include <algorithm>
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
@@ -9,11 +10,13 @@
 #include <string>
 #include <vector>
 
+#include "paged_decode_balanced.cuh"
 #include "paged_decode_kernels.cuh"
 
 namespace {
 
 thread_local std::string g_last_error;
+unsigned long long* g_phase_times = nullptr;  // debug: per-CTA phase timestamps, set by pfd_debug_phase_times
 std::atomic<int64_t> g_launches{0};
 
 int fail(int code, const char* fmt, ...) {
@@ -36,7 +39,7 @@ int check_launch(const char* what) {
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 constexpr int kWarps = 4;
-constexpr int kStages = 4;
+constexpr int kStages = 2;
 constexpr int kMaxDevices = 64;
 
 // Error word the kernels write (bounded waits that gave up).  The name is a host-side stand-in
@@ -149,7 +152,7 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
   tp.head_is_dim1 = head_is_dim1(a.k_stride_token, a.k_stride_head) ? 1 : 0;
   if (int rc = status_pointer(&tp.status)) return rc;
   auto kernel = pfd::paged_decode_fp8_partial_tma_kernel<QBF16, kWarps, kStages>;
-  constexpr int smem = 1024 + kWarps * kStages * 4096 + kWarps * kStages * 8 + 2 * kWarps * 16 * 4;
+  constexpr int smem = 1024 + kWarps * kStages * 8192 + kWarps * kStages * 8 + 2 * kWarps * 16 * 4;
   static bool configured[kMaxDevices] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -162,9 +165,82 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
   return check_launch("partial kernel (TMA)");
 }
 
+// ---- balanced persistent kernel -------------------------------------------------------------
+constexpr int kBalStages = 2;
+
+bool balanced_eligible(const pfd_decode_args& a) {
+  if (a.flags & (PFD_FLAG_FIXED_SPLITS | PFD_FLAG_PARTIAL_ONLY | PFD_FLAG_NO_DIRECT_OUT)) return false;
+  if (!tma_eligible(a)) return false;
+  if (a.semaphores == nullptr || a.num_semaphores < (int64_t)a.batch * a.num_kv_heads) return false;
+  if (!a.partial_output || !a.partial_max || !a.partial_sum || a.partial_dtype != PFD_DTYPE_F32) return false;
+  if (a.workspace_splits < 2 || a.batch > 8192) return false;
+  return true;
+}
+
+template <bool QBF16, int NH>
+int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, cudaStream_t stream) {
+  CUtensorMap mk, mv;
+  if (int rc = get_tensor_map(a.key_cache, a.k_stride_page, a.k_stride_token, a.k_stride_head, a.num_pages,
+                              a.num_kv_heads, &mk))
+    return rc;
+  if (int rc = get_tensor_map(a.value_cache, a.v_stride_page, a.v_stride_token, a.v_stride_head, a.num_pages,
+                              a.num_kv_heads, &mv))
+    return rc;
+  pfd::TmaParams tp{};
+  tp.head_is_dim1 = head_is_dim1(a.k_stride_token, a.k_stride_head) ? 1 : 0;
+  if (int rc = status_pointer(&tp.status)) return rc;
+  tp.phase_times = g_phase_times;
+  auto kernel = pfd::paged_decode_fp8_balanced_kernel<QBF16, NH, kBalStages>;
+  constexpr int kThreads = (pfd::kComputeWarps + 1) * 32;
+  const int rows = 8 * NH;
+  const int smem = 1024 + kWarps * kBalStages * 8192 + kWarps * kBalStages * 8 + rows * 128 * 4 +
+                   2 * kWarps * rows * 4 + (8 + kWarps) * 4 + (2 * a.batch + 1) * 4 + 16;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDevices) return fail(PFD_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  // per device: SM count, and the largest dynamic shared memory size configured so far
+  static int sm_count[kMaxDevices] = {0};
+  static int smem_set[kMaxDevices][2][2] = {};
+  {
+    std::lock_guard<std::mutex> lock(g_state_mutex);
+    if (sm_count[dev] == 0) {
+      const cudaError_t e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaDeviceGetAttribute failed: %s", cudaGetErrorString(e));
+    }
+    int& have = smem_set[dev][QBF16 ? 1 : 0][NH - 1];
+    if (smem > have) {
+      const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+      if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+      have = smem;
+    }
+  }
+  int per_sm = 0;
+  {
+    const cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem);
+    if (e != cudaSuccess || per_sm < 1)
+      return fail(PFD_ERR_CUDA, "balanced kernel does not fit on an SM (%d bytes of shared memory)", smem);
+  }
+  const int max_pages = (a.max_seq_len + pfd::kPage - 1) / pfd::kPage - a.kv_start / pfd::kPage;
+  const int max_pairs = (std::max(max_pages, 0) + 1) / 2;
+  pfd::BalancedParams bp{};
+  bp.batch = a.batch;
+  bp.workspace_splits = a.workspace_splits;
+  bp.min_chunk = std::max(1, (max_pairs + a.workspace_splits - 2) / (a.workspace_splits - 1));
+  bp.semaphores = a.semaphores;
+  // never more CTAs than the largest possible number of pairs
+  const int64_t pair_bound = (int64_t)max_pairs * a.batch * a.num_kv_heads;
+  int grid = sm_count[dev] * per_sm;
+  if (pair_bound < grid) grid = (int)std::max<int64_t>(pair_bound, 1);
+  kernel<<<grid, kThreads, smem, stream>>>(kp, tp, bp, mk, mv);
+  return check_launch("balanced decode kernel");
+}
+
 template <int D, bool QBF16>
 int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num_splits) {
   cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
+  if (D == 128 && balanced_eligible(a)) {
+    return kp.group <= 8 ? launch_balanced<QBF16, 1>(a, kp, stream) : launch_balanced<QBF16, 2>(a, kp, stream);
+  }
   const dim3 grid(num_splits, a.num_kv_heads, a.batch);
   if (D == 128 && tma_eligible(a)) {
     if (int rc = launch_partial_tma<QBF16>(a, kp, grid, stream)) return rc;
@@ -264,6 +340,7 @@ int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args) {
   kp.split_size = a.split_size; kp.kv_start = a.kv_start;
   kp.partial_dtype = a.partial_dtype;
   kp.direct_out = direct_ok ? 1 : 0;
+  kp.bt_cols = (a.max_seq_len + pfd::kPage - 1) / pfd::kPage;  // rows are at least this wide
 
   const bool bf16 = a.query_dtype == PFD_DTYPE_BF16;
   if (a.head_dim == 128)
@@ -328,6 +405,11 @@ int pfd_paged_decode_fp8_e4m3_split_out_noalloc(const pfd_decode_args* args) {
   a.partial_stride_h = splits;
   a.partial_stride_s = 1;
   return pfd_paged_decode_fp8_e4m3_split_out(&a);
+}
+
+int pfd_debug_phase_times(void* device_buffer) {
+  g_phase_times = static_cast<unsigned long long*>(device_buffer);
+  return PFD_OK;
 }
 
 int pfd_device_status(int32_t* status) {

@@ -53,6 +53,7 @@ struct KernelParams {
   int32_t split_size, kv_start;
   int32_t partial_dtype;
   int32_t direct_out;  // 1: a sequence with a single split writes its final result itself
+  int32_t bt_cols;     // width of a block-table row
 };
 
 // The one address function every kernel uses for "which cache slot holds token t of
@@ -82,7 +83,7 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
 // D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
 __device__ __forceinline__ void mma_m16n8k16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
                                              uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
@@ -158,17 +159,19 @@ struct WarpState {
 // ---- the three phases of one 16-token tile ------------------------------------------------
 // tok0 = global token index of row 0 of the page; tokens outside [lo, hi) are masked.
 
-// S = Q K^T for both 8-column tiles (raw, unscaled).
-template <int D>
-__device__ __forceinline__ void qk_scores(float (&s)[2][4], const uint32_t (&k)[2][D / 64][4],
+// S = Q K^T for NT 8-column tiles (raw, unscaled); k-steps outermost so that consecutive MMAs
+// belong to independent accumulators.
+template <int D, int NT>
+__device__ __forceinline__ void qk_scores(float (&s)[NT][4], const uint32_t (&k)[NT][D / 64][4],
                                           const uint32_t (&qa)[D / 16][4]) {
 #pragma unroll
-  for (int nt = 0; nt < 2; ++nt) {
-    s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+  for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
-    for (int l = 0; l < D / 64; ++l) {
+  for (int l = 0; l < D / 64; ++l) {
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < 4; ++w) {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
         const uint32_t word = k[nt][l][w];
         mma_m16n8k16(s[nt], qa[l * 4 + w], cvt_e4m3x2_to_f16x2(word),
                      cvt_e4m3x2_to_f16x2(word >> 16));
@@ -177,13 +180,14 @@ __device__ __forceinline__ void qk_scores(float (&s)[2][4], const uint32_t (&k)[
   }
 }
 
-// Scale, mask, online softmax; rescales O and returns P as the f16 A-fragment of the PV MMA.
-template <int D>
-__device__ __forceinline__ void softmax_step(WarpState<D>& st, float (&s)[2][4], uint32_t (&pa)[4],
-                                             float scale_log2, bool edge, int tok0, int lo, int hi,
-                                             int j) {
+// Scale, mask, online softmax over NT/2 pages; rescales O and returns P as the f16 A-fragments
+// of the PV MMAs (pa[t] for page t).  Column tile nt covers tokens tok0 + 8*nt + rho(.).
+template <int D, int NT>
+__device__ __forceinline__ void softmax_step(WarpState<D>& st, float (&s)[NT][4],
+                                             uint32_t (&pa)[NT / 2][4], float scale_log2, bool edge,
+                                             int tok0, int lo, int hi, int j) {
 #pragma unroll
-  for (int nt = 0; nt < 2; ++nt) {
+  for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       float x = s[nt][c] * scale_log2;
@@ -194,8 +198,12 @@ __device__ __forceinline__ void softmax_step(WarpState<D>& st, float (&s)[2][4],
       s[nt][c] = x;
     }
   }
-  float mx0 = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-  float mx1 = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+  float mx0 = fmaxf(s[0][0], s[0][1]), mx1 = fmaxf(s[0][2], s[0][3]);
+#pragma unroll
+  for (int nt = 1; nt < NT; ++nt) {
+    mx0 = fmaxf(mx0, fmaxf(s[nt][0], s[nt][1]));
+    mx1 = fmaxf(mx1, fmaxf(s[nt][2], s[nt][3]));
+  }
   mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
   mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
   mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
@@ -206,20 +214,18 @@ __device__ __forceinline__ void softmax_step(WarpState<D>& st, float (&s)[2][4],
   const float alpha1 = exp2f(st.m[1] - mn1);
   st.m[0] = mn0;
   st.m[1] = mn1;
-  float p[2][4];
+  float sum0 = 0.f, sum1 = 0.f;
 #pragma unroll
-  for (int nt = 0; nt < 2; ++nt) {
-    p[nt][0] = exp2f(s[nt][0] - mn0);
-    p[nt][1] = exp2f(s[nt][1] - mn0);
-    p[nt][2] = exp2f(s[nt][2] - mn1);
-    p[nt][3] = exp2f(s[nt][3] - mn1);
+  for (int nt = 0; nt < NT; ++nt) {
+    const float p0 = exp2f(s[nt][0] - mn0), p1 = exp2f(s[nt][1] - mn0);
+    const float p2 = exp2f(s[nt][2] - mn1), p3 = exp2f(s[nt][3] - mn1);
+    sum0 += p0 + p1;
+    sum1 += p2 + p3;
+    pa[nt >> 1][(nt & 1) * 2 + 0] = pack_f16x2(p0, p1);
+    pa[nt >> 1][(nt & 1) * 2 + 1] = pack_f16x2(p2, p3);
   }
-  st.l[0] = st.l[0] * alpha0 + ((p[0][0] + p[0][1]) + (p[1][0] + p[1][1]));
-  st.l[1] = st.l[1] * alpha1 + ((p[0][2] + p[0][3]) + (p[1][2] + p[1][3]));
-  pa[0] = pack_f16x2(p[0][0], p[0][1]);
-  pa[1] = pack_f16x2(p[0][2], p[0][3]);
-  pa[2] = pack_f16x2(p[1][0], p[1][1]);
-  pa[3] = pack_f16x2(p[1][2], p[1][3]);
+  st.l[0] = st.l[0] * alpha0 + sum0;
+  st.l[1] = st.l[1] * alpha1 + sum1;
   // the running max rarely moves after the first tiles: skip the 4*D/8 multiplies then
   if (__any_sync(0xffffffffu, (alpha0 != 1.f) | (alpha1 != 1.f))) {
 #pragma unroll
@@ -266,11 +272,11 @@ __device__ __forceinline__ void consume_tile(WarpState<D>& st, TileRegs<D>& t,
                                              const uint32_t (&qa)[D / 16][4], float scale_log2,
                                              int tok0, int lo, int hi, int j) {
   float s[2][4];
-  uint32_t pa[4];
+  uint32_t pa[1][4];
   const bool edge = (tok0 < lo) | (tok0 + kPage > hi);
-  qk_scores<D>(s, t.k, qa);
-  softmax_step<D>(st, s, pa, scale_log2, edge, tok0, lo, hi, j);
-  pv_accumulate<D>(st, t.v, pa, edge, tok0, lo, hi, j);
+  qk_scores<D, 2>(s, t.k, qa);
+  softmax_step<D, 2>(st, s, pa, scale_log2, edge, tok0, lo, hi, j);
+  pv_accumulate<D>(st, t.v, pa[0], edge, tok0, lo, hi, j);
 }
 
 // Q rows i and i+8 of the kv head's group as f16 A-fragments, d permuted to match the K loads:
@@ -360,25 +366,36 @@ __device__ __forceinline__ void cta_merge_and_store(WarpState<D>& st, const Kern
     sm_l[warp * 16 + i] = st.l[0] * f0;
     sm_l[warp * 16 + i + 8] = st.l[1] * f1;
   }
+  // Thread (i, j) owns d = (D/4)*j + (D/8)*e + m of rows i and i+8: as float4 chunks
+  // q = (D/16)*j + (D/32)*e + m/4.  The chunk index is XOR-swizzled with (j + 4*(i&1)) so that
+  // the eight lanes of a store phase hit eight different 16-byte bank groups.
   constexpr int CB = D / 8;
+  const int swz = (D == 128) ? ((j + 4 * (i & 1)) & 7) : 0;
 #pragma unroll
-  for (int m = 0; m < CB; ++m) {
-    // c0,c1 -> cols 2j, 2j+1 of n-tile m -> d = CB*(2j+e) + m
-    sm_o[(warp * 16 + i) * D + CB * (2 * j) + m] = st.o[m][0] * f0;
-    sm_o[(warp * 16 + i) * D + CB * (2 * j + 1) + m] = st.o[m][1] * f0;
-    sm_o[(warp * 16 + i + 8) * D + CB * (2 * j) + m] = st.o[m][2] * f1;
-    sm_o[(warp * 16 + i + 8) * D + CB * (2 * j + 1) + m] = st.o[m][3] * f1;
+  for (int e = 0; e < 2; ++e) {
+#pragma unroll
+    for (int m4 = 0; m4 < CB / 4; ++m4) {
+      const int q = ((D / 16) * j + (D / 32) * e + m4) ^ swz;
+      *reinterpret_cast<float4*>(sm_o + (warp * 16 + i) * D + 4 * q) =
+          make_float4(st.o[4 * m4][e] * f0, st.o[4 * m4 + 1][e] * f0, st.o[4 * m4 + 2][e] * f0,
+                      st.o[4 * m4 + 3][e] * f0);
+      *reinterpret_cast<float4*>(sm_o + (warp * 16 + i + 8) * D + 4 * q) =
+          make_float4(st.o[4 * m4][2 + e] * f1, st.o[4 * m4 + 1][2 + e] * f1,
+                      st.o[4 * m4 + 2][2 + e] * f1, st.o[4 * m4 + 3][2 + e] * f1);
+    }
   }
   __syncthreads();
   const bool direct = p.direct_out && nsplits_seq == 1;
   // g rows x D columns, 4 columns per thread-iteration
   for (int e = threadIdx.x; e < p.group * (D / 4); e += NWARPS * 32) {
     const int row = e / (D / 4), c4 = (e % (D / 4)) * 4;
+    const int ql = c4 >> 2;
+    const int qs = (D == 128) ? (ql ^ (((ql >> 3) + 4 * (row & 1)) & 7)) : ql;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float lsum = 0.f;
 #pragma unroll
     for (int w = 0; w < NWARPS; ++w) {
-      const float4 x = *reinterpret_cast<const float4*>(sm_o + (w * 16 + row) * D + c4);
+      const float4 x = *reinterpret_cast<const float4*>(sm_o + (w * 16 + row) * D + 4 * qs);
       acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
       lsum += sm_l[w * 16 + row];
     }
@@ -513,32 +530,55 @@ __device__ __forceinline__ uint4 lds_16(uint32_t addr) {
 struct TmaParams {
   int32_t head_is_dim1;  // 1: tensor-map dims are (D, head, token, page); 0: (D, token, head, page)
   int32_t* status;       // device error word (0 = ok)
+  unsigned long long* phase_times;  // optional [grid][8] nanosecond timestamps of a CTA's phases
 };
+
+__device__ __forceinline__ void mark_phase(const TmaParams& tp, int k, bool leader) {
+  if (tp.phase_times != nullptr && leader) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    tp.phase_times[(size_t)blockIdx.x * 8 + k] = t;
+  }
+}
+__device__ __forceinline__ void mark_phase(const TmaParams& tp, int k) { mark_phase(tp, k, threadIdx.x == 0); }
 
 constexpr int kErrTmaTimeout = 1;
 
 // Split-KV partial kernel for head_dim 128, K/V tiles staged by TMA.
 //
-// Every warp owns a private ring of NSTAGE stages of 4 KiB (K tile [16][128] + V tile
-// [16][128], 128-byte swizzled, 1 KiB aligned) and one mbarrier per stage; its lane 0 issues
-// the two tiled TMA loads of the warp's next page as soon as the warp has finished reading a
-// stage.  Warps never synchronise with each other inside the loop.  Up to NSTAGE * 4 KiB per
-// warp are in flight, independent of registers.
+// Every warp owns a private ring of NSTAGE stages and one mbarrier per stage.  A stage holds
+// two consecutive pages (32 tokens): [K0][K1][V0][V1], each tile [16][128] bytes, 128-byte
+// swizzled and 1 KiB aligned (8 KiB per stage).  Lane 0 issues the tiled TMA loads of the
+// warp's next page pair as soon as the warp has consumed a stage; warps never synchronise with
+// each other inside the loop, and the bytes in flight do not cost registers.  Two pages per
+// step give four independent QK^T accumulator chains and halve the per-token cost of the
+// softmax bookkeeping (shuffles, rescale).
 template <bool QBF16, int NWARPS, int NSTAGE>
 __global__ void __launch_bounds__(NWARPS * 32)
 paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
                                     const __grid_constant__ CUtensorMap tmap_k,
                                     const __grid_constant__ CUtensorMap tmap_v) {
   constexpr int D = 128;
-  constexpr uint32_t kTileBytes = kPage * D;      // 2 KiB
-  constexpr uint32_t kStageBytes = 2 * kTileBytes;
+  constexpr uint32_t kTileBytes = kPage * D;  // 2 KiB
+  constexpr uint32_t kStageBytes = 4 * kTileBytes;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-  const int seq_len = p.seq_lens[b];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
   const int lo = p.kv_start + split * p.split_size;
+
+  // Page ids of this warp's first 16 page pairs, one page per lane, fetched before the
+  // sequence length is known (the block-table row is bt_cols wide, so this stays inside it).
+  const int page_first = lo / kPage;
+  auto my_page = [&](int pair, int u) { return page_first + (warp + pair * NWARPS) * 2 + u; };
+  int ids_base = 0;
+  int32_t ids = 0;
+  {
+    const int pg = my_page(lane >> 1, lane & 1);
+    if (pg < p.bt_cols) ids = page_of(p.block_table, p.bt_stride_b, b, pg);
+  }
+  const int seq_len = p.seq_lens[b];
   const int hi = min(lo + p.split_size, seq_len);
   if (lo >= hi) return;
   const int nsplits_seq = (seq_len - p.kv_start + p.split_size - 1) / p.split_size;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -559,27 +599,30 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   }
   __syncwarp();
 
-  const int page_first = lo / kPage, page_last = (hi - 1) / kPage;
-  const int n_tiles = (page_last - page_first - warp + NWARPS) / NWARPS;  // pages warp, warp+NWARPS, ...
-  // page ids of this warp's next 32 tiles, one per lane
-  int ids_base = 0;
-  int32_t ids = 0;
-  if (lane < n_tiles) ids = page_of(p.block_table, p.bt_stride_b, b, page_first + warp + lane * NWARPS);
+  const int page_last = (hi - 1) / kPage;
+  const int n_pairs_cta = (page_last - page_first + 2) / 2;
+  const int n_pairs = (n_pairs_cta - warp + NWARPS - 1) / NWARPS;  // pairs warp, warp+NWARPS, ...
 
-  auto issue = [&](int t, int32_t phys) {  // lane 0 only
+  auto issue = [&](int t, int32_t phys0, int32_t phys1) {  // lane 0 only
     const int s = t % NSTAGE;
     const uint32_t bar = my_bars + 8 * s;
     const uint32_t dst = my_ring + s * kStageBytes;
-    mbar_expect_tx(bar, kStageBytes);
+    const bool two = my_page(t, 1) <= page_last;
+    mbar_expect_tx(bar, two ? kStageBytes : kStageBytes / 2);
     const int c1 = tp.head_is_dim1 ? kvh : 0;
     const int c2 = tp.head_is_dim1 ? 0 : kvh;
-    tma_load_tile(dst, &tmap_k, bar, c1, c2, phys);
-    tma_load_tile(dst + kTileBytes, &tmap_v, bar, c1, c2, phys);
+    tma_load_tile(dst, &tmap_k, bar, c1, c2, phys0);
+    tma_load_tile(dst + 2 * kTileBytes, &tmap_v, bar, c1, c2, phys0);
+    if (two) {
+      tma_load_tile(dst + kTileBytes, &tmap_k, bar, c1, c2, phys1);
+      tma_load_tile(dst + 3 * kTileBytes, &tmap_v, bar, c1, c2, phys1);
+    }
   };
 #pragma unroll
   for (int t = 0; t < NSTAGE; ++t) {
-    const int32_t phys = __shfl_sync(0xffffffffu, ids, t & 31);
-    if (lane == 0 && t < n_tiles) issue(t, phys);
+    const int32_t phys0 = __shfl_sync(0xffffffffu, ids, (2 * t) & 31);
+    const int32_t phys1 = __shfl_sync(0xffffffffu, ids, (2 * t + 1) & 31);
+    if (lane == 0 && t < n_pairs) issue(t, phys0, phys1);
   }
 
   uint32_t qa[D / 16][4];
@@ -594,7 +637,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   st.m[0] = st.m[1] = -INFINITY;
   st.l[0] = st.l[1] = 0.f;
 
-  // swizzled shared-memory offsets of this thread's fragments inside a stage
+  // swizzled shared-memory offsets of this thread's fragments inside a tile
   uint32_t k_off[2][2], v_off[4];
 #pragma unroll
   for (int nt = 0; nt < 2; ++nt)
@@ -604,54 +647,60 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
     const int row = v_row(j, r);
-    v_off[r] = kTileBytes + row * D + ((i ^ (row & 7)) << 4);
+    v_off[r] = row * D + ((i ^ (row & 7)) << 4);
   }
 
   bool ok = true;
   int t = 0;
-  for (; t < n_tiles; ++t) {
+  for (; t < n_pairs; ++t) {
     const int s = t % NSTAGE;
     const uint32_t parity = (t / NSTAGE) & 1;
     if (!mbar_wait_bounded(my_bars + 8 * s, parity)) { ok = false; break; }
     const uint32_t stage = my_ring + s * kStageBytes;
-    const int tok0 = (page_first + warp + t * NWARPS) * kPage;
-    const bool edge = (tok0 < lo) | (tok0 + kPage > hi);
-    float sc[2][4];
-    uint32_t pa[4];
+    const int tok0 = my_page(t, 0) * kPage;
+    // the second page of the last pair may not exist: its (stale) bytes are masked like any
+    // token beyond `hi`
+    const bool edge = (tok0 < lo) | (tok0 + 2 * kPage > hi);
+    float sc[4][4];
+    uint32_t pa[2][4];
     {
-      uint32_t k[2][2][4];
+      uint32_t k[4][2][4];
 #pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
+      for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
         for (int l = 0; l < 2; ++l) {
-          const uint4 x = lds_16(stage + k_off[nt][l]);
+          const uint4 x = lds_16(stage + (nt >> 1) * kTileBytes + k_off[nt & 1][l]);
           k[nt][l][0] = x.x; k[nt][l][1] = x.y; k[nt][l][2] = x.z; k[nt][l][3] = x.w;
         }
-      qk_scores<D>(sc, k, qa);
+      qk_scores<D, 4>(sc, k, qa);
     }
-    uint32_t v[4][4];
+    softmax_step<D, 4>(st, sc, pa, scale_log2, edge, tok0, lo, hi, j);
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const uint4 x = lds_16(stage + v_off[r]);
-      v[r][0] = x.x; v[r][1] = x.y; v[r][2] = x.z; v[r][3] = x.w;
+    for (int u = 0; u < 2; ++u) {
+      uint32_t v[4][4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const uint4 x = lds_16(stage + (2 + u) * kTileBytes + v_off[r]);
+        v[r][0] = x.x; v[r][1] = x.y; v[r][2] = x.z; v[r][3] = x.w;
+      }
+      pv_accumulate<D>(st, v, pa[u], edge, tok0 + u * kPage, lo, hi, j);
     }
-    softmax_step<D>(st, sc, pa, scale_log2, edge, tok0, lo, hi, j);
-    pv_accumulate<D>(st, v, pa, edge, tok0, lo, hi, j);
     // Every byte this warp read from the stage has been consumed by an MMA above, so the
-    // reads are complete: hand the stage back to TMA for the warp's tile t + NSTAGE.
+    // reads are complete: hand the stage back to TMA for the warp's pair t + NSTAGE.
     __syncwarp();
     const int tn = t + NSTAGE;
-    if (tn < n_tiles) {
-      if ((tn & 31) == 0) {  // next batch of 32 page ids
+    if (tn < n_pairs) {
+      if ((tn & 15) == 0) {  // next batch of 16 page pairs
         ids_base = tn;
         ids = 0;
-        if (tn + lane < n_tiles)
-          ids = page_of(p.block_table, p.bt_stride_b, b, page_first + warp + (tn + lane) * NWARPS);
+        const int pg = my_page(tn + (lane >> 1), lane & 1);
+        if (pg <= page_last) ids = page_of(p.block_table, p.bt_stride_b, b, pg);
       }
-      const int32_t phys = __shfl_sync(0xffffffffu, ids, (tn - ids_base) & 31);
+      const int32_t phys0 = __shfl_sync(0xffffffffu, ids, (2 * (tn - ids_base)) & 31);
+      const int32_t phys1 = __shfl_sync(0xffffffffu, ids, (2 * (tn - ids_base) + 1) & 31);
       if (lane == 0) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        issue(tn, phys);
+        issue(tn, phys0, phys1);
       }
     }
   }
@@ -660,7 +709,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
     // land before the ring is reused by the merge below.
     if (lane == 0) {
       atomicExch(tp.status, kErrTmaTimeout);
-      const int issued = min(n_tiles, t + NSTAGE);
+      const int issued = min(n_pairs, t + NSTAGE);
       for (int u = t + 1; u < issued; ++u) mbar_wait_bounded(my_bars + 8 * (u % NSTAGE), (u / NSTAGE) & 1);
     }
     __syncwarp();

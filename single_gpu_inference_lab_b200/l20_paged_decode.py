@@ -85,10 +85,13 @@ def paged_decode_fp8_e4m3_split_out_v2(
     sm_scale: float = 0.0,
     kv_start: int = 0,
     flags: int = 0,
+    semaphores: Optional[torch.Tensor] = None,
 ) -> Optional[torch.Tensor]:
     """Superset op: ``[Hkv]`` scale tensors (per layer and kv head), explicit softmax scale
     (0 = ``D**-0.5``), first attended token ``kv_start`` and, instead of or besides
-    ``output``, a packed fp32 ``[B, Hq, D + 2]`` ``(o, m, l)`` for cross-GPU merging."""
+    ``output``, a packed fp32 ``[B, Hq, D + 2]`` ``(o, m, l)`` for cross-GPU merging.
+    ``semaphores`` (int32 ``[B * Hkv]``, zero on entry, left zero) selects the one-kernel
+    balanced path for head_dim 128."""
     torch.ops.l20_stack.paged_decode_fp8_e4m3_split_out_v2(
         query,
         key_cache,
@@ -107,6 +110,7 @@ def paged_decode_fp8_e4m3_split_out_v2(
         split_size,
         kv_start,
         flags,
+        semaphores,
     )
     return output
 

@@ -42,9 +42,12 @@ def allocate_l20_paged_split_kv_workspace(
     max_seq_len: int,
     *,
     split_size: int = 512,
-) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-    """``(partial_output [B,Hq,S,D] f32, partial_max [B,Hq,S] f32, partial_sum, output)`` with
-    ``S = next_pow2(ceil(max_seq_len / split_size))`` as in the reference (:21-22)."""
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``(partial_output [B,Hq,S,D] f32, partial_max [B,Hq,S] f32, partial_sum, output,
+    semaphores)`` with ``S = next_pow2(ceil(max_seq_len / split_size))`` as in the reference
+    (:21-22).  The fifth entry (int32 zeros, one per sequence and head -- enough for any GQA
+    ratio) is what lets the operator run as one balanced kernel; callers that pass the tuple
+    through unchanged, as the reference hook does, get it for free."""
     batch, num_q_heads, head_dim = query.shape
     num_splits = _next_power_of_two(_cdiv(max_seq_len, split_size))
     partial_shape = (batch, num_q_heads, num_splits)
@@ -53,6 +56,7 @@ def allocate_l20_paged_split_kv_workspace(
         torch.empty(partial_shape, device=query.device, dtype=torch.float32),
         torch.empty(partial_shape, device=query.device, dtype=torch.float32),
         torch.empty_like(query),
+        torch.zeros(batch * num_q_heads, device=query.device, dtype=torch.int32),
     )
 
 
@@ -79,7 +83,7 @@ def l20_paged_split_kv_attention_fp8(
     max_seq_len: int | None = None,
     split_size: int = 512,
     output: torch.Tensor | None = None,
-    workspace: tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor] | None = None,
+    workspace: tuple[torch.Tensor, ...] | None = None,
 ) -> torch.Tensor:
     if not query.is_cuda or torch.cuda.get_device_capability(query.device) != REQUIRED_CAPABILITY:
         raise RuntimeError("requires an SM100 GPU")
@@ -105,7 +109,8 @@ def l20_paged_split_kv_attention_fp8(
     partial_shape = (batch, num_q_heads, num_splits)
     if workspace is None:
         workspace = allocate_l20_paged_split_kv_workspace(query, max_seq_len, split_size=split_size)
-    partial_output, partial_max, partial_sum, workspace_output = workspace
+    partial_output, partial_max, partial_sum, workspace_output = workspace[:4]
+    semaphores = workspace[4] if len(workspace) > 4 else None
     if output is None:
         output = workspace_output
     if (
@@ -116,7 +121,7 @@ def l20_paged_split_kv_attention_fp8(
     ):
         raise RuntimeError("paged split-KV workspace shape does not match the request")
     ops = _ops()
-    if isinstance(k_scale, torch.Tensor) or isinstance(v_scale, torch.Tensor):
+    if isinstance(k_scale, torch.Tensor) or isinstance(v_scale, torch.Tensor) or semaphores is not None:
         def as_vec(s):
             if isinstance(s, torch.Tensor):
                 return s.to(device=query.device, dtype=torch.float32).reshape(-1).expand(num_kv_heads).contiguous()
@@ -125,7 +130,7 @@ def l20_paged_split_kv_attention_fp8(
         ops.paged_decode_fp8_e4m3_split_out_v2(
             query, key_cache, value_cache, block_table, seq_lens,
             partial_output, partial_max, partial_sum, output,
-            as_vec(k_scale), as_vec(v_scale), max_seq_len, split_size,
+            as_vec(k_scale), as_vec(v_scale), max_seq_len, split_size, semaphores=semaphores,
         )
         return output
     return ops.paged_decode_fp8_e4m3_split_out(

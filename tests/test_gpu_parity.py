@@ -27,14 +27,19 @@ def cabi(built_libs):
     return module
 
 
-def workspace(q, max_seq_len, split_size, dtype=torch.float32, kv_start=0, poison=True):
+def workspace(q, max_seq_len, split_size, dtype=torch.float32, kv_start=0, poison=True, semaphores=True):
+    """(partial_output, partial_max, partial_sum, None, semaphores).  With semaphores (and
+    head_dim 128, f32 partials, flags 0) the library takes its one-kernel balanced path, which
+    needs a split axis of at least 2; flags 8 / 1 select the fixed-split TMA / plain-load paths."""
     b, hq, d = q.shape
-    s = max(1, -(-(max_seq_len - kv_start) // split_size))
+    s = max(2 if semaphores else 1, -(-(max_seq_len - kv_start) // split_size))
     fill = float("nan") if poison else 0.0
     return (
         torch.full((b, hq, s, d), fill, device=q.device, dtype=dtype),
         torch.full((b, hq, s), fill, device=q.device, dtype=torch.float32),
         torch.full((b, hq, s), fill, device=q.device, dtype=torch.float32),
+        None,
+        torch.zeros(b * hq, device=q.device, dtype=torch.int32) if semaphores else None,
     )
 
 
@@ -55,6 +60,7 @@ def run(cabi, w, split_size, *, flags=0, kv_start=0, partial_dtype=torch.float32
     )
     torch.cuda.synchronize()
     assert cabi.device_status() == 0, "a bounded device-side wait gave up"
+    assert int(ws[4].abs().sum()) == 0, "semaphores must be left at zero"
     return pk if packed else out
 
 
@@ -66,7 +72,7 @@ def expected(w, **kw):
 @pytest.mark.parametrize(
     "name", ["cfg1-qwen0.5b-b8", "cfg2-coder3b-b4", "cfg3-qwen7b-b24", "cfg4-llama8b-b2", "cfg5-prefix-b8"]
 )
-@pytest.mark.parametrize("flags", [0, 1])
+@pytest.mark.parametrize("flags", [0, 8, 1])
 def test_against_committed_reference_outputs(cabi, golden, name, flags):
     case = golden["cases"][name]
     w = make_inputs(case["workload"], seed=0, device="cpu", batch=case["batch"], shrink=case["shrink"])
@@ -102,15 +108,16 @@ def test_config1_full_size(cabi):
 def test_config2_full_size(cabi):
     w = make_inputs("qwen2.5-coder-3b-b64", seed=0)
     exp = expected(w)
-    for split in (256, 512):
-        assert_within_gate(run(cabi, w.to(DEV), split), exp, f"cfg2 split={split}")
+    for split, flags in ((256, 0), (512, 0), (512, 8), (1024, 1)):
+        assert_within_gate(run(cabi, w.to(DEV), split, flags=flags), exp, f"cfg2 split={split} flags={flags}")
 
 
 def test_config3_full_size_log_uniform_lengths(cabi):
     w = make_inputs("qwen2.5-7b-b256", seed=0)
     assert int(w.seq_lens.min()) <= 4
     exp = expected(w)
-    assert_within_gate(run(cabi, w.to(DEV), 512), exp, "cfg3")
+    for flags in (0, 8):
+        assert_within_gate(run(cabi, w.to(DEV), 512, flags=flags), exp, f"cfg3 flags={flags}")
 
 
 def test_config4_long_context_sampled_rows_and_split_invariance(cabi):
@@ -119,7 +126,7 @@ def test_config4_long_context_sampled_rows_and_split_invariance(cabi):
     split invariance covers the rest."""
     w = make_inputs("llama3-8b-long-b4", seed=0, device=DEV)
     out_a = run(cabi, w, 2048)
-    out_b = run(cabi, w, 512)
+    out_b = run(cabi, w, 512, flags=8)
     out_c = run(cabi, w, 8192)
     assert_within_gate(out_b, out_a, "split 512 vs 2048")
     assert_within_gate(out_c, out_a, "split 8192 vs 2048")
@@ -137,7 +144,8 @@ def test_config4_long_context_sampled_rows_and_split_invariance(cabi):
 def test_config5_shared_prefix_full_size(cabi):
     w = make_inputs("shared-prefix-b64", seed=0)
     exp = expected(w)
-    assert_within_gate(run(cabi, w.to(DEV), 512), exp, "cfg5")
+    for flags in (0, 8):
+        assert_within_gate(run(cabi, w.to(DEV), 512, flags=flags), exp, f"cfg5 flags={flags}")
 
 
 # ---------------------------------------------------------------- edge cases
@@ -154,7 +162,7 @@ def test_every_short_context_length(cabi, d, hq, hkv):
     q = torch.randn(b, hq, d).to(torch.bfloat16)
     exp = oracle.reference(q, kc, vc, table.long(), lens, ks, vs)
     for split in (16, 32, 64, 512):
-        for flags in (0, 1, 2):
+        for flags in (0, 8, 1, 2):
             out = torch.full_like(q, float("nan"), device=DEV)
             ws = workspace(q.to(DEV), 70, split)
             cabi.paged_decode_fp8_e4m3_split_out(
@@ -179,7 +187,7 @@ def test_unused_slots_may_hold_nan_bytes(cabi):
             kc[page, n % 16 :] = 0x7F
             vc[page, n % 16 :] = 0xFF
     w.key_cache, w.value_cache = kc.view(torch.float8_e4m3fn), vc.view(torch.float8_e4m3fn)
-    for flags in (0, 1):
+    for flags in (0, 8, 1):
         assert_within_gate(run(cabi, w.to(DEV), 64, flags=flags), exp, "nan slots")
 
 
@@ -227,7 +235,7 @@ def test_strided_cache_layouts(cabi, layout):
         big2[:, :, :hkv] = g.value_cache
         g.key_cache, g.value_cache = big[:, :, :hkv], big2[:, :, :hkv]
     assert not g.key_cache.is_contiguous()
-    for flags in (0, 1):
+    for flags in (0, 8, 1):
         assert_within_gate(run(cabi, g, 64, flags=flags), exp, layout)
 
 
@@ -291,7 +299,7 @@ def test_partials_match_oracle_split_semantics(cabi):
         max_seq_len=w.max_seq_len, split_size=split, output=out, workspace=ws, flags=2,
     )
     torch.cuda.synchronize()
-    po, pm, ps = (t.cpu() for t in ws)
+    po, pm, ps = (t.cpu() for t in ws[:3])
     for b in range(4):
         live = -(-int(w.seq_lens[b]) // split)
         assert torch.allclose(pm[b, :, :live], m[b, :, :live], atol=2e-3, rtol=1e-3)

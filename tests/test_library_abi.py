@@ -40,7 +40,7 @@ def test_ctypes_struct_matches_header_size(built_libs, tmp_path):
     subprocess.run(["gcc", f"-I{ROOT / 'include'}", str(src), "-o", str(exe)], check=True)
     size = int(subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout)
     assert size == ctypes.sizeof(cabi.DecodeArgs)
-    assert cabi.load().pfd_abi_version() == 1
+    assert cabi.load().pfd_abi_version() == 2
 
 
 def test_argument_errors_are_reported_without_a_gpu(built_libs):
@@ -111,7 +111,8 @@ def test_workspace_allocator_shapes():
     from single_gpu_inference_lab_b200 import l20_paged_split_kv as m
 
     q = torch.zeros(3, 16, 128, dtype=torch.bfloat16)
-    po, pm, ps, out = m.allocate_l20_paged_split_kv_workspace(q, 4097, split_size=512)
+    po, pm, ps, out, sem = m.allocate_l20_paged_split_kv_workspace(q, 4097, split_size=512)
+    assert sem.dtype == torch.int32 and sem.numel() >= 3 * 2 and int(sem.abs().sum()) == 0
     assert po.shape == (3, 16, 16, 128) and po.dtype == torch.float32  # next_pow2(9) = 16
     assert pm.shape == ps.shape == (3, 16, 16) and out.shape == q.shape and out.dtype == q.dtype
     assert m.choose_split_size(64, 2, 4096) % 16 == 0
