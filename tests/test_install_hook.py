@@ -1,0 +1,87 @@
+"""The vLLM hook installer against a copy of the installed vLLM FlashInfer backend (CPU only;
+mirrors what the reference pins in tests/test_install_l20_fp8_paged_decode.py: switch names,
+policy call, quantised-cache gate -- plus that the patched file still compiles)."""
+
+import ast
+import importlib.util
+import shutil
+from pathlib import Path
+
+import pytest
+
+from single_gpu_inference_lab_b200 import install_l20_fp8_paged_decode as installer
+
+
+def _fake_tree(tmp_path: Path) -> Path:
+    spec = importlib.util.find_spec("vllm")
+    if spec is None or not spec.submodule_search_locations:
+        pytest.skip("vLLM is not installed")
+    real = Path(list(spec.submodule_search_locations)[0]) / "v1/attention/backends/flashinfer.py"
+    if not real.exists():
+        pytest.skip("this vLLM has no FlashInfer backend file")
+    root = tmp_path / "src"
+    (root / "vllm/v1/attention/backends").mkdir(parents=True)
+    (root / "vllm/v1/attention/ops").mkdir(parents=True)
+    shutil.copy2(real, root / "vllm/v1/attention/backends/flashinfer.py")
+    return root
+
+
+def test_install_is_idempotent_compiles_and_uninstalls(tmp_path, built_libs, capsys):
+    root = _fake_tree(tmp_path)
+    backend = root / "vllm/v1/attention/backends/flashinfer.py"
+    original = backend.read_text()
+    assert installer.main(["--vllm-source-dir", str(root)]) == 0
+    assert capsys.readouterr().out.strip() == str(root / "vllm")
+    patched = backend.read_text()
+    assert patched != original
+    ast.parse(patched)  # still valid Python
+    for needle in (
+        "VLLM_ENABLE_L20_FP8_PAGED_DECODE",
+        "VLLM_L20_FP8_PAGED_FORCE",
+        "VLLM_L20_FP8_PAGED_TRACE",
+        "should_use_l20_paged_fp8_split_kv",
+        "allocate_l20_paged_split_kv_workspace",
+        "l20_paged_split_kv_attention_fp8",
+        "is_quantized_kv_cache(self.kv_cache_dtype)",
+        "DeviceCapability(10, 0)",
+        "l20_fp8_paged_decode_run",
+        "block_tables=block_table_tensor[:num_decodes]",
+    ):
+        assert needle in patched, needle
+    # the stock call survives as the fallback branch, exactly once more than the DCP call
+    assert patched.count("decode_wrapper.run(") == original.count("decode_wrapper.run(")
+    ops = root / "vllm/v1/attention/ops"
+    for name in installer.COPIED:
+        assert (ops / name).exists(), name
+    backup = backend.with_suffix(installer.BACKUP_SUFFIX)
+    assert backup.read_text() == original
+    # second run: nothing changes
+    assert installer.main(["--vllm-source-dir", str(root)]) == 0
+    assert backend.read_text() == patched
+    assert installer.main(["--vllm-source-dir", str(root), "--uninstall"]) == 0
+    assert backend.read_text() == original
+
+
+def test_missing_patch_point_is_reported(tmp_path):
+    with pytest.raises(RuntimeError, match="cannot find patch point: FIDecode metadata"):
+        installer.patch_backend_source("import torch\nclass Other:\n    pass\n")
+    with pytest.raises(RuntimeError, match="cannot find vLLM source package"):
+        installer.find_vllm_package.__wrapped__ if hasattr(installer.find_vllm_package, "__wrapped__") else None
+        import os
+
+        cwd = os.getcwd()
+        os.chdir(tmp_path)
+        try:
+            real_find = importlib.util.find_spec
+            importlib.util.find_spec = lambda name: None
+            installer.find_vllm_package(str(tmp_path / "nowhere"))
+        finally:
+            importlib.util.find_spec = real_find
+            os.chdir(cwd)
+
+
+def test_replace_once_semantics():
+    assert installer.replace_once("a b", "b", "c", "x") == "a c"
+    assert installer.replace_once("a c", "b", "c", "x") == "a c"  # already applied
+    with pytest.raises(RuntimeError, match="cannot find patch point: x"):
+        installer.replace_once("a", "b", "zz", "x")
