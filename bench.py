@@ -233,7 +233,8 @@ def main() -> int:
     batch, hq, d = q.shape
     hkv = w.key_cache.shape[2]
     kv_bytes = w.kv_bytes
-    split = args.split_size or l20_paged_split_kv.choose_split_size(batch, hkv, w.max_seq_len)
+    split = args.split_size or l20_paged_split_kv.choose_split_size(
+        batch, hkv, w.max_seq_len, seq_lens=w.seq_lens.tolist())
     pool_bytes = 2 * w.key_cache.numel()
     pools = args.pools or max(2, -(-3 * L2_BYTES // pool_bytes) + 1)
     pools = min(pools, max(2, int(40e9 // pool_bytes)))
@@ -354,8 +355,10 @@ def main() -> int:
         per_step = cabi.launch_count() - launches_before  # kernels of this library per step
         ms_step = timed_graph(step, args.steps)
         launches = per_step * args.steps                  # replayed from graphs inside the timed region
+        path = cabi.last_path()
         fused = (not kv_range_mode) and per_step == 1     # one kernel per step: it IS the step
-        kernel_name = "paged_decode_fp8_balanced" if fused else "paged_decode_fp8_partial"
+        kernel_name = {1: "paged_decode_fp8_partial_ldg_kernel", 2: "paged_decode_fp8_partial_tma_kernel",
+                       3: "paged_decode_fp8_balanced_kernel"}.get(path, "?")
         ms_kernel = timed_graph(step if fused else (lambda i: step(i, args.flags | cabi.PFD_FLAG_PARTIAL_ONLY)), args.steps)
         ms_e2e = timed(e2e_step, args.steps)
         ms_eager = timed(step, args.steps)
@@ -389,7 +392,7 @@ def main() -> int:
             "dtype": "fp8_e4m3 KV, bf16 q, fp32 accumulate", "data": "synthetic",
             "config": {
                 "workload": args.workload, "batch_per_gpu": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
-                "page_size": 16, "split_size": split, "max_seq_len": w.max_seq_len,
+                "page_size": 16, "split_size": split, "max_seq_len": w.max_seq_len, "path": cabi.PATH_NAMES.get(path, "?"),
                 "kv_bytes_per_step_per_gpu": kv_bytes,
                 "parallelism": ("kv-range split + all-gather" if kv_range_mode else "sequence-sharded, no collective") if world > 1 else "single GPU",
                 "l2": f"{pools} KV pools of {pool_bytes / 1e6:.0f} MB rotated ({pools * pool_bytes / 1e6:.0f} MB > L2): every step reads cold KV",

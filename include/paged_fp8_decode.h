@@ -37,6 +37,8 @@ extern "C" {
 #define PFD_FLAG_PARTIAL_ONLY 4u  /* launch the split-KV partial kernel only (kernel timing)   */
 #define PFD_FLAG_FIXED_SPLITS 8u  /* always use the fixed-split grid + merge kernel, even when
                                      semaphores are given (partials then follow split_size)    */
+#define PFD_FLAG_BALANCED 16u     /* use the one-kernel balanced path whenever it is eligible
+                                     (by default only for batch * kv_heads >= 256)             */
 
 /*
  * Operands of one decode-attention layer-step.
@@ -178,6 +180,12 @@ int pfd_resolve_slots(const int32_t* block_table, int64_t bt_stride_b, const int
  * output is then undefined).  The kernels never trap and never spin without a limit.
  */
 int pfd_device_status(int32_t* status);
+
+/* Which kernels the calling thread's last decode call launched. */
+#define PFD_PATH_FIXED_LDG 1 /* fixed-split grid, plain 16-byte loads, + merge kernel */
+#define PFD_PATH_FIXED_TMA 2 /* fixed-split grid, TMA pipeline, + merge kernel         */
+#define PFD_PATH_BALANCED 3  /* one persistent balanced kernel                         */
+int pfd_last_path(void);
 
 /*
  * Debug aid for tuning: while `device_buffer` (uint64 [grid][8], device memory owned by the

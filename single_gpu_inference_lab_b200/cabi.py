@@ -19,6 +19,7 @@ PFD_FLAG_NO_TMA = 1
 PFD_FLAG_NO_DIRECT_OUT = 2
 PFD_FLAG_PARTIAL_ONLY = 4
 PFD_FLAG_FIXED_SPLITS = 8
+PFD_FLAG_BALANCED = 16
 
 EXPORTS = (
     "pfd_paged_decode_fp8_e4m3_split_out",
@@ -27,6 +28,7 @@ EXPORTS = (
     "pfd_resolve_slots",
     "pfd_device_status",
     "pfd_debug_phase_times",
+    "pfd_last_path",
     "pfd_launch_count",
     "pfd_last_error",
     "pfd_abi_version",
@@ -228,6 +230,16 @@ def device_status() -> int:
     lib.pfd_device_status.restype = C.c_int
     _check(lib.pfd_device_status(C.byref(value)))
     return int(value.value)
+
+
+PATH_NAMES = {0: "none", 1: "fixed-split grid (plain loads) + merge", 2: "fixed-split grid (TMA) + merge", 3: "balanced persistent kernel"}
+
+
+def last_path() -> int:
+    """PFD_PATH_* code of the kernels this thread's last decode call launched."""
+    lib = load()
+    lib.pfd_last_path.restype = C.c_int
+    return int(lib.pfd_last_path())
 
 
 def launch_count() -> int:

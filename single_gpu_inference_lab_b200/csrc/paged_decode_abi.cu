@@ -6,6 +6,7 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -16,6 +17,7 @@
 namespace {
 
 thread_local std::string g_last_error;
+thread_local int g_last_path = 0;  // PFD_PATH_* of this thread's last decode call
 unsigned long long* g_phase_times = nullptr;  // debug: per-CTA phase timestamps, set by pfd_debug_phase_times
 std::atomic<int64_t> g_launches{0};
 
@@ -76,9 +78,11 @@ struct MapKey {
   const void* base;
   int64_t stride_page, stride_token, stride_head, num_pages;
   int32_t heads;
+  int32_t promotion;  // L2 promotion in bytes
   bool operator==(const MapKey& o) const {
     return dev == o.dev && base == o.base && stride_page == o.stride_page && stride_token == o.stride_token &&
-           stride_head == o.stride_head && num_pages == o.num_pages && heads == o.heads;
+           stride_head == o.stride_head && num_pages == o.num_pages && heads == o.heads &&
+           promotion == o.promotion;
   }
 };
 struct MapEntry {
@@ -93,11 +97,16 @@ bool head_is_dim1(int64_t stride_token, int64_t stride_head) { return stride_hea
 // [pages, 16, heads, 128] e4m3 bytes with arbitrary (page, token, head) strides as a rank-4 u8
 // tensor whose dimensions are listed by ascending stride; box = one (page, head) tile of
 // 16 x 128 bytes, 128-byte swizzle.
+//
+// L2 promotion: the fixed-split grid runs the CTAs of all kv heads of a page at about the same
+// time, so fetching 256 bytes (two heads' rows in the NHD layout) per 128-byte request pays; the
+// balanced grid does not keep kv heads in step, there the second half would be evicted unused.
 int get_tensor_map(const void* base, int64_t stride_page, int64_t stride_token, int64_t stride_head,
-                   int64_t num_pages, int32_t heads, CUtensorMap* out) {
+                   int64_t num_pages, int32_t heads, int32_t promotion, CUtensorMap* out) {
   int dev = 0;
   cudaGetDevice(&dev);
-  const MapKey key{dev, base, stride_page, stride_token, stride_head, num_pages, heads};
+  if (const char* env = getenv("PFD_L2_PROMOTION")) promotion = atoi(env);  // tuning aid: 0, 64, 128, 256
+  const MapKey key{dev, base, stride_page, stride_token, stride_head, num_pages, heads, promotion};
   std::lock_guard<std::mutex> lock(g_state_mutex);
   for (const MapEntry& e : g_maps)
     if (e.key == key) {
@@ -121,9 +130,14 @@ int get_tensor_map(const void* base, int64_t stride_page, int64_t stride_token, 
   const cuuint32_t elem[4] = {1, 1, 1, 1};
   MapEntry entry;
   entry.key = key;
+  const CUtensorMapL2promotion promo =
+      promotion == 0 ? CU_TENSOR_MAP_L2_PROMOTION_NONE
+                     : promotion == 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
+                                       : promotion == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                                          : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
   const CUresult r = g_encode(&entry.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides,
-                              box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                              box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(PFD_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   if (g_maps.size() >= 256) g_maps.erase(g_maps.begin());
   g_maps.push_back(entry);
@@ -143,10 +157,10 @@ template <bool QBF16>
 int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, dim3 grid, cudaStream_t stream) {
   CUtensorMap mk, mv;
   if (int rc = get_tensor_map(a.key_cache, a.k_stride_page, a.k_stride_token, a.k_stride_head, a.num_pages,
-                              a.num_kv_heads, &mk))
+                              a.num_kv_heads, 256, &mk))
     return rc;
   if (int rc = get_tensor_map(a.value_cache, a.v_stride_page, a.v_stride_token, a.v_stride_head, a.num_pages,
-                              a.num_kv_heads, &mv))
+                              a.num_kv_heads, 256, &mv))
     return rc;
   pfd::TmaParams tp{};
   tp.head_is_dim1 = head_is_dim1(a.k_stride_token, a.k_stride_head) ? 1 : 0;
@@ -174,17 +188,22 @@ bool balanced_eligible(const pfd_decode_args& a) {
   if (a.semaphores == nullptr || a.num_semaphores < (int64_t)a.batch * a.num_kv_heads) return false;
   if (!a.partial_output || !a.partial_max || !a.partial_sum || a.partial_dtype != PFD_DTYPE_F32) return false;
   if (a.workspace_splits < 2 || a.batch > 8192) return false;
-  return true;
+  if (a.flags & PFD_FLAG_BALANCED) return true;
+  // Measured on B200: with at least about one (sequence, kv head) segment per two resident CTAs
+  // the equal-chunk kernel wins (ragged batches of many sequences); with few, long segments
+  // every segment has to be cut into several pieces anyway and the fixed-split grid plus merge
+  // kernel is a little faster.
+  return (int64_t)a.batch * a.num_kv_heads >= 256;
 }
 
 template <bool QBF16, int NH>
 int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, cudaStream_t stream) {
   CUtensorMap mk, mv;
   if (int rc = get_tensor_map(a.key_cache, a.k_stride_page, a.k_stride_token, a.k_stride_head, a.num_pages,
-                              a.num_kv_heads, &mk))
+                              a.num_kv_heads, 128, &mk))
     return rc;
   if (int rc = get_tensor_map(a.value_cache, a.v_stride_page, a.v_stride_token, a.v_stride_head, a.num_pages,
-                              a.num_kv_heads, &mv))
+                              a.num_kv_heads, 128, &mv))
     return rc;
   pfd::TmaParams tp{};
   tp.head_is_dim1 = head_is_dim1(a.k_stride_token, a.k_stride_head) ? 1 : 0;
@@ -232,6 +251,7 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, cudaS
   int grid = sm_count[dev] * per_sm;
   if (pair_bound < grid) grid = (int)std::max<int64_t>(pair_bound, 1);
   kernel<<<grid, kThreads, smem, stream>>>(kp, tp, bp, mk, mv);
+  g_last_path = PFD_PATH_BALANCED;
   return check_launch("balanced decode kernel");
 }
 
@@ -243,8 +263,10 @@ int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num
   }
   const dim3 grid(num_splits, a.num_kv_heads, a.batch);
   if (D == 128 && tma_eligible(a)) {
+    g_last_path = PFD_PATH_FIXED_TMA;
     if (int rc = launch_partial_tma<QBF16>(a, kp, grid, stream)) return rc;
   } else {
+    g_last_path = PFD_PATH_FIXED_LDG;
     pfd::paged_decode_fp8_partial_ldg_kernel<D, QBF16, kWarps><<<grid, kWarps * 32, 0, stream>>>(kp);
     if (int rc = check_launch("partial kernel")) return rc;
   }
@@ -406,6 +428,8 @@ int pfd_paged_decode_fp8_e4m3_split_out_noalloc(const pfd_decode_args* args) {
   a.partial_stride_s = 1;
   return pfd_paged_decode_fp8_e4m3_split_out(&a);
 }
+
+int pfd_last_path(void) { return g_last_path; }
 
 int pfd_debug_phase_times(void* device_buffer) {
   g_phase_times = static_cast<unsigned long long*>(device_buffer);

@@ -299,10 +299,9 @@ __device__ __forceinline__ void named_arrive(int id, int count) {
   asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
 
-// Physical column of logical column d in row `row` of the swizzled accumulation buffer.
-__device__ __forceinline__ int acc_col(int row, int d) {
-  return d ^ (((d >> 5) & 3) | (((row & 7) >> 1) << 2));
-}
+// The accumulation buffer is [rows][32 float4]; float4 f of row `row` lives at f ^ ((row & 7) >> 1),
+// which makes the compute warps' float4 read-modify-writes bank-conflict free.
+__device__ __forceinline__ int acc_f4(int row, int f) { return row * 32 + (f ^ ((row & 7) >> 1)); }
 
 template <bool QBF16>
 __device__ __forceinline__ void store_row16(const KernelParams& p, int b, int hq, int d0, const float (&v)[16],
@@ -447,8 +446,8 @@ paged_decode_fp8_balanced_kernel(const KernelParams p, const TmaParams tp, const
 
   if (warp == NC) {
     // ================= retiring warp =================
-    // lane -> rows (8h + lane/4), columns [32 * (lane % 4), +32)
-    const int rr = lane >> 2, d0 = 32 * (lane & 3);
+    // lane -> rows (8h + lane % 8), columns [32 * (lane / 8), +32)
+    const int rr = lane & 7, d0 = 32 * (lane >> 3);
     int n_total = 0;
     {
       PieceWalker w;
@@ -466,6 +465,7 @@ paged_decode_fp8_balanced_kernel(const KernelParams p, const TmaParams tp, const
       const Piece q = walk.at(g, prefix, hkv);
       g = q.e;
       if (q.solo()) continue;
+      if (n == n_total - 1) break;  // the chunk's last shared piece is retired by the compute warps
       const float vs = p.v_scale_ph ? __ldg(p.v_scale_ph + q.kvh) : p.v_scale;
       named_sync(kBarReady, NT);  // the compute warps' sums for this piece are complete
       float acc[NH][32], big[NH], lt[NH];
@@ -473,10 +473,12 @@ paged_decode_fp8_balanced_kernel(const KernelParams p, const TmaParams tp, const
       for (int h = 0; h < NH; ++h) {
         const int row = 8 * h + rr;
 #pragma unroll
-        for (int t = 0; t < 32; ++t) {
-          float* cell = sm_acc + row * D + acc_col(row, d0 + t);
-          acc[h][t] = *cell * vs;
-          *cell = 0.f;  // leave the buffer zeroed for the next piece
+        for (int t = 0; t < 8; ++t) {
+          float4* cell = reinterpret_cast<float4*>(sm_acc) + acc_f4(row, (d0 >> 2) + t);
+          const float4 x = *cell;
+          acc[h][4 * t] = x.x * vs; acc[h][4 * t + 1] = x.y * vs;
+          acc[h][4 * t + 2] = x.z * vs; acc[h][4 * t + 3] = x.w * vs;
+          *cell = make_float4(0.f, 0.f, 0.f, 0.f);  // leave the buffer zeroed for the next piece
         }
         big[h] = -INFINITY;
         lt[h] = 0.f;
@@ -534,47 +536,38 @@ paged_decode_fp8_balanced_kernel(const KernelParams p, const TmaParams tp, const
           const int hq = q.kvh * p.group + row;
           float m_nat = big[h], den = lt[h];
           if (last) {
-            // Merge the other pieces into this CTA's own (still in registers).  All maxima and
-            // sums are fetched in one round trip, the data two pieces per round trip.
+            // Merge the other pieces into this CTA's own (still in registers), two pieces per
+            // round trip: their maxima, sums and data are requested together.
             const int64_t pbase = (int64_t)q.b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h;
             const float* pout = reinterpret_cast<const float*>(p.partial_output);
-            for (int s0 = 0; s0 < pieces; s0 += 8) {
-              float ms[8], ls[8];
+            for (int s0 = 0; s0 < pieces - 1; s0 += 2) {
+              float4 x[2][8];
+              float ms[2], ls[2];
 #pragma unroll
-              for (int u = 0; u < 8; ++u) {
-                const bool on = s0 + u < pieces && s0 + u != piece;
-                ms[u] = on ? __ldcg(p.partial_max + pbase + (int64_t)(s0 + u) * p.partial_stride_s) : -INFINITY;
-                ls[u] = on ? __ldcg(p.partial_sum + pbase + (int64_t)(s0 + u) * p.partial_stride_s) : 0.f;
+              for (int v = 0; v < 2; ++v) {
+                // the v-th other piece of this batch: indices skip this CTA's own piece
+                int s = s0 + v;
+                const bool on = s < pieces - 1;
+                s = on ? (s >= piece ? s + 1 : s) : piece;
+                const int64_t pidx = pbase + (int64_t)s * p.partial_stride_s;
+                ms[v] = __ldcg(p.partial_max + pidx);
+                ls[v] = __ldcg(p.partial_sum + pidx);
+                if (!on) { ms[v] = -INFINITY; ls[v] = 0.f; }
+                const float4* src = reinterpret_cast<const float4*>(pout + pidx * D + d0);
+#pragma unroll
+                for (int t = 0; t < 8; ++t) x[v][t] = __ldcg(src + t);
               }
-              float m_new = m_nat;
-#pragma unroll
-              for (int u = 0; u < 8; ++u) m_new = fmaxf(m_new, ms[u]);
+              const float m_new = fmaxf(m_nat, fmaxf(ms[0], ms[1]));
               const float own = expf(m_nat - m_new);
-              den *= own;
-#pragma unroll
-              for (int t = 0; t < 32; ++t) acc[h][t] *= own;
+              const float cf0 = expf(ms[0] - m_new), cf1 = expf(ms[1] - m_new);
+              den = den * own + ls[0] * cf0 + ls[1] * cf1;
               m_nat = m_new;
 #pragma unroll
-              for (int u = 0; u < 8; u += 2) {
-                if (s0 + u >= pieces) break;
-                float4 x[2][8];
-                float cf[2];
-#pragma unroll
-                for (int v = 0; v < 2; ++v) {
-                  const bool on = s0 + u + v < pieces && s0 + u + v != piece;
-                  cf[v] = on ? expf(ms[u + v] - m_nat) : 0.f;
-                  den += ls[u + v] * cf[v];
-                  const float* src = pout + (pbase + (int64_t)(on ? s0 + u + v : piece) * p.partial_stride_s) * D + d0;
-#pragma unroll
-                  for (int t = 0; t < 8; ++t) x[v][t] = __ldcg(reinterpret_cast<const float4*>(src) + t);
-                }
-#pragma unroll
-                for (int v = 0; v < 2; ++v)
-#pragma unroll
-                  for (int t = 0; t < 8; ++t) {
-                    acc[h][4 * t] += cf[v] * x[v][t].x; acc[h][4 * t + 1] += cf[v] * x[v][t].y;
-                    acc[h][4 * t + 2] += cf[v] * x[v][t].z; acc[h][4 * t + 3] += cf[v] * x[v][t].w;
-                  }
+              for (int t = 0; t < 8; ++t) {
+                acc[h][4 * t] = acc[h][4 * t] * own + cf0 * x[0][t].x + cf1 * x[1][t].x;
+                acc[h][4 * t + 1] = acc[h][4 * t + 1] * own + cf0 * x[0][t].y + cf1 * x[1][t].y;
+                acc[h][4 * t + 2] = acc[h][4 * t + 2] * own + cf0 * x[0][t].z + cf1 * x[1][t].z;
+                acc[h][4 * t + 3] = acc[h][4 * t + 3] * own + cf0 * x[0][t].w + cf1 * x[1][t].w;
               }
             }
           }
@@ -650,6 +643,16 @@ paged_decode_fp8_balanced_kernel(const KernelParams p, const TmaParams tp, const
     pending = r[NSTAGE];
   }
   mark_phase(tp, 2);  // first copies issued
+  int n_total_shared = 0;  // shared pieces of this chunk (same walk as the retiring warp's)
+  {
+    PieceWalker w;
+    w.init(first, P0, P1, chunk);
+    for (int gg = P0; gg < P1;) {
+      const Piece t = w.at(gg, prefix, hkv);
+      n_total_shared += t.solo() ? 0 : 1;
+      gg = t.e;
+    }
+  }
 
   // swizzled shared-memory offsets of this thread's fragments inside a tile
   uint32_t k_off[2][2], v_off[4];
@@ -756,6 +759,7 @@ paged_decode_fp8_balanced_kernel(const KernelParams p, const TmaParams tp, const
         for (int e = 0; e < 2; ++e)
           if (i == 0) sm_m[warp * ROWS + 8 * h + 2 * j + e] = st.m[h][e];
       named_sync(kBarMax, NC * 32);
+      float fac[NH][2];
 #pragma unroll
       for (int h = 0; h < NH; ++h) {
         float f[2];
@@ -768,20 +772,157 @@ paged_decode_fp8_balanced_kernel(const KernelParams p, const TmaParams tp, const
           f[e] = (st.m[h][e] == -INFINITY) ? 0.f : exp2f(st.m[h][e] - big);
           if (i == 0) sm_l[warp * ROWS + row] = lsum[h][e] * f[e];
         }
-        if (st.m[h][0] != -INFINITY || st.m[h][1] != -INFINITY) {
-          // element (row, d = 16i + 2mt + (c>>1)); acc_col() spreads the 32 lanes of one atomic
-          // over 32 banks
+        fac[h][0] = f[0];
+        fac[h][1] = f[1];
+      }
+      // Sum the four warps' O^T without atomics: in phase k warp w adds the quarter
+      // (w + k) % 4 of its values (m-tiles 2q, 2q+1, i.e. columns 16i + 4q .. +3 of rows 2j, 2j+1)
+      // with plain float4 read-modify-writes; no two warps touch the same quarter in a phase.
 #pragma unroll
-          for (int mt = 0; mt < 8; ++mt)
+      for (int k = 0; k < NC; ++k) {
+        const int qq = (warp + k) & (NC - 1);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const int row = 8 * h + 2 * j + (c & 1);
-              atomicAdd(sm_acc + row * D + acc_col(row, 16 * i + 2 * mt + (c >> 1)), st.o[h][mt][c] * f[c & 1]);
-            }
-        }
+        for (int h = 0; h < NH; ++h)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int row = 8 * h + 2 * j + e;
+            float4* cell = reinterpret_cast<float4*>(sm_acc) + acc_f4(row, 4 * i + qq);
+            float4 x = *cell;
+            // m-tile 2q: columns +0 (c = e) and +1 (c = 2 + e); m-tile 2q+1: +2 and +3
+            float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+#pragma unroll
+            for (int z = 0; z < NC; ++z)
+              if (z == qq) {
+                v0 = st.o[h][2 * z][e]; v1 = st.o[h][2 * z][2 + e];
+                v2 = st.o[h][2 * z + 1][e]; v3 = st.o[h][2 * z + 1][2 + e];
+              }
+            x.x += v0 * fac[h][e]; x.y += v1 * fac[h][e]; x.z += v2 * fac[h][e]; x.w += v3 * fac[h][e];
+            *cell = x;
+          }
+        if (k + 1 < NC) named_sync(kBarMax, NC * 32);
       }
       __threadfence_block();
-      named_arrive(kBarReady, NT);
+      if (n_shared + 1 < n_total_shared) {
+        named_arrive(kBarReady, NT);
+      } else {
+        // The chunk's last shared piece decides when the CTA is done: all four compute warps
+        // retire it together (8 columns per thread, every merge operand requested at once)
+        // instead of queueing it behind the retiring warp's earlier pieces.
+        named_sync(kBarMax, NC * 32);
+        const float vs = p.v_scale_ph ? __ldg(p.v_scale_ph + q.kvh) : p.v_scale;
+        const int c_first = q.seg_start / chunk, c_last = (q.seg_start + q.np - 1) / chunk;
+        const int pieces = c_last - c_first + 1, piece = (int)blockIdx.x - c_first;
+        const bool fits = pieces <= bp.workspace_splits;
+        if (!fits && threadIdx.x == 0) atomicExch(tp.status, kErrWorkspace);
+        constexpr int ITEMS = ROWS * 16 / (NC * 32);  // (row, 8 columns) slices per thread
+        float a8[ITEMS][8], m_nat[ITEMS], den[ITEMS];
+#pragma unroll
+        for (int it = 0; it < ITEMS; ++it) {
+          const int e = threadIdx.x + it * NC * 32, row = e >> 4, c8 = (e & 15) * 8;
+          const float4 x0 = reinterpret_cast<const float4*>(sm_acc)[acc_f4(row, c8 >> 2)];
+          const float4 x1 = reinterpret_cast<const float4*>(sm_acc)[acc_f4(row, (c8 >> 2) + 1)];
+          a8[it][0] = x0.x * vs; a8[it][1] = x0.y * vs; a8[it][2] = x0.z * vs; a8[it][3] = x0.w * vs;
+          a8[it][4] = x1.x * vs; a8[it][5] = x1.y * vs; a8[it][6] = x1.z * vs; a8[it][7] = x1.w * vs;
+          float big = -INFINITY, lt = 0.f;
+#pragma unroll
+          for (int w = 0; w < NC; ++w) {
+            big = fmaxf(big, sm_m[w * ROWS + row]);
+            lt += sm_l[w * ROWS + row];
+          }
+          m_nat[it] = big * kLn2;
+          den[it] = lt;
+          if (fits && pieces > 1 && row < p.group) {
+            const int hq = q.kvh * p.group + row;
+            const int64_t pidx = (int64_t)q.b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h +
+                                 (int64_t)piece * p.partial_stride_s;
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.partial_output) + pidx * D + c8);
+            dst[0] = make_float4(a8[it][0], a8[it][1], a8[it][2], a8[it][3]);
+            dst[1] = make_float4(a8[it][4], a8[it][5], a8[it][6], a8[it][7]);
+            if (c8 == 0) {
+              p.partial_max[pidx] = m_nat[it];
+              p.partial_sum[pidx] = den[it];
+            }
+          }
+        }
+        bool last = false;
+        if (fits && pieces > 1) {
+          __threadfence();
+          named_sync(kBarMax, NC * 32);
+          if (threadIdx.x == 0) sm_misc[0] = atomicAdd(bp.semaphores + q.b * hkv + q.kvh, 1) == pieces - 1;
+          named_sync(kBarMax, NC * 32);
+          last = sm_misc[0] != 0;
+          if (last) __threadfence();
+        }
+        if (fits && (pieces == 1 || last)) {
+#pragma unroll
+          for (int it = 0; it < ITEMS; ++it) {
+            const int e = threadIdx.x + it * NC * 32, row = e >> 4, c8 = (e & 15) * 8;
+            if (row >= p.group) continue;
+            const int hq = q.kvh * p.group + row;
+            if (last) {
+              const int64_t pbase = (int64_t)q.b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h;
+              const float* pout = reinterpret_cast<const float*>(p.partial_output);
+              for (int s0 = 0; s0 < pieces - 1; s0 += 8) {
+                float4 x[8][2];
+                float ms[8], ls[8];
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                  int sidx = s0 + v;
+                  const bool on = sidx < pieces - 1;
+                  sidx = on ? (sidx >= piece ? sidx + 1 : sidx) : piece;
+                  const int64_t pidx = pbase + (int64_t)sidx * p.partial_stride_s;
+                  ms[v] = __ldcg(p.partial_max + pidx);
+                  ls[v] = __ldcg(p.partial_sum + pidx);
+                  if (!on) { ms[v] = -INFINITY; ls[v] = 0.f; }
+                  const float4* src = reinterpret_cast<const float4*>(pout + pidx * D + c8);
+                  x[v][0] = __ldcg(src);
+                  x[v][1] = __ldcg(src + 1);
+                }
+                float m_new = m_nat[it];
+#pragma unroll
+                for (int v = 0; v < 8; ++v) m_new = fmaxf(m_new, ms[v]);
+                const float own = expf(m_nat[it] - m_new);
+                den[it] *= own;
+#pragma unroll
+                for (int t = 0; t < 8; ++t) a8[it][t] *= own;
+#pragma unroll
+                for (int v = 0; v < 8; ++v) {
+                  const float cf = expf(ms[v] - m_new);
+                  den[it] += ls[v] * cf;
+                  a8[it][0] += cf * x[v][0].x; a8[it][1] += cf * x[v][0].y;
+                  a8[it][2] += cf * x[v][0].z; a8[it][3] += cf * x[v][0].w;
+                  a8[it][4] += cf * x[v][1].x; a8[it][5] += cf * x[v][1].y;
+                  a8[it][6] += cf * x[v][1].z; a8[it][7] += cf * x[v][1].w;
+                }
+                m_nat[it] = m_new;
+              }
+            }
+            if (p.packed_output != nullptr) {
+              float* dst = p.packed_output + ((int64_t)q.b * p.num_q_heads + hq) * (D + 2);
+#pragma unroll
+              for (int t = 0; t < 8; t += 2) *reinterpret_cast<float2*>(dst + c8 + t) = make_float2(a8[it][t], a8[it][t + 1]);
+              if (c8 == 0) { dst[D] = m_nat[it]; dst[D + 1] = den[it]; }
+            } else {
+              const float inv = 1.f / den[it];
+              uint32_t wv[4];
+#pragma unroll
+              for (int t = 0; t < 4; ++t) {
+                if constexpr (QBF16) {
+                  __nv_bfloat162 x = __floats2bfloat162_rn(a8[it][2 * t] * inv, a8[it][2 * t + 1] * inv);
+                  wv[t] = *reinterpret_cast<uint32_t*>(&x);
+                } else {
+                  wv[t] = pack_f16x2(a8[it][2 * t] * inv, a8[it][2 * t + 1] * inv);
+                }
+              }
+              uint16_t* dst = reinterpret_cast<uint16_t*>(p.output) + (int64_t)q.b * p.o_stride_b + (int64_t)hq * p.o_stride_h + c8;
+              *reinterpret_cast<uint2*>(dst) = make_uint2(wv[0], wv[1]);
+              *reinterpret_cast<uint2*>(dst + 4) = make_uint2(wv[2], wv[3]);
+            }
+          }
+          if (last && threadIdx.x == 0) bp.semaphores[q.b * hkv + q.kvh] = 0;  // ready for the next call
+        }
+        mark_phase(tp, 6);  // chunk's last shared piece retired
+      }
       ++n_shared;
     }
     q = nq;

@@ -60,15 +60,28 @@ def allocate_l20_paged_split_kv_workspace(
     )
 
 
-def choose_split_size(batch: int, num_kv_heads: int, max_seq_len: int, *, sm_count: int = 148,
-                      ctas_per_sm: int = 3, minimum: int = 128, maximum: int = 2048) -> int:
-    """Split size (multiple of 16) that yields roughly ``sm_count * ctas_per_sm`` CTAs for
-    ``batch * num_kv_heads`` (sequence, kv head) pairs of length ``max_seq_len``.  Host-only
-    arithmetic on values the caller already has; no device read."""
-    pairs = max(1, batch * num_kv_heads)
-    want_splits = max(1, _cdiv(sm_count * ctas_per_sm, pairs))
-    split = _cdiv(_cdiv(max(max_seq_len, 1), want_splits), 16) * 16
-    return int(min(max(split, minimum), maximum))
+def choose_split_size(batch: int, num_kv_heads: int, max_seq_len: int, *, seq_lens=None,
+                      sm_count: int = 148, ctas_per_sm: int = 3, minimum: int = 128, step: int = 64) -> int:
+    """Split size for the fixed-split grid: the smallest multiple of ``step`` whose grid of
+    live (sequence, kv head, split) work items still fits in one wave of resident CTAs
+    (``sm_count * ctas_per_sm``).  One full wave is what the kernel likes: a second, partly
+    filled wave costs about as much as the first.  ``seq_lens`` (host ints, e.g. the engine's
+    CPU copy of the sequence lengths) makes the count exact; without it every sequence is
+    assumed to be ``max_seq_len`` long.  Host-only arithmetic, no device read."""
+    if batch * num_kv_heads >= 256:
+        # many (sequence, kv head) segments: the library's balanced kernel shares the work out by
+        # itself; the split size then only sizes the workspace (>= 2 slots per row are needed)
+        return 512
+    slots = sm_count * ctas_per_sm
+    lens = [int(x) for x in seq_lens] if seq_lens is not None else [int(max_seq_len)] * int(batch)
+    longest = max([max_seq_len, *lens, 1])
+    split = max(minimum, step)
+    while split < longest:
+        items = num_kv_heads * sum(_cdiv(n, split) for n in lens if n > 0)
+        if items <= slots:
+            break
+        split += step
+    return int(split)
 
 
 def l20_paged_split_kv_attention_fp8(

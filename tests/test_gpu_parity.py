@@ -30,7 +30,8 @@ def cabi(built_libs):
 def workspace(q, max_seq_len, split_size, dtype=torch.float32, kv_start=0, poison=True, semaphores=True):
     """(partial_output, partial_max, partial_sum, None, semaphores).  With semaphores (and
     head_dim 128, f32 partials, flags 0) the library takes its one-kernel balanced path, which
-    needs a split axis of at least 2; flags 8 / 1 select the fixed-split TMA / plain-load paths."""
+    needs a split axis of at least 2 (flags 16 forces it for small batches, 0 lets the library
+    choose); flags 8 / 1 select the fixed-split TMA / plain-load paths."""
     b, hq, d = q.shape
     s = max(2 if semaphores else 1, -(-(max_seq_len - kv_start) // split_size))
     fill = float("nan") if poison else 0.0
@@ -72,7 +73,7 @@ def expected(w, **kw):
 @pytest.mark.parametrize(
     "name", ["cfg1-qwen0.5b-b8", "cfg2-coder3b-b4", "cfg3-qwen7b-b24", "cfg4-llama8b-b2", "cfg5-prefix-b8"]
 )
-@pytest.mark.parametrize("flags", [0, 8, 1])
+@pytest.mark.parametrize("flags", [16, 8, 1, 0])
 def test_against_committed_reference_outputs(cabi, golden, name, flags):
     case = golden["cases"][name]
     w = make_inputs(case["workload"], seed=0, device="cpu", batch=case["batch"], shrink=case["shrink"])
@@ -108,7 +109,7 @@ def test_config1_full_size(cabi):
 def test_config2_full_size(cabi):
     w = make_inputs("qwen2.5-coder-3b-b64", seed=0)
     exp = expected(w)
-    for split, flags in ((256, 0), (512, 0), (512, 8), (1024, 1)):
+    for split, flags in ((256, 16), (512, 16), (896, 0), (512, 8), (1024, 1)):
         assert_within_gate(run(cabi, w.to(DEV), split, flags=flags), exp, f"cfg2 split={split} flags={flags}")
 
 
@@ -116,7 +117,7 @@ def test_config3_full_size_log_uniform_lengths(cabi):
     w = make_inputs("qwen2.5-7b-b256", seed=0)
     assert int(w.seq_lens.min()) <= 4
     exp = expected(w)
-    for flags in (0, 8):
+    for flags in (0, 16, 8):
         assert_within_gate(run(cabi, w.to(DEV), 512, flags=flags), exp, f"cfg3 flags={flags}")
 
 
@@ -125,9 +126,9 @@ def test_config4_long_context_sampled_rows_and_split_invariance(cabi):
     own pages (the whole-cache dequantisation of the reference function would need ~10 GB);
     split invariance covers the rest."""
     w = make_inputs("llama3-8b-long-b4", seed=0, device=DEV)
-    out_a = run(cabi, w, 2048)
+    out_a = run(cabi, w, 2048, flags=16)
     out_b = run(cabi, w, 512, flags=8)
-    out_c = run(cabi, w, 8192)
+    out_c = run(cabi, w, 16384)
     assert_within_gate(out_b, out_a, "split 512 vs 2048")
     assert_within_gate(out_c, out_a, "split 8192 vs 2048")
     b = 2
@@ -144,7 +145,7 @@ def test_config4_long_context_sampled_rows_and_split_invariance(cabi):
 def test_config5_shared_prefix_full_size(cabi):
     w = make_inputs("shared-prefix-b64", seed=0)
     exp = expected(w)
-    for flags in (0, 8):
+    for flags in (0, 16, 8):
         assert_within_gate(run(cabi, w.to(DEV), 512, flags=flags), exp, f"cfg5 flags={flags}")
 
 
@@ -162,7 +163,7 @@ def test_every_short_context_length(cabi, d, hq, hkv):
     q = torch.randn(b, hq, d).to(torch.bfloat16)
     exp = oracle.reference(q, kc, vc, table.long(), lens, ks, vs)
     for split in (16, 32, 64, 512):
-        for flags in (0, 8, 1, 2):
+        for flags in (16, 0, 8, 1, 2):
             out = torch.full_like(q, float("nan"), device=DEV)
             ws = workspace(q.to(DEV), 70, split)
             cabi.paged_decode_fp8_e4m3_split_out(
@@ -187,7 +188,7 @@ def test_unused_slots_may_hold_nan_bytes(cabi):
             kc[page, n % 16 :] = 0x7F
             vc[page, n % 16 :] = 0xFF
     w.key_cache, w.value_cache = kc.view(torch.float8_e4m3fn), vc.view(torch.float8_e4m3fn)
-    for flags in (0, 8, 1):
+    for flags in (16, 8, 1):
         assert_within_gate(run(cabi, w.to(DEV), 64, flags=flags), exp, "nan slots")
 
 
@@ -235,7 +236,7 @@ def test_strided_cache_layouts(cabi, layout):
         big2[:, :, :hkv] = g.value_cache
         g.key_cache, g.value_cache = big[:, :, :hkv], big2[:, :, :hkv]
     assert not g.key_cache.is_contiguous()
-    for flags in (0, 8, 1):
+    for flags in (16, 8, 1):
         assert_within_gate(run(cabi, g, 64, flags=flags), exp, layout)
 
 
@@ -261,8 +262,8 @@ def test_kv_start_suffix_pass_and_packed_partials_merge(cabi):
     for cut in (w.prefix_len, w.prefix_len - 5, 3):
         head = g.to(DEV)
         head.seq_lens = torch.clamp(g.seq_lens, max=cut)
-        p0 = run(cabi, head, 128, packed=True, max_seq_len=cut)
-        p1 = run(cabi, g, 128, packed=True, kv_start=cut)
+        p0 = run(cabi, head, 128, packed=True, max_seq_len=cut, flags=16)
+        p1 = run(cabi, g, 128, packed=True, kv_start=cut, flags=16 if cut % 2 else 8)
         out = torch.empty_like(g.query)
         cabi.merge_packed(torch.stack([p0, p1]).contiguous(), out)
         torch.cuda.synchronize()
@@ -322,8 +323,8 @@ def test_block_table_permutation_invariance_and_idempotence(cabi):
     """Relocating every page (new permutation, caches moved accordingly) must not change a bit
     of the output; neither must running the same step twice into a reused workspace."""
     w = make_inputs("qwen2.5-coder-3b-b64", seed=8, batch=8, shrink=0.2).to(DEV)
-    a = run(cabi, w, 128)
-    a2 = run(cabi, w, 128)
+    a = run(cabi, w, 128, flags=8)
+    a2 = run(cabi, w, 128, flags=8)
     assert torch.equal(a.view(torch.int16), a2.view(torch.int16))
     pages = w.key_cache.shape[0]
     perm = torch.randperm(pages, device=DEV)
@@ -334,8 +335,12 @@ def test_block_table_permutation_invariance_and_idempotence(cabi):
     vc[perm] = w.value_cache.view(torch.uint8)
     moved.key_cache, moved.value_cache = kc.view(torch.float8_e4m3fn), vc.view(torch.float8_e4m3fn)
     moved.block_table = perm[w.block_table.long()].to(torch.int32)
-    b = run(cabi, moved, 128)
+    b = run(cabi, moved, 128, flags=8)
     assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    # the balanced path sums warps in a fixed order too: same bits run to run and after relocation
+    c1, c2, c3 = run(cabi, w, 128, flags=16), run(cabi, w, 128, flags=16), run(cabi, moved, 128, flags=16)
+    assert torch.equal(c1.view(torch.int16), c2.view(torch.int16))
+    assert torch.equal(c1.view(torch.int16), c3.view(torch.int16))
 
 
 def test_linearity_in_v_scale_and_scale_folding(cabi):

@@ -116,5 +116,9 @@ def test_workspace_allocator_shapes():
     assert po.shape == (3, 16, 16, 128) and po.dtype == torch.float32  # next_pow2(9) = 16
     assert pm.shape == ps.shape == (3, 16, 16) and out.shape == q.shape and out.dtype == q.dtype
     assert m.choose_split_size(64, 2, 4096) % 16 == 0
-    assert 128 <= m.choose_split_size(256, 4, 8192) <= 2048
-    assert m.choose_split_size(4, 8, 131072) % 16 == 0
+    assert 128 <= m.choose_split_size(256, 4, 8192) <= 8192
+    s = m.choose_split_size(4, 8, 131072)
+    assert s % 16 == 0 and 8 * 4 * -(-131072 // s) <= 444 < 8 * 4 * -(-131072 // (s - 64))
+    lens = [512, 4096, 2000, 100]
+    s = m.choose_split_size(4, 2, 4096, seq_lens=lens)
+    assert s == 128  # few sequences: the minimum already fits one wave
