@@ -42,9 +42,12 @@ sys.path.insert(0, str(ROOT))
 
 FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum of one partial-kernel launch on the default
-# workload, from the ncu capture summarised under profiles/ (None until captured).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
+# captures summarised under profiles/ (the bench's own seed-0 workloads, full size).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {
+    ("qwen2.5-coder-3b-b64", 2): 80_438_016 + 3_118_592,   # partial_tma kernel
+    ("qwen2.5-7b-b256", 3): 226_127_104 + 9_285_888,       # balanced kernel
+}
 
 DEFAULT_WORKLOAD = "qwen2.5-coder-3b-b64"
 
@@ -60,6 +63,8 @@ def parse_args():
     p.add_argument("--pools", type=int, default=0, help="distinct KV pools rotated through (0 = enough to exceed L2 x3)")
     p.add_argument("--flags", type=int, default=0)
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--strong", action="store_true",
+                   help="N > 1: shard ONE batch by sequence over the ranks (token-balanced) instead of one batch per rank")
     return p.parse_args()
 
 
@@ -142,7 +147,7 @@ def cpu_reference_run(w, sample_rows: int, repeats: int):
 
     torch.set_num_threads(os.cpu_count() or 1)
     rows = torch.arange(sample_rows)
-    sub = sharding._compact(w, rows.to(w.query.device), 0, w.block_table.shape[1], w.seq_lens.cpu()[rows]).to("cpu")
+    sub = sharding.compact_rows(w, rows.to(w.query.device), 0, w.block_table.shape[1], w.seq_lens.cpu()[rows]).to("cpu")
     table = sub.block_table.long()
     hkv, d = sub.key_cache.shape[2], sub.key_cache.shape[3]
     nbytes = int(sub.seq_lens.sum()) * hkv * d * 2
@@ -225,6 +230,12 @@ def main() -> int:
         full_len = 131072
         lo, hi = sharding.kv_range_bounds(full_len, rank, world)
         w = make_inputs(args.workload, seed=rank, device=dev, shrink=(hi - lo) / full_len)
+        scaling = "strong"
+    elif args.strong and world > 1:
+        full = make_inputs(args.workload, seed=0, device=dev)  # same batch on every rank
+        w, _rows = sharding.shard_sequences(full, rank, world)
+        del full
+        torch.cuda.empty_cache()
         scaling = "strong"
     else:
         w = make_inputs(args.workload, seed=rank, device=dev)
@@ -332,7 +343,7 @@ def main() -> int:
             local = w.__class__(**{**w.__dict__, "query": dq, "block_table": dtable, "seq_lens": dlens,
                                    "key_cache": kcs[i % pools], "value_cache": vcs[i % pools]})
             if world > 1:
-                res = sharding.kv_range_decode(local, split_size=split, gather_buffer=gathered)
+                res = sharding.kv_range_decode(local, split_size=split, gather_buffer=gathered, workspace=ws, packed_buffer=packed)
             else:
                 res = l20_paged_split_kv.l20_paged_split_kv_attention_fp8(
                     dq, kcs[i % pools], vcs[i % pools], dtable, dlens, k_scale=w.k_scale, v_scale=w.v_scale,
@@ -394,13 +405,16 @@ def main() -> int:
                 "workload": args.workload, "batch_per_gpu": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
                 "page_size": 16, "split_size": split, "max_seq_len": w.max_seq_len, "path": cabi.PATH_NAMES.get(path, "?"),
                 "kv_bytes_per_step_per_gpu": kv_bytes,
-                "parallelism": ("kv-range split + all-gather" if kv_range_mode else "sequence-sharded, no collective") if world > 1 else "single GPU",
+                "parallelism": ("kv-range split + all-gather" if kv_range_mode else
+                                ("one batch sharded by sequence (token-balanced), no collective" if args.strong
+                                 else "one batch per GPU, no collective")) if world > 1 else "single GPU",
                 "l2": f"{pools} KV pools of {pool_bytes / 1e6:.0f} MB rotated ({pools * pool_bytes / 1e6:.0f} MB > L2): every step reads cold KV",
             },
             "pct_of_hbm_peak": round(100 * value / (peak * world), 2),
             "roofline": {
                 "bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
-                "frac": round(achieved / peak, 4), "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "frac": round(achieved / peak, 4),
+                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, path)) if world == 1 and not args.split_size else None,
                 "kernel": kernel_name, "us_per_launch": round(ms_kernel * 1e3, 3), "peak_source": peak_kind,
                 "algorithmic_bytes_per_launch": kv_bytes,
             },

@@ -41,7 +41,7 @@ def lpt_partition(lengths, world_size: int) -> list[list[int]]:
     return [sorted(p) for p in parts]
 
 
-def _compact(inputs: PagedDecodeInputs, rows, page_lo, page_hi, seq_lens) -> PagedDecodeInputs:
+def compact_rows(inputs: PagedDecodeInputs, rows, page_lo, page_hi, seq_lens) -> PagedDecodeInputs:
     """Keep block-table columns [page_lo, page_hi) of ``rows`` and move the pages they name into
     a dense local pool (local ids in order of first use)."""
     table = inputs.block_table[rows][:, page_lo:page_hi].cpu().long()
@@ -75,7 +75,7 @@ def shard_sequences(inputs: PagedDecodeInputs, rank: int, world_size: int) -> tu
     """This rank's sequences (token-balanced) with a compacted local page pool."""
     rows = lpt_partition(inputs.seq_lens.tolist(), world_size)[rank]
     idx = torch.tensor(rows, dtype=torch.long)
-    return _compact(inputs, idx, 0, inputs.block_table.shape[1], inputs.seq_lens.cpu()[idx]), rows
+    return compact_rows(inputs, idx, 0, inputs.block_table.shape[1], inputs.seq_lens.cpu()[idx]), rows
 
 
 def kv_range_bounds(max_seq_len: int, rank: int, world_size: int) -> tuple[int, int]:
@@ -92,16 +92,17 @@ def shard_kv_range(inputs: PagedDecodeInputs, rank: int, world_size: int) -> Pag
     lens = (inputs.seq_lens.cpu().long() - lo).clamp(0, max(hi - lo, 0))
     rows = torch.arange(inputs.query.shape[0])
     hi_page = max(hi // PAGE_SIZE, lo // PAGE_SIZE + 1)
-    return _compact(inputs, rows, lo // PAGE_SIZE, hi_page, lens)
+    return compact_rows(inputs, rows, lo // PAGE_SIZE, hi_page, lens)
 
 
-def _cuda_partial(local: PagedDecodeInputs, split_size: int) -> torch.Tensor:
+def _cuda_partial(local: PagedDecodeInputs, split_size: int, workspace=None, packed=None) -> torch.Tensor:
     from . import l20_paged_decode as ops
     from .l20_paged_split_kv import allocate_l20_paged_split_kv_workspace
 
     q = local.query
-    packed = torch.empty(q.shape[0], q.shape[1], q.shape[2] + 2, device=q.device, dtype=torch.float32)
-    ws = allocate_l20_paged_split_kv_workspace(q, max(local.max_seq_len, 1), split_size=split_size)
+    if packed is None:
+        packed = torch.empty(q.shape[0], q.shape[1], q.shape[2] + 2, device=q.device, dtype=torch.float32)
+    ws = workspace or allocate_l20_paged_split_kv_workspace(q, max(local.max_seq_len, 1), split_size=split_size)
     ops.paged_decode_fp8_e4m3_split_out_v2(
         q, local.key_cache, local.value_cache, local.block_table, local.seq_lens, ws[0], ws[1], ws[2], None,
         local.k_scale, local.v_scale, local.max_seq_len, split_size, packed_output=packed, semaphores=ws[4],
@@ -123,10 +124,16 @@ def kv_range_decode(
     partial_fn: Callable[[PagedDecodeInputs, int], torch.Tensor] = _cuda_partial,
     merge_fn: Callable[[torch.Tensor, torch.Tensor], torch.Tensor] = _cuda_merge,
     gather_buffer: Optional[torch.Tensor] = None,
+    workspace=None,
+    packed_buffer: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """One decode step of a KV-range-sharded batch: local packed partial, one all-gather of
-    ``[B, Hq, D + 2]`` fp32 per rank, LSE merge on every rank.  Returns ``[B, Hq, D]``."""
-    packed = partial_fn(local, split_size).contiguous()
+    ``[B, Hq, D + 2]`` fp32 per rank, LSE merge on every rank.  Returns ``[B, Hq, D]``.
+    ``workspace`` / ``packed_buffer`` / ``gather_buffer`` let a caller reuse its allocations."""
+    if partial_fn is _cuda_partial:
+        packed = _cuda_partial(local, split_size, workspace, packed_buffer)
+    else:
+        packed = partial_fn(local, split_size).contiguous()
     world = dist.get_world_size(group)
     if gather_buffer is None:
         gather_buffer = torch.empty((world, *packed.shape), device=packed.device, dtype=packed.dtype)
