@@ -37,8 +37,9 @@ extern "C" {
 #define PFD_FLAG_PARTIAL_ONLY 4u  /* launch the split-KV partial kernel only (kernel timing)   */
 #define PFD_FLAG_FIXED_SPLITS 8u  /* always use the fixed-split grid + merge kernel, even when
                                      semaphores are given (partials then follow split_size)    */
-#define PFD_FLAG_BALANCED 16u     /* use the one-kernel balanced path whenever it is eligible
-                                     (by default only for batch * kv_heads >= 256)             */
+#define PFD_FLAG_BALANCED 16u     /* use the one-kernel balanced path (needs semaphores, head_dim
+                                     128, f32 partials, workspace_splits >= 2); split_size then
+                                     only sizes the workspace                                  */
 
 /*
  * Operands of one decode-attention layer-step.
@@ -112,10 +113,10 @@ typedef struct pfd_decode_args {
   void* stream; /* cudaStream_t */
 
   /* Optional [batch * num_kv_heads] int32, all zero on entry and left all zero on return.
-   * With it (and head_dim 128, f32 partials, workspace_splits >= 2) the step runs as ONE
-   * kernel: a persistent grid shares the KV bytes of all sequences in equal chunks and the
-   * CTA that retires the last piece of a (sequence, kv head) merges the pieces itself.  The
-   * partial workspace then holds those pieces, not split_size-sized splits. */
+   * With it and PFD_FLAG_BALANCED (and head_dim 128, f32 partials, workspace_splits >= 2) the
+   * step runs as ONE kernel: a persistent grid shares the KV bytes of all sequences in equal
+   * chunks and the CTA that retires the last piece of a (sequence, kv head) merges the pieces
+   * itself.  The partial workspace then holds those pieces, not split_size-sized splits. */
   int32_t* semaphores;
   int64_t num_semaphores;
 } pfd_decode_args;

@@ -56,6 +56,13 @@ struct KernelParams {
   int32_t bt_cols;     // width of a block-table row
 };
 
+// Programmatic dependent launch: the split-KV partial kernel lets its dependent (the merge
+// kernel, launched with the programmatic-serialization attribute) be scheduled while it is
+// still running; the merge kernel reads seq_lens, then waits here until the whole partial grid
+// has completed and its memory is visible.  Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // The one address function every kernel uses for "which cache slot holds token t of
 // sequence b".  Returns the physical page; the slot is page * 16 + t % 16.
 __device__ __forceinline__ int32_t page_of(const int32_t* __restrict__ block_table,
@@ -431,6 +438,7 @@ __device__ __forceinline__ void cta_merge_and_store(WarpState<D>& st, const Kern
 template <int D, bool QBF16, int NWARPS>
 __global__ void __launch_bounds__(NWARPS * 32)
 paged_decode_fp8_partial_ldg_kernel(const KernelParams p) {
+  pdl_launch_dependents();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int seq_len = p.seq_lens[b];
   const int lo = p.kv_start + split * p.split_size;
@@ -561,6 +569,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   constexpr int D = 128;
   constexpr uint32_t kTileBytes = kPage * D;  // 2 KiB
   constexpr uint32_t kStageBytes = 4 * kTileBytes;
+  pdl_launch_dependents();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
   const int lo = p.kv_start + split * p.split_size;
@@ -736,18 +745,46 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
   for (int e = 0; e < E; ++e) acc[e] = 0.f;
   float big = -INFINITY, den = 0.f;
   if (ns == 1 && p.direct_out) return;  // written by the partial kernel
+  pdl_wait();  // the partial kernel's stores are complete and visible from here on
   if (ns > 0) {
     const int64_t base = (int64_t)b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h;
-    for (int s = lane; s < ns; s += 32) big = fmaxf(big, p.partial_max[base + s * p.partial_stride_s]);
+    // One pass with a running maximum; four splits per round trip, their maxima, sums and data
+    // requested together.
+    for (int s0 = 0; s0 < ns; s0 += 4) {
+      float mv[4], lv[4], xv[4][E];
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
-    for (int s = 0; s < ns; ++s) {
-      const int64_t pidx = base + s * p.partial_stride_s;
-      const float c = expf(p.partial_max[pidx] - big);
-      den += p.partial_sum[pidx] * c;
+      for (int u = 0; u < 4; ++u) {
+        const bool on = s0 + u < ns;
+        const int64_t pidx = base + (int64_t)(on ? s0 + u : 0) * p.partial_stride_s;
+        mv[u] = on ? p.partial_max[pidx] : -INFINITY;
+        lv[u] = on ? p.partial_sum[pidx] : 0.f;
+        if (p.partial_dtype == 0) {
+          const float* src = reinterpret_cast<const float*>(p.partial_output) + pidx * D + lane * E;
+          if constexpr (E == 4) {
+            const float4 x = *reinterpret_cast<const float4*>(src);
+            xv[u][0] = x.x; xv[u][1] = x.y; xv[u][2] = x.z; xv[u][3] = x.w;
+          } else {
+            const float2 x = *reinterpret_cast<const float2*>(src);
+            xv[u][0] = x.x; xv[u][1] = x.y;
+          }
+        } else {
 #pragma unroll
-      for (int e = 0; e < E; ++e)
-        acc[e] += c * load_partial_elem(p.partial_output, p.partial_dtype, pidx * D + lane * E + e);
+          for (int e = 0; e < E; ++e) xv[u][e] = load_partial_elem(p.partial_output, p.partial_dtype, pidx * D + lane * E + e);
+        }
+      }
+      const float m_new = fmaxf(fmaxf(big, fmaxf(mv[0], mv[1])), fmaxf(mv[2], mv[3]));
+      const float keep = (big == -INFINITY) ? 0.f : expf(big - m_new);
+      den *= keep;
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[e] *= keep;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float c = (mv[u] == -INFINITY) ? 0.f : expf(mv[u] - m_new);
+        den += lv[u] * c;
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[e] += c * xv[u][e];
+      }
+      big = m_new;
     }
   }
   if (p.packed_output != nullptr) {

@@ -62,26 +62,33 @@ def allocate_l20_paged_split_kv_workspace(
 
 def choose_split_size(batch: int, num_kv_heads: int, max_seq_len: int, *, seq_lens=None,
                       sm_count: int = 148, ctas_per_sm: int = 3, minimum: int = 128, step: int = 64) -> int:
-    """Split size for the fixed-split grid: the smallest multiple of ``step`` whose grid of
-    live (sequence, kv head, split) work items still fits in one wave of resident CTAs
-    (``sm_count * ctas_per_sm``).  One full wave is what the kernel likes: a second, partly
-    filled wave costs about as much as the first.  ``seq_lens`` (host ints, e.g. the engine's
+    """Split size for the fixed-split grid, from host-side knowledge only (no device read).
+
+    The kernel likes exactly one wave of live (sequence, kv head, split) work items: a second,
+    partly filled wave costs about as much as the first.  With ``target`` = token-heads per
+    resident CTA slot, the smallest multiple of ``step`` whose item count fits the
+    ``sm_count * ctas_per_sm`` slots is used if it is at most ``1.5 * target``; batches with more
+    (sequence, kv head) pairs than slots cannot fit one wave, they get ``0.8 * target`` (a few
+    waves of small items, measured best on B200).  ``seq_lens`` (host ints, e.g. the engine's
     CPU copy of the sequence lengths) makes the count exact; without it every sequence is
-    assumed to be ``max_seq_len`` long.  Host-only arithmetic, no device read."""
-    if batch * num_kv_heads >= 256:
-        # many (sequence, kv head) segments: the library's balanced kernel shares the work out by
-        # itself; the split size then only sizes the workspace (>= 2 slots per row are needed)
-        return 512
+    taken as ``max_seq_len`` long."""
     slots = sm_count * ctas_per_sm
     lens = [int(x) for x in seq_lens] if seq_lens is not None else [int(max_seq_len)] * int(batch)
-    longest = max([max_seq_len, *lens, 1])
-    split = max(minimum, step)
-    while split < longest:
-        items = num_kv_heads * sum(_cdiv(n, split) for n in lens if n > 0)
-        if items <= slots:
-            break
+    lens = [n for n in lens if n > 0] or [1]
+    longest = max(max_seq_len, max(lens))
+    target = max(1.0, num_kv_heads * sum(lens) / slots)
+
+    def round_up(x: float) -> int:
+        return max(minimum, _cdiv(int(x), step) * step)
+
+    split = round_up(target)
+    while split < longest and split <= 1.5 * target:
+        if num_kv_heads * sum(_cdiv(n, split) for n in lens) <= slots:
+            return int(split)
         split += step
-    return int(split)
+    if num_kv_heads * len(lens) <= slots and split >= longest:
+        return int(round_up(longest))  # one item per pair already fits
+    return int(min(round_up(0.8 * target), round_up(longest)))
 
 
 def l20_paged_split_kv_attention_fp8(

@@ -115,10 +115,10 @@ def test_workspace_allocator_shapes():
     assert sem.dtype == torch.int32 and sem.numel() >= 3 * 2 and int(sem.abs().sum()) == 0
     assert po.shape == (3, 16, 16, 128) and po.dtype == torch.float32  # next_pow2(9) = 16
     assert pm.shape == ps.shape == (3, 16, 16) and out.shape == q.shape and out.dtype == q.dtype
-    assert m.choose_split_size(64, 2, 4096) % 16 == 0
-    assert 128 <= m.choose_split_size(256, 4, 8192) <= 8192
-    s = m.choose_split_size(4, 8, 131072)
-    assert s % 16 == 0 and 8 * 4 * -(-131072 // s) <= 444 < 8 * 4 * -(-131072 // (s - 64))
-    lens = [512, 4096, 2000, 100]
-    s = m.choose_split_size(4, 2, 4096, seq_lens=lens)
-    assert s == 128  # few sequences: the minimum already fits one wave
+    assert m.choose_split_size(64, 2, 4096) % 64 == 0
+    s = m.choose_split_size(4, 8, 131072)  # 32 long segments: one wave of 444 slots
+    assert s % 64 == 0 and 8 * 4 * -(-131072 // s) <= 444 < 8 * 4 * -(-131072 // (s - 64))
+    assert m.choose_split_size(4, 2, 4096, seq_lens=[512, 4096, 2000, 100]) == 128  # tiny batch: the minimum
+    many = [900] * 256  # more (sequence, kv head) pairs than slots: a few waves of small items
+    s = m.choose_split_size(256, 4, 8192, seq_lens=many)
+    assert 128 <= s <= 2048 and s % 64 == 0
