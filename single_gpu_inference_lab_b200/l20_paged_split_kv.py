@@ -144,6 +144,8 @@ def l20_paged_split_kv_attention_fp8(
     if isinstance(k_scale, torch.Tensor) or isinstance(v_scale, torch.Tensor) or semaphores is not None:
         def as_vec(s):
             if isinstance(s, torch.Tensor):
+                if s.dtype == torch.float32 and s.device == query.device and s.shape == (num_kv_heads,) and s.is_contiguous():
+                    return s  # the common case costs nothing
                 return s.to(device=query.device, dtype=torch.float32).reshape(-1).expand(num_kv_heads).contiguous()
             return torch.full((num_kv_heads,), float(s), device=query.device, dtype=torch.float32)
 
