@@ -63,6 +63,8 @@ def parse_args():
     p.add_argument("--pools", type=int, default=0, help="distinct KV pools rotated through (0 = enough to exceed L2 x3)")
     p.add_argument("--flags", type=int, default=0)
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-shared-prefix", action="store_true",
+                   help="shared-prefix-b64 only: use the ordinary decode path instead of the dense tcgen05 prefix pass")
     p.add_argument("--strong", action="store_true",
                    help="N > 1: shard ONE batch by sequence over the ranks (token-balanced) instead of one batch per rank")
     return p.parse_args()
@@ -251,12 +253,25 @@ def main() -> int:
     pools = min(pools, max(2, int(40e9 // pool_bytes)))
     kcs = [w.key_cache] + [w.key_cache.clone() for _ in range(pools - 1)]
     vcs = [w.value_cache] + [w.value_cache.clone() for _ in range(pools - 1)]
+    shared_prefix = w.prefix_len > 0 and not args.no_shared_prefix and d == 128
+    if shared_prefix and not args.split_size:
+        split = 512
     ws = l20_paged_split_kv.allocate_l20_paged_split_kv_workspace(q, w.max_seq_len, split_size=split)
+    if shared_prefix:
+        from single_gpu_inference_lab_b200 import l20_shared_prefix_decode_dispatch as spd
+
+        ws = spd.allocate_shared_prefix_workspace(q, w.max_seq_len, w.prefix_len, suffix_split_size=split)
     out = ws[3]
     packed = torch.empty(batch, hq, d + 2, device=dev) if kv_range_mode else None
     gathered = torch.empty(world, batch, hq, d + 2, device=dev) if kv_range_mode else None
 
     def step(i: int, flags: int = args.flags):
+        if shared_prefix:
+            cabi.shared_prefix_decode_fp8_e4m3(
+                q, kcs[i % pools], vcs[i % pools], w.block_table, w.seq_lens, prefix_len=w.prefix_len,
+                k_scale=w.k_scale, v_scale=w.v_scale, max_seq_len=w.max_seq_len, split_size=split, output=out,
+                workspace=ws)
+            return
         cabi.paged_decode_fp8_e4m3_split_out(
             q, kcs[i % pools], vcs[i % pools], w.block_table, w.seq_lens, k_scale=w.k_scale, v_scale=w.v_scale,
             max_seq_len=w.max_seq_len, split_size=split, output=None if kv_range_mode else out,
@@ -348,6 +363,10 @@ def main() -> int:
                 res = l20_paged_split_kv.l20_paged_split_kv_attention_fp8(
                     dq, kcs[i % pools], vcs[i % pools], dtable, dlens, k_scale=w.k_scale, v_scale=w.v_scale,
                     max_seq_len=w.max_seq_len, split_size=split, workspace=ws)
+        elif shared_prefix:
+            res = spd.shared_paged_prefix_paged_suffix_gqa_decode_attention_fp8(
+                dq, kcs[i % pools], vcs[i % pools], dtable, dlens, w.prefix_len, k_scale=w.k_scale, v_scale=w.v_scale,
+                max_seq_len=w.max_seq_len, suffix_split_size=split, workspace=ws)
         else:
             res = l20_paged_split_kv.l20_paged_split_kv_attention_fp8(
                 dq, kcs[i % pools], vcs[i % pools], dtable, dlens, k_scale=w.k_scale, v_scale=w.v_scale,
@@ -367,9 +386,11 @@ def main() -> int:
         ms_step = timed_graph(step, args.steps)
         launches = per_step * args.steps                  # replayed from graphs inside the timed region
         path = cabi.last_path()
-        fused = (not kv_range_mode) and per_step == 1     # one kernel per step: it IS the step
+        fused = ((not kv_range_mode) and per_step == 1) or shared_prefix  # no single dominant kernel to time apart
         kernel_name = {1: "paged_decode_fp8_partial_ldg_kernel", 2: "paged_decode_fp8_partial_tma_kernel",
                        3: "paged_decode_fp8_balanced_kernel"}.get(path, "?")
+        if shared_prefix:
+            kernel_name = "shared_prefix_dense_kernel + paged_decode_fp8_partial_tma_kernel + paged_decode_merge_kernel"
         ms_kernel = timed_graph(step if fused else (lambda i: step(i, args.flags | cabi.PFD_FLAG_PARTIAL_ONLY)), args.steps)
         ms_e2e = timed(e2e_step, args.steps)
         ms_eager = timed(step, args.steps)
@@ -405,6 +426,9 @@ def main() -> int:
                 "workload": args.workload, "batch_per_gpu": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
                 "page_size": 16, "split_size": split, "max_seq_len": w.max_seq_len, "path": cabi.PATH_NAMES.get(path, "?"),
                 "kv_bytes_per_step_per_gpu": kv_bytes,
+                **({"shared_prefix_tokens": w.prefix_len,
+                    "unique_kv_bytes_per_step": int(w.prefix_len + (w.seq_lens - w.prefix_len).sum().item()) * hkv * d * 2,
+                    "prefix_pass": "dense tcgen05 (TMEM accumulators), 128 rows x 256 tokens per CTA"} if shared_prefix else {}),
                 "parallelism": ("kv-range split + all-gather" if kv_range_mode else
                                 ("one batch sharded by sequence (token-balanced), no collective" if args.strong
                                  else "one batch per GPU, no collective")) if world > 1 else "single GPU",

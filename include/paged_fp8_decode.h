@@ -156,6 +156,25 @@ int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args);
 int pfd_paged_decode_fp8_e4m3_split_out_noalloc(const pfd_decode_args* args);
 
 /*
+ * Decode step of a batch whose requests ALL share one paged prefix: block_table[b][0 ..
+ * prefix_len/16) names the same physical pages for every b (the caller checks that, e.g. with
+ * the grouping of find_l20_shared_prefix_groups,
+ * integrations/vllm/l20_shared_prefix_decode_dispatch.py:52-76).  Three kernels:
+ *   1. dense prefix pass on tcgen05 tensor cores: 128 (request, q head) rows x 256 prefix tokens
+ *      per CTA, K/V converted e4m3 -> f16 on the way into shared memory, accumulators in TMEM;
+ *      replaces _shared_paged_prefix_gqa_partial_kernel
+ *      (src/l20_stack/ops/triton_decode_attention.py:704-813);
+ *   2. suffix pass: the split-KV partial kernel with kv_start = prefix_len
+ *      (replaces _paged_suffix_gqa_partial_kernel, :815-912);
+ *   3. the LSE merge over prefix chunks and suffix splits
+ *      (replaces _prefix_suffix_gqa_reduce_kernel, :652-702).
+ * Needs head_dim 128, prefix_len a multiple of 16, an f32 workspace with
+ * workspace_splits >= ceil(prefix_len / 256) + ceil((max_seq_len - prefix_len) / split_size),
+ * and 16-byte aligned query rows.  kv_start must be 0.
+ */
+int pfd_shared_prefix_decode_fp8_e4m3(const pfd_decode_args* args, int32_t prefix_len);
+
+/*
  * LSE merge of `num_parts` packed partials [num_parts, rows, head_dim + 2] f32
  * (o un-normalised, m natural-log, l) into output [rows, head_dim] of `out_dtype`.
  * Same maths as _paged_split_kv_reduce (integrations/vllm/l20_paged_split_kv.py:459-488)

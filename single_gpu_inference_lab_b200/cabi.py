@@ -24,6 +24,7 @@ PFD_FLAG_BALANCED = 16
 EXPORTS = (
     "pfd_paged_decode_fp8_e4m3_split_out",
     "pfd_paged_decode_fp8_e4m3_split_out_noalloc",
+    "pfd_shared_prefix_decode_fp8_e4m3",
     "pfd_merge_packed",
     "pfd_resolve_slots",
     "pfd_device_status",
@@ -190,6 +191,17 @@ def paged_decode_fp8_e4m3_split_out(query, key_cache, value_cache, block_table, 
     args = decode_args(query, key_cache, value_cache, block_table, seq_lens, **kw)
     with torch.cuda.device(query.device):
         _check(load().pfd_paged_decode_fp8_e4m3_split_out(C.byref(args)))
+
+
+def shared_prefix_decode_fp8_e4m3(query, key_cache, value_cache, block_table, seq_lens, *, prefix_len, **kw) -> None:
+    """One layer-step through ``pfd_shared_prefix_decode_fp8_e4m3``: dense tcgen05 pass over the
+    prefix every request shares, split-KV pass over the private suffixes, one merge."""
+    args = decode_args(query, key_cache, value_cache, block_table, seq_lens, **kw)
+    lib = load()
+    lib.pfd_shared_prefix_decode_fp8_e4m3.argtypes = [C.POINTER(DecodeArgs), C.c_int32]
+    lib.pfd_shared_prefix_decode_fp8_e4m3.restype = C.c_int
+    with torch.cuda.device(query.device):
+        _check(lib.pfd_shared_prefix_decode_fp8_e4m3(C.byref(args), int(prefix_len)))
 
 
 NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024

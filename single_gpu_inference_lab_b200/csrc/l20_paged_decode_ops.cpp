@@ -33,7 +33,8 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
                 const c10::optional<at::Tensor>& packed_output, double k_scale, double v_scale,
                 const c10::optional<at::Tensor>& k_scale_ph, const c10::optional<at::Tensor>& v_scale_ph,
                 double sm_scale, int64_t max_seq_len, int64_t split_size, int64_t kv_start,
-                int64_t flags, const c10::optional<at::Tensor>& semaphores = c10::nullopt) {
+                int64_t flags, const c10::optional<at::Tensor>& semaphores = c10::nullopt,
+                int64_t prefix_len = 0) {
   TORCH_CHECK(query.is_cuda(), "query must be CUDA");
   TORCH_CHECK(query.scalar_type() == at::kHalf || query.scalar_type() == at::kBFloat16,
               "query must be FP16 or BF16");
@@ -147,7 +148,8 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
   }
   const at::cuda::CUDAGuard guard(query.device());
   a.stream = at::cuda::getCurrentCUDAStream().stream();
-  const int rc = pfd_paged_decode_fp8_e4m3_split_out(&a);
+  const int rc = prefix_len > 0 ? pfd_shared_prefix_decode_fp8_e4m3(&a, static_cast<int32_t>(prefix_len))
+                                : pfd_paged_decode_fp8_e4m3_split_out(&a);
   TORCH_CHECK(rc == PFD_OK, pfd_last_error());
 }
 
@@ -188,6 +190,19 @@ void paged_decode_fp8_e4m3_split_out_v2(at::Tensor query, at::Tensor key_cache, 
   run_decode(query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max,
              partial_sum, output, packed_output, 1.0, 1.0, k_scale, v_scale, sm_scale, max_seq_len,
              split_size, kv_start, flags, semaphores);
+}
+
+// Decode step of a batch whose requests all share the first prefix_len tokens' pages: dense
+// tcgen05 prefix pass + split-KV suffix pass + merge (pfd_shared_prefix_decode_fp8_e4m3).
+void shared_prefix_decode_fp8_e4m3(at::Tensor query, at::Tensor key_cache, at::Tensor value_cache,
+                                   at::Tensor block_table, at::Tensor seq_lens, at::Tensor partial_output,
+                                   at::Tensor partial_max, at::Tensor partial_sum, at::Tensor output,
+                                   at::Tensor k_scale, at::Tensor v_scale, double sm_scale,
+                                   int64_t max_seq_len, int64_t split_size, int64_t prefix_len) {
+  TORCH_CHECK(prefix_len > 0, "prefix_len must be positive");
+  run_decode(query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max, partial_sum,
+             output, c10::nullopt, 1.0, 1.0, k_scale, v_scale, sm_scale, max_seq_len, split_size, 0, 0,
+             c10::nullopt, prefix_len);
 }
 
 void merge_packed_partials(at::Tensor packed, at::Tensor output) {
@@ -244,6 +259,11 @@ TORCH_LIBRARY(l20_stack, module) {
       "Tensor(c!)? partial_sum, Tensor(d!)? output, Tensor(e!)? packed_output, "
       "Tensor k_scale, Tensor v_scale, float sm_scale, "
       "int max_seq_len, int split_size, int kv_start, int flags, Tensor(f!)? semaphores) -> ()");
+  module.def(
+      "shared_prefix_decode_fp8_e4m3("
+      "Tensor query, Tensor key_cache, Tensor value_cache, Tensor block_table, Tensor seq_lens, "
+      "Tensor(a!) partial_output, Tensor(b!) partial_max, Tensor(c!) partial_sum, Tensor(d!) output, "
+      "Tensor k_scale, Tensor v_scale, float sm_scale, int max_seq_len, int split_size, int prefix_len) -> ()");
   module.def("merge_packed_partials(Tensor packed, Tensor(a!) output) -> ()");
   module.def("resolve_slots(Tensor block_table, Tensor seq_lens, Tensor(a!) slots) -> ()");
 }
@@ -251,6 +271,7 @@ TORCH_LIBRARY(l20_stack, module) {
 TORCH_LIBRARY_IMPL(l20_stack, CUDA, module) {
   module.impl("paged_decode_fp8_e4m3_split_out", &paged_decode_fp8_e4m3_split_out);
   module.impl("paged_decode_fp8_e4m3_split_out_v2", &paged_decode_fp8_e4m3_split_out_v2);
+  module.impl("shared_prefix_decode_fp8_e4m3", &shared_prefix_decode_fp8_e4m3);
   module.impl("merge_packed_partials", &merge_packed_partials);
   module.impl("resolve_slots", &resolve_slots);
 }

@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "paged_decode_balanced.cuh"
+#include "shared_prefix_dense.cuh"
 #include "paged_decode_kernels.cuh"
 
 namespace {
@@ -300,7 +301,12 @@ const char* pfd_last_error(void) { return g_last_error.c_str(); }
 
 int64_t pfd_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
-int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args) {
+}  // extern "C"
+
+namespace {
+// slot_offset > 0: workspace slots [0, slot_offset) are filled by the dense prefix pass; the
+// split-KV kernels then write behind them and the merge kernel covers both.
+int decode_impl(const pfd_decode_args* args, int slot_offset) {
   if (args == nullptr) return fail(PFD_ERR_INVALID, "args is NULL");
   if (args->struct_size != sizeof(pfd_decode_args))
     return fail(PFD_ERR_INVALID, "pfd_decode_args size mismatch: caller %u, library %zu",
@@ -336,11 +342,11 @@ int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args) {
   const int span = a.max_seq_len > a.kv_start ? a.max_seq_len - a.kv_start : 0;
   int num_splits = (span + a.split_size - 1) / a.split_size;
   if (num_splits < 1) num_splits = 1;
-  const bool direct_ok = !(a.flags & PFD_FLAG_NO_DIRECT_OUT);
+  const bool direct_ok = !(a.flags & PFD_FLAG_NO_DIRECT_OUT) && slot_offset == 0;
   if (num_splits > 1 || !direct_ok) {
     if (!a.partial_output || !a.partial_max || !a.partial_sum)
       return fail(PFD_ERR_INVALID, "partial output workspace has wrong shape");
-    if (a.workspace_splits < num_splits)
+    if (a.workspace_splits < num_splits + slot_offset)
       return fail(PFD_ERR_INVALID, "partial output workspace has wrong shape");
     if (a.partial_dtype < PFD_DTYPE_F32 || a.partial_dtype > PFD_DTYPE_BF16)
       return fail(PFD_ERR_INVALID, "partial_output dtype must be f32, f16 or bf16");
@@ -375,12 +381,102 @@ int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args) {
   kp.partial_dtype = a.partial_dtype;
   kp.direct_out = direct_ok ? 1 : 0;
   kp.bt_cols = (a.max_seq_len + pfd::kPage - 1) / pfd::kPage;  // rows are at least this wide
+  kp.slot_offset = slot_offset;
 
   const bool bf16 = a.query_dtype == PFD_DTYPE_BF16;
   if (a.head_dim == 128)
     return bf16 ? launch_decode<128, true>(a, kp, num_splits) : launch_decode<128, false>(a, kp, num_splits);
   return bf16 ? launch_decode<64, true>(a, kp, num_splits) : launch_decode<64, false>(a, kp, num_splits);
 }
+
+template <bool QBF16>
+int launch_prefix(const pfd_decode_args& a, int prefix_len, int chunks) {
+  pfd::KernelParams kp{};
+  kp.query = a.query;
+  kp.key_cache = static_cast<const uint8_t*>(a.key_cache);
+  kp.value_cache = static_cast<const uint8_t*>(a.value_cache);
+  kp.block_table = a.block_table;
+  kp.seq_lens = a.seq_lens;
+  kp.k_scale_ph = a.k_scale_per_head;
+  kp.v_scale_ph = a.v_scale_per_head;
+  kp.partial_output = a.partial_output;
+  kp.partial_max = a.partial_max;
+  kp.partial_sum = a.partial_sum;
+  kp.q_stride_b = a.q_stride_b; kp.q_stride_h = a.q_stride_h;
+  kp.k_stride_page = a.k_stride_page; kp.k_stride_token = a.k_stride_token; kp.k_stride_head = a.k_stride_head;
+  kp.v_stride_page = a.v_stride_page; kp.v_stride_token = a.v_stride_token; kp.v_stride_head = a.v_stride_head;
+  kp.bt_stride_b = a.bt_stride_b;
+  kp.partial_stride_b = a.partial_stride_b; kp.partial_stride_h = a.partial_stride_h;
+  kp.partial_stride_s = a.partial_stride_s;
+  kp.k_scale = a.k_scale; kp.v_scale = a.v_scale;
+  kp.sm_scale = a.sm_scale != 0.f ? a.sm_scale : 1.0f / sqrtf(128.f);
+  kp.num_q_heads = a.num_q_heads; kp.num_kv_heads = a.num_kv_heads;
+  kp.group = a.num_q_heads / a.num_kv_heads;
+  pfd::PrefixParams pp{};
+  pp.prefix_len = prefix_len;
+  pp.batch = a.batch;
+  if (int rc = status_pointer(&pp.status)) return rc;
+  auto kernel = pfd::shared_prefix_dense_kernel<QBF16>;
+  constexpr int smem = 1024 + 160 * 1024 + 64;
+  static bool configured[kMaxDevices] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= kMaxDevices) return fail(PFD_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  if (!configured[dev]) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    configured[dev] = true;
+  }
+  const int rows = a.batch * kp.group;
+  const dim3 grid(chunks, (rows + pfd::kPrefixRows - 1) / pfd::kPrefixRows, a.num_kv_heads);
+  kernel<<<grid, 128, smem, static_cast<cudaStream_t>(a.stream)>>>(kp, pp);
+  return check_launch("shared-prefix dense kernel");
+}
+}  // namespace
+
+extern "C" {
+
+int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args) { return decode_impl(args, 0); }
+
+int pfd_shared_prefix_decode_fp8_e4m3(const pfd_decode_args* args, int32_t prefix_len) {
+  if (args == nullptr) return fail(PFD_ERR_INVALID, "args is NULL");
+  if (args->struct_size != sizeof(pfd_decode_args))
+    return fail(PFD_ERR_INVALID, "pfd_decode_args size mismatch: caller %u, library %zu", args->struct_size,
+                sizeof(pfd_decode_args));
+  pfd_decode_args a = *args;
+  if (a.head_dim != 128 || a.page_size != pfd::kPage)
+    return fail(PFD_ERR_UNSUPPORTED, "the shared-prefix pass needs head_dim 128 and page_size 16");
+  if (prefix_len <= 0 || prefix_len % pfd::kPage != 0 || prefix_len > a.max_seq_len)
+    return fail(PFD_ERR_INVALID, "prefix_len must be a positive multiple of 16 not above max_seq_len");
+  if (a.kv_start != 0) return fail(PFD_ERR_INVALID, "kv_start must be 0 for the shared-prefix pass");
+  if (a.batch <= 0) return a.batch == 0 ? PFD_OK : fail(PFD_ERR_INVALID, "invalid query");
+  if (a.num_kv_heads <= 0 || a.num_q_heads % a.num_kv_heads != 0 || a.num_q_heads / a.num_kv_heads > 16)
+    return fail(PFD_ERR_INVALID, "Q heads must be divisible by KV heads (at most 16 per KV head)");
+  if (!a.partial_output || !a.partial_max || !a.partial_sum || a.partial_dtype != PFD_DTYPE_F32)
+    return fail(PFD_ERR_INVALID, "the shared-prefix pass needs an f32 partial workspace");
+  const int chunks = (prefix_len + pfd::kPrefixChunk - 1) / pfd::kPrefixChunk;
+  if (!a.query || !a.key_cache || !a.value_cache || !a.block_table || !a.seq_lens)
+    return fail(PFD_ERR_INVALID, "NULL operand");
+  if ((reinterpret_cast<uintptr_t>(a.query) & 15u) || a.q_stride_h % 8 || a.q_stride_b % 8)
+    return fail(PFD_ERR_UNSUPPORTED, "query rows must be 16-byte aligned for the shared-prefix pass");
+  const bool bf16 = a.query_dtype == PFD_DTYPE_BF16;
+  if (!bf16 && a.query_dtype != PFD_DTYPE_F16) return fail(PFD_ERR_INVALID, "query must be FP16 or BF16");
+  // the suffix pass validates the rest (it sees the same operands) before anything is launched
+  a.kv_start = prefix_len;
+  a.flags |= PFD_FLAG_FIXED_SPLITS | PFD_FLAG_NO_DIRECT_OUT;
+  a.flags &= ~(uint32_t)(PFD_FLAG_PARTIAL_ONLY | PFD_FLAG_BALANCED);
+  {
+    const int span = a.max_seq_len - prefix_len;
+    const int ns = span > 0 ? (span + a.split_size - 1) / a.split_size : 1;
+    if (a.split_size < 16 || a.split_size % 16) return fail(PFD_ERR_INVALID, "split_size must be a multiple of 16");
+    if (a.workspace_splits < chunks + ns)
+      return fail(PFD_ERR_INVALID, "partial output workspace has wrong shape: the shared-prefix pass needs %d slots",
+                  chunks + ns);
+  }
+  if (int rc = bf16 ? launch_prefix<true>(a, prefix_len, chunks) : launch_prefix<false>(a, prefix_len, chunks)) return rc;
+  return decode_impl(&a, chunks);
+}
+
 
 // ---- allocation-free entry point -------------------------------------------------------
 // The partial workspace of the split-KV path as a fixed array in the library image.  In host

@@ -54,6 +54,7 @@ struct KernelParams {
   int32_t partial_dtype;
   int32_t direct_out;  // 1: a sequence with a single split writes its final result itself
   int32_t bt_cols;     // width of a block-table row
+  int32_t slot_offset; // workspace slots [0, slot_offset) are filled by another kernel (dense prefix pass)
 };
 
 // Programmatic dependent launch: the split-KV partial kernel lets its dependent (the merge
@@ -423,7 +424,7 @@ __device__ __forceinline__ void cta_merge_and_store(WarpState<D>& st, const Kern
       }
     } else {
       const int64_t pidx = (int64_t)b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h +
-                           (int64_t)split * p.partial_stride_s;
+                           (int64_t)(split + p.slot_offset) * p.partial_stride_s;
       store_partial_elem4(p.partial_output, p.partial_dtype, pidx * D + c4, acc);
       if (c4 == 0) {
         p.partial_max[pidx] = big_row * kLn2;
@@ -738,7 +739,7 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
   const int b = row / p.num_q_heads, hq = row % p.num_q_heads;
   const int seq_len = p.seq_lens[b];
   const int live = seq_len - p.kv_start;
-  const int ns = live > 0 ? (live + p.split_size - 1) / p.split_size : 0;
+  const int ns = (live > 0 ? (live + p.split_size - 1) / p.split_size : 0) + p.slot_offset;
   constexpr int E = D / 32;  // elements per lane
   float acc[E];
 #pragma unroll

@@ -1,0 +1,311 @@
+// Dense shared-prefix pass on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a.
+//
+// When every request of a batch attends the same paged prefix (same physical pages in every
+// block-table row), the (request, query head) rows of one kv head form a dense matrix:
+// 64 requests x 8 heads = 512 rows against the same K/V.  One CTA takes 128 of those rows
+// (M = 128), one kv head and one chunk of 256 prefix tokens:
+//
+//   S[128 x 256] = Q[128 x 128] K^T        tcgen05.mma kind::f16, accumulator in TMEM columns 0..255
+//   softmax row-wise, one thread per row (TMEM lane), no shuffles; P (f16) goes to shared memory
+//   O[128 x 128] = P[128 x 256] V          tcgen05.mma, accumulator in TMEM columns 256..383
+//
+// K and V are e4m3 in HBM; the CTA converts its 256 tokens to f16 (exact) while staging them
+// into the 128-byte-swizzled K-major layout the MMA reads (V transposed on the way, so that
+// tokens are the contiguous K dimension of the second product).  A whole chunk is one softmax
+// tile, so there is no running maximum and nothing in TMEM is ever rescaled.  The CTA writes
+// (o, m, l) of its rows into slot `chunk` of the ordinary split-KV workspace; the suffix pass
+// (the generic kernel with kv_start = prefix length) fills the slots after them and the usual
+// merge kernel finishes.
+//
+// Reference counterpart: _shared_paged_prefix_gqa_partial_kernel (tl.dot over BLOCK_M <= 8
+// rows x 128 tokens), src/l20_stack/ops/triton_decode_attention.py:704-813.
+#pragma once
+
+#include "paged_decode_kernels.cuh"
+
+namespace pfd {
+
+constexpr int kPrefixChunk = 256;  // prefix tokens per CTA
+constexpr int kPrefixRows = 128;   // (request, head) rows per CTA
+constexpr int kErrUmmaTimeout = 3;
+
+// ---- tcgen05 / TMEM primitives ---------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {  // one full warp
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {  // one full warp
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major operand in the canonical 128-byte-swizzled
+// layout: rows of 64 f16 (128 bytes), 8 rows per 1 KiB atom, atoms stacked along M/N
+// (stride-dimension byte offset 1024).  `addr` is the byte address of the first element of
+// the 16-element K slice to multiply (a multiple of 32 bytes inside the row).
+__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);       // start address, bits [0,14)
+  d |= (uint64_t)1 << 16;                      // leading-dimension byte offset (unused here), bits [16,30)
+  d |= (uint64_t)(1024 >> 4) << 32;            // stride-dimension byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                      // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                      // layout type: 128-byte swizzle
+  return d;
+}
+// Instruction descriptor of kind::f16: f16 x f16 -> f32, both operands K-major.
+__device__ __forceinline__ uint32_t umma_idesc_f16(int m, int n) {
+  return (1u << 4)                 // accumulator format f32
+         | (0u << 7) | (0u << 10)  // A and B are f16
+         | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {  // one thread
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t mbar) {  // one thread
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int t = 0; t < 32; ++t) v[t] = __uint_as_float(r[t]);
+}
+
+// Byte offset of the 16-byte chunk `c8` (8 f16) of row `row` inside one k-block
+// ([rows][64 f16], 128-byte swizzle, block base 1 KiB aligned).
+__device__ __forceinline__ uint32_t sw128_chunk(int row, int c8) {
+  return (uint32_t)((row >> 3) * 1024 + (row & 7) * 128 + ((c8 ^ (row & 7)) << 4));
+}
+
+// 16 e4m3 bytes -> 16 f16 (two 16-byte chunks)
+__device__ __forceinline__ void cvt16_e4m3_f16(const uint4& in, uint4& lo, uint4& hi) {
+  lo.x = cvt_e4m3x2_to_f16x2(in.x); lo.y = cvt_e4m3x2_to_f16x2(in.x >> 16);
+  lo.z = cvt_e4m3x2_to_f16x2(in.y); lo.w = cvt_e4m3x2_to_f16x2(in.y >> 16);
+  hi.x = cvt_e4m3x2_to_f16x2(in.z); hi.y = cvt_e4m3x2_to_f16x2(in.z >> 16);
+  hi.z = cvt_e4m3x2_to_f16x2(in.w); hi.w = cvt_e4m3x2_to_f16x2(in.w >> 16);
+}
+
+__device__ __forceinline__ void sts_16(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void sts_u16(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"((uint16_t)v) : "memory");
+}
+
+struct PrefixParams {
+  int32_t prefix_len;   // tokens shared by every request (multiple of 16)
+  int32_t batch;
+  int32_t* status;
+};
+
+// grid = (prefix chunks, 128-row tiles, kv heads), block = 128 threads, 1 CTA per SM.
+template <bool QBF16>
+__global__ void __launch_bounds__(128, 1)
+shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
+  constexpr int D = 128;
+  constexpr uint32_t kQBytes = kPrefixRows * D * 2;         // 32 KiB: 2 k-blocks of [128][64]
+  constexpr uint32_t kKBytes = kPrefixChunk * D * 2;        // 64 KiB: 2 k-blocks of [256][64]; later P: 4 x [128][64]
+  constexpr uint32_t kVBytes = D * kPrefixChunk * 2;        // 64 KiB: 4 k-blocks of [128 d][64 tokens]
+  const int chunk = blockIdx.x, mtile = blockIdx.y, kvh = blockIdx.z;
+  const int t = threadIdx.x, warp = t >> 5;
+  pdl_launch_dependents();
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sq = base, sk = base + kQBytes, sv = sk + kKBytes;
+  const uint32_t bars = sv + kVBytes;       // two mbarriers
+  const uint32_t tslot = bars + 16;         // TMEM base address written by tcgen05.alloc
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tslot_ptr = reinterpret_cast<volatile uint32_t*>(gen + kQBytes + kKBytes + kVBytes + 16);
+
+  if (t == 0) {
+    mbar_init(bars, 1);
+    mbar_init(bars + 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) tmem_alloc(tslot, 512);
+
+  const int tok_lo = chunk * kPrefixChunk;
+  const int tok_hi = min(tok_lo + kPrefixChunk, pp.prefix_len);
+
+  // ---- Q tile: thread t owns row (mtile * 128 + t) = (request, head of the group)
+  const int row_g = mtile * kPrefixRows + t;
+  const int b = row_g / p.group, head = row_g % p.group;
+  const bool row_live = b < pp.batch;
+  {
+    const uint16_t* q = reinterpret_cast<const uint16_t*>(p.query) + (int64_t)(row_live ? b : 0) * p.q_stride_b +
+                        (int64_t)(kvh * p.group + head) * p.q_stride_h;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      uint4 x = make_uint4(0u, 0u, 0u, 0u);
+      if (row_live) x = __ldg(reinterpret_cast<const uint4*>(q) + c);
+      if constexpr (QBF16) {
+        uint32_t* w = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
+          w[e] = pack_f16x2(__bfloat162float(v.x), __bfloat162float(v.y));
+        }
+      }
+      sts_16(sq + (c >> 3) * (kPrefixRows * 128) + sw128_chunk(t, c & 7), x);
+    }
+  }
+  // ---- K and V chunk: thread t stages tokens t and t + 128 of the chunk
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int tr = t + 128 * half;            // token row inside the chunk
+    const int tok = tok_lo + tr;
+    const bool live = tok < tok_hi;
+    const uint8_t* krow = nullptr;
+    const uint8_t* vrow = nullptr;
+    if (live) {
+      const int64_t phys = page_of(p.block_table, p.bt_stride_b, 0, tok / kPage);
+      krow = p.key_cache + phys * p.k_stride_page + (int64_t)(tok % kPage) * p.k_stride_token + (int64_t)kvh * p.k_stride_head;
+      vrow = p.value_cache + phys * p.v_stride_page + (int64_t)(tok % kPage) * p.v_stride_token + (int64_t)kvh * p.v_stride_head;
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {  // 16 bytes = 16 head-dim elements at a time
+      uint4 kin = make_uint4(0u, 0u, 0u, 0u), vin = make_uint4(0u, 0u, 0u, 0u);
+      if (live) {
+        kin = ldg_nc_16(krow + 16 * c);
+        vin = ldg_nc_16(vrow + 16 * c);
+      }
+      uint4 lo, hi;
+      cvt16_e4m3_f16(kin, lo, hi);
+      // K: row = token, k = d; elements 16c .. 16c+15 are chunks 2c, 2c+1 of k-block (c / 4)
+      const uint32_t kb = sk + (c >> 2) * (kPrefixChunk * 128);
+      sts_16(kb + sw128_chunk(tr, (2 * c) & 7), lo);
+      sts_16(kb + sw128_chunk(tr, (2 * c + 1) & 7), hi);
+      // V^T: row = d, k = token; token tr is element (tr % 64) of k-block (tr / 64)
+      cvt16_e4m3_f16(vin, lo, hi);
+      const uint32_t vb = sv + (tr >> 6) * (D * 128);
+      const int kk = tr & 63;
+      const uint32_t* w = reinterpret_cast<const uint32_t*>(&lo);
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const int d = 16 * c + e;
+        const uint32_t word = (e < 8) ? w[e >> 1] : reinterpret_cast<const uint32_t*>(&hi)[(e - 8) >> 1];
+        sts_u16(vb + sw128_chunk(d, kk >> 3) + (kk & 7) * 2, (e & 1) ? (word >> 16) : word);
+      }
+    }
+  }
+  // generic-proxy writes -> visible to the tensor core's (async proxy) reads
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tslot_ptr;
+
+  // ---- S = Q K^T : M 128, N 256, K 128 = 2 k-blocks x 4 slices of 16
+  if (t == 0) {
+    const uint32_t idesc = umma_idesc_f16(128, 256);
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+      for (int s = 0; s < 4; ++s)
+        umma_f16(tmem, umma_desc_k_sw128(sq + kb * (kPrefixRows * 128) + 32 * s),
+                 umma_desc_k_sw128(sk + kb * (kPrefixChunk * 128) + 32 * s), idesc, (kb | s) ? 1u : 0u);
+    umma_commit(bars);
+  }
+  bool ok = mbar_wait_bounded(bars, 0);
+  tc_fence_after_sync();
+
+  // ---- softmax of this thread's row over the chunk's 256 scores
+  const float ks = p.k_scale_ph ? __ldg(p.k_scale_ph + kvh) : p.k_scale;
+  const float vs = p.v_scale_ph ? __ldg(p.v_scale_ph + kvh) : p.v_scale;
+  const float scale_log2 = ks * p.sm_scale * kLog2e;
+  const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32 TMEM lanes
+  const int n_live = tok_hi - tok_lo;
+  float mx = -INFINITY;
+  for (int c = 0; c < kPrefixChunk / 32; ++c) {
+    float v[32];
+    tmem_ld32(lane_addr + 32 * c, v);
+#pragma unroll
+    for (int e = 0; e < 32; ++e)
+      if (32 * c + e < n_live) mx = fmaxf(mx, v[e]);
+  }
+  mx *= scale_log2;  // scale_log2 > 0: the maximum commutes with it
+  float lsum = 0.f;
+  for (int c = 0; c < kPrefixChunk / 32; ++c) {
+    float v[32];
+    tmem_ld32(lane_addr + 32 * c, v);
+#pragma unroll
+    for (int e8 = 0; e8 < 4; ++e8) {
+      uint4 out;
+      uint32_t* w = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        const int i0 = 8 * e8 + e;
+        const float p0 = (32 * c + i0 < n_live) ? exp2f(v[i0] * scale_log2 - mx) : 0.f;
+        const float p1 = (32 * c + i0 + 1 < n_live) ? exp2f(v[i0 + 1] * scale_log2 - mx) : 0.f;
+        lsum += p0 + p1;
+        w[e >> 1] = pack_f16x2(p0, p1);
+      }
+      // P: row = t, k = token 32c + 8*e8 ..: chunk ((32c + 8 e8) % 64) / 8 of k-block (32c / 64)
+      const int tokc = 32 * c + 8 * e8;
+      sts_16(sk + (tokc >> 6) * (kPrefixRows * 128) + sw128_chunk(t, (tokc & 63) >> 3), out);
+    }
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  // ---- O = P V : M 128, N 128, K 256 = 4 k-blocks x 4 slices
+  if (t == 0) {
+    const uint32_t idesc = umma_idesc_f16(128, 128);
+#pragma unroll
+    for (int kb = 0; kb < 4; ++kb)
+#pragma unroll
+      for (int s = 0; s < 4; ++s)
+        umma_f16(tmem + 256, umma_desc_k_sw128(sk + kb * (kPrefixRows * 128) + 32 * s),
+                 umma_desc_k_sw128(sv + kb * (D * 128) + 32 * s), idesc, (kb | s) ? 1u : 0u);
+    umma_commit(bars + 8);
+  }
+  ok = mbar_wait_bounded(bars + 8, 0) && ok;
+  tc_fence_after_sync();
+
+  // ---- (o, m, l) of this row into slot `chunk` of the workspace (every lane takes part in the
+  // aligned TMEM loads; only live rows store)
+  {
+    const int hq = kvh * p.group + head;
+    const int64_t pidx = (int64_t)(row_live ? b : 0) * p.partial_stride_b + (int64_t)hq * p.partial_stride_h +
+                         (int64_t)chunk * p.partial_stride_s;
+    float* dst = reinterpret_cast<float*>(p.partial_output) + pidx * D;
+    for (int c = 0; c < D / 32; ++c) {
+      float v[32];
+      tmem_ld32(lane_addr + 256 + 32 * c, v);
+      if (row_live) {
+#pragma unroll
+        for (int e = 0; e < 32; e += 4)
+          *reinterpret_cast<float4*>(dst + 32 * c + e) = make_float4(v[e] * vs, v[e + 1] * vs, v[e + 2] * vs, v[e + 3] * vs);
+      }
+    }
+    if (row_live) {
+      p.partial_max[pidx] = mx * kLn2;
+      p.partial_sum[pidx] = lsum;
+    }
+  }
+  if (!ok && t == 0) atomicExch(pp.status, kErrUmmaTimeout);
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace pfd

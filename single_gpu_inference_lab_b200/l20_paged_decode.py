@@ -115,6 +115,35 @@ def paged_decode_fp8_e4m3_split_out_v2(
     return output
 
 
+def shared_prefix_decode_fp8_e4m3(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    partial_output: torch.Tensor,
+    partial_max: torch.Tensor,
+    partial_sum: torch.Tensor,
+    output: torch.Tensor,
+    k_scale: torch.Tensor,
+    v_scale: torch.Tensor,
+    max_seq_len: int,
+    split_size: int,
+    prefix_len: int,
+    *,
+    sm_scale: float = 0.0,
+) -> torch.Tensor:
+    """Decode step of a batch whose block-table rows all start with the same ``prefix_len // 16``
+    pages: dense tcgen05 pass over the shared prefix, split-KV pass over the private suffixes,
+    one merge.  The workspace needs ``ceil(prefix_len / 256) + ceil((max_seq_len - prefix_len) /
+    split_size)`` slots on its split axis."""
+    torch.ops.l20_stack.shared_prefix_decode_fp8_e4m3(
+        query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max, partial_sum, output,
+        k_scale, v_scale, float(sm_scale), max_seq_len, split_size, prefix_len,
+    )
+    return output
+
+
 def merge_packed_partials(packed: torch.Tensor, output: torch.Tensor) -> torch.Tensor:
     """LSE-merge ``[parts, B, Hq, D + 2]`` packed partials into ``output [B, Hq, D]``."""
     torch.ops.l20_stack.merge_packed_partials(packed, output)
@@ -149,6 +178,10 @@ def _register_fake() -> None:
 
     @torch.library.register_fake("l20_stack::paged_decode_fp8_e4m3_split_out_v2")
     def _paged_decode_fp8_e4m3_split_out_v2_fake(*args):
+        return None
+
+    @torch.library.register_fake("l20_stack::shared_prefix_decode_fp8_e4m3")
+    def _shared_prefix_decode_fake(*args):
         return None
 
     @torch.library.register_fake("l20_stack::merge_packed_partials")
