@@ -176,7 +176,23 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
     if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     configured[dev] = true;
   }
-  kernel<<<grid, kWarps * 32, smem, stream>>>(kp, tp, mk, mv);
+  if (kp.slot_offset > 0) {
+    // behind the dense prefix pass: independent work, let it run beside that pass
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kWarps * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, kp, tp, mk, mv);
+    if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "partial kernel (TMA) launch failed: %s", cudaGetErrorString(e));
+  } else {
+    kernel<<<grid, kWarps * 32, smem, stream>>>(kp, tp, mk, mv);
+  }
   return check_launch("partial kernel (TMA)");
 }
 
@@ -416,8 +432,9 @@ int launch_prefix(const pfd_decode_args& a, int prefix_len, int chunks) {
   pp.prefix_len = prefix_len;
   pp.batch = a.batch;
   if (int rc = status_pointer(&pp.status)) return rc;
+  pp.phase_times = g_phase_times;
   auto kernel = pfd::shared_prefix_dense_kernel<QBF16>;
-  constexpr int smem = 1024 + 160 * 1024 + 64;
+  constexpr int smem = 1024 + 160 * 1024 + 32 + 2 * 4 * 128 * 4;
   static bool configured[kMaxDevices] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -429,7 +446,7 @@ int launch_prefix(const pfd_decode_args& a, int prefix_len, int chunks) {
   }
   const int rows = a.batch * kp.group;
   const dim3 grid(chunks, (rows + pfd::kPrefixRows - 1) / pfd::kPrefixRows, a.num_kv_heads);
-  kernel<<<grid, 128, smem, static_cast<cudaStream_t>(a.stream)>>>(kp, pp);
+  kernel<<<grid, 512, smem, static_cast<cudaStream_t>(a.stream)>>>(kp, pp);
   return check_launch("shared-prefix dense kernel");
 }
 }  // namespace

@@ -444,7 +444,7 @@ paged_decode_fp8_partial_ldg_kernel(const KernelParams p) {
   const int seq_len = p.seq_lens[b];
   const int lo = p.kv_start + split * p.split_size;
   const int hi = min(lo + p.split_size, seq_len);
-  if (lo >= hi) return;  // the merge kernel derives the live split count from seq_len
+  if (lo >= hi) { pdl_wait(); return; }  // the merge kernel derives the live split count from seq_len
   const int nsplits_seq = (seq_len - p.kv_start + p.split_size - 1) / p.split_size;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
 
@@ -486,6 +486,7 @@ paged_decode_fp8_partial_ldg_kernel(const KernelParams p) {
     cur = nxt;
   }
   cta_merge_and_store<D, QBF16, NWARPS>(st, p, b, kvh, split, nsplits_seq, vs, sm_m, sm_l, sm_o);
+  pdl_wait();  // see the TMA kernel
 }
 
 // ---- TMA pipeline ---------------------------------------------------------------------------
@@ -587,7 +588,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   }
   const int seq_len = p.seq_lens[b];
   const int hi = min(lo + p.split_size, seq_len);
-  if (lo >= hi) return;
+  if (lo >= hi) { pdl_wait(); return; }
   const int nsplits_seq = (seq_len - p.kv_start + p.split_size - 1) / p.split_size;
 
   extern __shared__ uint8_t smem_raw[];
@@ -726,6 +727,10 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   }
   __syncthreads();  // every warp is done with its ring: sm_o may alias it
   cta_merge_and_store<D, QBF16, NWARPS>(st, p, b, kvh, split, nsplits_seq, vs, sm_m, sm_l, sm_o);
+  // When this grid was launched as a programmatic dependent of the dense prefix pass (it never
+  // reads that pass's results, so it starts right away), it must not complete before that pass:
+  // the merge kernel behind it waits for *this* grid only.  A no-op for an ordinary launch.
+  pdl_wait();
 }
 
 // LSE merge over the live splits of each (sequence, q head); one warp per row.
@@ -749,12 +754,12 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
   pdl_wait();  // the partial kernel's stores are complete and visible from here on
   if (ns > 0) {
     const int64_t base = (int64_t)b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h;
-    // One pass with a running maximum; four splits per round trip, their maxima, sums and data
+    // One pass with a running maximum; eight splits per round trip, their maxima, sums and data
     // requested together.
-    for (int s0 = 0; s0 < ns; s0 += 4) {
-      float mv[4], lv[4], xv[4][E];
+    for (int s0 = 0; s0 < ns; s0 += 8) {
+      float mv[8], lv[8], xv[8][E];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         const bool on = s0 + u < ns;
         const int64_t pidx = base + (int64_t)(on ? s0 + u : 0) * p.partial_stride_s;
         mv[u] = on ? p.partial_max[pidx] : -INFINITY;
@@ -773,13 +778,15 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
           for (int e = 0; e < E; ++e) xv[u][e] = load_partial_elem(p.partial_output, p.partial_dtype, pidx * D + lane * E + e);
         }
       }
-      const float m_new = fmaxf(fmaxf(big, fmaxf(mv[0], mv[1])), fmaxf(mv[2], mv[3]));
+      float m_new = big;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) m_new = fmaxf(m_new, mv[u]);
       const float keep = (big == -INFINITY) ? 0.f : expf(big - m_new);
       den *= keep;
 #pragma unroll
       for (int e = 0; e < E; ++e) acc[e] *= keep;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         const float c = (mv[u] == -INFINITY) ? 0.f : expf(mv[u] - m_new);
         den += lv[u] * c;
 #pragma unroll

@@ -87,6 +87,29 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   for (int t = 0; t < 32; ++t) v[t] = __uint_as_float(r[t]);
 }
 
+// 128 consecutive fp32 columns of this thread's TMEM lane: four loads in flight, one wait.
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld128(uint32_t taddr, float (&v)[128]) {
+  uint32_t r[4][32];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) tmem_ld32_nowait(taddr + 32 * q, r[q]);
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+#pragma unroll
+    for (int t = 0; t < 32; ++t) v[32 * q + t] = __uint_as_float(r[q][t]);
+}
+
 // Byte offset of the 16-byte chunk `c8` (8 f16) of row `row` inside one k-block
 // ([rows][64 f16], 128-byte swizzle, block base 1 KiB aligned).
 __device__ __forceinline__ uint32_t sw128_chunk(int row, int c8) {
@@ -112,19 +135,35 @@ struct PrefixParams {
   int32_t prefix_len;   // tokens shared by every request (multiple of 16)
   int32_t batch;
   int32_t* status;
+  unsigned long long* phase_times;  // optional [grid][8] nanosecond timestamps (tuning aid)
 };
 
-// grid = (prefix chunks, 128-row tiles, kv heads), block = 128 threads, 1 CTA per SM.
+__device__ __forceinline__ void prefix_mark(const PrefixParams& pp, int k) {
+  if (pp.phase_times != nullptr && threadIdx.x == 0) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const size_t cta = blockIdx.x + gridDim.x * (blockIdx.y + (size_t)gridDim.y * blockIdx.z);
+    pp.phase_times[cta * 8 + k] = t;
+  }
+}
+
+// grid = (prefix chunks, 128-row tiles, kv heads), block = 512 threads, 1 CTA per SM.
+// Warp w works on TMEM lanes (= rows) 32 * (w % 4) .. +31, the only ones it may address, and on
+// column group w / 4 of whatever is being read: with 16 warps the staging, the softmax and the
+// stores around the two MMAs are spread over all four schedulers four warps deep.
 template <bool QBF16>
-__global__ void __launch_bounds__(128, 1)
+__global__ void __launch_bounds__(512, 1)
 shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   constexpr int D = 128;
   constexpr uint32_t kQBytes = kPrefixRows * D * 2;         // 32 KiB: 2 k-blocks of [128][64]
-  constexpr uint32_t kKBytes = kPrefixChunk * D * 2;        // 64 KiB: 2 k-blocks of [256][64]; later P: 4 x [128][64]
+  constexpr uint32_t kKBytes = kPrefixChunk * D * 2;        // 64 KiB: 2 k-blocks of [256][64]; later P: 4 x [128][64]; later O rows
   constexpr uint32_t kVBytes = D * kPrefixChunk * 2;        // 64 KiB: 4 k-blocks of [128 d][64 tokens]
   const int chunk = blockIdx.x, mtile = blockIdx.y, kvh = blockIdx.z;
-  const int t = threadIdx.x, warp = t >> 5;
+  const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
+  const int qd = warp & 3, cg = warp >> 2;  // TMEM lane quarter, column group
+  const int row = 32 * qd + lane;           // this thread's (request, head) row of the tile
   pdl_launch_dependents();
+  prefix_mark(pp, 0);
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -133,6 +172,7 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   const uint32_t tslot = bars + 16;         // TMEM base address written by tcgen05.alloc
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   volatile uint32_t* tslot_ptr = reinterpret_cast<volatile uint32_t*>(gen + kQBytes + kKBytes + kVBytes + 16);
+  float* red = reinterpret_cast<float*>(gen + kQBytes + kKBytes + kVBytes + 32);  // [2][4][128] row partials
 
   if (t == 0) {
     mbar_init(bars, 1);
@@ -144,15 +184,35 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   const int tok_lo = chunk * kPrefixChunk;
   const int tok_hi = min(tok_lo + kPrefixChunk, pp.prefix_len);
 
-  // ---- Q tile: thread t owns row (mtile * 128 + t) = (request, head of the group)
-  const int row_g = mtile * kPrefixRows + t;
+  // ---- K and V chunk: thread t stages half a token row (64 head-dim elements) of token t / 2
+  const int tr = t >> 1, dh = t & 1;
+  uint4 kin[4], vin[4];
+  {
+    const int tok = tok_lo + tr;
+    const bool live = tok < tok_hi;
+    int64_t phys = 0;
+    if (live) phys = page_of(p.block_table, p.bt_stride_b, 0, tok / kPage);
+    const uint8_t* krow = p.key_cache + phys * p.k_stride_page + (int64_t)(tok % kPage) * p.k_stride_token + (int64_t)kvh * p.k_stride_head;
+    const uint8_t* vrow = p.value_cache + phys * p.v_stride_page + (int64_t)(tok % kPage) * p.v_stride_token + (int64_t)kvh * p.v_stride_head;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      kin[c] = vin[c] = make_uint4(0u, 0u, 0u, 0u);
+      if (live) {
+        kin[c] = __ldg(reinterpret_cast<const uint4*>(krow) + 4 * dh + c);
+        vin[c] = __ldg(reinterpret_cast<const uint4*>(vrow) + 4 * dh + c);
+      }
+    }
+  }
+  // ---- Q tile: thread (row, cg) stages 32 of the row's 128 elements
+  const int row_g = mtile * kPrefixRows + row;
   const int b = row_g / p.group, head = row_g % p.group;
   const bool row_live = b < pp.batch;
   {
     const uint16_t* q = reinterpret_cast<const uint16_t*>(p.query) + (int64_t)(row_live ? b : 0) * p.q_stride_b +
                         (int64_t)(kvh * p.group + head) * p.q_stride_h;
 #pragma unroll
-    for (int c = 0; c < 16; ++c) {
+    for (int cc = 0; cc < 4; ++cc) {
+      const int c = 4 * cg + cc;
       uint4 x = make_uint4(0u, 0u, 0u, 0u);
       if (row_live) x = __ldg(reinterpret_cast<const uint4*>(q) + c);
       if constexpr (QBF16) {
@@ -163,46 +223,28 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
           w[e] = pack_f16x2(__bfloat162float(v.x), __bfloat162float(v.y));
         }
       }
-      sts_16(sq + (c >> 3) * (kPrefixRows * 128) + sw128_chunk(t, c & 7), x);
+      sts_16(sq + (c >> 3) * (kPrefixRows * 128) + sw128_chunk(row, c & 7), x);
     }
   }
-  // ---- K and V chunk: thread t stages tokens t and t + 128 of the chunk
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int tr = t + 128 * half;            // token row inside the chunk
-    const int tok = tok_lo + tr;
-    const bool live = tok < tok_hi;
-    const uint8_t* krow = nullptr;
-    const uint8_t* vrow = nullptr;
-    if (live) {
-      const int64_t phys = page_of(p.block_table, p.bt_stride_b, 0, tok / kPage);
-      krow = p.key_cache + phys * p.k_stride_page + (int64_t)(tok % kPage) * p.k_stride_token + (int64_t)kvh * p.k_stride_head;
-      vrow = p.value_cache + phys * p.v_stride_page + (int64_t)(tok % kPage) * p.v_stride_token + (int64_t)kvh * p.v_stride_head;
-    }
+  for (int cc = 0; cc < 4; ++cc) {  // 16 bytes = 16 head-dim elements at a time
+    const int c = 4 * dh + cc;
+    uint4 lo, hi;
+    cvt16_e4m3_f16(kin[cc], lo, hi);
+    // K: row = token, k = d; elements 16c .. 16c+15 are chunks 2c, 2c+1 of k-block (c / 4)
+    const uint32_t kb = sk + (c >> 2) * (kPrefixChunk * 128);
+    sts_16(kb + sw128_chunk(tr, (2 * c) & 7), lo);
+    sts_16(kb + sw128_chunk(tr, (2 * c + 1) & 7), hi);
+    // V^T: row = d, k = token; token tr is element (tr % 64) of k-block (tr / 64)
+    cvt16_e4m3_f16(vin[cc], lo, hi);
+    const uint32_t vb = sv + (tr >> 6) * (D * 128);
+    const int kk = tr & 63;
+    const uint32_t* w = reinterpret_cast<const uint32_t*>(&lo);
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {  // 16 bytes = 16 head-dim elements at a time
-      uint4 kin = make_uint4(0u, 0u, 0u, 0u), vin = make_uint4(0u, 0u, 0u, 0u);
-      if (live) {
-        kin = ldg_nc_16(krow + 16 * c);
-        vin = ldg_nc_16(vrow + 16 * c);
-      }
-      uint4 lo, hi;
-      cvt16_e4m3_f16(kin, lo, hi);
-      // K: row = token, k = d; elements 16c .. 16c+15 are chunks 2c, 2c+1 of k-block (c / 4)
-      const uint32_t kb = sk + (c >> 2) * (kPrefixChunk * 128);
-      sts_16(kb + sw128_chunk(tr, (2 * c) & 7), lo);
-      sts_16(kb + sw128_chunk(tr, (2 * c + 1) & 7), hi);
-      // V^T: row = d, k = token; token tr is element (tr % 64) of k-block (tr / 64)
-      cvt16_e4m3_f16(vin, lo, hi);
-      const uint32_t vb = sv + (tr >> 6) * (D * 128);
-      const int kk = tr & 63;
-      const uint32_t* w = reinterpret_cast<const uint32_t*>(&lo);
-#pragma unroll
-      for (int e = 0; e < 16; ++e) {
-        const int d = 16 * c + e;
-        const uint32_t word = (e < 8) ? w[e >> 1] : reinterpret_cast<const uint32_t*>(&hi)[(e - 8) >> 1];
-        sts_u16(vb + sw128_chunk(d, kk >> 3) + (kk & 7) * 2, (e & 1) ? (word >> 16) : word);
-      }
+    for (int e = 0; e < 16; ++e) {
+      const int d = 16 * c + e;
+      const uint32_t word = (e < 8) ? w[e >> 1] : reinterpret_cast<const uint32_t*>(&hi)[(e - 8) >> 1];
+      sts_u16(vb + sw128_chunk(d, kk >> 3) + (kk & 7) * 2, (e & 1) ? (word >> 16) : word);
     }
   }
   // generic-proxy writes -> visible to the tensor core's (async proxy) reads
@@ -211,6 +253,7 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tslot_ptr;
+  prefix_mark(pp, 1);  // operands staged
 
   // ---- S = Q K^T : M 128, N 256, K 128 = 2 k-blocks x 4 slices of 16
   if (t == 0) {
@@ -225,48 +268,54 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   }
   bool ok = mbar_wait_bounded(bars, 0);
   tc_fence_after_sync();
+  prefix_mark(pp, 2);  // S ready
 
-  // ---- softmax of this thread's row over the chunk's 256 scores
+  // ---- softmax: thread (row, cg) holds the row's scores of tokens [64 cg, 64 cg + 64)
   const float ks = p.k_scale_ph ? __ldg(p.k_scale_ph + kvh) : p.k_scale;
   const float vs = p.v_scale_ph ? __ldg(p.v_scale_ph + kvh) : p.v_scale;
   const float scale_log2 = ks * p.sm_scale * kLog2e;
-  const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);  // this warp's 32 TMEM lanes
+  const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);  // this warp's 32 TMEM lanes
   const int n_live = tok_hi - tok_lo;
+  float sc[64];
+  {
+    uint32_t r0[32], r1[32];
+    tmem_ld32_nowait(lane_addr + 64 * cg, r0);
+    tmem_ld32_nowait(lane_addr + 64 * cg + 32, r1);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int e = 0; e < 32; ++e) { sc[e] = __uint_as_float(r0[e]); sc[32 + e] = __uint_as_float(r1[e]); }
+  }
   float mx = -INFINITY;
-  for (int c = 0; c < kPrefixChunk / 32; ++c) {
-    float v[32];
-    tmem_ld32(lane_addr + 32 * c, v);
 #pragma unroll
-    for (int e = 0; e < 32; ++e)
-      if (32 * c + e < n_live) mx = fmaxf(mx, v[e]);
-  }
-  mx *= scale_log2;  // scale_log2 > 0: the maximum commutes with it
+  for (int e = 0; e < 64; ++e)
+    if (64 * cg + e < n_live) mx = fmaxf(mx, sc[e]);
+  red[cg * 128 + row] = mx;
+  __syncthreads();
+  mx = fmaxf(fmaxf(red[row], red[128 + row]), fmaxf(red[256 + row], red[384 + row])) * scale_log2;  // scale > 0
   float lsum = 0.f;
-  for (int c = 0; c < kPrefixChunk / 32; ++c) {
-    float v[32];
-    tmem_ld32(lane_addr + 32 * c, v);
 #pragma unroll
-    for (int e8 = 0; e8 < 4; ++e8) {
-      uint4 out;
-      uint32_t* w = reinterpret_cast<uint32_t*>(&out);
+  for (int e8 = 0; e8 < 8; ++e8) {
+    uint4 out;
+    uint32_t* w = reinterpret_cast<uint32_t*>(&out);
 #pragma unroll
-      for (int e = 0; e < 8; e += 2) {
-        const int i0 = 8 * e8 + e;
-        const float p0 = (32 * c + i0 < n_live) ? exp2f(v[i0] * scale_log2 - mx) : 0.f;
-        const float p1 = (32 * c + i0 + 1 < n_live) ? exp2f(v[i0 + 1] * scale_log2 - mx) : 0.f;
-        lsum += p0 + p1;
-        w[e >> 1] = pack_f16x2(p0, p1);
-      }
-      // P: row = t, k = token 32c + 8*e8 ..: chunk ((32c + 8 e8) % 64) / 8 of k-block (32c / 64)
-      const int tokc = 32 * c + 8 * e8;
-      sts_16(sk + (tokc >> 6) * (kPrefixRows * 128) + sw128_chunk(t, (tokc & 63) >> 3), out);
+    for (int e = 0; e < 8; e += 2) {
+      const int i0 = 8 * e8 + e;
+      const float p0 = (64 * cg + i0 < n_live) ? exp2f(sc[i0] * scale_log2 - mx) : 0.f;
+      const float p1 = (64 * cg + i0 + 1 < n_live) ? exp2f(sc[i0 + 1] * scale_log2 - mx) : 0.f;
+      lsum += p0 + p1;
+      w[e >> 1] = pack_f16x2(p0, p1);
     }
+    // P: row = row, k = token 64 cg + 8 e8 ..: chunk e8 of k-block cg
+    sts_16(sk + cg * (kPrefixRows * 128) + sw128_chunk(row, e8), out);
   }
+  red[512 + cg * 128 + row] = lsum;
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
+  lsum = red[512 + row] + red[640 + row] + red[768 + row] + red[896 + row];
 
+  prefix_mark(pp, 3);  // P written
   // ---- O = P V : M 128, N 128, K 256 = 4 k-blocks x 4 slices
   if (t == 0) {
     const uint32_t idesc = umma_idesc_f16(128, 128);
@@ -280,28 +329,38 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   }
   ok = mbar_wait_bounded(bars + 8, 0) && ok;
   tc_fence_after_sync();
+  prefix_mark(pp, 4);  // O ready
 
-  // ---- (o, m, l) of this row into slot `chunk` of the workspace (every lane takes part in the
-  // aligned TMEM loads; only live rows store)
+  // ---- (o, m, l) of the rows into slot `chunk` of the workspace.  Thread (row, cg) parks
+  // columns [32 cg, +32) of its row in shared memory (16-byte chunks XOR-swizzled by the row);
+  // then every warp writes whole rows, 32 lanes x 16 bytes = one contiguous 512-byte row per store.
   {
-    const int hq = kvh * p.group + head;
-    const int64_t pidx = (int64_t)(row_live ? b : 0) * p.partial_stride_b + (int64_t)hq * p.partial_stride_h +
-                         (int64_t)chunk * p.partial_stride_s;
-    float* dst = reinterpret_cast<float*>(p.partial_output) + pidx * D;
-    for (int c = 0; c < D / 32; ++c) {
-      float v[32];
-      tmem_ld32(lane_addr + 256 + 32 * c, v);
-      if (row_live) {
+    float v[32];
+    tmem_ld32(lane_addr + 256 + 32 * cg, v);
 #pragma unroll
-        for (int e = 0; e < 32; e += 4)
-          *reinterpret_cast<float4*>(dst + 32 * c + e) = make_float4(v[e] * vs, v[e + 1] * vs, v[e + 2] * vs, v[e + 3] * vs);
-      }
-    }
-    if (row_live) {
+    for (int c = 0; c < 8; ++c)
+      sts_16(sk + row * 512 + (((8 * cg + c) ^ (row & 31)) << 4),
+             make_uint4(__float_as_uint(v[4 * c] * vs), __float_as_uint(v[4 * c + 1] * vs),
+                        __float_as_uint(v[4 * c + 2] * vs), __float_as_uint(v[4 * c + 3] * vs)));
+    if (row_live && cg == 0) {
+      const int64_t pidx = (int64_t)b * p.partial_stride_b + (int64_t)(kvh * p.group + head) * p.partial_stride_h +
+                           (int64_t)chunk * p.partial_stride_s;
       p.partial_max[pidx] = mx * kLn2;
       p.partial_sum[pidx] = lsum;
     }
+    __syncthreads();
+    for (int r = 0; r < 8; ++r) {
+      const int orow = warp * 8 + r;
+      const int rg = mtile * kPrefixRows + orow;
+      const int rb = rg / p.group, rh = rg % p.group;
+      if (rb >= pp.batch) break;
+      const uint4 x = lds_16(sk + orow * 512 + ((lane ^ (orow & 31)) << 4));
+      const int64_t pidx = (int64_t)rb * p.partial_stride_b + (int64_t)(kvh * p.group + rh) * p.partial_stride_h +
+                           (int64_t)chunk * p.partial_stride_s;
+      reinterpret_cast<uint4*>(reinterpret_cast<float*>(p.partial_output) + pidx * D)[lane] = x;
+    }
   }
+  prefix_mark(pp, 5);  // stored
   if (!ok && t == 0) atomicExch(pp.status, kErrUmmaTimeout);
   tc_fence_before_sync();
   __syncthreads();
