@@ -10,8 +10,8 @@
 //   O[128 x 128] = P[128 x 256] V          tcgen05.mma, accumulator in TMEM columns 256..383
 //
 // K and V are e4m3 in HBM; the CTA converts its 256 tokens to f16 (exact) while staging them
-// into the 128-byte-swizzled K-major layout the MMA reads (V transposed on the way, so that
-// tokens are the contiguous K dimension of the second product).  A whole chunk is one softmax
+// as 128-byte-swizzled token rows: K is read as a K-major operand of the first product, V as an
+// MN-major operand of the second (head dim contiguous), so nothing is transposed.  A whole chunk is one softmax
 // tile, so there is no running maximum and nothing in TMEM is ever rescaled.  The CTA writes
 // (o, m, l) of its rows into slot `chunk` of the ordinary split-KV workspace; the suffix pass
 // (the generic kernel with kv_start = prefix length) fills the slots after them and the usual
@@ -53,11 +53,24 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t addr) {
   d |= (uint64_t)2 << 61;                      // layout type: 128-byte swizzle
   return d;
 }
-// Instruction descriptor of kind::f16: f16 x f16 -> f32, both operands K-major.
-__device__ __forceinline__ uint32_t umma_idesc_f16(int m, int n) {
+// Descriptor of an MN-major operand (the N index is contiguous in shared memory) in the canonical
+// 128-byte-swizzled layout: every K index is a 128-byte row of 64 consecutive N elements, 8 rows
+// per 1 KiB atom; atoms of consecutive K groups are 1 KiB apart (stride-dimension offset), blocks
+// of 64 N elements `n_block_bytes` apart (leading-dimension offset).
+__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t addr, uint32_t n_block_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr >> 4) & 0x3FFF);
+  d |= (uint64_t)((n_block_bytes >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor of kind::f16: f16 x f16 -> f32, A K-major, B K-major or MN-major.
+__device__ __forceinline__ uint32_t umma_idesc_f16(int m, int n, bool b_mn_major = false) {
   return (1u << 4)                 // accumulator format f32
          | (0u << 7) | (0u << 10)  // A and B are f16
-         | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+         | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                          uint32_t accumulate) {  // one thread
@@ -157,7 +170,7 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   constexpr int D = 128;
   constexpr uint32_t kQBytes = kPrefixRows * D * 2;         // 32 KiB: 2 k-blocks of [128][64]
   constexpr uint32_t kKBytes = kPrefixChunk * D * 2;        // 64 KiB: 2 k-blocks of [256][64]; later P: 4 x [128][64]; later O rows
-  constexpr uint32_t kVBytes = D * kPrefixChunk * 2;        // 64 KiB: 4 k-blocks of [128 d][64 tokens]
+  constexpr uint32_t kVBytes = D * kPrefixChunk * 2;        // 64 KiB: 2 d-blocks of [256 tokens][64]
   const int chunk = blockIdx.x, mtile = blockIdx.y, kvh = blockIdx.z;
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
   const int qd = warp & 3, cg = warp >> 2;  // TMEM lane quarter, column group
@@ -235,17 +248,12 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
     const uint32_t kb = sk + (c >> 2) * (kPrefixChunk * 128);
     sts_16(kb + sw128_chunk(tr, (2 * c) & 7), lo);
     sts_16(kb + sw128_chunk(tr, (2 * c + 1) & 7), hi);
-    // V^T: row = d, k = token; token tr is element (tr % 64) of k-block (tr / 64)
+    // V: the same token-major rows (two blocks of 64 head-dim elements); the second MMA reads
+    // them as an MN-major operand, so no transposition is needed
     cvt16_e4m3_f16(vin[cc], lo, hi);
-    const uint32_t vb = sv + (tr >> 6) * (D * 128);
-    const int kk = tr & 63;
-    const uint32_t* w = reinterpret_cast<const uint32_t*>(&lo);
-#pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      const int d = 16 * c + e;
-      const uint32_t word = (e < 8) ? w[e >> 1] : reinterpret_cast<const uint32_t*>(&hi)[(e - 8) >> 1];
-      sts_u16(vb + sw128_chunk(d, kk >> 3) + (kk & 7) * 2, (e & 1) ? (word >> 16) : word);
-    }
+    const uint32_t vb = sv + (c >> 2) * (kPrefixChunk * 128);
+    sts_16(vb + sw128_chunk(tr, (2 * c) & 7), lo);
+    sts_16(vb + sw128_chunk(tr, (2 * c + 1) & 7), hi);
   }
   // generic-proxy writes -> visible to the tensor core's (async proxy) reads
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -316,15 +324,14 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   lsum = red[512 + row] + red[640 + row] + red[768 + row] + red[896 + row];
 
   prefix_mark(pp, 3);  // P written
-  // ---- O = P V : M 128, N 128, K 256 = 4 k-blocks x 4 slices
+  // ---- O = P V : M 128, N 128, K 256 = 16 slices of 16 tokens.  A = P (K-major: 4 k-blocks of
+  // 64 tokens), B = V (MN-major: 16 tokens = two 1 KiB atoms, d blocks 32 KiB apart)
   if (t == 0) {
-    const uint32_t idesc = umma_idesc_f16(128, 128);
+    const uint32_t idesc = umma_idesc_f16(128, 128, true);
 #pragma unroll
-    for (int kb = 0; kb < 4; ++kb)
-#pragma unroll
-      for (int s = 0; s < 4; ++s)
-        umma_f16(tmem + 256, umma_desc_k_sw128(sk + kb * (kPrefixRows * 128) + 32 * s),
-                 umma_desc_k_sw128(sv + kb * (D * 128) + 32 * s), idesc, (kb | s) ? 1u : 0u);
+    for (int s = 0; s < 16; ++s)
+      umma_f16(tmem + 256, umma_desc_k_sw128(sk + (s >> 2) * (kPrefixRows * 128) + 32 * (s & 3)),
+               umma_desc_mn_sw128(sv + 2048 * s, kPrefixChunk * 128), idesc, s ? 1u : 0u);
     umma_commit(bars + 8);
   }
   ok = mbar_wait_bounded(bars + 8, 0) && ok;
