@@ -176,8 +176,10 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
     if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     configured[dev] = true;
   }
-  if (kp.slot_offset > 0) {
-    // behind the dense prefix pass: independent work, let it run beside that pass
+  {
+    // Programmatic dependent launch.  Behind the dense prefix pass: independent work, it runs
+    // beside that pass.  Otherwise: the CTAs may become resident while the preceding kernel of
+    // the stream drains; the kernel waits for that kernel's completion before its first access.
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(kWarps * 32);
@@ -190,8 +192,6 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
     cfg.numAttrs = 1;
     const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, kp, tp, mk, mv);
     if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "partial kernel (TMA) launch failed: %s", cudaGetErrorString(e));
-  } else {
-    kernel<<<grid, kWarps * 32, smem, stream>>>(kp, tp, mk, mv);
   }
   return check_launch("partial kernel (TMA)");
 }

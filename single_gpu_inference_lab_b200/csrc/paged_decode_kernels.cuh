@@ -572,6 +572,14 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   constexpr uint32_t kTileBytes = kPage * D;  // 2 KiB
   constexpr uint32_t kStageBytes = 4 * kTileBytes;
   pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_k)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_v)) : "memory");
+  }
+  // Launched as a programmatic dependent of whatever precedes it in the stream: the CTA may
+  // become resident while that kernel drains, but touches no memory before it has completed.
+  // (Behind the dense prefix pass the wait is at the end instead: the two passes are independent.)
+  if (p.slot_offset == 0) pdl_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
   const int lo = p.kv_start + split * p.split_size;
@@ -738,6 +746,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
 template <int D, bool QBF16>
 __global__ void __launch_bounds__(128)
 paged_decode_merge_kernel(const KernelParams p, int batch) {
+  pdl_launch_dependents();
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= batch * p.num_q_heads) return;
