@@ -61,7 +61,9 @@ def parse_args():
     p.add_argument("--workload", default=DEFAULT_WORKLOAD)
     p.add_argument("--split-size", type=int, default=0, help="0 = choose from the geometry")
     p.add_argument("--pools", type=int, default=0, help="distinct KV pools rotated through (0 = enough to exceed L2 x3)")
-    p.add_argument("--flags", type=int, default=0)
+    p.add_argument("--flags", type=int, default=32,
+                   help="PFD_FLAG_* bits of the timed calls; default PFD_FLAG_EARLY_METADATA: the block table "
+                        "and sequence lengths do not change between the timed layer-steps")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-shared-prefix", action="store_true",
                    help="shared-prefix-b64 only: use the ordinary decode path instead of the dense tcgen05 prefix pass")
@@ -388,7 +390,7 @@ def main() -> int:
         path = cabi.last_path()
         fused = ((not kv_range_mode) and per_step == 1) or shared_prefix  # no single dominant kernel to time apart
         kernel_name = {1: "paged_decode_fp8_partial_ldg_kernel", 2: "paged_decode_fp8_partial_tma_kernel",
-                       3: "paged_decode_fp8_balanced_kernel"}.get(path, "?")
+                       3: "paged_decode_fp8_chunk_kernel"}.get(path, "?")
         if shared_prefix:
             kernel_name = "shared_prefix_dense_kernel + paged_decode_fp8_partial_tma_kernel + paged_decode_merge_kernel"
         ms_kernel = timed_graph(step if fused else (lambda i: step(i, args.flags | cabi.PFD_FLAG_PARTIAL_ONLY)), args.steps)
@@ -425,6 +427,9 @@ def main() -> int:
             "config": {
                 "workload": args.workload, "batch_per_gpu": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
                 "page_size": 16, "split_size": split, "max_seq_len": w.max_seq_len, "path": cabi.PATH_NAMES.get(path, "?"),
+                "flags": args.flags,
+                "metadata": ("block_table and seq_lens are not rewritten between the timed layer-steps "
+                             "(PFD_FLAG_EARLY_METADATA)") if args.flags & cabi.PFD_FLAG_EARLY_METADATA else "no promise",
                 "kv_bytes_per_step_per_gpu": kv_bytes,
                 **({"shared_prefix_tokens": w.prefix_len,
                     "unique_kv_bytes_per_step": int(w.prefix_len + (w.seq_lens - w.prefix_len).sum().item()) * hkv * d * 2,
@@ -438,7 +443,7 @@ def main() -> int:
             "roofline": {
                 "bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4),
-                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, path)) if world == 1 and not args.split_size else None,
+                "traffic": None if (args.strong or kv_range_mode) else NCU_TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, path)),
                 "kernel": kernel_name, "us_per_launch": round(ms_kernel * 1e3, 3), "peak_source": peak_kind,
                 "algorithmic_bytes_per_launch": kv_bytes,
             },

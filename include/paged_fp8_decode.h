@@ -35,11 +35,16 @@ extern "C" {
 #define PFD_FLAG_NO_TMA 1u        /* stream K/V with plain 16-byte global loads instead of TMA */
 #define PFD_FLAG_NO_DIRECT_OUT 2u /* always go through the partial workspace + merge kernel    */
 #define PFD_FLAG_PARTIAL_ONLY 4u  /* launch the split-KV partial kernel only (kernel timing)   */
-#define PFD_FLAG_FIXED_SPLITS 8u  /* always use the fixed-split grid + merge kernel, even when
-                                     semaphores are given (partials then follow split_size)    */
-#define PFD_FLAG_BALANCED 16u     /* use the one-kernel balanced path (needs semaphores, head_dim
-                                     128, f32 partials, workspace_splits >= 2); split_size then
-                                     only sizes the workspace                                  */
+#define PFD_FLAG_FIXED_SPLITS 8u  /* always use the fixed-split grid + merge kernel             */
+#define PFD_FLAG_BALANCED 16u     /* use the balanced persistent kernel + its merge kernel when
+                                     the call qualifies (head_dim 128, at most 8 query heads per
+                                     kv head, dense f32 workspace of at least
+                                     pfd_balanced_workspace_rows() rows); split_size then only
+                                     sizes the workspace.  Otherwise the fixed-split grid runs. */
+#define PFD_FLAG_EARLY_METADATA 32u /* the caller vouches that the kernel preceding this call in
+                                     the stream does not write seq_lens or block_table (true for
+                                     every layer of a model step, whose metadata is built once):
+                                     the kernels may then read them while that kernel drains     */
 
 /*
  * Operands of one decode-attention layer-step.
@@ -112,11 +117,7 @@ typedef struct pfd_decode_args {
 
   void* stream; /* cudaStream_t */
 
-  /* Optional [batch * num_kv_heads] int32, all zero on entry and left all zero on return.
-   * With it and PFD_FLAG_BALANCED (and head_dim 128, f32 partials, workspace_splits >= 2) the
-   * step runs as ONE kernel: a persistent grid shares the KV bytes of all sequences in equal
-   * chunks and the CTA that retires the last piece of a (sequence, kv head) merges the pieces
-   * itself.  The partial workspace then holds those pieces, not split_size-sized splits. */
+  /* Unused (kept for layout compatibility): earlier builds counted retired pieces here. */
   int32_t* semaphores;
   int64_t num_semaphores;
 } pfd_decode_args;
@@ -128,6 +129,14 @@ typedef struct pfd_decode_args {
  * l20_paged_split_kv_attention_fp8 (integrations/vllm/l20_paged_split_kv.py:652-694).
  */
 int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args);
+
+/*
+ * Rows of (o, m, l) the workspace must hold for PFD_FLAG_BALANCED on the current device:
+ * batch * num_q_heads * workspace_splits >= this.  The balanced kernel gives every group of
+ * num_kv_heads warps two slots of num_q_heads rows.  Negative on error.  No counterpart in the
+ * reference, whose workspace is always [B, Hq, splits].
+ */
+int64_t pfd_balanced_workspace_rows(int32_t num_q_heads, int32_t num_kv_heads);
 
 /*
  * Allocation-free variant of pfd_paged_decode_fp8_e4m3_split_out.  It has no counterpart in

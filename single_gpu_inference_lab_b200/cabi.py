@@ -20,6 +20,7 @@ PFD_FLAG_NO_DIRECT_OUT = 2
 PFD_FLAG_PARTIAL_ONLY = 4
 PFD_FLAG_FIXED_SPLITS = 8
 PFD_FLAG_BALANCED = 16
+PFD_FLAG_EARLY_METADATA = 32
 
 EXPORTS = (
     "pfd_paged_decode_fp8_e4m3_split_out",
@@ -27,6 +28,7 @@ EXPORTS = (
     "pfd_shared_prefix_decode_fp8_e4m3",
     "pfd_merge_packed",
     "pfd_resolve_slots",
+    "pfd_balanced_workspace_rows",
     "pfd_device_status",
     "pfd_debug_phase_times",
     "pfd_last_path",
@@ -244,7 +246,18 @@ def device_status() -> int:
     return int(value.value)
 
 
-PATH_NAMES = {0: "none", 1: "fixed-split grid (plain loads) + merge", 2: "fixed-split grid (TMA) + merge", 3: "balanced persistent kernel"}
+PATH_NAMES = {0: "none", 1: "fixed-split grid (plain loads) + merge", 2: "fixed-split grid (TMA) + merge", 3: "balanced persistent kernel + merge"}
+
+
+def balanced_workspace_rows(num_q_heads: int, num_kv_heads: int) -> int:
+    """Rows ``B * Hq * splits`` the workspace needs for ``PFD_FLAG_BALANCED`` on the current device."""
+    lib = load()
+    lib.pfd_balanced_workspace_rows.argtypes = [C.c_int32, C.c_int32]
+    lib.pfd_balanced_workspace_rows.restype = C.c_int64
+    rows = int(lib.pfd_balanced_workspace_rows(num_q_heads, num_kv_heads))
+    if rows < 0:
+        raise RuntimeError(lib.pfd_last_error().decode())
+    return rows
 
 
 def last_path() -> int:

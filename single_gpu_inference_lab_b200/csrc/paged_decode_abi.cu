@@ -197,85 +197,113 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
 }
 
 // ---- balanced persistent kernel -------------------------------------------------------------
-constexpr int kBalStages = 2;
+constexpr int kChunkStages = 2;
+constexpr int kChunkWarps = 12;  // per CTA, one CTA per SM
+constexpr int kChunkMaxBatch = 2048;
+constexpr int kChunkPieceCost = 2;  // half page pairs charged for starting a sequence
 
-bool balanced_eligible(const pfd_decode_args& a) {
-  if (a.flags & (PFD_FLAG_FIXED_SPLITS | PFD_FLAG_PARTIAL_ONLY | PFD_FLAG_NO_DIRECT_OUT)) return false;
-  if (!tma_eligible(a)) return false;
-  if (a.semaphores == nullptr || a.num_semaphores < (int64_t)a.batch * a.num_kv_heads) return false;
-  if (!a.partial_output || !a.partial_max || !a.partial_sum || a.partial_dtype != PFD_DTYPE_F32) return false;
-  if (a.workspace_splits < 2 || a.batch > 8192) return false;
-  // Opt-in: measured on B200 the fixed-split grid with a well-chosen split size and the merge
-  // kernel chained by programmatic dependent launch is 5-15 % faster than the balanced kernel
-  // on all five reference workloads; the balanced kernel needs no tuning of split_size and
-  // beats a badly chosen one (e.g. the reference hook's constant 512 on many short sequences).
-  return (a.flags & PFD_FLAG_BALANCED) != 0;
+int sm_count_of(int dev, int* out) {
+  static int sm_count[kMaxDevices] = {0};
+  if (dev < 0 || dev >= kMaxDevices) return fail(PFD_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_state_mutex);
+  if (sm_count[dev] == 0) {
+    const cudaError_t e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaDeviceGetAttribute failed: %s", cudaGetErrorString(e));
+  }
+  *out = sm_count[dev];
+  return PFD_OK;
 }
 
-template <bool QBF16, int NH>
-int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, cudaStream_t stream) {
+// The balanced path treats the workspace as a flat array of (o, m, l) rows: two slots of
+// num_q_heads rows for each group of num_kv_heads warps.  It needs a dense f32 workspace of
+// that capacity; a call that does not qualify runs on the fixed-split grid instead.
+bool balanced_eligible(const pfd_decode_args& a, const pfd::KernelParams& kp, int sms) {
+  if (a.flags & (PFD_FLAG_FIXED_SPLITS | PFD_FLAG_NO_TMA | PFD_FLAG_NO_DIRECT_OUT)) return false;
+  if (kp.slot_offset != 0) return false;  // slots in front belong to the dense prefix pass
+  if (!tma_eligible(a) || kp.group > 8 || a.batch > kChunkMaxBatch) return false;
+  if (a.num_kv_heads > kChunkWarps * sms / 2) return false;  // one warp per kv head and group
+  if (!a.partial_output || !a.partial_max || !a.partial_sum || a.partial_dtype != PFD_DTYPE_F32) return false;
+  if (a.partial_stride_s != 1 || a.partial_stride_h != a.workspace_splits ||
+      a.partial_stride_b != (int64_t)a.num_q_heads * a.workspace_splits)
+    return false;
+  const int64_t rows = (int64_t)a.batch * a.num_q_heads * a.workspace_splits;
+  return rows >= 2LL * (sms * kChunkWarps / a.num_kv_heads) * a.num_q_heads;
+}
+
+template <bool QBF16>
+int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int sms, cudaStream_t stream) {
   CUtensorMap mk, mv;
   if (int rc = get_tensor_map(a.key_cache, a.k_stride_page, a.k_stride_token, a.k_stride_head, a.num_pages,
-                              a.num_kv_heads, 128, &mk))
+                              a.num_kv_heads, 256, &mk))
     return rc;
   if (int rc = get_tensor_map(a.value_cache, a.v_stride_page, a.v_stride_token, a.v_stride_head, a.num_pages,
-                              a.num_kv_heads, 128, &mv))
+                              a.num_kv_heads, 256, &mv))
     return rc;
   pfd::TmaParams tp{};
   tp.head_is_dim1 = head_is_dim1(a.k_stride_token, a.k_stride_head) ? 1 : 0;
   if (int rc = status_pointer(&tp.status)) return rc;
   tp.phase_times = g_phase_times;
-  auto kernel = pfd::paged_decode_fp8_balanced_kernel<QBF16, NH, kBalStages>;
-  constexpr int kThreads = (pfd::kComputeWarps + 1) * 32;
-  const int rows = 8 * NH;
-  const int smem = 1024 + kWarps * kBalStages * 8192 + kWarps * kBalStages * 8 + rows * 128 * 4 +
-                   2 * kWarps * rows * 4 + (8 + kWarps) * 4 + (2 * a.batch + 1) * 4 + 16;
+  auto kernel = pfd::paged_decode_fp8_chunk_kernel<QBF16, kChunkStages, kChunkWarps>;
+  constexpr int kThreads = kChunkWarps * 32;
+  // ring + mbarriers + scan scratch + prefix[B + 1] + lens[B], sized for the largest batch
+  constexpr int smem = 1024 + kChunkWarps * kChunkStages * 8192 + kChunkWarps * kChunkStages * 8 +
+                       kChunkWarps * 4 + (2 * kChunkMaxBatch + 1) * 4 + 16;
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev < 0 || dev >= kMaxDevices) return fail(PFD_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
-  // per device: SM count, and the largest dynamic shared memory size configured so far
-  static int sm_count[kMaxDevices] = {0};
-  static int smem_set[kMaxDevices][2][2] = {};
+  static bool configured[kMaxDevices][2] = {};
   {
     std::lock_guard<std::mutex> lock(g_state_mutex);
-    if (sm_count[dev] == 0) {
-      const cudaError_t e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-      if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaDeviceGetAttribute failed: %s", cudaGetErrorString(e));
-    }
-    int& have = smem_set[dev][QBF16 ? 1 : 0][NH - 1];
-    if (smem > have) {
+    if (!configured[dev][QBF16 ? 1 : 0]) {
       const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
-      have = smem;
+      configured[dev][QBF16 ? 1 : 0] = true;
     }
   }
-  int per_sm = 0;
+  pfd::ChunkParams cp{};
+  cp.batch = a.batch;
+  cp.num_warps = sms * kChunkWarps;
+  cp.piece_cost = kChunkPieceCost;
+  if (const char* env = getenv("PFD_PIECE_COST")) cp.piece_cost = std::max(0, std::min(atoi(env), 64));  // tuning aid
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
   {
-    const cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem);
-    if (e != cudaSuccess || per_sm < 1)
-      return fail(PFD_ERR_CUDA, "balanced kernel does not fit on an SM (%d bytes of shared memory)", smem);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(sms);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, kp, tp, cp, mk, mv);
+    if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "balanced decode kernel launch failed: %s", cudaGetErrorString(e));
+    if (int rc = check_launch("balanced decode kernel")) return rc;
   }
-  const int max_pages = (a.max_seq_len + pfd::kPage - 1) / pfd::kPage - a.kv_start / pfd::kPage;
-  const int max_pairs = (std::max(max_pages, 0) + 1) / 2;
-  pfd::BalancedParams bp{};
-  bp.batch = a.batch;
-  bp.workspace_splits = a.workspace_splits;
-  bp.min_chunk = std::max(1, (max_pairs + a.workspace_splits - 2) / (a.workspace_splits - 1));
-  bp.semaphores = a.semaphores;
-  // never more CTAs than the largest possible number of pairs
-  const int64_t pair_bound = (int64_t)max_pairs * a.batch * a.num_kv_heads;
-  int grid = sm_count[dev] * per_sm;
-  if (pair_bound < grid) grid = (int)std::max<int64_t>(pair_bound, 1);
-  kernel<<<grid, kThreads, smem, stream>>>(kp, tp, bp, mk, mv);
   g_last_path = PFD_PATH_BALANCED;
-  return check_launch("balanced decode kernel");
+  if (a.flags & PFD_FLAG_PARTIAL_ONLY) return PFD_OK;
+  {
+    const int rows = a.batch * a.num_q_heads;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3((rows + 3) / 4);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, pfd::paged_decode_chunk_merge_kernel<QBF16>, kp, tp, cp);
+    if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "balanced merge kernel launch failed: %s", cudaGetErrorString(e));
+  }
+  return check_launch("balanced merge kernel");
 }
 
 template <int D, bool QBF16>
 int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num_splits) {
   cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
-  if (D == 128 && balanced_eligible(a)) {
-    return kp.group <= 8 ? launch_balanced<QBF16, 1>(a, kp, stream) : launch_balanced<QBF16, 2>(a, kp, stream);
+  if (D == 128) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    if (int rc = sm_count_of(dev, &sms)) return rc;
+    if (balanced_eligible(a, kp, sms)) return launch_balanced<QBF16>(a, kp, sms, stream);
   }
   const dim3 grid(num_splits, a.num_kv_heads, a.batch);
   if (D == 128 && tma_eligible(a)) {
@@ -398,6 +426,9 @@ int decode_impl(const pfd_decode_args* args, int slot_offset) {
   kp.direct_out = direct_ok ? 1 : 0;
   kp.bt_cols = (a.max_seq_len + pfd::kPage - 1) / pfd::kPage;  // rows are at least this wide
   kp.slot_offset = slot_offset;
+  kp.early_metadata = (a.flags & PFD_FLAG_EARLY_METADATA) ? 1 : 0;
+  kp.kv_evict_first = 1;
+  if (const char* env = getenv("PFD_KV_EVICT_FIRST")) kp.kv_evict_first = atoi(env) != 0;  // tuning aid
 
   const bool bf16 = a.query_dtype == PFD_DTYPE_BF16;
   if (a.head_dim == 128)
@@ -551,10 +582,20 @@ int pfd_paged_decode_fp8_e4m3_split_out_noalloc(const pfd_decode_args* args) {
   a.partial_stride_b = (int64_t)a.num_q_heads * splits;
   a.partial_stride_h = splits;
   a.partial_stride_s = 1;
+  a.flags |= PFD_FLAG_FIXED_SPLITS;  // the array is sized for split_size-sized splits
   return pfd_paged_decode_fp8_e4m3_split_out(&a);
 }
 
 int pfd_last_path(void) { return g_last_path; }
+
+int64_t pfd_balanced_workspace_rows(int32_t num_q_heads, int32_t num_kv_heads) {
+  if (num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads)
+    return fail(PFD_ERR_INVALID, "Q heads must be divisible by KV heads");
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaGetDevice failed");
+  if (int rc = sm_count_of(dev, &sms)) return rc;
+  return 2LL * (sms * kChunkWarps / num_kv_heads) * num_q_heads;
+}
 
 int pfd_debug_phase_times(void* device_buffer) {
   g_phase_times = static_cast<unsigned long long*>(device_buffer);

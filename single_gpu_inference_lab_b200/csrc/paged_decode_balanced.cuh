@@ -1,17 +1,19 @@
 // Balanced, persistent form of the split-KV decode step for head_dim 128 (sm_100a).
 //
-// Instead of a grid of fixed (sequence, kv head, split) work items, a fixed number of CTAs
-// (a multiple of the SM count) share the flattened list of page pairs of all (sequence,
-// kv head) segments in equal contiguous chunks, so every CTA streams the same number of KV
-// bytes whatever the mix of context lengths.  A CTA walks the segments its chunk overlaps;
-// its four compute warps take the chunk's page pairs round-robin, each through a private TMA
-// ring that keeps loading across segment boundaries, and reduce their (m, l, O) for a segment
-// in shared memory.  A fifth warp retires segments: it turns the reduced sums into the final
-// output, or -- for a segment that straddles chunks -- into an (o, m, l) piece in the caller's
-// workspace, and the CTA that retires the last piece (a per-segment semaphore) merges them.
-// The compute warps never wait for a global-memory round trip at a segment boundary, and
-// there is no second kernel launch.  Whole segments of at most kSoloPairs page pairs skip the
-// CTA-level reduction altogether: one warp streams them and writes their output itself.
+// Instead of a grid of fixed (sequence, kv head, split) work items, a fixed number of warps
+// (twelve per SM) share the flattened list of page pairs of all sequences: the warps form
+// groups of one warp per kv head, and every group takes an equal contiguous chunk of the list,
+// so every warp streams the same number of KV bytes whatever the mix of context lengths, and
+// no CTA is launched for a split that does not exist.  The warps of a group read the same pages
+// at about the same time, each its own head, which keeps the rows of a page that lie next to
+// each other in memory (token-major layout) in one burst of DRAM traffic.  A warp walks the
+// sequences its chunk overlaps on its own: no barrier, no shared accumulator, one private TMA
+// ring that keeps loading across sequence boundaries.  A sequence that lies inside one chunk
+// is finished by that warp (final output rows, or the packed (o, m, l) form); the piece of a
+// sequence that straddles chunks goes to the caller's workspace as (o, m, l), into one of the
+// two slots every group owns, and the merge kernel behind (programmatic dependent launch)
+// combines the pieces.  Both kernels derive the chunking from seq_lens alone, so nothing but
+// the pieces themselves passes between them.
 //
 // Maths per page pair and warp, "heads as columns": S^T = K Q^T and O^T += V^T P^T with
 // mma.sync.m16n8k16 (f16 in, f32 accumulate).  Tokens (resp. head-dim rows) fill the 16-row M
@@ -24,14 +26,43 @@
 
 namespace pfd {
 
-struct BalancedParams {
+struct ChunkParams {
   int32_t batch;
-  int32_t min_chunk;        // lower bound on pairs per CTA so that pieces fit the workspace
-  int32_t workspace_splits; // capacity of the workspace's split axis
-  int32_t* semaphores;      // [batch * num_kv_heads], zero between calls
+  int32_t num_warps;   // warps of the whole grid; the merge kernel is told the same number
+  int32_t piece_cost;  // what starting a sequence costs a warp, in half page pairs
 };
 
-constexpr int kErrWorkspace = 2;
+// How the work is cut.  Cost is counted in half page pairs: sequence b owns the cost range that
+// starts at 2 * (pairs before b) + piece_cost * b, first piece_cost units for taking the
+// sequence up (query fetch, state reset, output rows), then two units per page pair.  The cost
+// axis is cut into `groups` contiguous chunks whose lengths differ by at most one unit, and a
+// page pair belongs to the chunk that holds its first unit.  Tiny workloads use fewer groups so
+// that no chunk is shorter than kMinChunkCost units (a chunk inside a sequence is never empty).
+constexpr int kMinChunkCost = 8;
+struct Chunking {
+  int base, rem, groups, piece_cost;
+  __device__ __forceinline__ Chunking(int total_pairs, int batch, int max_groups, int cost) : piece_cost(cost) {
+    const int total = 2 * total_pairs + cost * batch;
+    groups = max(min(max_groups, total / kMinChunkCost), 1);
+    base = total / groups;
+    rem = total - base * groups;
+  }
+  __device__ __forceinline__ int start_of(int c) const { return c * base + min(c, rem); }
+  __device__ __forceinline__ int chunk_of(int unit) const {
+    const int wide = rem * (base + 1);
+    return unit < wide ? unit / (base + 1) : rem + (unit - wide) / max(base, 1);
+  }
+  // first cost unit of pair 0 of sequence b, given the pairs before b
+  __device__ __forceinline__ int first_unit(int pairs_before, int b) const {
+    return 2 * pairs_before + piece_cost * (b + 1);
+  }
+};
+
+// Page pairs of a sequence of `len` tokens when attention starts at page `page_first`.
+__device__ __forceinline__ int pairs_of(int len, int page_first) {
+  const int pages = len > page_first * kPage ? (len + kPage - 1) / kPage - page_first : 0;
+  return (pages + 1) >> 1;
+}
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
   uint32_t d;
@@ -213,96 +244,6 @@ __device__ __forceinline__ void bal_step(BalState<NH>& st, uint32_t stage, const
   }
 }
 
-// Segment cursor over the flattened pair list (uniform across a warp).
-struct SegCursor {
-  int b, kvh;  // current segment
-  int np;      // page pairs in it
-  int start;   // global pair index of its first pair
-};
-
-// Advance `c` until its segment contains global pair `gp` (gp < total is the caller's duty).
-__device__ __forceinline__ void seg_seek(SegCursor& c, int gp, const int32_t* prefix, int hkv) {
-  while (gp >= c.start + c.np) {
-    c.start += c.np;
-    if (++c.kvh == hkv) {
-      c.kvh = 0;
-      ++c.b;
-      c.np = prefix[c.b + 1] - prefix[c.b];
-    }
-  }
-}
-
-// The part of one segment that lies inside a CTA's chunk [P0, P1).
-struct Piece {
-  int b, kvh;
-  int seg_start, np;  // the whole segment
-  int a, e;           // global pair range of the piece
-  int owner;          // >= 0: a small whole segment handled by that compute warp alone ("solo")
-  __device__ __forceinline__ bool solo() const { return owner >= 0; }
-};
-
-constexpr int kSoloPairsMin = 4;
-constexpr int kComputeWarps = 4;
-constexpr int kBarMax = 1, kBarReady = 2, kBarFree = 3;  // named barriers (0 is __syncthreads)
-
-// Walks the pieces of a chunk in order.  Every walker (each compute warp's producer and
-// consumer side, and the retiring warp) sees the same pieces with the same owners: a solo piece
-// goes to the compute warp with the least work assigned so far.
-struct PieceWalker {
-  SegCursor c;
-  int P0, P1, solo_max;
-  int load[kComputeWarps];  // pairs assigned to each compute warp so far
-
-  __device__ __forceinline__ void init(const SegCursor& first, int p0, int p1, int chunk) {
-    c = first; P0 = p0; P1 = p1;
-    solo_max = max(kSoloPairsMin, chunk >> 3);
-#pragma unroll
-    for (int w = 0; w < kComputeWarps; ++w) load[w] = 0;
-  }
-  // The piece that contains global pair g (P0 <= g < P1); call with increasing g only.
-  __device__ __forceinline__ Piece at(int g, const int32_t* prefix, int hkv) {
-    seg_seek(c, g, prefix, hkv);
-    Piece q;
-    q.b = c.b; q.kvh = c.kvh; q.seg_start = c.start; q.np = c.np;
-    q.a = max(c.start, P0);
-    q.e = min(c.start + c.np, P1);
-    q.owner = -1;
-    const int len = q.e - q.a;
-    if (q.a == c.start && q.e == c.start + c.np && c.np <= solo_max) {
-      int best = 0, least = load[0];
-#pragma unroll
-      for (int w = 1; w < kComputeWarps; ++w)
-        if (load[w] < least) { least = load[w]; best = w; }
-      q.owner = best;
-#pragma unroll
-      for (int w = 0; w < kComputeWarps; ++w)
-        if (w == best) load[w] += len;
-    } else {
-#pragma unroll
-      for (int w = 0; w < kComputeWarps; ++w) load[w] += (len - w + kComputeWarps - 1) / kComputeWarps;
-    }
-    return q;
-  }
-};
-
-// First pair of compute warp `warp` in piece `q` (>= q.e if it has none) and its stride.
-__device__ __forceinline__ int piece_first(const Piece& q, int warp) {
-  if (q.solo()) return q.owner == warp ? q.a : q.e;
-  return q.a + warp;
-}
-__device__ __forceinline__ int piece_stride(const Piece& q) { return q.solo() ? 1 : kComputeWarps; }
-
-__device__ __forceinline__ void named_sync(int id, int count) {
-  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-__device__ __forceinline__ void named_arrive(int id, int count) {
-  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-
-// The accumulation buffer is [rows][32 float4]; float4 f of row `row` lives at f ^ ((row & 7) >> 1),
-// which makes the compute warps' float4 read-modify-writes bank-conflict free.
-__device__ __forceinline__ int acc_f4(int row, int f) { return row * 32 + (f ^ ((row & 7) >> 1)); }
-
 template <bool QBF16>
 __device__ __forceinline__ void store_row16(const KernelParams& p, int b, int hq, int d0, const float (&v)[16],
                                             float m_nat, float l, bool write_ml) {
@@ -332,43 +273,55 @@ __device__ __forceinline__ void store_row16(const KernelParams& p, int b, int hq
   }
 }
 
-// grid = persistent CTAs (a multiple of the SM count); block = 4 compute warps + 1 retiring warp.
-template <bool QBF16, int NH, int NSTAGE>
-__global__ void __launch_bounds__(160, (NH == 1 ? 3 : 1))
-paged_decode_fp8_balanced_kernel(const KernelParams p, const TmaParams tp, const BalancedParams bp,
-                                 const __grid_constant__ CUtensorMap tmap_k,
-                                 const __grid_constant__ CUtensorMap tmap_v) {
+// Workspace row of query head `hq` in slot `which` of warp group `grp` (0: the piece that begins
+// the chunk, 1: the piece that ends it).  The workspace is used as a flat array of (o[D], m, l) rows.
+__device__ __forceinline__ int64_t chunk_slot_row(int grp, int which, int num_q_heads, int hq) {
+  return ((int64_t)(2 * grp + which)) * num_q_heads + hq;
+}
+
+// grid = one CTA per SM; block = NWARPS independent warps.
+template <bool QBF16, int NSTAGE, int NWARPS>
+__global__ void __launch_bounds__(NWARPS * 32, 1)
+paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const ChunkParams cp,
+                              const __grid_constant__ CUtensorMap tmap_k,
+                              const __grid_constant__ CUtensorMap tmap_v) {
   constexpr int D = 128;
-  constexpr int NC = kComputeWarps;
-  constexpr int NT = (NC + 1) * 32;
+  constexpr int NT = NWARPS * 32;
   constexpr uint32_t kTile = kPage * D;
   constexpr uint32_t kStage = 4 * kTile;
-  constexpr int ROWS = 8 * NH;  // head rows of the accumulation buffer
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_k)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_v)) : "memory");
+  }
+  // A programmatic dependent of whatever precedes it in the stream (normally the previous
+  // layer-step's merge kernel, which still reads the workspace): no memory access before that
+  // kernel has completed -- except, if the caller vouches that the preceding kernel does not
+  // write them, the reads of seq_lens and block_table.
+  if (!p.early_metadata) pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
-  const int B = bp.batch, hkv = p.num_kv_heads;
+  const int B = cp.batch, hkv = p.num_kv_heads;
   const int page_first = p.kv_start / kPage;
+  const int W = (int)blockIdx.x * NWARPS + warp;
+  const int grp = W / hkv, kvh = W - grp * hkv;  // one warp per kv head and group
+  const int num_groups = cp.num_warps / hkv;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* base = smem_raw + (ring - smem_u32(smem_raw));
-  uint8_t* after = base + NC * NSTAGE * kStage;
-  const uint32_t bars = ring + NC * NSTAGE * kStage;
-  float* sm_acc = reinterpret_cast<float*>(after + NC * NSTAGE * 8);  // [ROWS][D], swizzled, zero when free
-  float* sm_m = sm_acc + ROWS * D;                                   // [NC][ROWS]
-  float* sm_l = sm_m + NC * ROWS;                                    // [NC][ROWS]
-  int32_t* sm_misc = reinterpret_cast<int32_t*>(sm_l + NC * ROWS);   // [1 .. NC+1] scan scratch
-  int32_t* prefix = sm_misc + 8 + NC;                                // [B + 1] pairs before sequence b
-  int32_t* lens = prefix + (B + 1);                                  // [B]
+  const uint32_t bars = ring + NWARPS * NSTAGE * kStage;
+  int32_t* sm_scan = reinterpret_cast<int32_t*>(base + NWARPS * NSTAGE * kStage + NWARPS * NSTAGE * 8);  // [NWARPS]
+  int32_t* prefix = sm_scan + NWARPS;  // [B + 1] pairs before sequence b
+  int32_t* lens = prefix + (B + 1);    // [B]
 
-  mark_phase(tp, 0);  // start
-  const uint32_t my_ring = ring + warp * NSTAGE * kStage;  // compute warps only
+  mark_phase_at(tp, W, 0, lane == 0);  // start
+  const uint32_t my_ring = ring + warp * NSTAGE * kStage;
   const uint32_t my_bars = bars + warp * NSTAGE * 8;
-  if (warp < NC && lane == 0) {
+  if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < NSTAGE; ++s) mbar_init(my_bars + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int e = threadIdx.x; e < ROWS * D / 4; e += NT) reinterpret_cast<float4*>(sm_acc)[e] = make_float4(0.f, 0.f, 0.f, 0.f);
 
   // ---- pairs per sequence and their exclusive prefix sum (every CTA computes the same)
   {
@@ -380,8 +333,7 @@ paged_decode_fp8_balanced_kernel(const KernelParams p, const TmaParams tp, const
       if (b < B) {
         const int len = p.seq_lens[b];
         lens[b] = len;
-        const int pages = len > page_first * kPage ? (len + kPage - 1) / kPage - page_first : 0;
-        local += (pages + 1) >> 1;
+        local += pairs_of(len, page_first);
       }
     }
     int incl = local;  // inclusive scan over the CTA's threads
@@ -390,269 +342,102 @@ paged_decode_fp8_balanced_kernel(const KernelParams p, const TmaParams tp, const
       const int x = __shfl_up_sync(0xffffffffu, incl, off);
       if (lane >= off) incl += x;
     }
-    if (lane == 31) sm_misc[1 + warp] = incl;
+    if (lane == 31) sm_scan[warp] = incl;
     __syncthreads();
     int before = 0;
-    for (int w = 0; w < warp; ++w) before += sm_misc[1 + w];
+    for (int w = 0; w < warp; ++w) before += sm_scan[w];
     int run = before + incl - local;
     for (int q = 0; q < per; ++q) {
       const int b = b0 + q;
       if (b < B) {
         prefix[b] = run;
-        const int len = lens[b];
-        const int pages = len > page_first * kPage ? (len + kPage - 1) / kPage - page_first : 0;
-        run += (pages + 1) >> 1;
+        run += pairs_of(lens[b], page_first);
       }
     }
     if (threadIdx.x == NT - 1) prefix[B] = before + incl;
-    __syncthreads();
+    __syncthreads();  // the last CTA-wide barrier: from here on the warps are on their own
   }
-  // Sequences with nothing to attend (seq_len <= kv_start) belong to no chunk: their rows are
-  // filled here, zeros or (0, -inf, 0) in packed form, spread over all CTAs.
-  for (int row = blockIdx.x * NT + threadIdx.x; row < B * p.num_q_heads; row += gridDim.x * NT) {
-    const int b = row / p.num_q_heads, hq = row % p.num_q_heads;
-    if (lens[b] > p.kv_start) continue;
-    if (p.packed_output != nullptr) {
-      float* dst = p.packed_output + (int64_t)row * (D + 2);
-      for (int d = 0; d < D; ++d) dst[d] = 0.f;
-      dst[D] = -INFINITY;
-      dst[D + 1] = 0.f;
-    } else {
-      uint16_t* dst = reinterpret_cast<uint16_t*>(p.output) + (int64_t)b * p.o_stride_b + (int64_t)hq * p.o_stride_h;
-      for (int d = 0; d < D; ++d) dst[d] = 0;
-    }
-  }
-  mark_phase(tp, 1);  // scan done
-  const int total = prefix[B] * hkv;
-  int chunk = (total + (int)gridDim.x - 1) / (int)gridDim.x;
-  chunk = max(chunk, bp.min_chunk);
-  const int P0 = min((int)blockIdx.x * chunk, total);
-  const int P1 = min(P0 + chunk, total);
-  if (P0 >= P1) return;
-
-  // ---- first segment of the chunk: largest b with hkv * prefix[b] <= P0, then the kv head
-  SegCursor first;
-  {
-    int lo_b = 0, hi_b = B;  // prefix[lo_b]*hkv <= P0 < prefix[hi_b]*hkv
+  mark_phase_at(tp, W, 1, lane == 0);  // scan done
+  const int total = prefix[B];
+  const Chunking chunks(total, B, max(num_groups, 1), cp.piece_cost);
+  // Pairs whose first cost unit lies before cost position c.
+  auto pairs_before = [&](int c) {
+    if (c >= 2 * total + chunks.piece_cost * B) return total;
+    int lo_b = 0, hi_b = B;  // largest b whose cost range starts at or before c
     while (hi_b - lo_b > 1) {
       const int mid = (lo_b + hi_b) >> 1;
-      if (prefix[mid] * hkv <= P0) lo_b = mid; else hi_b = mid;
+      if (2 * prefix[mid] + chunks.piece_cost * mid <= c) lo_b = mid; else hi_b = mid;
     }
-    first.b = lo_b;
-    first.np = prefix[lo_b + 1] - prefix[lo_b];
-    first.kvh = (P0 - prefix[lo_b] * hkv) / first.np;
-    first.start = prefix[lo_b] * hkv + first.kvh * first.np;
-  }
-
-  if (warp == NC) {
-    // ================= retiring warp =================
-    // lane -> rows (8h + lane % 8), columns [32 * (lane / 8), +32)
-    const int rr = lane & 7, d0 = 32 * (lane >> 3);
-    int n_total = 0;
-    {
-      PieceWalker w;
-      w.init(first, P0, P1, chunk);
-      for (int g = P0; g < P1;) {
-        const Piece q = w.at(g, prefix, hkv);
-        n_total += q.solo() ? 0 : 1;
-        g = q.e;
-      }
-    }
-    PieceWalker walk;
-    walk.init(first, P0, P1, chunk);
-    int n = 0;
-    for (int g = P0; g < P1;) {
-      const Piece q = walk.at(g, prefix, hkv);
-      g = q.e;
-      if (q.solo()) continue;
-      if (n == n_total - 1) break;  // the chunk's last shared piece is retired by the compute warps
-      const float vs = p.v_scale_ph ? __ldg(p.v_scale_ph + q.kvh) : p.v_scale;
-      named_sync(kBarReady, NT);  // the compute warps' sums for this piece are complete
-      float acc[NH][32], big[NH], lt[NH];
-#pragma unroll
-      for (int h = 0; h < NH; ++h) {
-        const int row = 8 * h + rr;
-#pragma unroll
-        for (int t = 0; t < 8; ++t) {
-          float4* cell = reinterpret_cast<float4*>(sm_acc) + acc_f4(row, (d0 >> 2) + t);
-          const float4 x = *cell;
-          acc[h][4 * t] = x.x * vs; acc[h][4 * t + 1] = x.y * vs;
-          acc[h][4 * t + 2] = x.z * vs; acc[h][4 * t + 3] = x.w * vs;
-          *cell = make_float4(0.f, 0.f, 0.f, 0.f);  // leave the buffer zeroed for the next piece
-        }
-        big[h] = -INFINITY;
-        lt[h] = 0.f;
-#pragma unroll
-        for (int w = 0; w < NC; ++w) {
-          big[h] = fmaxf(big[h], sm_m[w * ROWS + row]);
-          lt[h] += sm_l[w * ROWS + row];
-        }
-        big[h] *= kLn2;
-      }
-      __threadfence_block();
-      if (n + 1 < n_total) named_arrive(kBarFree, NT);  // buffer and sm_m/sm_l may be reused
-      ++n;
-      mark_phase(tp, 5, lane == 0);
-
-      const int c_first = q.seg_start / chunk, c_last = (q.seg_start + q.np - 1) / chunk;
-      const int pieces = c_last - c_first + 1;
-      const int piece = (int)blockIdx.x - c_first;
-      if (pieces > bp.workspace_splits) {  // cannot happen with the host's min_chunk; never write past the workspace
-        if (lane == 0) atomicExch(tp.status, kErrWorkspace);
-        continue;
-      }
-      bool last = false;
-      if (pieces > 1) {
-#pragma unroll
-        for (int h = 0; h < NH; ++h) {
-          const int row = 8 * h + rr;
-          if (row < p.group) {
-            const int hq = q.kvh * p.group + row;
-            const int64_t pidx = (int64_t)q.b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h +
-                                 (int64_t)piece * p.partial_stride_s;
-            float* dst = reinterpret_cast<float*>(p.partial_output) + pidx * D + d0;
-#pragma unroll
-            for (int t = 0; t < 32; t += 4)
-              *reinterpret_cast<float4*>(dst + t) = make_float4(acc[h][t], acc[h][t + 1], acc[h][t + 2], acc[h][t + 3]);
-            if (d0 == 0) {
-              p.partial_max[pidx] = big[h];
-              p.partial_sum[pidx] = lt[h];
-            }
-          }
-        }
-        __threadfence();
-        __syncwarp();
-        int old = 0;
-        if (lane == 0) old = atomicAdd(bp.semaphores + q.b * hkv + q.kvh, 1);
-        old = __shfl_sync(0xffffffffu, old, 0);
-        last = old == pieces - 1;
-        if (last) __threadfence();
-      }
-      if (pieces == 1 || last) {
-#pragma unroll
-        for (int h = 0; h < NH; ++h) {
-          const int row = 8 * h + rr;
-          if (row >= p.group) continue;
-          const int hq = q.kvh * p.group + row;
-          float m_nat = big[h], den = lt[h];
-          if (last) {
-            // Merge the other pieces into this CTA's own (still in registers), two pieces per
-            // round trip: their maxima, sums and data are requested together.
-            const int64_t pbase = (int64_t)q.b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h;
-            const float* pout = reinterpret_cast<const float*>(p.partial_output);
-            for (int s0 = 0; s0 < pieces - 1; s0 += 2) {
-              float4 x[2][8];
-              float ms[2], ls[2];
-#pragma unroll
-              for (int v = 0; v < 2; ++v) {
-                // the v-th other piece of this batch: indices skip this CTA's own piece
-                int s = s0 + v;
-                const bool on = s < pieces - 1;
-                s = on ? (s >= piece ? s + 1 : s) : piece;
-                const int64_t pidx = pbase + (int64_t)s * p.partial_stride_s;
-                ms[v] = __ldcg(p.partial_max + pidx);
-                ls[v] = __ldcg(p.partial_sum + pidx);
-                if (!on) { ms[v] = -INFINITY; ls[v] = 0.f; }
-                const float4* src = reinterpret_cast<const float4*>(pout + pidx * D + d0);
-#pragma unroll
-                for (int t = 0; t < 8; ++t) x[v][t] = __ldcg(src + t);
-              }
-              const float m_new = fmaxf(m_nat, fmaxf(ms[0], ms[1]));
-              const float own = expf(m_nat - m_new);
-              const float cf0 = expf(ms[0] - m_new), cf1 = expf(ms[1] - m_new);
-              den = den * own + ls[0] * cf0 + ls[1] * cf1;
-              m_nat = m_new;
-#pragma unroll
-              for (int t = 0; t < 8; ++t) {
-                acc[h][4 * t] = acc[h][4 * t] * own + cf0 * x[0][t].x + cf1 * x[1][t].x;
-                acc[h][4 * t + 1] = acc[h][4 * t + 1] * own + cf0 * x[0][t].y + cf1 * x[1][t].y;
-                acc[h][4 * t + 2] = acc[h][4 * t + 2] * own + cf0 * x[0][t].z + cf1 * x[1][t].z;
-                acc[h][4 * t + 3] = acc[h][4 * t + 3] * own + cf0 * x[0][t].w + cf1 * x[1][t].w;
-              }
-            }
-          }
-          float lo16[16], hi16[16];
-#pragma unroll
-          for (int t = 0; t < 16; ++t) { lo16[t] = acc[h][t]; hi16[t] = acc[h][16 + t]; }
-          store_row16<QBF16>(p, q.b, hq, d0, lo16, m_nat, den, d0 == 0);
-          store_row16<QBF16>(p, q.b, hq, d0 + 16, hi16, m_nat, den, false);
-        }
-        if (last && lane == 0) bp.semaphores[q.b * hkv + q.kvh] = 0;  // ready for the next call
-      }
-      mark_phase(tp, 6, lane == 0);  // piece retired
-    }
+    const int off = c - chunks.first_unit(prefix[lo_b], lo_b);  // units into the pairs of lo_b
+    return prefix[lo_b] + min(max((off + 1) >> 1, 0), prefix[lo_b + 1] - prefix[lo_b]);
+  };
+  const int C0 = chunks.start_of(grp);
+  const int P0 = grp < chunks.groups ? pairs_before(C0) : total;
+  const int P1 = grp < chunks.groups ? pairs_before(chunks.start_of(grp + 1)) : total;
+  const int n = P1 - P0;
+  if (n <= 0) {
+    if (p.early_metadata) pdl_wait();  // this grid must not complete before the preceding one
     return;
   }
 
-  // ================= compute warps =================
-  // ---- producer side: this warp's pairs in chunk order, each into the next ring stage
-  struct PairRef { int32_t phys0, phys1, kvh; bool two, valid; };
-  PieceWalker pwalk;
-  pwalk.init(first, P0, P1, chunk);
-  Piece pp = pwalk.at(P0, prefix, hkv);
-  int px = piece_first(pp, warp);
-  bool pdone = false;
-  auto producer_settle = [&]() {  // move to the next piece in which this warp has a pair
-    while (!pdone && px >= pp.e) {
-      if (pp.e >= P1) { pdone = true; break; }
-      pp = pwalk.at(pp.e, prefix, hkv);
-      px = piece_first(pp, warp);
+  // Sequence that holds pair g of the list (0 <= g < total): largest b with prefix[b] <= g.
+  auto seq_of = [&](int g) {
+    int lo_b = 0, hi_b = B;
+    while (hi_b - lo_b > 1) {
+      const int mid = (lo_b + hi_b) >> 1;
+      if (prefix[mid] <= g) lo_b = mid; else hi_b = mid;
+    }
+    return lo_b;
+  };
+
+  // ---- producer side.  Page ids of 16 consecutive pairs of the chunk, one page per lane
+  // (lane 2t + u holds page u of pair base + t, -1 if there is none).
+  auto fetch_ids = [&](int base_t) {
+    int32_t phys = -1;
+    const int g = P0 + base_t + (lane >> 1);
+    if (base_t < n && g < P1) {
+      const int b = seq_of(g);
+      const int page = page_first + 2 * (g - prefix[b]) + (lane & 1);
+      if (page <= (lens[b] - 1) / kPage) phys = page_of(p.block_table, p.bt_stride_b, b, page);
+    }
+    return phys;
+  };
+  auto fire = [&](int t, int32_t ids, int base_t) {  // all lanes call; lane 0 issues
+    const int32_t phys0 = __shfl_sync(0xffffffffu, ids, (2 * (t - base_t)) & 31);
+    const int32_t phys1 = __shfl_sync(0xffffffffu, ids, (2 * (t - base_t) + 1) & 31);
+    if (lane == 0) {
+      const uint32_t bar = my_bars + 8 * (t % NSTAGE);
+      const uint32_t dst = my_ring + (t % NSTAGE) * kStage;
+      const bool two = phys1 >= 0;
+      mbar_expect_tx(bar, two ? kStage : kStage / 2);
+      const int c1 = tp.head_is_dim1 ? kvh : 0;
+      const int c2 = tp.head_is_dim1 ? 0 : kvh;
+      if (p.kv_evict_first) {
+        const uint64_t pol = l2_policy_evict_first();
+        tma_load_tile(dst, &tmap_k, bar, c1, c2, phys0, pol);
+        tma_load_tile(dst + 2 * kTile, &tmap_v, bar, c1, c2, phys0, pol);
+        if (two) {
+          tma_load_tile(dst + kTile, &tmap_k, bar, c1, c2, phys1, pol);
+          tma_load_tile(dst + 3 * kTile, &tmap_v, bar, c1, c2, phys1, pol);
+        }
+      } else {
+        tma_load_tile(dst, &tmap_k, bar, c1, c2, phys0);
+        tma_load_tile(dst + 2 * kTile, &tmap_v, bar, c1, c2, phys0);
+        if (two) {
+          tma_load_tile(dst + kTile, &tmap_k, bar, c1, c2, phys1);
+          tma_load_tile(dst + 3 * kTile, &tmap_v, bar, c1, c2, phys1);
+        }
+      }
     }
   };
-  producer_settle();
-  auto locate = [&]() {  // page ids of this warp's next pair (global loads, all lanes alike)
-    PairRef r;
-    r.valid = !pdone;
-    r.phys0 = r.phys1 = r.kvh = 0;
-    r.two = false;
-    if (!pdone) {
-      const int page0 = page_first + 2 * (px - pp.seg_start);
-      const int last_page = (lens[pp.b] - 1) / kPage;
-      r.two = page0 + 1 <= last_page;
-      r.kvh = pp.kvh;
-      const int32_t* row = p.block_table + (int64_t)pp.b * p.bt_stride_b;
-      r.phys0 = __ldg(row + page0);
-      r.phys1 = r.two ? __ldg(row + page0 + 1) : 0;
-      px += piece_stride(pp);
-      producer_settle();
-    }
-    return r;
-  };
-  auto fire = [&](int k, const PairRef& r) {  // lane 0 only
-    const uint32_t bar = my_bars + 8 * (k % NSTAGE);
-    const uint32_t dst = my_ring + (k % NSTAGE) * kStage;
-    mbar_expect_tx(bar, r.two ? kStage : kStage / 2);
-    const int c1 = tp.head_is_dim1 ? r.kvh : 0;
-    const int c2 = tp.head_is_dim1 ? 0 : r.kvh;
-    tma_load_tile(dst, &tmap_k, bar, c1, c2, r.phys0);
-    tma_load_tile(dst + 2 * kTile, &tmap_v, bar, c1, c2, r.phys0);
-    if (r.two) {
-      tma_load_tile(dst + kTile, &tmap_k, bar, c1, c2, r.phys1);
-      tma_load_tile(dst + 3 * kTile, &tmap_v, bar, c1, c2, r.phys1);
-    }
-  };
+  int32_t ids_cur = fetch_ids(0), ids_next = fetch_ids(16);
+  int ids_base = 0;
   __syncwarp();
-  PairRef pending;
-  {
-    PairRef r[NSTAGE + 1];
+  if (p.early_metadata) pdl_wait();
 #pragma unroll
-    for (int k = 0; k <= NSTAGE; ++k) r[k] = locate();
-#pragma unroll
-    for (int k = 0; k < NSTAGE; ++k)
-      if (r[k].valid && lane == 0) fire(k, r[k]);
-    pending = r[NSTAGE];
-  }
-  mark_phase(tp, 2);  // first copies issued
-  int n_total_shared = 0;  // shared pieces of this chunk (same walk as the retiring warp's)
-  {
-    PieceWalker w;
-    w.init(first, P0, P1, chunk);
-    for (int gg = P0; gg < P1;) {
-      const Piece t = w.at(gg, prefix, hkv);
-      n_total_shared += t.solo() ? 0 : 1;
-      gg = t.e;
-    }
-  }
+  for (int t = 0; t < NSTAGE; ++t)
+    if (t < n) fire(t, ids_cur, 0);
+  mark_phase_at(tp, W, 2, lane == 0);  // first copies issued
 
   // swizzled shared-memory offsets of this thread's fragments inside a tile
   uint32_t k_off[2][2], v_off[4];
@@ -667,276 +452,193 @@ paged_decode_fp8_balanced_kernel(const KernelParams p, const TmaParams tp, const
     v_off[r] = row * D + ((i ^ (row & 7)) << 4);
   }
 
-  // ---- consumer side: the pieces this warp takes part in (shared ones, and its own solo ones),
-  // in chunk order; the query of the next such piece is fetched while the current one retires
-  PieceWalker cwalk;
-  cwalk.init(first, P0, P1, chunk);
-  int g = P0;
-  auto next_piece = [&](Piece& q) {  // false when the chunk is exhausted
-    while (g < P1) {
-      q = cwalk.at(g, prefix, hkv);
-      g = q.e;
-      if (!q.solo() || q.owner == warp) return true;
-    }
-    return false;
-  };
-  BalState<NH> st;
-  int cons = 0;      // pairs this warp has consumed
-  int n_shared = 0;  // pieces reduced through shared memory so far
+  // ---- consumer side: the pieces of the chunk in order
+  struct Cursor { int b, np, start; };  // current sequence, its pairs, list index of its first pair
+  Cursor cur;
+  cur.b = seq_of(P0);
+  cur.np = prefix[cur.b + 1] - prefix[cur.b];
+  cur.start = prefix[cur.b];
+  const float ks = p.k_scale_ph ? __ldg(p.k_scale_ph + kvh) : p.k_scale;
+  const float vs = p.v_scale_ph ? __ldg(p.v_scale_ph + kvh) : p.v_scale;
+  const float scale_log2 = ks * p.sm_scale * kLog2e;
+  uint32_t qb[1][8][2];
+  bal_load_q<QBF16, 1>(qb, p, cur.b, kvh, i, j);
+  BalState<1> st;
   bool ok = true;
-  Piece q;
-  bool have = next_piece(q);
-  uint32_t qb[NH][8][2];
-  if (have && piece_first(q, warp) < q.e) bal_load_q<QBF16, NH>(qb, p, q.b, q.kvh, i, j);
-  bool first_piece = true;
-  while (have) {
-    const int x0 = piece_first(q, warp), stride = piece_stride(q);
-    const int seq_len = lens[q.b];
-    const float ks = p.k_scale_ph ? __ldg(p.k_scale_ph + q.kvh) : p.k_scale;
-    const float scale_log2 = ks * p.sm_scale * kLog2e;
-    bal_reset<NH>(st);
-    for (int x = x0; ok && x < q.e; x += stride) {
-      const int s = cons % NSTAGE;
-      if (!mbar_wait_bounded(my_bars + 8 * s, (cons / NSTAGE) & 1)) { ok = false; break; }
-      if (cons == 0) mark_phase(tp, 3);  // first data landed
-      const int tok0 = (page_first + 2 * (x - q.seg_start)) * kPage;
-      bal_step<NH>(st, my_ring + s * kStage, k_off, v_off, qb, scale_log2, tok0, p.kv_start, seq_len, i, j);
-      // all reads of the stage fed MMAs above: hand it back to TMA for this warp's pair cons + NSTAGE
+  int t = 0;  // pairs consumed
+  int g = P0;
+#pragma unroll 1
+  while (ok && g < P1) {
+    const int e = min(cur.start + cur.np, P1);
+    // the next piece's query is requested now and used when this piece is done
+    Cursor nxt = cur;
+    uint32_t qn[1][8][2];
+    if (e < P1) {
+      do {  // sequences with nothing to attend have no pairs
+        nxt.start += nxt.np;
+        ++nxt.b;
+        nxt.np = prefix[nxt.b + 1] - prefix[nxt.b];
+      } while (nxt.np == 0);
+      bal_load_q<QBF16, 1>(qn, p, nxt.b, kvh, i, j);
+    }
+    const int seq_len = lens[cur.b];
+    const bool whole = cur.start >= P0 && cur.start + cur.np <= P1;
+    bal_reset<1>(st);
+#pragma unroll 1
+    for (; g < e; ++g, ++t) {
+      const int s = t % NSTAGE;
+      if (!mbar_wait_bounded(my_bars + 8 * s, (t / NSTAGE) & 1)) { ok = false; break; }
+      if (t == 0) mark_phase_at(tp, W, 3, lane == 0);  // first data landed
+      const int tok0 = (page_first + 2 * (g - cur.start)) * kPage;
+      bal_step<1>(st, my_ring + s * kStage, k_off, v_off, qb, scale_log2, tok0, p.kv_start, seq_len, i, j);
+      // all reads of the stage fed MMAs above: hand it back to TMA for the chunk's pair t + NSTAGE
       __syncwarp();
-      if (pending.valid) {
-        if (lane == 0) {
-          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-          fire(cons + NSTAGE, pending);
+      const int tn = t + NSTAGE;
+      if (tn < n) {
+        if ((tn & 15) == 0) {
+          ids_cur = ids_next;
+          ids_base = tn;
+          ids_next = fetch_ids(tn + 16);
         }
-        pending = locate();
+        if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        fire(tn, ids_cur, ids_base);
       }
-      ++cons;
     }
-    if (first_piece) mark_phase(tp, 4);  // (warp 0) streaming of its first piece done
-    first_piece = false;
+    if (!ok) break;
 
-    // next piece and its query: the loads fly while this piece is reduced
-    Piece nq;
-    const bool have_next = next_piece(nq);
-    uint32_t qn[NH][8][2];
-    if (have_next && piece_first(nq, warp) < nq.e) bal_load_q<QBF16, NH>(qn, p, nq.b, nq.kvh, i, j);
-
-    // ---- this warp's sums over the tokens it saw
-    float lsum[NH][2];
+    // ---- the piece is complete: this thread's sums over the tokens it saw
+    float lsum[2];
 #pragma unroll
-    for (int h = 0; h < NH; ++h)
+    for (int c = 0; c < 2; ++c) {
+      float x = st.l[0][c];
+      x += __shfl_xor_sync(0xffffffffu, x, 4);
+      x += __shfl_xor_sync(0xffffffffu, x, 8);
+      x += __shfl_xor_sync(0xffffffffu, x, 16);
+      lsum[c] = x;
+    }
+    const int which = chunks.first_unit(cur.start, cur.b) > C0 ? 1 : 0;
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        float x = st.l[h][e];
-        x += __shfl_xor_sync(0xffffffffu, x, 4);
-        x += __shfl_xor_sync(0xffffffffu, x, 8);
-        x += __shfl_xor_sync(0xffffffffu, x, 16);
-        lsum[h][e] = x;
+    for (int c = 0; c < 2; ++c) {
+      const int row = 2 * j + c;
+      if (row >= p.group) continue;
+      float v[16];
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        v[2 * mt] = st.o[0][mt][c] * vs;
+        v[2 * mt + 1] = st.o[0][mt][2 + c] * vs;
       }
-    if (q.solo()) {
-      // a small whole segment: write its rows straight from registers
-      const float vs = p.v_scale_ph ? __ldg(p.v_scale_ph + q.kvh) : p.v_scale;
-#pragma unroll
-      for (int h = 0; h < NH; ++h)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int row = 8 * h + 2 * j + e;
-          if (row >= p.group) continue;
-          float v[16];
-#pragma unroll
-          for (int mt = 0; mt < 8; ++mt) {
-            v[2 * mt] = st.o[h][mt][e] * vs;
-            v[2 * mt + 1] = st.o[h][mt][2 + e] * vs;
-          }
-          store_row16<QBF16>(p, q.b, q.kvh * p.group + row, 16 * i, v, st.m[h][e] * kLn2, lsum[h][e], i == 0);
-        }
-    } else {
-      // ---- reduction over the compute warps in shared memory; the retiring warp takes it from there
-      if (n_shared > 0) named_sync(kBarFree, NT);  // previous piece has been read out
-#pragma unroll
-      for (int h = 0; h < NH; ++h)
-#pragma unroll
-        for (int e = 0; e < 2; ++e)
-          if (i == 0) sm_m[warp * ROWS + 8 * h + 2 * j + e] = st.m[h][e];
-      named_sync(kBarMax, NC * 32);
-      float fac[NH][2];
-#pragma unroll
-      for (int h = 0; h < NH; ++h) {
-        float f[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int row = 8 * h + 2 * j + e;
-          float big = -INFINITY;
-#pragma unroll
-          for (int w = 0; w < NC; ++w) big = fmaxf(big, sm_m[w * ROWS + row]);
-          f[e] = (st.m[h][e] == -INFINITY) ? 0.f : exp2f(st.m[h][e] - big);
-          if (i == 0) sm_l[warp * ROWS + row] = lsum[h][e] * f[e];
-        }
-        fac[h][0] = f[0];
-        fac[h][1] = f[1];
-      }
-      // Sum the four warps' O^T without atomics: in phase k warp w adds the quarter
-      // (w + k) % 4 of its values (m-tiles 2q, 2q+1, i.e. columns 16i + 4q .. +3 of rows 2j, 2j+1)
-      // with plain float4 read-modify-writes; no two warps touch the same quarter in a phase.
-#pragma unroll
-      for (int k = 0; k < NC; ++k) {
-        const int qq = (warp + k) & (NC - 1);
-#pragma unroll
-        for (int h = 0; h < NH; ++h)
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int row = 8 * h + 2 * j + e;
-            float4* cell = reinterpret_cast<float4*>(sm_acc) + acc_f4(row, 4 * i + qq);
-            float4 x = *cell;
-            // m-tile 2q: columns +0 (c = e) and +1 (c = 2 + e); m-tile 2q+1: +2 and +3
-            float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
-#pragma unroll
-            for (int z = 0; z < NC; ++z)
-              if (z == qq) {
-                v0 = st.o[h][2 * z][e]; v1 = st.o[h][2 * z][2 + e];
-                v2 = st.o[h][2 * z + 1][e]; v3 = st.o[h][2 * z + 1][2 + e];
-              }
-            x.x += v0 * fac[h][e]; x.y += v1 * fac[h][e]; x.z += v2 * fac[h][e]; x.w += v3 * fac[h][e];
-            *cell = x;
-          }
-        if (k + 1 < NC) named_sync(kBarMax, NC * 32);
-      }
-      __threadfence_block();
-      if (n_shared + 1 < n_total_shared) {
-        named_arrive(kBarReady, NT);
+      if (whole) {
+        store_row16<QBF16>(p, cur.b, kvh * p.group + row, 16 * i, v, st.m[0][c] * kLn2, lsum[c], i == 0);
       } else {
-        // The chunk's last shared piece decides when the CTA is done: all four compute warps
-        // retire it together (8 columns per thread, every merge operand requested at once)
-        // instead of queueing it behind the retiring warp's earlier pieces.
-        named_sync(kBarMax, NC * 32);
-        const float vs = p.v_scale_ph ? __ldg(p.v_scale_ph + q.kvh) : p.v_scale;
-        const int c_first = q.seg_start / chunk, c_last = (q.seg_start + q.np - 1) / chunk;
-        const int pieces = c_last - c_first + 1, piece = (int)blockIdx.x - c_first;
-        const bool fits = pieces <= bp.workspace_splits;
-        if (!fits && threadIdx.x == 0) atomicExch(tp.status, kErrWorkspace);
-        constexpr int ITEMS = ROWS * 16 / (NC * 32);  // (row, 8 columns) slices per thread
-        float a8[ITEMS][8], m_nat[ITEMS], den[ITEMS];
+        const int64_t r = chunk_slot_row(grp, which, p.num_q_heads, kvh * p.group + row);
+        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.partial_output) + r * D + 16 * i);
 #pragma unroll
-        for (int it = 0; it < ITEMS; ++it) {
-          const int e = threadIdx.x + it * NC * 32, row = e >> 4, c8 = (e & 15) * 8;
-          const float4 x0 = reinterpret_cast<const float4*>(sm_acc)[acc_f4(row, c8 >> 2)];
-          const float4 x1 = reinterpret_cast<const float4*>(sm_acc)[acc_f4(row, (c8 >> 2) + 1)];
-          a8[it][0] = x0.x * vs; a8[it][1] = x0.y * vs; a8[it][2] = x0.z * vs; a8[it][3] = x0.w * vs;
-          a8[it][4] = x1.x * vs; a8[it][5] = x1.y * vs; a8[it][6] = x1.z * vs; a8[it][7] = x1.w * vs;
-          float big = -INFINITY, lt = 0.f;
-#pragma unroll
-          for (int w = 0; w < NC; ++w) {
-            big = fmaxf(big, sm_m[w * ROWS + row]);
-            lt += sm_l[w * ROWS + row];
-          }
-          m_nat[it] = big * kLn2;
-          den[it] = lt;
-          if (fits && pieces > 1 && row < p.group) {
-            const int hq = q.kvh * p.group + row;
-            const int64_t pidx = (int64_t)q.b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h +
-                                 (int64_t)piece * p.partial_stride_s;
-            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.partial_output) + pidx * D + c8);
-            dst[0] = make_float4(a8[it][0], a8[it][1], a8[it][2], a8[it][3]);
-            dst[1] = make_float4(a8[it][4], a8[it][5], a8[it][6], a8[it][7]);
-            if (c8 == 0) {
-              p.partial_max[pidx] = m_nat[it];
-              p.partial_sum[pidx] = den[it];
-            }
-          }
+        for (int f = 0; f < 4; ++f) dst[f] = make_float4(v[4 * f], v[4 * f + 1], v[4 * f + 2], v[4 * f + 3]);
+        if (i == 0) {
+          p.partial_max[r] = st.m[0][c] * kLn2;
+          p.partial_sum[r] = lsum[c];
         }
-        bool last = false;
-        if (fits && pieces > 1) {
-          __threadfence();
-          named_sync(kBarMax, NC * 32);
-          if (threadIdx.x == 0) sm_misc[0] = atomicAdd(bp.semaphores + q.b * hkv + q.kvh, 1) == pieces - 1;
-          named_sync(kBarMax, NC * 32);
-          last = sm_misc[0] != 0;
-          if (last) __threadfence();
-        }
-        if (fits && (pieces == 1 || last)) {
-#pragma unroll
-          for (int it = 0; it < ITEMS; ++it) {
-            const int e = threadIdx.x + it * NC * 32, row = e >> 4, c8 = (e & 15) * 8;
-            if (row >= p.group) continue;
-            const int hq = q.kvh * p.group + row;
-            if (last) {
-              const int64_t pbase = (int64_t)q.b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h;
-              const float* pout = reinterpret_cast<const float*>(p.partial_output);
-              for (int s0 = 0; s0 < pieces - 1; s0 += 8) {
-                float4 x[8][2];
-                float ms[8], ls[8];
-#pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                  int sidx = s0 + v;
-                  const bool on = sidx < pieces - 1;
-                  sidx = on ? (sidx >= piece ? sidx + 1 : sidx) : piece;
-                  const int64_t pidx = pbase + (int64_t)sidx * p.partial_stride_s;
-                  ms[v] = __ldcg(p.partial_max + pidx);
-                  ls[v] = __ldcg(p.partial_sum + pidx);
-                  if (!on) { ms[v] = -INFINITY; ls[v] = 0.f; }
-                  const float4* src = reinterpret_cast<const float4*>(pout + pidx * D + c8);
-                  x[v][0] = __ldcg(src);
-                  x[v][1] = __ldcg(src + 1);
-                }
-                float m_new = m_nat[it];
-#pragma unroll
-                for (int v = 0; v < 8; ++v) m_new = fmaxf(m_new, ms[v]);
-                const float own = expf(m_nat[it] - m_new);
-                den[it] *= own;
-#pragma unroll
-                for (int t = 0; t < 8; ++t) a8[it][t] *= own;
-#pragma unroll
-                for (int v = 0; v < 8; ++v) {
-                  const float cf = expf(ms[v] - m_new);
-                  den[it] += ls[v] * cf;
-                  a8[it][0] += cf * x[v][0].x; a8[it][1] += cf * x[v][0].y;
-                  a8[it][2] += cf * x[v][0].z; a8[it][3] += cf * x[v][0].w;
-                  a8[it][4] += cf * x[v][1].x; a8[it][5] += cf * x[v][1].y;
-                  a8[it][6] += cf * x[v][1].z; a8[it][7] += cf * x[v][1].w;
-                }
-                m_nat[it] = m_new;
-              }
-            }
-            if (p.packed_output != nullptr) {
-              float* dst = p.packed_output + ((int64_t)q.b * p.num_q_heads + hq) * (D + 2);
-#pragma unroll
-              for (int t = 0; t < 8; t += 2) *reinterpret_cast<float2*>(dst + c8 + t) = make_float2(a8[it][t], a8[it][t + 1]);
-              if (c8 == 0) { dst[D] = m_nat[it]; dst[D + 1] = den[it]; }
-            } else {
-              const float inv = 1.f / den[it];
-              uint32_t wv[4];
-#pragma unroll
-              for (int t = 0; t < 4; ++t) {
-                if constexpr (QBF16) {
-                  __nv_bfloat162 x = __floats2bfloat162_rn(a8[it][2 * t] * inv, a8[it][2 * t + 1] * inv);
-                  wv[t] = *reinterpret_cast<uint32_t*>(&x);
-                } else {
-                  wv[t] = pack_f16x2(a8[it][2 * t] * inv, a8[it][2 * t + 1] * inv);
-                }
-              }
-              uint16_t* dst = reinterpret_cast<uint16_t*>(p.output) + (int64_t)q.b * p.o_stride_b + (int64_t)hq * p.o_stride_h + c8;
-              *reinterpret_cast<uint2*>(dst) = make_uint2(wv[0], wv[1]);
-              *reinterpret_cast<uint2*>(dst + 4) = make_uint2(wv[2], wv[3]);
-            }
-          }
-          if (last && threadIdx.x == 0) bp.semaphores[q.b * hkv + q.kvh] = 0;  // ready for the next call
-        }
-        mark_phase(tp, 6);  // chunk's last shared piece retired
       }
-      ++n_shared;
     }
-    q = nq;
-    have = have_next;
+    cur = nxt;
 #pragma unroll
-    for (int h = 0; h < NH; ++h)
-#pragma unroll
-      for (int t = 0; t < 8; ++t) { qb[h][t][0] = qn[h][t][0]; qb[h][t][1] = qn[h][t][1]; }
+    for (int f = 0; f < 8; ++f) { qb[0][f][0] = qn[0][f][0]; qb[0][f][1] = qn[0][f][1]; }
   }
+  mark_phase_at(tp, W, 4, lane == 0);  // chunk done
   if (!ok && lane == 0) {
     // a copy never landed: record it; give the copies still in flight a bounded chance to land
     atomicExch(tp.status, kErrTmaTimeout);
-    for (int u = cons + 1; u < cons + NSTAGE; ++u) mbar_wait_bounded(my_bars + 8 * (u % NSTAGE), (u / NSTAGE) & 1);
+    const int issued = min(n, t + NSTAGE);
+    for (int u = t + 1; u < issued; ++u) mbar_wait_bounded(my_bars + 8 * (u % NSTAGE), (u / NSTAGE) & 1);
   }
+}
+
+// LSE merge of the pieces the chunk kernel left in the workspace; one warp per (sequence, q head)
+// row.  A row whose segment lay inside one chunk has been written already.  Same maths as
+// _paged_split_kv_reduce (integrations/vllm/l20_paged_split_kv.py:459-488).
+template <bool QBF16>
+__global__ void __launch_bounds__(128)
+paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const ChunkParams cp) {
+  constexpr int D = 128, E = 4;
+  pdl_launch_dependents();
+  mark_phase_at(tp, blockIdx.x, 5, threadIdx.x == 0);  // merge CTA resident
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= cp.batch * p.num_q_heads) return;
+  const int b = row / p.num_q_heads, hq = row % p.num_q_heads;
+  const int page_first = p.kv_start / kPage;
+  // seq_lens is an input of the whole step, not a result of the chunk kernel: the chunking is
+  // recomputed here while that kernel is still running.
+  int below = 0, all = 0;
+  for (int x = lane; x < cp.batch; x += 32) {
+    const int np = pairs_of(__ldg(p.seq_lens + x), page_first);
+    all += np;
+    below += x < b ? np : 0;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    all += __shfl_xor_sync(0xffffffffu, all, off);
+    below += __shfl_xor_sync(0xffffffffu, below, off);
+  }
+  const int np = pairs_of(__ldg(p.seq_lens + b), page_first);
+  const Chunking chunks(all, cp.batch, max(cp.num_warps / p.num_kv_heads, 1), cp.piece_cost);
+  const int s0 = chunks.first_unit(below, b);
+  const int w_first = np > 0 ? chunks.chunk_of(s0) : 0;
+  const int ns = np > 0 ? chunks.chunk_of(s0 + 2 * (np - 1)) - w_first + 1 : 0;
+  if (ns == 1) return;  // written by the chunk kernel
+  float acc[E] = {0.f, 0.f, 0.f, 0.f};
+  float big = -INFINITY, den = 0.f;
+  pdl_wait();  // the chunk kernel's stores are complete and visible from here on
+  mark_phase_at(tp, blockIdx.x, 6, threadIdx.x == 0);  // chunk kernel complete
+  constexpr int kBatch = 16;  // pieces requested per round trip
+  for (int k0 = 0; k0 < ns; k0 += kBatch) {
+    float mv[kBatch], lv[kBatch];
+    float4 xv[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const bool on = k0 + u < ns;
+      const int w = w_first + (on ? k0 + u : 0);
+      const int64_t r = chunk_slot_row(w, s0 > chunks.start_of(w) ? 1 : 0, p.num_q_heads, hq);
+      mv[u] = on ? p.partial_max[r] : -INFINITY;
+      lv[u] = on ? p.partial_sum[r] : 0.f;
+      xv[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.partial_output) + r * D + lane * E);
+    }
+    float m_new = big;
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) m_new = fmaxf(m_new, mv[u]);
+    const float keep = (big == -INFINITY) ? 0.f : expf(big - m_new);
+    den *= keep;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] *= keep;
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const float c = (mv[u] == -INFINITY) ? 0.f : expf(mv[u] - m_new);
+      den += lv[u] * c;
+      acc[0] += c * xv[u].x; acc[1] += c * xv[u].y; acc[2] += c * xv[u].z; acc[3] += c * xv[u].w;
+    }
+    big = m_new;
+  }
+  if (p.packed_output != nullptr) {
+    float* dst = p.packed_output + (int64_t)row * (D + 2);
+    *reinterpret_cast<float2*>(dst + lane * E) = make_float2(acc[0], acc[1]);
+    *reinterpret_cast<float2*>(dst + lane * E + 2) = make_float2(acc[2], acc[3]);
+    if (lane == 0) { dst[D] = big; dst[D + 1] = den; }
+    return;
+  }
+  mark_phase_at(tp, blockIdx.x, 7, threadIdx.x == 0);  // merged
+  const float inv = ns > 0 ? 1.f / den : 0.f;
+  uint16_t* dst = reinterpret_cast<uint16_t*>(p.output) + (int64_t)b * p.o_stride_b + (int64_t)hq * p.o_stride_h + lane * E;
+  uint32_t w0, w1;
+  if constexpr (QBF16) {
+    __nv_bfloat162 x = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
+    __nv_bfloat162 y = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+    w0 = *reinterpret_cast<uint32_t*>(&x);
+    w1 = *reinterpret_cast<uint32_t*>(&y);
+  } else {
+    w0 = pack_f16x2(acc[0] * inv, acc[1] * inv);
+    w1 = pack_f16x2(acc[2] * inv, acc[3] * inv);
+  }
+  *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
 }
 
 }  // namespace pfd

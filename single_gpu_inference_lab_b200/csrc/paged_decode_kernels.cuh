@@ -55,6 +55,8 @@ struct KernelParams {
   int32_t direct_out;  // 1: a sequence with a single split writes its final result itself
   int32_t bt_cols;     // width of a block-table row
   int32_t slot_offset; // workspace slots [0, slot_offset) are filled by another kernel (dense prefix pass)
+  int32_t early_metadata;  // 1: seq_lens and block_table may be read before the preceding kernel has completed
+  int32_t kv_evict_first;  // 1: K/V tiles are loaded with the L2 evict-first hint
 };
 
 // Programmatic dependent launch: the split-KV partial kernel lets its dependent (the merge
@@ -529,6 +531,23 @@ __device__ __forceinline__ void tma_load_tile(uint32_t dst, const void* tmap, ui
       : "memory");
 }
 
+// The same load with an L2 eviction-priority hint.  K/V bytes are read once per step: marked
+// evict-first they do not push the step's small reused data (query rows, block table, the
+// partial results the merge kernel reads back) out of L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  return policy;
+}
+__device__ __forceinline__ void tma_load_tile(uint32_t dst, const void* tmap, uint32_t bar, int c1,
+                                              int c2, int c3, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(0), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
+      : "memory");
+}
+
 __device__ __forceinline__ uint4 lds_16(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -543,12 +562,15 @@ struct TmaParams {
   unsigned long long* phase_times;  // optional [grid][8] nanosecond timestamps of a CTA's phases
 };
 
-__device__ __forceinline__ void mark_phase(const TmaParams& tp, int k, bool leader) {
+__device__ __forceinline__ void mark_phase_at(const TmaParams& tp, int slot, int k, bool leader) {
   if (tp.phase_times != nullptr && leader) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    tp.phase_times[(size_t)blockIdx.x * 8 + k] = t;
+    tp.phase_times[(size_t)slot * 8 + k] = t;
   }
+}
+__device__ __forceinline__ void mark_phase(const TmaParams& tp, int k, bool leader) {
+  mark_phase_at(tp, blockIdx.x, k, leader);
 }
 __device__ __forceinline__ void mark_phase(const TmaParams& tp, int k) { mark_phase(tp, k, threadIdx.x == 0); }
 
@@ -579,7 +601,9 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   // Launched as a programmatic dependent of whatever precedes it in the stream: the CTA may
   // become resident while that kernel drains, but touches no memory before it has completed.
   // (Behind the dense prefix pass the wait is at the end instead: the two passes are independent.)
-  if (p.slot_offset == 0) pdl_wait();
+  // With early_metadata the caller vouches that seq_lens and block_table are not written by
+  // that kernel: their reads below are then allowed to come first.
+  if (p.slot_offset == 0 && !p.early_metadata) pdl_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
   const int lo = p.kv_start + split * p.split_size;
@@ -597,6 +621,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   const int seq_len = p.seq_lens[b];
   const int hi = min(lo + p.split_size, seq_len);
   if (lo >= hi) { pdl_wait(); return; }
+  if (p.slot_offset == 0 && p.early_metadata) pdl_wait();
   const int nsplits_seq = (seq_len - p.kv_start + p.split_size - 1) / p.split_size;
 
   extern __shared__ uint8_t smem_raw[];
@@ -630,11 +655,21 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
     mbar_expect_tx(bar, two ? kStageBytes : kStageBytes / 2);
     const int c1 = tp.head_is_dim1 ? kvh : 0;
     const int c2 = tp.head_is_dim1 ? 0 : kvh;
-    tma_load_tile(dst, &tmap_k, bar, c1, c2, phys0);
-    tma_load_tile(dst + 2 * kTileBytes, &tmap_v, bar, c1, c2, phys0);
-    if (two) {
-      tma_load_tile(dst + kTileBytes, &tmap_k, bar, c1, c2, phys1);
-      tma_load_tile(dst + 3 * kTileBytes, &tmap_v, bar, c1, c2, phys1);
+    if (p.kv_evict_first) {
+      const uint64_t pol = l2_policy_evict_first();
+      tma_load_tile(dst, &tmap_k, bar, c1, c2, phys0, pol);
+      tma_load_tile(dst + 2 * kTileBytes, &tmap_v, bar, c1, c2, phys0, pol);
+      if (two) {
+        tma_load_tile(dst + kTileBytes, &tmap_k, bar, c1, c2, phys1, pol);
+        tma_load_tile(dst + 3 * kTileBytes, &tmap_v, bar, c1, c2, phys1, pol);
+      }
+    } else {
+      tma_load_tile(dst, &tmap_k, bar, c1, c2, phys0);
+      tma_load_tile(dst + 2 * kTileBytes, &tmap_v, bar, c1, c2, phys0);
+      if (two) {
+        tma_load_tile(dst + kTileBytes, &tmap_k, bar, c1, c2, phys1);
+        tma_load_tile(dst + 3 * kTileBytes, &tmap_v, bar, c1, c2, phys1);
+      }
     }
   };
 #pragma unroll

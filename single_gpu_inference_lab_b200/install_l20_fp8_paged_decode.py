@@ -175,6 +175,7 @@ CALL_NEW = """                else:
                             split_size=512,
                             output=out_decode.view_as(decode_query),
                             workspace=self._l20_fp8_workspace,
+                            metadata_stable=True,  # built once per model step
                         )
                         trace_path = l20_os.getenv("VLLM_L20_FP8_PAGED_TRACE")
                         if trace_path:

@@ -16,6 +16,13 @@ import torch
 
 _LOADED = False
 
+# flag bits of the superset op (PFD_FLAG_* of include/paged_fp8_decode.h)
+FLAG_NO_TMA = 1
+FLAG_NO_DIRECT_OUT = 2
+FLAG_PARTIAL_ONLY = 4
+FLAG_FIXED_SPLITS = 8
+FLAG_EARLY_METADATA = 32
+
 
 def load_library(path: Optional[Union[str, Path]] = None) -> None:
     global _LOADED
@@ -90,8 +97,8 @@ def paged_decode_fp8_e4m3_split_out_v2(
     """Superset op: ``[Hkv]`` scale tensors (per layer and kv head), explicit softmax scale
     (0 = ``D**-0.5``), first attended token ``kv_start`` and, instead of or besides
     ``output``, a packed fp32 ``[B, Hq, D + 2]`` ``(o, m, l)`` for cross-GPU merging.
-    ``semaphores`` (int32 ``[B * Hkv]``, zero on entry, left zero) selects the one-kernel
-    balanced path for head_dim 128."""
+    ``flags`` are the ``FLAG_*`` bits above.  ``semaphores`` is accepted and ignored (earlier
+    builds counted retired pieces there)."""
     torch.ops.l20_stack.paged_decode_fp8_e4m3_split_out_v2(
         query,
         key_cache,

@@ -37,26 +37,48 @@ def _ops():
     return l20_paged_decode
 
 
+BALANCED_WARPS_PER_SM = 12  # warps of the balanced persistent kernel on every SM
+BALANCED_MAX_GROUP = 8      # query heads per kv head it handles
+
+
+def balanced_workspace_splits(query: torch.Tensor, num_kv_heads: int | None = None) -> int:
+    """Smallest split axis ``S`` with which a ``[B, Hq, S]`` workspace can hold the pieces of the
+    balanced persistent kernel: two slots of ``Hq`` rows for every group of ``Hkv`` warps, i.e.
+    ``2 * (12 * SMs // Hkv) * Hq`` rows (``pfd_balanced_workspace_rows``).  Without
+    ``num_kv_heads`` the bound for the largest supported GQA ratio is used (about 15 MB of fp32
+    rows on a 148-SM part, whatever the batch)."""
+    batch, num_q_heads, _ = query.shape
+    sms = torch.cuda.get_device_properties(query.device).multi_processor_count if query.is_cuda else 148
+    warps = sms * BALANCED_WARPS_PER_SM
+    if num_kv_heads:
+        rows = 2 * (warps // int(num_kv_heads)) * num_q_heads
+    else:
+        rows = 2 * warps * min(BALANCED_MAX_GROUP, num_q_heads)
+    return _cdiv(rows, max(batch * num_q_heads, 1))
+
+
 def allocate_l20_paged_split_kv_workspace(
     query: torch.Tensor,
     max_seq_len: int,
     *,
     split_size: int = 512,
-) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
-    """``(partial_output [B,Hq,S,D] f32, partial_max [B,Hq,S] f32, partial_sum, output,
-    semaphores)`` with ``S = next_pow2(ceil(max_seq_len / split_size))`` as in the reference
-    (:21-22).  The fifth entry (int32 zeros, one per sequence and head -- enough for any GQA
-    ratio) is what lets the operator run as one balanced kernel; callers that pass the tuple
-    through unchanged, as the reference hook does, get it for free."""
+    num_kv_heads: int | None = None,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]:
+    """``(partial_output [B,Hq,S,D] f32, partial_max [B,Hq,S] f32, partial_sum, output)`` as in
+    the reference (:14-30), where ``S = next_pow2(ceil(max_seq_len / split_size))`` (:21-22).
+    Here ``S`` is also at least ``balanced_workspace_splits(query)``, which only matters for
+    small batches: with that capacity the operator runs its balanced persistent kernel, which
+    treats the workspace as a flat list of rows and needs no tuning of ``split_size``."""
     batch, num_q_heads, head_dim = query.shape
     num_splits = _next_power_of_two(_cdiv(max_seq_len, split_size))
+    if head_dim == 128:
+        num_splits = max(num_splits, balanced_workspace_splits(query, num_kv_heads))
     partial_shape = (batch, num_q_heads, num_splits)
     return (
         torch.empty((*partial_shape, head_dim), device=query.device, dtype=torch.float32),
         torch.empty(partial_shape, device=query.device, dtype=torch.float32),
         torch.empty(partial_shape, device=query.device, dtype=torch.float32),
         torch.empty_like(query),
-        torch.zeros(batch * num_q_heads, device=query.device, dtype=torch.int32),
     )
 
 
@@ -104,7 +126,12 @@ def l20_paged_split_kv_attention_fp8(
     split_size: int = 512,
     output: torch.Tensor | None = None,
     workspace: tuple[torch.Tensor, ...] | None = None,
+    metadata_stable: bool = False,
 ) -> torch.Tensor:
+    """``metadata_stable=True`` (not in the reference) tells the operator that the kernel
+    running before it on the stream does not write ``block_table`` or ``seq_lens`` -- true for
+    every layer of a model step, whose metadata is built once -- so that it may read them while
+    that kernel drains (``PFD_FLAG_EARLY_METADATA``)."""
     if not query.is_cuda or torch.cuda.get_device_capability(query.device) != REQUIRED_CAPABILITY:
         raise RuntimeError("requires an SM100 GPU")
     if query.ndim != 3 or key_cache.ndim != 4 or value_cache.shape != key_cache.shape:
@@ -130,18 +157,19 @@ def l20_paged_split_kv_attention_fp8(
     if workspace is None:
         workspace = allocate_l20_paged_split_kv_workspace(query, max_seq_len, split_size=split_size)
     partial_output, partial_max, partial_sum, workspace_output = workspace[:4]
-    semaphores = workspace[4] if len(workspace) > 4 else None
     if output is None:
         output = workspace_output
     if (
-        partial_output.shape != (*partial_shape, head_dim)
-        or partial_max.shape != partial_shape
-        or partial_sum.shape != partial_shape
+        partial_output.shape[:2] != partial_shape[:2]
+        or partial_output.shape[2] < num_splits
+        or partial_output.shape[3] != head_dim
+        or partial_max.shape != partial_output.shape[:3]
+        or partial_sum.shape != partial_output.shape[:3]
         or output.shape != query.shape
     ):
         raise RuntimeError("paged split-KV workspace shape does not match the request")
     ops = _ops()
-    if isinstance(k_scale, torch.Tensor) or isinstance(v_scale, torch.Tensor) or semaphores is not None:
+    if isinstance(k_scale, torch.Tensor) or isinstance(v_scale, torch.Tensor) or metadata_stable:
         def as_vec(s):
             if isinstance(s, torch.Tensor):
                 if s.dtype == torch.float32 and s.device == query.device and s.shape == (num_kv_heads,) and s.is_contiguous():
@@ -152,7 +180,8 @@ def l20_paged_split_kv_attention_fp8(
         ops.paged_decode_fp8_e4m3_split_out_v2(
             query, key_cache, value_cache, block_table, seq_lens,
             partial_output, partial_max, partial_sum, output,
-            as_vec(k_scale), as_vec(v_scale), max_seq_len, split_size, semaphores=semaphores,
+            as_vec(k_scale), as_vec(v_scale), max_seq_len, split_size,
+            flags=ops.FLAG_EARLY_METADATA if metadata_stable else 0,
         )
         return output
     return ops.paged_decode_fp8_e4m3_split_out(

@@ -105,7 +105,7 @@ def _cuda_partial(local: PagedDecodeInputs, split_size: int, workspace=None, pac
     ws = workspace or allocate_l20_paged_split_kv_workspace(q, max(local.max_seq_len, 1), split_size=split_size)
     ops.paged_decode_fp8_e4m3_split_out_v2(
         q, local.key_cache, local.value_cache, local.block_table, local.seq_lens, ws[0], ws[1], ws[2], None,
-        local.k_scale, local.v_scale, local.max_seq_len, split_size, packed_output=packed, semaphores=ws[4],
+        local.k_scale, local.v_scale, local.max_seq_len, split_size, packed_output=packed,
     )
     return packed
 

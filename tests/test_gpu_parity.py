@@ -27,29 +27,44 @@ def cabi(built_libs):
     return module
 
 
-def workspace(q, max_seq_len, split_size, dtype=torch.float32, kv_start=0, poison=True, semaphores=True):
-    """(partial_output, partial_max, partial_sum, None, semaphores).  With semaphores (and
-    head_dim 128, f32 partials, flags 0) the library takes its one-kernel balanced path, which
-    needs a split axis of at least 2 (flags 16 forces it for small batches, 0 lets the library
-    choose); flags 8 / 1 select the fixed-split TMA / plain-load paths."""
+PATH_LDG, PATH_TMA, PATH_BALANCED = 1, 2, 3
+
+
+def workspace(q, max_seq_len, split_size, dtype=torch.float32, kv_start=0, poison=True, min_rows=0):
+    """(partial_output, partial_max, partial_sum, None) with one slot per split, or as many as
+    it takes to hold ``min_rows`` rows (the capacity the balanced persistent kernel asks for)."""
     b, hq, d = q.shape
-    s = max(2 if semaphores else 1, -(-(max_seq_len - kv_start) // split_size))
+    s = max(1, -(-(max_seq_len - kv_start) // split_size), -(-min_rows // (b * hq)))
     fill = float("nan") if poison else 0.0
     return (
         torch.full((b, hq, s, d), fill, device=q.device, dtype=dtype),
         torch.full((b, hq, s), fill, device=q.device, dtype=torch.float32),
         torch.full((b, hq, s), fill, device=q.device, dtype=torch.float32),
         None,
-        torch.zeros(b * hq, device=q.device, dtype=torch.int32) if semaphores else None,
     )
+
+
+def expected_path(cabi, q, num_kv_heads, flags, partial_dtype=torch.float32):
+    """Which kernels a call must have launched.  flags 0 / 16: the library's choice, i.e. the
+    balanced persistent kernel for head_dim 128 with at most 8 query heads per kv head and an
+    f32 workspace that is large enough; 8: fixed-split grid with TMA; 1: with plain loads."""
+    _, hq, d = q.shape
+    if flags & 1 or d != 128:
+        return PATH_LDG
+    if flags & (8 | 2) or partial_dtype != torch.float32 or hq // num_kv_heads > 8:
+        return PATH_TMA
+    return PATH_BALANCED
 
 
 def run(cabi, w, split_size, *, flags=0, kv_start=0, partial_dtype=torch.float32, packed=False,
         k_scale=None, v_scale=None, max_seq_len=None):
     """w: PagedDecodeInputs on the GPU. Returns output (and packed partial if asked)."""
     q = w.query
+    hkv = w.key_cache.shape[2]
     msl = w.max_seq_len if max_seq_len is None else max_seq_len
-    ws = workspace(q, msl, split_size, partial_dtype, kv_start)
+    want = expected_path(cabi, q, hkv, flags, partial_dtype)
+    rows = cabi.balanced_workspace_rows(q.shape[1], hkv) if want == PATH_BALANCED else 0
+    ws = workspace(q, msl, split_size, partial_dtype, kv_start, min_rows=rows)
     out = torch.full_like(q, float("nan"))
     pk = torch.full((q.shape[0], q.shape[1], q.shape[2] + 2), float("nan"), device=q.device) if packed else None
     cabi.paged_decode_fp8_e4m3_split_out(
@@ -61,7 +76,7 @@ def run(cabi, w, split_size, *, flags=0, kv_start=0, partial_dtype=torch.float32
     )
     torch.cuda.synchronize()
     assert cabi.device_status() == 0, "a bounded device-side wait gave up"
-    assert int(ws[4].abs().sum()) == 0, "semaphores must be left at zero"
+    assert cabi.last_path() == want, f"flags={flags}: path {cabi.last_path()}, expected {want}"
     return pk if packed else out
 
 
@@ -165,12 +180,15 @@ def test_every_short_context_length(cabi, d, hq, hkv):
     for split in (16, 32, 64, 512):
         for flags in (16, 0, 8, 1, 2):
             out = torch.full_like(q, float("nan"), device=DEV)
-            ws = workspace(q.to(DEV), 70, split)
+            want = expected_path(cabi, q, hkv, flags)
+            rows = cabi.balanced_workspace_rows(hq, hkv) if want == PATH_BALANCED else 0
+            ws = workspace(q.to(DEV), 70, split, min_rows=rows)
             cabi.paged_decode_fp8_e4m3_split_out(
                 q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), lens.to(DEV), k_scale=ks.to(DEV), v_scale=vs.to(DEV),
                 max_seq_len=70, split_size=split, output=out, workspace=ws, flags=flags,
             )
             torch.cuda.synchronize()
+            assert cabi.last_path() == want, f"flags={flags}"
             assert_within_gate(out, exp, f"d={d} hq={hq} hkv={hkv} split={split} flags={flags}")
 
 
@@ -385,7 +403,7 @@ def test_torch_op_reference_signature_and_wrapper_module(built_libs, golden):
         l20_paged_split_kv.l20_paged_split_kv_attention_fp8(
             g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens, k_scale=1.0, v_scale=1.0,
             max_seq_len=w.max_seq_len, split_size=256,
-            workspace=l20_paged_split_kv.allocate_l20_paged_split_kv_workspace(g.query, 16, split_size=256),
+            workspace=l20_paged_split_kv.allocate_l20_paged_split_kv_workspace(g.query[:2], 16, split_size=256),
         )
     with pytest.raises(RuntimeError, match="split_size must be a multiple of 16"):
         l20_paged_decode.paged_decode_fp8_e4m3_split_out(

@@ -111,10 +111,17 @@ def test_workspace_allocator_shapes():
     from single_gpu_inference_lab_b200 import l20_paged_split_kv as m
 
     q = torch.zeros(3, 16, 128, dtype=torch.bfloat16)
-    po, pm, ps, out, sem = m.allocate_l20_paged_split_kv_workspace(q, 4097, split_size=512)
-    assert sem.dtype == torch.int32 and sem.numel() >= 3 * 2 and int(sem.abs().sum()) == 0
-    assert po.shape == (3, 16, 16, 128) and po.dtype == torch.float32  # next_pow2(9) = 16
-    assert pm.shape == ps.shape == (3, 16, 16) and out.shape == q.shape and out.dtype == q.dtype
+    # head_dim 64: the reference shape, S = next_pow2(ceil(4097 / 512)) = 16
+    q64 = torch.zeros(3, 14, 64, dtype=torch.bfloat16)
+    po, pm, ps, out = m.allocate_l20_paged_split_kv_workspace(q64, 4097, split_size=512)
+    assert po.shape == (3, 14, 16, 64) and po.dtype == torch.float32
+    assert pm.shape == ps.shape == (3, 14, 16) and out.shape == q64.shape and out.dtype == q64.dtype
+    # head_dim 128: at least the rows the balanced kernel wants, 2 * (12 * 148 // Hkv) * Hq
+    po, pm, ps, out = m.allocate_l20_paged_split_kv_workspace(q, 4097, split_size=512, num_kv_heads=2)
+    assert po.shape[:2] == (3, 16) and po.shape[3] == 128 and pm.shape == ps.shape == po.shape[:3]
+    assert po.shape[2] == -(-2 * (12 * 148 // 2) * 16 // (3 * 16)) and po.shape[2] >= 16
+    big = torch.zeros(256, 28, 128, dtype=torch.bfloat16)
+    assert m.allocate_l20_paged_split_kv_workspace(big, 8192, split_size=512)[0].shape == (256, 28, 16, 128)
     assert m.choose_split_size(64, 2, 4096) % 64 == 0
     s = m.choose_split_size(4, 8, 131072)  # 32 long segments: one wave of 444 slots
     assert s % 64 == 0 and 8 * 4 * -(-131072 // s) <= 444 < 8 * 4 * -(-131072 // (s - 64))
