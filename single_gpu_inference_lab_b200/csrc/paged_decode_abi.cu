@@ -197,8 +197,11 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
 }
 
 // ---- balanced persistent kernel -------------------------------------------------------------
-constexpr int kChunkStages = 2;
-constexpr int kChunkWarps = 12;  // per CTA, one CTA per SM
+// Eight warps with three 8 KiB stages each keep 192 KiB per SM in flight; measured on B200 this
+// beats twelve warps x two stages (smaller chunks, more pieces to merge) and six x four (the
+// warps no longer keep up with the copies).
+constexpr int kChunkStages = 3;
+constexpr int kChunkWarps = 8;  // per CTA, one CTA per SM
 constexpr int kChunkMaxBatch = 2048;
 constexpr int kChunkPieceCost = 2;  // half page pairs charged for starting a sequence
 
@@ -230,7 +233,7 @@ bool balanced_eligible(const pfd_decode_args& a, const pfd::KernelParams& kp, in
   return rows >= 2LL * (sms * kChunkWarps / a.num_kv_heads) * a.num_q_heads;
 }
 
-template <bool QBF16>
+template <bool QBF16, int kStagesT, int kWarpsT>
 int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int sms, cudaStream_t stream) {
   CUtensorMap mk, mv;
   if (int rc = get_tensor_map(a.key_cache, a.k_stride_page, a.k_stride_token, a.k_stride_head, a.num_pages,
@@ -243,11 +246,11 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
   tp.head_is_dim1 = head_is_dim1(a.k_stride_token, a.k_stride_head) ? 1 : 0;
   if (int rc = status_pointer(&tp.status)) return rc;
   tp.phase_times = g_phase_times;
-  auto kernel = pfd::paged_decode_fp8_chunk_kernel<QBF16, kChunkStages, kChunkWarps>;
-  constexpr int kThreads = kChunkWarps * 32;
+  auto kernel = pfd::paged_decode_fp8_chunk_kernel<QBF16, kStagesT, kWarpsT>;
+  constexpr int kThreads = kWarpsT * 32;
   // ring + mbarriers + scan scratch + prefix[B + 1] + lens[B], sized for the largest batch
-  constexpr int smem = 1024 + kChunkWarps * kChunkStages * 8192 + kChunkWarps * kChunkStages * 8 +
-                       kChunkWarps * 4 + (2 * kChunkMaxBatch + 1) * 4 + 16;
+  constexpr int smem = 1024 + kWarpsT * kStagesT * 8192 + kWarpsT * kStagesT * 8 +
+                       kWarpsT * 4 + (2 * kChunkMaxBatch + 1) * 4 + 16;
   int dev = 0;
   cudaGetDevice(&dev);
   static bool configured[kMaxDevices][2] = {};
@@ -261,7 +264,7 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
   }
   pfd::ChunkParams cp{};
   cp.batch = a.batch;
-  cp.num_warps = sms * kChunkWarps;
+  cp.num_warps = sms * kWarpsT;
   cp.piece_cost = kChunkPieceCost;
   if (const char* env = getenv("PFD_PIECE_COST")) cp.piece_cost = std::max(0, std::min(atoi(env), 64));  // tuning aid
   cudaLaunchAttribute attr[1];
@@ -282,15 +285,19 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
   g_last_path = PFD_PATH_BALANCED;
   if (a.flags & PFD_FLAG_PARTIAL_ONLY) return PFD_OK;
   {
+    // Few rows mean few, long sequences whose pieces are many: four warps then share a row.
     const int rows = a.batch * a.num_q_heads;
+    const bool wide = rows <= 4 * sms;
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((rows + 3) / 4);
+    cfg.gridDim = dim3(wide ? rows : (rows + 3) / 4);
     cfg.blockDim = dim3(128);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, pfd::paged_decode_chunk_merge_kernel<QBF16>, kp, tp, cp);
+    const cudaError_t e =
+        wide ? cudaLaunchKernelEx(&cfg, pfd::paged_decode_chunk_merge_kernel<QBF16, 4>, kp, tp, cp)
+             : cudaLaunchKernelEx(&cfg, pfd::paged_decode_chunk_merge_kernel<QBF16, 1>, kp, tp, cp);
     if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "balanced merge kernel launch failed: %s", cudaGetErrorString(e));
   }
   return check_launch("balanced merge kernel");
@@ -303,7 +310,7 @@ int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     if (int rc = sm_count_of(dev, &sms)) return rc;
-    if (balanced_eligible(a, kp, sms)) return launch_balanced<QBF16>(a, kp, sms, stream);
+    if (balanced_eligible(a, kp, sms)) return launch_balanced<QBF16, kChunkStages, kChunkWarps>(a, kp, sms, stream);
   }
   const dim3 grid(num_splits, a.num_kv_heads, a.batch);
   if (D == 128 && tma_eligible(a)) {
@@ -428,7 +435,6 @@ int decode_impl(const pfd_decode_args* args, int slot_offset) {
   kp.slot_offset = slot_offset;
   kp.early_metadata = (a.flags & PFD_FLAG_EARLY_METADATA) ? 1 : 0;
   kp.kv_evict_first = 1;
-  if (const char* env = getenv("PFD_KV_EVICT_FIRST")) kp.kv_evict_first = atoi(env) != 0;  // tuning aid
 
   const bool bf16 = a.query_dtype == PFD_DTYPE_BF16;
   if (a.head_dim == 128)

@@ -1,7 +1,7 @@
 // Balanced, persistent form of the split-KV decode step for head_dim 128 (sm_100a).
 //
 // Instead of a grid of fixed (sequence, kv head, split) work items, a fixed number of warps
-// (twelve per SM) share the flattened list of page pairs of all sequences: the warps form
+// (eight per SM) share the flattened list of page pairs of all sequences: the warps form
 // groups of one warp per kv head, and every group takes an equal contiguous chunk of the list,
 // so every warp streams the same number of KV bytes whatever the mix of context lengths, and
 // no CTA is launched for a split that does not exist.  The warps of a group read the same pages
@@ -553,18 +553,22 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
   }
 }
 
-// LSE merge of the pieces the chunk kernel left in the workspace; one warp per (sequence, q head)
-// row.  A row whose segment lay inside one chunk has been written already.  Same maths as
-// _paged_split_kv_reduce (integrations/vllm/l20_paged_split_kv.py:459-488).
-template <bool QBF16>
+// LSE merge of the pieces the chunk kernel left in the workspace.  WPR = 1: one warp per
+// (sequence, q head) row, four rows per CTA; WPR = 4: the four warps of a CTA share one row,
+// warp w taking pieces w, w + 4, ..., and combine through shared memory.  A row whose sequence
+// lay inside one chunk has been written already.  Same maths as _paged_split_kv_reduce
+// (integrations/vllm/l20_paged_split_kv.py:459-488).
+template <bool QBF16, int WPR>
 __global__ void __launch_bounds__(128)
 paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const ChunkParams cp) {
   constexpr int D = 128, E = 4;
+  static_assert(WPR == 1 || WPR == 4, "one or four warps per row");
   pdl_launch_dependents();
   mark_phase_at(tp, blockIdx.x, 5, threadIdx.x == 0);  // merge CTA resident
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= cp.batch * p.num_q_heads) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = WPR == 1 ? blockIdx.x * 4 + warp : blockIdx.x;
+  const int part = WPR == 1 ? 0 : warp;
+  if (row >= cp.batch * p.num_q_heads) return;  // WPR == 1 only: whole warps, no barrier below
   const int b = row / p.num_q_heads, hq = row % p.num_q_heads;
   const int page_first = p.kv_start / kPage;
   // seq_lens is an input of the whole step, not a result of the chunk kernel: the chunking is
@@ -585,19 +589,20 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
   const int s0 = chunks.first_unit(below, b);
   const int w_first = np > 0 ? chunks.chunk_of(s0) : 0;
   const int ns = np > 0 ? chunks.chunk_of(s0 + 2 * (np - 1)) - w_first + 1 : 0;
-  if (ns == 1) return;  // written by the chunk kernel
+  if (ns == 1) return;  // written by the chunk kernel (the whole CTA returns: one row per CTA if WPR == 4)
   float acc[E] = {0.f, 0.f, 0.f, 0.f};
   float big = -INFINITY, den = 0.f;
   pdl_wait();  // the chunk kernel's stores are complete and visible from here on
   mark_phase_at(tp, blockIdx.x, 6, threadIdx.x == 0);  // chunk kernel complete
-  constexpr int kBatch = 16;  // pieces requested per round trip
-  for (int k0 = 0; k0 < ns; k0 += kBatch) {
+  constexpr int kBatch = WPR == 1 ? 16 : 8;  // pieces requested per round trip
+  for (int k0 = part; k0 < ns; k0 += kBatch * WPR) {
     float mv[kBatch], lv[kBatch];
     float4 xv[kBatch];
 #pragma unroll
     for (int u = 0; u < kBatch; ++u) {
-      const bool on = k0 + u < ns;
-      const int w = w_first + (on ? k0 + u : 0);
+      const int k = k0 + u * WPR;
+      const bool on = k < ns;
+      const int w = w_first + (on ? k : 0);
       const int64_t r = chunk_slot_row(w, s0 > chunks.start_of(w) ? 1 : 0, p.num_q_heads, hq);
       mv[u] = on ? p.partial_max[r] : -INFINITY;
       lv[u] = on ? p.partial_sum[r] : 0.f;
@@ -617,6 +622,26 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
       acc[0] += c * xv[u].x; acc[1] += c * xv[u].y; acc[2] += c * xv[u].z; acc[3] += c * xv[u].w;
     }
     big = m_new;
+  }
+  if constexpr (WPR == 4) {
+    // combine the four warps' (acc, big, den) of this row; warp 0 finishes
+    __shared__ __align__(16) float sh_acc[4][D];
+    __shared__ float sh_m[4], sh_l[4];
+    *reinterpret_cast<float4*>(&sh_acc[warp][lane * E]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    if (lane == 0) { sh_m[warp] = big; sh_l[warp] = den; }
+    __syncthreads();
+    if (warp != 0) return;
+    float m_all = fmaxf(fmaxf(sh_m[0], sh_m[1]), fmaxf(sh_m[2], sh_m[3]));
+    den = 0.f;
+    acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float c = (sh_m[w] == -INFINITY) ? 0.f : expf(sh_m[w] - m_all);
+      const float4 x = *reinterpret_cast<const float4*>(&sh_acc[w][lane * E]);
+      den += sh_l[w] * c;
+      acc[0] += c * x.x; acc[1] += c * x.y; acc[2] += c * x.z; acc[3] += c * x.w;
+    }
+    big = m_all;
   }
   if (p.packed_output != nullptr) {
     float* dst = p.packed_output + (int64_t)row * (D + 2);

@@ -37,15 +37,15 @@ def _ops():
     return l20_paged_decode
 
 
-BALANCED_WARPS_PER_SM = 12  # warps of the balanced persistent kernel on every SM
+BALANCED_WARPS_PER_SM = 8  # warps of the balanced persistent kernel on every SM
 BALANCED_MAX_GROUP = 8      # query heads per kv head it handles
 
 
 def balanced_workspace_splits(query: torch.Tensor, num_kv_heads: int | None = None) -> int:
     """Smallest split axis ``S`` with which a ``[B, Hq, S]`` workspace can hold the pieces of the
     balanced persistent kernel: two slots of ``Hq`` rows for every group of ``Hkv`` warps, i.e.
-    ``2 * (12 * SMs // Hkv) * Hq`` rows (``pfd_balanced_workspace_rows``).  Without
-    ``num_kv_heads`` the bound for the largest supported GQA ratio is used (about 15 MB of fp32
+    ``2 * (8 * SMs // Hkv) * Hq`` rows (``pfd_balanced_workspace_rows``).  Without
+    ``num_kv_heads`` the bound for the largest supported GQA ratio is used (about 10 MB of fp32
     rows on a 148-SM part, whatever the batch)."""
     batch, num_q_heads, _ = query.shape
     sms = torch.cuda.get_device_properties(query.device).multi_processor_count if query.is_cuda else 148

@@ -116,10 +116,10 @@ def test_workspace_allocator_shapes():
     po, pm, ps, out = m.allocate_l20_paged_split_kv_workspace(q64, 4097, split_size=512)
     assert po.shape == (3, 14, 16, 64) and po.dtype == torch.float32
     assert pm.shape == ps.shape == (3, 14, 16) and out.shape == q64.shape and out.dtype == q64.dtype
-    # head_dim 128: at least the rows the balanced kernel wants, 2 * (12 * 148 // Hkv) * Hq
+    # head_dim 128: at least the rows the balanced kernel wants, 2 * (8 * 148 // Hkv) * Hq
     po, pm, ps, out = m.allocate_l20_paged_split_kv_workspace(q, 4097, split_size=512, num_kv_heads=2)
     assert po.shape[:2] == (3, 16) and po.shape[3] == 128 and pm.shape == ps.shape == po.shape[:3]
-    assert po.shape[2] == -(-2 * (12 * 148 // 2) * 16 // (3 * 16)) and po.shape[2] >= 16
+    assert po.shape[2] == -(-2 * (8 * 148 // 2) * 16 // (3 * 16)) and po.shape[2] >= 16
     big = torch.zeros(256, 28, 128, dtype=torch.bfloat16)
     assert m.allocate_l20_paged_split_kv_workspace(big, 8192, split_size=512)[0].shape == (256, 28, 16, 128)
     assert m.choose_split_size(64, 2, 4096) % 64 == 0
