@@ -22,6 +22,8 @@
 // movmatrix per 8 tokens.
 #pragma once
 
+#include <type_traits>
+
 #include "paged_decode_kernels.cuh"
 
 namespace pfd {
@@ -555,11 +557,13 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
 
 // LSE merge of the pieces the chunk kernel left in the workspace.  WPR = 1: one warp per
 // (sequence, q head) row, four rows per CTA; WPR = 4: the four warps of a CTA share one row,
-// warp w taking pieces w, w + 4, ..., and combine through shared memory.  A row whose sequence
-// lay inside one chunk has been written already.  Same maths as _paged_split_kv_reduce
+// warp w taking pieces w, w + 4, ..., and combine through shared memory.  KB pieces are
+// requested per round trip (rows with at most four pieces take a shorter code path); MINB is
+// the CTAs per SM the register budget is held to.  A row whose sequence lay inside one chunk
+// has been written already.  Same maths as _paged_split_kv_reduce
 // (integrations/vllm/l20_paged_split_kv.py:459-488).
-template <bool QBF16, int WPR>
-__global__ void __launch_bounds__(128)
+template <bool QBF16, int WPR, int KB, int MINB>
+__global__ void __launch_bounds__(128, MINB)
 paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const ChunkParams cp) {
   constexpr int D = 128, E = 4;
   static_assert(WPR == 1 || WPR == 4, "one or four warps per row");
@@ -592,14 +596,13 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
   if (ns == 1) return;  // written by the chunk kernel (the whole CTA returns: one row per CTA if WPR == 4)
   float acc[E] = {0.f, 0.f, 0.f, 0.f};
   float big = -INFINITY, den = 0.f;
-  pdl_wait();  // the chunk kernel's stores are complete and visible from here on
-  mark_phase_at(tp, blockIdx.x, 6, threadIdx.x == 0);  // chunk kernel complete
-  constexpr int kBatch = WPR == 1 ? 16 : 8;  // pieces requested per round trip
-  for (int k0 = part; k0 < ns; k0 += kBatch * WPR) {
-    float mv[kBatch], lv[kBatch];
-    float4 xv[kBatch];
+  // pieces k0, k0 + WPR, ... (K of them) in one round trip, folded into (acc, big, den)
+  auto round = [&](auto kc, int k0) {
+    constexpr int K = decltype(kc)::value;
+    float mv[K], lv[K];
+    float4 xv[K];
 #pragma unroll
-    for (int u = 0; u < kBatch; ++u) {
+    for (int u = 0; u < K; ++u) {
       const int k = k0 + u * WPR;
       const bool on = k < ns;
       const int w = w_first + (on ? k : 0);
@@ -610,18 +613,25 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
     }
     float m_new = big;
 #pragma unroll
-    for (int u = 0; u < kBatch; ++u) m_new = fmaxf(m_new, mv[u]);
+    for (int u = 0; u < K; ++u) m_new = fmaxf(m_new, mv[u]);
     const float keep = (big == -INFINITY) ? 0.f : expf(big - m_new);
     den *= keep;
 #pragma unroll
     for (int e = 0; e < E; ++e) acc[e] *= keep;
 #pragma unroll
-    for (int u = 0; u < kBatch; ++u) {
+    for (int u = 0; u < K; ++u) {
       const float c = (mv[u] == -INFINITY) ? 0.f : expf(mv[u] - m_new);
       den += lv[u] * c;
       acc[0] += c * xv[u].x; acc[1] += c * xv[u].y; acc[2] += c * xv[u].z; acc[3] += c * xv[u].w;
     }
     big = m_new;
+  };
+  pdl_wait();  // the chunk kernel's stores are complete and visible from here on
+  mark_phase_at(tp, blockIdx.x, 6, threadIdx.x == 0);  // chunk kernel complete
+  if (WPR == 1 && ns <= 4) {
+    if (ns > 0) round(std::integral_constant<int, 4>{}, 0);
+  } else {
+    for (int k0 = part; k0 < ns; k0 += KB * WPR) round(std::integral_constant<int, KB>{}, k0);
   }
   if constexpr (WPR == 4) {
     // combine the four warps' (acc, big, den) of this row; warp 0 finishes
