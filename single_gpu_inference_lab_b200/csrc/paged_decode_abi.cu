@@ -285,11 +285,10 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
   g_last_path = PFD_PATH_BALANCED;
   if (a.flags & PFD_FLAG_PARTIAL_ONLY) return PFD_OK;
   {
-    // Few rows mean few, long sequences whose pieces are many: four warps then share a row.
-    // Many rows: a smaller register budget so that the grid needs fewer waves.
+    // Few rows mean few, long sequences whose pieces are many: four warps then share a row,
+    // which also puts more loads in flight per SM.  Either way 64 registers, 8 CTAs per SM.
     const int rows = a.batch * a.num_q_heads;
-    const bool wide = rows <= 4 * sms;
-    const bool deep = !wide && rows <= 16 * sms;
+    const bool wide = rows <= 8 * sms;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(wide ? rows : (rows + 3) / 4);
     cfg.blockDim = dim3(128);
@@ -298,9 +297,8 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const cudaError_t e =
-        wide   ? cudaLaunchKernelEx(&cfg, pfd::paged_decode_chunk_merge_kernel<QBF16, 4, 8, 4>, kp, tp, cp)
-        : deep ? cudaLaunchKernelEx(&cfg, pfd::paged_decode_chunk_merge_kernel<QBF16, 1, 16, 4>, kp, tp, cp)
-               : cudaLaunchKernelEx(&cfg, pfd::paged_decode_chunk_merge_kernel<QBF16, 1, 8, 8>, kp, tp, cp);
+        wide ? cudaLaunchKernelEx(&cfg, pfd::paged_decode_chunk_merge_kernel<QBF16, 4, 4, 8>, kp, tp, cp)
+             : cudaLaunchKernelEx(&cfg, pfd::paged_decode_chunk_merge_kernel<QBF16, 1, 8, 8>, kp, tp, cp);
     if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "balanced merge kernel launch failed: %s", cudaGetErrorString(e));
   }
   return check_launch("balanced merge kernel");
