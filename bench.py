@@ -45,8 +45,9 @@ L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
 # captures summarised under profiles/ (the bench's own seed-0 workloads, full size).
 NCU_TRAFFIC_BYTES_PER_LAUNCH = {
-    ("qwen2.5-coder-3b-b64", 2): 80_438_016 + 3_118_592,   # partial_tma kernel
-    ("qwen2.5-7b-b256", 3): 226_127_104 + 9_285_888,       # balanced kernel
+    ("qwen2.5-coder-3b-b64", 3): 80_427_520 + 3_423_488,   # chunk kernel (mean of two launches)
+    ("qwen2.5-7b-b256", 3): 224_103_040 + 7_126_144,       # chunk kernel
+    ("qwen2.5-coder-3b-b64", 2): 80_438_016 + 3_118_592,   # fixed-split TMA kernel (--flags 40)
 }
 
 DEFAULT_WORKLOAD = "qwen2.5-coder-3b-b64"
