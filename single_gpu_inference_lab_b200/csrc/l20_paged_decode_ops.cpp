@@ -5,8 +5,8 @@
 //       integrations/vllm/cuda/l20_paged_decode.cpp:128-135 (schema), :138-143 (CUDA impl),
 //       :153-155 (pybind export of the same launcher)
 // and adds "paged_decode_fp8_e4m3_split_out_v2" (per-kv-head scale tensors, explicit softmax
-// scale, kv_start, optional packed (o, m, l) output, optional semaphores for the one-kernel path) plus "merge_packed_partials" and
-// "resolve_slots".  Every op only unpacks tensors into the C ABI of libpaged_fp8_decode.so
+// scale, kv_start, optional packed (o, m, l) output, PFD_FLAG_* bits; the semaphores operand is
+// accepted and unused) plus "merge_packed_partials" and "resolve_slots".  Every op only unpacks tensors into the C ABI of libpaged_fp8_decode.so
 // (include/paged_fp8_decode.h); there is no computation here and no fallback.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
