@@ -3,8 +3,8 @@
 
 Runs the reference project's OWN torch implementation of the path --
 ``reference()`` and ``quantize_fp8_e4m3()`` of
-``scripts/smoke_cuda_paged_fp8_decode_op.py`` (:13-41), imported from its source tree
-(default ``/root/reference``, override with ``--reference-root``) -- on seeded CPU inputs and
+``scripts/smoke_cuda_paged_fp8_decode_op.py`` (:13-41), imported from a checkout of that
+project (``--reference-root``, or the ``REFERENCE_ROOT`` environment variable) -- on seeded CPU inputs and
 stores inputs digests + outputs in ``tests/golden/paged_decode_golden.pt``.
 
 The reference function hard-codes ``device="cuda"`` in one ``torch.arange`` call (:29); the
@@ -12,12 +12,13 @@ only change made here is to strip that keyword while the function runs, so every
 on the CPU.  Nothing of this file or of the reference tree is needed at test time: the
 fixtures travel, the reference does not.
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py --reference-root <checkout of single-gpu-inference-lab>
 """
 
 from __future__ import annotations
 
 import argparse
+import os
 import contextlib
 import hashlib
 import importlib.util
@@ -95,7 +96,7 @@ def smoke_recipe(ref, batch: int, context: int, q_heads: int, kv_heads: int):
 
 def main() -> int:
     parser = argparse.ArgumentParser()
-    parser.add_argument("--reference-root", default="/root/reference")
+    parser.add_argument("--reference-root", default=os.environ.get("REFERENCE_ROOT"), required="REFERENCE_ROOT" not in os.environ)
     args = parser.parse_args()
     ref = load_reference(Path(args.reference_root))
     golden: dict = {"torch": torch.__version__, "cases": {}, "smoke": {}}
