@@ -62,6 +62,9 @@ def parse_args():
     p.add_argument("--workload", default=DEFAULT_WORKLOAD)
     p.add_argument("--split-size", type=int, default=0, help="0 = choose from the geometry")
     p.add_argument("--pools", type=int, default=0, help="distinct KV pools rotated through (0 = enough to exceed L2 x3)")
+    p.add_argument("--kv-dtype", choices=["fp8", "bf16", "fp16"], default="fp8",
+                   help="fp8: the e4m3 path (headline); bf16 / fp16: the non-quantised sibling operator, "
+                        "caches and query in that type (single GPU, batch-sharded or weak scaling only)")
     p.add_argument("--flags", type=int, default=32,
                    help="PFD_FLAG_* bits of the timed calls; default PFD_FLAG_EARLY_METADATA: the block table "
                         "and sequence lengths do not change between the timed layer-steps")
@@ -155,11 +158,14 @@ def cpu_reference_run(w, sample_rows: int, repeats: int):
     sub = sharding.compact_rows(w, rows.to(w.query.device), 0, w.block_table.shape[1], w.seq_lens.cpu()[rows]).to("cpu")
     table = sub.block_table.long()
     hkv, d = sub.key_cache.shape[2], sub.key_cache.shape[3]
-    nbytes = int(sub.seq_lens.sum()) * hkv * d * 2
+    nbytes = int(sub.seq_lens.sum()) * hkv * d * 2 * sub.key_cache.element_size()
     best = float("inf")
     for attempt in range(repeats + 1):  # the first pass is the warm-up
         t0 = time.perf_counter()
-        oracle.reference(sub.query, sub.key_cache, sub.value_cache, table, sub.seq_lens, sub.k_scale, sub.v_scale)
+        if sub.key_cache.dtype == torch.float8_e4m3fn:
+            oracle.reference(sub.query, sub.key_cache, sub.value_cache, table, sub.seq_lens, sub.k_scale, sub.v_scale)
+        else:
+            oracle.reference_kv16(sub.query, sub.key_cache, sub.value_cache, table, sub.seq_lens)
         dt = time.perf_counter() - t0
         if attempt > 0 or repeats == 0:
             best = min(best, dt)
@@ -229,7 +235,9 @@ def main() -> int:
         dist.init_process_group("nccl", device_id=dev)
     cabi.load()
 
-    kv_range_mode = args.workload == "llama3-8b-long-b4"
+    kv16 = {"fp8": None, "bf16": torch.bfloat16, "fp16": torch.float16}[args.kv_dtype]
+    gen_kw = {} if kv16 is None else {"kv_dtype": kv16, "query_dtype": kv16}
+    kv_range_mode = args.workload == "llama3-8b-long-b4" and kv16 is None
     # -------- inputs: every rank builds its own batch directly on its GPU
     if kv_range_mode:
         full_len = 131072
@@ -237,13 +245,13 @@ def main() -> int:
         w = make_inputs(args.workload, seed=rank, device=dev, shrink=(hi - lo) / full_len)
         scaling = "strong"
     elif args.strong and world > 1:
-        full = make_inputs(args.workload, seed=0, device=dev)  # same batch on every rank
+        full = make_inputs(args.workload, seed=0, device=dev, **gen_kw)  # same batch on every rank
         w, _rows = sharding.shard_sequences(full, rank, world)
         del full
         torch.cuda.empty_cache()
         scaling = "strong"
     else:
-        w = make_inputs(args.workload, seed=rank, device=dev)
+        w = make_inputs(args.workload, seed=rank, device=dev, **gen_kw)
         scaling = "weak"
     q = w.query
     batch, hq, d = q.shape
@@ -256,7 +264,7 @@ def main() -> int:
     pools = min(pools, max(2, int(40e9 // pool_bytes)))
     kcs = [w.key_cache] + [w.key_cache.clone() for _ in range(pools - 1)]
     vcs = [w.value_cache] + [w.value_cache.clone() for _ in range(pools - 1)]
-    shared_prefix = w.prefix_len > 0 and not args.no_shared_prefix and d == 128
+    shared_prefix = w.prefix_len > 0 and not args.no_shared_prefix and d == 128 and kv16 is None
     if shared_prefix and not args.split_size:
         split = 512
     ws = l20_paged_split_kv.allocate_l20_paged_split_kv_workspace(q, w.max_seq_len, split_size=split)
@@ -269,6 +277,11 @@ def main() -> int:
     gathered = torch.empty(world, batch, hq, d + 2, device=dev) if kv_range_mode else None
 
     def step(i: int, flags: int = args.flags):
+        if kv16 is not None:
+            cabi.paged_decode_kv16_split_out(
+                q, kcs[i % pools], vcs[i % pools], w.block_table, w.seq_lens, max_seq_len=w.max_seq_len,
+                split_size=split, output=out, workspace=ws, flags=flags)
+            return
         if shared_prefix:
             cabi.shared_prefix_decode_fp8_e4m3(
                 q, kcs[i % pools], vcs[i % pools], w.block_table, w.seq_lens, prefix_len=w.prefix_len,
@@ -343,20 +356,31 @@ def main() -> int:
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
-    # -------- e2e operands: pinned host copies of the per-step inputs
-    host_q = q.cpu().pin_memory()
-    host_table = w.block_table.cpu().pin_memory()
-    host_lens = w.seq_lens.cpu().pin_memory()
-    host_out = torch.empty_like(host_q).pin_memory()
-    dq, dtable, dlens = torch.empty_like(q), torch.empty_like(w.block_table), torch.empty_like(w.seq_lens)
-    h2d = host_q.numel() * host_q.element_size() + host_table.numel() * 4 + host_lens.numel() * 4
+    # -------- e2e operands: the per-step inputs (q, block table, lengths) packed into ONE pinned host
+    # buffer and copied with one transfer into a device buffer the operands are views of
+    def aligned(n: int) -> int:
+        return (n + 255) // 256 * 256
+
+    q_bytes, t_bytes, l_bytes = q.numel() * q.element_size(), w.block_table.numel() * 4, w.seq_lens.numel() * 4
+    off_t, off_l = aligned(q_bytes), aligned(q_bytes) + aligned(t_bytes)
+    host_in = torch.empty(off_l + aligned(l_bytes), dtype=torch.uint8).pin_memory()
+    dev_in = torch.empty_like(host_in, device=dev)
+
+    def views(buf):
+        return (buf[:q_bytes].view(q.dtype).view(q.shape),
+                buf[off_t:off_t + t_bytes].view(torch.int32).view(w.block_table.shape),
+                buf[off_l:off_l + l_bytes].view(torch.int32).view(w.seq_lens.shape))
+
+    hq_v, ht_v, hl_v = views(host_in)
+    hq_v.copy_(q.cpu()); ht_v.copy_(w.block_table.cpu()); hl_v.copy_(w.seq_lens.cpu())
+    dq, dtable, dlens = views(dev_in)
+    host_out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    h2d = q_bytes + t_bytes + l_bytes
     d2h = host_out.numel() * host_out.element_size()
     stream = torch.cuda.current_stream()
 
     def e2e_step(i: int):
-        dq.copy_(host_q, non_blocking=True)
-        dtable.copy_(host_table, non_blocking=True)
-        dlens.copy_(host_lens, non_blocking=True)
+        dev_in.copy_(host_in, non_blocking=True)
         if kv_range_mode:
             local = w.__class__(**{**w.__dict__, "query": dq, "block_table": dtable, "seq_lens": dlens,
                                    "key_cache": kcs[i % pools], "value_cache": vcs[i % pools]})
@@ -366,6 +390,10 @@ def main() -> int:
                 res = l20_paged_split_kv.l20_paged_split_kv_attention_fp8(
                     dq, kcs[i % pools], vcs[i % pools], dtable, dlens, k_scale=w.k_scale, v_scale=w.v_scale,
                     max_seq_len=w.max_seq_len, split_size=split, workspace=ws)
+        elif kv16 is not None:
+            res = l20_paged_split_kv.l20_paged_split_kv_attention(
+                dq, kcs[i % pools], vcs[i % pools], dtable, dlens, split_size=split, workspace=ws,
+                max_seq_len=w.max_seq_len)
         elif shared_prefix:
             res = spd.shared_paged_prefix_paged_suffix_gqa_decode_attention_fp8(
                 dq, kcs[i % pools], vcs[i % pools], dtable, dlens, w.prefix_len, k_scale=w.k_scale, v_scale=w.v_scale,
@@ -391,7 +419,7 @@ def main() -> int:
         path = cabi.last_path()
         fused = ((not kv_range_mode) and per_step == 1) or shared_prefix  # no single dominant kernel to time apart
         kernel_name = {1: "paged_decode_fp8_partial_ldg_kernel", 2: "paged_decode_fp8_partial_tma_kernel",
-                       3: "paged_decode_fp8_chunk_kernel"}.get(path, "?")
+                       3: "paged_decode_fp8_chunk_kernel", 4: "paged_decode_fp8_chunk_kernel<KV16>"}.get(path, "?")
         if shared_prefix:
             kernel_name = "shared_prefix_dense_kernel + paged_decode_fp8_partial_tma_kernel + paged_decode_merge_kernel"
         ms_kernel = timed_graph(step if fused else (lambda i: step(i, args.flags | cabi.PFD_FLAG_PARTIAL_ONLY)), args.steps)
@@ -424,7 +452,8 @@ def main() -> int:
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": round(ms_step, 6), "us_per_layer_step": round(ms_step * 1e3, 3),
             "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-            "dtype": "fp8_e4m3 KV, bf16 q, fp32 accumulate", "data": "synthetic",
+            "dtype": ("fp8_e4m3 KV, bf16 q, fp32 accumulate" if kv16 is None
+                      else f"{args.kv_dtype} KV and q, fp32 accumulate"), "data": "synthetic",
             "config": {
                 "workload": args.workload, "batch_per_gpu": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
                 "page_size": 16, "split_size": split, "max_seq_len": w.max_seq_len, "path": cabi.PATH_NAMES.get(path, "?"),

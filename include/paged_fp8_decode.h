@@ -131,6 +131,19 @@ typedef struct pfd_decode_args {
 int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args);
 
 /*
+ * The non-quantised sibling: one decode-attention layer-step over K/V caches stored in the
+ * query's own 16-bit type (fp16 or bf16), head_dim 128, at most 8 query heads per KV head.
+ * Replaces l20_paged_decode_split_out_cuda (integrations/vllm/cuda/l20_paged_decode.cu:549-600;
+ * op schema l20_paged_decode.cpp:121-127).  Same struct; k_stride_* / v_stride_* count
+ * elements of the cache type, k_scale / v_scale and the per-head scale pointers are ignored.
+ * It always runs the balanced persistent kernel.  The workspace (f32, f16 or bf16 partials,
+ * dense [batch, num_q_heads, workspace_splits]) is used as a flat list of rows; any workspace of
+ * at least 2 * num_q_heads rows works, one of pfd_balanced_workspace_rows() rows or more lets
+ * every SM take part.
+ */
+int pfd_paged_decode_kv16_split_out(const pfd_decode_args* args);
+
+/*
  * Rows of (o, m, l) the workspace must hold for PFD_FLAG_BALANCED on the current device:
  * batch * num_q_heads * workspace_splits >= this.  The balanced kernel gives every group of
  * num_kv_heads warps two slots of num_q_heads rows.  Negative on error.  No counterpart in the
@@ -213,7 +226,8 @@ int pfd_device_status(int32_t* status);
 /* Which kernels the calling thread's last decode call launched. */
 #define PFD_PATH_FIXED_LDG 1 /* fixed-split grid, plain 16-byte loads, + merge kernel */
 #define PFD_PATH_FIXED_TMA 2 /* fixed-split grid, TMA pipeline, + merge kernel         */
-#define PFD_PATH_BALANCED 3  /* one persistent balanced kernel                         */
+#define PFD_PATH_BALANCED 3  /* balanced persistent kernel + its merge kernel            */
+#define PFD_PATH_BALANCED_KV16 4 /* the same for 16-bit caches (pfd_paged_decode_kv16_split_out) */
 int pfd_last_path(void);
 
 /*

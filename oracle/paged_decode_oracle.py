@@ -134,6 +134,30 @@ def reference(query, key_cache, value_cache, table, seq_lens, k_scale, v_scale, 
     ).to(query.dtype)
 
 
+def reference_kv16(query, key_cache, value_cache, table, seq_lens, *, kv_start: int = 0) -> torch.Tensor:
+    """The non-quantised sibling: restatement of ``reference()`` of
+    scripts/smoke_cuda_paged_decode_op.py:13-30 (caches in the query's fp16 / bf16 type, no
+    scales): per sequence gather ``table[b, t // 16]``, ``t % 16``; fp32 einsum / softmax /
+    einsum; cast to the query dtype."""
+    scale = query.shape[-1] ** -0.5
+    outputs = []
+    for batch in range(query.shape[0]):
+        length = int(seq_lens[batch])
+        token = torch.arange(kv_start, length, device=query.device)
+        physical = table[batch, token // PAGE_SIZE]
+        offsets = token % PAGE_SIZE
+        keys = key_cache[physical, offsets]
+        values = value_cache[physical, offsets]
+        kv_heads = keys.shape[1]
+        group = query.shape[1] // kv_heads
+        keys = keys.repeat_interleave(group, dim=1)
+        values = values.repeat_interleave(group, dim=1)
+        scores = torch.einsum("hd,thd->ht", query[batch].float(), keys.float()) * scale
+        probs = scores.softmax(dim=-1)
+        outputs.append(torch.einsum("ht,thd->hd", probs, values.float()))
+    return torch.stack(outputs).to(query.dtype)
+
+
 def split_partials(
     query: torch.Tensor,
     key_cache: torch.Tensor,

@@ -25,6 +25,7 @@ PFD_FLAG_EARLY_METADATA = 32
 EXPORTS = (
     "pfd_paged_decode_fp8_e4m3_split_out",
     "pfd_paged_decode_fp8_e4m3_split_out_noalloc",
+    "pfd_paged_decode_kv16_split_out",
     "pfd_shared_prefix_decode_fp8_e4m3",
     "pfd_merge_packed",
     "pfd_resolve_slots",
@@ -195,6 +196,18 @@ def paged_decode_fp8_e4m3_split_out(query, key_cache, value_cache, block_table, 
         _check(load().pfd_paged_decode_fp8_e4m3_split_out(C.byref(args)))
 
 
+def paged_decode_kv16_split_out(query, key_cache, value_cache, block_table, seq_lens, **kw) -> None:
+    """One layer-step over fp16 / bf16 caches (the query's dtype) through
+    ``pfd_paged_decode_kv16_split_out``; same keywords as above, the scales are ignored."""
+    if key_cache.dtype != query.dtype or value_cache.dtype != query.dtype:
+        raise RuntimeError("K/V cache must have the query's dtype")
+    kw.setdefault("k_scale", 1.0)
+    kw.setdefault("v_scale", 1.0)
+    args = decode_args(query, key_cache, value_cache, block_table, seq_lens, **kw)
+    with torch.cuda.device(query.device):
+        _check(load().pfd_paged_decode_kv16_split_out(C.byref(args)))
+
+
 def shared_prefix_decode_fp8_e4m3(query, key_cache, value_cache, block_table, seq_lens, *, prefix_len, **kw) -> None:
     """One layer-step through ``pfd_shared_prefix_decode_fp8_e4m3``: dense tcgen05 pass over the
     prefix every request shares, split-KV pass over the private suffixes, one merge."""
@@ -246,7 +259,7 @@ def device_status() -> int:
     return int(value.value)
 
 
-PATH_NAMES = {0: "none", 1: "fixed-split grid (plain loads) + merge", 2: "fixed-split grid (TMA) + merge", 3: "balanced persistent kernel + merge"}
+PATH_NAMES = {0: "none", 1: "fixed-split grid (plain loads) + merge", 2: "fixed-split grid (TMA) + merge", 3: "balanced persistent kernel + merge", 4: "balanced persistent kernel (16-bit caches) + merge"}
 
 
 def balanced_workspace_rows(num_q_heads: int, num_kv_heads: int) -> int:

@@ -34,13 +34,18 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
                 const c10::optional<at::Tensor>& k_scale_ph, const c10::optional<at::Tensor>& v_scale_ph,
                 double sm_scale, int64_t max_seq_len, int64_t split_size, int64_t kv_start,
                 int64_t flags, const c10::optional<at::Tensor>& semaphores = c10::nullopt,
-                int64_t prefix_len = 0) {
+                int64_t prefix_len = 0, bool kv16 = false) {
   TORCH_CHECK(query.is_cuda(), "query must be CUDA");
   TORCH_CHECK(query.scalar_type() == at::kHalf || query.scalar_type() == at::kBFloat16,
               "query must be FP16 or BF16");
-  TORCH_CHECK(key_cache.scalar_type() == at::kFloat8_e4m3fn &&
-                  value_cache.scalar_type() == at::kFloat8_e4m3fn,
-              "K/V cache must be torch.float8_e4m3fn");
+  if (kv16) {
+    TORCH_CHECK(key_cache.scalar_type() == query.scalar_type() && value_cache.scalar_type() == query.scalar_type(),
+                "K/V cache must have the query's dtype");
+  } else {
+    TORCH_CHECK(key_cache.scalar_type() == at::kFloat8_e4m3fn &&
+                    value_cache.scalar_type() == at::kFloat8_e4m3fn,
+                "K/V cache must be torch.float8_e4m3fn");
+  }
   TORCH_CHECK(query.dim() == 3 && query.stride(2) == 1, "invalid query");
   TORCH_CHECK(key_cache.dim() == 4 && key_cache.size(3) == query.size(2) && key_cache.stride(3) == 1 &&
                   value_cache.dim() == 4 && value_cache.stride(3) == 1,
@@ -148,8 +153,9 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
   }
   const at::cuda::CUDAGuard guard(query.device());
   a.stream = at::cuda::getCurrentCUDAStream().stream();
-  const int rc = prefix_len > 0 ? pfd_shared_prefix_decode_fp8_e4m3(&a, static_cast<int32_t>(prefix_len))
-                                : pfd_paged_decode_fp8_e4m3_split_out(&a);
+  const int rc = kv16             ? pfd_paged_decode_kv16_split_out(&a)
+                 : prefix_len > 0 ? pfd_shared_prefix_decode_fp8_e4m3(&a, static_cast<int32_t>(prefix_len))
+                                  : pfd_paged_decode_fp8_e4m3_split_out(&a);
   TORCH_CHECK(rc == PFD_OK, pfd_last_error());
 }
 
@@ -164,6 +170,26 @@ at::Tensor paged_decode_fp8_e4m3_split_out(at::Tensor query, at::Tensor key_cach
              partial_sum, output, c10::nullopt, k_scale, v_scale, c10::nullopt, c10::nullopt, 0.0,
              max_seq_len, split_size, 0, 0);
   return output;
+}
+
+// The non-quantised sibling, same argument list as the reference dispatch function
+// (integrations/vllm/cuda/l20_paged_decode.cpp:60-87; schema :121-127): caches in the query's dtype.
+at::Tensor paged_decode_split_out(at::Tensor query, at::Tensor key_cache, at::Tensor value_cache,
+                                  at::Tensor block_table, at::Tensor seq_lens, at::Tensor partial_output,
+                                  at::Tensor partial_max, at::Tensor partial_sum, at::Tensor output,
+                                  int64_t max_seq_len, int64_t split_size) {
+  run_decode(query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max,
+             partial_sum, output, c10::nullopt, 1.0, 1.0, c10::nullopt, c10::nullopt, 0.0,
+             max_seq_len, split_size, 0, 0, c10::nullopt, 0, /*kv16=*/true);
+  return output;
+}
+
+void paged_decode_split_out_void(at::Tensor query, at::Tensor key_cache, at::Tensor value_cache,
+                                 at::Tensor block_table, at::Tensor seq_lens, at::Tensor partial_output,
+                                 at::Tensor partial_max, at::Tensor partial_sum, at::Tensor output,
+                                 int64_t max_seq_len, int64_t split_size) {
+  paged_decode_split_out(query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max,
+                         partial_sum, output, max_seq_len, split_size);
 }
 
 void paged_decode_fp8_e4m3_split_out_void(at::Tensor query, at::Tensor key_cache, at::Tensor value_cache,
@@ -244,6 +270,13 @@ void resolve_slots(at::Tensor block_table, at::Tensor seq_lens, at::Tensor slots
 
 TORCH_LIBRARY(l20_stack, module) {
   module.def(
+      "paged_decode_split_out("
+      "Tensor query, Tensor key_cache, Tensor value_cache, "
+      "Tensor block_table, Tensor seq_lens, "
+      "Tensor(a!) partial_output, Tensor(b!) partial_max, "
+      "Tensor(c!) partial_sum, Tensor(d!) output, "
+      "int max_seq_len, int split_size) -> Tensor(d!)");
+  module.def(
       "paged_decode_fp8_e4m3_split_out("
       "Tensor query, Tensor key_cache, Tensor value_cache, "
       "Tensor block_table, Tensor seq_lens, "
@@ -269,6 +302,7 @@ TORCH_LIBRARY(l20_stack, module) {
 }
 
 TORCH_LIBRARY_IMPL(l20_stack, CUDA, module) {
+  module.impl("paged_decode_split_out", &paged_decode_split_out);
   module.impl("paged_decode_fp8_e4m3_split_out", &paged_decode_fp8_e4m3_split_out);
   module.impl("paged_decode_fp8_e4m3_split_out_v2", &paged_decode_fp8_e4m3_split_out_v2);
   module.impl("shared_prefix_decode_fp8_e4m3", &shared_prefix_decode_fp8_e4m3);
@@ -277,6 +311,7 @@ TORCH_LIBRARY_IMPL(l20_stack, CUDA, module) {
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, module) {
+  module.def("paged_decode_split_out", &paged_decode_split_out_void);
   module.def("paged_decode_fp8_e4m3_split_out", &paged_decode_fp8_e4m3_split_out_void);
   module.def("launch_count", []() { return pfd_launch_count(); });
 }

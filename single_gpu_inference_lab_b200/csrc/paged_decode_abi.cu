@@ -79,11 +79,12 @@ struct MapKey {
   const void* base;
   int64_t stride_page, stride_token, stride_head, num_pages;
   int32_t heads;
-  int32_t promotion;  // L2 promotion in bytes
+  int32_t promotion;   // L2 promotion in bytes
+  int32_t elem_bytes;  // 1: e4m3, 2: fp16 / bf16
   bool operator==(const MapKey& o) const {
     return dev == o.dev && base == o.base && stride_page == o.stride_page && stride_token == o.stride_token &&
            stride_head == o.stride_head && num_pages == o.num_pages && heads == o.heads &&
-           promotion == o.promotion;
+           promotion == o.promotion && elem_bytes == o.elem_bytes;
   }
 };
 struct MapEntry {
@@ -102,12 +103,14 @@ bool head_is_dim1(int64_t stride_token, int64_t stride_head) { return stride_hea
 // L2 promotion: the fixed-split grid runs the CTAs of all kv heads of a page at about the same
 // time, so fetching 256 bytes (two heads' rows in the NHD layout) per 128-byte request pays; the
 // balanced grid does not keep kv heads in step, there the second half would be evicted unused.
+// (With 2-byte elements the strides are given in elements and the box is half a row, 64
+// elements = 128 bytes, so that the 128-byte swizzle still applies.)
 int get_tensor_map(const void* base, int64_t stride_page, int64_t stride_token, int64_t stride_head,
-                   int64_t num_pages, int32_t heads, int32_t promotion, CUtensorMap* out) {
+                   int64_t num_pages, int32_t heads, int32_t promotion, CUtensorMap* out, int32_t elem_bytes = 1) {
   int dev = 0;
   cudaGetDevice(&dev);
   if (const char* env = getenv("PFD_L2_PROMOTION")) promotion = atoi(env);  // tuning aid: 0, 64, 128, 256
-  const MapKey key{dev, base, stride_page, stride_token, stride_head, num_pages, heads, promotion};
+  const MapKey key{dev, base, stride_page, stride_token, stride_head, num_pages, heads, promotion, elem_bytes};
   std::lock_guard<std::mutex> lock(g_state_mutex);
   for (const MapEntry& e : g_maps)
     if (e.key == key) {
@@ -125,9 +128,10 @@ int get_tensor_map(const void* base, int64_t stride_page, int64_t stride_token, 
   const bool h1 = head_is_dim1(stride_token, stride_head);
   const cuuint64_t dims[4] = {128, (cuuint64_t)(h1 ? heads : 16), (cuuint64_t)(h1 ? 16 : heads),
                               (cuuint64_t)num_pages};
-  const cuuint64_t strides[3] = {(cuuint64_t)(h1 ? stride_head : stride_token),
-                                 (cuuint64_t)(h1 ? stride_token : stride_head), (cuuint64_t)stride_page};
-  const cuuint32_t box[4] = {128, (cuuint32_t)(h1 ? 1 : 16), (cuuint32_t)(h1 ? 16 : 1), 1};
+  const cuuint64_t strides[3] = {(cuuint64_t)(h1 ? stride_head : stride_token) * elem_bytes,
+                                 (cuuint64_t)(h1 ? stride_token : stride_head) * elem_bytes,
+                                 (cuuint64_t)stride_page * elem_bytes};
+  const cuuint32_t box[4] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)(h1 ? 1 : 16), (cuuint32_t)(h1 ? 16 : 1), 1};
   const cuuint32_t elem[4] = {1, 1, 1, 1};
   MapEntry entry;
   entry.key = key;
@@ -136,7 +140,8 @@ int get_tensor_map(const void* base, int64_t stride_page, int64_t stride_token, 
                      : promotion == 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B
                                        : promotion == 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
                                                           : CU_TENSOR_MAP_L2_PROMOTION_L2_256B;
-  const CUresult r = g_encode(&entry.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides,
+  const CUresult r = g_encode(&entry.map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+                              4, const_cast<void*>(base), dims, strides,
                               box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(PFD_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -203,6 +208,9 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
 constexpr int kChunkStages = 3;
 constexpr int kChunkWarps = 8;  // per CTA, one CTA per SM
 constexpr int kChunkMaxBatch = 2048;
+// 16-bit caches: a stage of two pages is 16 KiB, six warps x two stages fill the same 192 KiB.
+constexpr int kChunkStages16 = 2;
+constexpr int kChunkWarps16 = 6;
 constexpr int kChunkPieceCost = 2;  // half page pairs charged for starting a sequence
 
 int sm_count_of(int dev, int* out) {
@@ -233,27 +241,30 @@ bool balanced_eligible(const pfd_decode_args& a, const pfd::KernelParams& kp, in
   return rows >= 2LL * (sms * kChunkWarps / a.num_kv_heads) * a.num_q_heads;
 }
 
-template <bool QBF16, int kStagesT, int kWarpsT>
-int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int sms, cudaStream_t stream) {
+// max_groups > 0 caps the number of warp groups (a workspace with room for fewer slots).
+template <bool QBF16, int kStagesT, int kWarpsT, bool KV16 = false>
+int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int sms, cudaStream_t stream,
+                    int max_groups = 0) {
   CUtensorMap mk, mv;
+  constexpr int kElem = KV16 ? 2 : 1;
   if (int rc = get_tensor_map(a.key_cache, a.k_stride_page, a.k_stride_token, a.k_stride_head, a.num_pages,
-                              a.num_kv_heads, 256, &mk))
+                              a.num_kv_heads, 256, &mk, kElem))
     return rc;
   if (int rc = get_tensor_map(a.value_cache, a.v_stride_page, a.v_stride_token, a.v_stride_head, a.num_pages,
-                              a.num_kv_heads, 256, &mv))
+                              a.num_kv_heads, 256, &mv, kElem))
     return rc;
   pfd::TmaParams tp{};
   tp.head_is_dim1 = head_is_dim1(a.k_stride_token, a.k_stride_head) ? 1 : 0;
   if (int rc = status_pointer(&tp.status)) return rc;
   tp.phase_times = g_phase_times;
-  auto kernel = pfd::paged_decode_fp8_chunk_kernel<QBF16, kStagesT, kWarpsT>;
+  auto kernel = pfd::paged_decode_fp8_chunk_kernel<QBF16, kStagesT, kWarpsT, KV16>;
   constexpr int kThreads = kWarpsT * 32;
   // ring + mbarriers + scan scratch + prefix[B + 1] + lens[B], sized for the largest batch
-  constexpr int smem = 1024 + kWarpsT * kStagesT * 8192 + kWarpsT * kStagesT * 8 +
+  constexpr int smem = 1024 + kWarpsT * kStagesT * 8192 * kElem + kWarpsT * kStagesT * 8 +
                        kWarpsT * 4 + (2 * kChunkMaxBatch + 1) * 4 + 16;
   int dev = 0;
   cudaGetDevice(&dev);
-  static bool configured[kMaxDevices][2] = {};
+  static bool configured[kMaxDevices][2] = {};  // one array per instantiation of this template
   {
     std::lock_guard<std::mutex> lock(g_state_mutex);
     if (!configured[dev][QBF16 ? 1 : 0]) {
@@ -265,6 +276,7 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
   pfd::ChunkParams cp{};
   cp.batch = a.batch;
   cp.num_warps = sms * kWarpsT;
+  if (max_groups > 0) cp.num_warps = std::min(cp.num_warps, max_groups * a.num_kv_heads);
   cp.piece_cost = kChunkPieceCost;
   if (const char* env = getenv("PFD_PIECE_COST")) cp.piece_cost = std::max(0, std::min(atoi(env), 64));  // tuning aid
   cudaLaunchAttribute attr[1];
@@ -282,7 +294,7 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
     if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "balanced decode kernel launch failed: %s", cudaGetErrorString(e));
     if (int rc = check_launch("balanced decode kernel")) return rc;
   }
-  g_last_path = PFD_PATH_BALANCED;
+  g_last_path = KV16 ? PFD_PATH_BALANCED_KV16 : PFD_PATH_BALANCED;
   if (a.flags & PFD_FLAG_PARTIAL_ONLY) return PFD_OK;
   {
     // Few rows mean few, long sequences whose pieces are many: four warps then share a row,
@@ -356,6 +368,40 @@ int64_t pfd_launch_count(void) { return g_launches.load(std::memory_order_relaxe
 }  // extern "C"
 
 namespace {
+pfd::KernelParams fill_params(const pfd_decode_args& a, int group, bool direct_ok, int slot_offset) {
+  pfd::KernelParams kp{};
+  kp.query = a.query;
+  kp.key_cache = static_cast<const uint8_t*>(a.key_cache);
+  kp.value_cache = static_cast<const uint8_t*>(a.value_cache);
+  kp.block_table = a.block_table;
+  kp.seq_lens = a.seq_lens;
+  kp.k_scale_ph = a.k_scale_per_head;
+  kp.v_scale_ph = a.v_scale_per_head;
+  kp.partial_output = a.partial_output;
+  kp.partial_max = a.partial_max;
+  kp.partial_sum = a.partial_sum;
+  kp.output = a.output;
+  kp.packed_output = a.packed_output;
+  kp.q_stride_b = a.q_stride_b; kp.q_stride_h = a.q_stride_h;
+  kp.k_stride_page = a.k_stride_page; kp.k_stride_token = a.k_stride_token; kp.k_stride_head = a.k_stride_head;
+  kp.v_stride_page = a.v_stride_page; kp.v_stride_token = a.v_stride_token; kp.v_stride_head = a.v_stride_head;
+  kp.bt_stride_b = a.bt_stride_b;
+  kp.partial_stride_b = a.partial_stride_b; kp.partial_stride_h = a.partial_stride_h;
+  kp.partial_stride_s = a.partial_stride_s;
+  kp.o_stride_b = a.o_stride_b; kp.o_stride_h = a.o_stride_h;
+  kp.k_scale = a.k_scale; kp.v_scale = a.v_scale;
+  kp.sm_scale = a.sm_scale != 0.f ? a.sm_scale : 1.0f / sqrtf(static_cast<float>(a.head_dim));
+  kp.num_q_heads = a.num_q_heads; kp.num_kv_heads = a.num_kv_heads; kp.group = group;
+  kp.split_size = a.split_size; kp.kv_start = a.kv_start;
+  kp.partial_dtype = a.partial_dtype;
+  kp.direct_out = direct_ok ? 1 : 0;
+  kp.bt_cols = (a.max_seq_len + pfd::kPage - 1) / pfd::kPage;  // rows are at least this wide
+  kp.slot_offset = slot_offset;
+  kp.early_metadata = (a.flags & PFD_FLAG_EARLY_METADATA) ? 1 : 0;
+  kp.kv_evict_first = 1;
+  return kp;
+}
+
 // slot_offset > 0: workspace slots [0, slot_offset) are filled by the dense prefix pass; the
 // split-KV kernels then write behind them and the merge kernel covers both.
 int decode_impl(const pfd_decode_args* args, int slot_offset) {
@@ -406,36 +452,7 @@ int decode_impl(const pfd_decode_args* args, int slot_offset) {
       return fail(PFD_ERR_UNSUPPORTED, "partial_output must be 16-byte aligned");
   }
 
-  pfd::KernelParams kp{};
-  kp.query = a.query;
-  kp.key_cache = static_cast<const uint8_t*>(a.key_cache);
-  kp.value_cache = static_cast<const uint8_t*>(a.value_cache);
-  kp.block_table = a.block_table;
-  kp.seq_lens = a.seq_lens;
-  kp.k_scale_ph = a.k_scale_per_head;
-  kp.v_scale_ph = a.v_scale_per_head;
-  kp.partial_output = a.partial_output;
-  kp.partial_max = a.partial_max;
-  kp.partial_sum = a.partial_sum;
-  kp.output = a.output;
-  kp.packed_output = a.packed_output;
-  kp.q_stride_b = a.q_stride_b; kp.q_stride_h = a.q_stride_h;
-  kp.k_stride_page = a.k_stride_page; kp.k_stride_token = a.k_stride_token; kp.k_stride_head = a.k_stride_head;
-  kp.v_stride_page = a.v_stride_page; kp.v_stride_token = a.v_stride_token; kp.v_stride_head = a.v_stride_head;
-  kp.bt_stride_b = a.bt_stride_b;
-  kp.partial_stride_b = a.partial_stride_b; kp.partial_stride_h = a.partial_stride_h;
-  kp.partial_stride_s = a.partial_stride_s;
-  kp.o_stride_b = a.o_stride_b; kp.o_stride_h = a.o_stride_h;
-  kp.k_scale = a.k_scale; kp.v_scale = a.v_scale;
-  kp.sm_scale = a.sm_scale != 0.f ? a.sm_scale : 1.0f / sqrtf(static_cast<float>(a.head_dim));
-  kp.num_q_heads = a.num_q_heads; kp.num_kv_heads = a.num_kv_heads; kp.group = group;
-  kp.split_size = a.split_size; kp.kv_start = a.kv_start;
-  kp.partial_dtype = a.partial_dtype;
-  kp.direct_out = direct_ok ? 1 : 0;
-  kp.bt_cols = (a.max_seq_len + pfd::kPage - 1) / pfd::kPage;  // rows are at least this wide
-  kp.slot_offset = slot_offset;
-  kp.early_metadata = (a.flags & PFD_FLAG_EARLY_METADATA) ? 1 : 0;
-  kp.kv_evict_first = 1;
+  const pfd::KernelParams kp = fill_params(a, group, direct_ok, slot_offset);
 
   const bool bf16 = a.query_dtype == PFD_DTYPE_BF16;
   if (a.head_dim == 128)
@@ -492,6 +509,62 @@ int launch_prefix(const pfd_decode_args& a, int prefix_len, int chunks) {
 extern "C" {
 
 int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args) { return decode_impl(args, 0); }
+
+// ---- non-quantised sibling: caches in the query's 16-bit type --------------------------------
+int pfd_paged_decode_kv16_split_out(const pfd_decode_args* args) {
+  if (args == nullptr) return fail(PFD_ERR_INVALID, "args is NULL");
+  if (args->struct_size != sizeof(pfd_decode_args))
+    return fail(PFD_ERR_INVALID, "pfd_decode_args size mismatch: caller %u, library %zu", args->struct_size,
+                sizeof(pfd_decode_args));
+  const pfd_decode_args& a = *args;
+  if (a.batch < 0 || a.num_q_heads <= 0 || a.num_kv_heads <= 0) return fail(PFD_ERR_INVALID, "invalid query");
+  if (a.head_dim != 128) return fail(PFD_ERR_UNSUPPORTED, "head_dim must be 128 for 16-bit caches");
+  if (a.page_size != pfd::kPage) return fail(PFD_ERR_UNSUPPORTED, "page_size must be 16");
+  if (a.num_q_heads % a.num_kv_heads != 0) return fail(PFD_ERR_INVALID, "Q heads must be divisible by KV heads");
+  const int group = a.num_q_heads / a.num_kv_heads;
+  if (group > 8) return fail(PFD_ERR_UNSUPPORTED, "at most 8 query heads per KV head for 16-bit caches");
+  if (a.query_dtype != PFD_DTYPE_F16 && a.query_dtype != PFD_DTYPE_BF16)
+    return fail(PFD_ERR_INVALID, "query must be FP16 or BF16");
+  if (a.split_size < 16 || a.split_size % 16 != 0) return fail(PFD_ERR_INVALID, "split_size must be a multiple of 16");
+  if (a.kv_start < 0 || a.max_seq_len < 0) return fail(PFD_ERR_INVALID, "negative length");
+  if (a.batch == 0) return PFD_OK;
+  if (a.batch > kChunkMaxBatch) return fail(PFD_ERR_UNSUPPORTED, "at most %d sequences per call", kChunkMaxBatch);
+  if (!a.query || !a.key_cache || !a.value_cache || !a.block_table || !a.seq_lens)
+    return fail(PFD_ERR_INVALID, "NULL operand");
+  if (!a.output && !a.packed_output) return fail(PFD_ERR_INVALID, "no output given");
+  if (a.q_stride_h % 2 || a.q_stride_b % 2 || (reinterpret_cast<uintptr_t>(a.query) & 3u))
+    return fail(PFD_ERR_UNSUPPORTED, "query rows must be 4-byte aligned");
+  if (!aligned16(a.key_cache) || !aligned16(a.value_cache) || a.k_stride_page % 8 || a.k_stride_token % 8 ||
+      a.k_stride_head % 8 || a.v_stride_page % 8 || a.v_stride_token % 8 || a.v_stride_head % 8)
+    return fail(PFD_ERR_UNSUPPORTED, "K/V cache base and strides must be multiples of 16 bytes");
+  if (!(a.k_stride_page > 0 && a.v_stride_page > 0 && a.k_stride_token > 0 && a.v_stride_token > 0 &&
+        a.k_stride_head > 0 && a.v_stride_head > 0 && a.num_pages > 0 &&
+        head_is_dim1(a.k_stride_token, a.k_stride_head) == head_is_dim1(a.v_stride_token, a.v_stride_head)))
+    return fail(PFD_ERR_UNSUPPORTED, "K and V caches must share one (page, token, head) order with positive strides");
+  if (!a.partial_output || !a.partial_max || !a.partial_sum)
+    return fail(PFD_ERR_INVALID, "partial output workspace has wrong shape");
+  if (a.partial_dtype < PFD_DTYPE_F32 || a.partial_dtype > PFD_DTYPE_BF16)
+    return fail(PFD_ERR_INVALID, "partial_output dtype must be f32, f16 or bf16");
+  if (!aligned16(a.partial_output)) return fail(PFD_ERR_UNSUPPORTED, "partial_output must be 16-byte aligned");
+  if (a.partial_stride_s != 1 || a.partial_stride_h != a.workspace_splits ||
+      a.partial_stride_b != (int64_t)a.num_q_heads * a.workspace_splits)
+    return fail(PFD_ERR_UNSUPPORTED, "the partial workspace must be dense [batch, q heads, splits]");
+  // The workspace is a flat list of rows, two slots of num_q_heads rows per group of warps: its
+  // size caps the number of groups (the reference's [B, Hq, ceil(max/split)] always holds one).
+  const int64_t rows = (int64_t)a.batch * a.num_q_heads * a.workspace_splits;
+  const int64_t groups = rows / (2LL * a.num_q_heads);
+  if (groups < 1) return fail(PFD_ERR_INVALID, "partial output workspace has wrong shape");
+  int dev = 0, sms = 0;
+  cudaGetDevice(&dev);
+  if (int rc = sm_count_of(dev, &sms)) return rc;
+  if (a.num_kv_heads > kChunkWarps16 * sms / 2) return fail(PFD_ERR_UNSUPPORTED, "too many KV heads");
+  const pfd::KernelParams kp = fill_params(a, group, !(a.flags & PFD_FLAG_NO_DIRECT_OUT), 0);
+  cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
+  const int cap = (int)std::min<int64_t>(groups, 1 << 20);
+  return a.query_dtype == PFD_DTYPE_BF16
+             ? launch_balanced<true, kChunkStages16, kChunkWarps16, true>(a, kp, sms, stream, cap)
+             : launch_balanced<false, kChunkStages16, kChunkWarps16, true>(a, kp, sms, stream, cap);
+}
 
 int pfd_shared_prefix_decode_fp8_e4m3(const pfd_decode_args* args, int32_t prefix_len) {
   if (args == nullptr) return fail(PFD_ERR_INVALID, "args is NULL");

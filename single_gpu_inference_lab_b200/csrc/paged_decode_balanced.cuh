@@ -275,21 +275,178 @@ __device__ __forceinline__ void store_row16(const KernelParams& p, int b, int hq
   }
 }
 
+
+// ---- 16-bit (fp16 / bf16) K/V caches ---------------------------------------------------------
+// Same kernel, other tiles: a (page, head) tile is 16 rows of 256 bytes, staged as two
+// 128-byte-swizzled halves of 2 KiB ([d 0..63], [d 64..127]); fragments come from ldmatrix, K
+// as it lies (tokens x d), V transposed (d x tokens); no conversion step.  Accumulators are in
+// the natural MMA layout: o[mt][c] is d = 16 mt + i + 8 (c >> 1), head 2j + (c & 1).
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+template <bool BF16>
+__device__ __forceinline__ void mma_16816_kv16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  if constexpr (BF16) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  } else {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack_kv16(float lo, float hi) {
+  if constexpr (BF16) {
+    __nv_bfloat162 x = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&x);
+  } else {
+    return pack_f16x2(lo, hi);
+  }
+}
+
+// Q of head i as B-fragments in natural order: k-step ks covers d = 16 ks + 2j + {0,1 | 8,9}.
+__device__ __forceinline__ void kv16_load_q(uint32_t (&qb)[1][8][2], const KernelParams& p, int b, int kvh,
+                                            int i, int j) {
+  const bool live = i < p.group;
+  const uint32_t* q = reinterpret_cast<const uint32_t*>(
+      reinterpret_cast<const uint16_t*>(p.query) + (int64_t)b * p.q_stride_b +
+      (int64_t)(kvh * p.group + (live ? i : 0)) * p.q_stride_h);
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    qb[0][ks][0] = live ? __ldg(q + 8 * ks + j) : 0u;
+    qb[0][ks][1] = live ? __ldg(q + 8 * ks + 4 + j) : 0u;
+  }
+}
+
+// One step = two consecutive pages of one sequence, read from a stage [K0][K1][V0][V1] of
+// 4 KiB tiles (two swizzled halves each).  tok0 = token index of page 0's row 0.
+template <bool BF16>
+__device__ __forceinline__ void kv16_step(BalState<1>& st, uint32_t stage, const uint32_t (&qb)[1][8][2],
+                                          float scale_log2, int tok0, int lo, int hi, int lane) {
+  constexpr uint32_t kTile = 2 * kPage * 128;
+  const int i = lane >> 2, j = lane & 3;
+  const int mid = lane >> 3, r8 = lane & 7;
+  const bool edge = (tok0 < lo) | (tok0 + 2 * kPage > hi);
+  float s[2][4];
+#pragma unroll
+  for (int u = 0; u < 2; ++u) s[u][0] = s[u][1] = s[u][2] = s[u][3] = 0.f;
+  {
+    // K: matrix `mid` of an x4 load = rows 8 (mid & 1) .., 16-byte chunk 2 ks + (mid >> 1)
+    const int row = (mid & 1) * 8 + r8;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int chunk = 2 * ks + (mid >> 1);
+      const uint32_t off = (chunk >> 3) * 2048 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        uint32_t a[4];
+        ldsm_x4(stage + u * kTile + off, a);
+        mma_16816_kv16<BF16>(s[u], a, qb[0][ks][0], qb[0][ks][1]);
+      }
+    }
+  }
+  // scale + mask: s[u][c] is (token 16u + 8(c>>1) + i, head 2j + (c&1))
+#pragma unroll
+  for (int u = 0; u < 2; ++u)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      bool dead = false;
+      if (edge) {
+        const int tok = tok0 + u * kPage + 8 * (c >> 1) + i;
+        dead = (tok < lo) | (tok >= hi);
+      }
+      s[u][c] = dead ? -INFINITY : s[u][c] * scale_log2;
+    }
+  uint32_t pb[2][2];
+  {
+    float mx[2], alpha[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float x = fmaxf(fmaxf(s[0][e], s[0][2 + e]), fmaxf(s[1][e], s[1][2 + e]));
+      x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 4));
+      x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 8));
+      x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 16));
+      mx[e] = fmaxf(st.m[0][e], x);
+      alpha[e] = exp2f(st.m[0][e] - mx[e]);
+      st.m[0][e] = mx[e];
+    }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const float p0 = exp2f(s[u][0] - mx[0]), p1 = exp2f(s[u][1] - mx[1]);
+      const float p2 = exp2f(s[u][2] - mx[0]), p3 = exp2f(s[u][3] - mx[1]);
+      sum[0] += p0 + p2;
+      sum[1] += p1 + p3;
+      // (token i, heads 2j, 2j+1) -> transpose -> (tokens 2j, 2j+1; head i)
+      pb[u][0] = movmatrix_trans(pack_kv16<BF16>(p0, p1));
+      pb[u][1] = movmatrix_trans(pack_kv16<BF16>(p2, p3));
+    }
+    st.l[0][0] = st.l[0][0] * alpha[0] + sum[0];
+    st.l[0][1] = st.l[0][1] * alpha[1] + sum[1];
+    if (__any_sync(0xffffffffu, (alpha[0] != 1.f) | (alpha[1] != 1.f))) {
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        st.o[0][mt][0] *= alpha[0]; st.o[0][mt][1] *= alpha[1];
+        st.o[0][mt][2] *= alpha[0]; st.o[0][mt][3] *= alpha[1];
+      }
+    }
+  }
+  // O^T += V^T P^T.  V^T fragments by transposing loads: matrix `mid` = tokens 8 (mid >> 1) ..,
+  // chunk 2 mt + (mid & 1); a[0], a[1] hold tokens 2j, 2j+1 and a[2], a[3] tokens 8 + 2j, 9 + 2j.
+  {
+    const int row = (mid >> 1) * 8 + r8;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      uint32_t keep_lo = 0xffffffffu, keep_hi = 0xffffffffu;  // bytes of tokens outside the range may hold anything
+      if (edge) {
+        const int t0 = tok0 + u * kPage + 2 * j;
+        const auto live = [&](int t) { return (t >= lo) & (t < hi); };
+        keep_lo = (live(t0) ? 0x0000ffffu : 0u) | (live(t0 + 1) ? 0xffff0000u : 0u);
+        keep_hi = (live(t0 + 8) ? 0x0000ffffu : 0u) | (live(t0 + 9) ? 0xffff0000u : 0u);
+      }
+#pragma unroll
+      for (int mt = 0; mt < 8; ++mt) {
+        const int chunk = 2 * mt + (mid & 1);
+        const uint32_t off = (chunk >> 3) * 2048 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
+        uint32_t a[4];
+        ldsm_x4_trans(stage + (2 + u) * kTile + off, a);
+        if (edge) { a[0] &= keep_lo; a[1] &= keep_lo; a[2] &= keep_hi; a[3] &= keep_hi; }
+        mma_16816_kv16<BF16>(st.o[0][mt], a, pb[u][0], pb[u][1]);
+      }
+    }
+  }
+}
+
+// One value of a piece into the workspace in its storage type.
+__device__ __forceinline__ void store_partial_scalar(void* base, int dtype, int64_t idx, float v) {
+  if (dtype == 0) reinterpret_cast<float*>(base)[idx] = v;
+  else if (dtype == 1) reinterpret_cast<__half*>(base)[idx] = __float2half_rn(v);
+  else reinterpret_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
+}
+
 // Workspace row of query head `hq` in slot `which` of warp group `grp` (0: the piece that begins
 // the chunk, 1: the piece that ends it).  The workspace is used as a flat array of (o[D], m, l) rows.
 __device__ __forceinline__ int64_t chunk_slot_row(int grp, int which, int num_q_heads, int hq) {
   return ((int64_t)(2 * grp + which)) * num_q_heads + hq;
 }
 
-// grid = one CTA per SM; block = NWARPS independent warps.
-template <bool QBF16, int NSTAGE, int NWARPS>
+// grid = one CTA per SM; block = NWARPS independent warps.  KV16 = false: e4m3 caches;
+// true: caches in the query's 16-bit type (the reference's non-quantised sibling operator).
+template <bool QBF16, int NSTAGE, int NWARPS, bool KV16 = false>
 __global__ void __launch_bounds__(NWARPS * 32, 1)
 paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const ChunkParams cp,
                               const __grid_constant__ CUtensorMap tmap_k,
                               const __grid_constant__ CUtensorMap tmap_v) {
   constexpr int D = 128;
   constexpr int NT = NWARPS * 32;
-  constexpr uint32_t kTile = kPage * D;
+  constexpr uint32_t kTile = (KV16 ? 2 : 1) * kPage * D;
   constexpr uint32_t kStage = 4 * kTile;
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
@@ -414,21 +571,26 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       mbar_expect_tx(bar, two ? kStage : kStage / 2);
       const int c1 = tp.head_is_dim1 ? kvh : 0;
       const int c2 = tp.head_is_dim1 ? 0 : kvh;
-      if (p.kv_evict_first) {
-        const uint64_t pol = l2_policy_evict_first();
-        tma_load_tile(dst, &tmap_k, bar, c1, c2, phys0, pol);
-        tma_load_tile(dst + 2 * kTile, &tmap_v, bar, c1, c2, phys0, pol);
-        if (two) {
-          tma_load_tile(dst + kTile, &tmap_k, bar, c1, c2, phys1, pol);
-          tma_load_tile(dst + 3 * kTile, &tmap_v, bar, c1, c2, phys1, pol);
+      const uint64_t pol = l2_policy_evict_first();
+      const auto load = [&](uint32_t to, const CUtensorMap* map, int32_t phys) {
+        if constexpr (KV16) {  // two halves of 64 elements
+          if (p.kv_evict_first) {
+            tma_load_tile_x(to, map, bar, 0, c1, c2, phys, pol);
+            tma_load_tile_x(to + kTile / 2, map, bar, 64, c1, c2, phys, pol);
+          } else {
+            tma_load_tile_x(to, map, bar, 0, c1, c2, phys);
+            tma_load_tile_x(to + kTile / 2, map, bar, 64, c1, c2, phys);
+          }
+        } else {
+          if (p.kv_evict_first) tma_load_tile(to, map, bar, c1, c2, phys, pol);
+          else tma_load_tile(to, map, bar, c1, c2, phys);
         }
-      } else {
-        tma_load_tile(dst, &tmap_k, bar, c1, c2, phys0);
-        tma_load_tile(dst + 2 * kTile, &tmap_v, bar, c1, c2, phys0);
-        if (two) {
-          tma_load_tile(dst + kTile, &tmap_k, bar, c1, c2, phys1);
-          tma_load_tile(dst + 3 * kTile, &tmap_v, bar, c1, c2, phys1);
-        }
+      };
+      load(dst, &tmap_k, phys0);
+      load(dst + 2 * kTile, &tmap_v, phys0);
+      if (two) {
+        load(dst + kTile, &tmap_k, phys1);
+        load(dst + 3 * kTile, &tmap_v, phys1);
       }
     }
   };
@@ -460,11 +622,15 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
   cur.b = seq_of(P0);
   cur.np = prefix[cur.b + 1] - prefix[cur.b];
   cur.start = prefix[cur.b];
-  const float ks = p.k_scale_ph ? __ldg(p.k_scale_ph + kvh) : p.k_scale;
-  const float vs = p.v_scale_ph ? __ldg(p.v_scale_ph + kvh) : p.v_scale;
+  const float ks = KV16 ? 1.f : (p.k_scale_ph ? __ldg(p.k_scale_ph + kvh) : p.k_scale);
+  const float vs = KV16 ? 1.f : (p.v_scale_ph ? __ldg(p.v_scale_ph + kvh) : p.v_scale);
   const float scale_log2 = ks * p.sm_scale * kLog2e;
+  const auto load_q = [&](uint32_t (&dst)[1][8][2], int b) {
+    if constexpr (KV16) kv16_load_q(dst, p, b, kvh, i, j);
+    else bal_load_q<QBF16, 1>(dst, p, b, kvh, i, j);
+  };
   uint32_t qb[1][8][2];
-  bal_load_q<QBF16, 1>(qb, p, cur.b, kvh, i, j);
+  load_q(qb, cur.b);
   BalState<1> st;
   bool ok = true;
   int t = 0;  // pairs consumed
@@ -481,7 +647,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
         ++nxt.b;
         nxt.np = prefix[nxt.b + 1] - prefix[nxt.b];
       } while (nxt.np == 0);
-      bal_load_q<QBF16, 1>(qn, p, nxt.b, kvh, i, j);
+      load_q(qn, nxt.b);
     }
     const int seq_len = lens[cur.b];
     const bool whole = cur.start >= P0 && cur.start + cur.np <= P1;
@@ -492,7 +658,8 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       if (!mbar_wait_bounded(my_bars + 8 * s, (t / NSTAGE) & 1)) { ok = false; break; }
       if (t == 0) mark_phase_at(tp, W, 3, lane == 0);  // first data landed
       const int tok0 = (page_first + 2 * (g - cur.start)) * kPage;
-      bal_step<1>(st, my_ring + s * kStage, k_off, v_off, qb, scale_log2, tok0, p.kv_start, seq_len, i, j);
+      if constexpr (KV16) kv16_step<QBF16>(st, my_ring + s * kStage, qb, scale_log2, tok0, p.kv_start, seq_len, lane);
+      else bal_step<1>(st, my_ring + s * kStage, k_off, v_off, qb, scale_log2, tok0, p.kv_start, seq_len, i, j);
       // all reads of the stage fed MMAs above: hand it back to TMA for the chunk's pair t + NSTAGE
       __syncwarp();
       const int tn = t + NSTAGE;
@@ -523,6 +690,40 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
     for (int c = 0; c < 2; ++c) {
       const int row = 2 * j + c;
       if (row >= p.group) continue;
+      const int hq = kvh * p.group + row;
+      if constexpr (KV16) {
+        // natural layout: this thread holds d = 16 mt + i and 16 mt + i + 8 of the row
+        const float m_nat = st.m[0][c] * kLn2;
+        const int64_t r = whole ? 0 : chunk_slot_row(grp, which, p.num_q_heads, hq);
+        const float inv = 1.f / lsum[c];
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            const int d = 16 * mt + i + 8 * hh;
+            const float x = st.o[0][mt][2 * hh + c];
+            if (!whole) {
+              store_partial_scalar(p.partial_output, p.partial_dtype, r * D + d, x);
+            } else if (p.packed_output != nullptr) {
+              p.packed_output[((int64_t)cur.b * p.num_q_heads + hq) * (D + 2) + d] = x;
+            } else {
+              const int64_t o = (int64_t)cur.b * p.o_stride_b + (int64_t)hq * p.o_stride_h + d;
+              if constexpr (QBF16) reinterpret_cast<__nv_bfloat16*>(p.output)[o] = __float2bfloat16_rn(x * inv);
+              else reinterpret_cast<__half*>(p.output)[o] = __float2half_rn(x * inv);
+            }
+          }
+        if (i == 0) {
+          if (!whole) {
+            p.partial_max[r] = m_nat;
+            p.partial_sum[r] = lsum[c];
+          } else if (p.packed_output != nullptr) {
+            float* dst = p.packed_output + ((int64_t)cur.b * p.num_q_heads + hq) * (D + 2);
+            dst[D] = m_nat;
+            dst[D + 1] = lsum[c];
+          }
+        }
+        continue;
+      }
       float v[16];
 #pragma unroll
       for (int mt = 0; mt < 8; ++mt) {
@@ -530,9 +731,9 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
         v[2 * mt + 1] = st.o[0][mt][2 + c] * vs;
       }
       if (whole) {
-        store_row16<QBF16>(p, cur.b, kvh * p.group + row, 16 * i, v, st.m[0][c] * kLn2, lsum[c], i == 0);
+        store_row16<QBF16>(p, cur.b, hq, 16 * i, v, st.m[0][c] * kLn2, lsum[c], i == 0);
       } else {
-        const int64_t r = chunk_slot_row(grp, which, p.num_q_heads, kvh * p.group + row);
+        const int64_t r = chunk_slot_row(grp, which, p.num_q_heads, hq);
         float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.partial_output) + r * D + 16 * i);
 #pragma unroll
         for (int f = 0; f < 4; ++f) dst[f] = make_float4(v[4 * f], v[4 * f + 1], v[4 * f + 2], v[4 * f + 3]);
@@ -609,7 +810,20 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
       const int64_t r = chunk_slot_row(w, s0 > chunks.start_of(w) ? 1 : 0, p.num_q_heads, hq);
       mv[u] = on ? p.partial_max[r] : -INFINITY;
       lv[u] = on ? p.partial_sum[r] : 0.f;
-      xv[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.partial_output) + r * D + lane * E);
+      if (p.partial_dtype == 0) {
+        xv[u] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.partial_output) + r * D + lane * E);
+      } else {
+        const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.partial_output) + r * D + lane * E);
+        if (p.partial_dtype == 1) {
+          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+          const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+          xv[u] = make_float4(a.x, a.y, c.x, c.y);
+        } else {
+          const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+          const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+          xv[u] = make_float4(a.x, a.y, c.x, c.y);
+        }
+      }
     }
     float m_new = big;
 #pragma unroll

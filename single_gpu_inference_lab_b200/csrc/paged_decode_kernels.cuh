@@ -548,6 +548,24 @@ __device__ __forceinline__ void tma_load_tile(uint32_t dst, const void* tmap, ui
       : "memory");
 }
 
+// The same two loads with an explicit innermost coordinate (in elements of the tensor map).
+__device__ __forceinline__ void tma_load_tile_x(uint32_t dst, const void* tmap, uint32_t bar, int x, int c1,
+                                                int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_tile_x(uint32_t dst, const void* tmap, uint32_t bar, int x, int c1,
+                                                int c2, int c3, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(c1), "r"(c2), "r"(c3), "l"(policy)
+      : "memory");
+}
+
 __device__ __forceinline__ uint4 lds_16(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"

@@ -40,6 +40,27 @@ def load_library(path: Optional[Union[str, Path]] = None) -> None:
     _LOADED = True
 
 
+def paged_decode_split_out(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    partial_output: torch.Tensor,
+    partial_max: torch.Tensor,
+    partial_sum: torch.Tensor,
+    output: torch.Tensor,
+    max_seq_len: int,
+    split_size: int,
+) -> torch.Tensor:
+    """The non-quantised sibling: caches in the query's fp16 / bf16 type.  Same call as the
+    reference wrapper (l20_paged_decode.py:20-45); returns ``output``."""
+    return torch.ops.l20_stack.paged_decode_split_out(
+        query, key_cache, value_cache, block_table, seq_lens,
+        partial_output, partial_max, partial_sum, output, max_seq_len, split_size,
+    )
+
+
 def paged_decode_fp8_e4m3_split_out(
     query: torch.Tensor,
     key_cache: torch.Tensor,
@@ -165,6 +186,11 @@ def resolve_slots(block_table: torch.Tensor, seq_lens: torch.Tensor, max_seq_len
 
 
 def _register_fake() -> None:
+    @torch.library.register_fake("l20_stack::paged_decode_split_out")
+    def _(query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max, partial_sum,
+          output, max_seq_len, split_size):
+        return output
+
     @torch.library.register_fake("l20_stack::paged_decode_fp8_e4m3_split_out")
     def _paged_decode_fp8_e4m3_split_out_fake(
         query,

@@ -7,6 +7,8 @@ Same public surface as the module the reference's vLLM hook copies into
 * ``l20_paged_split_kv_attention_fp8(query, key_cache, value_cache, block_table, seq_lens, *,
   k_scale, v_scale, max_seq_len=None, split_size=512, output=None, workspace=None)`` (:597-695)
 * ``should_use_l20_paged_fp8_split_kv(batch, max_seq_len)``                          (:705-709)
+* ``l20_paged_split_kv_attention(...)`` / ``should_use_l20_paged_split_kv``: the fp16 / bf16
+  cache siblings (:491-594, :698-702)
 
 with the same ``RuntimeError`` texts where the condition still exists.  Differences, all
 supersets: bf16 or fp16 queries, head_dim 64 or 128, any number of splits (the reference
@@ -189,6 +191,68 @@ def l20_paged_split_kv_attention_fp8(
         partial_output, partial_max, partial_sum, output,
         float(k_scale), float(v_scale), max_seq_len, split_size,
     )
+
+
+def l20_paged_split_kv_attention(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    *,
+    split_size: int = 512,
+    workspace: tuple[torch.Tensor, ...] | None = None,
+    max_seq_len: int | None = None,
+    output: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """The non-quantised sibling (reference :491-594): K/V caches in the query's fp16 / bf16
+    type.  ``page_granular`` / ``grouped_gqa`` of the reference select between its Triton kernel
+    variants and have no counterpart here.  ``max_seq_len`` (not in the reference, which always
+    reads it back from the device, :517) avoids that host synchronisation."""
+    if not query.is_cuda or torch.cuda.get_device_capability(query.device) != REQUIRED_CAPABILITY:
+        raise RuntimeError("requires an SM100 GPU")
+    if query.ndim != 3 or key_cache.ndim != 4 or value_cache.shape != key_cache.shape:
+        raise RuntimeError("expected Q=[B,H,D], cache=[pages,page,Hkv,D]")
+    batch, num_q_heads, head_dim = query.shape
+    _, page_size, num_kv_heads, cache_dim = key_cache.shape
+    if (
+        head_dim != 128
+        or cache_dim != head_dim
+        or page_size != 16
+        or num_q_heads % num_kv_heads
+        or num_q_heads // num_kv_heads > 8
+        or block_table.shape[0] != batch
+        or seq_lens.numel() != batch
+        or key_cache.dtype != query.dtype
+        or value_cache.dtype != query.dtype
+    ):
+        raise RuntimeError("requires compatible head_dim=128 GQA tensors")
+    if max_seq_len is None:
+        max_seq_len = int(seq_lens.max().item())
+    if workspace is None:
+        workspace = allocate_l20_paged_split_kv_workspace(query, max_seq_len, split_size=split_size,
+                                                          num_kv_heads=num_kv_heads)
+    partial_output, partial_max, partial_sum, workspace_output = workspace[:4]
+    if output is None:
+        output = workspace_output
+    if (
+        partial_output.shape[:2] != (batch, num_q_heads)
+        or partial_output.shape[3] != head_dim
+        or partial_max.shape != partial_output.shape[:3]
+        or partial_sum.shape != partial_output.shape[:3]
+        or output.shape != query.shape
+    ):
+        raise RuntimeError("paged split-KV workspace shape does not match the request")
+    return _ops().paged_decode_split_out(
+        query, key_cache, value_cache, block_table, seq_lens,
+        partial_output, partial_max, partial_sum, output, max_seq_len, split_size,
+    )
+
+
+def should_use_l20_paged_split_kv(batch: int, max_seq_len: int) -> bool:
+    # Same policy as the reference (:698-702): off until a serving A/B says otherwise.
+    del batch, max_seq_len
+    return False
 
 
 def should_use_l20_paged_fp8_split_kv(batch: int, max_seq_len: int) -> bool:

@@ -55,9 +55,9 @@ class PagedDecodeInputs:
     @property
     def kv_bytes(self) -> int:
         """Algorithmic KV bytes of one step: every K and V byte of every live
-        token once, ``sum_b ctx_b * Hkv * D * 2``."""
+        token once, ``sum_b ctx_b * Hkv * D * 2`` times the bytes per cache element."""
         hkv, d = self.key_cache.shape[2], self.key_cache.shape[3]
-        return int(self.seq_lens.sum().item()) * hkv * d * 2
+        return int(self.seq_lens.sum().item()) * hkv * d * 2 * self.key_cache.element_size()
 
     def to(self, device) -> "PagedDecodeInputs":
         moved = {
@@ -109,8 +109,12 @@ def make_inputs(
     batch: int | None = None,
     shrink: float = 1.0,
     query_dtype: torch.dtype = torch.bfloat16,
+    kv_dtype: torch.dtype | None = None,
 ) -> PagedDecodeInputs:
     """Build one seeded decode step.
+
+    ``kv_dtype`` (fp16 / bf16) builds the caches of the non-quantised sibling operator
+    instead: N(0, 1) values stored as they are, both scales one.
 
     Index data (lengths, block table) always comes from a CPU generator seeded
     with ``seed`` so that it is identical everywhere.  K/V/q values come from a
@@ -160,12 +164,17 @@ def make_inputs(
             cursor += n
 
     shape = (total_pages, PAGE_SIZE, hkv, d)
-    key_cache, k_scale = quantize_per_head(
-        torch.randn(shape, generator=dev_gen, device=dev, dtype=torch.float32)
-    )
-    value_cache, v_scale = quantize_per_head(
-        torch.randn(shape, generator=dev_gen, device=dev, dtype=torch.float32)
-    )
+    if kv_dtype is not None:
+        key_cache = torch.randn(shape, generator=dev_gen, device=dev, dtype=torch.float32).to(kv_dtype)
+        value_cache = torch.randn(shape, generator=dev_gen, device=dev, dtype=torch.float32).to(kv_dtype)
+        k_scale = v_scale = torch.ones(hkv, device=dev, dtype=torch.float32)
+    else:
+        key_cache, k_scale = quantize_per_head(
+            torch.randn(shape, generator=dev_gen, device=dev, dtype=torch.float32)
+        )
+        value_cache, v_scale = quantize_per_head(
+            torch.randn(shape, generator=dev_gen, device=dev, dtype=torch.float32)
+        )
     query = torch.randn(bsz, hq, d, generator=dev_gen, device=dev, dtype=torch.float32).to(query_dtype)
     return PagedDecodeInputs(
         name=name,

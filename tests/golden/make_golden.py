@@ -70,8 +70,16 @@ def arange_on_cpu():
         torch.arange = real
 
 
-def load_reference(root: Path):
-    path = root / "scripts/smoke_cuda_paged_fp8_decode_op.py"
+KV16_CASES = [
+    # (case name, workload, batch, shrink, dtype): the non-quantised sibling
+    ("kv16-cfg2-coder3b-b4-bf16", "qwen2.5-coder-3b-b64", 4, 0.25, torch.bfloat16),
+    ("kv16-cfg3-qwen7b-b24-bf16", "qwen2.5-7b-b256", 24, 0.125, torch.bfloat16),
+    ("kv16-cfg4-llama8b-b2-fp16", "llama3-8b-long-b4", 2, 1.0 / 64, torch.float16),
+]
+
+
+def load_reference(root: Path, script: str = "scripts/smoke_cuda_paged_fp8_decode_op.py"):
+    path = root / script
     spec = importlib.util.spec_from_file_location("ref_smoke", path)
     module = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(module)
@@ -124,6 +132,20 @@ def main() -> int:
             k_scale=ks, v_scale=vs, cache_sha256=digest(kc, vc), output=out.clone(),
         )
         print("smoke", batch, context, hq, hkv, ks, vs)
+
+    # the fp16 / bf16 sibling: reference() of scripts/smoke_cuda_paged_decode_op.py:13-30
+    ref16 = load_reference(Path(args.reference_root), "scripts/smoke_cuda_paged_decode_op.py")
+    golden["kv16"] = {}
+    for name, workload, batch, shrink, dtype in KV16_CASES:
+        w = make_inputs(workload, seed=0, device="cpu", batch=batch, shrink=shrink, query_dtype=dtype, kv_dtype=dtype)
+        with arange_on_cpu():
+            out = ref16.reference(w.query, w.key_cache, w.value_cache, w.block_table.long(), w.seq_lens)
+        golden["kv16"][name] = dict(
+            workload=workload, batch=batch, shrink=shrink, dtype=str(dtype).replace("torch.", ""),
+            inputs_sha256=digest(w.query, w.key_cache, w.value_cache, w.block_table, w.seq_lens),
+            output=out.clone(),
+        )
+        print(name, tuple(out.shape), out.dtype, "tokens", int(w.seq_lens.sum()))
 
     torch.save(golden, HERE / "paged_decode_golden.pt")
     print("wrote", HERE / "paged_decode_golden.pt")

@@ -40,6 +40,20 @@ def test_oracle_reproduces_reference_smoke_recipe(golden):
         assert torch.equal(out.view(torch.int16), case["output"].view(torch.int16)), key
 
 
+@pytest.mark.parametrize(
+    "name", ["kv16-cfg2-coder3b-b4-bf16", "kv16-cfg3-qwen7b-b24-bf16", "kv16-cfg4-llama8b-b2-fp16"]
+)
+def test_kv16_oracle_reproduces_reference_outputs_bit_for_bit(golden, name):
+    """The non-quantised sibling against reference() of scripts/smoke_cuda_paged_decode_op.py."""
+    case = golden["kv16"][name]
+    dtype = getattr(torch, case["dtype"])
+    w = make_inputs(case["workload"], seed=0, device="cpu", batch=case["batch"], shrink=case["shrink"],
+                    query_dtype=dtype, kv_dtype=dtype)
+    assert digest(w.query, w.key_cache, w.value_cache, w.block_table, w.seq_lens) == case["inputs_sha256"]
+    out = oracle.reference_kv16(w.query, w.key_cache, w.value_cache, w.block_table.long(), w.seq_lens)
+    assert out.dtype == dtype and torch.equal(out.view(torch.int16), case["output"].view(torch.int16))
+
+
 def test_per_head_quantisation_matches_per_tensor_recipe_on_one_head():
     torch.manual_seed(3)
     x = torch.randn(5, 16, 1, 64)
