@@ -364,7 +364,9 @@ __device__ __forceinline__ void kv16_step(BalState<1>& st, uint32_t stage, const
       }
       s[u][c] = dead ? -INFINITY : s[u][c] * scale_log2;
     }
-  uint32_t pb[2][2];
+  // P^T B-fragments.  bf16 keeps 8 bits of a probability: there P goes in as two bf16 terms
+  // (p = hi + lo, 16 bits together) and the PV product takes two MMAs; f16 keeps 11 bits.
+  uint32_t pb[2][2], pl[2][2];
   {
     float mx[2], alpha[2];
 #pragma unroll
@@ -387,6 +389,11 @@ __device__ __forceinline__ void kv16_step(BalState<1>& st, uint32_t stage, const
       // (token i, heads 2j, 2j+1) -> transpose -> (tokens 2j, 2j+1; head i)
       pb[u][0] = movmatrix_trans(pack_kv16<BF16>(p0, p1));
       pb[u][1] = movmatrix_trans(pack_kv16<BF16>(p2, p3));
+      if constexpr (BF16) {
+        const auto hi = [](float x) { return __bfloat162float(__float2bfloat16_rn(x)); };
+        pl[u][0] = movmatrix_trans(pack_kv16<true>(p0 - hi(p0), p1 - hi(p1)));
+        pl[u][1] = movmatrix_trans(pack_kv16<true>(p2 - hi(p2), p3 - hi(p3)));
+      }
     }
     st.l[0][0] = st.l[0][0] * alpha[0] + sum[0];
     st.l[0][1] = st.l[0][1] * alpha[1] + sum[1];
@@ -419,6 +426,7 @@ __device__ __forceinline__ void kv16_step(BalState<1>& st, uint32_t stage, const
         ldsm_x4_trans(stage + (2 + u) * kTile + off, a);
         if (edge) { a[0] &= keep_lo; a[1] &= keep_lo; a[2] &= keep_hi; a[3] &= keep_hi; }
         mma_16816_kv16<BF16>(st.o[0][mt], a, pb[u][0], pb[u][1]);
+        if constexpr (BF16) mma_16816_kv16<true>(st.o[0][mt], a, pl[u][0], pl[u][1]);
       }
     }
   }
