@@ -18,7 +18,7 @@
 extern "C" {
 #endif
 
-#define PFD_ABI_VERSION 2
+#define PFD_ABI_VERSION 3
 
 /* element types of query / output / partial_output */
 #define PFD_DTYPE_F32 0
@@ -120,6 +120,13 @@ typedef struct pfd_decode_args {
   /* Unused (kept for layout compatibility): earlier builds counted retired pieces here. */
   int32_t* semaphores;
   int64_t num_semaphores;
+
+  /* Optional [batch + 1] int32: with it, block_table is a flat list of page ids and the pages of
+   * sequence b are block_table[page_indptr[b] ...] (FlashInfer's indptr / indices addressing,
+   * l20_paged_decode_split_indices_out_cuda, integrations/vllm/cuda/l20_paged_decode.cu:600-649);
+   * bt_stride_b is ignored.  Only the balanced persistent kernel reads it: a call that would
+   * run on the fixed-split grid or the shared-prefix pass is refused with PFD_ERR_UNSUPPORTED. */
+  const int32_t* page_indptr;
 } pfd_decode_args;
 
 /*

@@ -89,6 +89,7 @@ class DecodeArgs(C.Structure):
         ("stream", C.c_void_p),
         ("semaphores", C.c_void_p),
         ("num_semaphores", C.c_int64),
+        ("page_indptr", C.c_void_p),
     ]
 
 
@@ -141,8 +142,10 @@ def _stream(t: torch.Tensor) -> int:
 def decode_args(
     query, key_cache, value_cache, block_table, seq_lens, *, k_scale, v_scale, max_seq_len,
     split_size, output=None, packed_output=None, workspace=None, kv_start=0, sm_scale=0.0, flags=0,
+    page_indptr=None,
 ) -> DecodeArgs:
-    """Fill ``pfd_decode_args`` from torch tensors (device buffers)."""
+    """Fill ``pfd_decode_args`` from torch tensors (device buffers).  With ``page_indptr``
+    (int32 ``[B + 1]``) ``block_table`` is the flat list of page ids it indexes."""
     a = DecodeArgs()
     a.struct_size = C.sizeof(DecodeArgs)
     a.flags = flags
@@ -161,7 +164,9 @@ def decode_args(
     a.k_stride_page, a.k_stride_token, a.k_stride_head = key_cache.stride()[:3]
     a.v_stride_page, a.v_stride_token, a.v_stride_head = value_cache.stride()[:3]
     a.block_table = block_table.data_ptr()
-    a.bt_stride_b = block_table.stride(0)
+    a.bt_stride_b = block_table.stride(0) if page_indptr is None else 0
+    if page_indptr is not None:
+        a.page_indptr = page_indptr.data_ptr()
     a.seq_lens = seq_lens.data_ptr()
     if isinstance(k_scale, torch.Tensor):
         a.k_scale_per_head = k_scale.data_ptr()

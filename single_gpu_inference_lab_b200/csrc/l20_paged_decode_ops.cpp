@@ -34,7 +34,8 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
                 const c10::optional<at::Tensor>& k_scale_ph, const c10::optional<at::Tensor>& v_scale_ph,
                 double sm_scale, int64_t max_seq_len, int64_t split_size, int64_t kv_start,
                 int64_t flags, const c10::optional<at::Tensor>& semaphores = c10::nullopt,
-                int64_t prefix_len = 0, bool kv16 = false) {
+                int64_t prefix_len = 0, bool kv16 = false,
+                const c10::optional<at::Tensor>& page_indptr = c10::nullopt) {
   TORCH_CHECK(query.is_cuda(), "query must be CUDA");
   TORCH_CHECK(query.scalar_type() == at::kHalf || query.scalar_type() == at::kBFloat16,
               "query must be FP16 or BF16");
@@ -53,16 +54,25 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
   TORCH_CHECK(key_cache.sizes() == value_cache.sizes(), "K/V cache mismatch");
   TORCH_CHECK(key_cache.is_cuda() && value_cache.is_cuda() && block_table.is_cuda() && seq_lens.is_cuda(),
               "all operands must be CUDA");
-  TORCH_CHECK(block_table.scalar_type() == at::kInt && block_table.dim() == 2 &&
-                  block_table.stride(1) == 1 && block_table.size(0) == query.size(0),
-              "int32 block table");
+  if (page_indptr.has_value()) {  // block_table is the flat list of page ids the indptr indexes
+    TORCH_CHECK(block_table.scalar_type() == at::kInt && block_table.dim() == 1 && block_table.is_contiguous(),
+                "int32 page indices");
+    TORCH_CHECK(page_indptr->is_cuda() && page_indptr->scalar_type() == at::kInt && page_indptr->is_contiguous() &&
+                    page_indptr->numel() == query.size(0) + 1,
+                "int32 page indptr with batch + 1 entries");
+  } else {
+    TORCH_CHECK(block_table.scalar_type() == at::kInt && block_table.dim() == 2 &&
+                    block_table.stride(1) == 1 && block_table.size(0) == query.size(0),
+                "int32 block table");
+  }
   TORCH_CHECK(seq_lens.scalar_type() == at::kInt && seq_lens.is_contiguous() &&
                   seq_lens.numel() == query.size(0),
               "int32 sequence lengths");
   TORCH_CHECK(split_size >= 16 && split_size % 16 == 0, "split_size must be a multiple of 16");
   TORCH_CHECK(key_cache.size(2) > 0 && query.size(1) % key_cache.size(2) == 0,
               "Q heads must be divisible by KV heads");
-  TORCH_CHECK(max_seq_len >= 0 && max_seq_len <= block_table.size(1) * key_cache.size(1),
+  TORCH_CHECK(max_seq_len >= 0 && (page_indptr.has_value() ||
+                                   max_seq_len <= block_table.size(1) * key_cache.size(1)),
               "max_seq_len exceeds the block table");
 
   pfd_decode_args a{};
@@ -93,7 +103,8 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
   a.v_stride_token = value_cache.stride(1);
   a.v_stride_head = value_cache.stride(2);
   a.block_table = block_table.data_ptr<int32_t>();
-  a.bt_stride_b = block_table.stride(0);
+  a.bt_stride_b = page_indptr.has_value() ? 0 : block_table.stride(0);
+  if (page_indptr.has_value()) a.page_indptr = page_indptr->data_ptr<int32_t>();
   a.seq_lens = seq_lens.data_ptr<int32_t>();
   if (k_scale_ph.has_value()) {
     TORCH_CHECK(k_scale_ph->is_cuda() && k_scale_ph->scalar_type() == at::kFloat &&
@@ -182,6 +193,17 @@ at::Tensor paged_decode_split_out(at::Tensor query, at::Tensor key_cache, at::Te
              partial_sum, output, c10::nullopt, 1.0, 1.0, c10::nullopt, c10::nullopt, 0.0,
              max_seq_len, split_size, 0, 0, c10::nullopt, 0, /*kv16=*/true);
   return output;
+}
+
+// The same with FlashInfer's page addressing (indptr [B + 1], indices): argument list of
+// l20_paged_decode_split_indices_out_cuda (integrations/vllm/cuda/l20_paged_decode.cu:600-612).
+void paged_decode_split_indices_out(at::Tensor query, at::Tensor key_cache, at::Tensor value_cache,
+                                    at::Tensor page_indptr, at::Tensor page_indices, at::Tensor seq_lens,
+                                    at::Tensor partial_output, at::Tensor partial_max, at::Tensor partial_sum,
+                                    at::Tensor output, int64_t max_seq_len, int64_t split_size) {
+  run_decode(query, key_cache, value_cache, page_indices, seq_lens, partial_output, partial_max,
+             partial_sum, output, c10::nullopt, 1.0, 1.0, c10::nullopt, c10::nullopt, 0.0,
+             max_seq_len, split_size, 0, 0, c10::nullopt, 0, /*kv16=*/true, page_indptr);
 }
 
 void paged_decode_split_out_void(at::Tensor query, at::Tensor key_cache, at::Tensor value_cache,
@@ -277,6 +299,13 @@ TORCH_LIBRARY(l20_stack, module) {
       "Tensor(c!) partial_sum, Tensor(d!) output, "
       "int max_seq_len, int split_size) -> Tensor(d!)");
   module.def(
+      "paged_decode_split_indices_out("
+      "Tensor query, Tensor key_cache, Tensor value_cache, "
+      "Tensor page_indptr, Tensor page_indices, Tensor seq_lens, "
+      "Tensor(a!) partial_output, Tensor(b!) partial_max, "
+      "Tensor(c!) partial_sum, Tensor(d!) output, "
+      "int max_seq_len, int split_size) -> ()");
+  module.def(
       "paged_decode_fp8_e4m3_split_out("
       "Tensor query, Tensor key_cache, Tensor value_cache, "
       "Tensor block_table, Tensor seq_lens, "
@@ -303,6 +332,7 @@ TORCH_LIBRARY(l20_stack, module) {
 
 TORCH_LIBRARY_IMPL(l20_stack, CUDA, module) {
   module.impl("paged_decode_split_out", &paged_decode_split_out);
+  module.impl("paged_decode_split_indices_out", &paged_decode_split_indices_out);
   module.impl("paged_decode_fp8_e4m3_split_out", &paged_decode_fp8_e4m3_split_out);
   module.impl("paged_decode_fp8_e4m3_split_out_v2", &paged_decode_fp8_e4m3_split_out_v2);
   module.impl("shared_prefix_decode_fp8_e4m3", &shared_prefix_decode_fp8_e4m3);
@@ -312,6 +342,7 @@ TORCH_LIBRARY_IMPL(l20_stack, CUDA, module) {
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, module) {
   module.def("paged_decode_split_out", &paged_decode_split_out_void);
+  module.def("paged_decode_split_indices_out", &paged_decode_split_indices_out);
   module.def("paged_decode_fp8_e4m3_split_out", &paged_decode_fp8_e4m3_split_out_void);
   module.def("launch_count", []() { return pfd_launch_count(); });
 }

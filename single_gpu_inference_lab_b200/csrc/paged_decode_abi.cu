@@ -325,6 +325,10 @@ int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num
     if (int rc = sm_count_of(dev, &sms)) return rc;
     if (balanced_eligible(a, kp, sms)) return launch_balanced<QBF16, kChunkStages, kChunkWarps>(a, kp, sms, stream);
   }
+  if (a.page_indptr != nullptr)
+    return fail(PFD_ERR_UNSUPPORTED,
+                "page_indptr addressing needs the balanced kernel (head_dim 128, at most 8 query heads per KV "
+                "head, dense f32 workspace of pfd_balanced_workspace_rows() rows)");
   const dim3 grid(num_splits, a.num_kv_heads, a.batch);
   if (D == 128 && tma_eligible(a)) {
     g_last_path = PFD_PATH_FIXED_TMA;
@@ -375,6 +379,7 @@ pfd::KernelParams fill_params(const pfd_decode_args& a, int group, bool direct_o
   kp.value_cache = static_cast<const uint8_t*>(a.value_cache);
   kp.block_table = a.block_table;
   kp.seq_lens = a.seq_lens;
+  kp.page_indptr = a.page_indptr;
   kp.k_scale_ph = a.k_scale_per_head;
   kp.v_scale_ph = a.v_scale_per_head;
   kp.partial_output = a.partial_output;
@@ -577,6 +582,7 @@ int pfd_shared_prefix_decode_fp8_e4m3(const pfd_decode_args* args, int32_t prefi
   if (prefix_len <= 0 || prefix_len % pfd::kPage != 0 || prefix_len > a.max_seq_len)
     return fail(PFD_ERR_INVALID, "prefix_len must be a positive multiple of 16 not above max_seq_len");
   if (a.kv_start != 0) return fail(PFD_ERR_INVALID, "kv_start must be 0 for the shared-prefix pass");
+  if (a.page_indptr != nullptr) return fail(PFD_ERR_UNSUPPORTED, "the shared-prefix pass needs a block table");
   if (a.batch <= 0) return a.batch == 0 ? PFD_OK : fail(PFD_ERR_INVALID, "invalid query");
   if (a.num_kv_heads <= 0 || a.num_q_heads % a.num_kv_heads != 0 || a.num_q_heads / a.num_kv_heads > 16)
     return fail(PFD_ERR_INVALID, "Q heads must be divisible by KV heads (at most 16 per KV head)");

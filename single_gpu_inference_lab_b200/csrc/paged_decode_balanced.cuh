@@ -565,7 +565,9 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
     if (base_t < n && g < P1) {
       const int b = seq_of(g);
       const int page = page_first + 2 * (g - prefix[b]) + (lane & 1);
-      if (page <= (lens[b] - 1) / kPage) phys = page_of(p.block_table, p.bt_stride_b, b, page);
+      if (page <= (lens[b] - 1) / kPage)
+        phys = p.page_indptr ? __ldg(p.block_table + __ldg(p.page_indptr + b) + page)
+                             : page_of(p.block_table, p.bt_stride_b, b, page);
     }
     return phys;
   };

@@ -35,6 +35,7 @@ struct KernelParams {
   const uint8_t* __restrict__ value_cache;
   const int32_t* __restrict__ block_table;
   const int32_t* __restrict__ seq_lens;
+  const int32_t* __restrict__ page_indptr;  // optional: block_table is then a flat list, row b starts at page_indptr[b]
   const float* __restrict__ k_scale_ph;
   const float* __restrict__ v_scale_ph;
   void* partial_output;

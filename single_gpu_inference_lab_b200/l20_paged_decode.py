@@ -61,6 +61,30 @@ def paged_decode_split_out(
     )
 
 
+def paged_decode_split_indices_out(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    page_indptr: torch.Tensor,
+    page_indices: torch.Tensor,
+    seq_lens: torch.Tensor,
+    partial_output: torch.Tensor,
+    partial_max: torch.Tensor,
+    partial_sum: torch.Tensor,
+    output: torch.Tensor,
+    max_seq_len: int,
+    split_size: int,
+) -> torch.Tensor:
+    """The fp16 / bf16 cache operator with FlashInfer's page addressing: the pages of sequence
+    ``b`` are ``page_indices[page_indptr[b] : page_indptr[b + 1]]`` (reference launcher
+    integrations/vllm/cuda/l20_paged_decode.cu:600-649, exported through pybind only)."""
+    torch.ops.l20_stack.paged_decode_split_indices_out(
+        query, key_cache, value_cache, page_indptr, page_indices, seq_lens,
+        partial_output, partial_max, partial_sum, output, max_seq_len, split_size,
+    )
+    return output
+
+
 def paged_decode_fp8_e4m3_split_out(
     query: torch.Tensor,
     key_cache: torch.Tensor,
@@ -190,6 +214,11 @@ def _register_fake() -> None:
     def _(query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max, partial_sum,
           output, max_seq_len, split_size):
         return output
+
+    @torch.library.register_fake("l20_stack::paged_decode_split_indices_out")
+    def _(query, key_cache, value_cache, page_indptr, page_indices, seq_lens, partial_output, partial_max,
+          partial_sum, output, max_seq_len, split_size):
+        return None
 
     @torch.library.register_fake("l20_stack::paged_decode_fp8_e4m3_split_out")
     def _paged_decode_fp8_e4m3_split_out_fake(

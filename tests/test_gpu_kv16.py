@@ -150,3 +150,45 @@ def test_dispatcher_op_with_the_reference_smoke_call(built_libs):
         out2 = l20_paged_split_kv.l20_paged_split_kv_attention(q, kc, vc, table, lens, split_size=64)
         torch.cuda.synchronize()
         assert_within_gate(out2, exp, "wrapper with its own workspace")
+
+
+def test_indptr_indices_addressing_matches_block_table(cabi, built_libs):
+    """FlashInfer's addressing (flat page list + indptr) gives the bits the block table gives,
+    for the 16-bit operator (C ABI and dispatcher op) and for the FP8 operator's balanced path."""
+    from single_gpu_inference_lab_b200 import l20_paged_decode
+
+    w16 = make_inputs("qwen2.5-7b-b256", seed=3, batch=40, shrink=0.25, kv_dtype=torch.bfloat16).to(DEV)
+    w8 = make_inputs("qwen2.5-7b-b256", seed=3, batch=40, shrink=0.25).to(DEV)
+    for w, call in ((w16, cabi.paged_decode_kv16_split_out), (w8, cabi.paged_decode_fp8_e4m3_split_out)):
+        q = w.query
+        pages = (w.seq_lens.cpu() + 15) // 16
+        indptr = torch.zeros(q.shape[0] + 1, dtype=torch.int32)
+        indptr[1:] = torch.cumsum(pages, 0)
+        indices = torch.cat([w.block_table[b, : int(pages[b])].cpu() for b in range(q.shape[0])]).to(torch.int32)
+        splits = -(-cabi.balanced_workspace_rows(q.shape[1], w.key_cache.shape[2]) // (q.shape[0] * q.shape[1]))
+        outs = []
+        for table, ptr in ((w.block_table, None), (indices.to(DEV), indptr.to(DEV))):
+            out = torch.full_like(q, float("nan"))
+            call(q, w.key_cache, w.value_cache, table, w.seq_lens, k_scale=w.k_scale, v_scale=w.v_scale,
+                 max_seq_len=w.max_seq_len, split_size=512, output=out, workspace=workspace(q, splits),
+                 page_indptr=ptr)
+            torch.cuda.synchronize()
+            assert cabi.device_status() == 0
+            outs.append(out)
+        assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+        if w is w16:
+            assert_within_gate(outs[1], expected(w), "indptr addressing")
+            ws = workspace(q, splits)
+            out = torch.full_like(q, float("nan"))
+            l20_paged_decode.paged_decode_split_indices_out(
+                q, w.key_cache, w.value_cache, indptr.to(DEV), indices.to(DEV), w.seq_lens, ws[0], ws[1], ws[2], out,
+                w.max_seq_len, 512)
+            torch.cuda.synchronize()
+            assert torch.equal(out.view(torch.int16), outs[0].view(torch.int16))
+    # a call that cannot take the balanced path refuses the addressing instead of misreading the list
+    small = workspace(w8.query, -(-w8.max_seq_len // 512))
+    with pytest.raises(RuntimeError, match="page_indptr addressing needs the balanced kernel"):
+        cabi.paged_decode_fp8_e4m3_split_out(
+            w8.query, w8.key_cache, w8.value_cache, indices.to(DEV), w8.seq_lens, k_scale=w8.k_scale, v_scale=w8.v_scale,
+            max_seq_len=w8.max_seq_len, split_size=512, output=torch.empty_like(w8.query), workspace=small,
+            page_indptr=indptr.to(DEV), flags=8)
