@@ -13,6 +13,13 @@ FP8-KV decode steps through ``l20_paged_split_kv_attention_fp8`` when
 ``VLLM_L20_FP8_PAGED_TRACE=<path>`` appends one JSON line per dispatched step with the
 reference's keys.  ``--uninstall`` restores the backup ``flashinfer.py.l20-fp8-paged-backup``.
 
+The same block also carries the non-quantised sibling, which the reference installs with a
+second installer at the same call site (integrations/vllm/install_l20_paged_decode.py:95-170,
+always on for a few shapes): here ``VLLM_ENABLE_L20_PAGED_DECODE=1`` sends decode steps over
+fp16 / bf16 caches (head_dim 128, at most 8 query heads per KV head) through
+``l20_paged_split_kv_attention`` when ``should_use_l20_paged_split_kv`` agrees or
+``VLLM_L20_PAGED_FORCE=1``.
+
 What differs from the reference installer, because vLLM on sm_100 differs from vLLM on sm_89:
 
 * it is self-sufficient: the reference FP8 installer only works after its fp16 sibling
@@ -135,6 +142,42 @@ CALL_NEW = """                else:
                             int(l20_fp8_batch),
                             int(l20_fp8_max_seq),
                         )
+                    # the non-quantised sibling (fp16 / bf16 caches): VLLM_ENABLE_L20_PAGED_DECODE=1
+                    l20_kv16_enabled = (
+                        not l20_fp8_enabled
+                        and l20_os.getenv("VLLM_ENABLE_L20_PAGED_DECODE", "0") == "1"
+                        and current_platform.get_device_capability()
+                        == DeviceCapability(10, 0)
+                        and not torch.cuda.is_current_stream_capturing()
+                        and not is_quantized_kv_cache(self.kv_cache_dtype)
+                        and attn_metadata.decode.block_tables is not None
+                        and l20_fp8_max_seq > 0
+                        and decode_query.dim() == 3
+                        and decode_query.shape[-1] == 128
+                        and decode_query.dtype in (torch.float16, torch.bfloat16)
+                        and self.window_left == -1
+                        and not self.logits_soft_cap
+                        and abs(self.scale - decode_query.shape[-1] ** -0.5) < 1e-6
+                        and kv_cache_permute.dim() == 5
+                        and kv_cache_permute.shape[1] == 2
+                        and kv_cache_permute.shape[3 if l20_fp8_hnd else 2] == 16
+                        and kv_cache_permute.shape[-1] == 128
+                        and kv_cache_permute.dtype == decode_query.dtype
+                        and decode_query.shape[1]
+                        <= 8 * kv_cache_permute.shape[2 if l20_fp8_hnd else 3]
+                    )
+                    if (
+                        l20_kv16_enabled
+                        and l20_os.getenv("VLLM_L20_PAGED_FORCE", "0") != "1"
+                    ):
+                        from vllm.v1.attention.ops.l20_paged_split_kv import (
+                            should_use_l20_paged_split_kv,
+                        )
+
+                        l20_kv16_enabled = should_use_l20_paged_split_kv(
+                            int(l20_fp8_batch),
+                            int(l20_fp8_max_seq),
+                        )
                     if l20_fp8_enabled:
                         from vllm.v1.attention.ops.l20_paged_split_kv import (
                             allocate_l20_paged_split_kv_workspace,
@@ -193,6 +236,41 @@ CALL_NEW = """                else:
                                     )
                                     + "\\n"
                                 )
+                    elif l20_kv16_enabled:
+                        from vllm.v1.attention.ops.l20_paged_split_kv import (
+                            allocate_l20_paged_split_kv_workspace,
+                            l20_paged_split_kv_attention,
+                        )
+
+                        l20_kv16_shape = (
+                            l20_fp8_batch,
+                            decode_query.shape[1],
+                            decode_query.dtype,
+                        )
+                        if getattr(self, "_l20_kv16_workspace_shape", None) != l20_kv16_shape:
+                            self._l20_kv16_workspace = (
+                                allocate_l20_paged_split_kv_workspace(
+                                    decode_query,
+                                    l20_fp8_max_seq,
+                                    split_size=512,
+                                )
+                            )
+                            self._l20_kv16_workspace_shape = l20_kv16_shape
+                        key_cache, value_cache = kv_cache_permute.unbind(1)
+                        if l20_fp8_hnd:
+                            key_cache = key_cache.permute(0, 2, 1, 3)
+                            value_cache = value_cache.permute(0, 2, 1, 3)
+                        l20_paged_split_kv_attention(
+                            decode_query,
+                            key_cache,
+                            value_cache,
+                            attn_metadata.decode.block_tables,
+                            attn_metadata.decode.seq_lens,
+                            split_size=512,
+                            workspace=self._l20_kv16_workspace,
+                            max_seq_len=l20_fp8_max_seq,
+                            output=out_decode.view_as(decode_query),
+                        )
                     else:
                         decode_wrapper.run(
                             decode_query,

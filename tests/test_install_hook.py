@@ -46,6 +46,13 @@ def test_install_is_idempotent_compiles_and_uninstalls(tmp_path, built_libs, cap
         "DeviceCapability(10, 0)",
         "l20_fp8_paged_decode_run",
         "block_tables=block_table_tensor[:num_decodes]",
+        # the non-quantised sibling shares the call site
+        "VLLM_ENABLE_L20_PAGED_DECODE",
+        "VLLM_L20_PAGED_FORCE",
+        "should_use_l20_paged_split_kv",
+        "l20_paged_split_kv_attention(",
+        "not is_quantized_kv_cache(self.kv_cache_dtype)",
+        "metadata_stable=True",
     ):
         assert needle in patched, needle
     # the stock call survives as the fallback branch, exactly once more than the DCP call
