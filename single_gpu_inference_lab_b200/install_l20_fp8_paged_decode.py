@@ -18,7 +18,7 @@ second installer at the same call site (integrations/vllm/install_l20_paged_deco
 always on for a few shapes): here ``VLLM_ENABLE_L20_PAGED_DECODE=1`` sends decode steps over
 fp16 / bf16 caches (head_dim 128, at most 8 query heads per KV head) through
 ``l20_paged_split_kv_attention`` when ``should_use_l20_paged_split_kv`` agrees or
-``VLLM_L20_PAGED_FORCE=1``.
+``VLLM_L20_PAGED_FORCE=1``; ``VLLM_L20_PAGED_TRACE=<path>`` traces those steps.
 
 What differs from the reference installer, because vLLM on sm_100 differs from vLLM on sm_89:
 
@@ -271,6 +271,22 @@ CALL_NEW = """                else:
                             max_seq_len=l20_fp8_max_seq,
                             output=out_decode.view_as(decode_query),
                         )
+                        trace_path = l20_os.getenv("VLLM_L20_PAGED_TRACE")
+                        if trace_path:
+                            with open(trace_path, "a", encoding="utf-8") as trace_file:
+                                trace_file.write(
+                                    l20_json.dumps(
+                                        {
+                                            "event": "l20_paged_decode_run",
+                                            "batch": int(l20_fp8_batch),
+                                            "max_seq_len": int(l20_fp8_max_seq),
+                                            "q_heads": int(decode_query.shape[1]),
+                                            "kv_heads": int(key_cache.shape[2]),
+                                        },
+                                        sort_keys=True,
+                                    )
+                                    + "\\n"
+                                )
                     else:
                         decode_wrapper.run(
                             decode_query,

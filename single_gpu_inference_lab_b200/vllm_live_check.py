@@ -1,0 +1,179 @@
+#!/usr/bin/env python3
+"""Run the hook inside a live vLLM engine and compare it with the stock FlashInfer decode.
+
+What it does, on a B200 with vLLM installed and no model files at hand:
+
+1. builds an overlay of the installed ``vllm`` package in a work directory (symlinks, except
+   ``v1/attention/backends/flashinfer.py`` and ``v1/attention/ops/``, which are copies) and
+   runs ``install_l20_fp8_paged_decode.py`` on it -- the installed package is not touched;
+2. writes the config of a small Qwen2-shaped model (4 layers, 16 query / 2 KV heads of 128) and
+   lets vLLM create it with ``load_format="dummy"``; the weights are then re-drawn at a
+   realistic scale from a fixed seed, so that attention matters to the logits;
+3. generates greedily from 8 random prompts of 300-1500 tokens, twice, each in a fresh
+   process: stock, and with the hook's switches set (``--kv-cache-dtype fp8``: the FP8
+   operator; ``auto``: the fp16 / bf16 sibling);
+4. prints one JSON line: hook hits counted from the trace file, how many generated tokens agree
+   step by step, and the largest difference of the top-3 log-probabilities over the agreeing
+   steps (sequences are compared up to their first different token).
+
+This is the miniature of the reference's serving A/B campaign
+(scripts/run_vllm_l20_fp8_paged_campaign.sh): it checks that the patched branch is taken and
+gives the same answers, not serving throughput.
+"""
+
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import json
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+COPIED_PATHS = ("v1/attention/backends/flashinfer.py", "v1/attention/ops")
+
+CHILD = r'''
+import json, os, random, time
+import torch
+from vllm import LLM, SamplingParams
+
+llm = LLM(model=os.environ["LIVE_MODEL"], load_format="dummy", skip_tokenizer_init=True, enforce_eager=True,
+          kv_cache_dtype=os.environ["LIVE_KV"], block_size=16, dtype="bfloat16", max_model_len=4096,
+          gpu_memory_utilization=0.3, seed=0, enable_prefix_caching=False,
+          attention_config={"backend": "FLASHINFER", "use_trtllm_attention": False})
+
+
+def reinit(model):
+    g = torch.Generator(device="cuda").manual_seed(1234)
+    for name, p in sorted(model.named_parameters()):
+        if p.dim() == 1:
+            p.data.fill_(0.0 if name.endswith("bias") else 1.0)
+        else:
+            p.data.copy_(torch.randn(p.shape, generator=g, device=p.device, dtype=torch.float32).mul_(0.02))
+    return True
+
+
+llm.apply_model(reinit)
+rng = random.Random(0)
+prompts = [{"prompt_token_ids": [rng.randrange(10, 31000) for _ in range(rng.randrange(300, 1500))]} for _ in range(8)]
+params = SamplingParams(temperature=0.0, max_tokens=12, logprobs=3, detokenize=False, ignore_eos=True)
+t0 = time.time()
+outs = llm.generate(prompts, params)
+seconds = time.time() - t0
+result = []
+for o in outs:
+    c = o.outputs[0]
+    result.append([
+        {"token": int(tok), "top": sorted(((int(k), float(v.logprob)) for k, v in lp.items()), key=lambda x: -x[1])[:3]}
+        for tok, lp in zip(c.token_ids, c.logprobs)
+    ])
+print("LIVE_RESULT " + json.dumps({"seconds": seconds, "outputs": result}))
+'''
+
+
+def overlay(real: Path, dst: Path, copy_rel) -> None:
+    """``dst`` mirrors ``real`` with symlinks; the entries ``copy_rel`` (and the directories
+    that lead to them) are real copies."""
+    copy_rel = [Path(p) for p in copy_rel]
+
+    def build(rdir: Path, ddir: Path, rel: Path) -> None:
+        ddir.mkdir(parents=True, exist_ok=True)
+        for entry in rdir.iterdir():
+            erel, target = rel / entry.name, ddir / entry.name
+            if any(c == erel for c in copy_rel):
+                if entry.is_dir():
+                    shutil.copytree(entry, target, dirs_exist_ok=True)
+                else:
+                    shutil.copy2(entry, target)
+            elif entry.is_dir() and any(erel in c.parents for c in copy_rel):
+                build(entry, target, erel)
+            elif not target.exists():
+                target.symlink_to(entry)
+
+    build(real, dst, Path("."))
+
+
+def write_model_config(path: Path) -> None:
+    path.mkdir(parents=True, exist_ok=True)
+    config = {
+        "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 2048,
+        "num_attention_heads": 16, "num_key_value_heads": 2, "num_hidden_layers": 4, "intermediate_size": 4096,
+        "vocab_size": 32000, "max_position_embeddings": 8192, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+        "hidden_act": "silu", "tie_word_embeddings": False, "torch_dtype": "bfloat16", "bos_token_id": 1,
+        "eos_token_id": 2, "use_sliding_window": False,
+    }
+    (path / "config.json").write_text(json.dumps(config))
+
+
+def run_engine(work: Path, kv: str, extra_env: dict, log: Path) -> dict:
+    env = dict(os.environ)
+    env.update(extra_env)
+    env["PYTHONPATH"] = str(work / "vllm_src") + os.pathsep + env.get("PYTHONPATH", "")
+    env["VLLM_ENABLE_V1_MULTIPROCESSING"] = "0"
+    env["LIVE_MODEL"] = str(work / "model")
+    env["LIVE_KV"] = kv
+    proc = subprocess.run([sys.executable, "-c", CHILD], env=env, capture_output=True, text=True, timeout=1200)
+    log.write_text(proc.stdout[-20000:] + "\n==== stderr\n" + proc.stderr[-20000:])
+    for line in proc.stdout.splitlines():
+        if line.startswith("LIVE_RESULT "):
+            return json.loads(line[len("LIVE_RESULT "):])
+    raise RuntimeError(f"the engine run failed (exit code {proc.returncode}); see {log}")
+
+
+def main(argv: list[str] | None = None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    parser.add_argument("--kv-cache-dtype", choices=["fp8", "auto"], default="fp8")
+    parser.add_argument("--workdir", help="where the overlay, the model config and the logs go (default: a new temporary directory)")
+    args = parser.parse_args(argv)
+
+    spec = importlib.util.find_spec("vllm")  # located, not imported
+    if spec is None or not spec.submodule_search_locations:
+        raise RuntimeError("vLLM is not installed")
+    work = Path(args.workdir) if args.workdir else Path(tempfile.mkdtemp(prefix="l20-live-"))
+    work.mkdir(parents=True, exist_ok=True)
+    if (work / "vllm_src").exists():
+        shutil.rmtree(work / "vllm_src")
+    overlay(Path(list(spec.submodule_search_locations)[0]), work / "vllm_src" / "vllm", COPIED_PATHS)
+    sys.path.insert(0, str(PKG.parent))
+    from single_gpu_inference_lab_b200 import install_l20_fp8_paged_decode as installer
+
+    installer.main(["--vllm-source-dir", str(work / "vllm_src")])
+    write_model_config(work / "model")
+
+    kv = args.kv_cache_dtype
+    trace = work / f"trace_{kv}.jsonl"
+    trace.unlink(missing_ok=True)
+    stock = run_engine(work, kv, {}, work / f"{kv}_stock.log")
+    switches = (
+        {"VLLM_ENABLE_L20_FP8_PAGED_DECODE": "1", "VLLM_L20_FP8_PAGED_FORCE": "1", "VLLM_L20_FP8_PAGED_TRACE": str(trace)}
+        if kv == "fp8"
+        else {"VLLM_ENABLE_L20_PAGED_DECODE": "1", "VLLM_L20_PAGED_FORCE": "1", "VLLM_L20_PAGED_TRACE": str(trace)}
+    )
+    hooked = run_engine(work, kv, switches, work / f"{kv}_hook.log")
+
+    hits = [json.loads(line) for line in trace.read_text().splitlines()] if trace.exists() else []
+    compared = agree = 0
+    worst = 0.0
+    for a, b in zip(stock["outputs"], hooked["outputs"]):
+        for sa, sb in zip(a, b):
+            compared += 1
+            if sa["token"] != sb["token"]:
+                break
+            agree += 1
+            da, db = dict(sa["top"]), dict(sb["top"])
+            worst = max([worst] + [abs(da[k] - db[k]) for k in da if k in db])
+    print(json.dumps({
+        "kv_cache_dtype": kv, "hook_hits": len(hits),
+        "hook_hits_beyond_warmup": sum(1 for h in hits if h["max_seq_len"] > 64),
+        "generated_steps_compared": compared, "same_token": agree, "max_abs_logprob_diff": worst,
+        "workdir": str(work),
+    }))
+    return 0 if hits and agree >= compared * 0.8 else 1
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

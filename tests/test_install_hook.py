@@ -49,6 +49,8 @@ def test_install_is_idempotent_compiles_and_uninstalls(tmp_path, built_libs, cap
         # the non-quantised sibling shares the call site
         "VLLM_ENABLE_L20_PAGED_DECODE",
         "VLLM_L20_PAGED_FORCE",
+        "VLLM_L20_PAGED_TRACE",
+        "l20_paged_decode_run",
         "should_use_l20_paged_split_kv",
         "l20_paged_split_kv_attention(",
         "not is_quantized_kv_cache(self.kv_cache_dtype)",
@@ -92,3 +94,28 @@ def test_replace_once_semantics():
     assert installer.replace_once("a c", "b", "c", "x") == "a c"  # already applied
     with pytest.raises(RuntimeError, match="cannot find patch point: x"):
         installer.replace_once("a", "b", "zz", "x")
+
+
+def test_live_check_overlay_leaves_the_installed_package_alone(tmp_path):
+    """The overlay the live engine check patches: copies where the installer writes, symlinks
+    elsewhere."""
+    from single_gpu_inference_lab_b200 import vllm_live_check as live
+
+    real = tmp_path / "real/vllm"
+    (real / "v1/attention/backends").mkdir(parents=True)
+    (real / "v1/attention/ops").mkdir(parents=True)
+    (real / "model_executor").mkdir()
+    (real / "__init__.py").write_text("x = 1\n")
+    (real / "v1/attention/backends/flashinfer.py").write_text("stock\n")
+    (real / "v1/attention/backends/other.py").write_text("other\n")
+    (real / "v1/attention/ops/common.py").write_text("common\n")
+    dst = tmp_path / "overlay/vllm"
+    live.overlay(real, dst, live.COPIED_PATHS)
+    assert (dst / "__init__.py").is_symlink() and (dst / "model_executor").is_symlink()
+    assert (dst / "v1/attention/backends/other.py").is_symlink()
+    patched = dst / "v1/attention/backends/flashinfer.py"
+    assert not patched.is_symlink() and not (dst / "v1/attention/ops").is_symlink()
+    patched.write_text("patched\n")
+    (dst / "v1/attention/ops/new.py").write_text("new\n")
+    assert (real / "v1/attention/backends/flashinfer.py").read_text() == "stock\n"
+    assert not (real / "v1/attention/ops/new.py").exists()
