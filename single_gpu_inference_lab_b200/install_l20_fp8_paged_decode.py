@@ -7,7 +7,9 @@ Same role, command line and switches as the reference installer
 FP8-KV decode steps through ``l20_paged_split_kv_attention_fp8`` when
 
 * ``VLLM_ENABLE_L20_FP8_PAGED_DECODE=1`` is set, the GPU is sm_100, the step is not being
-  captured into a CUDA graph, the cache is a non-NVFP4 FP8 cache, head_dim is 64 or 128, and
+  captured into a CUDA graph (unless ``VLLM_L20_PAGED_CUDAGRAPH=1``: the operator allocates
+  nothing and synchronises nothing, so it can be recorded), the cache is a non-NVFP4 FP8 cache,
+  head_dim is 64 or 128, and
 * the policy ``should_use_l20_paged_fp8_split_kv`` agrees, or ``VLLM_L20_FP8_PAGED_FORCE=1``;
 
 ``VLLM_L20_FP8_PAGED_TRACE=<path>`` appends one JSON line per dispatched step with the
@@ -20,7 +22,12 @@ fp16 / bf16 caches (head_dim 128, at most 8 query heads per KV head) through
 ``l20_paged_split_kv_attention`` when ``should_use_l20_paged_split_kv`` agrees or
 ``VLLM_L20_PAGED_FORCE=1``; ``VLLM_L20_PAGED_TRACE=<path>`` traces those steps.
 
-What differs from the reference installer, because vLLM on sm_100 differs from vLLM on sm_89:
+What differs from the reference installer, because vLLM on sm_100 differs from vLLM on sm_89
+(and because in eager mode the host time of this block is most of a layer's decode time):
+
+* the switches, the GPU capability and the cache dtype are read once per attention layer and
+  kept on it (the reference reads the environment on every call); the cache views are made
+  once per cache buffer;
 
 * it is self-sufficient: the reference FP8 installer only works after its fp16 sibling
   installer has added ``block_tables / seq_lens / max_seq_len`` to ``FIDecode`` and nested the
@@ -108,32 +115,58 @@ CALL_OLD = """                else:
 """
 
 CALL_NEW = """                else:
+                    # What cannot change while the engine runs is decided once per layer: the
+                    # switches, the GPU, the cache dtype, the attention variant.
+                    l20_static = getattr(self, "_l20_static_gate", None)
+                    if l20_static is None:
+                        l20_common = (
+                            current_platform.get_device_capability()
+                            == DeviceCapability(10, 0)
+                            and self.window_left == -1
+                            and not self.logits_soft_cap
+                        )
+                        l20_static = self._l20_static_gate = {
+                            "fp8": l20_common
+                            and l20_os.getenv("VLLM_ENABLE_L20_FP8_PAGED_DECODE", "0") == "1"
+                            and not self.is_kvcache_nvfp4
+                            and is_quantized_kv_cache(self.kv_cache_dtype),
+                            "fp8_force": l20_os.getenv("VLLM_L20_FP8_PAGED_FORCE", "0") == "1",
+                            "fp8_trace": l20_os.getenv("VLLM_L20_FP8_PAGED_TRACE"),
+                            "kv16": l20_common
+                            and l20_os.getenv("VLLM_ENABLE_L20_PAGED_DECODE", "0") == "1"
+                            and not is_quantized_kv_cache(self.kv_cache_dtype),
+                            "kv16_force": l20_os.getenv("VLLM_L20_PAGED_FORCE", "0") == "1",
+                            "kv16_trace": l20_os.getenv("VLLM_L20_PAGED_TRACE"),
+                            # the operator is capturable: VLLM_L20_PAGED_CUDAGRAPH=1 keeps the hook on
+                            # while vLLM records its decode graphs (the reference always steps aside)
+                            "graphs": l20_os.getenv("VLLM_L20_PAGED_CUDAGRAPH", "0") == "1",
+                            "hnd": get_kv_cache_layout() == "HND",
+                            "views": None,
+                        }
                     l20_fp8_batch = decode_query.shape[0]
                     l20_fp8_max_seq = attn_metadata.decode.max_seq_len
-                    l20_fp8_force = (
-                        l20_os.getenv("VLLM_L20_FP8_PAGED_FORCE", "0") == "1"
-                    )
-                    l20_fp8_hnd = get_kv_cache_layout() == "HND"
-                    l20_fp8_enabled = (
-                        l20_os.getenv("VLLM_ENABLE_L20_FP8_PAGED_DECODE", "0") == "1"
-                        and current_platform.get_device_capability()
-                        == DeviceCapability(10, 0)
-                        and not torch.cuda.is_current_stream_capturing()
-                        and not self.is_kvcache_nvfp4
-                        and is_quantized_kv_cache(self.kv_cache_dtype)
+                    l20_fp8_hnd = l20_static["hnd"]
+                    l20_dynamic = (
+                        (l20_static["fp8"] or l20_static["kv16"])
+                        and (
+                            l20_static["graphs"]
+                            or not torch.cuda.is_current_stream_capturing()
+                        )
                         and attn_metadata.decode.block_tables is not None
                         and l20_fp8_max_seq > 0
                         and decode_query.dim() == 3
-                        and decode_query.shape[-1] in (64, 128)
-                        and self.window_left == -1
-                        and not self.logits_soft_cap
                         and abs(self.scale - decode_query.shape[-1] ** -0.5) < 1e-6
                         and kv_cache_permute.dim() == 5
                         and kv_cache_permute.shape[1] == 2
                         and kv_cache_permute.shape[3 if l20_fp8_hnd else 2] == 16
                         and kv_cache_permute.shape[-1] == decode_query.shape[-1]
                     )
-                    if l20_fp8_enabled and not l20_fp8_force:
+                    l20_fp8_enabled = (
+                        l20_dynamic
+                        and l20_static["fp8"]
+                        and decode_query.shape[-1] in (64, 128)
+                    )
+                    if l20_fp8_enabled and not l20_static["fp8_force"]:
                         from vllm.v1.attention.ops.l20_paged_split_kv import (
                             should_use_l20_paged_fp8_split_kv,
                         )
@@ -144,32 +177,15 @@ CALL_NEW = """                else:
                         )
                     # the non-quantised sibling (fp16 / bf16 caches): VLLM_ENABLE_L20_PAGED_DECODE=1
                     l20_kv16_enabled = (
-                        not l20_fp8_enabled
-                        and l20_os.getenv("VLLM_ENABLE_L20_PAGED_DECODE", "0") == "1"
-                        and current_platform.get_device_capability()
-                        == DeviceCapability(10, 0)
-                        and not torch.cuda.is_current_stream_capturing()
-                        and not is_quantized_kv_cache(self.kv_cache_dtype)
-                        and attn_metadata.decode.block_tables is not None
-                        and l20_fp8_max_seq > 0
-                        and decode_query.dim() == 3
+                        l20_dynamic
+                        and l20_static["kv16"]
                         and decode_query.shape[-1] == 128
                         and decode_query.dtype in (torch.float16, torch.bfloat16)
-                        and self.window_left == -1
-                        and not self.logits_soft_cap
-                        and abs(self.scale - decode_query.shape[-1] ** -0.5) < 1e-6
-                        and kv_cache_permute.dim() == 5
-                        and kv_cache_permute.shape[1] == 2
-                        and kv_cache_permute.shape[3 if l20_fp8_hnd else 2] == 16
-                        and kv_cache_permute.shape[-1] == 128
                         and kv_cache_permute.dtype == decode_query.dtype
                         and decode_query.shape[1]
                         <= 8 * kv_cache_permute.shape[2 if l20_fp8_hnd else 3]
                     )
-                    if (
-                        l20_kv16_enabled
-                        and l20_os.getenv("VLLM_L20_PAGED_FORCE", "0") != "1"
-                    ):
+                    if l20_kv16_enabled and not l20_static["kv16_force"]:
                         from vllm.v1.attention.ops.l20_paged_split_kv import (
                             should_use_l20_paged_split_kv,
                         )
@@ -178,16 +194,35 @@ CALL_NEW = """                else:
                             int(l20_fp8_batch),
                             int(l20_fp8_max_seq),
                         )
-                    if l20_fp8_enabled:
+                    if l20_fp8_enabled or l20_kv16_enabled:
                         from vllm.v1.attention.ops.l20_paged_split_kv import (
                             allocate_l20_paged_split_kv_workspace,
+                            l20_paged_split_kv_attention,
                             l20_paged_split_kv_attention_fp8,
                         )
 
+                        # logical [pages, 16, Hkv, D] views of the layer's cache, made once per buffer
+                        l20_views = l20_static["views"]
+                        if l20_views is None or l20_views[0] != kv_cache_permute.data_ptr():
+                            key_cache, value_cache = kv_cache_permute.unbind(1)
+                            if l20_fp8_hnd:
+                                # [pages, Hkv, 16, D] -> logical [pages, 16, Hkv, D] view
+                                key_cache = key_cache.permute(0, 2, 1, 3)
+                                value_cache = value_cache.permute(0, 2, 1, 3)
+                            if l20_fp8_enabled and key_cache.dtype == torch.uint8:
+                                key_cache = key_cache.view(torch.float8_e4m3fn)
+                                value_cache = value_cache.view(torch.float8_e4m3fn)
+                            l20_views = l20_static["views"] = (
+                                kv_cache_permute.data_ptr(),
+                                key_cache,
+                                value_cache,
+                            )
+                        key_cache, value_cache = l20_views[1], l20_views[2]
                         l20_fp8_shape = (
                             l20_fp8_batch,
                             decode_query.shape[1],
                             (l20_fp8_max_seq + 511) // 512,
+                            decode_query.dtype,
                         )
                         if getattr(self, "_l20_fp8_workspace_shape", None) != l20_fp8_shape:
                             self._l20_fp8_workspace = (
@@ -198,14 +233,7 @@ CALL_NEW = """                else:
                                 )
                             )
                             self._l20_fp8_workspace_shape = l20_fp8_shape
-                        key_cache, value_cache = kv_cache_permute.unbind(1)
-                        if l20_fp8_hnd:
-                            # [pages, Hkv, 16, D] -> logical [pages, 16, Hkv, D] view
-                            key_cache = key_cache.permute(0, 2, 1, 3)
-                            value_cache = value_cache.permute(0, 2, 1, 3)
-                        if key_cache.dtype == torch.uint8:
-                            key_cache = key_cache.view(torch.float8_e4m3fn)
-                            value_cache = value_cache.view(torch.float8_e4m3fn)
+                    if l20_fp8_enabled:
                         l20_paged_split_kv_attention_fp8(
                             decode_query,
                             key_cache,
@@ -220,7 +248,7 @@ CALL_NEW = """                else:
                             workspace=self._l20_fp8_workspace,
                             metadata_stable=True,  # built once per model step
                         )
-                        trace_path = l20_os.getenv("VLLM_L20_FP8_PAGED_TRACE")
+                        trace_path = l20_static["fp8_trace"]
                         if trace_path:
                             with open(trace_path, "a", encoding="utf-8") as trace_file:
                                 trace_file.write(
@@ -237,29 +265,6 @@ CALL_NEW = """                else:
                                     + "\\n"
                                 )
                     elif l20_kv16_enabled:
-                        from vllm.v1.attention.ops.l20_paged_split_kv import (
-                            allocate_l20_paged_split_kv_workspace,
-                            l20_paged_split_kv_attention,
-                        )
-
-                        l20_kv16_shape = (
-                            l20_fp8_batch,
-                            decode_query.shape[1],
-                            decode_query.dtype,
-                        )
-                        if getattr(self, "_l20_kv16_workspace_shape", None) != l20_kv16_shape:
-                            self._l20_kv16_workspace = (
-                                allocate_l20_paged_split_kv_workspace(
-                                    decode_query,
-                                    l20_fp8_max_seq,
-                                    split_size=512,
-                                )
-                            )
-                            self._l20_kv16_workspace_shape = l20_kv16_shape
-                        key_cache, value_cache = kv_cache_permute.unbind(1)
-                        if l20_fp8_hnd:
-                            key_cache = key_cache.permute(0, 2, 1, 3)
-                            value_cache = value_cache.permute(0, 2, 1, 3)
                         l20_paged_split_kv_attention(
                             decode_query,
                             key_cache,
@@ -267,11 +272,11 @@ CALL_NEW = """                else:
                             attn_metadata.decode.block_tables,
                             attn_metadata.decode.seq_lens,
                             split_size=512,
-                            workspace=self._l20_kv16_workspace,
+                            workspace=self._l20_fp8_workspace,
                             max_seq_len=l20_fp8_max_seq,
                             output=out_decode.view_as(decode_query),
                         )
-                        trace_path = l20_os.getenv("VLLM_L20_PAGED_TRACE")
+                        trace_path = l20_static["kv16_trace"]
                         if trace_path:
                             with open(trace_path, "a", encoding="utf-8") as trace_file:
                                 trace_file.write(

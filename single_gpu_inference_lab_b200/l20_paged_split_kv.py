@@ -33,10 +33,40 @@ def _cdiv(a: int, b: int) -> int:
     return -(-int(a) // int(b))
 
 
-def _ops():
-    from . import l20_paged_decode  # loads l20_paged_decode_ops.so or raises
+_OPS = None
+_CAPABILITY: dict = {}
+_SCALE_VECTORS: dict = {}
 
-    return l20_paged_decode
+
+def _ops():
+    global _OPS
+    if _OPS is None:
+        from . import l20_paged_decode  # loads l20_paged_decode_ops.so or raises
+
+        _OPS = l20_paged_decode
+    return _OPS
+
+
+def _on_required_gpu(tensor: torch.Tensor) -> bool:
+    """Capability gate, looked up once per device (this runs once per layer and decode step)."""
+    if not tensor.is_cuda:
+        return False
+    key = tensor.device.index
+    if key not in _CAPABILITY:
+        _CAPABILITY[key] = torch.cuda.get_device_capability(tensor.device) == REQUIRED_CAPABILITY
+    return _CAPABILITY[key]
+
+
+def _scale_vector(value: float, num_kv_heads: int, device: torch.device) -> torch.Tensor:
+    """``[Hkv]`` float32 tensor filled with a per-layer Python-float scale, built once per
+    (device, heads, value): no fill kernel on the per-step path."""
+    key = (device.index, num_kv_heads, float(value))
+    vec = _SCALE_VECTORS.get(key)
+    if vec is None:
+        if len(_SCALE_VECTORS) > 4096:
+            _SCALE_VECTORS.clear()
+        vec = _SCALE_VECTORS[key] = torch.full((num_kv_heads,), float(value), device=device, dtype=torch.float32)
+    return vec
 
 
 BALANCED_WARPS_PER_SM = 8  # warps of the balanced persistent kernel on every SM
@@ -134,7 +164,7 @@ def l20_paged_split_kv_attention_fp8(
     running before it on the stream does not write ``block_table`` or ``seq_lens`` -- true for
     every layer of a model step, whose metadata is built once -- so that it may read them while
     that kernel drains (``PFD_FLAG_EARLY_METADATA``)."""
-    if not query.is_cuda or torch.cuda.get_device_capability(query.device) != REQUIRED_CAPABILITY:
+    if not _on_required_gpu(query):
         raise RuntimeError("requires an SM100 GPU")
     if query.ndim != 3 or key_cache.ndim != 4 or value_cache.shape != key_cache.shape:
         raise RuntimeError("expected Q=[B,H,D], cache=[pages,page,Hkv,D]")
@@ -177,7 +207,7 @@ def l20_paged_split_kv_attention_fp8(
                 if s.dtype == torch.float32 and s.device == query.device and s.shape == (num_kv_heads,) and s.is_contiguous():
                     return s  # the common case costs nothing
                 return s.to(device=query.device, dtype=torch.float32).reshape(-1).expand(num_kv_heads).contiguous()
-            return torch.full((num_kv_heads,), float(s), device=query.device, dtype=torch.float32)
+            return _scale_vector(s, num_kv_heads, query.device)
 
         ops.paged_decode_fp8_e4m3_split_out_v2(
             query, key_cache, value_cache, block_table, seq_lens,
@@ -209,7 +239,7 @@ def l20_paged_split_kv_attention(
     type.  ``page_granular`` / ``grouped_gqa`` of the reference select between its Triton kernel
     variants and have no counterpart here.  ``max_seq_len`` (not in the reference, which always
     reads it back from the device, :517) avoids that host synchronisation."""
-    if not query.is_cuda or torch.cuda.get_device_capability(query.device) != REQUIRED_CAPABILITY:
+    if not _on_required_gpu(query):
         raise RuntimeError("requires an SM100 GPU")
     if query.ndim != 3 or key_cache.ndim != 4 or value_cache.shape != key_cache.shape:
         raise RuntimeError("expected Q=[B,H,D], cache=[pages,page,Hkv,D]")

@@ -16,9 +16,12 @@ What it does, on a B200 with vLLM installed and no model files at hand:
    step by step, and the largest difference of the top-3 log-probabilities over the agreeing
    steps (sequences are compared up to their first different token).
 
-This is the miniature of the reference's serving A/B campaign
-(scripts/run_vllm_l20_fp8_paged_campaign.sh): it checks that the patched branch is taken and
-gives the same answers, not serving throughput.
+With ``--ab`` it times decoding instead (the miniature of the reference's serving A/B campaign,
+scripts/run_vllm_l20_fp8_paged_campaign.sh): a model of ``--layers`` layers of the same shape,
+``--batch`` prompts of ``--prompt-len`` tokens, ``--new-tokens`` greedy tokens; per engine the
+time of a 1-token generation is subtracted from that of a (1 + new-tokens)-token generation
+(best of two each), which leaves the decode steps; eager mode, so launch overheads of the whole
+model are in both numbers.
 """
 
 from __future__ import annotations
@@ -41,7 +44,8 @@ import json, os, random, time
 import torch
 from vllm import LLM, SamplingParams
 
-llm = LLM(model=os.environ["LIVE_MODEL"], load_format="dummy", skip_tokenizer_init=True, enforce_eager=True,
+llm = LLM(model=os.environ["LIVE_MODEL"], load_format="dummy", skip_tokenizer_init=True,
+          enforce_eager=os.environ.get("LIVE_GRAPHS", "0") != "1",
           kv_cache_dtype=os.environ["LIVE_KV"], block_size=16, dtype="bfloat16", max_model_len=4096,
           gpu_memory_utilization=0.3, seed=0, enable_prefix_caching=False,
           attention_config={"backend": "FLASHINFER", "use_trtllm_attention": False})
@@ -56,6 +60,25 @@ def reinit(model):
             p.data.copy_(torch.randn(p.shape, generator=g, device=p.device, dtype=torch.float32).mul_(0.02))
     return True
 
+
+AB = int(os.environ.get("LIVE_AB", "0"))
+if AB:
+    batch, plen, new = (int(os.environ[k]) for k in ("LIVE_BATCH", "LIVE_PROMPT_LEN", "LIVE_NEW_TOKENS"))
+    rng = random.Random(0)
+    prompts = [{"prompt_token_ids": [rng.randrange(10, 31000) for _ in range(plen)]} for _ in range(batch)]
+    def timed(max_tokens):
+        best = 1e9
+        for _ in range(2):
+            t0 = time.time()
+            llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=max_tokens, detokenize=False, ignore_eos=True),
+                         use_tqdm=False)
+            best = min(best, time.time() - t0)
+        return best
+    timed(2)  # warm-up of every code path
+    t1, tn = timed(1), timed(1 + new)
+    print("LIVE_RESULT " + json.dumps({"prefill_seconds": t1, "total_seconds": tn,
+                                       "ms_per_decode_step": (tn - t1) / new * 1e3}))
+    raise SystemExit(0)
 
 llm.apply_model(reinit)
 rng = random.Random(0)
@@ -97,11 +120,11 @@ def overlay(real: Path, dst: Path, copy_rel) -> None:
     build(real, dst, Path("."))
 
 
-def write_model_config(path: Path) -> None:
+def write_model_config(path: Path, layers: int = 4) -> None:
     path.mkdir(parents=True, exist_ok=True)
     config = {
         "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 2048,
-        "num_attention_heads": 16, "num_key_value_heads": 2, "num_hidden_layers": 4, "intermediate_size": 4096,
+        "num_attention_heads": 16, "num_key_value_heads": 2, "num_hidden_layers": layers, "intermediate_size": 4096,
         "vocab_size": 32000, "max_position_embeddings": 8192, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
         "hidden_act": "silu", "tie_word_embeddings": False, "torch_dtype": "bfloat16", "bos_token_id": 1,
         "eos_token_id": 2, "use_sliding_window": False,
@@ -128,6 +151,14 @@ def main(argv: list[str] | None = None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--kv-cache-dtype", choices=["fp8", "auto"], default="fp8")
     parser.add_argument("--workdir", help="where the overlay, the model config and the logs go (default: a new temporary directory)")
+    parser.add_argument("--ab", action="store_true", help="time decode steps, stock against hooked")
+    parser.add_argument("--layers", type=int, default=36)
+    parser.add_argument("--batch", type=int, default=64)
+    parser.add_argument("--prompt-len", type=int, default=2048)
+    parser.add_argument("--new-tokens", type=int, default=32)
+    parser.add_argument("--cuda-graphs", action="store_true",
+                        help="let vLLM compile and record CUDA graphs (both engines), and keep the hook on while "
+                             "it records (VLLM_L20_PAGED_CUDAGRAPH=1); hook hits are then counted at recording time")
     args = parser.parse_args(argv)
 
     spec = importlib.util.find_spec("vllm")  # located, not imported
@@ -142,18 +173,38 @@ def main(argv: list[str] | None = None) -> int:
     from single_gpu_inference_lab_b200 import install_l20_fp8_paged_decode as installer
 
     installer.main(["--vllm-source-dir", str(work / "vllm_src")])
-    write_model_config(work / "model")
+    write_model_config(work / "model", args.layers if args.ab else 4)
 
     kv = args.kv_cache_dtype
+    if args.ab:
+        shape = {"LIVE_AB": "1", "LIVE_BATCH": str(args.batch), "LIVE_PROMPT_LEN": str(args.prompt_len),
+                 "LIVE_NEW_TOKENS": str(args.new_tokens), "LIVE_GRAPHS": "1" if args.cuda_graphs else "0"}
+        on = ({"VLLM_ENABLE_L20_FP8_PAGED_DECODE": "1", "VLLM_L20_FP8_PAGED_FORCE": "1"} if kv == "fp8"
+              else {"VLLM_ENABLE_L20_PAGED_DECODE": "1", "VLLM_L20_PAGED_FORCE": "1"})
+        stock = run_engine(work, kv, shape, work / f"{kv}_ab_stock.log")
+        if args.cuda_graphs:
+            on["VLLM_L20_PAGED_CUDAGRAPH"] = "1"
+        hooked = run_engine(work, kv, {**shape, **on}, work / f"{kv}_ab_hook.log")
+        print(json.dumps({
+            "kv_cache_dtype": kv, "layers": args.layers, "batch": args.batch, "prompt_len": args.prompt_len,
+            "new_tokens": args.new_tokens, "mode": "cuda graphs" if args.cuda_graphs else "eager",
+            "stock_ms_per_decode_step": round(stock["ms_per_decode_step"], 4),
+            "hook_ms_per_decode_step": round(hooked["ms_per_decode_step"], 4),
+            "stock_prefill_s": round(stock["prefill_seconds"], 4), "hook_prefill_s": round(hooked["prefill_seconds"], 4),
+        }))
+        return 0
     trace = work / f"trace_{kv}.jsonl"
     trace.unlink(missing_ok=True)
-    stock = run_engine(work, kv, {}, work / f"{kv}_stock.log")
+    graphs = {"LIVE_GRAPHS": "1"} if args.cuda_graphs else {}
+    stock = run_engine(work, kv, graphs, work / f"{kv}_stock.log")
     switches = (
         {"VLLM_ENABLE_L20_FP8_PAGED_DECODE": "1", "VLLM_L20_FP8_PAGED_FORCE": "1", "VLLM_L20_FP8_PAGED_TRACE": str(trace)}
         if kv == "fp8"
         else {"VLLM_ENABLE_L20_PAGED_DECODE": "1", "VLLM_L20_PAGED_FORCE": "1", "VLLM_L20_PAGED_TRACE": str(trace)}
     )
-    hooked = run_engine(work, kv, switches, work / f"{kv}_hook.log")
+    if args.cuda_graphs:
+        switches["VLLM_L20_PAGED_CUDAGRAPH"] = "1"
+    hooked = run_engine(work, kv, {**graphs, **switches}, work / f"{kv}_hook.log")
 
     hits = [json.loads(line) for line in trace.read_text().splitlines()] if trace.exists() else []
     compared = agree = 0
@@ -167,7 +218,7 @@ def main(argv: list[str] | None = None) -> int:
             da, db = dict(sa["top"]), dict(sb["top"])
             worst = max([worst] + [abs(da[k] - db[k]) for k in da if k in db])
     print(json.dumps({
-        "kv_cache_dtype": kv, "hook_hits": len(hits),
+        "kv_cache_dtype": kv, "mode": "cuda graphs" if args.cuda_graphs else "eager", "hook_hits": len(hits),
         "hook_hits_beyond_warmup": sum(1 for h in hits if h["max_seq_len"] > 64),
         "generated_steps_compared": compared, "same_token": agree, "max_abs_logprob_diff": worst,
         "workdir": str(work),
