@@ -40,15 +40,17 @@ PKG = Path(__file__).resolve().parent
 COPIED_PATHS = ("v1/attention/backends/flashinfer.py", "v1/attention/ops")
 
 CHILD = r'''
-import json, os, random, time
+import json, math, os, random, time
 import torch
 from vllm import LLM, SamplingParams
 
 llm = LLM(model=os.environ["LIVE_MODEL"], load_format="dummy", skip_tokenizer_init=True,
           enforce_eager=os.environ.get("LIVE_GRAPHS", "0") != "1",
-          kv_cache_dtype=os.environ["LIVE_KV"], block_size=16, dtype="bfloat16", max_model_len=4096,
-          gpu_memory_utilization=0.3, seed=0, enable_prefix_caching=False,
-          attention_config={"backend": "FLASHINFER", "use_trtllm_attention": False})
+          kv_cache_dtype=os.environ["LIVE_KV"], block_size=16, dtype="bfloat16",
+          max_model_len=int(os.environ.get("LIVE_MAX_LEN", "4096")), max_num_seqs=int(os.environ.get("LIVE_BATCH", "64")),
+          gpu_memory_utilization=float(os.environ.get("LIVE_MEM", "0.3")), seed=0, enable_prefix_caching=False,
+          attention_config={"backend": "FLASHINFER",
+                            **({} if os.environ.get("LIVE_TRTLLM_AUTO", "0") == "1" else {"use_trtllm_attention": False})})
 
 
 def reinit(model):
@@ -65,7 +67,11 @@ AB = int(os.environ.get("LIVE_AB", "0"))
 if AB:
     batch, plen, new = (int(os.environ[k]) for k in ("LIVE_BATCH", "LIVE_PROMPT_LEN", "LIVE_NEW_TOKENS"))
     rng = random.Random(0)
-    prompts = [{"prompt_token_ids": [rng.randrange(10, 31000) for _ in range(plen)]} for _ in range(batch)]
+    if os.environ.get("LIVE_LOGUNIFORM", "0") == "1":  # lengths log-uniform in [16, plen]
+        lens = [max(16, int(round(math.exp(rng.uniform(math.log(16), math.log(plen)))))) for _ in range(batch)]
+    else:
+        lens = [plen] * batch
+    prompts = [{"prompt_token_ids": [rng.randrange(10, 31000) for _ in range(n)]} for n in lens]
     def timed(max_tokens):
         best = 1e9
         for _ in range(2):
@@ -120,12 +126,14 @@ def overlay(real: Path, dst: Path, copy_rel) -> None:
     build(real, dst, Path("."))
 
 
-def write_model_config(path: Path, layers: int = 4) -> None:
+def write_model_config(path: Path, layers: int = 4, q_heads: int = 16, kv_heads: int = 2,
+                       intermediate: int = 4096) -> None:
     path.mkdir(parents=True, exist_ok=True)
     config = {
-        "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 2048,
-        "num_attention_heads": 16, "num_key_value_heads": 2, "num_hidden_layers": layers, "intermediate_size": 4096,
-        "vocab_size": 32000, "max_position_embeddings": 8192, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
+        "architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 128 * q_heads,
+        "num_attention_heads": q_heads, "num_key_value_heads": kv_heads, "num_hidden_layers": layers,
+        "intermediate_size": intermediate,
+        "vocab_size": 32000, "max_position_embeddings": 32768, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0,
         "hidden_act": "silu", "tie_word_embeddings": False, "torch_dtype": "bfloat16", "bos_token_id": 1,
         "eos_token_id": 2, "use_sliding_window": False,
     }
@@ -156,6 +164,12 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--batch", type=int, default=64)
     parser.add_argument("--prompt-len", type=int, default=2048)
     parser.add_argument("--new-tokens", type=int, default=32)
+    parser.add_argument("--q-heads", type=int, default=16, help="with --ab: query heads of 128 (hidden size = 128 x this)")
+    parser.add_argument("--kv-heads", type=int, default=2)
+    parser.add_argument("--intermediate", type=int, default=4096)
+    parser.add_argument("--stock-auto", action="store_true",
+                        help="with --ab: a third engine with use_trtllm_attention left to vLLM's own choice")
+    parser.add_argument("--log-uniform", action="store_true", help="with --ab: prompt lengths log-uniform in [16, prompt-len]")
     parser.add_argument("--cuda-graphs", action="store_true",
                         help="let vLLM compile and record CUDA graphs (both engines), and keep the hook on while "
                              "it records (VLLM_L20_PAGED_CUDAGRAPH=1); hook hits are then counted at recording time")
@@ -173,20 +187,30 @@ def main(argv: list[str] | None = None) -> int:
     from single_gpu_inference_lab_b200 import install_l20_fp8_paged_decode as installer
 
     installer.main(["--vllm-source-dir", str(work / "vllm_src")])
-    write_model_config(work / "model", args.layers if args.ab else 4)
+    if args.ab:
+        write_model_config(work / "model", args.layers, args.q_heads, args.kv_heads, args.intermediate)
+    else:
+        write_model_config(work / "model")
 
     kv = args.kv_cache_dtype
     if args.ab:
         shape = {"LIVE_AB": "1", "LIVE_BATCH": str(args.batch), "LIVE_PROMPT_LEN": str(args.prompt_len),
-                 "LIVE_NEW_TOKENS": str(args.new_tokens), "LIVE_GRAPHS": "1" if args.cuda_graphs else "0"}
+                 "LIVE_NEW_TOKENS": str(args.new_tokens), "LIVE_GRAPHS": "1" if args.cuda_graphs else "0",
+                 "LIVE_LOGUNIFORM": "1" if args.log_uniform else "0", "LIVE_MEM": "0.5",
+                 "LIVE_MAX_LEN": str(max(4096, args.prompt_len + args.new_tokens + 16))}
         on = ({"VLLM_ENABLE_L20_FP8_PAGED_DECODE": "1", "VLLM_L20_FP8_PAGED_FORCE": "1"} if kv == "fp8"
               else {"VLLM_ENABLE_L20_PAGED_DECODE": "1", "VLLM_L20_PAGED_FORCE": "1"})
         stock = run_engine(work, kv, shape, work / f"{kv}_ab_stock.log")
         if args.cuda_graphs:
             on["VLLM_L20_PAGED_CUDAGRAPH"] = "1"
         hooked = run_engine(work, kv, {**shape, **on}, work / f"{kv}_ab_hook.log")
+        auto = None
+        if args.stock_auto:  # what vLLM picks by itself on this GPU (may be the TRTLLM-gen decode, which the hook never sees)
+            auto = run_engine(work, kv, {**shape, "LIVE_TRTLLM_AUTO": "1"}, work / f"{kv}_ab_stock_auto.log")
         print(json.dumps({
-            "kv_cache_dtype": kv, "layers": args.layers, "batch": args.batch, "prompt_len": args.prompt_len,
+            **({"stock_auto_backend_ms_per_decode_step": round(auto["ms_per_decode_step"], 4)} if auto else {}),
+            "kv_cache_dtype": kv, "layers": args.layers, "q_heads": args.q_heads, "kv_heads": args.kv_heads,
+            "batch": args.batch, "prompt_len": args.prompt_len, "log_uniform_lengths": args.log_uniform,
             "new_tokens": args.new_tokens, "mode": "cuda graphs" if args.cuda_graphs else "eager",
             "stock_ms_per_decode_step": round(stock["ms_per_decode_step"], 4),
             "hook_ms_per_decode_step": round(hooked["ms_per_decode_step"], 4),
