@@ -24,8 +24,7 @@ MIN_CHUNK_COST = 8
 
 
 def pairs_of(seq_len: int, kv_start: int = 0) -> int:
-    first = kv_start // PAGE
-    pages = -(-seq_len // PAGE) - first if seq_len > first * PAGE else 0
+    pages = -(-seq_len // PAGE) - kv_start // PAGE if seq_len > kv_start else 0
     return (pages + 1) // 2
 
 

@@ -60,9 +60,11 @@ struct Chunking {
   }
 };
 
-// Page pairs of a sequence of `len` tokens when attention starts at page `page_first`.
-__device__ __forceinline__ int pairs_of(int len, int page_first) {
-  const int pages = len > page_first * kPage ? (len + kPage - 1) / kPage - page_first : 0;
+// Page pairs of a sequence of `len` tokens when attention starts at token `kv_start`: none if
+// the sequence ends at or before it (a page that holds only tokens in front of kv_start would
+// give a piece without a single live token, hence 0 / 0).
+__device__ __forceinline__ int pairs_of(int len, int kv_start) {
+  const int pages = len > kv_start ? (len + kPage - 1) / kPage - kv_start / kPage : 0;
   return (pages + 1) >> 1;
 }
 
@@ -500,7 +502,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       if (b < B) {
         const int len = p.seq_lens[b];
         lens[b] = len;
-        local += pairs_of(len, page_first);
+        local += pairs_of(len, p.kv_start);
       }
     }
     int incl = local;  // inclusive scan over the CTA's threads
@@ -518,7 +520,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       const int b = b0 + q;
       if (b < B) {
         prefix[b] = run;
-        run += pairs_of(lens[b], page_first);
+        run += pairs_of(lens[b], p.kv_start);
       }
     }
     if (threadIdx.x == NT - 1) prefix[B] = before + incl;
@@ -785,12 +787,11 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
   const int part = WPR == 1 ? 0 : warp;
   if (row >= cp.batch * p.num_q_heads) return;  // WPR == 1 only: whole warps, no barrier below
   const int b = row / p.num_q_heads, hq = row % p.num_q_heads;
-  const int page_first = p.kv_start / kPage;
   // seq_lens is an input of the whole step, not a result of the chunk kernel: the chunking is
   // recomputed here while that kernel is still running.
   int below = 0, all = 0;
   for (int x = lane; x < cp.batch; x += 32) {
-    const int np = pairs_of(__ldg(p.seq_lens + x), page_first);
+    const int np = pairs_of(__ldg(p.seq_lens + x), p.kv_start);
     all += np;
     below += x < b ? np : 0;
   }
@@ -799,7 +800,7 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
     all += __shfl_xor_sync(0xffffffffu, all, off);
     below += __shfl_xor_sync(0xffffffffu, below, off);
   }
-  const int np = pairs_of(__ldg(p.seq_lens + b), page_first);
+  const int np = pairs_of(__ldg(p.seq_lens + b), p.kv_start);
   const Chunking chunks(all, cp.batch, max(cp.num_warps / p.num_kv_heads, 1), cp.piece_cost);
   const int s0 = chunks.first_unit(below, b);
   const int w_first = np > 0 ? chunks.chunk_of(s0) : 0;
