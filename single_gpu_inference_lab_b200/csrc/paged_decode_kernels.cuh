@@ -437,6 +437,23 @@ __device__ __forceinline__ void cta_merge_and_store(WarpState<D>& st, const Kern
   }
 }
 
+// Rows of a (sequence, kv head) with nothing to attend (seq_len <= kv_start), written by the
+// partial kernel when no merge kernel follows (one split, direct output): zeros, or (0, -inf, 0)
+// in packed form -- what the merge kernel writes for such rows when it does run.
+template <int D>
+__device__ __forceinline__ void write_empty_rows(const KernelParams& p, int b, int kvh) {
+  for (int e = threadIdx.x; e < p.group * D; e += blockDim.x) {
+    const int hq = kvh * p.group + e / D, d = e % D;
+    if (p.packed_output != nullptr) {
+      float* dst = p.packed_output + ((int64_t)b * p.num_q_heads + hq) * (D + 2);
+      dst[d] = 0.f;
+      if (d == 0) { dst[D] = -INFINITY; dst[D + 1] = 0.f; }
+    } else {
+      reinterpret_cast<uint16_t*>(p.output)[(int64_t)b * p.o_stride_b + (int64_t)hq * p.o_stride_h + d] = 0;
+    }
+  }
+}
+
 // Split-KV partial kernel, plain global loads (any 16-byte-aligned strides).
 // grid = (splits, kv heads, sequences), block = NWARPS * 32.
 template <int D, bool QBF16, int NWARPS>
@@ -447,7 +464,11 @@ paged_decode_fp8_partial_ldg_kernel(const KernelParams p) {
   const int seq_len = p.seq_lens[b];
   const int lo = p.kv_start + split * p.split_size;
   const int hi = min(lo + p.split_size, seq_len);
-  if (lo >= hi) { pdl_wait(); return; }  // the merge kernel derives the live split count from seq_len
+  if (lo >= hi) {  // the merge kernel derives the live split count from seq_len
+    pdl_wait();
+    if (split == 0 && gridDim.x == 1 && p.direct_out) write_empty_rows<D>(p, b, kvh);
+    return;
+  }
   const int nsplits_seq = (seq_len - p.kv_start + p.split_size - 1) / p.split_size;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
 
@@ -639,7 +660,11 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   }
   const int seq_len = p.seq_lens[b];
   const int hi = min(lo + p.split_size, seq_len);
-  if (lo >= hi) { pdl_wait(); return; }
+  if (lo >= hi) {
+    pdl_wait();
+    if (split == 0 && gridDim.x == 1 && p.direct_out) write_empty_rows<D>(p, b, kvh);
+    return;
+  }
   if (p.slot_offset == 0 && p.early_metadata) pdl_wait();
   const int nsplits_seq = (seq_len - p.kv_start + p.split_size - 1) / p.split_size;
 

@@ -151,3 +151,33 @@ def test_graph_replay_with_metadata_rewritten_in_place(built_libs, kv16):
         torch.cuda.synchronize()
         exp = expected(new_q, kc, vc, new_table, new_lens, ks, vs)
         assert_within_gate(ws[3], exp, f"replay {step} kv16={kv16}")
+
+
+@pytest.mark.parametrize("flags,d", [(8, 128), (1, 128), (0, 64)])
+def test_random_cases_fixed_split_grid(cabi, flags, d):
+    """The same for the fixed-split grid (TMA and plain loads) and head_dim 64, small split sizes."""
+    rng = random.Random(77 + flags + d)
+    for case in range(30):
+        q, kc, vc, table, lens, ks, vs = random_case(rng, False)
+        if d == 64:
+            q, kc, vc = q[..., :64].contiguous(), kc[..., :64].contiguous(), vc[..., :64].contiguous()
+        hkv = kc.shape[2]
+        kv_start = rng.choice([0, 0, 5, 16, 37]) if int(lens.max()) > 40 else 0
+        exp = expected(q, kc, vc, table, lens, ks, vs, kv_start)
+        split = rng.choice([16, 64, 256, 1024])
+        g = [t.to(DEV) for t in (q, kc, vc, table, lens)]
+        splits = max(1, -(-(int(lens.max()) - kv_start) // split))
+        ws = (
+            torch.full((q.shape[0], q.shape[1], splits, d), float("nan"), device=DEV),
+            torch.full((q.shape[0], q.shape[1], splits), float("nan"), device=DEV),
+            torch.full((q.shape[0], q.shape[1], splits), float("nan"), device=DEV),
+            None,
+        )
+        out = torch.full_like(g[0], float("nan"))
+        what = f"case {case}: flags={flags} d={d} B={q.shape[0]} Hq={q.shape[1]} Hkv={hkv} max={int(lens.max())} kv_start={kv_start} split={split}"
+        cabi.paged_decode_fp8_e4m3_split_out(*g, k_scale=ks.to(DEV), v_scale=vs.to(DEV), max_seq_len=int(lens.max()),
+                                             split_size=split, output=out, workspace=ws, kv_start=kv_start, flags=flags)
+        torch.cuda.synchronize()
+        assert cabi.device_status() == 0, what
+        assert cabi.last_path() == (1 if (flags & 1 or d == 64) else 2), what
+        assert_within_gate(out, exp, what)
