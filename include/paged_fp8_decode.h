@@ -238,6 +238,45 @@ int pfd_device_status(int32_t* status);
 int pfd_last_path(void);
 
 /*
+ * The producer step: rotary embedding of the new tokens' query and key (in place) and append of
+ * key / value to the paged cache, optionally quantised to FP8-e4m3 with per-kv-head scales.
+ * Replaces l20_rope_and_cache (integrations/vllm/l20_rope_kv.py:256-328), which handles fp16 /
+ * bf16 caches only ("quantized KV cache is not supported", :273-274).
+ * Strides count elements.  cos_sin_cache is [max_position, rotary_dim]: cos of the rotary_dim / 2
+ * frequencies, then sin (vLLM's layout), float32 or the query's type.  slot_mapping[t] =
+ * block * block_size + offset, negative = do not store that token.  cache_dtype: PFD_DTYPE_F16 /
+ * PFD_DTYPE_BF16 (must equal query_dtype) or PFD_DTYPE_E4M3; scales are read for E4M3 only.
+ */
+#define PFD_DTYPE_E4M3 3
+typedef struct pfd_rope_args {
+  uint32_t struct_size; /* sizeof(pfd_rope_args) */
+  int32_t num_tokens, num_q_heads, num_kv_heads, head_dim, rotary_dim, block_size;
+  int32_t is_neox;       /* 1: pairs (i, i + rotary_dim / 2); 0: pairs (2i, 2i + 1) */
+  int32_t query_dtype;   /* of query, key, value */
+  int32_t cos_sin_dtype; /* PFD_DTYPE_F32 or query_dtype */
+  int32_t cache_dtype;
+  void* query;           /* [tokens, num_q_heads, head_dim], rotated in place */
+  int64_t q_stride_t, q_stride_h;
+  void* key;             /* [tokens, num_kv_heads, head_dim], rotated in place */
+  int64_t k_stride_t, k_stride_h;
+  const void* value;
+  int64_t v_stride_t, v_stride_h;
+  const int64_t* positions;
+  const void* cos_sin_cache;
+  int64_t cos_sin_stride;
+  const int64_t* slot_mapping;
+  void* key_cache;       /* logical [blocks, block_size, num_kv_heads, head_dim] */
+  int64_t kc_stride_block, kc_stride_token, kc_stride_head;
+  void* value_cache;
+  int64_t vc_stride_block, vc_stride_token, vc_stride_head;
+  float k_scale, v_scale;
+  const float* k_scale_per_head; /* optional [num_kv_heads], overrides k_scale */
+  const float* v_scale_per_head;
+  void* stream;
+} pfd_rope_args;
+int pfd_rope_quant_append(const pfd_rope_args* args);
+
+/*
  * Debug aid for tuning: while `device_buffer` (uint64 [grid][8], device memory owned by the
  * caller) is set, thread 0 of every CTA of the balanced kernel stores nanosecond timestamps
  * (%globaltimer) of its phases there.  NULL switches it off (the default).

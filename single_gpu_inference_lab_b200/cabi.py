@@ -29,6 +29,7 @@ EXPORTS = (
     "pfd_shared_prefix_decode_fp8_e4m3",
     "pfd_merge_packed",
     "pfd_resolve_slots",
+    "pfd_rope_quant_append",
     "pfd_balanced_workspace_rows",
     "pfd_device_status",
     "pfd_debug_phase_times",

@@ -253,6 +253,71 @@ void shared_prefix_decode_fp8_e4m3(at::Tensor query, at::Tensor key_cache, at::T
              c10::nullopt, prefix_len);
 }
 
+// Rotary embedding of the new tokens' query and key (in place) + append of key / value to the
+// paged cache; argument list of the reference's l20_rope_and_cache
+// (integrations/vllm/l20_rope_kv.py:256-266) plus the scales an FP8 cache needs.
+void rope_and_cache(at::Tensor query, at::Tensor key, at::Tensor value, at::Tensor positions,
+                    at::Tensor cos_sin_cache, bool is_neox, at::Tensor key_cache, at::Tensor value_cache,
+                    at::Tensor slot_mapping, c10::optional<at::Tensor> k_scale, c10::optional<at::Tensor> v_scale) {
+  TORCH_CHECK(query.is_cuda() && (query.scalar_type() == at::kHalf || query.scalar_type() == at::kBFloat16),
+              "l20_rope_and_cache supports FP16 and BF16");
+  TORCH_CHECK(key.scalar_type() == query.scalar_type() && value.scalar_type() == query.scalar_type(),
+              "Q, K, and V must use the same dtype");
+  TORCH_CHECK(query.dim() == 3 && key.dim() == 3 && value.dim() == 3, "Q, K, and V must be [tokens, heads, head_dim]");
+  TORCH_CHECK(key.sizes() == value.sizes() && query.size(0) == key.size(0) && query.size(2) == key.size(2),
+              "Q, K, and V shapes are incompatible");
+  TORCH_CHECK(query.stride(2) == 1 && key.stride(2) == 1 && value.stride(2) == 1, "head_dim must be contiguous");
+  const bool fp8 = key_cache.scalar_type() == at::kFloat8_e4m3fn || key_cache.scalar_type() == at::kByte;
+  TORCH_CHECK(fp8 || key_cache.scalar_type() == query.scalar_type(), "the caches must be FP8-e4m3 or have the query's dtype");
+  TORCH_CHECK(key_cache.dim() == 4 && value_cache.sizes() == key_cache.sizes() &&
+                  value_cache.scalar_type() == key_cache.scalar_type() && key_cache.stride(3) == 1 &&
+                  value_cache.stride(3) == 1,
+              "cache must use NHD [blocks, block, heads, dim]");
+  TORCH_CHECK(key_cache.size(2) == key.size(1) && key_cache.size(3) == key.size(2), "cache head shape must match K/V");
+  TORCH_CHECK(positions.scalar_type() == at::kLong && slot_mapping.scalar_type() == at::kLong &&
+                  positions.is_contiguous() && slot_mapping.is_contiguous() && positions.numel() == query.size(0) &&
+                  slot_mapping.numel() == query.size(0),
+              "positions and slot_mapping must match token count");
+  TORCH_CHECK(cos_sin_cache.dim() == 2 && cos_sin_cache.stride(1) == 1 &&
+                  (cos_sin_cache.scalar_type() == at::kFloat || cos_sin_cache.scalar_type() == query.scalar_type()),
+              "cos_sin_cache must be [max_position, rotary_dim] in float32 or the query's dtype");
+  pfd_rope_args a{};
+  a.struct_size = sizeof(a);
+  a.num_tokens = static_cast<int32_t>(query.size(0));
+  a.num_q_heads = static_cast<int32_t>(query.size(1));
+  a.num_kv_heads = static_cast<int32_t>(key.size(1));
+  a.head_dim = static_cast<int32_t>(query.size(2));
+  a.rotary_dim = static_cast<int32_t>(cos_sin_cache.size(1));
+  a.block_size = static_cast<int32_t>(key_cache.size(1));
+  a.is_neox = is_neox ? 1 : 0;
+  a.query_dtype = dtype_code(query.scalar_type(), "query");
+  a.cos_sin_dtype = cos_sin_cache.scalar_type() == at::kFloat ? PFD_DTYPE_F32 : a.query_dtype;
+  a.cache_dtype = fp8 ? PFD_DTYPE_E4M3 : a.query_dtype;
+  a.query = query.data_ptr(); a.q_stride_t = query.stride(0); a.q_stride_h = query.stride(1);
+  a.key = key.data_ptr(); a.k_stride_t = key.stride(0); a.k_stride_h = key.stride(1);
+  a.value = value.data_ptr(); a.v_stride_t = value.stride(0); a.v_stride_h = value.stride(1);
+  a.positions = positions.data_ptr<int64_t>();
+  a.cos_sin_cache = cos_sin_cache.data_ptr();
+  a.cos_sin_stride = cos_sin_cache.stride(0);
+  a.slot_mapping = slot_mapping.data_ptr<int64_t>();
+  a.key_cache = key_cache.data_ptr();
+  a.kc_stride_block = key_cache.stride(0); a.kc_stride_token = key_cache.stride(1); a.kc_stride_head = key_cache.stride(2);
+  a.value_cache = value_cache.data_ptr();
+  a.vc_stride_block = value_cache.stride(0); a.vc_stride_token = value_cache.stride(1); a.vc_stride_head = value_cache.stride(2);
+  a.k_scale = a.v_scale = 1.0f;
+  if (fp8) {
+    TORCH_CHECK(k_scale.has_value() && v_scale.has_value(), "FP8 caches need k_scale and v_scale");
+    for (const at::Tensor* s : {&*k_scale, &*v_scale})
+      TORCH_CHECK(s->is_cuda() && s->scalar_type() == at::kFloat && s->is_contiguous() && s->numel() == key.size(1),
+                  "scales must be float32 CUDA tensors with one entry per KV head");
+    a.k_scale_per_head = k_scale->data_ptr<float>();
+    a.v_scale_per_head = v_scale->data_ptr<float>();
+  }
+  const at::cuda::CUDAGuard guard(query.device());
+  a.stream = at::cuda::getCurrentCUDAStream().stream();
+  TORCH_CHECK(pfd_rope_quant_append(&a) == PFD_OK, pfd_last_error());
+}
+
 void merge_packed_partials(at::Tensor packed, at::Tensor output) {
   TORCH_CHECK(packed.is_cuda() && packed.scalar_type() == at::kFloat && packed.is_contiguous() &&
                   packed.dim() == 4,
@@ -326,6 +391,10 @@ TORCH_LIBRARY(l20_stack, module) {
       "Tensor query, Tensor key_cache, Tensor value_cache, Tensor block_table, Tensor seq_lens, "
       "Tensor(a!) partial_output, Tensor(b!) partial_max, Tensor(c!) partial_sum, Tensor(d!) output, "
       "Tensor k_scale, Tensor v_scale, float sm_scale, int max_seq_len, int split_size, int prefix_len) -> ()");
+  module.def(
+      "rope_and_cache(Tensor(a!) query, Tensor(b!) key, Tensor value, Tensor positions, Tensor cos_sin_cache, "
+      "bool is_neox, Tensor(c!) key_cache, Tensor(d!) value_cache, Tensor slot_mapping, "
+      "Tensor? k_scale, Tensor? v_scale) -> ()");
   module.def("merge_packed_partials(Tensor packed, Tensor(a!) output) -> ()");
   module.def("resolve_slots(Tensor block_table, Tensor seq_lens, Tensor(a!) slots) -> ()");
 }
@@ -336,6 +405,7 @@ TORCH_LIBRARY_IMPL(l20_stack, CUDA, module) {
   module.impl("paged_decode_fp8_e4m3_split_out", &paged_decode_fp8_e4m3_split_out);
   module.impl("paged_decode_fp8_e4m3_split_out_v2", &paged_decode_fp8_e4m3_split_out_v2);
   module.impl("shared_prefix_decode_fp8_e4m3", &shared_prefix_decode_fp8_e4m3);
+  module.impl("rope_and_cache", &rope_and_cache);
   module.impl("merge_packed_partials", &merge_packed_partials);
   module.impl("resolve_slots", &resolve_slots);
 }

@@ -14,6 +14,7 @@
 #include "paged_decode_balanced.cuh"
 #include "shared_prefix_dense.cuh"
 #include "paged_decode_kernels.cuh"
+#include "rope_kv_append.cuh"
 
 namespace {
 
@@ -670,6 +671,52 @@ int pfd_paged_decode_fp8_e4m3_split_out_noalloc(const pfd_decode_args* args) {
   a.partial_stride_s = 1;
   a.flags |= PFD_FLAG_FIXED_SPLITS;  // the array is sized for split_size-sized splits
   return pfd_paged_decode_fp8_e4m3_split_out(&a);
+}
+
+int pfd_rope_quant_append(const pfd_rope_args* args) {
+  if (args == nullptr) return fail(PFD_ERR_INVALID, "args is NULL");
+  if (args->struct_size != sizeof(pfd_rope_args))
+    return fail(PFD_ERR_INVALID, "pfd_rope_args size mismatch: caller %u, library %zu", args->struct_size,
+                sizeof(pfd_rope_args));
+  const pfd_rope_args& a = *args;
+  if (a.num_tokens < 0 || a.num_q_heads <= 0 || a.num_kv_heads <= 0 || a.head_dim <= 0 || a.block_size <= 0)
+    return fail(PFD_ERR_INVALID, "invalid geometry");
+  if (a.query_dtype != PFD_DTYPE_F16 && a.query_dtype != PFD_DTYPE_BF16)
+    return fail(PFD_ERR_INVALID, "query must be FP16 or BF16");
+  if (a.rotary_dim <= 0 || a.rotary_dim > a.head_dim || a.rotary_dim % 2)
+    return fail(PFD_ERR_INVALID, "invalid cos_sin_cache rotary dimension");
+  if (a.cos_sin_dtype != PFD_DTYPE_F32 && a.cos_sin_dtype != a.query_dtype)
+    return fail(PFD_ERR_INVALID, "cos_sin_cache must be float32 or have the query's dtype");
+  if (a.cache_dtype != PFD_DTYPE_E4M3 && a.cache_dtype != a.query_dtype)
+    return fail(PFD_ERR_INVALID, "the caches must be FP8-e4m3 or have the query's dtype");
+  if (a.num_tokens == 0) return PFD_OK;
+  if (!a.query || !a.key || !a.value || !a.positions || !a.cos_sin_cache || !a.slot_mapping || !a.key_cache ||
+      !a.value_cache)
+    return fail(PFD_ERR_INVALID, "NULL operand");
+  if (a.cache_dtype == PFD_DTYPE_E4M3 &&
+      ((!a.k_scale_per_head && !(a.k_scale > 0.f)) || (!a.v_scale_per_head && !(a.v_scale > 0.f))))
+    return fail(PFD_ERR_INVALID, "FP8 caches need positive scales");
+  pfd::RopeParams p{};
+  p.query = a.query; p.key = a.key; p.value = a.value;
+  p.positions = a.positions; p.cos_sin_cache = a.cos_sin_cache; p.slot_mapping = a.slot_mapping;
+  p.key_cache = a.key_cache; p.value_cache = a.value_cache;
+  p.k_scale_ph = a.k_scale_per_head; p.v_scale_ph = a.v_scale_per_head;
+  p.k_scale = a.k_scale; p.v_scale = a.v_scale;
+  p.q_stride_t = a.q_stride_t; p.q_stride_h = a.q_stride_h;
+  p.k_stride_t = a.k_stride_t; p.k_stride_h = a.k_stride_h;
+  p.v_stride_t = a.v_stride_t; p.v_stride_h = a.v_stride_h;
+  p.kc_stride_block = a.kc_stride_block; p.kc_stride_token = a.kc_stride_token; p.kc_stride_head = a.kc_stride_head;
+  p.vc_stride_block = a.vc_stride_block; p.vc_stride_token = a.vc_stride_token; p.vc_stride_head = a.vc_stride_head;
+  p.cs_stride = a.cos_sin_stride;
+  p.num_tokens = a.num_tokens; p.num_q_heads = a.num_q_heads; p.num_kv_heads = a.num_kv_heads;
+  p.head_dim = a.head_dim; p.rotary_dim = a.rotary_dim; p.block_size = a.block_size;
+  p.is_neox = a.is_neox ? 1 : 0;
+  p.cos_sin_f32 = a.cos_sin_dtype == PFD_DTYPE_F32 ? 1 : 0;
+  p.cache_fp8 = a.cache_dtype == PFD_DTYPE_E4M3 ? 1 : 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
+  if (a.query_dtype == PFD_DTYPE_BF16) pfd::rope_quant_append_kernel<true><<<a.num_tokens, 256, 0, stream>>>(p);
+  else pfd::rope_quant_append_kernel<false><<<a.num_tokens, 256, 0, stream>>>(p);
+  return check_launch("rope + append kernel");
 }
 
 int pfd_last_path(void) { return g_last_path; }

@@ -734,24 +734,24 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
             dst[D + 1] = lsum[c];
           }
         }
-        continue;
-      }
-      float v[16];
-#pragma unroll
-      for (int mt = 0; mt < 8; ++mt) {
-        v[2 * mt] = st.o[0][mt][c] * vs;
-        v[2 * mt + 1] = st.o[0][mt][2 + c] * vs;
-      }
-      if (whole) {
-        store_row16<QBF16>(p, cur.b, hq, 16 * i, v, st.m[0][c] * kLn2, lsum[c], i == 0);
       } else {
-        const int64_t r = chunk_slot_row(grp, which, p.num_q_heads, hq);
-        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.partial_output) + r * D + 16 * i);
+        float v[16];
 #pragma unroll
-        for (int f = 0; f < 4; ++f) dst[f] = make_float4(v[4 * f], v[4 * f + 1], v[4 * f + 2], v[4 * f + 3]);
-        if (i == 0) {
-          p.partial_max[r] = st.m[0][c] * kLn2;
-          p.partial_sum[r] = lsum[c];
+        for (int mt = 0; mt < 8; ++mt) {
+          v[2 * mt] = st.o[0][mt][c] * vs;
+          v[2 * mt + 1] = st.o[0][mt][2 + c] * vs;
+        }
+        if (whole) {
+          store_row16<QBF16>(p, cur.b, hq, 16 * i, v, st.m[0][c] * kLn2, lsum[c], i == 0);
+        } else {
+          const int64_t r = chunk_slot_row(grp, which, p.num_q_heads, hq);
+          float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.partial_output) + r * D + 16 * i);
+#pragma unroll
+          for (int f = 0; f < 4; ++f) dst[f] = make_float4(v[4 * f], v[4 * f + 1], v[4 * f + 2], v[4 * f + 3]);
+          if (i == 0) {
+            p.partial_max[r] = st.m[0][c] * kLn2;
+            p.partial_sum[r] = lsum[c];
+          }
         }
       }
     }

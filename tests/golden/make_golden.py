@@ -21,6 +21,7 @@ import argparse
 import os
 import contextlib
 import hashlib
+import importlib
 import importlib.util
 import sys
 from pathlib import Path
@@ -146,6 +147,26 @@ def main() -> int:
             output=out.clone(),
         )
         print(name, tuple(out.shape), out.dtype, "tokens", int(w.seq_lens.sum()))
+
+    # the producer step: rope_kv_reference of src/l20_stack/ops/triton_rope_kv.py:147-173
+    sys.path.insert(0, str(Path(args.reference_root) / "src"))  # the module imports its own package
+    rope = importlib.import_module("l20_stack.ops.triton_rope_kv")
+    golden["rope"] = {}
+    for name, tokens, hkv, d, rot, dtype in [("t37-h2-d128-r128-bf16", 37, 2, 128, 128, torch.bfloat16),
+                                             ("t64-h4-d128-r64-fp16", 64, 4, 128, 64, torch.float16),
+                                             ("t9-h8-d64-r64-bf16", 9, 8, 64, 64, torch.bfloat16)]:
+        gen = torch.Generator().manual_seed(41)
+        k = torch.randn(tokens, hkv, d, generator=gen).to(dtype)
+        v = torch.randn(tokens, hkv, d, generator=gen).to(dtype)
+        angle = torch.rand(tokens, rot // 2, generator=gen) * 6.2831853
+        cos, sin = torch.cos(angle), torch.sin(angle)
+        slots = torch.randperm(4 * tokens, generator=gen)[:tokens]
+        kc = torch.zeros(4 * tokens, hkv, d, dtype=dtype)
+        vc = torch.zeros_like(kc)
+        kc, vc = rope.rope_kv_reference(k, v, cos, sin, slots, kc, vc)
+        golden["rope"][name] = dict(tokens=tokens, kv_heads=hkv, head_dim=d, rotary_dim=rot,
+                                    dtype=str(dtype).replace("torch.", ""), key_cache=kc.clone(), value_cache=vc.clone())
+        print("rope", name)
 
     torch.save(golden, HERE / "paged_decode_golden.pt")
     print("wrote", HERE / "paged_decode_golden.pt")

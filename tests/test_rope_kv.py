@@ -1,0 +1,137 @@
+"""The producer step (rotary embedding + paged KV append, optionally quantised to FP8):
+the CPU oracle against the reference's own outputs, and the CUDA kernel against the oracle --
+bit for bit -- and against the decode operator that consumes what it wrote."""
+
+import pytest
+import torch
+
+from oracle import paged_decode_oracle as decode_oracle
+from oracle import rope_kv_oracle as oracle
+
+from helpers import assert_within_gate
+
+DEV = "cuda:0"
+
+
+def golden_inputs(case):
+    """The seeded inputs tests/golden/make_golden.py fed to the reference's rope_kv_reference."""
+    tokens, hkv, d, rot = case["tokens"], case["kv_heads"], case["head_dim"], case["rotary_dim"]
+    dtype = getattr(torch, case["dtype"])
+    gen = torch.Generator().manual_seed(41)
+    k = torch.randn(tokens, hkv, d, generator=gen).to(dtype)
+    v = torch.randn(tokens, hkv, d, generator=gen).to(dtype)
+    angle = torch.rand(tokens, rot // 2, generator=gen) * 6.2831853
+    slots = torch.randperm(4 * tokens, generator=gen)[:tokens]
+    return k, v, torch.cos(angle), torch.sin(angle), slots, dtype
+
+
+def test_oracle_reproduces_reference_rope_kv_outputs_bit_for_bit(golden):
+    for name, case in golden["rope"].items():
+        k, v, cos, sin, slots, dtype = golden_inputs(case)
+        tokens, hkv, d = k.shape
+        # the reference writes a flat [slots, Hkv, D] cache from per-token cos / sin rows: the same thing
+        # as a one-token-per-block paged cache and a cos_sin table indexed by the token number
+        table = torch.cat([cos, sin], dim=1)
+        kc = torch.zeros(4 * tokens, 1, hkv, d, dtype=dtype)
+        _, _, kc2, vc2 = oracle.rope_and_cache(
+            torch.zeros(tokens, hkv, d, dtype=dtype), k, v, torch.arange(tokens), table, True, kc, torch.zeros_like(kc), slots
+        )
+        assert torch.equal(kc2[:, 0].view(torch.int16), case["key_cache"].view(torch.int16)), name
+        assert torch.equal(vc2[:, 0].view(torch.int16), case["value_cache"].view(torch.int16)), name
+
+
+def make_step(seed, tokens, hq, hkv, d, rot, dtype, cache_dtype, table_dtype, block_size=16):
+    gen = torch.Generator().manual_seed(seed)
+    q = torch.randn(tokens, hq, d, generator=gen).to(dtype)
+    k = torch.randn(tokens, hkv, d, generator=gen).to(dtype)
+    v = torch.randn(tokens, hkv, d, generator=gen).to(dtype)
+    max_pos = 512
+    angle = torch.rand(max_pos, rot // 2, generator=gen) * 6.2831853
+    cos_sin = torch.cat([torch.cos(angle), torch.sin(angle)], dim=1).to(table_dtype)
+    positions = torch.randint(0, max_pos, (tokens,), generator=gen)
+    blocks = 2 * tokens // block_size + 3
+    slots = torch.randperm(blocks * block_size, generator=gen)[:tokens]
+    slots[tokens // 2] = -1  # a padded token: rotated, not stored
+    if cache_dtype == torch.float8_e4m3fn:
+        kc = torch.full((blocks, block_size, hkv, d), 0x11, dtype=torch.uint8).view(torch.float8_e4m3fn)
+        vc = torch.full((blocks, block_size, hkv, d), 0x22, dtype=torch.uint8).view(torch.float8_e4m3fn)
+        ks = torch.rand(hkv, generator=gen) * 0.02 + 0.003
+        vs = torch.rand(hkv, generator=gen) * 0.02 + 0.003
+    else:
+        kc = torch.full((blocks, block_size, hkv, d), 7.0, dtype=dtype)
+        vc = torch.full((blocks, block_size, hkv, d), -7.0, dtype=dtype)
+        ks = vs = None
+    return q, k, v, positions, cos_sin, kc, vc, slots, ks, vs
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("is_neox", [True, False])
+@pytest.mark.parametrize("cache", ["same", "fp8"])
+def test_kernel_matches_oracle_bit_for_bit(built_libs, is_neox, cache):
+    from single_gpu_inference_lab_b200 import l20_rope_kv
+
+    for seed, (tokens, hq, hkv, d, rot, dtype, table_dtype) in enumerate([
+        (64, 16, 2, 128, 128, torch.bfloat16, torch.float32),
+        (5, 28, 4, 128, 64, torch.float16, torch.float16),
+        (256, 14, 2, 64, 64, torch.bfloat16, torch.bfloat16),
+        (1, 32, 8, 128, 32, torch.float16, torch.float32),
+    ]):
+        cache_dtype = torch.float8_e4m3fn if cache == "fp8" else dtype
+        q, k, v, pos, cs, kc, vc, slots, ks, vs = make_step(seed, tokens, hq, hkv, d, rot, dtype, cache_dtype, table_dtype)
+        eq, ek, ekc, evc = oracle.rope_and_cache(q, k, v, pos, cs, is_neox, kc, vc, slots, ks, vs)
+        g = [t.to(DEV) for t in (q, k, v, pos, cs, kc, vc, slots)]
+        gq, gk, gv, gpos, gcs, gkc, gvc, gslots = g
+        l20_rope_kv.l20_rope_and_cache(gq, gk, gv, gpos, gcs, is_neox, gkc, gvc, gslots,
+                                       k_scale=None if ks is None else ks.to(DEV), v_scale=None if vs is None else vs.to(DEV))
+        torch.cuda.synchronize()
+        what = f"tokens={tokens} hq={hq} hkv={hkv} d={d} rot={rot} {dtype} neox={is_neox} cache={cache}"
+        assert torch.equal(gq.cpu().view(torch.int16), eq.view(torch.int16)), "query " + what
+        assert torch.equal(gk.cpu().view(torch.int16), ek.view(torch.int16)), "key " + what
+        as_bits = (lambda t: t.view(torch.uint8)) if cache == "fp8" else (lambda t: t.view(torch.int16))
+        assert torch.equal(as_bits(gkc.cpu()), as_bits(ekc)), "key cache " + what
+        assert torch.equal(as_bits(gvc.cpu()), as_bits(evc)), "value cache " + what
+
+
+@pytest.mark.gpu
+def test_append_then_decode_equals_the_oracles(built_libs):
+    """One decode step of a small model layer: append the new token of every sequence with the
+    producer kernel, then attend with the FP8 decode operator; compare with the two CPU oracles
+    chained the same way."""
+    from single_gpu_inference_lab_b200 import l20_paged_split_kv, l20_rope_kv
+    from single_gpu_inference_lab_b200.workloads import make_inputs
+
+    w = make_inputs("qwen2.5-coder-3b-b64", seed=12, batch=12, shrink=0.2)
+    batch, hq, d = w.query.shape
+    hkv = w.key_cache.shape[2]
+    gen = torch.Generator().manual_seed(3)
+    # the new token of each sequence overwrites its last position
+    positions = (w.seq_lens.long() - 1)
+    slots = w.block_table[torch.arange(batch), positions // 16].long() * 16 + positions % 16
+    q = torch.randn(batch, hq, d, generator=gen).to(torch.bfloat16)
+    k = torch.randn(batch, hkv, d, generator=gen).to(torch.bfloat16)
+    v = torch.randn(batch, hkv, d, generator=gen).to(torch.bfloat16)
+    angle = torch.arange(int(positions.max()) + 1)[:, None] * (1e4 ** (-torch.arange(0, d, 2) / d))[None, :]
+    cos_sin = torch.cat([torch.cos(angle), torch.sin(angle)], dim=1).float()
+    eq, _, ekc, evc = oracle.rope_and_cache(q, k, v, positions, cos_sin, True, w.key_cache, w.value_cache, slots,
+                                            w.k_scale, w.v_scale)
+    exp = decode_oracle.reference(eq, ekc, evc, w.block_table.long(), w.seq_lens, w.k_scale, w.v_scale)
+    g = w.to(DEV)
+    gq, gk, gv = q.to(DEV), k.to(DEV), v.to(DEV)
+    l20_rope_kv.l20_rope_and_cache(gq, gk, gv, positions.to(DEV), cos_sin.to(DEV), True, g.key_cache, g.value_cache,
+                                   slots.to(DEV), k_scale=g.k_scale, v_scale=g.v_scale)
+    out = l20_paged_split_kv.l20_paged_split_kv_attention_fp8(
+        gq, g.key_cache, g.value_cache, g.block_table, g.seq_lens, k_scale=g.k_scale, v_scale=g.v_scale,
+        max_seq_len=w.max_seq_len, split_size=256)
+    torch.cuda.synchronize()
+    assert torch.equal(g.key_cache.cpu().view(torch.uint8), ekc.view(torch.uint8))
+    assert_within_gate(out, exp, "append + decode")
+
+
+def test_wrapper_argument_errors_without_a_gpu():
+    from single_gpu_inference_lab_b200 import l20_rope_kv
+
+    q = torch.zeros(2, 4, 128, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="requires an SM100 GPU"):
+        l20_rope_kv.l20_rope_and_cache(q, q, q, torch.zeros(2, dtype=torch.long), torch.zeros(8, 128), True,
+                                       torch.zeros(1, 16, 4, 128, dtype=torch.bfloat16),
+                                       torch.zeros(1, 16, 4, 128, dtype=torch.bfloat16), torch.zeros(2, dtype=torch.long))
