@@ -36,11 +36,12 @@ extern "C" {
 #define PFD_FLAG_NO_DIRECT_OUT 2u /* always go through the partial workspace + merge kernel    */
 #define PFD_FLAG_PARTIAL_ONLY 4u  /* launch the split-KV partial kernel only (kernel timing)   */
 #define PFD_FLAG_FIXED_SPLITS 8u  /* always use the fixed-split grid + merge kernel             */
-#define PFD_FLAG_BALANCED 16u     /* use the balanced persistent kernel + its merge kernel when
-                                     the call qualifies (head_dim 128, at most 8 query heads per
-                                     kv head, dense f32 workspace of at least
-                                     pfd_balanced_workspace_rows() rows); split_size then only
-                                     sizes the workspace.  Otherwise the fixed-split grid runs. */
+#define PFD_FLAG_BALANCED 16u     /* no effect (kept for callers of earlier builds): the balanced
+                                     persistent kernel + its merge kernel run whenever the call
+                                     qualifies -- head_dim 128, at most 8 query heads per kv head,
+                                     dense f32 workspace of at least pfd_balanced_workspace_rows()
+                                     rows; split_size then only sizes the workspace.  Otherwise,
+                                     or with PFD_FLAG_FIXED_SPLITS, the fixed-split grid runs.    */
 #define PFD_FLAG_EARLY_METADATA 32u /* the caller vouches that the kernel preceding this call in
                                      the stream does not write seq_lens or block_table (true for
                                      every layer of a model step, whose metadata is built once):
@@ -151,7 +152,7 @@ int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args);
 int pfd_paged_decode_kv16_split_out(const pfd_decode_args* args);
 
 /*
- * Rows of (o, m, l) the workspace must hold for PFD_FLAG_BALANCED on the current device:
+ * Rows of (o, m, l) the workspace must hold for the balanced persistent kernel on the current device:
  * batch * num_q_heads * workspace_splits >= this.  The balanced kernel gives every group of
  * num_kv_heads warps two slots of num_q_heads rows.  Negative on error.  No counterpart in the
  * reference, whose workspace is always [B, Hq, splits].

@@ -269,7 +269,7 @@ PATH_NAMES = {0: "none", 1: "fixed-split grid (plain loads) + merge", 2: "fixed-
 
 
 def balanced_workspace_rows(num_q_heads: int, num_kv_heads: int) -> int:
-    """Rows ``B * Hq * splits`` the workspace needs for ``PFD_FLAG_BALANCED`` on the current device."""
+    """Rows ``B * Hq * splits`` the workspace needs for the balanced persistent kernel on the current device."""
     lib = load()
     lib.pfd_balanced_workspace_rows.argtypes = [C.c_int32, C.c_int32]
     lib.pfd_balanced_workspace_rows.restype = C.c_int64
