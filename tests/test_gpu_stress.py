@@ -29,7 +29,7 @@ def cabi(built_libs):
 
 
 def random_case(rng: random.Random, kv16: bool):
-    hkv = rng.choice([1, 2, 4, 8])
+    hkv = rng.choice([1, 2, 3, 4, 6, 8])
     group = rng.choice([1, 2, 4, 7, 8])
     hq = hkv * group
     batch = rng.choice([1, 2, 3, 5, 17, 40])
