@@ -65,6 +65,9 @@ def parse_args():
     p.add_argument("--kv-dtype", choices=["fp8", "bf16", "fp16"], default="fp8",
                    help="fp8: the e4m3 path (headline); bf16 / fp16: the non-quantised sibling operator, "
                         "caches and query in that type (single GPU, batch-sharded or weak scaling only)")
+    p.add_argument("--graph-collective", action="store_true",
+                   help="KV-range mode on several GPUs: replay the step, all-gather included, from a CUDA graph "
+                        "instead of launching every step eagerly")
     p.add_argument("--flags", type=int, default=32,
                    help="PFD_FLAG_* bits of the timed calls; default PFD_FLAG_EARLY_METADATA: the block table "
                         "and sequence lengths do not change between the timed layer-steps")
@@ -324,7 +327,7 @@ def main() -> int:
         """Same, with the K steps replayed from CUDA graphs (a graph of `chunk` consecutive
         steps replayed, plus one for the remainder) so that host launch overhead does not
         pace the device: exactly `steps` steps run inside the timed region."""
-        if kv_range_mode and world > 1:
+        if kv_range_mode and world > 1 and not args.graph_collective:
             return timed(fn, steps)  # the collective is launched eagerly
         chunk = min(steps, max(pools, (64 // pools) * pools))
         reps, rest = divmod(steps, chunk)
