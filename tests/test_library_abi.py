@@ -129,3 +129,23 @@ def test_workspace_allocator_shapes():
     many = [900] * 256  # more (sequence, kv head) pairs than slots: a few waves of small items
     s = m.choose_split_size(256, 4, 8192, seq_lens=many)
     assert 128 <= s <= 2048 and s % 64 == 0
+
+
+def test_missing_libraries_fail_loudly_and_the_package_never_imports_the_oracle(tmp_path, monkeypatch):
+    """No CPU or eager path stands behind the operator: without its shared libraries every entry
+    point raises, and no module of the package reaches for the test oracle."""
+    import re
+    from pathlib import Path
+
+    from single_gpu_inference_lab_b200 import cabi, l20_paged_decode
+
+    monkeypatch.setattr(cabi, "_lib", None)
+    monkeypatch.setattr(cabi, "library_path", lambda: tmp_path / "libpaged_fp8_decode.so")
+    with pytest.raises(RuntimeError, match="there is no fallback implementation"):
+        cabi.load()
+    with pytest.raises(RuntimeError, match="has no fallback implementation"):
+        l20_paged_decode.load_library(tmp_path / "l20_paged_decode_ops.so")
+    package = Path(cabi.__file__).resolve().parent
+    for source in list(package.glob("*.py")) + list((package / "csrc").glob("*")):
+        text = source.read_text(errors="ignore")
+        assert not re.search(r"^\s*(from|import)\s+oracle\b", text, re.M), source
