@@ -343,7 +343,12 @@ int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num
     const int rows = a.batch * a.num_q_heads;
     // programmatic dependent launch: the merge grid is scheduled while the partial grid drains
     cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3((rows + 3) / 4);
+    // few rows and more than eight slots per row: four warps share a row (one round trip instead of several)
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    if (int rc = sm_count_of(dev, &sms)) return rc;
+    const bool wide = rows <= 8 * sms && num_splits + kp.slot_offset > 8;
+    cfg.gridDim = dim3(wide ? rows : (rows + 3) / 4);
     cfg.blockDim = dim3(128);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
@@ -353,7 +358,8 @@ int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     const int batch = a.batch;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, pfd::paged_decode_merge_kernel<D, QBF16>, kp, batch);
+    const cudaError_t e = wide ? cudaLaunchKernelEx(&cfg, pfd::paged_decode_merge_kernel<D, QBF16, 4>, kp, batch)
+                               : cudaLaunchKernelEx(&cfg, pfd::paged_decode_merge_kernel<D, QBF16, 1>, kp, batch);
     if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "merge kernel launch failed: %s", cudaGetErrorString(e));
     if (int rc = check_launch("merge kernel")) return rc;
   }

@@ -820,15 +820,20 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   pdl_wait();
 }
 
-// LSE merge over the live splits of each (sequence, q head); one warp per row.
+// LSE merge over the live splits of each (sequence, q head).  WPR = 1: one warp per row, four
+// rows per CTA; WPR = 4 (few rows, many splits): the four warps of a CTA share one row, warp w
+// taking splits w, w + 4, ..., and combine through shared memory.
 // Same maths as _paged_split_kv_reduce (integrations/vllm/l20_paged_split_kv.py:459-488).
-template <int D, bool QBF16>
+template <int D, bool QBF16, int WPR = 1>
 __global__ void __launch_bounds__(128)
 paged_decode_merge_kernel(const KernelParams p, int batch) {
+  static_assert(WPR == 1 || WPR == 4, "one or four warps per row");
   pdl_launch_dependents();
-  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int warp = threadIdx.x >> 5;
+  const int row = WPR == 1 ? blockIdx.x * 4 + warp : blockIdx.x;
+  const int part = WPR == 1 ? 0 : warp;
   const int lane = threadIdx.x & 31;
-  if (row >= batch * p.num_q_heads) return;
+  if (row >= batch * p.num_q_heads) return;  // WPR == 1 only: whole warps, no barrier below
   const int b = row / p.num_q_heads, hq = row % p.num_q_heads;
   const int seq_len = p.seq_lens[b];
   const int live = seq_len - p.kv_start;
@@ -838,18 +843,18 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
 #pragma unroll
   for (int e = 0; e < E; ++e) acc[e] = 0.f;
   float big = -INFINITY, den = 0.f;
-  if (ns == 1 && p.direct_out) return;  // written by the partial kernel
+  if (ns == 1 && p.direct_out) return;  // written by the partial kernel (with WPR == 4 the whole CTA returns)
   pdl_wait();  // the partial kernel's stores are complete and visible from here on
   if (ns > 0) {
     const int64_t base = (int64_t)b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h;
     // One pass with a running maximum; eight splits per round trip, their maxima, sums and data
     // requested together.
-    for (int s0 = 0; s0 < ns; s0 += 8) {
+    for (int s0 = part; s0 < ns; s0 += 8 * WPR) {
       float mv[8], lv[8], xv[8][E];
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        const bool on = s0 + u < ns;
-        const int64_t pidx = base + (int64_t)(on ? s0 + u : 0) * p.partial_stride_s;
+        const bool on = s0 + u * WPR < ns;
+        const int64_t pidx = base + (int64_t)(on ? s0 + u * WPR : 0) * p.partial_stride_s;
         mv[u] = on ? p.partial_max[pidx] : -INFINITY;
         lv[u] = on ? p.partial_sum[pidx] : 0.f;
         if (p.partial_dtype == 0) {
@@ -882,6 +887,27 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
       }
       big = m_new;
     }
+  }
+  if constexpr (WPR == 4) {
+    __shared__ float sh_acc[4][D];
+    __shared__ float sh_m[4], sh_l[4];
+#pragma unroll
+    for (int e = 0; e < E; ++e) sh_acc[warp][lane * E + e] = acc[e];
+    if (lane == 0) { sh_m[warp] = big; sh_l[warp] = den; }
+    __syncthreads();
+    if (warp != 0) return;
+    const float m_all = fmaxf(fmaxf(sh_m[0], sh_m[1]), fmaxf(sh_m[2], sh_m[3]));
+    den = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float c = (sh_m[w] == -INFINITY) ? 0.f : expf(sh_m[w] - m_all);
+      den += sh_l[w] * c;
+#pragma unroll
+      for (int e = 0; e < E; ++e) acc[e] += c * sh_acc[w][lane * E + e];
+    }
+    big = m_all;
   }
   if (p.packed_output != nullptr) {
     float* dst = p.packed_output + (int64_t)row * (D + 2);
