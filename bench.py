@@ -19,9 +19,13 @@ step), with microseconds per layer-step beside it.  One JSON line is printed by 
                    on this host's cores on the same batch.
 * ``--impl reference`` times only that CPU path and prints its own line.
 
-With N > 1 every rank runs the same geometry on its own sequences (no data-path collective);
-``--workload llama3-8b-long-b4`` instead splits each sequence's KV range over the ranks and
-merges the partials after one NCCL all-gather.
+With N > 1 every rank runs the same geometry on its own sequences (no data-path collective;
+``--strong`` shards ONE batch by sequence instead); ``--workload llama3-8b-long-b4`` splits each
+sequence's KV range over the ranks and merges the partials after one NCCL all-gather
+(``--graph-collective`` replays that step, collective included, from a CUDA graph).
+``--kv-dtype bf16|fp16`` times the non-quantised sibling operator on the same geometries;
+``--flags`` are the ``PFD_FLAG_*`` bits of the timed calls (default: early metadata reads; add 8
+for the fixed-split grid).
 """
 
 from __future__ import annotations
