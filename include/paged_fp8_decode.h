@@ -277,13 +277,6 @@ typedef struct pfd_rope_args {
 } pfd_rope_args;
 int pfd_rope_quant_append(const pfd_rope_args* args);
 
-/*
- * Debug aid for tuning: while `device_buffer` (uint64 [grid][8], device memory owned by the
- * caller) is set, thread 0 of every CTA of the balanced kernel stores nanosecond timestamps
- * (%globaltimer) of its phases there.  NULL switches it off (the default).
- */
-int pfd_debug_phase_times(void* device_buffer);
-
 /* Number of kernels this library has launched in this process (for launch accounting). */
 int64_t pfd_launch_count(void);
 

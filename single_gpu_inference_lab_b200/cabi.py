@@ -32,7 +32,6 @@ EXPORTS = (
     "pfd_rope_quant_append",
     "pfd_balanced_workspace_rows",
     "pfd_device_status",
-    "pfd_debug_phase_times",
     "pfd_last_path",
     "pfd_launch_count",
     "pfd_last_error",

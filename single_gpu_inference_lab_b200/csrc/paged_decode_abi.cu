@@ -20,7 +20,7 @@ namespace {
 
 thread_local std::string g_last_error;
 thread_local int g_last_path = 0;  // PFD_PATH_* of this thread's last decode call
-unsigned long long* g_phase_times = nullptr;  // debug: per-CTA phase timestamps, set by pfd_debug_phase_times
+unsigned long long* g_phase_times = nullptr;  // tuning builds (-DPFD_PHASE_STAMPS) only: stamp buffer
 std::atomic<int64_t> g_launches{0};
 
 int fail(int code, const char* fmt, ...) {
@@ -736,10 +736,14 @@ int64_t pfd_balanced_workspace_rows(int32_t num_q_heads, int32_t num_kv_heads) {
   return 2LL * (sms * kChunkWarps / num_kv_heads) * num_q_heads;
 }
 
+#ifdef PFD_PHASE_STAMPS
+// Tuning builds only: while `device_buffer` (uint64 [slots][8], caller-owned device memory) is
+// set, the kernels store %globaltimer stamps of their phases there.  Not part of the shipped ABI.
 int pfd_debug_phase_times(void* device_buffer) {
   g_phase_times = static_cast<unsigned long long*>(device_buffer);
   return PFD_OK;
 }
+#endif
 
 int pfd_device_status(int32_t* status) {
   if (status == nullptr) return fail(PFD_ERR_INVALID, "status is NULL");

@@ -484,6 +484,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
   int32_t* lens = prefix + (B + 1);    // [B]
 
   mark_phase_at(tp, W, 0, lane == 0);  // start
+  mark_value_at(tp, W, 5, lane == 0, sm_id());
   const uint32_t my_ring = ring + warp * NSTAGE * kStage;
   const uint32_t my_bars = bars + warp * NSTAGE * 8;
   if (lane == 0) {
@@ -669,6 +670,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       const int s = t % NSTAGE;
       if (!mbar_wait_bounded(my_bars + 8 * s, (t / NSTAGE) & 1)) { ok = false; break; }
       if (t == 0) mark_phase_at(tp, W, 3, lane == 0);  // first data landed
+      if (t == n / 2) mark_phase_at(tp, W, 6, lane == 0);  // half of the chunk consumed
       const int tok0 = (page_first + 2 * (g - cur.start)) * kPage;
       if constexpr (KV16) kv16_step<QBF16>(st, my_ring + s * kStage, qb, scale_log2, tok0, p.kv_start, seq_len, lane);
       else bal_step<1>(st, my_ring + s * kStage, k_off, v_off, qb, scale_log2, tok0, p.kv_start, seq_len, i, j);
@@ -760,6 +762,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
     for (int f = 0; f < 8; ++f) { qb[0][f][0] = qn[0][f][0]; qb[0][f][1] = qn[0][f][1]; }
   }
   mark_phase_at(tp, W, 4, lane == 0);  // chunk done
+  mark_value_at(tp, W, 7, lane == 0, (unsigned long long)n);
   if (!ok && lane == 0) {
     // a copy never landed: record it; give the copies still in flight a bounded chance to land
     atomicExch(tp.status, kErrTmaTimeout);
@@ -781,11 +784,13 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
   constexpr int D = 128, E = 4;
   static_assert(WPR == 1 || WPR == 4, "one or four warps per row");
   pdl_launch_dependents();
-  mark_phase_at(tp, blockIdx.x, 5, threadIdx.x == 0);  // merge CTA resident
+  mark_phase_at(tp, cp.num_warps + blockIdx.x, 5, threadIdx.x == 0);  // merge CTA resident
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = WPR == 1 ? blockIdx.x * 4 + warp : blockIdx.x;
   const int part = WPR == 1 ? 0 : warp;
-  if (row >= cp.batch * p.num_q_heads) return;  // WPR == 1 only: whole warps, no barrier below
+  // Every exit path waits for the chunk kernel first: a dependent grid that completed early would
+  // let the next kernel of the stream start while the chunk kernel is still writing.
+  if (row >= cp.batch * p.num_q_heads) { pdl_wait(); return; }  // WPR == 1 only: whole warps, no barrier below
   const int b = row / p.num_q_heads, hq = row % p.num_q_heads;
   // seq_lens is an input of the whole step, not a result of the chunk kernel: the chunking is
   // recomputed here while that kernel is still running.
@@ -805,7 +810,7 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
   const int s0 = chunks.first_unit(below, b);
   const int w_first = np > 0 ? chunks.chunk_of(s0) : 0;
   const int ns = np > 0 ? chunks.chunk_of(s0 + 2 * (np - 1)) - w_first + 1 : 0;
-  if (ns == 1) return;  // written by the chunk kernel (the whole CTA returns: one row per CTA if WPR == 4)
+  if (ns == 1) { pdl_wait(); return; }  // written by the chunk kernel (the whole CTA returns: one row per CTA if WPR == 4)
   float acc[E] = {0.f, 0.f, 0.f, 0.f};
   float big = -INFINITY, den = 0.f;
   // pieces k0, k0 + WPR, ... (K of them) in one round trip, folded into (acc, big, den)
@@ -852,7 +857,7 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
     big = m_new;
   };
   pdl_wait();  // the chunk kernel's stores are complete and visible from here on
-  mark_phase_at(tp, blockIdx.x, 6, threadIdx.x == 0);  // chunk kernel complete
+  mark_phase_at(tp, cp.num_warps + blockIdx.x, 6, threadIdx.x == 0);  // chunk kernel complete
   if (WPR == 1 && ns <= 4) {
     if (ns > 0) round(std::integral_constant<int, 4>{}, 0);
   } else {
@@ -885,7 +890,7 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
     if (lane == 0) { dst[D] = big; dst[D + 1] = den; }
     return;
   }
-  mark_phase_at(tp, blockIdx.x, 7, threadIdx.x == 0);  // merged
+  mark_phase_at(tp, cp.num_warps + blockIdx.x, 7, threadIdx.x == 0);  // merged
   const float inv = ns > 0 ? 1.f / den : 0.f;
   uint16_t* dst = reinterpret_cast<uint16_t*>(p.output) + (int64_t)b * p.o_stride_b + (int64_t)hq * p.o_stride_h + lane * E;
   uint32_t w0, w1;

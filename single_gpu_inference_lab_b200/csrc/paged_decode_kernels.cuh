@@ -599,20 +599,34 @@ __device__ __forceinline__ uint4 lds_16(uint32_t addr) {
 struct TmaParams {
   int32_t head_is_dim1;  // 1: tensor-map dims are (D, head, token, page); 0: (D, token, head, page)
   int32_t* status;       // device error word (0 = ok)
-  unsigned long long* phase_times;  // optional [grid][8] nanosecond timestamps of a CTA's phases
+  unsigned long long* phase_times;  // [slots][8] nanosecond stamps; read only in builds with PFD_PHASE_STAMPS
 };
 
+// Tuning aid, compiled in only with -DPFD_PHASE_STAMPS (the shipped library leaves it out): the
+// leader lane stores a %globaltimer stamp of phase k into phase_times[slot][k].
 __device__ __forceinline__ void mark_phase_at(const TmaParams& tp, int slot, int k, bool leader) {
+#ifdef PFD_PHASE_STAMPS
   if (tp.phase_times != nullptr && leader) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     tp.phase_times[(size_t)slot * 8 + k] = t;
   }
+#else
+  (void)tp; (void)slot; (void)k; (void)leader;
+#endif
 }
-__device__ __forceinline__ void mark_phase(const TmaParams& tp, int k, bool leader) {
-  mark_phase_at(tp, blockIdx.x, k, leader);
+__device__ __forceinline__ void mark_value_at(const TmaParams& tp, int slot, int k, bool leader, unsigned long long v) {
+#ifdef PFD_PHASE_STAMPS
+  if (tp.phase_times != nullptr && leader) tp.phase_times[(size_t)slot * 8 + k] = v;
+#else
+  (void)tp; (void)slot; (void)k; (void)leader; (void)v;
+#endif
 }
-__device__ __forceinline__ void mark_phase(const TmaParams& tp, int k) { mark_phase(tp, k, threadIdx.x == 0); }
+__device__ __forceinline__ unsigned sm_id() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
+  return r;
+}
 
 constexpr int kErrTmaTimeout = 1;
 
@@ -833,7 +847,9 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
   const int row = WPR == 1 ? blockIdx.x * 4 + warp : blockIdx.x;
   const int part = WPR == 1 ? 0 : warp;
   const int lane = threadIdx.x & 31;
-  if (row >= batch * p.num_q_heads) return;  // WPR == 1 only: whole warps, no barrier below
+  // Every exit path waits for the partial kernel first: a dependent grid that completed early
+  // would let the next kernel of the stream start while the partial kernel is still writing.
+  if (row >= batch * p.num_q_heads) { pdl_wait(); return; }  // WPR == 1 only: whole warps, no barrier below
   const int b = row / p.num_q_heads, hq = row % p.num_q_heads;
   const int seq_len = p.seq_lens[b];
   const int live = seq_len - p.kv_start;
@@ -843,8 +859,8 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
 #pragma unroll
   for (int e = 0; e < E; ++e) acc[e] = 0.f;
   float big = -INFINITY, den = 0.f;
-  if (ns == 1 && p.direct_out) return;  // written by the partial kernel (with WPR == 4 the whole CTA returns)
   pdl_wait();  // the partial kernel's stores are complete and visible from here on
+  if (ns == 1 && p.direct_out) return;  // written by the partial kernel (with WPR == 4 the whole CTA returns)
   if (ns > 0) {
     const int64_t base = (int64_t)b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h;
     // One pass with a running maximum; eight splits per round trip, their maxima, sums and data

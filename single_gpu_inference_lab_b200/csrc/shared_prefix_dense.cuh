@@ -148,16 +148,21 @@ struct PrefixParams {
   int32_t prefix_len;   // tokens shared by every request (multiple of 16)
   int32_t batch;
   int32_t* status;
-  unsigned long long* phase_times;  // optional [grid][8] nanosecond timestamps (tuning aid)
+  unsigned long long* phase_times;  // [grid][8] nanosecond stamps; read only in builds with PFD_PHASE_STAMPS
 };
 
+// Tuning aid, compiled in only with -DPFD_PHASE_STAMPS.
 __device__ __forceinline__ void prefix_mark(const PrefixParams& pp, int k) {
+#ifdef PFD_PHASE_STAMPS
   if (pp.phase_times != nullptr && threadIdx.x == 0) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     const size_t cta = blockIdx.x + gridDim.x * (blockIdx.y + (size_t)gridDim.y * blockIdx.z);
     pp.phase_times[cta * 8 + k] = t;
   }
+#else
+  (void)pp; (void)k;
+#endif
 }
 
 // grid = (prefix chunks, 128-row tiles, kv heads), block = 512 threads, 1 CTA per SM.

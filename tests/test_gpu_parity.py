@@ -28,6 +28,7 @@ def cabi(built_libs):
 
 
 PATH_LDG, PATH_TMA, PATH_BALANCED = 1, 2, 3
+EARLY = 32  # PFD_FLAG_EARLY_METADATA: what the benchmark and the vLLM hook pass
 
 
 def workspace(q, max_seq_len, split_size, dtype=torch.float32, kv_start=0, poison=True, min_rows=0):
@@ -118,13 +119,14 @@ def test_config1_full_size(cabi):
     w = make_inputs("qwen2.5-0.5b-b8", seed=0)
     exp = expected(w)
     for split in (16, 128, 1024):
-        assert_within_gate(run(cabi, w.to(DEV), split), exp, f"cfg1 split={split}")
+        for flags in (0, EARLY):
+            assert_within_gate(run(cabi, w.to(DEV), split, flags=flags), exp, f"cfg1 split={split} flags={flags}")
 
 
 def test_config2_full_size(cabi):
     w = make_inputs("qwen2.5-coder-3b-b64", seed=0)
     exp = expected(w)
-    for split, flags in ((256, 16), (512, 16), (896, 0), (512, 8), (1024, 1)):
+    for split, flags in ((256, 16), (512, 16), (896, 0), (512, 8), (1024, 1), (512, EARLY), (896, EARLY | 8), (256, EARLY | 1)):
         assert_within_gate(run(cabi, w.to(DEV), split, flags=flags), exp, f"cfg2 split={split} flags={flags}")
 
 
@@ -132,7 +134,7 @@ def test_config3_full_size_log_uniform_lengths(cabi):
     w = make_inputs("qwen2.5-7b-b256", seed=0)
     assert int(w.seq_lens.min()) <= 4
     exp = expected(w)
-    for flags in (0, 16, 8):
+    for flags in (0, 16, 8, EARLY, EARLY | 8):
         assert_within_gate(run(cabi, w.to(DEV), 512, flags=flags), exp, f"cfg3 flags={flags}")
 
 
@@ -144,6 +146,10 @@ def test_config4_long_context_sampled_rows_and_split_invariance(cabi):
     out_a = run(cabi, w, 2048, flags=16)
     out_b = run(cabi, w, 512, flags=8)
     out_c = run(cabi, w, 16384)
+    out_d = run(cabi, w, 2048, flags=EARLY)
+    out_e = run(cabi, w, 1024, flags=EARLY | 8)
+    assert_within_gate(out_d, out_a, "early metadata vs not")
+    assert_within_gate(out_e, out_a, "early metadata, fixed split 1024 vs 2048")
     assert_within_gate(out_b, out_a, "split 512 vs 2048")
     assert_within_gate(out_c, out_a, "split 8192 vs 2048")
     b = 2
@@ -160,7 +166,7 @@ def test_config4_long_context_sampled_rows_and_split_invariance(cabi):
 def test_config5_shared_prefix_full_size(cabi):
     w = make_inputs("shared-prefix-b64", seed=0)
     exp = expected(w)
-    for flags in (0, 16, 8):
+    for flags in (0, 16, 8, EARLY, EARLY | 8):
         assert_within_gate(run(cabi, w.to(DEV), 512, flags=flags), exp, f"cfg5 flags={flags}")
 
 
@@ -178,7 +184,7 @@ def test_every_short_context_length(cabi, d, hq, hkv):
     q = torch.randn(b, hq, d).to(torch.bfloat16)
     exp = oracle.reference(q, kc, vc, table.long(), lens, ks, vs)
     for split in (16, 32, 64, 512):
-        for flags in (16, 0, 8, 1, 2):
+        for flags in (16, 0, 8, 1, 2, EARLY, EARLY | 8, EARLY | 1):
             out = torch.full_like(q, float("nan"), device=DEV)
             want = expected_path(cabi, q, hkv, flags)
             rows = cabi.balanced_workspace_rows(hq, hkv) if want == PATH_BALANCED else 0
@@ -218,6 +224,39 @@ def test_max_seq_len_larger_than_every_sequence_and_empty_splits(cabi):
     w.block_table = wide
     out = run(cabi, w.to(DEV), 64, max_seq_len=640)
     assert_within_gate(out, exp, "msl=640")
+
+
+def test_consumer_right_behind_the_call_sees_finished_rows(cabi):
+    """Stream order without a host synchronisation: a kernel enqueued right behind the call (here a
+    copy of the output) must see finished rows.  The merge grid is a programmatic dependent of the
+    partial grid; when every one of its rows is already final it must still not complete early.
+    Cases: one short sequence (one warp group, nothing to merge), and lengths that all fit one
+    split while max_seq_len asks for several."""
+    torch.manual_seed(3)
+    hq, hkv, d, pages = 16, 2, 128, 8
+    for batch, ctx, msl, flags in ((1, 64, 64, 0), (1, 64, 64, EARLY), (3, 60, 640, 8), (3, 60, 640, EARLY | 8)):
+        lens = torch.full((batch,), ctx, dtype=torch.int32)
+        table = torch.randperm(batch * 40).to(torch.int32).reshape(batch, 40)
+        kc, ks = oracle.quantize_fp8_e4m3_per_head(torch.randn(batch * 40, 16, hkv, d))
+        vc, vs = oracle.quantize_fp8_e4m3_per_head(torch.randn(batch * 40, 16, hkv, d))
+        q = torch.randn(batch, hq, d).to(torch.bfloat16)
+        exp = oracle.reference(q, kc, vc, table.long(), lens, ks, vs)
+        g = [t.to(DEV) for t in (q, kc, vc, table, lens, ks, vs)]
+        want = expected_path(cabi, q, hkv, flags)
+        rows = cabi.balanced_workspace_rows(hq, hkv) if want == PATH_BALANCED else 0
+        ws = workspace(g[0], msl, 64, min_rows=rows)
+        out = torch.empty_like(g[0])
+        copies = []
+        for _ in range(200):
+            out.fill_(float("nan"))
+            cabi.paged_decode_fp8_e4m3_split_out(
+                g[0], g[1], g[2], g[3], g[4], k_scale=g[5], v_scale=g[6], max_seq_len=msl, split_size=64,
+                output=out, workspace=ws, flags=flags)
+            copies.append(out.clone())
+        torch.cuda.synchronize()
+        assert cabi.last_path() == want
+        for c in copies:
+            assert_within_gate(c, exp, f"batch={batch} ctx={ctx} max_seq_len={msl} flags={flags}")
 
 
 def test_zero_length_sequence_gives_zeros(cabi):

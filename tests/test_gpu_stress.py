@@ -89,13 +89,14 @@ def test_random_cases(cabi, kv16):
             None,
         )
         out = torch.full_like(g[0], float("nan"))
-        what = f"case {case}: kv16={kv16} B={q.shape[0]} Hq={q.shape[1]} Hkv={hkv} max={int(lens.max())} kv_start={kv_start}"
+        flags = rng.choice([0, 32])  # with and without early metadata reads
+        what = f"case {case}: kv16={kv16} B={q.shape[0]} Hq={q.shape[1]} Hkv={hkv} max={int(lens.max())} kv_start={kv_start} flags={flags}"
         if kv16:
             cabi.paged_decode_kv16_split_out(*g, max_seq_len=int(lens.max()), split_size=512, output=out, workspace=ws,
-                                             kv_start=kv_start)
+                                             kv_start=kv_start, flags=flags)
         else:
             cabi.paged_decode_fp8_e4m3_split_out(*g, k_scale=ks.to(DEV), v_scale=vs.to(DEV), max_seq_len=int(lens.max()),
-                                                 split_size=512, output=out, workspace=ws, kv_start=kv_start)
+                                                 split_size=512, output=out, workspace=ws, kv_start=kv_start, flags=flags)
         torch.cuda.synchronize()
         assert cabi.device_status() == 0, what
         assert cabi.last_path() in (3, 4), what
@@ -165,6 +166,7 @@ def test_random_cases_fixed_split_grid(cabi, flags, d):
         kv_start = rng.choice([0, 0, 5, 16, 37]) if int(lens.max()) > 40 else 0
         exp = expected(q, kc, vc, table, lens, ks, vs, kv_start)
         split = rng.choice([16, 64, 256, 1024])
+        call_flags = flags | rng.choice([0, 32])  # with and without early metadata reads
         g = [t.to(DEV) for t in (q, kc, vc, table, lens)]
         splits = max(1, -(-(int(lens.max()) - kv_start) // split))
         ws = (
@@ -174,9 +176,9 @@ def test_random_cases_fixed_split_grid(cabi, flags, d):
             None,
         )
         out = torch.full_like(g[0], float("nan"))
-        what = f"case {case}: flags={flags} d={d} B={q.shape[0]} Hq={q.shape[1]} Hkv={hkv} max={int(lens.max())} kv_start={kv_start} split={split}"
+        what = f"case {case}: flags={call_flags} d={d} B={q.shape[0]} Hq={q.shape[1]} Hkv={hkv} max={int(lens.max())} kv_start={kv_start} split={split}"
         cabi.paged_decode_fp8_e4m3_split_out(*g, k_scale=ks.to(DEV), v_scale=vs.to(DEV), max_seq_len=int(lens.max()),
-                                             split_size=split, output=out, workspace=ws, kv_start=kv_start, flags=flags)
+                                             split_size=split, output=out, workspace=ws, kv_start=kv_start, flags=call_flags)
         torch.cuda.synchronize()
         assert cabi.device_status() == 0, what
         assert cabi.last_path() == (1 if (flags & 1 or d == 64) else 2), what
