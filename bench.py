@@ -78,6 +78,8 @@ def parse_args():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-shared-prefix", action="store_true",
                    help="shared-prefix-b64 only: use the ordinary decode path instead of the dense tcgen05 prefix pass")
+    p.add_argument("--no-plan", action="store_true",
+                   help="do not plan the step: every call derives its work split itself and a merge kernel follows")
     p.add_argument("--strong", action="store_true",
                    help="N > 1: shard ONE batch by sequence over the ranks (token-balanced) instead of one batch per rank")
     return p.parse_args()
@@ -280,6 +282,13 @@ def main() -> int:
 
         ws = spd.allocate_shared_prefix_workspace(q, w.max_seq_len, w.prefix_len, suffix_split_size=split)
     out = ws[3]
+    # The plan of the model step: block table and lengths are the same for every layer, so the
+    # work split is computed once, outside the timed layer-steps, as an engine does per step.
+    plan = None
+    if not args.no_plan and not shared_prefix and d == 128 and hq // hkv <= 8 and not (args.flags & (1 | 2 | 8)):
+        plan = cabi.plan_decode(q, w.key_cache, w.value_cache, w.block_table, w.seq_lens, max_seq_len=w.max_seq_len,
+                                split_size=split, workspace=ws)
+        torch.cuda.synchronize()
     packed = torch.empty(batch, hq, d + 2, device=dev) if kv_range_mode else None
     gathered = torch.empty(world, batch, hq, d + 2, device=dev) if kv_range_mode else None
 
@@ -287,7 +296,7 @@ def main() -> int:
         if kv16 is not None:
             cabi.paged_decode_kv16_split_out(
                 q, kcs[i % pools], vcs[i % pools], w.block_table, w.seq_lens, max_seq_len=w.max_seq_len,
-                split_size=split, output=out, workspace=ws, flags=flags)
+                split_size=split, output=out, workspace=ws, flags=flags, plan=plan)
             return
         if shared_prefix:
             cabi.shared_prefix_decode_fp8_e4m3(
@@ -298,7 +307,7 @@ def main() -> int:
         cabi.paged_decode_fp8_e4m3_split_out(
             q, kcs[i % pools], vcs[i % pools], w.block_table, w.seq_lens, k_scale=w.k_scale, v_scale=w.v_scale,
             max_seq_len=w.max_seq_len, split_size=split, output=None if kv_range_mode else out,
-            packed_output=packed, workspace=ws, flags=flags,
+            packed_output=packed, workspace=ws, flags=flags, plan=plan,
         )
         if kv_range_mode and not (flags & cabi.PFD_FLAG_PARTIAL_ONLY):
             if world > 1:
@@ -426,7 +435,8 @@ def main() -> int:
         path = cabi.last_path()
         fused = ((not kv_range_mode) and per_step == 1) or shared_prefix  # no single dominant kernel to time apart
         kernel_name = {1: "paged_decode_fp8_partial_ldg_kernel", 2: "paged_decode_fp8_partial_tma_kernel",
-                       3: "paged_decode_fp8_chunk_kernel", 4: "paged_decode_fp8_chunk_kernel<KV16>"}.get(path, "?")
+                       3: "paged_decode_fp8_chunk_kernel", 4: "paged_decode_fp8_chunk_kernel<KV16>",
+                       5: "paged_decode_fp8_chunk_kernel", 6: "paged_decode_fp8_chunk_kernel<KV16>"}.get(path, "?")
         if shared_prefix:
             kernel_name = "shared_prefix_dense_kernel + paged_decode_fp8_partial_tma_kernel + paged_decode_merge_kernel"
         ms_kernel = timed_graph(step if fused else (lambda i: step(i, args.flags | cabi.PFD_FLAG_PARTIAL_ONLY)), args.steps)

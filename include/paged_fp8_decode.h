@@ -18,7 +18,7 @@
 extern "C" {
 #endif
 
-#define PFD_ABI_VERSION 3
+#define PFD_ABI_VERSION 4
 
 /* element types of query / output / partial_output */
 #define PFD_DTYPE_F32 0
@@ -36,16 +36,19 @@ extern "C" {
 #define PFD_FLAG_NO_DIRECT_OUT 2u /* always go through the partial workspace + merge kernel    */
 #define PFD_FLAG_PARTIAL_ONLY 4u  /* launch the split-KV partial kernel only (kernel timing)   */
 #define PFD_FLAG_FIXED_SPLITS 8u  /* always use the fixed-split grid + merge kernel             */
-#define PFD_FLAG_BALANCED 16u     /* no effect (kept for callers of earlier builds): the balanced
-                                     persistent kernel + its merge kernel run whenever the call
-                                     qualifies -- head_dim 128, at most 8 query heads per kv head,
-                                     dense f32 workspace of at least pfd_balanced_workspace_rows()
-                                     rows; split_size then only sizes the workspace.  Otherwise,
-                                     or with PFD_FLAG_FIXED_SPLITS, the fixed-split grid runs.    */
 #define PFD_FLAG_EARLY_METADATA 32u /* the caller vouches that the kernel preceding this call in
-                                     the stream does not write seq_lens or block_table (true for
-                                     every layer of a model step, whose metadata is built once):
-                                     the kernels may then read them while that kernel drains     */
+                                     the stream writes neither seq_lens, block_table nor the plan
+                                     (true for every layer of a model step, whose metadata is
+                                     built once; not true for a call enqueued right behind
+                                     pfd_plan_decode): the kernels may then read them while that
+                                     kernel drains                                               */
+/*
+ * Kernel selection.  For head_dim 128, at most 8 query heads per kv head, a TMA-describable
+ * cache and a dense f32 workspace of at least pfd_balanced_workspace_rows() rows the balanced
+ * persistent kernel runs (split_size then only sizes the workspace): with `plan` set it is the
+ * only launch of the step, without it a merge kernel follows.  Anything else, or
+ * PFD_FLAG_FIXED_SPLITS, runs the fixed-split grid + merge kernel.
+ */
 
 /*
  * Operands of one decode-attention layer-step.
@@ -118,16 +121,18 @@ typedef struct pfd_decode_args {
 
   void* stream; /* cudaStream_t */
 
-  /* Unused (kept for layout compatibility): earlier builds counted retired pieces here. */
-  int32_t* semaphores;
-  int64_t num_semaphores;
-
   /* Optional [batch + 1] int32: with it, block_table is a flat list of page ids and the pages of
    * sequence b are block_table[page_indptr[b] ...] (FlashInfer's indptr / indices addressing,
    * l20_paged_decode_split_indices_out_cuda, integrations/vllm/cuda/l20_paged_decode.cu:600-649);
    * bt_stride_b is ignored.  Only the balanced persistent kernel reads it: a call that would
    * run on the fixed-split grid or the shared-prefix pass is refused with PFD_ERR_UNSUPPORTED. */
   const int32_t* page_indptr;
+
+  /* Optional device buffer written by pfd_plan_decode() for the same batch, lengths, block table,
+   * kv_start, head counts and workspace: the balanced persistent kernel then reads its work split
+   * from it and combines the pieces of cut sequences itself (one launch per step).  NULL, or a
+   * call that does not run the balanced kernel: ignored. */
+  void* plan;
 } pfd_decode_args;
 
 /*
@@ -150,6 +155,23 @@ int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args);
  * every SM take part.
  */
 int pfd_paged_decode_kv16_split_out(const pfd_decode_args* args);
+
+/*
+ * Plan of a model step's decode-attention calls: everything the balanced persistent kernel
+ * derives from seq_lens and block_table alone (pair prefix sum, every warp group's range and
+ * first page ids, arrival counters for the pieces of cut sequences), computed once by a small
+ * kernel on args->stream and then shared by the calls of all layers, which pass it as
+ * args->plan.  `cache_elem_bytes` is 1 for pfd_paged_decode_fp8_e4m3_split_out and 2 for
+ * pfd_paged_decode_kv16_split_out (they run different warp counts).  Reads of `args`: batch,
+ * head counts, head_dim, kv_start, the workspace fields, seq_lens, block_table / page_indptr,
+ * stream.  Returns PFD_ERR_UNSUPPORTED (nothing launched) when the call would not run the
+ * balanced kernel.  A plan stays valid while those inputs do not change; using it with other
+ * values makes the kernel set device status 2 and write nothing.  Calls that share a plan must
+ * not overlap on the GPU (same stream, or ordered by events).  The reference has no counterpart:
+ * its kernels take one CTA per (query head, split, sequence) and need no work split.
+ */
+int64_t pfd_plan_bytes(int32_t batch, int32_t num_kv_heads);
+int pfd_plan_decode(const pfd_decode_args* args, int32_t cache_elem_bytes, void* plan, int64_t plan_bytes);
 
 /*
  * Rows of (o, m, l) the workspace must hold for the balanced persistent kernel on the current device:
@@ -227,15 +249,34 @@ int pfd_resolve_slots(const int32_t* block_table, int64_t bt_stride_b, const int
 /*
  * Synchronises with the current device and reads (then clears) the error word the kernels set
  * when a bounded wait gave up: 0 = none, 1 = a TMA copy did not complete in time (the step's
- * output is then undefined).  The kernels never trap and never spin without a limit.
+ * output is then undefined), 2 = args->plan was made for other inputs (nothing was written).
+ * The kernels never trap and never spin without a limit.
  */
 int pfd_device_status(int32_t* status);
+
+/*
+ * Every device-side wait (for a TMA copy, for the tensor cores) gives up after this many
+ * nanoseconds, sets the error word and lets the kernel finish.  Default 200 ms: a decode step
+ * lasts well under one.  Process-wide, read at launch.
+ */
+int pfd_set_wait_limit_ns(uint64_t limit_ns);
+
+/*
+ * Self-test of that mechanism (it allocates one pinned host word while it runs): a one-warp
+ * kernel arms a barrier for bytes that no copy will deliver and waits for them with the given
+ * limit.  Returns after the kernel has finished; pfd_device_status() then reads 1, and
+ * *waited_ns (optional) holds how long the wait lasted on the device.  Nothing traps, faults
+ * or stays in flight.
+ */
+int pfd_selftest_bounded_wait(uint64_t limit_ns, uint64_t* waited_ns, void* stream);
 
 /* Which kernels the calling thread's last decode call launched. */
 #define PFD_PATH_FIXED_LDG 1 /* fixed-split grid, plain 16-byte loads, + merge kernel */
 #define PFD_PATH_FIXED_TMA 2 /* fixed-split grid, TMA pipeline, + merge kernel         */
 #define PFD_PATH_BALANCED 3  /* balanced persistent kernel + its merge kernel            */
 #define PFD_PATH_BALANCED_KV16 4 /* the same for 16-bit caches (pfd_paged_decode_kv16_split_out) */
+#define PFD_PATH_PLANNED 5       /* balanced persistent kernel with a plan: one launch        */
+#define PFD_PATH_PLANNED_KV16 6  /* the same for 16-bit caches                                 */
 int pfd_last_path(void);
 
 /*

@@ -19,7 +19,6 @@ PFD_FLAG_NO_TMA = 1
 PFD_FLAG_NO_DIRECT_OUT = 2
 PFD_FLAG_PARTIAL_ONLY = 4
 PFD_FLAG_FIXED_SPLITS = 8
-PFD_FLAG_BALANCED = 16
 PFD_FLAG_EARLY_METADATA = 32
 
 EXPORTS = (
@@ -31,7 +30,11 @@ EXPORTS = (
     "pfd_resolve_slots",
     "pfd_rope_quant_append",
     "pfd_balanced_workspace_rows",
+    "pfd_plan_bytes",
+    "pfd_plan_decode",
     "pfd_device_status",
+    "pfd_set_wait_limit_ns",
+    "pfd_selftest_bounded_wait",
     "pfd_last_path",
     "pfd_launch_count",
     "pfd_last_error",
@@ -87,9 +90,8 @@ class DecodeArgs(C.Structure):
         ("o_stride_h", C.c_int64),
         ("packed_output", C.c_void_p),
         ("stream", C.c_void_p),
-        ("semaphores", C.c_void_p),
-        ("num_semaphores", C.c_int64),
         ("page_indptr", C.c_void_p),
+        ("plan", C.c_void_p),
     ]
 
 
@@ -142,10 +144,11 @@ def _stream(t: torch.Tensor) -> int:
 def decode_args(
     query, key_cache, value_cache, block_table, seq_lens, *, k_scale, v_scale, max_seq_len,
     split_size, output=None, packed_output=None, workspace=None, kv_start=0, sm_scale=0.0, flags=0,
-    page_indptr=None,
+    page_indptr=None, plan=None,
 ) -> DecodeArgs:
     """Fill ``pfd_decode_args`` from torch tensors (device buffers).  With ``page_indptr``
-    (int32 ``[B + 1]``) ``block_table`` is the flat list of page ids it indexes."""
+    (int32 ``[B + 1]``) ``block_table`` is the flat list of page ids it indexes.  ``plan`` is the
+    buffer ``plan_decode`` filled for the same inputs."""
     a = DecodeArgs()
     a.struct_size = C.sizeof(DecodeArgs)
     a.flags = flags
@@ -182,16 +185,44 @@ def decode_args(
         a.partial_dtype = _dtype_code(po.dtype)
         a.partial_stride_b, a.partial_stride_h, a.partial_stride_s = pm.stride()
         a.workspace_splits = po.shape[2]
-        if len(workspace) > 4 and workspace[4] is not None:
-            a.semaphores = workspace[4].data_ptr()
-            a.num_semaphores = workspace[4].numel()
     if output is not None:
         a.output = output.data_ptr()
         a.o_stride_b, a.o_stride_h = output.stride(0), output.stride(1)
     if packed_output is not None:
         a.packed_output = packed_output.data_ptr()
+    if plan is not None:
+        a.plan = plan.data_ptr()
     a.stream = _stream(query)
     return a
+
+
+def plan_bytes(batch: int, num_kv_heads: int) -> int:
+    """Size of the plan buffer of ``plan_decode`` on the current device (``pfd_plan_bytes``)."""
+    lib = load()
+    lib.pfd_plan_bytes.argtypes = [C.c_int32, C.c_int32]
+    lib.pfd_plan_bytes.restype = C.c_int64
+    n = int(lib.pfd_plan_bytes(int(batch), int(num_kv_heads)))
+    if n < 0:
+        raise RuntimeError(lib.pfd_last_error().decode())
+    return n
+
+
+def plan_decode(query, key_cache, value_cache, block_table, seq_lens, *, plan=None, **kw) -> torch.Tensor:
+    """``pfd_plan_decode``: the work split of a model step's decode calls, computed once from the
+    lengths and the block table; pass the returned int32 buffer as ``plan=`` to the decode calls
+    of every layer.  Keywords as for ``decode_args``."""
+    kw.setdefault("k_scale", 1.0)
+    kw.setdefault("v_scale", 1.0)
+    args = decode_args(query, key_cache, value_cache, block_table, seq_lens, **kw)
+    if plan is None:
+        with torch.cuda.device(query.device):
+            plan = torch.empty(plan_bytes(query.shape[0], key_cache.shape[2]) // 4, dtype=torch.int32, device=query.device)
+    lib = load()
+    lib.pfd_plan_decode.argtypes = [C.POINTER(DecodeArgs), C.c_int32, C.c_void_p, C.c_int64]
+    lib.pfd_plan_decode.restype = C.c_int
+    with torch.cuda.device(query.device):
+        _check(lib.pfd_plan_decode(C.byref(args), key_cache.element_size(), plan.data_ptr(), plan.numel() * 4))
+    return plan
 
 
 def paged_decode_fp8_e4m3_split_out(query, key_cache, value_cache, block_table, seq_lens, **kw) -> None:
@@ -264,7 +295,29 @@ def device_status() -> int:
     return int(value.value)
 
 
-PATH_NAMES = {0: "none", 1: "fixed-split grid (plain loads) + merge", 2: "fixed-split grid (TMA) + merge", 3: "balanced persistent kernel + merge", 4: "balanced persistent kernel (16-bit caches) + merge"}
+def set_wait_limit_ns(limit_ns: int) -> None:
+    """How long a device-side wait may last before it gives up and sets the error word (``pfd_set_wait_limit_ns``)."""
+    lib = load()
+    lib.pfd_set_wait_limit_ns.argtypes = [C.c_uint64]
+    lib.pfd_set_wait_limit_ns.restype = C.c_int
+    _check(lib.pfd_set_wait_limit_ns(int(limit_ns)))
+
+
+def selftest_bounded_wait(limit_ns: int) -> int:
+    """Run the bounded-wait self-test kernel; returns the nanoseconds the wait lasted on the device.
+    ``device_status()`` reads 1 afterwards."""
+    lib = load()
+    lib.pfd_selftest_bounded_wait.argtypes = [C.c_uint64, C.POINTER(C.c_uint64), C.c_void_p]
+    lib.pfd_selftest_bounded_wait.restype = C.c_int
+    waited = C.c_uint64(0)
+    _check(lib.pfd_selftest_bounded_wait(int(limit_ns), C.byref(waited), torch.cuda.current_stream().cuda_stream))
+    return int(waited.value)
+
+
+PATH_NAMES = {0: "none", 1: "fixed-split grid (plain loads) + merge", 2: "fixed-split grid (TMA) + merge",
+              3: "balanced persistent kernel + merge", 4: "balanced persistent kernel (16-bit caches) + merge",
+              5: "balanced persistent kernel with a plan (one launch)",
+              6: "balanced persistent kernel with a plan (16-bit caches, one launch)"}
 
 
 def balanced_workspace_rows(num_q_heads: int, num_kv_heads: int) -> int:

@@ -5,8 +5,9 @@
 //       integrations/vllm/cuda/l20_paged_decode.cpp:128-135 (schema), :138-143 (CUDA impl),
 //       :153-155 (pybind export of the same launcher)
 // and adds "paged_decode_fp8_e4m3_split_out_v2" (per-kv-head scale tensors, explicit softmax
-// scale, kv_start, optional packed (o, m, l) output, PFD_FLAG_* bits; the semaphores operand is
-// accepted and unused) plus "merge_packed_partials" and "resolve_slots".  Every op only unpacks tensors into the C ABI of libpaged_fp8_decode.so
+// scale, kv_start, optional packed (o, m, l) output, PFD_FLAG_* bits, an optional plan),
+// "plan_decode", "merge_packed_partials" and "resolve_slots".  Every op only unpacks tensors
+// into the C ABI of libpaged_fp8_decode.so
 // (include/paged_fp8_decode.h); there is no computation here and no fallback.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -33,9 +34,9 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
                 const c10::optional<at::Tensor>& packed_output, double k_scale, double v_scale,
                 const c10::optional<at::Tensor>& k_scale_ph, const c10::optional<at::Tensor>& v_scale_ph,
                 double sm_scale, int64_t max_seq_len, int64_t split_size, int64_t kv_start,
-                int64_t flags, const c10::optional<at::Tensor>& semaphores = c10::nullopt,
+                int64_t flags, const c10::optional<at::Tensor>& plan = c10::nullopt,
                 int64_t prefix_len = 0, bool kv16 = false,
-                const c10::optional<at::Tensor>& page_indptr = c10::nullopt) {
+                const c10::optional<at::Tensor>& page_indptr = c10::nullopt, bool plan_only = false) {
   TORCH_CHECK(query.is_cuda(), "query must be CUDA");
   TORCH_CHECK(query.scalar_type() == at::kHalf || query.scalar_type() == at::kBFloat16,
               "query must be FP16 or BF16");
@@ -156,14 +157,18 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
                 "packed_output must be float32 [B, Hq, D + 2]");
     a.packed_output = packed_output->data_ptr<float>();
   }
-  if (semaphores.has_value()) {
-    TORCH_CHECK(semaphores->is_cuda() && semaphores->scalar_type() == at::kInt && semaphores->is_contiguous(),
-                "semaphores must be a contiguous int32 CUDA tensor");
-    a.semaphores = semaphores->data_ptr<int32_t>();
-    a.num_semaphores = semaphores->numel();
+  if (plan.has_value()) {
+    TORCH_CHECK(plan->is_cuda() && plan->scalar_type() == at::kInt && plan->is_contiguous(),
+                "plan must be a contiguous int32 CUDA tensor");
+    a.plan = plan->data_ptr<int32_t>();
   }
   const at::cuda::CUDAGuard guard(query.device());
   a.stream = at::cuda::getCurrentCUDAStream().stream();
+  if (plan_only) {
+    TORCH_CHECK(plan.has_value(), "plan_decode needs a plan buffer");
+    TORCH_CHECK(pfd_plan_decode(&a, kv16 ? 2 : 1, a.plan, plan->numel() * 4) == PFD_OK, pfd_last_error());
+    return;
+  }
   const int rc = kv16             ? pfd_paged_decode_kv16_split_out(&a)
                  : prefix_len > 0 ? pfd_shared_prefix_decode_fp8_e4m3(&a, static_cast<int32_t>(prefix_len))
                                   : pfd_paged_decode_fp8_e4m3_split_out(&a);
@@ -193,6 +198,17 @@ at::Tensor paged_decode_split_out(at::Tensor query, at::Tensor key_cache, at::Te
              partial_sum, output, c10::nullopt, 1.0, 1.0, c10::nullopt, c10::nullopt, 0.0,
              max_seq_len, split_size, 0, 0, c10::nullopt, 0, /*kv16=*/true);
   return output;
+}
+
+// Superset of the above: PFD_FLAG_* bits and an optional plan (pfd_plan_decode).
+void paged_decode_split_out_v2(at::Tensor query, at::Tensor key_cache, at::Tensor value_cache,
+                               at::Tensor block_table, at::Tensor seq_lens, at::Tensor partial_output,
+                               at::Tensor partial_max, at::Tensor partial_sum, at::Tensor output,
+                               int64_t max_seq_len, int64_t split_size, int64_t flags,
+                               c10::optional<at::Tensor> plan) {
+  run_decode(query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max,
+             partial_sum, output, c10::nullopt, 1.0, 1.0, c10::nullopt, c10::nullopt, 0.0,
+             max_seq_len, split_size, 0, flags, plan, 0, /*kv16=*/true);
 }
 
 // The same with FlashInfer's page addressing (indptr [B + 1], indices): argument list of
@@ -233,11 +249,28 @@ void paged_decode_fp8_e4m3_split_out_v2(at::Tensor query, at::Tensor key_cache, 
                                         c10::optional<at::Tensor> packed_output, at::Tensor k_scale,
                                         at::Tensor v_scale, double sm_scale, int64_t max_seq_len,
                                         int64_t split_size, int64_t kv_start, int64_t flags,
-                                        c10::optional<at::Tensor> semaphores) {
+                                        c10::optional<at::Tensor> plan) {
   TORCH_CHECK(output.has_value() || packed_output.has_value(), "no output given");
   run_decode(query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max,
              partial_sum, output, packed_output, 1.0, 1.0, k_scale, v_scale, sm_scale, max_seq_len,
-             split_size, kv_start, flags, semaphores);
+             split_size, kv_start, flags, plan);
+}
+
+// The work split of a model step's decode calls (pfd_plan_decode), written into `plan`; the
+// caches are passed for their geometry only.  plan.numel() * 4 >= plan_bytes(batch, kv heads).
+void plan_decode(at::Tensor query, at::Tensor key_cache, at::Tensor value_cache, at::Tensor block_table,
+                 at::Tensor seq_lens, at::Tensor partial_output, at::Tensor partial_max, at::Tensor partial_sum,
+                 at::Tensor plan, int64_t max_seq_len, int64_t split_size, int64_t kv_start) {
+  const bool kv16 = key_cache.scalar_type() == query.scalar_type();
+  run_decode(query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max, partial_sum,
+             c10::nullopt, c10::nullopt, 1.0, 1.0, c10::nullopt, c10::nullopt, 0.0, max_seq_len, split_size,
+             kv_start, 0, plan, 0, kv16, c10::nullopt, /*plan_only=*/true);
+}
+
+int64_t plan_bytes(int64_t batch, int64_t num_kv_heads) {
+  const int64_t n = pfd_plan_bytes(static_cast<int32_t>(batch), static_cast<int32_t>(num_kv_heads));
+  TORCH_CHECK(n >= 0, pfd_last_error());
+  return n;
 }
 
 // Decode step of a batch whose requests all share the first prefix_len tokens' pages: dense
@@ -364,6 +397,11 @@ TORCH_LIBRARY(l20_stack, module) {
       "Tensor(c!) partial_sum, Tensor(d!) output, "
       "int max_seq_len, int split_size) -> Tensor(d!)");
   module.def(
+      "paged_decode_split_out_v2("
+      "Tensor query, Tensor key_cache, Tensor value_cache, Tensor block_table, Tensor seq_lens, "
+      "Tensor(a!) partial_output, Tensor(b!) partial_max, Tensor(c!) partial_sum, Tensor(d!) output, "
+      "int max_seq_len, int split_size, int flags, Tensor(e!)? plan) -> ()");
+  module.def(
       "paged_decode_split_indices_out("
       "Tensor query, Tensor key_cache, Tensor value_cache, "
       "Tensor page_indptr, Tensor page_indices, Tensor seq_lens, "
@@ -385,7 +423,11 @@ TORCH_LIBRARY(l20_stack, module) {
       "Tensor(a!)? partial_output, Tensor(b!)? partial_max, "
       "Tensor(c!)? partial_sum, Tensor(d!)? output, Tensor(e!)? packed_output, "
       "Tensor k_scale, Tensor v_scale, float sm_scale, "
-      "int max_seq_len, int split_size, int kv_start, int flags, Tensor(f!)? semaphores) -> ()");
+      "int max_seq_len, int split_size, int kv_start, int flags, Tensor(f!)? plan) -> ()");
+  module.def(
+      "plan_decode(Tensor query, Tensor key_cache, Tensor value_cache, Tensor block_table, Tensor seq_lens, "
+      "Tensor partial_output, Tensor partial_max, Tensor partial_sum, Tensor(a!) plan, "
+      "int max_seq_len, int split_size, int kv_start) -> ()");
   module.def(
       "shared_prefix_decode_fp8_e4m3("
       "Tensor query, Tensor key_cache, Tensor value_cache, Tensor block_table, Tensor seq_lens, "
@@ -395,15 +437,18 @@ TORCH_LIBRARY(l20_stack, module) {
       "rope_and_cache(Tensor(a!) query, Tensor(b!) key, Tensor value, Tensor positions, Tensor cos_sin_cache, "
       "bool is_neox, Tensor(c!) key_cache, Tensor(d!) value_cache, Tensor slot_mapping, "
       "Tensor? k_scale, Tensor? v_scale) -> ()");
+  module.def("plan_bytes(int batch, int num_kv_heads) -> int", &plan_bytes);
   module.def("merge_packed_partials(Tensor packed, Tensor(a!) output) -> ()");
   module.def("resolve_slots(Tensor block_table, Tensor seq_lens, Tensor(a!) slots) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(l20_stack, CUDA, module) {
   module.impl("paged_decode_split_out", &paged_decode_split_out);
+  module.impl("paged_decode_split_out_v2", &paged_decode_split_out_v2);
   module.impl("paged_decode_split_indices_out", &paged_decode_split_indices_out);
   module.impl("paged_decode_fp8_e4m3_split_out", &paged_decode_fp8_e4m3_split_out);
   module.impl("paged_decode_fp8_e4m3_split_out_v2", &paged_decode_fp8_e4m3_split_out_v2);
+  module.impl("plan_decode", &plan_decode);
   module.impl("shared_prefix_decode_fp8_e4m3", &shared_prefix_decode_fp8_e4m3);
   module.impl("rope_and_cache", &rope_and_cache);
   module.impl("merge_packed_partials", &merge_packed_partials);

@@ -22,6 +22,8 @@ thread_local std::string g_last_error;
 thread_local int g_last_path = 0;  // PFD_PATH_* of this thread's last decode call
 unsigned long long* g_phase_times = nullptr;  // tuning builds (-DPFD_PHASE_STAMPS) only: stamp buffer
 std::atomic<int64_t> g_launches{0};
+// How long a device-side wait for a copy may last before it gives up (pfd_set_wait_limit_ns).
+std::atomic<unsigned long long> g_wait_limit_ns{200ull * 1000 * 1000};
 
 int fail(int code, const char* fmt, ...) {
   char buf[512];
@@ -110,7 +112,6 @@ int get_tensor_map(const void* base, int64_t stride_page, int64_t stride_token, 
                    int64_t num_pages, int32_t heads, int32_t promotion, CUtensorMap* out, int32_t elem_bytes = 1) {
   int dev = 0;
   cudaGetDevice(&dev);
-  if (const char* env = getenv("PFD_L2_PROMOTION")) promotion = atoi(env);  // tuning aid: 0, 64, 128, 256
   const MapKey key{dev, base, stride_page, stride_token, stride_head, num_pages, heads, promotion, elem_bytes};
   std::lock_guard<std::mutex> lock(g_state_mutex);
   for (const MapEntry& e : g_maps)
@@ -172,6 +173,7 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
   pfd::TmaParams tp{};
   tp.head_is_dim1 = head_is_dim1(a.k_stride_token, a.k_stride_head) ? 1 : 0;
   if (int rc = status_pointer(&tp.status)) return rc;
+  tp.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   auto kernel = pfd::paged_decode_fp8_partial_tma_kernel<QBF16, kWarps, kStages>;
   constexpr int smem = 1024 + kWarps * kStages * 8192 + kWarps * kStages * 8 + 2 * kWarps * 16 * 4;
   static bool configured[kMaxDevices] = {false};
@@ -229,10 +231,10 @@ int sm_count_of(int dev, int* out) {
 // The balanced path treats the workspace as a flat array of (o, m, l) rows: two slots of
 // num_q_heads rows for each group of num_kv_heads warps.  It needs a dense f32 workspace of
 // that capacity; a call that does not qualify runs on the fixed-split grid instead.
-bool balanced_eligible(const pfd_decode_args& a, const pfd::KernelParams& kp, int sms) {
+bool balanced_eligible(const pfd_decode_args& a, int group, int slot_offset, int sms) {
   if (a.flags & (PFD_FLAG_FIXED_SPLITS | PFD_FLAG_NO_TMA | PFD_FLAG_NO_DIRECT_OUT)) return false;
-  if (kp.slot_offset != 0) return false;  // slots in front belong to the dense prefix pass
-  if (!tma_eligible(a) || kp.group > 8 || a.batch > kChunkMaxBatch) return false;
+  if (slot_offset != 0) return false;  // slots in front belong to the dense prefix pass
+  if (a.head_dim != 128 || !tma_eligible(a) || group > 8 || a.batch > kChunkMaxBatch) return false;
   if (a.num_kv_heads > kChunkWarps * sms / 2) return false;  // one warp per kv head and group
   if (!a.partial_output || !a.partial_max || !a.partial_sum || a.partial_dtype != PFD_DTYPE_F32) return false;
   if (a.partial_stride_s != 1 || a.partial_stride_h != a.workspace_splits ||
@@ -240,6 +242,14 @@ bool balanced_eligible(const pfd_decode_args& a, const pfd::KernelParams& kp, in
     return false;
   const int64_t rows = (int64_t)a.batch * a.num_q_heads * a.workspace_splits;
   return rows >= 2LL * (sms * kChunkWarps / a.num_kv_heads) * a.num_q_heads;
+}
+
+// Warps of the balanced grid that take part: all of them, or fewer when the workspace has room
+// for fewer slots (max_groups > 0).  The plan is made for the same number.
+int balanced_num_warps(int sms, int warps_per_cta, int num_kv_heads, int max_groups) {
+  int n = sms * warps_per_cta;
+  if (max_groups > 0) n = std::min(n, max_groups * num_kv_heads);
+  return n;
 }
 
 // max_groups > 0 caps the number of warp groups (a workspace with room for fewer slots).
@@ -257,6 +267,7 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
   pfd::TmaParams tp{};
   tp.head_is_dim1 = head_is_dim1(a.k_stride_token, a.k_stride_head) ? 1 : 0;
   if (int rc = status_pointer(&tp.status)) return rc;
+  tp.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   tp.phase_times = g_phase_times;
   auto kernel = pfd::paged_decode_fp8_chunk_kernel<QBF16, kStagesT, kWarpsT, KV16>;
   constexpr int kThreads = kWarpsT * 32;
@@ -276,10 +287,13 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
   }
   pfd::ChunkParams cp{};
   cp.batch = a.batch;
-  cp.num_warps = sms * kWarpsT;
-  if (max_groups > 0) cp.num_warps = std::min(cp.num_warps, max_groups * a.num_kv_heads);
+  cp.num_warps = balanced_num_warps(sms, kWarpsT, a.num_kv_heads, max_groups);
   cp.piece_cost = kChunkPieceCost;
-  if (const char* env = getenv("PFD_PIECE_COST")) cp.piece_cost = std::max(0, std::min(atoi(env), 64));  // tuning aid
+  // A plan is used when the pieces can be combined in the kernel: f32 pieces, and not a timing
+  // run of the streaming part alone.
+  const bool planned = a.plan != nullptr && a.partial_dtype == PFD_DTYPE_F32;
+  cp.plan = planned ? static_cast<int32_t*>(a.plan) : nullptr;
+  cp.merge_in_kernel = planned && !(a.flags & PFD_FLAG_PARTIAL_ONLY) ? 1 : 0;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -295,8 +309,9 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
     if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "balanced decode kernel launch failed: %s", cudaGetErrorString(e));
     if (int rc = check_launch("balanced decode kernel")) return rc;
   }
-  g_last_path = KV16 ? PFD_PATH_BALANCED_KV16 : PFD_PATH_BALANCED;
-  if (a.flags & PFD_FLAG_PARTIAL_ONLY) return PFD_OK;
+  g_last_path = planned ? (KV16 ? PFD_PATH_PLANNED_KV16 : PFD_PATH_PLANNED)
+                        : (KV16 ? PFD_PATH_BALANCED_KV16 : PFD_PATH_BALANCED);
+  if (planned || (a.flags & PFD_FLAG_PARTIAL_ONLY)) return PFD_OK;
   {
     // Few rows mean few, long sequences whose pieces are many: four warps then share a row,
     // which also puts more loads in flight per SM.  Either way 64 registers, 8 CTAs per SM.
@@ -324,7 +339,7 @@ int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     if (int rc = sm_count_of(dev, &sms)) return rc;
-    if (balanced_eligible(a, kp, sms)) return launch_balanced<QBF16, kChunkStages, kChunkWarps>(a, kp, sms, stream);
+    if (balanced_eligible(a, kp.group, kp.slot_offset, sms)) return launch_balanced<QBF16, kChunkStages, kChunkWarps>(a, kp, sms, stream);
   }
   if (a.page_indptr != nullptr)
     return fail(PFD_ERR_UNSUPPORTED,
@@ -411,6 +426,10 @@ pfd::KernelParams fill_params(const pfd_decode_args& a, int group, bool direct_o
   kp.slot_offset = slot_offset;
   kp.early_metadata = (a.flags & PFD_FLAG_EARLY_METADATA) ? 1 : 0;
   kp.kv_evict_first = 1;
+#ifdef PFD_BOUNDS_CHECK
+  kp.dbg_ws_rows = (int64_t)a.batch * a.num_q_heads * a.workspace_splits;
+  kp.dbg_batch = a.batch;
+#endif
   return kp;
 }
 
@@ -499,6 +518,7 @@ int launch_prefix(const pfd_decode_args& a, int prefix_len, int chunks) {
   pp.prefix_len = prefix_len;
   pp.batch = a.batch;
   if (int rc = status_pointer(&pp.status)) return rc;
+  pp.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   pp.phase_times = g_phase_times;
   auto kernel = pfd::shared_prefix_dense_kernel<QBF16>;
   constexpr int smem = 1024 + 160 * 1024 + 32 + 2 * 4 * 128 * 4;
@@ -523,7 +543,14 @@ extern "C" {
 int pfd_paged_decode_fp8_e4m3_split_out(const pfd_decode_args* args) { return decode_impl(args, 0); }
 
 // ---- non-quantised sibling: caches in the query's 16-bit type --------------------------------
-int pfd_paged_decode_kv16_split_out(const pfd_decode_args* args) {
+}  // extern "C"
+
+namespace {
+// Argument checks of the 16-bit-cache operator; *cap = the number of warp groups its workspace
+// has room for (two slots of num_q_heads rows each).  A workspace too small for one group's
+// slots -- the reference's [B, Hq, ceil(max / split)] sizing for a single short request -- still
+// runs: with one group every sequence lies inside one chunk and nothing is written to it.
+int validate_kv16(const pfd_decode_args* args, int* cap, int* sms_out, bool need_output) {
   if (args == nullptr) return fail(PFD_ERR_INVALID, "args is NULL");
   if (args->struct_size != sizeof(pfd_decode_args))
     return fail(PFD_ERR_INVALID, "pfd_decode_args size mismatch: caller %u, library %zu", args->struct_size,
@@ -539,11 +566,13 @@ int pfd_paged_decode_kv16_split_out(const pfd_decode_args* args) {
     return fail(PFD_ERR_INVALID, "query must be FP16 or BF16");
   if (a.split_size < 16 || a.split_size % 16 != 0) return fail(PFD_ERR_INVALID, "split_size must be a multiple of 16");
   if (a.kv_start < 0 || a.max_seq_len < 0) return fail(PFD_ERR_INVALID, "negative length");
+  *cap = 1;
+  *sms_out = 0;
   if (a.batch == 0) return PFD_OK;
   if (a.batch > kChunkMaxBatch) return fail(PFD_ERR_UNSUPPORTED, "at most %d sequences per call", kChunkMaxBatch);
   if (!a.query || !a.key_cache || !a.value_cache || !a.block_table || !a.seq_lens)
     return fail(PFD_ERR_INVALID, "NULL operand");
-  if (!a.output && !a.packed_output) return fail(PFD_ERR_INVALID, "no output given");
+  if (need_output && !a.output && !a.packed_output) return fail(PFD_ERR_INVALID, "no output given");
   if (a.q_stride_h % 2 || a.q_stride_b % 2 || (reinterpret_cast<uintptr_t>(a.query) & 3u))
     return fail(PFD_ERR_UNSUPPORTED, "query rows must be 4-byte aligned");
   if (!aligned16(a.key_cache) || !aligned16(a.value_cache) || a.k_stride_page % 8 || a.k_stride_token % 8 ||
@@ -553,29 +582,106 @@ int pfd_paged_decode_kv16_split_out(const pfd_decode_args* args) {
         a.k_stride_head > 0 && a.v_stride_head > 0 && a.num_pages > 0 &&
         head_is_dim1(a.k_stride_token, a.k_stride_head) == head_is_dim1(a.v_stride_token, a.v_stride_head)))
     return fail(PFD_ERR_UNSUPPORTED, "K and V caches must share one (page, token, head) order with positive strides");
-  if (!a.partial_output || !a.partial_max || !a.partial_sum)
-    return fail(PFD_ERR_INVALID, "partial output workspace has wrong shape");
-  if (a.partial_dtype < PFD_DTYPE_F32 || a.partial_dtype > PFD_DTYPE_BF16)
-    return fail(PFD_ERR_INVALID, "partial_output dtype must be f32, f16 or bf16");
-  if (!aligned16(a.partial_output)) return fail(PFD_ERR_UNSUPPORTED, "partial_output must be 16-byte aligned");
-  if (a.partial_stride_s != 1 || a.partial_stride_h != a.workspace_splits ||
-      a.partial_stride_b != (int64_t)a.num_q_heads * a.workspace_splits)
-    return fail(PFD_ERR_UNSUPPORTED, "the partial workspace must be dense [batch, q heads, splits]");
-  // The workspace is a flat list of rows, two slots of num_q_heads rows per group of warps: its
-  // size caps the number of groups (the reference's [B, Hq, ceil(max/split)] always holds one).
-  const int64_t rows = (int64_t)a.batch * a.num_q_heads * a.workspace_splits;
-  const int64_t groups = rows / (2LL * a.num_q_heads);
-  if (groups < 1) return fail(PFD_ERR_INVALID, "partial output workspace has wrong shape");
-  int dev = 0, sms = 0;
+  int64_t groups = 0;
+  if (a.partial_output || a.partial_max || a.partial_sum) {
+    if (!a.partial_output || !a.partial_max || !a.partial_sum)
+      return fail(PFD_ERR_INVALID, "partial output workspace has wrong shape");
+    if (a.partial_dtype < PFD_DTYPE_F32 || a.partial_dtype > PFD_DTYPE_BF16)
+      return fail(PFD_ERR_INVALID, "partial_output dtype must be f32, f16 or bf16");
+    if (!aligned16(a.partial_output)) return fail(PFD_ERR_UNSUPPORTED, "partial_output must be 16-byte aligned");
+    if (a.partial_stride_s != 1 || a.partial_stride_h != a.workspace_splits ||
+        a.partial_stride_b != (int64_t)a.num_q_heads * a.workspace_splits)
+      return fail(PFD_ERR_UNSUPPORTED, "the partial workspace must be dense [batch, q heads, splits]");
+    // The workspace is a flat list of rows, two slots of num_q_heads rows per group of warps: its
+    // size caps the number of groups.
+    const int64_t rows = (int64_t)a.batch * a.num_q_heads * a.workspace_splits;
+    groups = rows / (2LL * a.num_q_heads);
+  }
+  int dev = 0;
   cudaGetDevice(&dev);
-  if (int rc = sm_count_of(dev, &sms)) return rc;
-  if (a.num_kv_heads > kChunkWarps16 * sms / 2) return fail(PFD_ERR_UNSUPPORTED, "too many KV heads");
+  if (int rc = sm_count_of(dev, sms_out)) return rc;
+  if (a.num_kv_heads > kChunkWarps16 * *sms_out / 2) return fail(PFD_ERR_UNSUPPORTED, "too many KV heads");
+  *cap = (int)std::min<int64_t>(std::max<int64_t>(groups, 1), 1 << 20);
+  return PFD_OK;
+}
+}  // namespace
+
+extern "C" {
+
+int pfd_paged_decode_kv16_split_out(const pfd_decode_args* args) {
+  int cap = 1, sms = 0;
+  if (int rc = validate_kv16(args, &cap, &sms, true)) return rc;
+  const pfd_decode_args& a = *args;
+  if (a.batch == 0) return PFD_OK;
+  const int group = a.num_q_heads / a.num_kv_heads;
   const pfd::KernelParams kp = fill_params(a, group, !(a.flags & PFD_FLAG_NO_DIRECT_OUT), 0);
   cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
-  const int cap = (int)std::min<int64_t>(groups, 1 << 20);
   return a.query_dtype == PFD_DTYPE_BF16
              ? launch_balanced<true, kChunkStages16, kChunkWarps16, true>(a, kp, sms, stream, cap)
              : launch_balanced<false, kChunkStages16, kChunkWarps16, true>(a, kp, sms, stream, cap);
+}
+
+int64_t pfd_plan_bytes(int32_t batch, int32_t num_kv_heads) {
+  if (batch < 0 || batch > kChunkMaxBatch || num_kv_heads <= 0)
+    return fail(PFD_ERR_INVALID, "batch must be 0 .. %d and num_kv_heads positive", kChunkMaxBatch);
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaGetDevice failed");
+  if (int rc = sm_count_of(dev, &sms)) return rc;
+  const int max_groups = std::max(sms * kChunkWarps / num_kv_heads, 1);
+  return 4 * pfd::plan_words(batch, max_groups, num_kv_heads);
+}
+
+int pfd_plan_decode(const pfd_decode_args* args, int32_t cache_elem_bytes, void* plan, int64_t plan_bytes) {
+  if (plan == nullptr) return fail(PFD_ERR_INVALID, "plan is NULL");
+  if (cache_elem_bytes != 1 && cache_elem_bytes != 2) return fail(PFD_ERR_INVALID, "cache_elem_bytes must be 1 or 2");
+  if (reinterpret_cast<uintptr_t>(plan) & 15u) return fail(PFD_ERR_UNSUPPORTED, "plan must be 16-byte aligned");
+  int num_warps = 0;
+  if (cache_elem_bytes == 2) {
+    int cap = 1, sms = 0;
+    if (int rc = validate_kv16(args, &cap, &sms, false)) return rc;
+    if (args->batch == 0) return PFD_OK;
+    num_warps = balanced_num_warps(sms, kChunkWarps16, args->num_kv_heads, cap);
+  } else {
+    if (args == nullptr) return fail(PFD_ERR_INVALID, "args is NULL");
+    if (args->struct_size != sizeof(pfd_decode_args))
+      return fail(PFD_ERR_INVALID, "pfd_decode_args size mismatch: caller %u, library %zu", args->struct_size,
+                  sizeof(pfd_decode_args));
+    const pfd_decode_args& a = *args;
+    if (a.batch < 0 || a.num_q_heads <= 0 || a.num_kv_heads <= 0 || a.num_q_heads % a.num_kv_heads)
+      return fail(PFD_ERR_INVALID, "invalid query");
+    if (a.kv_start < 0) return fail(PFD_ERR_INVALID, "negative length");
+    if (a.batch == 0) return PFD_OK;
+    if (!a.block_table || !a.seq_lens) return fail(PFD_ERR_INVALID, "NULL operand");
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    if (int rc = sm_count_of(dev, &sms)) return rc;
+    if (a.page_size != pfd::kPage || !balanced_eligible(a, a.num_q_heads / a.num_kv_heads, 0, sms))
+      return fail(PFD_ERR_UNSUPPORTED,
+                  "no plan: this call does not run the balanced kernel (head_dim 128, at most 8 query heads per KV "
+                  "head, TMA-describable cache, dense f32 workspace of pfd_balanced_workspace_rows() rows, no "
+                  "fixed-split flags)");
+    num_warps = balanced_num_warps(sms, kChunkWarps, a.num_kv_heads, 0);
+  }
+  const pfd_decode_args& a = *args;
+  const int max_groups = std::max(num_warps / a.num_kv_heads, 1);
+  const int64_t need = 4 * pfd::plan_words(a.batch, max_groups, a.num_kv_heads);
+  if (plan_bytes < need)
+    return fail(PFD_ERR_INVALID, "plan buffer holds %lld bytes, this call needs %lld (pfd_plan_bytes)",
+                (long long)plan_bytes, (long long)need);
+  pfd::PlanParams pp{};
+  pp.seq_lens = a.seq_lens;
+  pp.block_table = a.block_table;
+  pp.page_indptr = a.page_indptr;
+  pp.bt_stride_b = a.bt_stride_b;
+  pp.batch = a.batch;
+  pp.kv_start = a.kv_start;
+  pp.num_kv_heads = a.num_kv_heads;
+  pp.max_groups = max_groups;
+  pp.piece_cost = kChunkPieceCost;
+  pp.plan = static_cast<int32_t*>(plan);
+  const int ctas = std::max(1, std::min(8, (max_groups + 31) / 32));
+  pfd::plan_decode_kernel<<<ctas, 1024, 0, static_cast<cudaStream_t>(a.stream)>>>(pp);
+  return check_launch("plan kernel");
 }
 
 int pfd_shared_prefix_decode_fp8_e4m3(const pfd_decode_args* args, int32_t prefix_len) {
@@ -605,7 +711,8 @@ int pfd_shared_prefix_decode_fp8_e4m3(const pfd_decode_args* args, int32_t prefi
   // the suffix pass validates the rest (it sees the same operands) before anything is launched
   a.kv_start = prefix_len;
   a.flags |= PFD_FLAG_FIXED_SPLITS | PFD_FLAG_NO_DIRECT_OUT;
-  a.flags &= ~(uint32_t)(PFD_FLAG_PARTIAL_ONLY | PFD_FLAG_BALANCED);
+  a.flags &= ~(uint32_t)PFD_FLAG_PARTIAL_ONLY;
+  a.plan = nullptr;
   {
     const int span = a.max_seq_len - prefix_len;
     const int ns = span > 0 ? (span + a.split_size - 1) / a.split_size : 1;
@@ -745,11 +852,47 @@ int pfd_debug_phase_times(void* device_buffer) {
 }
 #endif
 
+int pfd_set_wait_limit_ns(uint64_t limit_ns) {
+  if (limit_ns == 0) return fail(PFD_ERR_INVALID, "the wait limit must be positive");
+  g_wait_limit_ns.store(limit_ns, std::memory_order_relaxed);
+  return PFD_OK;
+}
+
+int pfd_selftest_bounded_wait(uint64_t limit_ns, uint64_t* waited_ns, void* stream) {
+  if (limit_ns == 0 || limit_ns > 1000ull * 1000 * 1000)
+    return fail(PFD_ERR_INVALID, "limit_ns must be between 1 ns and 1 s");
+  int32_t* status = nullptr;
+  if (int rc = status_pointer(&status)) return rc;
+  unsigned long long* dev_waited = nullptr;
+  // the word behind the status word of the same symbol would need a second symbol: keep the
+  // result in mapped pinned host memory instead, which needs no device allocation
+  unsigned long long* host_waited = nullptr;
+  if (waited_ns != nullptr) {
+    if (cudaHostAlloc(reinterpret_cast<void**>(&host_waited), sizeof(unsigned long long), cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer(reinterpret_cast<void**>(&dev_waited), host_waited, 0) != cudaSuccess) {
+      if (host_waited) cudaFreeHost(host_waited);
+      return fail(PFD_ERR_CUDA, "pinned host memory for the self-test is not available");
+    }
+    *host_waited = 0;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  pfd::bounded_wait_selftest_kernel<<<1, 32, 0, s>>>(status, limit_ns, dev_waited);
+  int rc = check_launch("bounded-wait self-test kernel");
+  if (rc == PFD_OK && cudaStreamSynchronize(s) != cudaSuccess) rc = fail(PFD_ERR_CUDA, "the self-test kernel failed");
+  if (waited_ns != nullptr) {
+    *waited_ns = *host_waited;
+    cudaFreeHost(host_waited);
+  }
+  return rc;
+}
+
 int pfd_device_status(int32_t* status) {
   if (status == nullptr) return fail(PFD_ERR_INVALID, "status is NULL");
   int32_t* p = nullptr;
   if (int rc = status_pointer(&p)) return rc;
-  cudaError_t e = cudaMemcpy(status, p, sizeof(int32_t), cudaMemcpyDeviceToHost);
+  cudaError_t e = cudaDeviceSynchronize();  // kernels on non-blocking streams included
+  if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaDeviceSynchronize failed: %s", cudaGetErrorString(e));
+  e = cudaMemcpy(status, p, sizeof(int32_t), cudaMemcpyDeviceToHost);
   if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "reading the device status failed: %s", cudaGetErrorString(e));
   if (*status != 0) {
     const int32_t zero = 0;

@@ -32,6 +32,8 @@ struct ChunkParams {
   int32_t batch;
   int32_t num_warps;   // warps of the whole grid; the merge kernel is told the same number
   int32_t piece_cost;  // what starting a sequence costs a warp, in half page pairs
+  int32_t merge_in_kernel;  // 1 (needs a plan): pieces are combined by their last arriver, no merge kernel follows
+  int32_t* plan;       // device plan written by plan_decode_kernel, or nullptr
 };
 
 // How the work is cut.  Cost is counted in half page pairs: sequence b owns the cost range that
@@ -447,8 +449,299 @@ __device__ __forceinline__ int64_t chunk_slot_row(int grp, int which, int num_q_
   return ((int64_t)(2 * grp + which)) * num_q_heads + hq;
 }
 
+// ---- the plan ------------------------------------------------------------------------------
+// Everything the chunk kernel derives from seq_lens and block_table alone, computed once per
+// model step (the metadata is the same for every layer) by plan_decode_kernel and read by the
+// chunk kernel of every layer: the pair prefix sum, each warp group's range of the pair list
+// with the page ids of its first 16 pairs (so a warp's first copies leave after one round trip
+// to L2), and one arrival counter per (sequence, kv head) that lets the pieces of a cut
+// sequence be combined inside the chunk kernel, by the warp whose piece arrives last.
+// Layout, in 32-bit words:
+//   [0, 16)            header (kPlan* indices below)
+//   [16, 16 + B + 1)   pairs before sequence b
+//   [.., + B)          sequence lengths
+//   groups_off         per group kPlanGroupWords words: P0, P1, 2 reserved, 32 page ids
+//   counters_off       B * Hkv arrival counters (page pairs consumed), zero between launches
+constexpr int kPlanMagic = 0x70666431;
+constexpr int kPlanHeaderWords = 16;
+constexpr int kPlanGroupWords = 36;
+enum { kPlanWMagic = 0, kPlanWBatch, kPlanWKvStart, kPlanWKvHeads, kPlanWMaxGroups, kPlanWPieceCost, kPlanWTotal,
+       kPlanWIndptr };
+__host__ __device__ inline int64_t plan_groups_off(int batch) { return (kPlanHeaderWords + 2 * (int64_t)batch + 1 + 3) & ~3LL; }
+__host__ __device__ inline int64_t plan_counters_off(int batch, int max_groups) {
+  return plan_groups_off(batch) + (int64_t)max_groups * kPlanGroupWords;
+}
+__host__ __device__ inline int64_t plan_words(int batch, int max_groups, int num_kv_heads) {
+  return plan_counters_off(batch, max_groups) + (int64_t)batch * num_kv_heads;
+}
+
+constexpr int kErrPlanMismatch = 2;
+
+// What a warp needs to walk the flattened pair list: the prefix sum and the lengths (shared
+// memory), the geometry, and the chunking.
+struct PairList {
+  const int32_t* prefix;  // [B + 1]
+  const int32_t* lens;    // [B]
+  int B, page_first;
+  // Sequence that holds pair g of the list (0 <= g < total): largest b with prefix[b] <= g.
+  __device__ __forceinline__ int seq_of(int g) const {
+    int lo_b = 0, hi_b = B;
+    while (hi_b - lo_b > 1) {
+      const int mid = (lo_b + hi_b) >> 1;
+      if (prefix[mid] <= g) lo_b = mid; else hi_b = mid;
+    }
+    return lo_b;
+  }
+  // Pairs whose first cost unit lies before cost position c.
+  __device__ __forceinline__ int pairs_before(const Chunking& chunks, int c) const {
+    const int total = prefix[B];
+    if (c >= 2 * total + chunks.piece_cost * B) return total;
+    int lo_b = 0, hi_b = B;  // largest b whose cost range starts at or before c
+    while (hi_b - lo_b > 1) {
+      const int mid = (lo_b + hi_b) >> 1;
+      if (2 * prefix[mid] + chunks.piece_cost * mid <= c) lo_b = mid; else hi_b = mid;
+    }
+    const int off = c - chunks.first_unit(prefix[lo_b], lo_b);  // units into the pairs of lo_b
+    return prefix[lo_b] + min(max((off + 1) >> 1, 0), prefix[lo_b + 1] - prefix[lo_b]);
+  }
+  // Page ids of 16 consecutive pairs of the chunk [P0, P1), one page per lane (lane 2t + u holds
+  // page u of pair P0 + base_t + t, -1 if there is none).
+  __device__ __forceinline__ int32_t fetch_ids(const KernelParams& p, int P0, int P1, int base_t, int lane) const {
+    int32_t phys = -1;
+    const int g = P0 + base_t + (lane >> 1);
+    if (g < P1) {
+      const int b = seq_of(g);
+      const int page = page_first + 2 * (g - prefix[b]) + (lane & 1);
+      if (page <= (lens[b] - 1) / kPage)
+        phys = p.page_indptr ? __ldg(p.block_table + __ldg(p.page_indptr + b) + page)
+                             : page_of(p.block_table, p.bt_stride_b, b, page);
+    }
+    return phys;
+  }
+};
+
+// Pairs per sequence and their exclusive prefix sum into shared memory, by all NT threads of the
+// CTA (every CTA computes the same).  Ends with a CTA-wide barrier.
+template <int NT>
+__device__ __forceinline__ void scan_pairs(const int32_t* __restrict__ seq_lens, int B, int kv_start,
+                                           int32_t* sm_scan, int32_t* prefix, int32_t* lens) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int per = (B + NT - 1) / NT;
+  const int b0 = threadIdx.x * per;
+  int local = 0;
+  for (int q = 0; q < per; ++q) {
+    const int b = b0 + q;
+    if (b < B) {
+      const int len = seq_lens[b];
+      lens[b] = len;
+      local += pairs_of(len, kv_start);
+    }
+  }
+  int incl = local;  // inclusive scan over the CTA's threads
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int x = __shfl_up_sync(0xffffffffu, incl, off);
+    if (lane >= off) incl += x;
+  }
+  if (lane == 31) sm_scan[warp] = incl;
+  __syncthreads();
+  int before = 0;
+  for (int w = 0; w < warp; ++w) before += sm_scan[w];
+  int run = before + incl - local;
+  for (int q = 0; q < per; ++q) {
+    const int b = b0 + q;
+    if (b < B) {
+      prefix[b] = run;
+      run += pairs_of(lens[b], kv_start);
+    }
+  }
+  if (threadIdx.x == NT - 1) prefix[B] = before + incl;
+  __syncthreads();
+}
+
+struct PlanParams {
+  const int32_t* __restrict__ seq_lens;
+  const int32_t* __restrict__ block_table;
+  const int32_t* __restrict__ page_indptr;
+  int64_t bt_stride_b;
+  int32_t batch, kv_start, num_kv_heads, max_groups, piece_cost;
+  int32_t* plan;
+};
+
+// Writes the plan.  grid = a few CTAs (each repeats the scan, then takes every gridDim-th warp
+// group), block = 1024 threads.  Needs batch <= kPlanMaxBatch.
+constexpr int kPlanMaxBatch = 2048;
+__global__ void __launch_bounds__(1024) plan_decode_kernel(const PlanParams pp) {
+  constexpr int NT = 1024;
+  __shared__ int32_t sm_scan[NT / 32];
+  __shared__ int32_t prefix[kPlanMaxBatch + 1];
+  __shared__ int32_t lens[kPlanMaxBatch];
+  const int B = pp.batch;
+  scan_pairs<NT>(pp.seq_lens, B, pp.kv_start, sm_scan, prefix, lens);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int32_t* plan = pp.plan;
+  if (blockIdx.x == 0) {
+    if (threadIdx.x < kPlanHeaderWords) {
+      int32_t v = 0;
+      switch (threadIdx.x) {
+        case kPlanWMagic: v = kPlanMagic; break;
+        case kPlanWBatch: v = B; break;
+        case kPlanWKvStart: v = pp.kv_start; break;
+        case kPlanWKvHeads: v = pp.num_kv_heads; break;
+        case kPlanWMaxGroups: v = pp.max_groups; break;
+        case kPlanWPieceCost: v = pp.piece_cost; break;
+        case kPlanWTotal: v = prefix[B]; break;
+        case kPlanWIndptr: v = pp.page_indptr != nullptr ? 1 : 0; break;
+        default: break;
+      }
+      plan[threadIdx.x] = v;
+    }
+    for (int x = threadIdx.x; x <= B; x += NT) plan[kPlanHeaderWords + x] = prefix[x];
+    for (int x = threadIdx.x; x < B; x += NT) plan[kPlanHeaderWords + B + 1 + x] = lens[x];
+  }
+  {
+    int32_t* counters = plan + plan_counters_off(B, pp.max_groups);
+    const int n = B * pp.num_kv_heads;
+    for (int x = blockIdx.x * NT + threadIdx.x; x < n; x += gridDim.x * NT) counters[x] = 0;
+  }
+  KernelParams kp{};  // only what fetch_ids reads
+  kp.block_table = pp.block_table;
+  kp.page_indptr = pp.page_indptr;
+  kp.bt_stride_b = pp.bt_stride_b;
+  const PairList list{prefix, lens, B, pp.kv_start / kPage};
+  const Chunking chunks(prefix[B], B, max(pp.max_groups, 1), pp.piece_cost);
+  for (int grp = blockIdx.x * (NT / 32) + warp; grp < pp.max_groups; grp += gridDim.x * (NT / 32)) {
+    const int total = prefix[B];
+    const int P0 = grp < chunks.groups ? list.pairs_before(chunks, chunks.start_of(grp)) : total;
+    const int P1 = grp < chunks.groups ? list.pairs_before(chunks, chunks.start_of(grp + 1)) : total;
+    const int32_t id = list.fetch_ids(kp, P0, P1, 0, lane);
+    int32_t* gw = plan + plan_groups_off(B) + (int64_t)grp * kPlanGroupWords;
+    if (lane == 0) { gw[0] = P0; gw[1] = P1; gw[2] = 0; gw[3] = 0; }
+    gw[4 + lane] = id;
+  }
+}
+
+// (Builds with -DPFD_BOUNDS_CHECK, a debugging aid, verify every workspace row and sequence index
+// first and record a bad one through the stamp buffer instead of using it.)
+// In-kernel LSE merge of the pieces of one (sequence, kv head), run by the warp whose piece
+// arrived last: rows (query head h of the group, piece k) are fetched 32 at a time (one 512-byte
+// row per load instruction, all in flight together) from the workspace, which the pieces'
+// writers left in L2, and folded head by head with a running maximum.  Same maths as
+// _paged_split_kv_reduce (integrations/vllm/l20_paged_split_kv.py:459-488).
+template <bool QBF16>
+__device__ __forceinline__ void merge_pieces_of_sequence(const KernelParams& p, const Chunking& chunks, int b, int kvh,
+                                                       int np, int s0, int lane, const TmaParams& tp, int dbg) {
+  constexpr int D = 128, RB = 32;
+  const int w_first = chunks.chunk_of(s0);
+  const int ns = chunks.chunk_of(s0 + 2 * (np - 1)) - w_first + 1;
+#ifdef PFD_BOUNDS_CHECK
+  if (ns < 1 || w_first < 0 || w_first + ns > chunks.groups || b < 0 || b >= p.dbg_batch) {
+    mark_value_at(tp, dbg + 5, 0, lane == 0, ((unsigned long long)(unsigned)ns << 32) | (unsigned)w_first);
+    mark_value_at(tp, dbg + 5, 1, lane == 0, ((unsigned long long)(unsigned)b << 32) | (unsigned)np);
+    mark_value_at(tp, dbg + 5, 2, lane == 0, (unsigned long long)(unsigned)s0);
+    return;
+  }
+#else
+  (void)tp; (void)dbg;
+#endif
+  const int rows = ns * p.group;  // row r = h * ns + k
+  const float* po = reinterpret_cast<const float*>(p.partial_output);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float big = -INFINITY, den = 0.f;
+  for (int r0 = 0; r0 < rows; r0 += RB) {
+    float4 xv[RB];
+    float m_mine = -INFINITY, l_mine = 0.f;
+    {
+      const int r = r0 + lane;
+      if (r < rows) {
+        const int h = r / ns, k = r - h * ns, w = w_first + k;
+        const int64_t row = chunk_slot_row(w, s0 > chunks.start_of(w) ? 1 : 0, p.num_q_heads, kvh * p.group + h);
+#ifdef PFD_BOUNDS_CHECK
+        if (row < 0 || row >= p.dbg_ws_rows) { mark_value_at(tp, dbg + 1, 0, true, (unsigned long long)row); } else
+#endif
+        {
+          m_mine = __ldcg(p.partial_max + row);
+          l_mine = __ldcg(p.partial_sum + row);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < RB; ++u) {
+      const int r = r0 + u;
+      xv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r < rows) {
+        const int h = r / ns, k = r - h * ns, w = w_first + k;
+        const int64_t row = chunk_slot_row(w, s0 > chunks.start_of(w) ? 1 : 0, p.num_q_heads, kvh * p.group + h);
+#ifdef PFD_BOUNDS_CHECK
+        if (row < 0 || row >= p.dbg_ws_rows) { mark_value_at(tp, dbg + 1, 1, lane == 0, (unsigned long long)row); } else
+#endif
+        xv[u] = __ldcg(reinterpret_cast<const float4*>(po + row * D) + lane);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < RB; ++u) {
+      const int r = r0 + u;
+      const float mv = __shfl_sync(0xffffffffu, m_mine, u);
+      const float lv = __shfl_sync(0xffffffffu, l_mine, u);
+      if (r < rows) {  // warp-uniform
+        const int h = r / ns, k = r - h * ns;
+        if (k == 0) { acc[0] = acc[1] = acc[2] = acc[3] = 0.f; big = -INFINITY; den = 0.f; }
+        const float m_new = fmaxf(big, mv);
+        const float keep = (big == -INFINITY) ? 0.f : expf(big - m_new);
+        const float c = (mv == -INFINITY) ? 0.f : expf(mv - m_new);
+        den = den * keep + lv * c;
+        acc[0] = acc[0] * keep + c * xv[u].x; acc[1] = acc[1] * keep + c * xv[u].y;
+        acc[2] = acc[2] * keep + c * xv[u].z; acc[3] = acc[3] * keep + c * xv[u].w;
+        big = m_new;
+        if (k == ns - 1) {
+          const int hq = kvh * p.group + h;
+          if (p.packed_output != nullptr) {
+            float* dst = p.packed_output + ((int64_t)b * p.num_q_heads + hq) * (D + 2);
+            *reinterpret_cast<float2*>(dst + lane * 4) = make_float2(acc[0], acc[1]);
+            *reinterpret_cast<float2*>(dst + lane * 4 + 2) = make_float2(acc[2], acc[3]);
+            if (lane == 0) { dst[D] = big; dst[D + 1] = den; }
+          } else {
+            const float inv = 1.f / den;
+            uint16_t* dst = reinterpret_cast<uint16_t*>(p.output) + (int64_t)b * p.o_stride_b + (int64_t)hq * p.o_stride_h + lane * 4;
+            uint32_t w0, w1;
+            if constexpr (QBF16) {
+              __nv_bfloat162 x = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
+              __nv_bfloat162 y = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+              w0 = *reinterpret_cast<uint32_t*>(&x);
+              w1 = *reinterpret_cast<uint32_t*>(&y);
+            } else {
+              w0 = pack_f16x2(acc[0] * inv, acc[1] * inv);
+              w1 = pack_f16x2(acc[2] * inv, acc[3] * inv);
+            }
+            *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
+          }
+        }
+      }
+    }
+  }
+}
+
+// Rows of sequences with nothing to attend (seq_len <= kv_start): zeros, or (0, -inf, 0) packed.
+// The merge kernel writes them when it runs; with a plan the chunk kernel does, sequence b by
+// warp b mod (warps of the grid).
+template <int D>
+__device__ __forceinline__ void write_empty_sequence(const KernelParams& p, int b, int lane) {
+  for (int hq = 0; hq < p.num_q_heads; ++hq) {
+    if (p.packed_output != nullptr) {
+      float* dst = p.packed_output + ((int64_t)b * p.num_q_heads + hq) * (D + 2);
+      for (int d = lane; d < D; d += 32) dst[d] = 0.f;
+      if (lane == 0) { dst[D] = -INFINITY; dst[D + 1] = 0.f; }
+    } else {
+      uint16_t* dst = reinterpret_cast<uint16_t*>(p.output) + (int64_t)b * p.o_stride_b + (int64_t)hq * p.o_stride_h;
+      for (int d = lane; d < D; d += 32) dst[d] = 0;
+    }
+  }
+}
+
 // grid = one CTA per SM; block = NWARPS independent warps.  KV16 = false: e4m3 caches;
 // true: caches in the query's 16-bit type (the reference's non-quantised sibling operator).
+// cp.plan == nullptr: every CTA derives the work split itself and the merge kernel behind
+// combines the pieces; with a plan the split is read and the pieces are combined in here.
 template <bool QBF16, int NSTAGE, int NWARPS, bool KV16 = false>
 __global__ void __launch_bounds__(NWARPS * 32, 1)
 paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const ChunkParams cp,
@@ -464,9 +757,9 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_v)) : "memory");
   }
   // A programmatic dependent of whatever precedes it in the stream (normally the previous
-  // layer-step's merge kernel, which still reads the workspace): no memory access before that
+  // layer-step's last kernel, which may still read the workspace): no memory access before that
   // kernel has completed -- except, if the caller vouches that the preceding kernel does not
-  // write them, the reads of seq_lens and block_table.
+  // write them, the reads of seq_lens, block_table and the plan.
   if (!p.early_metadata) pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
   const int B = cp.batch, hkv = p.num_kv_heads;
@@ -474,6 +767,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
   const int W = (int)blockIdx.x * NWARPS + warp;
   const int grp = W / hkv, kvh = W - grp * hkv;  // one warp per kv head and group
   const int num_groups = cp.num_warps / hkv;
+  const bool planned = cp.plan != nullptr;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -482,6 +776,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
   int32_t* sm_scan = reinterpret_cast<int32_t*>(base + NWARPS * NSTAGE * kStage + NWARPS * NSTAGE * 8);  // [NWARPS]
   int32_t* prefix = sm_scan + NWARPS;  // [B + 1] pairs before sequence b
   int32_t* lens = prefix + (B + 1);    // [B]
+  const PairList list{prefix, lens, B, page_first};
 
   mark_phase_at(tp, W, 0, lane == 0);  // start
   mark_value_at(tp, W, 5, lane == 0, sm_id());
@@ -491,89 +786,41 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
 #pragma unroll
     for (int s = 0; s < NSTAGE; ++s) mbar_init(my_bars + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copies' completions see initialised barriers
   }
 
-  // ---- pairs per sequence and their exclusive prefix sum (every CTA computes the same)
-  {
-    const int per = (B + NT - 1) / NT;
-    const int b0 = threadIdx.x * per;
-    int local = 0;
-    for (int q = 0; q < per; ++q) {
-      const int b = b0 + q;
-      if (b < B) {
-        const int len = p.seq_lens[b];
-        lens[b] = len;
-        local += pairs_of(len, p.kv_start);
-      }
-    }
-    int incl = local;  // inclusive scan over the CTA's threads
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const int x = __shfl_up_sync(0xffffffffu, incl, off);
-      if (lane >= off) incl += x;
-    }
-    if (lane == 31) sm_scan[warp] = incl;
-    __syncthreads();
-    int before = 0;
-    for (int w = 0; w < warp; ++w) before += sm_scan[w];
-    int run = before + incl - local;
-    for (int q = 0; q < per; ++q) {
-      const int b = b0 + q;
-      if (b < B) {
-        prefix[b] = run;
-        run += pairs_of(lens[b], p.kv_start);
-      }
-    }
-    if (threadIdx.x == NT - 1) prefix[B] = before + incl;
-    __syncthreads();  // the last CTA-wide barrier: from here on the warps are on their own
+  int total, P0, P1;
+  int32_t ids_cur;
+  bool plan_ok = true;
+  if (planned) {
+    // one round trip: header, this group's range and the page ids of its first 16 pairs.  Every
+    // lane reads the same header words (broadcast loads), so nothing below depends on the lane.
+    const int32_t* gw = cp.plan + plan_groups_off(B) + (int64_t)min(grp, num_groups - 1) * kPlanGroupWords;
+    const int4 h0 = __ldg(reinterpret_cast<const int4*>(cp.plan));      // magic, batch, kv_start, kv heads
+    const int4 h1 = __ldg(reinterpret_cast<const int4*>(cp.plan) + 1);  // groups, piece cost, total, indptr
+    P0 = __ldg(gw);
+    P1 = __ldg(gw + 1);
+    ids_cur = __ldg(gw + 4 + lane);
+    plan_ok = h0.x == kPlanMagic && h0.y == B && h0.z == p.kv_start && h0.w == hkv && h1.x == num_groups &&
+              h1.y == cp.piece_cost && h1.w == (p.page_indptr != nullptr ? 1 : 0);
+    total = h1.z;
+    if (grp >= num_groups || !plan_ok) { P0 = P1 = total; ids_cur = -1; }
+    // prefix sum and lengths into shared memory; used only after the barrier further down
+    for (int x = threadIdx.x; x < 2 * B + 1; x += NT) prefix[x] = __ldg(cp.plan + kPlanHeaderWords + x);
+  } else {
+    scan_pairs<NT>(p.seq_lens, B, p.kv_start, sm_scan, prefix, lens);  // ends with the last CTA-wide barrier
+    total = prefix[B];
   }
-  mark_phase_at(tp, W, 1, lane == 0);  // scan done
-  const int total = prefix[B];
+  mark_phase_at(tp, W, 1, lane == 0);  // split known
   const Chunking chunks(total, B, max(num_groups, 1), cp.piece_cost);
-  // Pairs whose first cost unit lies before cost position c.
-  auto pairs_before = [&](int c) {
-    if (c >= 2 * total + chunks.piece_cost * B) return total;
-    int lo_b = 0, hi_b = B;  // largest b whose cost range starts at or before c
-    while (hi_b - lo_b > 1) {
-      const int mid = (lo_b + hi_b) >> 1;
-      if (2 * prefix[mid] + chunks.piece_cost * mid <= c) lo_b = mid; else hi_b = mid;
-    }
-    const int off = c - chunks.first_unit(prefix[lo_b], lo_b);  // units into the pairs of lo_b
-    return prefix[lo_b] + min(max((off + 1) >> 1, 0), prefix[lo_b + 1] - prefix[lo_b]);
-  };
   const int C0 = chunks.start_of(grp);
-  const int P0 = grp < chunks.groups ? pairs_before(C0) : total;
-  const int P1 = grp < chunks.groups ? pairs_before(chunks.start_of(grp + 1)) : total;
-  const int n = P1 - P0;
-  if (n <= 0) {
-    if (p.early_metadata) pdl_wait();  // this grid must not complete before the preceding one
-    return;
+  if (!planned) {
+    P0 = grp < chunks.groups ? list.pairs_before(chunks, C0) : total;
+    P1 = grp < chunks.groups ? list.pairs_before(chunks, chunks.start_of(grp + 1)) : total;
+    ids_cur = list.fetch_ids(p, P0, P1, 0, lane);
   }
+  const int n = P1 - P0;
 
-  // Sequence that holds pair g of the list (0 <= g < total): largest b with prefix[b] <= g.
-  auto seq_of = [&](int g) {
-    int lo_b = 0, hi_b = B;
-    while (hi_b - lo_b > 1) {
-      const int mid = (lo_b + hi_b) >> 1;
-      if (prefix[mid] <= g) lo_b = mid; else hi_b = mid;
-    }
-    return lo_b;
-  };
-
-  // ---- producer side.  Page ids of 16 consecutive pairs of the chunk, one page per lane
-  // (lane 2t + u holds page u of pair base + t, -1 if there is none).
-  auto fetch_ids = [&](int base_t) {
-    int32_t phys = -1;
-    const int g = P0 + base_t + (lane >> 1);
-    if (base_t < n && g < P1) {
-      const int b = seq_of(g);
-      const int page = page_first + 2 * (g - prefix[b]) + (lane & 1);
-      if (page <= (lens[b] - 1) / kPage)
-        phys = p.page_indptr ? __ldg(p.block_table + __ldg(p.page_indptr + b) + page)
-                             : page_of(p.block_table, p.bt_stride_b, b, page);
-    }
-    return phys;
-  };
   auto fire = [&](int t, int32_t ids, int base_t) {  // all lanes call; lane 0 issues
     const int32_t phys0 = __shfl_sync(0xffffffffu, ids, (2 * (t - base_t)) & 31);
     const int32_t phys1 = __shfl_sync(0xffffffffu, ids, (2 * (t - base_t) + 1) & 31);
@@ -607,14 +854,26 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       }
     }
   };
-  int32_t ids_cur = fetch_ids(0), ids_next = fetch_ids(16);
-  int ids_base = 0;
   __syncwarp();
   if (p.early_metadata) pdl_wait();
 #pragma unroll
   for (int t = 0; t < NSTAGE; ++t)
     if (t < n) fire(t, ids_cur, 0);
   mark_phase_at(tp, W, 2, lane == 0);  // first copies issued
+  if (planned) {
+    __syncthreads();  // the last CTA-wide barrier: prefix and lens are in shared memory
+    if (!plan_ok) {   // a plan made for another call: nothing is computed, the host reads the status word
+      if (threadIdx.x == 0) atomicExch(tp.status, kErrPlanMismatch);
+      return;
+    }
+    if (cp.merge_in_kernel)  // rows of sequences with nothing to attend
+      for (int b = W; b < B; b += cp.num_warps)
+        if (prefix[b + 1] == prefix[b]) write_empty_sequence<D>(p, b, lane);
+  }
+  if (n <= 0) return;  // (any pdl_wait this grid owes has been executed above)
+
+  int32_t ids_next = list.fetch_ids(p, P0, P1, 16, lane);
+  int ids_base = 0;
 
   // swizzled shared-memory offsets of this thread's fragments inside a tile
   uint32_t k_off[2][2], v_off[4];
@@ -632,7 +891,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
   // ---- consumer side: the pieces of the chunk in order
   struct Cursor { int b, np, start; };  // current sequence, its pairs, list index of its first pair
   Cursor cur;
-  cur.b = seq_of(P0);
+  cur.b = list.seq_of(P0);
   cur.np = prefix[cur.b + 1] - prefix[cur.b];
   cur.start = prefix[cur.b];
   const float ks = KV16 ? 1.f : (p.k_scale_ph ? __ldg(p.k_scale_ph + kvh) : p.k_scale);
@@ -651,6 +910,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
 #pragma unroll 1
   while (ok && g < P1) {
     const int e = min(cur.start + cur.np, P1);
+    const int piece_first = g;
     // the next piece's query is requested now and used when this piece is done
     Cursor nxt = cur;
     uint32_t qn[1][8][2];
@@ -668,7 +928,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
 #pragma unroll 1
     for (; g < e; ++g, ++t) {
       const int s = t % NSTAGE;
-      if (!mbar_wait_bounded(my_bars + 8 * s, (t / NSTAGE) & 1)) { ok = false; break; }
+      if (!mbar_wait_bounded(my_bars + 8 * s, (t / NSTAGE) & 1, tp.wait_limit_ns)) { ok = false; break; }
       if (t == 0) mark_phase_at(tp, W, 3, lane == 0);  // first data landed
       if (t == n / 2) mark_phase_at(tp, W, 6, lane == 0);  // half of the chunk consumed
       const int tok0 = (page_first + 2 * (g - cur.start)) * kPage;
@@ -681,7 +941,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
         if ((tn & 15) == 0) {
           ids_cur = ids_next;
           ids_base = tn;
-          ids_next = fetch_ids(tn + 16);
+          ids_next = list.fetch_ids(p, P0, P1, tn + 16, lane);
         }
         if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         fire(tn, ids_cur, ids_base);
@@ -699,7 +959,13 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       x += __shfl_xor_sync(0xffffffffu, x, 16);
       lsum[c] = x;
     }
-    const int which = chunks.first_unit(cur.start, cur.b) > C0 ? 1 : 0;
+    const int s0 = chunks.first_unit(cur.start, cur.b);
+    const int which = s0 > C0 ? 1 : 0;
+#ifdef PFD_BOUNDS_CHECK
+    if (!whole && chunk_slot_row(grp, which, p.num_q_heads, p.num_q_heads - 1) >= p.dbg_ws_rows)
+      mark_value_at(tp, 2 * cp.num_warps + 2, 0, lane == 0, ((unsigned long long)(unsigned)grp << 32) | (unsigned)which);
+    if (cur.b < 0 || cur.b >= B) mark_value_at(tp, 2 * cp.num_warps + 4, 0, lane == 0, (unsigned long long)(unsigned)cur.b);
+#endif
 #pragma unroll
     for (int c = 0; c < 2; ++c) {
       const int row = 2 * j + c;
@@ -757,6 +1023,30 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
         }
       }
     }
+    if (!whole && cp.merge_in_kernel) {
+      // Publish the piece, then count this warp's pairs of the sequence in: the warp that
+      // completes the count finds every other piece in L2 and writes the final rows.
+      __threadfence();
+      __syncwarp();
+      const int mine = e - piece_first;
+      int32_t* counter = cp.plan + plan_counters_off(B, num_groups) + (int64_t)cur.b * hkv + kvh;
+#ifdef PFD_BOUNDS_CHECK
+      if (cur.b < 0 || cur.b >= B || mine <= 0 || mine > cur.np) {
+        mark_value_at(tp, 2 * cp.num_warps + 3, 0, lane == 0, ((unsigned long long)(unsigned)cur.b << 32) | (unsigned)mine);
+        mark_value_at(tp, 2 * cp.num_warps + 3, 1, lane == 0, ((unsigned long long)(unsigned)cur.np << 32) | (unsigned)W);
+      }
+#endif
+      int before = 0;
+      if (lane == 0) before = atomicAdd(counter, mine);
+      before = __shfl_sync(0xffffffffu, before, 0);
+      if (before + mine == cur.np) {
+        __threadfence();
+        mark_phase_at(tp, cp.num_warps + W, 0, lane == 0);  // merge begins
+        merge_pieces_of_sequence<QBF16>(p, chunks, cur.b, kvh, cur.np, s0, lane, tp, 2 * cp.num_warps);
+        if (lane == 0) *counter = 0;  // ready for the next launch that uses this plan
+        mark_phase_at(tp, cp.num_warps + W, 1, lane == 0);  // merged
+      }
+    }
     cur = nxt;
 #pragma unroll
     for (int f = 0; f < 8; ++f) { qb[0][f][0] = qn[0][f][0]; qb[0][f][1] = qn[0][f][1]; }
@@ -767,7 +1057,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
     // a copy never landed: record it; give the copies still in flight a bounded chance to land
     atomicExch(tp.status, kErrTmaTimeout);
     const int issued = min(n, t + NSTAGE);
-    for (int u = t + 1; u < issued; ++u) mbar_wait_bounded(my_bars + 8 * (u % NSTAGE), (u / NSTAGE) & 1);
+    for (int u = t + 1; u < issued; ++u) mbar_wait_bounded(my_bars + 8 * (u % NSTAGE), (u / NSTAGE) & 1, tp.wait_limit_ns);
   }
 }
 

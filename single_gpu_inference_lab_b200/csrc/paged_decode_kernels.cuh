@@ -58,6 +58,10 @@ struct KernelParams {
   int32_t slot_offset; // workspace slots [0, slot_offset) are filled by another kernel (dense prefix pass)
   int32_t early_metadata;  // 1: seq_lens and block_table may be read before the preceding kernel has completed
   int32_t kv_evict_first;  // 1: K/V tiles are loaded with the L2 evict-first hint
+#ifdef PFD_BOUNDS_CHECK
+  int64_t dbg_ws_rows;     // self-checking builds: rows of the workspace, sequences of the batch
+  int32_t dbg_batch;
+#endif
 };
 
 // Programmatic dependent launch: the split-KV partial kernel lets its dependent (the merge
@@ -534,12 +538,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after kSpinLimit polls (each poll itself suspends for a while in
-// hardware) so that a copy that never lands cannot hang the GPU; the caller records an error.
-constexpr uint32_t kSpinLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
-    if (mbar_try_wait(bar, parity)) return true;
+// Bounded wait: gives up when `limit_ns` nanoseconds (by %globaltimer) have passed, or after
+// kSpinLimit rounds of polls whatever the clock says, so that a copy that never lands cannot
+// hang the GPU; the caller records an error and carries on.
+constexpr uint32_t kSpinLimit = 1u << 24;
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, unsigned long long limit_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t round = 0; round < kSpinLimit; ++round) {
+#pragma unroll 1
+    for (int k = 0; k < 8; ++k)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > limit_ns) return false;
   }
   return false;
 }
@@ -596,9 +611,14 @@ __device__ __forceinline__ uint4 lds_16(uint32_t addr) {
   return v;
 }
 
+// Self-test of the bounded wait: one warp arms a barrier for bytes that no copy will ever
+// deliver and waits; the wait must give up after limit_ns and set the error word.
+__global__ void bounded_wait_selftest_kernel(int32_t* status, unsigned long long limit_ns, unsigned long long* waited_ns);
+
 struct TmaParams {
   int32_t head_is_dim1;  // 1: tensor-map dims are (D, head, token, page); 0: (D, token, head, page)
   int32_t* status;       // device error word (0 = ok)
+  unsigned long long wait_limit_ns;  // after this long a wait for a copy gives up and sets the error word
   unsigned long long* phase_times;  // [slots][8] nanosecond stamps; read only in builds with PFD_PHASE_STAMPS
 };
 
@@ -629,6 +649,23 @@ __device__ __forceinline__ unsigned sm_id() {
 }
 
 constexpr int kErrTmaTimeout = 1;
+
+__global__ void bounded_wait_selftest_kernel(int32_t* status, unsigned long long limit_ns, unsigned long long* waited_ns) {
+  __shared__ __align__(8) unsigned long long bar_storage;
+  const uint32_t bar = smem_u32(&bar_storage);
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_expect_tx(bar, 16);  // the arrival is in, the 16 bytes never come
+  }
+  __syncwarp();
+  const unsigned long long t0 = global_timer_ns();
+  const bool ok = mbar_wait_bounded(bar, 0, limit_ns);
+  if (threadIdx.x == 0) {
+    if (!ok) atomicExch(status, kErrTmaTimeout);
+    if (waited_ns != nullptr) *waited_ns = global_timer_ns() - t0;
+  }
+}
 
 // Split-KV partial kernel for head_dim 128, K/V tiles staged by TMA.
 //
@@ -698,6 +735,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
 #pragma unroll
     for (int s = 0; s < NSTAGE; ++s) mbar_init(my_bars + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copies' completions see initialised barriers
   }
   __syncwarp();
 
@@ -767,7 +805,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   for (; t < n_pairs; ++t) {
     const int s = t % NSTAGE;
     const uint32_t parity = (t / NSTAGE) & 1;
-    if (!mbar_wait_bounded(my_bars + 8 * s, parity)) { ok = false; break; }
+    if (!mbar_wait_bounded(my_bars + 8 * s, parity, tp.wait_limit_ns)) { ok = false; break; }
     const uint32_t stage = my_ring + s * kStageBytes;
     const int tok0 = my_page(t, 0) * kPage;
     // the second page of the last pair may not exist: its (stale) bytes are masked like any
@@ -822,7 +860,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
     if (lane == 0) {
       atomicExch(tp.status, kErrTmaTimeout);
       const int issued = min(n_pairs, t + NSTAGE);
-      for (int u = t + 1; u < issued; ++u) mbar_wait_bounded(my_bars + 8 * (u % NSTAGE), (u / NSTAGE) & 1);
+      for (int u = t + 1; u < issued; ++u) mbar_wait_bounded(my_bars + 8 * (u % NSTAGE), (u / NSTAGE) & 1, tp.wait_limit_ns);
     }
     __syncwarp();
   }

@@ -148,6 +148,7 @@ struct PrefixParams {
   int32_t prefix_len;   // tokens shared by every request (multiple of 16)
   int32_t batch;
   int32_t* status;
+  unsigned long long wait_limit_ns;  // after this long a wait for the tensor cores gives up and sets the error word
   unsigned long long* phase_times;  // [grid][8] nanosecond stamps; read only in builds with PFD_PHASE_STAMPS
 };
 
@@ -279,7 +280,7 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
                  umma_desc_k_sw128(sk + kb * (kPrefixChunk * 128) + 32 * s), idesc, (kb | s) ? 1u : 0u);
     umma_commit(bars);
   }
-  bool ok = mbar_wait_bounded(bars, 0);
+  bool ok = mbar_wait_bounded(bars, 0, pp.wait_limit_ns);
   tc_fence_after_sync();
   prefix_mark(pp, 2);  // S ready
 
@@ -339,7 +340,7 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
                umma_desc_mn_sw128(sv + 2048 * s, kPrefixChunk * 128), idesc, s ? 1u : 0u);
     umma_commit(bars + 8);
   }
-  ok = mbar_wait_bounded(bars + 8, 0) && ok;
+  ok = mbar_wait_bounded(bars + 8, 0, pp.wait_limit_ns) && ok;
   tc_fence_after_sync();
   prefix_mark(pp, 4);  // O ready
 

@@ -61,6 +61,30 @@ def paged_decode_split_out(
     )
 
 
+def paged_decode_split_out_v2(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    partial_output: torch.Tensor,
+    partial_max: torch.Tensor,
+    partial_sum: torch.Tensor,
+    output: torch.Tensor,
+    max_seq_len: int,
+    split_size: int,
+    *,
+    flags: int = 0,
+    plan: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """The non-quantised sibling with ``FLAG_*`` bits and an optional ``plan`` (see ``plan_decode``)."""
+    torch.ops.l20_stack.paged_decode_split_out_v2(
+        query, key_cache, value_cache, block_table, seq_lens,
+        partial_output, partial_max, partial_sum, output, max_seq_len, split_size, flags, plan,
+    )
+    return output
+
+
 def paged_decode_split_indices_out(
     query: torch.Tensor,
     key_cache: torch.Tensor,
@@ -137,13 +161,13 @@ def paged_decode_fp8_e4m3_split_out_v2(
     sm_scale: float = 0.0,
     kv_start: int = 0,
     flags: int = 0,
-    semaphores: Optional[torch.Tensor] = None,
+    plan: Optional[torch.Tensor] = None,
 ) -> Optional[torch.Tensor]:
     """Superset op: ``[Hkv]`` scale tensors (per layer and kv head), explicit softmax scale
     (0 = ``D**-0.5``), first attended token ``kv_start`` and, instead of or besides
     ``output``, a packed fp32 ``[B, Hq, D + 2]`` ``(o, m, l)`` for cross-GPU merging.
-    ``flags`` are the ``FLAG_*`` bits above.  ``semaphores`` is accepted and ignored (earlier
-    builds counted retired pieces there)."""
+    ``flags`` are the ``FLAG_*`` bits above.  ``plan`` is the buffer ``plan_decode`` filled for the
+    same lengths, block table and workspace: with it the step is a single kernel launch."""
     torch.ops.l20_stack.paged_decode_fp8_e4m3_split_out_v2(
         query,
         key_cache,
@@ -162,9 +186,39 @@ def paged_decode_fp8_e4m3_split_out_v2(
         split_size,
         kv_start,
         flags,
-        semaphores,
+        plan,
     )
     return output
+
+
+def plan_decode(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    partial_output: torch.Tensor,
+    partial_max: torch.Tensor,
+    partial_sum: torch.Tensor,
+    max_seq_len: int,
+    split_size: int,
+    *,
+    kv_start: int = 0,
+    plan: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Work split of a model step's decode-attention calls (``pfd_plan_decode``): one small
+    kernel over the lengths and the block table, whose result every layer's call of the step
+    reuses (``plan=``).  The caches and the workspace are passed for their geometry only; FP8
+    caches plan for ``paged_decode_fp8_e4m3_split_out_v2``, caches in the query's type for the
+    non-quantised sibling.  Raises when the call would not run the balanced kernel."""
+    if plan is None:
+        words = torch.ops.l20_stack.plan_bytes(query.shape[0], key_cache.shape[2]) // 4
+        plan = torch.empty(words, dtype=torch.int32, device=query.device)
+    torch.ops.l20_stack.plan_decode(
+        query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max, partial_sum, plan,
+        max_seq_len, split_size, kv_start,
+    )
+    return plan
 
 
 def shared_prefix_decode_fp8_e4m3(
@@ -240,6 +294,14 @@ def _register_fake() -> None:
 
     @torch.library.register_fake("l20_stack::paged_decode_fp8_e4m3_split_out_v2")
     def _paged_decode_fp8_e4m3_split_out_v2_fake(*args):
+        return None
+
+    @torch.library.register_fake("l20_stack::paged_decode_split_out_v2")
+    def _paged_decode_split_out_v2_fake(*args):
+        return None
+
+    @torch.library.register_fake("l20_stack::plan_decode")
+    def _plan_decode_fake(*args):
         return None
 
     @torch.library.register_fake("l20_stack::shared_prefix_decode_fp8_e4m3")

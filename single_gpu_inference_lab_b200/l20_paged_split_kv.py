@@ -159,11 +159,14 @@ def l20_paged_split_kv_attention_fp8(
     output: torch.Tensor | None = None,
     workspace: tuple[torch.Tensor, ...] | None = None,
     metadata_stable: bool = False,
+    plan: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """``metadata_stable=True`` (not in the reference) tells the operator that the kernel
-    running before it on the stream does not write ``block_table`` or ``seq_lens`` -- true for
-    every layer of a model step, whose metadata is built once -- so that it may read them while
-    that kernel drains (``PFD_FLAG_EARLY_METADATA``)."""
+    running before it on the stream does not write ``block_table``, ``seq_lens`` or ``plan`` --
+    true for every layer of a model step, whose metadata is built once -- so that it may read
+    them while that kernel drains (``PFD_FLAG_EARLY_METADATA``).  ``plan`` (not in the reference
+    either) is the result of ``plan_l20_paged_split_kv`` for the same step: with it the call is
+    one kernel launch."""
     if not _on_required_gpu(query):
         raise RuntimeError("requires an SM100 GPU")
     if query.ndim != 3 or key_cache.ndim != 4 or value_cache.shape != key_cache.shape:
@@ -201,7 +204,7 @@ def l20_paged_split_kv_attention_fp8(
     ):
         raise RuntimeError("paged split-KV workspace shape does not match the request")
     ops = _ops()
-    if isinstance(k_scale, torch.Tensor) or isinstance(v_scale, torch.Tensor) or metadata_stable:
+    if isinstance(k_scale, torch.Tensor) or isinstance(v_scale, torch.Tensor) or metadata_stable or plan is not None:
         def as_vec(s):
             if isinstance(s, torch.Tensor):
                 if s.dtype == torch.float32 and s.device == query.device and s.shape == (num_kv_heads,) and s.is_contiguous():
@@ -213,7 +216,7 @@ def l20_paged_split_kv_attention_fp8(
             query, key_cache, value_cache, block_table, seq_lens,
             partial_output, partial_max, partial_sum, output,
             as_vec(k_scale), as_vec(v_scale), max_seq_len, split_size,
-            flags=ops.FLAG_EARLY_METADATA if metadata_stable else 0,
+            flags=ops.FLAG_EARLY_METADATA if metadata_stable else 0, plan=plan,
         )
         return output
     return ops.paged_decode_fp8_e4m3_split_out(
@@ -234,9 +237,11 @@ def l20_paged_split_kv_attention(
     workspace: tuple[torch.Tensor, ...] | None = None,
     max_seq_len: int | None = None,
     output: torch.Tensor | None = None,
+    metadata_stable: bool = False,
+    plan: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """The non-quantised sibling (reference :491-594): K/V caches in the query's fp16 / bf16
-    type.  ``page_granular`` / ``grouped_gqa`` of the reference select between its Triton kernel
+    type.  ``metadata_stable`` / ``plan`` as for the FP8 wrapper.  ``page_granular`` / ``grouped_gqa`` of the reference select between its Triton kernel
     variants and have no counterpart here.  ``max_seq_len`` (not in the reference, which always
     reads it back from the device, :517) avoids that host synchronisation."""
     if not _on_required_gpu(query):
@@ -273,9 +278,43 @@ def l20_paged_split_kv_attention(
         or output.shape != query.shape
     ):
         raise RuntimeError("paged split-KV workspace shape does not match the request")
-    return _ops().paged_decode_split_out(
+    ops = _ops()
+    if metadata_stable or plan is not None:
+        return ops.paged_decode_split_out_v2(
+            query, key_cache, value_cache, block_table, seq_lens,
+            partial_output, partial_max, partial_sum, output, max_seq_len, split_size,
+            flags=ops.FLAG_EARLY_METADATA if metadata_stable else 0, plan=plan,
+        )
+    return ops.paged_decode_split_out(
         query, key_cache, value_cache, block_table, seq_lens,
         partial_output, partial_max, partial_sum, output, max_seq_len, split_size,
+    )
+
+
+def plan_l20_paged_split_kv(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    *,
+    max_seq_len: int,
+    split_size: int = 512,
+    workspace: tuple[torch.Tensor, ...],
+    plan: torch.Tensor | None = None,
+) -> torch.Tensor | None:
+    """Once per model step (not in the reference, whose kernels need no work split): the plan the
+    decode calls of all layers of the step share -- pass it as ``plan=`` to
+    ``l20_paged_split_kv_attention_fp8`` / ``l20_paged_split_kv_attention``.  One small kernel
+    over the lengths and the block table; ``plan`` reuses a buffer.  Returns ``None`` for
+    geometries the balanced kernel does not take (their calls need no plan)."""
+    _, num_q_heads, head_dim = query.shape
+    num_kv_heads = key_cache.shape[2]
+    if head_dim != 128 or num_q_heads // num_kv_heads > BALANCED_MAX_GROUP or workspace[0].dtype != torch.float32:
+        return None
+    return _ops().plan_decode(
+        query, key_cache, value_cache, block_table, seq_lens, workspace[0], workspace[1], workspace[2],
+        max_seq_len, split_size, plan=plan,
     )
 
 

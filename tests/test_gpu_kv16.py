@@ -13,6 +13,7 @@ pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
 PATH_KV16 = 4
+PATH_KV16_PLANNED = 6
 
 
 @pytest.fixture(scope="module")
@@ -33,21 +34,27 @@ def workspace(q, splits, dtype=torch.float32):
     )
 
 
-def run(cabi, w, *, splits=None, partial_dtype=torch.float32, kv_start=0, packed=False, flags=0):
+def run(cabi, w, *, splits=None, partial_dtype=torch.float32, kv_start=0, packed=False, flags=0, planned=False):
+    """planned: pfd_plan_decode first, then the call with that plan (one launch, merge inside)."""
     q = w.query
     hkv = w.key_cache.shape[2]
     if splits is None:  # room for every warp group
         splits = max(1, -(-cabi.balanced_workspace_rows(q.shape[1], hkv) // (q.shape[0] * q.shape[1])))
     out = torch.full_like(q, float("nan"))
     pk = torch.full((q.shape[0], q.shape[1], q.shape[2] + 2), float("nan"), device=q.device) if packed else None
+    ws = workspace(q, splits, partial_dtype)
+    plan = None
+    if planned:
+        plan = cabi.plan_decode(q, w.key_cache, w.value_cache, w.block_table, w.seq_lens, max_seq_len=w.max_seq_len,
+                                split_size=512, workspace=ws, kv_start=kv_start)
     cabi.paged_decode_kv16_split_out(
         q, w.key_cache, w.value_cache, w.block_table, w.seq_lens, max_seq_len=w.max_seq_len, split_size=512,
-        output=None if packed else out, packed_output=pk, workspace=workspace(q, splits, partial_dtype),
-        kv_start=kv_start, flags=flags,
+        output=None if packed else out, packed_output=pk, workspace=ws,
+        kv_start=kv_start, flags=flags, plan=plan,
     )
     torch.cuda.synchronize()
     assert cabi.device_status() == 0, "a bounded device-side wait gave up"
-    assert cabi.last_path() == PATH_KV16
+    assert cabi.last_path() == (PATH_KV16_PLANNED if planned and partial_dtype == torch.float32 else PATH_KV16)
     return pk if packed else out
 
 
@@ -64,14 +71,18 @@ def test_against_committed_reference_outputs(cabi, golden, name):
     w = make_inputs(case["workload"], seed=0, device="cpu", batch=case["batch"], shrink=case["shrink"],
                     query_dtype=dtype, kv_dtype=dtype)
     for splits in (None, 1, 3):  # full capacity; the smallest legal workspaces (few warp groups)
-        assert_within_gate(run(cabi, w.to(DEV), splits=splits), case["output"], f"{name} splits={splits}")
+        for planned in (False, True):
+            assert_within_gate(run(cabi, w.to(DEV), splits=splits, planned=planned), case["output"],
+                               f"{name} splits={splits} planned={planned}")
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_config2_and_config3_full_size(cabi, dtype):
     for name in ("qwen2.5-coder-3b-b64", "qwen2.5-7b-b256"):
         w = make_inputs(name, seed=0, query_dtype=dtype, kv_dtype=dtype)
-        assert_within_gate(run(cabi, w.to(DEV)), expected(w), f"{name} {dtype}")
+        exp = expected(w)
+        assert_within_gate(run(cabi, w.to(DEV)), exp, f"{name} {dtype}")
+        assert_within_gate(run(cabi, w.to(DEV), planned=True, flags=32), exp, f"{name} {dtype} planned")
 
 
 @pytest.mark.parametrize("hq,hkv", [(16, 2), (28, 4), (32, 8), (8, 8), (12, 2)])
@@ -110,12 +121,16 @@ def test_hnd_layout_partial_dtypes_kv_start_and_packed_output(cabi):
     g.value_cache = g.value_cache.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
     assert not g.key_cache.is_contiguous()
     assert_within_gate(run(cabi, g), exp, "hnd")
+    assert_within_gate(run(cabi, g, planned=True), exp, "hnd planned")
     for pdtype in (torch.float16, torch.bfloat16):  # the reference keeps partials in the query dtype
-        out = run(cabi, g, partial_dtype=pdtype)
-        assert torch.allclose(out.float().cpu(), exp.float(), atol=2e-2, rtol=2e-2)
+        for planned in (False, True):  # a plan is ignored for 16-bit partials
+            out = run(cabi, g, partial_dtype=pdtype, planned=planned)
+            assert torch.allclose(out.float().cpu(), exp.float(), atol=2e-2, rtol=2e-2)
     # suffix only, as packed (o, m, l)
     cut = 100
+    pk2 = run(cabi, g, kv_start=cut, packed=True, planned=True)
     pk = run(cabi, g, kv_start=cut, packed=True)
+    assert torch.allclose((pk2[..., :-2] / pk2[..., -1:]).nan_to_num(), (pk[..., :-2] / pk[..., -1:]).nan_to_num(), atol=1e-5, rtol=1e-4)
     sub = oracle.reference_kv16(w.query, w.key_cache, w.value_cache, w.block_table.long(), w.seq_lens, kv_start=cut)
     has = (w.seq_lens > cut).nonzero().flatten().tolist()
     got = (pk[..., :-2] / pk[..., -1:]).cpu()
@@ -127,7 +142,7 @@ def test_dispatcher_op_with_the_reference_smoke_call(built_libs):
     fp16 partial workspace with ceil(context / 64) splits."""
     from single_gpu_inference_lab_b200 import l20_paged_decode, l20_paged_split_kv  # noqa: F401
 
-    for batch, context in ((1, 129), (3, 1000)):
+    for batch, context in ((1, 129), (3, 1000), (1, 50)):  # the last: one request, one split, 12 workspace rows
         torch.manual_seed(17)
         pages_per = (context + 15) // 16
         pages = batch * pages_per

@@ -71,7 +71,7 @@ def expected(q, kc, vc, table, lens, ks, vs, kv_start=0):
 @pytest.mark.parametrize("kv16", [False, True])
 def test_random_cases(cabi, kv16):
     rng = random.Random(2024 + kv16)
-    for case in range(40):
+    for case in range(100):
         q, kc, vc, table, lens, ks, vs = random_case(rng, kv16)
         hkv = kc.shape[2]
         kv_start = rng.choice([0, 0, 0, 5, 16, 37]) if int(lens.max()) > 40 else 0
@@ -90,21 +90,30 @@ def test_random_cases(cabi, kv16):
         )
         out = torch.full_like(g[0], float("nan"))
         flags = rng.choice([0, 32])  # with and without early metadata reads
-        what = f"case {case}: kv16={kv16} B={q.shape[0]} Hq={q.shape[1]} Hkv={hkv} max={int(lens.max())} kv_start={kv_start} flags={flags}"
+        planned = rng.random() < 0.6  # one launch with a plan, or chunk kernel + merge kernel
+        what = (f"case {case}: kv16={kv16} B={q.shape[0]} Hq={q.shape[1]} Hkv={hkv} max={int(lens.max())} "
+                f"kv_start={kv_start} flags={flags} planned={planned}")
+        plan = None
+        if planned:
+            plan = cabi.plan_decode(*g, max_seq_len=int(lens.max()), split_size=512, workspace=ws, kv_start=kv_start)
+            if flags:  # the plan kernel must not be the kernel right in front of an early-metadata call
+                torch.cuda.synchronize()
         if kv16:
             cabi.paged_decode_kv16_split_out(*g, max_seq_len=int(lens.max()), split_size=512, output=out, workspace=ws,
-                                             kv_start=kv_start, flags=flags)
+                                             kv_start=kv_start, flags=flags, plan=plan)
         else:
             cabi.paged_decode_fp8_e4m3_split_out(*g, k_scale=ks.to(DEV), v_scale=vs.to(DEV), max_seq_len=int(lens.max()),
-                                                 split_size=512, output=out, workspace=ws, kv_start=kv_start, flags=flags)
+                                                 split_size=512, output=out, workspace=ws, kv_start=kv_start, flags=flags,
+                                                 plan=plan)
         torch.cuda.synchronize()
         assert cabi.device_status() == 0, what
-        assert cabi.last_path() in (3, 4), what
+        assert cabi.last_path() == ((6 if kv16 else 5) if planned else (4 if kv16 else 3)), what
         assert_within_gate(out, exp, what)
 
 
+@pytest.mark.parametrize("planned", [False, True])
 @pytest.mark.parametrize("kv16", [False, True])
-def test_graph_replay_with_metadata_rewritten_in_place(built_libs, kv16):
+def test_graph_replay_with_metadata_rewritten_in_place(built_libs, kv16, planned):
     from single_gpu_inference_lab_b200 import l20_paged_split_kv as m
 
     torch.manual_seed(5)
@@ -127,12 +136,25 @@ def test_graph_replay_with_metadata_rewritten_in_place(built_libs, kv16):
     gks, gvs = (None, None) if kv16 else (ks.to(DEV), vs.to(DEV))
     ws = m.allocate_l20_paged_split_kv_workspace(q, max_len, split_size=512, num_kv_heads=hkv)
 
+    plan_buf = m.plan_l20_paged_split_kv(q, gk, gv, table, lens, max_seq_len=max_len, split_size=512, workspace=ws) if planned else None
+    filler = torch.zeros(1 << 16, device=DEV)
+
     def call():
-        if kv16:
-            m.l20_paged_split_kv_attention(q, gk, gv, table, lens, split_size=512, workspace=ws, max_seq_len=max_len)
-        else:
-            m.l20_paged_split_kv_attention_fp8(q, gk, gv, table, lens, k_scale=gks, v_scale=gvs,
-                                               max_seq_len=max_len, split_size=512, workspace=ws, metadata_stable=True)
+        # what an engine records per step: the plan from the step's metadata, other work, then
+        # the layers' attention calls (two of them here) that share the plan
+        plan = None
+        if planned:
+            plan = m.plan_l20_paged_split_kv(q, gk, gv, table, lens, max_seq_len=max_len, split_size=512, workspace=ws,
+                                             plan=plan_buf)
+            filler.add_(1.0)
+        for _ in range(2):
+            if kv16:
+                m.l20_paged_split_kv_attention(q, gk, gv, table, lens, split_size=512, workspace=ws, max_seq_len=max_len,
+                                               metadata_stable=True, plan=plan)
+            else:
+                m.l20_paged_split_kv_attention_fp8(q, gk, gv, table, lens, k_scale=gks, v_scale=gvs,
+                                                   max_seq_len=max_len, split_size=512, workspace=ws, metadata_stable=True,
+                                                   plan=plan)
 
     call()  # lazy initialisation outside the capture
     torch.cuda.synchronize()
@@ -140,8 +162,8 @@ def test_graph_replay_with_metadata_rewritten_in_place(built_libs, kv16):
     with torch.cuda.graph(graph):
         call()
     gen = torch.Generator().manual_seed(9)
-    for step in range(6):
-        new_lens = torch.randint(0 if step == 3 else 1, max_len + 1, (batch,), generator=gen).to(torch.int32)
+    for step in range(40):
+        new_lens = torch.randint(0 if step % 4 == 3 else 1, max_len + 1, (batch,), generator=gen).to(torch.int32)
         if step == 5:
             new_lens[:] = max_len
         new_table = torch.randperm(total, generator=gen).to(torch.int32).reshape(batch, pages_per)

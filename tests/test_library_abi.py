@@ -40,7 +40,7 @@ def test_ctypes_struct_matches_header_size(built_libs, tmp_path):
     subprocess.run(["gcc", f"-I{ROOT / 'include'}", str(src), "-o", str(exe)], check=True)
     size = int(subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout)
     assert size == ctypes.sizeof(cabi.DecodeArgs)
-    assert cabi.load().pfd_abi_version() == 3
+    assert cabi.load().pfd_abi_version() == 4
 
 
 def test_argument_errors_are_reported_without_a_gpu(built_libs):
