@@ -78,6 +78,8 @@ def parse_args():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-shared-prefix", action="store_true",
                    help="shared-prefix-b64 only: use the ordinary decode path instead of the dense tcgen05 prefix pass")
+    p.add_argument("--single-launch", action="store_true",
+                   help="with the plan: combine the pieces of cut sequences inside the balanced kernel (PFD_FLAG_SINGLE_LAUNCH)")
     p.add_argument("--no-plan", action="store_true",
                    help="do not plan the step: every call derives its work split itself and a merge kernel follows")
     p.add_argument("--strong", action="store_true",
@@ -289,6 +291,8 @@ def main() -> int:
         plan = cabi.plan_decode(q, w.key_cache, w.value_cache, w.block_table, w.seq_lens, max_seq_len=w.max_seq_len,
                                 split_size=split, workspace=ws)
         torch.cuda.synchronize()
+        if args.single_launch:
+            args.flags |= cabi.PFD_FLAG_SINGLE_LAUNCH
     packed = torch.empty(batch, hq, d + 2, device=dev) if kv_range_mode else None
     gathered = torch.empty(world, batch, hq, d + 2, device=dev) if kv_range_mode else None
 

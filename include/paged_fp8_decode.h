@@ -42,11 +42,15 @@ extern "C" {
                                      built once; not true for a call enqueued right behind
                                      pfd_plan_decode): the kernels may then read them while that
                                      kernel drains                                               */
+#define PFD_FLAG_SINGLE_LAUNCH 64u /* with `plan`: the balanced kernel also combines the pieces of cut
+                                     sequences (the warp whose piece arrives last does it), so the
+                                     step is one launch and no merge kernel follows; measured slower
+                                     on B200 than the two launches, for callers that want one node  */
 /*
  * Kernel selection.  For head_dim 128, at most 8 query heads per kv head, a TMA-describable
  * cache and a dense f32 workspace of at least pfd_balanced_workspace_rows() rows the balanced
- * persistent kernel runs (split_size then only sizes the workspace): with `plan` set it is the
- * only launch of the step, without it a merge kernel follows.  Anything else, or
+ * persistent kernel + its merge kernel run (split_size then only sizes the workspace); with `plan`
+ * set both read their work split instead of deriving it.  Anything else, or
  * PFD_FLAG_FIXED_SPLITS, runs the fixed-split grid + merge kernel.
  */
 
@@ -129,8 +133,8 @@ typedef struct pfd_decode_args {
   const int32_t* page_indptr;
 
   /* Optional device buffer written by pfd_plan_decode() for the same batch, lengths, block table,
-   * kv_start, head counts and workspace: the balanced persistent kernel then reads its work split
-   * from it and combines the pieces of cut sequences itself (one launch per step).  NULL, or a
+   * kv_start, head counts and workspace: the balanced persistent kernel and its merge kernel then
+   * read their work split from it (and PFD_FLAG_SINGLE_LAUNCH becomes available).  NULL, or a
    * call that does not run the balanced kernel: ignored. */
   void* plan;
 } pfd_decode_args;
@@ -275,8 +279,8 @@ int pfd_selftest_bounded_wait(uint64_t limit_ns, uint64_t* waited_ns, void* stre
 #define PFD_PATH_FIXED_TMA 2 /* fixed-split grid, TMA pipeline, + merge kernel         */
 #define PFD_PATH_BALANCED 3  /* balanced persistent kernel + its merge kernel            */
 #define PFD_PATH_BALANCED_KV16 4 /* the same for 16-bit caches (pfd_paged_decode_kv16_split_out) */
-#define PFD_PATH_PLANNED 5       /* balanced persistent kernel with a plan: one launch        */
-#define PFD_PATH_PLANNED_KV16 6  /* the same for 16-bit caches                                 */
+#define PFD_PATH_FUSED 5       /* balanced persistent kernel alone (PFD_FLAG_SINGLE_LAUNCH)   */
+#define PFD_PATH_FUSED_KV16 6  /* the same for 16-bit caches                                  */
 int pfd_last_path(void);
 
 /*

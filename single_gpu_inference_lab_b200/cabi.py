@@ -20,6 +20,7 @@ PFD_FLAG_NO_DIRECT_OUT = 2
 PFD_FLAG_PARTIAL_ONLY = 4
 PFD_FLAG_FIXED_SPLITS = 8
 PFD_FLAG_EARLY_METADATA = 32
+PFD_FLAG_SINGLE_LAUNCH = 64
 
 EXPORTS = (
     "pfd_paged_decode_fp8_e4m3_split_out",
@@ -316,8 +317,8 @@ def selftest_bounded_wait(limit_ns: int) -> int:
 
 PATH_NAMES = {0: "none", 1: "fixed-split grid (plain loads) + merge", 2: "fixed-split grid (TMA) + merge",
               3: "balanced persistent kernel + merge", 4: "balanced persistent kernel (16-bit caches) + merge",
-              5: "balanced persistent kernel with a plan (one launch)",
-              6: "balanced persistent kernel with a plan (16-bit caches, one launch)"}
+              5: "balanced persistent kernel alone (pieces combined inside, one launch)",
+              6: "balanced persistent kernel alone (16-bit caches, one launch)"}
 
 
 def balanced_workspace_rows(num_q_heads: int, num_kv_heads: int) -> int:

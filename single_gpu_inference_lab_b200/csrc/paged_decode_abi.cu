@@ -269,7 +269,11 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
   if (int rc = status_pointer(&tp.status)) return rc;
   tp.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   tp.phase_times = g_phase_times;
-  auto kernel = pfd::paged_decode_fp8_chunk_kernel<QBF16, kStagesT, kWarpsT, KV16>;
+  // A plan needs f32 pieces (its in-kernel merge reads them as such; the merge kernel takes either).
+  const bool planned = a.plan != nullptr && a.partial_dtype == PFD_DTYPE_F32;
+  const bool fused = planned && (a.flags & PFD_FLAG_SINGLE_LAUNCH) && !(a.flags & PFD_FLAG_PARTIAL_ONLY);
+  auto kernel = fused ? pfd::paged_decode_fp8_chunk_kernel<QBF16, kStagesT, kWarpsT, KV16, true>
+                      : pfd::paged_decode_fp8_chunk_kernel<QBF16, kStagesT, kWarpsT, KV16, false>;
   constexpr int kThreads = kWarpsT * 32;
   // ring + mbarriers + scan scratch + prefix[B + 1] + lens[B], sized for the largest batch
   constexpr int smem = 1024 + kWarpsT * kStagesT * 8192 * kElem + kWarpsT * kStagesT * 8 +
@@ -279,21 +283,17 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
   static bool configured[kMaxDevices][2] = {};  // one array per instantiation of this template
   {
     std::lock_guard<std::mutex> lock(g_state_mutex);
-    if (!configured[dev][QBF16 ? 1 : 0]) {
+    if (!configured[dev][fused ? 1 : 0]) {
       const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
       if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
-      configured[dev][QBF16 ? 1 : 0] = true;
+      configured[dev][fused ? 1 : 0] = true;
     }
   }
   pfd::ChunkParams cp{};
   cp.batch = a.batch;
   cp.num_warps = balanced_num_warps(sms, kWarpsT, a.num_kv_heads, max_groups);
   cp.piece_cost = kChunkPieceCost;
-  // A plan is used when the pieces can be combined in the kernel: f32 pieces, and not a timing
-  // run of the streaming part alone.
-  const bool planned = a.plan != nullptr && a.partial_dtype == PFD_DTYPE_F32;
   cp.plan = planned ? static_cast<int32_t*>(a.plan) : nullptr;
-  cp.merge_in_kernel = planned && !(a.flags & PFD_FLAG_PARTIAL_ONLY) ? 1 : 0;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -309,9 +309,9 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
     if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "balanced decode kernel launch failed: %s", cudaGetErrorString(e));
     if (int rc = check_launch("balanced decode kernel")) return rc;
   }
-  g_last_path = planned ? (KV16 ? PFD_PATH_PLANNED_KV16 : PFD_PATH_PLANNED)
-                        : (KV16 ? PFD_PATH_BALANCED_KV16 : PFD_PATH_BALANCED);
-  if (planned || (a.flags & PFD_FLAG_PARTIAL_ONLY)) return PFD_OK;
+  g_last_path = fused ? (KV16 ? PFD_PATH_FUSED_KV16 : PFD_PATH_FUSED)
+                      : (KV16 ? PFD_PATH_BALANCED_KV16 : PFD_PATH_BALANCED);
+  if (fused || (a.flags & PFD_FLAG_PARTIAL_ONLY)) return PFD_OK;
   {
     // Few rows mean few, long sequences whose pieces are many: four warps then share a row,
     // which also puts more loads in flight per SM.  Either way 64 registers, 8 CTAs per SM.

@@ -32,16 +32,18 @@ struct ChunkParams {
   int32_t batch;
   int32_t num_warps;   // warps of the whole grid; the merge kernel is told the same number
   int32_t piece_cost;  // what starting a sequence costs a warp, in half page pairs
-  int32_t merge_in_kernel;  // 1 (needs a plan): pieces are combined by their last arriver, no merge kernel follows
   int32_t* plan;       // device plan written by plan_decode_kernel, or nullptr
 };
 
-// How the work is cut.  Cost is counted in half page pairs: sequence b owns the cost range that
-// starts at 2 * (pairs before b) + piece_cost * b, first piece_cost units for taking the
-// sequence up (query fetch, state reset, output rows), then two units per page pair.  The cost
-// axis is cut into `groups` contiguous chunks whose lengths differ by at most one unit, and a
-// page pair belongs to the chunk that holds its first unit.  Tiny workloads use fewer groups so
-// that no chunk is shorter than kMinChunkCost units (a chunk inside a sequence is never empty).
+// How the work is cut.  Cost is counted in pages: sequence b owns the cost range that starts at
+// 2 * (pairs before b) + piece_cost * b, first piece_cost units for taking the sequence up
+// (query fetch, state reset, output rows), then one unit per page, two per page pair (the
+// second unit of a last pair that holds a single page stands for nothing).  The cost axis is
+// cut into `groups` contiguous chunks whose lengths differ by at most one unit, and a page
+// belongs to the chunk that holds its unit: a chunk boundary may fall between the two pages of a
+// pair, which then both neighbours step through, each loading and attending its own page only.
+// Tiny workloads use fewer groups so that no chunk is shorter than kMinChunkCost units (a chunk
+// inside a sequence is never empty).
 constexpr int kMinChunkCost = 8;
 struct Chunking {
   int base, rem, groups, piece_cost;
@@ -68,6 +70,11 @@ struct Chunking {
 __device__ __forceinline__ int pairs_of(int len, int kv_start) {
   const int pages = len > kv_start ? (len + kPage - 1) / kPage - kv_start / kPage : 0;
   return (pages + 1) >> 1;
+}
+
+// Pages of such a sequence (its cost units that stand for data).
+__device__ __forceinline__ int pages_of(int len, int kv_start) {
+  return len > kv_start ? (len + kPage - 1) / kPage - kv_start / kPage : 0;
 }
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
@@ -460,7 +467,7 @@ __device__ __forceinline__ int64_t chunk_slot_row(int grp, int which, int num_q_
 //   [0, 16)            header (kPlan* indices below)
 //   [16, 16 + B + 1)   pairs before sequence b
 //   [.., + B)          sequence lengths
-//   groups_off         per group kPlanGroupWords words: P0, P1, 2 reserved, 32 page ids
+//   groups_off         per group kPlanGroupWords words: P0, P1, split flags, 1 reserved, 32 page ids
 //   counters_off       B * Hkv arrival counters (page pairs consumed), zero between launches
 constexpr int kPlanMagic = 0x70666431;
 constexpr int kPlanHeaderWords = 16;
@@ -482,7 +489,7 @@ constexpr int kErrPlanMismatch = 2;
 struct PairList {
   const int32_t* prefix;  // [B + 1]
   const int32_t* lens;    // [B]
-  int B, page_first;
+  int B, page_first, kv_start;
   // Sequence that holds pair g of the list (0 <= g < total): largest b with prefix[b] <= g.
   __device__ __forceinline__ int seq_of(int g) const {
     int lo_b = 0, hi_b = B;
@@ -492,33 +499,61 @@ struct PairList {
     }
     return lo_b;
   }
-  // Pairs whose first cost unit lies before cost position c.
-  __device__ __forceinline__ int pairs_before(const Chunking& chunks, int c) const {
+  // The chunk boundary at cost position c: returns the pairs whose first unit lies before c;
+  // *split is set when the last of them has its second page at c, i.e. the boundary falls inside
+  // that pair (its second page belongs to the chunk that starts at c).
+  __device__ __forceinline__ int boundary(const Chunking& chunks, int c, bool* split) const {
     const int total = prefix[B];
+    *split = false;
     if (c >= 2 * total + chunks.piece_cost * B) return total;
     int lo_b = 0, hi_b = B;  // largest b whose cost range starts at or before c
     while (hi_b - lo_b > 1) {
       const int mid = (lo_b + hi_b) >> 1;
       if (2 * prefix[mid] + chunks.piece_cost * mid <= c) lo_b = mid; else hi_b = mid;
     }
-    const int off = c - chunks.first_unit(prefix[lo_b], lo_b);  // units into the pairs of lo_b
+    const int off = c - chunks.first_unit(prefix[lo_b], lo_b);  // units into the pages of lo_b
+    *split = off > 0 && (off & 1) && off < pages_of(lens[lo_b], kv_start);
     return prefix[lo_b] + min(max((off + 1) >> 1, 0), prefix[lo_b + 1] - prefix[lo_b]);
   }
-  // Page ids of 16 consecutive pairs of the chunk [P0, P1), one page per lane (lane 2t + u holds
-  // page u of pair P0 + base_t + t, -1 if there is none).
-  __device__ __forceinline__ int32_t fetch_ids(const KernelParams& p, int P0, int P1, int base_t, int lane) const {
-    int32_t phys = -1;
-    const int g = P0 + base_t + (lane >> 1);
-    if (g < P1) {
-      const int b = seq_of(g);
-      const int page = page_first + 2 * (g - prefix[b]) + (lane & 1);
-      if (page <= (lens[b] - 1) / kPage)
-        phys = p.page_indptr ? __ldg(p.block_table + __ldg(p.page_indptr + b) + page)
-                             : page_of(p.block_table, p.bt_stride_b, b, page);
-    }
-    return phys;
-  }
 };
+
+// The pairs a chunk steps through, [P0, P1) of the flattened pair list, and whether its first
+// (last) pair is shared with the chunk in front (behind): then only the pair's second (first)
+// page is this chunk's.
+struct ChunkRange {
+  int P0, P1;
+  bool head_split, tail_split;
+};
+__device__ __forceinline__ ChunkRange chunk_range(const PairList& list, const Chunking& chunks, int grp) {
+  ChunkRange r;
+  const int total = list.prefix[list.B];
+  if (grp >= chunks.groups) {
+    r.P0 = r.P1 = total;
+    r.head_split = r.tail_split = false;
+    return r;
+  }
+  const int before = list.boundary(chunks, chunks.start_of(grp), &r.head_split);
+  r.P0 = before - (r.head_split ? 1 : 0);
+  r.P1 = list.boundary(chunks, chunks.start_of(grp + 1), &r.tail_split);
+  return r;
+}
+
+// Page ids of 16 consecutive pairs of a chunk, one page per lane (lane 2t + u holds page u of
+// pair P0 + base_t + t, -1 if there is none or it is the neighbouring chunk's).
+__device__ __forceinline__ int32_t fetch_ids(const PairList& list, const KernelParams& p, const ChunkRange& cr,
+                                             int base_t, int lane) {
+  int32_t phys = -1;
+  const int g = cr.P0 + base_t + (lane >> 1);
+  if (g < cr.P1) {
+    const int b = list.seq_of(g);
+    const int page = list.page_first + 2 * (g - list.prefix[b]) + (lane & 1);
+    const bool theirs = (cr.head_split && g == cr.P0 && !(lane & 1)) || (cr.tail_split && g == cr.P1 - 1 && (lane & 1));
+    if (!theirs && page <= (list.lens[b] - 1) / kPage)
+      phys = p.page_indptr ? __ldg(p.block_table + __ldg(p.page_indptr + b) + page)
+                           : page_of(p.block_table, p.bt_stride_b, b, page);
+  }
+  return phys;
+}
 
 // Pairs per sequence and their exclusive prefix sum into shared memory, by all NT threads of the
 // CTA (every CTA computes the same).  Ends with a CTA-wide barrier.
@@ -608,116 +643,133 @@ __global__ void __launch_bounds__(1024) plan_decode_kernel(const PlanParams pp) 
   kp.block_table = pp.block_table;
   kp.page_indptr = pp.page_indptr;
   kp.bt_stride_b = pp.bt_stride_b;
-  const PairList list{prefix, lens, B, pp.kv_start / kPage};
+  const PairList list{prefix, lens, B, pp.kv_start / kPage, pp.kv_start};
   const Chunking chunks(prefix[B], B, max(pp.max_groups, 1), pp.piece_cost);
   for (int grp = blockIdx.x * (NT / 32) + warp; grp < pp.max_groups; grp += gridDim.x * (NT / 32)) {
-    const int total = prefix[B];
-    const int P0 = grp < chunks.groups ? list.pairs_before(chunks, chunks.start_of(grp)) : total;
-    const int P1 = grp < chunks.groups ? list.pairs_before(chunks, chunks.start_of(grp + 1)) : total;
-    const int32_t id = list.fetch_ids(kp, P0, P1, 0, lane);
+    const ChunkRange cr = chunk_range(list, chunks, grp);
+    const int32_t id = fetch_ids(list, kp, cr, 0, lane);
     int32_t* gw = plan + plan_groups_off(B) + (int64_t)grp * kPlanGroupWords;
-    if (lane == 0) { gw[0] = P0; gw[1] = P1; gw[2] = 0; gw[3] = 0; }
+    if (lane == 0) { gw[0] = cr.P0; gw[1] = cr.P1; gw[2] = (cr.head_split ? 1 : 0) | (cr.tail_split ? 2 : 0); gw[3] = 0; }
     gw[4 + lane] = id;
   }
 }
 
-// (Builds with -DPFD_BOUNDS_CHECK, a debugging aid, verify every workspace row and sequence index
-// first and record a bad one through the stamp buffer instead of using it.)
 // In-kernel LSE merge of the pieces of one (sequence, kv head), run by the warp whose piece
 // arrived last: rows (query head h of the group, piece k) are fetched 32 at a time (one 512-byte
-// row per load instruction, all in flight together) from the workspace, which the pieces'
+// row per load instruction, all 32 in flight together) from the workspace, which the pieces'
 // writers left in L2, and folded head by head with a running maximum.  Same maths as
 // _paged_split_kv_reduce (integrations/vllm/l20_paged_split_kv.py:459-488).
-template <bool QBF16>
-__device__ __forceinline__ void merge_pieces_of_sequence(const KernelParams& p, const Chunking& chunks, int b, int kvh,
-                                                       int np, int s0, int lane, const TmaParams& tp, int dbg) {
-  constexpr int D = 128, RB = 32;
-  const int w_first = chunks.chunk_of(s0);
-  const int ns = chunks.chunk_of(s0 + 2 * (np - 1)) - w_first + 1;
+// Kept out of line on purpose: with registers of its own the 32 loads of a batch stay in
+// flight together; inlined into the streaming loop they were issued one after the other.
+struct MergeJob {
+  const float* po;   // workspace rows (o), maxima, sums
+  const float* pm;
+  const float* pl;
+  void* output;
+  float* packed;
+  int64_t o_stride_b, o_stride_h;
+  int32_t num_q_heads, hq0, group;  // hq0: first query head of the kv head
+  int32_t ns, w_first, which0;      // pieces, chunk of piece 0, slot of piece 0 in its chunk
+  int32_t b;
 #ifdef PFD_BOUNDS_CHECK
-  if (ns < 1 || w_first < 0 || w_first + ns > chunks.groups || b < 0 || b >= p.dbg_batch) {
-    mark_value_at(tp, dbg + 5, 0, lane == 0, ((unsigned long long)(unsigned)ns << 32) | (unsigned)w_first);
-    mark_value_at(tp, dbg + 5, 1, lane == 0, ((unsigned long long)(unsigned)b << 32) | (unsigned)np);
-    mark_value_at(tp, dbg + 5, 2, lane == 0, (unsigned long long)(unsigned)s0);
-    return;
-  }
-#else
-  (void)tp; (void)dbg;
+  int64_t ws_rows;                  // self-checking builds: rows of the workspace
+  unsigned long long* report;
 #endif
-  const int rows = ns * p.group;  // row r = h * ns + k
-  const float* po = reinterpret_cast<const float*>(p.partial_output);
+};
+
+template <bool QBF16, bool PACKED>
+__device__ __noinline__ void merge_pieces_of_sequence(const MergeJob j, const int lane) {
+  constexpr int D = 128, RB = 32;
+  const int ns = j.ns;
+  const int rows = ns * j.group;  // row r = h * ns + k
+  // Piece k of the sequence lies in chunk w_first + k: in that chunk's first slot, except piece 0
+  // when the sequence begins inside its chunk (then it is the chunk's last piece, slot 1).
+  const auto row_of = [&](int h, int k) -> int64_t {
+    return (int64_t)(2 * (j.w_first + k) + (k == 0 ? j.which0 : 0)) * j.num_q_heads + j.hq0 + h;
+  };
+  // (h, k) of the row after (h, k); `on` false keeps it (the row after the last stays the last).
+  // Written with selects, not branches: everything here is the same in all lanes, but the
+  // compiler cannot know, and a branch with its reconvergence per row costs more than the maths.
+  const auto advance = [&](int& h, int& k, bool on) {
+    const int k2 = k + 1;
+    const bool wrap = on & (k2 == ns);
+    k = on ? (wrap ? 0 : k2) : k;
+    h += wrap ? 1 : 0;
+  };
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   float big = -INFINITY, den = 0.f;
+  int h_base = 0, k_base = 0;  // (h, k) of row r0
   for (int r0 = 0; r0 < rows; r0 += RB) {
+    // All loads of a batch are unconditional (rows past the end repeat the last one) so that
+    // they leave back to back: one round trip to L2 per batch.
     float4 xv[RB];
-    float m_mine = -INFINITY, l_mine = 0.f;
+    float m_mine, l_mine;
     {
-      const int r = r0 + lane;
-      if (r < rows) {
-        const int h = r / ns, k = r - h * ns, w = w_first + k;
-        const int64_t row = chunk_slot_row(w, s0 > chunks.start_of(w) ? 1 : 0, p.num_q_heads, kvh * p.group + h);
+      const int r = min(r0 + lane, rows - 1);
+      const int h = r / ns, k = r - h * ns;
+      const int64_t row = row_of(h, k);
 #ifdef PFD_BOUNDS_CHECK
-        if (row < 0 || row >= p.dbg_ws_rows) { mark_value_at(tp, dbg + 1, 0, true, (unsigned long long)row); } else
+      if (row < 0 || row >= j.ws_rows) { if (j.report) *j.report = (unsigned long long)row | (1ull << 63); return; }
 #endif
-        {
-          m_mine = __ldcg(p.partial_max + row);
-          l_mine = __ldcg(p.partial_sum + row);
-        }
+      m_mine = __ldcg(j.pm + row);
+      l_mine = __ldcg(j.pl + row);
+      if (r0 + lane >= rows) { m_mine = -INFINITY; l_mine = 0.f; }  // no such row: weight 0 below
+    }
+    {
+      int h = h_base, k = k_base;
+#pragma unroll
+      for (int u = 0; u < RB; ++u) {
+        xv[u] = __ldcg(reinterpret_cast<const float4*>(j.po + row_of(h, k) * D) + lane);
+        advance(h, k, r0 + u + 1 < rows);
       }
     }
+    // Scheduling fence: an empty statement that takes all 128 loaded values, so that no use of a
+    // row can be moved in front of the load of a later row (which would serialise the loads).
+    static_assert(RB == 32, "the statement below names 32 rows");
+    asm volatile("" : "+f"(xv[0].x), "+f"(xv[0].y), "+f"(xv[0].z), "+f"(xv[0].w), "+f"(xv[1].x), "+f"(xv[1].y), "+f"(xv[1].z), "+f"(xv[1].w), "+f"(xv[2].x), "+f"(xv[2].y), "+f"(xv[2].z), "+f"(xv[2].w), "+f"(xv[3].x), "+f"(xv[3].y), "+f"(xv[3].z), "+f"(xv[3].w), "+f"(xv[4].x), "+f"(xv[4].y), "+f"(xv[4].z), "+f"(xv[4].w), "+f"(xv[5].x), "+f"(xv[5].y), "+f"(xv[5].z), "+f"(xv[5].w), "+f"(xv[6].x), "+f"(xv[6].y), "+f"(xv[6].z), "+f"(xv[6].w), "+f"(xv[7].x), "+f"(xv[7].y), "+f"(xv[7].z), "+f"(xv[7].w), "+f"(xv[8].x), "+f"(xv[8].y), "+f"(xv[8].z), "+f"(xv[8].w), "+f"(xv[9].x), "+f"(xv[9].y), "+f"(xv[9].z), "+f"(xv[9].w), "+f"(xv[10].x), "+f"(xv[10].y), "+f"(xv[10].z), "+f"(xv[10].w), "+f"(xv[11].x), "+f"(xv[11].y), "+f"(xv[11].z), "+f"(xv[11].w), "+f"(xv[12].x), "+f"(xv[12].y), "+f"(xv[12].z), "+f"(xv[12].w), "+f"(xv[13].x), "+f"(xv[13].y), "+f"(xv[13].z), "+f"(xv[13].w), "+f"(xv[14].x), "+f"(xv[14].y), "+f"(xv[14].z), "+f"(xv[14].w), "+f"(xv[15].x), "+f"(xv[15].y), "+f"(xv[15].z), "+f"(xv[15].w), "+f"(xv[16].x), "+f"(xv[16].y), "+f"(xv[16].z), "+f"(xv[16].w), "+f"(xv[17].x), "+f"(xv[17].y), "+f"(xv[17].z), "+f"(xv[17].w), "+f"(xv[18].x), "+f"(xv[18].y), "+f"(xv[18].z), "+f"(xv[18].w), "+f"(xv[19].x), "+f"(xv[19].y), "+f"(xv[19].z), "+f"(xv[19].w), "+f"(xv[20].x), "+f"(xv[20].y), "+f"(xv[20].z), "+f"(xv[20].w), "+f"(xv[21].x), "+f"(xv[21].y), "+f"(xv[21].z), "+f"(xv[21].w), "+f"(xv[22].x), "+f"(xv[22].y), "+f"(xv[22].z), "+f"(xv[22].w), "+f"(xv[23].x), "+f"(xv[23].y), "+f"(xv[23].z), "+f"(xv[23].w), "+f"(xv[24].x), "+f"(xv[24].y), "+f"(xv[24].z), "+f"(xv[24].w), "+f"(xv[25].x), "+f"(xv[25].y), "+f"(xv[25].z), "+f"(xv[25].w), "+f"(xv[26].x), "+f"(xv[26].y), "+f"(xv[26].z), "+f"(xv[26].w), "+f"(xv[27].x), "+f"(xv[27].y), "+f"(xv[27].z), "+f"(xv[27].w), "+f"(xv[28].x), "+f"(xv[28].y), "+f"(xv[28].z), "+f"(xv[28].w), "+f"(xv[29].x), "+f"(xv[29].y), "+f"(xv[29].z), "+f"(xv[29].w), "+f"(xv[30].x), "+f"(xv[30].y), "+f"(xv[30].z), "+f"(xv[30].w), "+f"(xv[31].x), "+f"(xv[31].y), "+f"(xv[31].z), "+f"(xv[31].w));
+    int h = h_base, k = k_base;
 #pragma unroll
     for (int u = 0; u < RB; ++u) {
-      const int r = r0 + u;
-      xv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (r < rows) {
-        const int h = r / ns, k = r - h * ns, w = w_first + k;
-        const int64_t row = chunk_slot_row(w, s0 > chunks.start_of(w) ? 1 : 0, p.num_q_heads, kvh * p.group + h);
-#ifdef PFD_BOUNDS_CHECK
-        if (row < 0 || row >= p.dbg_ws_rows) { mark_value_at(tp, dbg + 1, 1, lane == 0, (unsigned long long)row); } else
-#endif
-        xv[u] = __ldcg(reinterpret_cast<const float4*>(po + row * D) + lane);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < RB; ++u) {
-      const int r = r0 + u;
-      const float mv = __shfl_sync(0xffffffffu, m_mine, u);
+      const bool live = r0 + u < rows;
+      const float mv = __shfl_sync(0xffffffffu, m_mine, u);  // -inf for rows past the end
       const float lv = __shfl_sync(0xffffffffu, l_mine, u);
-      if (r < rows) {  // warp-uniform
-        const int h = r / ns, k = r - h * ns;
-        if (k == 0) { acc[0] = acc[1] = acc[2] = acc[3] = 0.f; big = -INFINITY; den = 0.f; }
-        const float m_new = fmaxf(big, mv);
-        const float keep = (big == -INFINITY) ? 0.f : expf(big - m_new);
-        const float c = (mv == -INFINITY) ? 0.f : expf(mv - m_new);
-        den = den * keep + lv * c;
-        acc[0] = acc[0] * keep + c * xv[u].x; acc[1] = acc[1] * keep + c * xv[u].y;
-        acc[2] = acc[2] * keep + c * xv[u].z; acc[3] = acc[3] * keep + c * xv[u].w;
-        big = m_new;
-        if (k == ns - 1) {
-          const int hq = kvh * p.group + h;
-          if (p.packed_output != nullptr) {
-            float* dst = p.packed_output + ((int64_t)b * p.num_q_heads + hq) * (D + 2);
-            *reinterpret_cast<float2*>(dst + lane * 4) = make_float2(acc[0], acc[1]);
-            *reinterpret_cast<float2*>(dst + lane * 4 + 2) = make_float2(acc[2], acc[3]);
-            if (lane == 0) { dst[D] = big; dst[D + 1] = den; }
-          } else {
-            const float inv = 1.f / den;
-            uint16_t* dst = reinterpret_cast<uint16_t*>(p.output) + (int64_t)b * p.o_stride_b + (int64_t)hq * p.o_stride_h + lane * 4;
-            uint32_t w0, w1;
-            if constexpr (QBF16) {
-              __nv_bfloat162 x = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
-              __nv_bfloat162 y = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
-              w0 = *reinterpret_cast<uint32_t*>(&x);
-              w1 = *reinterpret_cast<uint32_t*>(&y);
-            } else {
-              w0 = pack_f16x2(acc[0] * inv, acc[1] * inv);
-              w1 = pack_f16x2(acc[2] * inv, acc[3] * inv);
-            }
-            *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
-          }
+      const bool first = k == 0;
+      const float big_in = first ? -INFINITY : big;
+      const float m_new = fmaxf(big_in, mv);
+      const float keep = (big_in == -INFINITY) ? 0.f : expf(big_in - m_new);
+      const float c = (mv == -INFINITY) ? 0.f : expf(mv - m_new);
+      den = den * keep + lv * c;
+      acc[0] = acc[0] * keep + c * xv[u].x; acc[1] = acc[1] * keep + c * xv[u].y;
+      acc[2] = acc[2] * keep + c * xv[u].z; acc[3] = acc[3] * keep + c * xv[u].w;
+      big = m_new;
+      const bool last = live & (k == ns - 1);
+      const int hq = j.hq0 + h;
+      if constexpr (PACKED) {
+        float* dst = j.packed + ((int64_t)j.b * j.num_q_heads + hq) * (D + 2);
+        if (last) {
+          *reinterpret_cast<float2*>(dst + lane * 4) = make_float2(acc[0], acc[1]);
+          *reinterpret_cast<float2*>(dst + lane * 4 + 2) = make_float2(acc[2], acc[3]);
+          if (lane == 0) { dst[D] = big; dst[D + 1] = den; }
         }
+      } else {
+        const float inv = 1.f / den;
+        uint16_t* dst = reinterpret_cast<uint16_t*>(j.output) + (int64_t)j.b * j.o_stride_b + (int64_t)hq * j.o_stride_h + lane * 4;
+        uint32_t w0, w1;
+        if constexpr (QBF16) {
+          __nv_bfloat162 x = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
+          __nv_bfloat162 y = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+          w0 = *reinterpret_cast<uint32_t*>(&x);
+          w1 = *reinterpret_cast<uint32_t*>(&y);
+        } else {
+          w0 = pack_f16x2(acc[0] * inv, acc[1] * inv);
+          w1 = pack_f16x2(acc[2] * inv, acc[3] * inv);
+        }
+        if (last) *reinterpret_cast<uint2*>(dst) = make_uint2(w0, w1);
       }
+      advance(h, k, live);
     }
+    h_base = h;
+    k_base = k;
   }
 }
 
@@ -740,9 +792,13 @@ __device__ __forceinline__ void write_empty_sequence(const KernelParams& p, int 
 
 // grid = one CTA per SM; block = NWARPS independent warps.  KV16 = false: e4m3 caches;
 // true: caches in the query's 16-bit type (the reference's non-quantised sibling operator).
-// cp.plan == nullptr: every CTA derives the work split itself and the merge kernel behind
-// combines the pieces; with a plan the split is read and the pieces are combined in here.
-template <bool QBF16, int NSTAGE, int NWARPS, bool KV16 = false>
+// cp.plan == nullptr: every CTA derives the work split itself; with a plan it is read.  The
+// merge kernel behind combines the pieces of cut sequences -- unless FUSED (needs a plan): then
+// the warp whose piece of a sequence arrives last combines them in here and no merge kernel
+// follows.  FUSED is a separate instantiation because the merge code costs the streaming loop
+// registers; on B200 it is the slower of the two (one warp per sequence and kv head merges
+// where the merge kernel has a warp per row).
+template <bool QBF16, int NSTAGE, int NWARPS, bool KV16 = false, bool FUSED = false>
 __global__ void __launch_bounds__(NWARPS * 32, 1)
 paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const ChunkParams cp,
                               const __grid_constant__ CUtensorMap tmap_k,
@@ -776,7 +832,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
   int32_t* sm_scan = reinterpret_cast<int32_t*>(base + NWARPS * NSTAGE * kStage + NWARPS * NSTAGE * 8);  // [NWARPS]
   int32_t* prefix = sm_scan + NWARPS;  // [B + 1] pairs before sequence b
   int32_t* lens = prefix + (B + 1);    // [B]
-  const PairList list{prefix, lens, B, page_first};
+  const PairList list{prefix, lens, B, page_first, p.kv_start};
 
   mark_phase_at(tp, W, 0, lane == 0);  // start
   mark_value_at(tp, W, 5, lane == 0, sm_id());
@@ -789,7 +845,8 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copies' completions see initialised barriers
   }
 
-  int total, P0, P1;
+  int total;
+  ChunkRange cr;
   int32_t ids_cur;
   bool plan_ok = true;
   if (planned) {
@@ -798,13 +855,16 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
     const int32_t* gw = cp.plan + plan_groups_off(B) + (int64_t)min(grp, num_groups - 1) * kPlanGroupWords;
     const int4 h0 = __ldg(reinterpret_cast<const int4*>(cp.plan));      // magic, batch, kv_start, kv heads
     const int4 h1 = __ldg(reinterpret_cast<const int4*>(cp.plan) + 1);  // groups, piece cost, total, indptr
-    P0 = __ldg(gw);
-    P1 = __ldg(gw + 1);
+    const int4 g0 = __ldg(reinterpret_cast<const int4*>(gw));  // P0, P1, split flags, -
+    cr.P0 = g0.x;
+    cr.P1 = g0.y;
+    cr.head_split = (g0.z & 1) != 0;
+    cr.tail_split = (g0.z & 2) != 0;
     ids_cur = __ldg(gw + 4 + lane);
     plan_ok = h0.x == kPlanMagic && h0.y == B && h0.z == p.kv_start && h0.w == hkv && h1.x == num_groups &&
               h1.y == cp.piece_cost && h1.w == (p.page_indptr != nullptr ? 1 : 0);
     total = h1.z;
-    if (grp >= num_groups || !plan_ok) { P0 = P1 = total; ids_cur = -1; }
+    if (grp >= num_groups || !plan_ok) { cr.P0 = cr.P1 = total; cr.head_split = cr.tail_split = false; ids_cur = -1; }
     // prefix sum and lengths into shared memory; used only after the barrier further down
     for (int x = threadIdx.x; x < 2 * B + 1; x += NT) prefix[x] = __ldg(cp.plan + kPlanHeaderWords + x);
   } else {
@@ -815,10 +875,10 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
   const Chunking chunks(total, B, max(num_groups, 1), cp.piece_cost);
   const int C0 = chunks.start_of(grp);
   if (!planned) {
-    P0 = grp < chunks.groups ? list.pairs_before(chunks, C0) : total;
-    P1 = grp < chunks.groups ? list.pairs_before(chunks, chunks.start_of(grp + 1)) : total;
-    ids_cur = list.fetch_ids(p, P0, P1, 0, lane);
+    cr = chunk_range(list, chunks, grp);
+    ids_cur = fetch_ids(list, p, cr, 0, lane);
   }
+  const int P0 = cr.P0, P1 = cr.P1;
   const int n = P1 - P0;
 
   auto fire = [&](int t, int32_t ids, int base_t) {  // all lanes call; lane 0 issues
@@ -827,8 +887,8 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
     if (lane == 0) {
       const uint32_t bar = my_bars + 8 * (t % NSTAGE);
       const uint32_t dst = my_ring + (t % NSTAGE) * kStage;
-      const bool two = phys1 >= 0;
-      mbar_expect_tx(bar, two ? kStage : kStage / 2);
+      const bool has0 = phys0 >= 0, has1 = phys1 >= 0;  // a page of a shared pair may be the neighbour's
+      mbar_expect_tx(bar, ((has0 ? 1 : 0) + (has1 ? 1 : 0)) * (kStage / 2));
       const int c1 = tp.head_is_dim1 ? kvh : 0;
       const int c2 = tp.head_is_dim1 ? 0 : kvh;
       const uint64_t pol = l2_policy_evict_first();
@@ -846,9 +906,11 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
           else tma_load_tile(to, map, bar, c1, c2, phys);
         }
       };
-      load(dst, &tmap_k, phys0);
-      load(dst + 2 * kTile, &tmap_v, phys0);
-      if (two) {
+      if (has0) {
+        load(dst, &tmap_k, phys0);
+        load(dst + 2 * kTile, &tmap_v, phys0);
+      }
+      if (has1) {
         load(dst + kTile, &tmap_k, phys1);
         load(dst + 3 * kTile, &tmap_v, phys1);
       }
@@ -866,13 +928,13 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       if (threadIdx.x == 0) atomicExch(tp.status, kErrPlanMismatch);
       return;
     }
-    if (cp.merge_in_kernel)  // rows of sequences with nothing to attend
+    if constexpr (FUSED)  // rows of sequences with nothing to attend
       for (int b = W; b < B; b += cp.num_warps)
         if (prefix[b + 1] == prefix[b]) write_empty_sequence<D>(p, b, lane);
   }
   if (n <= 0) return;  // (any pdl_wait this grid owes has been executed above)
 
-  int32_t ids_next = list.fetch_ids(p, P0, P1, 16, lane);
+  int32_t ids_next = fetch_ids(list, p, cr, 16, lane);
   int ids_base = 0;
 
   // swizzled shared-memory offsets of this thread's fragments inside a tile
@@ -923,7 +985,9 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       load_q(qn, nxt.b);
     }
     const int seq_len = lens[cur.b];
-    const bool whole = cur.start >= P0 && cur.start + cur.np <= P1;
+    // every page of the sequence is this chunk's: no piece, the final rows are written here
+    const bool whole = cur.start >= P0 && cur.start + cur.np <= P1 && !(cr.head_split && cur.start == P0) &&
+                       !(cr.tail_split && cur.start + cur.np == P1);
     bal_reset<1>(st);
 #pragma unroll 1
     for (; g < e; ++g, ++t) {
@@ -932,8 +996,12 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       if (t == 0) mark_phase_at(tp, W, 3, lane == 0);  // first data landed
       if (t == n / 2) mark_phase_at(tp, W, 6, lane == 0);  // half of the chunk consumed
       const int tok0 = (page_first + 2 * (g - cur.start)) * kPage;
-      if constexpr (KV16) kv16_step<QBF16>(st, my_ring + s * kStage, qb, scale_log2, tok0, p.kv_start, seq_len, lane);
-      else bal_step<1>(st, my_ring + s * kStage, k_off, v_off, qb, scale_log2, tok0, p.kv_start, seq_len, i, j);
+      // tokens attended in this step: the sequence's, minus the page of a shared pair that is the
+      // neighbouring chunk's (not loaded: whatever the stage holds there is masked like a tail)
+      const int lo = (cr.head_split && g == P0) ? max(p.kv_start, tok0 + kPage) : p.kv_start;
+      const int hi = (cr.tail_split && g == P1 - 1) ? min(seq_len, tok0 + kPage) : seq_len;
+      if constexpr (KV16) kv16_step<QBF16>(st, my_ring + s * kStage, qb, scale_log2, tok0, lo, hi, lane);
+      else bal_step<1>(st, my_ring + s * kStage, k_off, v_off, qb, scale_log2, tok0, lo, hi, i, j);
       // all reads of the stage fed MMAs above: hand it back to TMA for the chunk's pair t + NSTAGE
       __syncwarp();
       const int tn = t + NSTAGE;
@@ -941,7 +1009,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
         if ((tn & 15) == 0) {
           ids_cur = ids_next;
           ids_base = tn;
-          ids_next = list.fetch_ids(p, P0, P1, tn + 16, lane);
+          ids_next = fetch_ids(list, p, cr, tn + 16, lane);
         }
         if (lane == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         fire(tn, ids_cur, ids_base);
@@ -1023,15 +1091,18 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
         }
       }
     }
-    if (!whole && cp.merge_in_kernel) {
-      // Publish the piece, then count this warp's pairs of the sequence in: the warp that
+    if constexpr (FUSED) if (!whole) {
+      // Publish the piece, then count this warp's pages of the sequence in: the warp that
       // completes the count finds every other piece in L2 and writes the final rows.
       __threadfence();
       __syncwarp();
-      const int mine = e - piece_first;
+      const int seq_pages = pages_of(seq_len, p.kv_start);
+      const int page_a = 2 * (piece_first - cur.start) + ((cr.head_split && piece_first == P0) ? 1 : 0);
+      const int page_e = min(2 * (e - cur.start), seq_pages) - ((cr.tail_split && e == P1) ? 1 : 0);
+      const int mine = page_e - page_a;
       int32_t* counter = cp.plan + plan_counters_off(B, num_groups) + (int64_t)cur.b * hkv + kvh;
 #ifdef PFD_BOUNDS_CHECK
-      if (cur.b < 0 || cur.b >= B || mine <= 0 || mine > cur.np) {
+      if (cur.b < 0 || cur.b >= B || mine <= 0 || mine > seq_pages) {
         mark_value_at(tp, 2 * cp.num_warps + 3, 0, lane == 0, ((unsigned long long)(unsigned)cur.b << 32) | (unsigned)mine);
         mark_value_at(tp, 2 * cp.num_warps + 3, 1, lane == 0, ((unsigned long long)(unsigned)cur.np << 32) | (unsigned)W);
       }
@@ -1039,10 +1110,30 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       int before = 0;
       if (lane == 0) before = atomicAdd(counter, mine);
       before = __shfl_sync(0xffffffffu, before, 0);
-      if (before + mine == cur.np) {
+      if (before + mine == seq_pages) {
         __threadfence();
         mark_phase_at(tp, cp.num_warps + W, 0, lane == 0);  // merge begins
-        merge_pieces_of_sequence<QBF16>(p, chunks, cur.b, kvh, cur.np, s0, lane, tp, 2 * cp.num_warps);
+        MergeJob job;
+        job.po = reinterpret_cast<const float*>(p.partial_output);
+        job.pm = p.partial_max;
+        job.pl = p.partial_sum;
+        job.output = p.output;
+        job.packed = p.packed_output;
+        job.o_stride_b = p.o_stride_b;
+        job.o_stride_h = p.o_stride_h;
+        job.num_q_heads = p.num_q_heads;
+        job.hq0 = kvh * p.group;
+        job.group = p.group;
+        job.w_first = chunks.chunk_of(s0);
+        job.ns = chunks.chunk_of(s0 + seq_pages - 1) - job.w_first + 1;
+        job.which0 = s0 > chunks.start_of(job.w_first) ? 1 : 0;
+        job.b = cur.b;
+#ifdef PFD_BOUNDS_CHECK
+        job.ws_rows = p.dbg_ws_rows;
+        job.report = tp.phase_times ? tp.phase_times + (size_t)(2 * cp.num_warps + 1) * 8 : nullptr;
+#endif
+        if (p.packed_output != nullptr) merge_pieces_of_sequence<QBF16, true>(job, lane);
+        else merge_pieces_of_sequence<QBF16, false>(job, lane);
         if (lane == 0) *counter = 0;  // ready for the next launch that uses this plan
         mark_phase_at(tp, cp.num_warps + W, 1, lane == 0);  // merged
       }
@@ -1083,23 +1174,33 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
   if (row >= cp.batch * p.num_q_heads) { pdl_wait(); return; }  // WPR == 1 only: whole warps, no barrier below
   const int b = row / p.num_q_heads, hq = row % p.num_q_heads;
   // seq_lens is an input of the whole step, not a result of the chunk kernel: the chunking is
-  // recomputed here while that kernel is still running.
-  int below = 0, all = 0;
-  for (int x = lane; x < cp.batch; x += 32) {
-    const int np = pairs_of(__ldg(p.seq_lens + x), p.kv_start);
-    all += np;
-    below += x < b ? np : 0;
-  }
+  // read from the plan, or recomputed here, while that kernel is still running.
+  int below = 0, all = 0, np = 0, seq_pages = 0;
+  if (cp.plan != nullptr) {
+    const int32_t* pre = cp.plan + kPlanHeaderWords;
+    below = __ldg(pre + b);
+    np = __ldg(pre + b + 1) - below;
+    all = __ldg(pre + cp.batch);
+    seq_pages = pages_of(__ldg(pre + cp.batch + 1 + b), p.kv_start);
+  } else {
+    for (int x = lane; x < cp.batch; x += 32) {
+      const int n = pairs_of(__ldg(p.seq_lens + x), p.kv_start);
+      all += n;
+      below += x < b ? n : 0;
+    }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    all += __shfl_xor_sync(0xffffffffu, all, off);
-    below += __shfl_xor_sync(0xffffffffu, below, off);
+    for (int off = 16; off > 0; off >>= 1) {
+      all += __shfl_xor_sync(0xffffffffu, all, off);
+      below += __shfl_xor_sync(0xffffffffu, below, off);
+    }
+    const int len = __ldg(p.seq_lens + b);
+    np = pairs_of(len, p.kv_start);
+    seq_pages = pages_of(len, p.kv_start);
   }
-  const int np = pairs_of(__ldg(p.seq_lens + b), p.kv_start);
   const Chunking chunks(all, cp.batch, max(cp.num_warps / p.num_kv_heads, 1), cp.piece_cost);
   const int s0 = chunks.first_unit(below, b);
   const int w_first = np > 0 ? chunks.chunk_of(s0) : 0;
-  const int ns = np > 0 ? chunks.chunk_of(s0 + 2 * (np - 1)) - w_first + 1 : 0;
+  const int ns = np > 0 ? chunks.chunk_of(s0 + seq_pages - 1) - w_first + 1 : 0;
   if (ns == 1) { pdl_wait(); return; }  // written by the chunk kernel (the whole CTA returns: one row per CTA if WPR == 4)
   float acc[E] = {0.f, 0.f, 0.f, 0.f};
   float big = -INFINITY, den = 0.f;

@@ -22,6 +22,7 @@ FLAG_NO_DIRECT_OUT = 2
 FLAG_PARTIAL_ONLY = 4
 FLAG_FIXED_SPLITS = 8
 FLAG_EARLY_METADATA = 32
+FLAG_SINGLE_LAUNCH = 64
 
 
 def load_library(path: Optional[Union[str, Path]] = None) -> None:
@@ -167,7 +168,7 @@ def paged_decode_fp8_e4m3_split_out_v2(
     (0 = ``D**-0.5``), first attended token ``kv_start`` and, instead of or besides
     ``output``, a packed fp32 ``[B, Hq, D + 2]`` ``(o, m, l)`` for cross-GPU merging.
     ``flags`` are the ``FLAG_*`` bits above.  ``plan`` is the buffer ``plan_decode`` filled for the
-    same lengths, block table and workspace: with it the step is a single kernel launch."""
+    same lengths, block table and workspace (``FLAG_SINGLE_LAUNCH`` needs one)."""
     torch.ops.l20_stack.paged_decode_fp8_e4m3_split_out_v2(
         query,
         key_cache,

@@ -160,13 +160,16 @@ def l20_paged_split_kv_attention_fp8(
     workspace: tuple[torch.Tensor, ...] | None = None,
     metadata_stable: bool = False,
     plan: torch.Tensor | None = None,
+    single_launch: bool = False,
 ) -> torch.Tensor:
     """``metadata_stable=True`` (not in the reference) tells the operator that the kernel
     running before it on the stream does not write ``block_table``, ``seq_lens`` or ``plan`` --
     true for every layer of a model step, whose metadata is built once -- so that it may read
     them while that kernel drains (``PFD_FLAG_EARLY_METADATA``).  ``plan`` (not in the reference
-    either) is the result of ``plan_l20_paged_split_kv`` for the same step: with it the call is
-    one kernel launch."""
+    either) is the result of ``plan_l20_paged_split_kv`` for the same step: the kernels then read
+    their work split instead of deriving it; ``single_launch`` (needs a plan) makes the balanced
+    kernel combine the pieces of cut sequences itself, one launch instead of two
+    (``PFD_FLAG_SINGLE_LAUNCH``; the slower of the two on B200)."""
     if not _on_required_gpu(query):
         raise RuntimeError("requires an SM100 GPU")
     if query.ndim != 3 or key_cache.ndim != 4 or value_cache.shape != key_cache.shape:
@@ -216,7 +219,8 @@ def l20_paged_split_kv_attention_fp8(
             query, key_cache, value_cache, block_table, seq_lens,
             partial_output, partial_max, partial_sum, output,
             as_vec(k_scale), as_vec(v_scale), max_seq_len, split_size,
-            flags=ops.FLAG_EARLY_METADATA if metadata_stable else 0, plan=plan,
+            flags=(ops.FLAG_EARLY_METADATA if metadata_stable else 0) | (ops.FLAG_SINGLE_LAUNCH if single_launch else 0),
+            plan=plan,
         )
         return output
     return ops.paged_decode_fp8_e4m3_split_out(
@@ -239,9 +243,10 @@ def l20_paged_split_kv_attention(
     output: torch.Tensor | None = None,
     metadata_stable: bool = False,
     plan: torch.Tensor | None = None,
+    single_launch: bool = False,
 ) -> torch.Tensor:
     """The non-quantised sibling (reference :491-594): K/V caches in the query's fp16 / bf16
-    type.  ``metadata_stable`` / ``plan`` as for the FP8 wrapper.  ``page_granular`` / ``grouped_gqa`` of the reference select between its Triton kernel
+    type.  ``metadata_stable`` / ``plan`` / ``single_launch`` as for the FP8 wrapper.  ``page_granular`` / ``grouped_gqa`` of the reference select between its Triton kernel
     variants and have no counterpart here.  ``max_seq_len`` (not in the reference, which always
     reads it back from the device, :517) avoids that host synchronisation."""
     if not _on_required_gpu(query):
@@ -283,7 +288,8 @@ def l20_paged_split_kv_attention(
         return ops.paged_decode_split_out_v2(
             query, key_cache, value_cache, block_table, seq_lens,
             partial_output, partial_max, partial_sum, output, max_seq_len, split_size,
-            flags=ops.FLAG_EARLY_METADATA if metadata_stable else 0, plan=plan,
+            flags=(ops.FLAG_EARLY_METADATA if metadata_stable else 0) | (ops.FLAG_SINGLE_LAUNCH if single_launch else 0),
+            plan=plan,
         )
     return ops.paged_decode_split_out(
         query, key_cache, value_cache, block_table, seq_lens,

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 
 DEV = "cuda:0"
 PATH_KV16 = 4
-PATH_KV16_PLANNED = 6
+PATH_KV16_FUSED = 6
 
 
 @pytest.fixture(scope="module")
@@ -35,7 +35,10 @@ def workspace(q, splits, dtype=torch.float32):
 
 
 def run(cabi, w, *, splits=None, partial_dtype=torch.float32, kv_start=0, packed=False, flags=0, planned=False):
-    """planned: pfd_plan_decode first, then the call with that plan (one launch, merge inside)."""
+    """planned: pfd_plan_decode first, then the call with that plan; "fused": with
+    PFD_FLAG_SINGLE_LAUNCH on top (pieces combined inside the balanced kernel)."""
+    if planned == "fused":
+        flags |= 64
     q = w.query
     hkv = w.key_cache.shape[2]
     if splits is None:  # room for every warp group
@@ -54,7 +57,7 @@ def run(cabi, w, *, splits=None, partial_dtype=torch.float32, kv_start=0, packed
     )
     torch.cuda.synchronize()
     assert cabi.device_status() == 0, "a bounded device-side wait gave up"
-    assert cabi.last_path() == (PATH_KV16_PLANNED if planned and partial_dtype == torch.float32 else PATH_KV16)
+    assert cabi.last_path() == (PATH_KV16_FUSED if planned == "fused" and partial_dtype == torch.float32 else PATH_KV16)
     return pk if packed else out
 
 
@@ -71,7 +74,7 @@ def test_against_committed_reference_outputs(cabi, golden, name):
     w = make_inputs(case["workload"], seed=0, device="cpu", batch=case["batch"], shrink=case["shrink"],
                     query_dtype=dtype, kv_dtype=dtype)
     for splits in (None, 1, 3):  # full capacity; the smallest legal workspaces (few warp groups)
-        for planned in (False, True):
+        for planned in (False, True, "fused"):
             assert_within_gate(run(cabi, w.to(DEV), splits=splits, planned=planned), case["output"],
                                f"{name} splits={splits} planned={planned}")
 
@@ -83,6 +86,7 @@ def test_config2_and_config3_full_size(cabi, dtype):
         exp = expected(w)
         assert_within_gate(run(cabi, w.to(DEV)), exp, f"{name} {dtype}")
         assert_within_gate(run(cabi, w.to(DEV), planned=True, flags=32), exp, f"{name} {dtype} planned")
+        assert_within_gate(run(cabi, w.to(DEV), planned="fused", flags=32), exp, f"{name} {dtype} fused")
 
 
 @pytest.mark.parametrize("hq,hkv", [(16, 2), (28, 4), (32, 8), (8, 8), (12, 2)])
@@ -122,13 +126,14 @@ def test_hnd_layout_partial_dtypes_kv_start_and_packed_output(cabi):
     assert not g.key_cache.is_contiguous()
     assert_within_gate(run(cabi, g), exp, "hnd")
     assert_within_gate(run(cabi, g, planned=True), exp, "hnd planned")
+    assert_within_gate(run(cabi, g, planned="fused"), exp, "hnd fused")
     for pdtype in (torch.float16, torch.bfloat16):  # the reference keeps partials in the query dtype
-        for planned in (False, True):  # a plan is ignored for 16-bit partials
+        for planned in (False, "fused"):  # a plan is ignored for 16-bit partials
             out = run(cabi, g, partial_dtype=pdtype, planned=planned)
             assert torch.allclose(out.float().cpu(), exp.float(), atol=2e-2, rtol=2e-2)
     # suffix only, as packed (o, m, l)
     cut = 100
-    pk2 = run(cabi, g, kv_start=cut, packed=True, planned=True)
+    pk2 = run(cabi, g, kv_start=cut, packed=True, planned="fused")
     pk = run(cabi, g, kv_start=cut, packed=True)
     assert torch.allclose((pk2[..., :-2] / pk2[..., -1:]).nan_to_num(), (pk[..., :-2] / pk[..., -1:]).nan_to_num(), atol=1e-5, rtol=1e-4)
     sub = oracle.reference_kv16(w.query, w.key_cache, w.value_cache, w.block_table.long(), w.seq_lens, kv_start=cut)

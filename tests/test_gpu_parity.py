@@ -27,9 +27,11 @@ def cabi(built_libs):
     return module
 
 
-PATH_LDG, PATH_TMA, PATH_BALANCED, PATH_PLANNED = 1, 2, 3, 5
+PATH_LDG, PATH_TMA, PATH_BALANCED, PATH_FUSED = 1, 2, 3, 5
 EARLY = 32  # PFD_FLAG_EARLY_METADATA: what the benchmark and the vLLM hook pass
+SINGLE = 64  # PFD_FLAG_SINGLE_LAUNCH: pieces combined inside the balanced kernel (needs a plan)
 PLAN = 1 << 20  # not a library flag: the test helpers call pfd_plan_decode first and pass the plan
+FUSED = PLAN | SINGLE
 
 
 def workspace(q, max_seq_len, split_size, dtype=torch.float32, kv_start=0, poison=True, min_rows=0):
@@ -49,23 +51,23 @@ def workspace(q, max_seq_len, split_size, dtype=torch.float32, kv_start=0, poiso
 def expected_path(cabi, q, num_kv_heads, flags, partial_dtype=torch.float32):
     """Which kernels a call must have launched.  flags 0: the library's choice, i.e. the balanced
     persistent kernel for head_dim 128 with at most 8 query heads per kv head and an f32 workspace
-    that is large enough (PLAN: with a plan, as one launch); 8: fixed-split grid with TMA; 1: with
-    plain loads."""
+    that is large enough (PLAN: both kernels read a plan; FUSED: the balanced kernel alone); 8:
+    fixed-split grid with TMA; 1: with plain loads."""
     _, hq, d = q.shape
     if flags & 1 or d != 128:
         return PATH_LDG
     if flags & (8 | 2) or partial_dtype != torch.float32 or hq // num_kv_heads > 8:
         return PATH_TMA
-    return PATH_PLANNED if flags & PLAN else PATH_BALANCED
+    return PATH_FUSED if (flags & FUSED) == FUSED else PATH_BALANCED
 
 
 def balanced(path):
-    return path in (PATH_BALANCED, PATH_PLANNED)
+    return path in (PATH_BALANCED, PATH_FUSED)
 
 
-def make_plan(cabi, want, q, kc, vc, table, lens, ws, msl, split_size, kv_start=0):
-    """The plan of a call that is to run the planned path (None otherwise)."""
-    if want != PATH_PLANNED:
+def make_plan(cabi, want, flags, q, kc, vc, table, lens, ws, msl, split_size, kv_start=0):
+    """The plan of a call that asks for one (PLAN) and runs the balanced kernel (None otherwise)."""
+    if not (flags & PLAN) or not balanced(want):
         return None
     return cabi.plan_decode(q, kc, vc, table, lens, max_seq_len=msl, split_size=split_size, workspace=ws, kv_start=kv_start)
 
@@ -81,7 +83,7 @@ def run(cabi, w, split_size, *, flags=0, kv_start=0, partial_dtype=torch.float32
     ws = workspace(q, msl, split_size, partial_dtype, kv_start, min_rows=rows)
     out = torch.full_like(q, float("nan"))
     pk = torch.full((q.shape[0], q.shape[1], q.shape[2] + 2), float("nan"), device=q.device) if packed else None
-    plan = make_plan(cabi, want, q, w.key_cache, w.value_cache, w.block_table, w.seq_lens, ws, msl, split_size, kv_start)
+    plan = make_plan(cabi, want, flags, q, w.key_cache, w.value_cache, w.block_table, w.seq_lens, ws, msl, split_size, kv_start)
     flags &= ~PLAN
     cabi.paged_decode_fp8_e4m3_split_out(
         q, w.key_cache, w.value_cache, w.block_table, w.seq_lens,
@@ -104,7 +106,7 @@ def expected(w, **kw):
 @pytest.mark.parametrize(
     "name", ["cfg1-qwen0.5b-b8", "cfg2-coder3b-b4", "cfg3-qwen7b-b24", "cfg4-llama8b-b2", "cfg5-prefix-b8"]
 )
-@pytest.mark.parametrize("flags", [PLAN, 8, 1, 0, PLAN | EARLY])
+@pytest.mark.parametrize("flags", [PLAN, FUSED, 8, 1, 0, PLAN | EARLY, FUSED | EARLY])
 def test_against_committed_reference_outputs(cabi, golden, name, flags):
     case = golden["cases"][name]
     w = make_inputs(case["workload"], seed=0, device="cpu", batch=case["batch"], shrink=case["shrink"])
@@ -141,7 +143,7 @@ def test_config1_full_size(cabi):
 def test_config2_full_size(cabi):
     w = make_inputs("qwen2.5-coder-3b-b64", seed=0)
     exp = expected(w)
-    for split, flags in ((256, PLAN), (512, 0), (896, 0), (512, 8), (1024, 1), (512, EARLY), (896, EARLY | 8), (256, EARLY | 1), (512, PLAN | EARLY)):
+    for split, flags in ((256, PLAN), (512, 0), (896, 0), (512, 8), (1024, 1), (512, EARLY), (896, EARLY | 8), (256, EARLY | 1), (512, PLAN | EARLY), (512, FUSED), (256, FUSED | EARLY)):
         assert_within_gate(run(cabi, w.to(DEV), split, flags=flags), exp, f"cfg2 split={split} flags={flags}")
 
 
@@ -149,7 +151,7 @@ def test_config3_full_size_log_uniform_lengths(cabi):
     w = make_inputs("qwen2.5-7b-b256", seed=0)
     assert int(w.seq_lens.min()) <= 4
     exp = expected(w)
-    for flags in (0, PLAN, 8, EARLY, EARLY | 8, PLAN | EARLY):
+    for flags in (0, PLAN, FUSED, 8, EARLY, EARLY | 8, PLAN | EARLY, FUSED | EARLY):
         assert_within_gate(run(cabi, w.to(DEV), 512, flags=flags), exp, f"cfg3 flags={flags}")
 
 
@@ -164,6 +166,8 @@ def test_config4_long_context_sampled_rows_and_split_invariance(cabi):
     out_d = run(cabi, w, 2048, flags=EARLY)
     out_f = run(cabi, w, 2048, flags=PLAN | EARLY)
     assert_within_gate(out_f, out_a, "planned, early metadata vs not")
+    out_g = run(cabi, w, 2048, flags=FUSED | EARLY)
+    assert_within_gate(out_g, out_a, "pieces combined inside the balanced kernel vs the merge kernel")
     out_e = run(cabi, w, 1024, flags=EARLY | 8)
     assert_within_gate(out_d, out_a, "early metadata vs not")
     assert_within_gate(out_e, out_a, "early metadata, fixed split 1024 vs 2048")
@@ -183,7 +187,7 @@ def test_config4_long_context_sampled_rows_and_split_invariance(cabi):
 def test_config5_shared_prefix_full_size(cabi):
     w = make_inputs("shared-prefix-b64", seed=0)
     exp = expected(w)
-    for flags in (0, PLAN, 8, EARLY, EARLY | 8, PLAN | EARLY):
+    for flags in (0, PLAN, FUSED, 8, EARLY, EARLY | 8, PLAN | EARLY):
         assert_within_gate(run(cabi, w.to(DEV), 512, flags=flags), exp, f"cfg5 flags={flags}")
 
 
@@ -201,13 +205,13 @@ def test_every_short_context_length(cabi, d, hq, hkv):
     q = torch.randn(b, hq, d).to(torch.bfloat16)
     exp = oracle.reference(q, kc, vc, table.long(), lens, ks, vs)
     for split in (16, 32, 64, 512):
-        for flags in (PLAN, 0, 8, 1, 2, EARLY, EARLY | 8, EARLY | 1, PLAN | EARLY):
+        for flags in (PLAN, FUSED, 0, 8, 1, 2, EARLY, EARLY | 8, EARLY | 1, PLAN | EARLY, FUSED | EARLY):
             out = torch.full_like(q, float("nan"), device=DEV)
             want = expected_path(cabi, q, hkv, flags)
             rows = cabi.balanced_workspace_rows(hq, hkv) if balanced(want) else 0
             ws = workspace(q.to(DEV), 70, split, min_rows=rows)
             g = [t.to(DEV) for t in (q, kc, vc, table, lens)]
-            plan = make_plan(cabi, want, *g, ws, 70, split)
+            plan = make_plan(cabi, want, flags, *g, ws, 70, split)
             cabi.paged_decode_fp8_e4m3_split_out(
                 *g, k_scale=ks.to(DEV), v_scale=vs.to(DEV),
                 max_seq_len=70, split_size=split, output=out, workspace=ws, flags=flags & ~PLAN, plan=plan,
@@ -231,7 +235,7 @@ def test_unused_slots_may_hold_nan_bytes(cabi):
             kc[page, n % 16 :] = 0x7F
             vc[page, n % 16 :] = 0xFF
     w.key_cache, w.value_cache = kc.view(torch.float8_e4m3fn), vc.view(torch.float8_e4m3fn)
-    for flags in (PLAN, 0, 8, 1):
+    for flags in (PLAN, FUSED, 0, 8, 1):
         assert_within_gate(run(cabi, w.to(DEV), 64, flags=flags), exp, "nan slots")
 
 
@@ -253,7 +257,7 @@ def test_consumer_right_behind_the_call_sees_finished_rows(cabi):
     split while max_seq_len asks for several."""
     torch.manual_seed(3)
     hq, hkv, d, pages = 16, 2, 128, 8
-    for batch, ctx, msl, flags in ((1, 64, 64, 0), (1, 64, 64, EARLY), (3, 60, 640, 8), (3, 60, 640, EARLY | 8), (1, 64, 64, PLAN), (2, 640, 640, PLAN | EARLY)):
+    for batch, ctx, msl, flags in ((1, 64, 64, 0), (1, 64, 64, EARLY), (3, 60, 640, 8), (3, 60, 640, EARLY | 8), (1, 64, 64, FUSED), (2, 640, 640, FUSED | EARLY), (2, 640, 640, PLAN | EARLY)):
         lens = torch.full((batch,), ctx, dtype=torch.int32)
         table = torch.randperm(batch * 40).to(torch.int32).reshape(batch, 40)
         kc, ks = oracle.quantize_fp8_e4m3_per_head(torch.randn(batch * 40, 16, hkv, d))
@@ -264,7 +268,7 @@ def test_consumer_right_behind_the_call_sees_finished_rows(cabi):
         want = expected_path(cabi, q, hkv, flags)
         rows = cabi.balanced_workspace_rows(hq, hkv) if balanced(want) else 0
         ws = workspace(g[0], msl, 64, min_rows=rows)
-        plan = make_plan(cabi, want, *g[:5], ws, msl, 64)
+        plan = make_plan(cabi, want, flags, *g[:5], ws, msl, 64)
         torch.cuda.synchronize()
         out = torch.empty_like(g[0])
         copies = []
@@ -314,7 +318,7 @@ def test_strided_cache_layouts(cabi, layout):
         big2[:, :, :hkv] = g.value_cache
         g.key_cache, g.value_cache = big[:, :, :hkv], big2[:, :, :hkv]
     assert not g.key_cache.is_contiguous()
-    for flags in (PLAN, 0, 8, 1):
+    for flags in (PLAN, FUSED, 0, 8, 1):
         assert_within_gate(run(cabi, g, 64, flags=flags), exp, layout)
 
 
@@ -340,8 +344,8 @@ def test_kv_start_suffix_pass_and_packed_partials_merge(cabi):
     for cut in (w.prefix_len, w.prefix_len - 5, 3):
         head = g.to(DEV)
         head.seq_lens = torch.clamp(g.seq_lens, max=cut)
-        p0 = run(cabi, head, 128, packed=True, max_seq_len=cut, flags=PLAN if cut == 3 else 0)
-        p1 = run(cabi, g, 128, packed=True, kv_start=cut, flags=PLAN if cut % 2 else 8)
+        p0 = run(cabi, head, 128, packed=True, max_seq_len=cut, flags=FUSED if cut == 3 else 0)
+        p1 = run(cabi, g, 128, packed=True, kv_start=cut, flags=(FUSED if cut == 3 else PLAN) if cut % 2 else 8)
         out = torch.empty_like(g.query)
         cabi.merge_packed(torch.stack([p0, p1]).contiguous(), out)
         torch.cuda.synchronize()
@@ -419,8 +423,8 @@ def test_block_table_permutation_invariance_and_idempotence(cabi):
     c1, c2, c3 = run(cabi, w, 128, flags=0), run(cabi, w, 128, flags=0), run(cabi, moved, 128, flags=0)
     assert torch.equal(c1.view(torch.int16), c2.view(torch.int16))
     assert torch.equal(c1.view(torch.int16), c3.view(torch.int16))
-    # with a plan the pieces of a cut sequence are folded in a fixed order as well
-    c1, c2, c3 = run(cabi, w, 128, flags=PLAN), run(cabi, w, 128, flags=PLAN), run(cabi, moved, 128, flags=PLAN)
+    # combined inside the balanced kernel the pieces of a cut sequence are folded in a fixed order as well
+    c1, c2, c3 = run(cabi, w, 128, flags=FUSED), run(cabi, w, 128, flags=FUSED), run(cabi, moved, 128, flags=FUSED)
     assert torch.equal(c1.view(torch.int16), c2.view(torch.int16))
     assert torch.equal(c1.view(torch.int16), c3.view(torch.int16))
 

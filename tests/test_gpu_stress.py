@@ -90,14 +90,17 @@ def test_random_cases(cabi, kv16):
         )
         out = torch.full_like(g[0], float("nan"))
         flags = rng.choice([0, 32])  # with and without early metadata reads
-        planned = rng.random() < 0.6  # one launch with a plan, or chunk kernel + merge kernel
+        planned = rng.random() < 0.7  # both kernels read a plan, or derive the split themselves
+        fused = planned and rng.random() < 0.5  # pieces combined inside the balanced kernel (one launch)
         what = (f"case {case}: kv16={kv16} B={q.shape[0]} Hq={q.shape[1]} Hkv={hkv} max={int(lens.max())} "
-                f"kv_start={kv_start} flags={flags} planned={planned}")
+                f"kv_start={kv_start} flags={flags} planned={planned} fused={fused}")
         plan = None
         if planned:
             plan = cabi.plan_decode(*g, max_seq_len=int(lens.max()), split_size=512, workspace=ws, kv_start=kv_start)
             if flags:  # the plan kernel must not be the kernel right in front of an early-metadata call
                 torch.cuda.synchronize()
+            if fused:
+                flags |= 64
         if kv16:
             cabi.paged_decode_kv16_split_out(*g, max_seq_len=int(lens.max()), split_size=512, output=out, workspace=ws,
                                              kv_start=kv_start, flags=flags, plan=plan)
@@ -107,11 +110,11 @@ def test_random_cases(cabi, kv16):
                                                  plan=plan)
         torch.cuda.synchronize()
         assert cabi.device_status() == 0, what
-        assert cabi.last_path() == ((6 if kv16 else 5) if planned else (4 if kv16 else 3)), what
+        assert cabi.last_path() == ((6 if kv16 else 5) if fused else (4 if kv16 else 3)), what
         assert_within_gate(out, exp, what)
 
 
-@pytest.mark.parametrize("planned", [False, True])
+@pytest.mark.parametrize("planned", [False, True, "fused"])
 @pytest.mark.parametrize("kv16", [False, True])
 def test_graph_replay_with_metadata_rewritten_in_place(built_libs, kv16, planned):
     from single_gpu_inference_lab_b200 import l20_paged_split_kv as m
@@ -150,11 +153,11 @@ def test_graph_replay_with_metadata_rewritten_in_place(built_libs, kv16, planned
         for _ in range(2):
             if kv16:
                 m.l20_paged_split_kv_attention(q, gk, gv, table, lens, split_size=512, workspace=ws, max_seq_len=max_len,
-                                               metadata_stable=True, plan=plan)
+                                               metadata_stable=True, plan=plan, single_launch=planned == "fused")
             else:
                 m.l20_paged_split_kv_attention_fp8(q, gk, gv, table, lens, k_scale=gks, v_scale=gvs,
                                                    max_seq_len=max_len, split_size=512, workspace=ws, metadata_stable=True,
-                                                   plan=plan)
+                                                   plan=plan, single_launch=planned == "fused")
 
     call()  # lazy initialisation outside the capture
     torch.cuda.synchronize()
