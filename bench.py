@@ -3,29 +3,38 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
-One *step* is one decode-attention layer-step over one synthetic batch (partial kernel +
-LSE merge kernel).  Metric: KV bytes read per second (``sum_b ctx_b * Hkv * D * 2`` bytes per
-step), with microseconds per layer-step beside it.  One JSON line is printed by rank 0.
+One *step* is one decode-attention layer-step over one synthetic batch.  Metric: KV bytes read
+per second (``sum_b ctx_b * Hkv * D * 2`` bytes per step), microseconds per layer-step beside
+it.  Rank 0 prints ONE JSON line.
 
-* ``value``        device-resident operands, CUDA events around K back-to-back steps; successive
-                   steps use different KV pools so that every step reads from HBM, not L2.
-* ``roofline``     the split-KV partial kernel alone (same pools, merge skipped), against the
-                   measured HBM copy peak.
+* ``value``        device-resident operands, CUDA events around K back-to-back steps replayed from
+                   CUDA graphs; successive steps use different KV pools so that every step reads
+                   from HBM, not L2.  Median of ``repeats`` such K-step runs.
+* ``correct`` / ``max_abs_error``  the exact call that is timed (same flags, split, workspace,
+                   plan, pool 0), run once before the timing and checked against the CPU oracle
+                   on a bounded sample of sequences (gate ``|a-b| <= 2e-3 + 1e-2 |b|``).
+* ``roofline``     the dominant kernel alone (merge skipped) against the measured HBM copy peak;
+                   ``traffic`` is read from ``profiles/traffic.json`` (ncu captures).
+* ``isolated``     the same step with an unrelated ordinary kernel launched between steps, i.e.
+                   without the overlap of one step's prologue with the previous step's tail that
+                   programmatic dependent launch gives back-to-back decode calls.
 * ``e2e``          the call a serving hook makes (``l20_paged_split_kv_attention_fp8``) with the
                    step's query / block table / sequence lengths copied from pinned host memory
                    and the output copied back, every step.  The KV cache is the resident state of
                    the serving engine and stays on the device.
+* ``per_config``   (N = 1) the other four configurations, each with the same fields in short.
+* ``sharded``      (N > 1) the two sharded forms: the batch of 256 split by sequence over the
+                   ranks (no communication) and the long-context batch split by KV range (packed
+                   partials exchanged, merged on every rank), with the one-GPU figure measured in
+                   the same run on rank 0 and the time of exchange + merge alone.
 * ``cpu_baseline`` the CPU oracle (torch restatement of the reference's own torch path) timed
                    on this host's cores on the same batch.
 * ``--impl reference`` times only that CPU path and prints its own line.
 
-With N > 1 every rank runs the same geometry on its own sequences (no data-path collective;
-``--strong`` shards ONE batch by sequence instead); ``--workload llama3-8b-long-b4`` splits each
-sequence's KV range over the ranks and merges the partials after one NCCL all-gather
-(``--graph-collective`` replays that step, collective included, from a CUDA graph).
-``--kv-dtype bf16|fp16`` times the non-quantised sibling operator on the same geometries;
-``--flags`` are the ``PFD_FLAG_*`` bits of the timed calls (default: early metadata reads; add 8
-for the fixed-split grid).
+With N > 1 the headline is one batch per GPU, the same batch (seed) on every rank, no data-path
+collective ("weak").  ``--strong`` / ``--workload llama3-8b-long-b4`` make a sharded form the
+headline instead.  ``--kv-dtype bf16|fp16`` times the non-quantised sibling operator; ``--flags``
+are the ``PFD_FLAG_*`` bits of the timed calls (default: early metadata reads).
 """
 
 from __future__ import annotations
@@ -46,15 +55,11 @@ sys.path.insert(0, str(ROOT))
 
 FALLBACK_HBM_GBS = 6650.0
 L2_BYTES = 126 * 1024 * 1024
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
-# captures summarised under profiles/ (the bench's own seed-0 workloads, full size).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = {
-    ("qwen2.5-coder-3b-b64", 3): 80_427_520 + 3_423_488,   # chunk kernel (mean of two launches)
-    ("qwen2.5-7b-b256", 3): 224_103_040 + 7_126_144,       # chunk kernel
-    ("qwen2.5-coder-3b-b64", 2): 80_438_016 + 3_118_592,   # fixed-split TMA kernel (--flags 40)
-}
-
 DEFAULT_WORKLOAD = "qwen2.5-coder-3b-b64"
+ALL_WORKLOADS = ("qwen2.5-0.5b-b8", "qwen2.5-coder-3b-b64", "qwen2.5-7b-b256", "llama3-8b-long-b4", "shared-prefix-b64")
+KERNEL_NAMES = {1: "paged_decode_fp8_partial_ldg_kernel", 2: "paged_decode_fp8_partial_tma_kernel",
+                3: "paged_decode_fp8_chunk_kernel", 4: "paged_decode_fp8_chunk_kernel<KV16>",
+                5: "paged_decode_fp8_chunk_kernel<FUSED>", 6: "paged_decode_fp8_chunk_kernel<KV16,FUSED>"}
 
 
 def parse_args():
@@ -62,6 +67,7 @@ def parse_args():
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=600)
     p.add_argument("--warmup", type=int, default=30)
+    p.add_argument("--repeats", type=int, default=5, help="K-step runs; the median is reported")
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--workload", default=DEFAULT_WORKLOAD)
     p.add_argument("--split-size", type=int, default=0, help="0 = choose from the geometry")
@@ -70,18 +76,19 @@ def parse_args():
                    help="fp8: the e4m3 path (headline); bf16 / fp16: the non-quantised sibling operator, "
                         "caches and query in that type (single GPU, batch-sharded or weak scaling only)")
     p.add_argument("--graph-collective", action="store_true",
-                   help="KV-range mode on several GPUs: replay the step, all-gather included, from a CUDA graph "
+                   help="KV-range mode on several GPUs: replay the step, exchange included, from a CUDA graph "
                         "instead of launching every step eagerly")
     p.add_argument("--flags", type=int, default=32,
                    help="PFD_FLAG_* bits of the timed calls; default PFD_FLAG_EARLY_METADATA: the block table "
                         "and sequence lengths do not change between the timed layer-steps")
     p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-per-config", action="store_true", help="skip the per_config / sharded sections")
     p.add_argument("--no-shared-prefix", action="store_true",
                    help="shared-prefix-b64 only: use the ordinary decode path instead of the dense tcgen05 prefix pass")
     p.add_argument("--single-launch", action="store_true",
                    help="with the plan: combine the pieces of cut sequences inside the balanced kernel (PFD_FLAG_SINGLE_LAUNCH)")
     p.add_argument("--no-plan", action="store_true",
-                   help="do not plan the step: every call derives its work split itself and a merge kernel follows")
+                   help="do not plan the step: every call derives its work split itself")
     p.add_argument("--strong", action="store_true",
                    help="N > 1: shard ONE batch by sequence over the ranks (token-balanced) instead of one batch per rank")
     return p.parse_args()
@@ -93,6 +100,32 @@ def measured_peak() -> tuple[float, str]:
         return float(peaks["hbm_gbs"]), "measured"
     except Exception:
         return FALLBACK_HBM_GBS, "fallback"
+
+
+def ncu_traffic(workload: str, kernel: str):
+    """dram bytes read + written per launch of `kernel` on `workload`, from the tracked summary of
+    the ncu captures (None when there is no capture of that pair)."""
+    try:
+        table = json.loads((ROOT / "profiles" / "traffic.json").read_text())
+    except Exception:
+        return None
+    for row in table.get("captures", []):
+        if row.get("workload") == workload and row.get("kernel") == kernel:
+            return int(row["dram_bytes_read"]) + int(row["dram_bytes_write"])
+    return None
+
+
+def bind_to_own_cores(local_rank: int, local_world: int) -> list[int]:
+    """Give every rank of the node its own slice of the host cores, so that the per-step host
+    path of one rank (copies, launches, stream sync) is not scheduled on another rank's cores."""
+    try:
+        cores = sorted(os.sched_getaffinity(0))
+        per = max(1, len(cores) // max(local_world, 1))
+        mine = cores[local_rank * per:(local_rank + 1) * per] or cores
+        os.sched_setaffinity(0, mine)
+        return mine
+    except Exception:
+        return []
 
 
 class ClockSampler:
@@ -158,6 +191,7 @@ class ClockSampler:
         }
 
 
+# --------------------------------------------------------------------------- CPU oracle legs
 def cpu_reference_run(w, sample_rows: int, repeats: int):
     """Time the CPU oracle on the first ``sample_rows`` sequences (their pages compacted into
     a cache of their own first, outside the timed region); returns (GB/s, seconds, bytes)."""
@@ -181,6 +215,39 @@ def cpu_reference_run(w, sample_rows: int, repeats: int):
         if attempt > 0 or repeats == 0:
             best = min(best, dt)
     return nbytes / best / 1e9, best, nbytes
+
+
+def check_against_oracle(w, out: torch.Tensor, token_budget: int = 150_000) -> tuple[bool, float, str]:
+    """Compare ``out`` (the timed call's result) with the CPU oracle on a bounded sample of
+    sequences: the first, the last, the longest and the shortest, then more until the budget of
+    tokens is spent.  The checker only: nothing here is timed."""
+    from oracle import paged_decode_oracle as oracle
+    from single_gpu_inference_lab_b200 import sharding
+
+    lens = w.seq_lens.cpu().long()
+    batch = lens.numel()
+    order = [0, batch - 1, int(lens.argmax()), int(lens.argmin())] + list(range(1, batch - 1))
+    rows, spent = [], 0
+    for b in order:
+        if b in rows or int(lens[b]) == 0:
+            continue
+        if rows and spent + int(lens[b]) > token_budget:
+            continue
+        rows.append(b)
+        spent += int(lens[b])
+        if spent >= token_budget:
+            break
+    idx = torch.tensor(sorted(rows))
+    sub = sharding.compact_rows(w, idx.to(w.query.device), 0, w.block_table.shape[1], lens[idx]).to("cpu")
+    if sub.key_cache.dtype == torch.float8_e4m3fn:
+        exp = oracle.reference(sub.query, sub.key_cache, sub.value_cache, sub.block_table.long(), sub.seq_lens,
+                               sub.k_scale, sub.v_scale)
+    else:
+        exp = oracle.reference_kv16(sub.query, sub.key_cache, sub.value_cache, sub.block_table.long(), sub.seq_lens)
+    got = out[idx.to(out.device)].float().cpu()
+    err = (got - exp.float()).abs()
+    ok = bool(torch.isfinite(got).all()) and bool((err <= 2e-3 + 1e-2 * exp.float().abs()).all())
+    return ok, float(err.max()), f"{len(rows)} of {batch} sequences ({spent} tokens)"
 
 
 def run_reference_arm(args, rank: int) -> int:
@@ -223,130 +290,151 @@ def run_reference_arm(args, rank: int) -> int:
     return 0
 
 
-def main() -> int:
-    args = parse_args()
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.impl == "reference":
-        return run_reference_arm(args, rank)
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device: the operator has no CPU path")
-    if world != args.gpus:
-        raise RuntimeError(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+# --------------------------------------------------------------------------- one workload on this rank
+class Case:
+    """One workload resident on this rank's GPU: inputs, rotating KV pools, workspace, plan and
+    the timed call.  ``mode``: "batch" (this rank's own batch), "strong" (its share of one batch
+    split by sequence), "kv-range" (its KV range of every sequence, packed partials exchanged)."""
 
-    import torch.distributed as dist
+    def __init__(self, args, workload: str, dev, rank: int, world: int, mode: str, seed: int = 0):
+        from single_gpu_inference_lab_b200 import cabi, l20_paged_split_kv, sharding
+        from single_gpu_inference_lab_b200.workloads import make_inputs
 
-    from single_gpu_inference_lab_b200 import cabi, l20_paged_split_kv, sharding
-    from single_gpu_inference_lab_b200.workloads import make_inputs
+        self.args, self.workload, self.dev, self.rank, self.world, self.mode = args, workload, dev, rank, world, mode
+        self.cabi = cabi
+        kv16 = {"fp8": None, "bf16": torch.bfloat16, "fp16": torch.float16}[args.kv_dtype]
+        self.kv16 = kv16
+        gen_kw = {} if kv16 is None else {"kv_dtype": kv16, "query_dtype": kv16}
+        if mode == "kv-range":
+            full_len = 131072
+            lo, hi = sharding.kv_range_bounds(full_len, rank, world)
+            w = make_inputs(workload, seed=seed + rank, device=dev, shrink=(hi - lo) / full_len)
+        elif mode == "strong":
+            full = make_inputs(workload, seed=seed, device=dev, **gen_kw)  # same batch on every rank
+            w, _rows = sharding.shard_sequences(full, rank, world)
+            del full
+            torch.cuda.empty_cache()
+        else:
+            w = make_inputs(workload, seed=seed, device=dev, **gen_kw)
+        self.w = w
+        q = w.query
+        self.batch, self.hq, self.d = q.shape
+        self.hkv = w.key_cache.shape[2]
+        self.kv_bytes = w.kv_bytes
+        self.split = args.split_size or l20_paged_split_kv.choose_split_size(
+            self.batch, self.hkv, w.max_seq_len, seq_lens=w.seq_lens.tolist())
+        self.pool_bytes = 2 * w.key_cache.numel() * w.key_cache.element_size()
+        pools = args.pools or max(2, -(-3 * L2_BYTES // self.pool_bytes) + 1)
+        self.pools = min(pools, max(2, int(40e9 // self.pool_bytes)))
+        self.kcs = [w.key_cache] + [w.key_cache.clone() for _ in range(self.pools - 1)]
+        self.vcs = [w.value_cache] + [w.value_cache.clone() for _ in range(self.pools - 1)]
+        self.shared_prefix = w.prefix_len > 0 and not args.no_shared_prefix and self.d == 128 and kv16 is None
+        if self.shared_prefix and not args.split_size:
+            self.split = 512
+        self.ws = l20_paged_split_kv.allocate_l20_paged_split_kv_workspace(q, w.max_seq_len, split_size=self.split)
+        if self.shared_prefix:
+            from single_gpu_inference_lab_b200 import l20_shared_prefix_decode_dispatch as spd
 
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    cabi.load()
+            self.spd = spd
+            self.ws = spd.allocate_shared_prefix_workspace(q, w.max_seq_len, w.prefix_len, suffix_split_size=self.split)
+        self.out = self.ws[3]
+        self.flags = args.flags
+        # The plan of the model step: block table and lengths are the same for every layer, so the
+        # work split is computed once, outside the timed layer-steps, as an engine does per step.
+        self.plan = None
+        if not args.no_plan and not self.shared_prefix and self.d == 128 and self.hq // self.hkv <= 8 and not (self.flags & (1 | 2 | 8)):
+            self.plan = cabi.plan_decode(q, w.key_cache, w.value_cache, w.block_table, w.seq_lens, max_seq_len=w.max_seq_len,
+                                         split_size=self.split, workspace=self.ws)
+            torch.cuda.synchronize()
+            if args.single_launch:
+                self.flags |= cabi.PFD_FLAG_SINGLE_LAUNCH
+        kvr = mode == "kv-range"
+        self.packed = torch.empty(self.batch, self.hq, self.d + 2, device=dev) if kvr else None
+        self.gathered = torch.empty(world, self.batch, self.hq, self.d + 2, device=dev) if kvr else None
+        self.filler = torch.zeros(1 << 14, device=dev)
 
-    kv16 = {"fp8": None, "bf16": torch.bfloat16, "fp16": torch.float16}[args.kv_dtype]
-    gen_kw = {} if kv16 is None else {"kv_dtype": kv16, "query_dtype": kv16}
-    kv_range_mode = args.workload == "llama3-8b-long-b4" and kv16 is None
-    # -------- inputs: every rank builds its own batch directly on its GPU
-    if kv_range_mode:
-        full_len = 131072
-        lo, hi = sharding.kv_range_bounds(full_len, rank, world)
-        w = make_inputs(args.workload, seed=rank, device=dev, shrink=(hi - lo) / full_len)
-        scaling = "strong"
-    elif args.strong and world > 1:
-        full = make_inputs(args.workload, seed=0, device=dev, **gen_kw)  # same batch on every rank
-        w, _rows = sharding.shard_sequences(full, rank, world)
-        del full
-        torch.cuda.empty_cache()
-        scaling = "strong"
-    else:
-        w = make_inputs(args.workload, seed=rank, device=dev, **gen_kw)
-        scaling = "weak"
-    q = w.query
-    batch, hq, d = q.shape
-    hkv = w.key_cache.shape[2]
-    kv_bytes = w.kv_bytes
-    split = args.split_size or l20_paged_split_kv.choose_split_size(
-        batch, hkv, w.max_seq_len, seq_lens=w.seq_lens.tolist())
-    pool_bytes = 2 * w.key_cache.numel()
-    pools = args.pools or max(2, -(-3 * L2_BYTES // pool_bytes) + 1)
-    pools = min(pools, max(2, int(40e9 // pool_bytes)))
-    kcs = [w.key_cache] + [w.key_cache.clone() for _ in range(pools - 1)]
-    vcs = [w.value_cache] + [w.value_cache.clone() for _ in range(pools - 1)]
-    shared_prefix = w.prefix_len > 0 and not args.no_shared_prefix and d == 128 and kv16 is None
-    if shared_prefix and not args.split_size:
-        split = 512
-    ws = l20_paged_split_kv.allocate_l20_paged_split_kv_workspace(q, w.max_seq_len, split_size=split)
-    if shared_prefix:
-        from single_gpu_inference_lab_b200 import l20_shared_prefix_decode_dispatch as spd
+    # -- the timed call
+    def step(self, i: int, flags=None, exchange: bool = True):
+        import torch.distributed as dist
 
-        ws = spd.allocate_shared_prefix_workspace(q, w.max_seq_len, w.prefix_len, suffix_split_size=split)
-    out = ws[3]
-    # The plan of the model step: block table and lengths are the same for every layer, so the
-    # work split is computed once, outside the timed layer-steps, as an engine does per step.
-    plan = None
-    if not args.no_plan and not shared_prefix and d == 128 and hq // hkv <= 8 and not (args.flags & (1 | 2 | 8)):
-        plan = cabi.plan_decode(q, w.key_cache, w.value_cache, w.block_table, w.seq_lens, max_seq_len=w.max_seq_len,
-                                split_size=split, workspace=ws)
-        torch.cuda.synchronize()
-        if args.single_launch:
-            args.flags |= cabi.PFD_FLAG_SINGLE_LAUNCH
-    packed = torch.empty(batch, hq, d + 2, device=dev) if kv_range_mode else None
-    gathered = torch.empty(world, batch, hq, d + 2, device=dev) if kv_range_mode else None
-
-    def step(i: int, flags: int = args.flags):
-        if kv16 is not None:
+        cabi, w = self.cabi, self.w
+        flags = self.flags if flags is None else flags
+        kc, vc = self.kcs[i % self.pools], self.vcs[i % self.pools]
+        if self.kv16 is not None:
             cabi.paged_decode_kv16_split_out(
-                q, kcs[i % pools], vcs[i % pools], w.block_table, w.seq_lens, max_seq_len=w.max_seq_len,
-                split_size=split, output=out, workspace=ws, flags=flags, plan=plan)
+                w.query, kc, vc, w.block_table, w.seq_lens, max_seq_len=w.max_seq_len,
+                split_size=self.split, output=self.out, workspace=self.ws, flags=flags, plan=self.plan)
             return
-        if shared_prefix:
+        if self.shared_prefix:
             cabi.shared_prefix_decode_fp8_e4m3(
-                q, kcs[i % pools], vcs[i % pools], w.block_table, w.seq_lens, prefix_len=w.prefix_len,
-                k_scale=w.k_scale, v_scale=w.v_scale, max_seq_len=w.max_seq_len, split_size=split, output=out,
-                workspace=ws)
+                w.query, kc, vc, w.block_table, w.seq_lens, prefix_len=w.prefix_len,
+                k_scale=w.k_scale, v_scale=w.v_scale, max_seq_len=w.max_seq_len, split_size=self.split, output=self.out,
+                workspace=self.ws)
             return
+        kvr = self.mode == "kv-range"
         cabi.paged_decode_fp8_e4m3_split_out(
-            q, kcs[i % pools], vcs[i % pools], w.block_table, w.seq_lens, k_scale=w.k_scale, v_scale=w.v_scale,
-            max_seq_len=w.max_seq_len, split_size=split, output=None if kv_range_mode else out,
-            packed_output=packed, workspace=ws, flags=flags, plan=plan,
+            w.query, kc, vc, w.block_table, w.seq_lens, k_scale=w.k_scale, v_scale=w.v_scale,
+            max_seq_len=w.max_seq_len, split_size=self.split, output=None if kvr else self.out,
+            packed_output=self.packed, workspace=self.ws, flags=flags, plan=self.plan,
         )
-        if kv_range_mode and not (flags & cabi.PFD_FLAG_PARTIAL_ONLY):
-            if world > 1:
-                dist.all_gather_into_tensor(gathered.view(-1, hq, d + 2), packed)
+        if kvr and exchange and not (flags & cabi.PFD_FLAG_PARTIAL_ONLY):
+            if self.world > 1:
+                dist.all_gather_into_tensor(self.gathered.view(-1, self.hq, self.d + 2), self.packed)
             else:
-                gathered[0].copy_(packed)
-            cabi.merge_packed(gathered, out)
+                self.gathered[0].copy_(self.packed)
+            cabi.merge_packed(self.gathered, self.out)
 
-    def barrier():
+    def exchange_only(self, i: int):
+        """KV-range mode: the exchange of the packed partials and the merge, without the kernel."""
+        import torch.distributed as dist
+
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.gathered.view(-1, self.hq, self.d + 2), self.packed)
+        else:
+            self.gathered[0].copy_(self.packed)
+        self.cabi.merge_packed(self.gathered, self.out)
+
+    def isolated_step(self, i: int):
+        """The step behind an unrelated ordinary kernel: no overlap with the previous step."""
+        self.filler.add_(1.0)
+        self.step(i)
+
+    # -- timing helpers (device time, CUDA events on the launching stream, max over ranks)
+    def barrier(self):
+        import torch.distributed as dist
+
         torch.cuda.synchronize()
-        if world > 1:
+        if self.world > 1:
             dist.barrier()
             torch.cuda.synchronize()
 
-    def timed(fn, steps: int) -> float:
-        """ms per step, CUDA events on the launching stream, max over ranks."""
-        barrier()
+    def _max_over_ranks(self, ms: float) -> float:
+        import torch.distributed as dist
+
+        t = torch.tensor([ms], device=self.dev)
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed_eager(self, fn, steps: int) -> float:
+        self.barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(steps):
             fn(i)
         e1.record()
-        barrier()
-        ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+        self.barrier()
+        return self._max_over_ranks(e0.elapsed_time(e1) / steps)
 
-    def timed_graph(fn, steps: int) -> float:
-        """Same, with the K steps replayed from CUDA graphs (a graph of `chunk` consecutive
-        steps replayed, plus one for the remainder) so that host launch overhead does not
-        pace the device: exactly `steps` steps run inside the timed region."""
-        if kv_range_mode and world > 1 and not args.graph_collective:
-            return timed(fn, steps)  # the collective is launched eagerly
-        chunk = min(steps, max(pools, (64 // pools) * pools))
+    def timed_graph(self, fn, steps: int, repeats: int = 1, collective: bool = False) -> tuple[float, list[float]]:
+        """ms per step with the K steps replayed from CUDA graphs (a graph of `chunk` consecutive
+        steps replayed, plus one for the remainder) so that host launch overhead does not pace
+        the device: exactly `steps` steps run inside each timed region.  Returns the median of
+        `repeats` such regions and all of them."""
+        if collective and self.world > 1 and not self.args.graph_collective:
+            runs = [self.timed_eager(fn, steps) for _ in range(repeats)]  # the collective is launched eagerly
+            return statistics.median(runs), runs
+        chunk = min(steps, max(self.pools, (64 // self.pools) * self.pools))
         reps, rest = divmod(steps, chunk)
         side = torch.cuda.Stream()
         graphs = []
@@ -362,19 +450,124 @@ def main() -> int:
                 graphs.append(g)
         torch.cuda.synchronize()
         graphs[0].replay()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            graphs[0].replay()
-        if graphs[1] is not None:
-            graphs[1].replay()
-        e1.record()
-        barrier()
-        ms = torch.tensor([e0.elapsed_time(e1) / steps], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+        runs = []
+        for _ in range(repeats):
+            self.barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                graphs[0].replay()
+            if graphs[1] is not None:
+                graphs[1].replay()
+            e1.record()
+            self.barrier()
+            runs.append(self._max_over_ranks(e0.elapsed_time(e1) / steps))
+        return statistics.median(runs), runs
+
+    def measure(self, steps: int, warmup: int, repeats: int, check: bool, isolated: bool = True) -> dict:
+        """Warm up, check the timed call against the oracle, then time step / kernel / isolated."""
+        cabi = self.cabi
+        kvr = self.mode == "kv-range"
+        for i in range(max(warmup, 3)):
+            self.step(i)
+        torch.cuda.synchronize()
+        res = {}
+        if check:
+            self.out.fill_(float("nan"))
+            self.step(0)
+            torch.cuda.synchronize()
+            res["status"] = cabi.device_status()
+            if kvr and self.world > 1:
+                res["correct"], res["max_abs_error"] = None, None
+                res["checked"] = "KV-range shards hold independent data; parity of this mode is tests/test_multi_gpu.py"
+            else:
+                ok, err, what = check_against_oracle(self.w, self.out)
+                res["correct"], res["max_abs_error"], res["checked"] = bool(ok and res["status"] == 0), err, what
+        before = cabi.launch_count()
+        self.step(0)
+        res["launches_per_step"] = cabi.launch_count() - before
+        res["path"] = cabi.last_path()
+        ms_step, runs = self.timed_graph(self.step, steps, repeats, collective=kvr)
+        res["ms_step"], res["runs_us"] = ms_step, [round(r * 1e3, 3) for r in runs]
+        single = self.shared_prefix or res["launches_per_step"] == 1
+        if single:
+            res["ms_kernel"] = ms_step
+        else:
+            res["ms_kernel"], _ = self.timed_graph(
+                lambda i: self.step(i, self.flags | cabi.PFD_FLAG_PARTIAL_ONLY, exchange=False), steps, 1)
+        if isolated:
+            res["ms_isolated"], _ = self.timed_graph(self.isolated_step, steps, 1, collective=kvr)
+            ms_fill, _ = self.timed_graph(lambda i: self.filler.add_(1.0), steps, 1)
+            res["ms_isolated"] = max(res["ms_isolated"] - ms_fill, 0.0)
+        if kvr:
+            res["ms_exchange"], _ = self.timed_graph(self.exchange_only, steps, 1, collective=True)
+        return res
+
+    def kernel_name(self, path: int) -> str:
+        if self.shared_prefix:
+            return "shared_prefix_dense_kernel + paged_decode_fp8_partial_tma_kernel + paged_decode_merge_kernel"
+        return KERNEL_NAMES.get(path, "?")
+
+    def release(self):
+        del self.kcs, self.vcs, self.ws, self.w
+        torch.cuda.empty_cache()
+
+
+def short_report(case: Case, res: dict, peak: float, world_bytes: float, world: int) -> dict:
+    """The per-configuration fields of ``per_config`` / ``sharded``."""
+    us = res["ms_step"] * 1e3
+    gbs = world_bytes / (res["ms_step"] * 1e-3) / 1e9
+    out = {
+        "us_per_layer_step": round(us, 3), "kv_read_gbs": round(gbs, 1),
+        "step_frac_of_hbm_peak": round(gbs / (peak * world), 4),
+        "kernel": case.kernel_name(res["path"]), "kernel_us": round(res["ms_kernel"] * 1e3, 3),
+        "kernel_frac_of_hbm_peak": round(case.kv_bytes / (res["ms_kernel"] * 1e-3) / 1e9 / peak, 4),
+        "path": case.cabi.PATH_NAMES.get(res["path"], "?"), "launches_per_step": res["launches_per_step"],
+        "kv_bytes_per_step_per_gpu": case.kv_bytes, "runs_us": res["runs_us"],
+    }
+    if "ms_isolated" in res:
+        out["isolated_us_per_layer_step"] = round(res["ms_isolated"] * 1e3, 3)
+    if "correct" in res:
+        out["correct"], out["max_abs_error"], out["checked"] = res["correct"], res["max_abs_error"], res["checked"]
+    if "ms_exchange" in res:
+        out["exchange_and_merge_us"] = round(res["ms_exchange"] * 1e3, 3)
+    return out
+
+
+def main() -> int:
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_world = int(os.environ.get("LOCAL_WORLD_SIZE", str(world)))
+    if args.impl == "reference":
+        return run_reference_arm(args, rank)
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the operator has no CPU path")
+    if world != args.gpus:
+        raise RuntimeError(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+
+    import torch.distributed as dist
+
+    from single_gpu_inference_lab_b200 import cabi, l20_paged_split_kv, sharding
+
+    cores = bind_to_own_cores(local_rank, local_world) if world > 1 else []
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cabi.load()
+    peak, peak_kind = measured_peak()
+
+    kv16 = args.kv_dtype != "fp8"
+    if args.workload == "llama3-8b-long-b4" and not kv16:
+        mode, scaling = "kv-range", "strong"
+    elif args.strong and world > 1:
+        mode, scaling = "strong", "strong"
+    else:
+        mode, scaling = "batch", "weak"
+    case = Case(args, args.workload, dev, rank, world, mode)
+    w, q = case.w, case.w.query
 
     # -------- e2e operands: the per-step inputs (q, block table, lengths) packed into ONE pinned host
     # buffer and copied with one transfer into a device buffer the operands are views of
@@ -398,115 +591,169 @@ def main() -> int:
     h2d = q_bytes + t_bytes + l_bytes
     d2h = host_out.numel() * host_out.element_size()
     stream = torch.cuda.current_stream()
+    split, pools, ws = case.split, case.pools, case.ws
 
     def e2e_step(i: int):
         dev_in.copy_(host_in, non_blocking=True)
-        if kv_range_mode:
+        kc, vc = case.kcs[i % pools], case.vcs[i % pools]
+        if mode == "kv-range":
             local = w.__class__(**{**w.__dict__, "query": dq, "block_table": dtable, "seq_lens": dlens,
-                                   "key_cache": kcs[i % pools], "value_cache": vcs[i % pools]})
+                                   "key_cache": kc, "value_cache": vc})
             if world > 1:
-                res = sharding.kv_range_decode(local, split_size=split, gather_buffer=gathered, workspace=ws, packed_buffer=packed)
+                res = sharding.kv_range_decode(local, split_size=split, gather_buffer=case.gathered, workspace=ws,
+                                               packed_buffer=case.packed)
             else:
                 res = l20_paged_split_kv.l20_paged_split_kv_attention_fp8(
-                    dq, kcs[i % pools], vcs[i % pools], dtable, dlens, k_scale=w.k_scale, v_scale=w.v_scale,
+                    dq, kc, vc, dtable, dlens, k_scale=w.k_scale, v_scale=w.v_scale,
                     max_seq_len=w.max_seq_len, split_size=split, workspace=ws)
-        elif kv16 is not None:
+        elif case.kv16 is not None:
             res = l20_paged_split_kv.l20_paged_split_kv_attention(
-                dq, kcs[i % pools], vcs[i % pools], dtable, dlens, split_size=split, workspace=ws,
-                max_seq_len=w.max_seq_len)
-        elif shared_prefix:
-            res = spd.shared_paged_prefix_paged_suffix_gqa_decode_attention_fp8(
-                dq, kcs[i % pools], vcs[i % pools], dtable, dlens, w.prefix_len, k_scale=w.k_scale, v_scale=w.v_scale,
+                dq, kc, vc, dtable, dlens, split_size=split, workspace=ws, max_seq_len=w.max_seq_len)
+        elif case.shared_prefix:
+            res = case.spd.shared_paged_prefix_paged_suffix_gqa_decode_attention_fp8(
+                dq, kc, vc, dtable, dlens, w.prefix_len, k_scale=w.k_scale, v_scale=w.v_scale,
                 max_seq_len=w.max_seq_len, suffix_split_size=split, workspace=ws)
         else:
             res = l20_paged_split_kv.l20_paged_split_kv_attention_fp8(
-                dq, kcs[i % pools], vcs[i % pools], dtable, dlens, k_scale=w.k_scale, v_scale=w.v_scale,
+                dq, kc, vc, dtable, dlens, k_scale=w.k_scale, v_scale=w.v_scale,
                 max_seq_len=w.max_seq_len, split_size=split, workspace=ws)
         host_out.copy_(res, non_blocking=True)
         stream.synchronize()  # the host consumes the step's result
 
-    # -------- warm-up, then the timed loops under clock sampling
-    for i in range(max(args.warmup, 3)):
-        step(i)
-    for i in range(3):
-        e2e_step(i)
+    # -------- the headline workload, under clock sampling
     with ClockSampler(local_rank) as clocks:
-        launches_before = cabi.launch_count()
-        step(0)
-        per_step = cabi.launch_count() - launches_before  # kernels of this library per step
-        ms_step = timed_graph(step, args.steps)
-        launches = per_step * args.steps                  # replayed from graphs inside the timed region
-        path = cabi.last_path()
-        fused = ((not kv_range_mode) and per_step == 1) or shared_prefix  # no single dominant kernel to time apart
-        kernel_name = {1: "paged_decode_fp8_partial_ldg_kernel", 2: "paged_decode_fp8_partial_tma_kernel",
-                       3: "paged_decode_fp8_chunk_kernel", 4: "paged_decode_fp8_chunk_kernel<KV16>",
-                       5: "paged_decode_fp8_chunk_kernel", 6: "paged_decode_fp8_chunk_kernel<KV16>"}.get(path, "?")
-        if shared_prefix:
-            kernel_name = "shared_prefix_dense_kernel + paged_decode_fp8_partial_tma_kernel + paged_decode_merge_kernel"
-        ms_kernel = timed_graph(step if fused else (lambda i: step(i, args.flags | cabi.PFD_FLAG_PARTIAL_ONLY)), args.steps)
-        ms_e2e = timed(e2e_step, args.steps)
-        ms_eager = timed(step, args.steps)
+        res = case.measure(args.steps, args.warmup, args.repeats, check=True)
+        for i in range(3):
+            e2e_step(i)
+        ms_e2e = case.timed_eager(e2e_step, args.steps)
+        ms_eager = case.timed_eager(case.step, args.steps)
 
-    # -------- aggregate over ranks
-    total_bytes = torch.tensor([float(kv_bytes)], device=dev, dtype=torch.float64)
+    total_bytes = torch.tensor([float(case.kv_bytes)], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(total_bytes)
     total_bytes = float(total_bytes.item())
-    peak, peak_kind = measured_peak()
+    ms_step, ms_kernel = res["ms_step"], res["ms_kernel"]
     value = total_bytes / (ms_step * 1e-3) / 1e9
     e2e_value = total_bytes / (ms_e2e * 1e-3) / 1e9
-    achieved = kv_bytes / (ms_kernel * 1e-3) / 1e9  # one GPU's kernel, one GPU's peak
+    achieved = case.kv_bytes / (ms_kernel * 1e-3) / 1e9  # one GPU's kernel, one GPU's peak
+    correct_all = torch.tensor([1.0 if res.get("correct") in (True, None) else 0.0], device=dev)
+    if world > 1:
+        dist.all_reduce(correct_all, op=dist.ReduceOp.MIN)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        rows = batch if not kv_range_mode else 1
-        repeats = 3 if kv_bytes < 5e8 else 1
+        rows = case.batch if mode != "kv-range" else 1
+        repeats = 3 if case.kv_bytes < 5e8 else 1
         gbs, secs, nbytes = cpu_reference_run(w, rows, repeats)
         cpu_baseline = {
             "value": round(gbs, 4), "unit": "GB/s", "cores": os.cpu_count(), "kind": "port",
-            "sample": f"{rows} of {batch} sequences, best of {repeats}, {secs * 1e3:.0f} ms per pass",
+            "sample": f"{rows} of {case.batch} sequences, best of {repeats}, {secs * 1e3:.0f} ms per pass",
         }
 
+    line = None
     if rank == 0:
+        kernel_name = case.kernel_name(res["path"])
+        short_kernel = kernel_name.split("<")[0] if res["path"] in KERNEL_NAMES else kernel_name
         line = {
             "metric": "decode_attn_kv_read_gbs", "value": round(value, 2), "unit": "GB/s",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "repeats": args.repeats,
             "ms_per_step": round(ms_step, 6), "us_per_layer_step": round(ms_step * 1e3, 3),
+            "runs_us_per_layer_step": res["runs_us"],
             "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-            "dtype": ("fp8_e4m3 KV, bf16 q, fp32 accumulate" if kv16 is None
+            "dtype": ("fp8_e4m3 KV, bf16 q, fp32 accumulate" if not kv16
                       else f"{args.kv_dtype} KV and q, fp32 accumulate"), "data": "synthetic",
+            "correct": bool(correct_all.item() > 0.5), "max_abs_error": res.get("max_abs_error"),
+            "checked": res.get("checked"),
             "config": {
-                "workload": args.workload, "batch_per_gpu": batch, "q_heads": hq, "kv_heads": hkv, "head_dim": d,
-                "page_size": 16, "split_size": split, "max_seq_len": w.max_seq_len, "path": cabi.PATH_NAMES.get(path, "?"),
-                "flags": args.flags,
+                "workload": args.workload, "batch_per_gpu": case.batch, "q_heads": case.hq, "kv_heads": case.hkv,
+                "head_dim": case.d, "page_size": 16, "split_size": split, "max_seq_len": w.max_seq_len,
+                "path": cabi.PATH_NAMES.get(res["path"], "?"), "flags": case.flags,
+                "plan": ("computed once per model step (pfd_plan_decode), outside the timed layer-steps"
+                         if case.plan is not None else "none"),
                 "metadata": ("block_table and seq_lens are not rewritten between the timed layer-steps "
-                             "(PFD_FLAG_EARLY_METADATA)") if args.flags & cabi.PFD_FLAG_EARLY_METADATA else "no promise",
-                "kv_bytes_per_step_per_gpu": kv_bytes,
+                             "(PFD_FLAG_EARLY_METADATA)") if case.flags & cabi.PFD_FLAG_EARLY_METADATA else "no promise",
+                "kv_bytes_per_step_per_gpu": case.kv_bytes,
                 **({"shared_prefix_tokens": w.prefix_len,
-                    "unique_kv_bytes_per_step": int(w.prefix_len + (w.seq_lens - w.prefix_len).sum().item()) * hkv * d * 2,
-                    "prefix_pass": "dense tcgen05 (TMEM accumulators), 128 rows x 256 tokens per CTA"} if shared_prefix else {}),
-                "parallelism": ("kv-range split + all-gather" if kv_range_mode else
-                                ("one batch sharded by sequence (token-balanced), no collective" if args.strong
-                                 else "one batch per GPU, no collective")) if world > 1 else "single GPU",
-                "l2": f"{pools} KV pools of {pool_bytes / 1e6:.0f} MB rotated ({pools * pool_bytes / 1e6:.0f} MB > L2): every step reads cold KV",
+                    "unique_kv_bytes_per_step": int(w.prefix_len + (w.seq_lens - w.prefix_len).sum().item()) * case.hkv * case.d * 2,
+                    "prefix_pass": "dense tcgen05 (TMEM accumulators), 128 rows x 256 tokens per CTA"} if case.shared_prefix else {}),
+                "parallelism": ("kv-range split, packed partials exchanged (all-gather), merged on every rank" if mode == "kv-range" else
+                                ("one batch sharded by sequence (token-balanced), no collective" if mode == "strong"
+                                 else "the same batch on every GPU, no collective")) if world > 1 else "single GPU",
+                "l2": f"{pools} KV pools of {case.pool_bytes / 1e6:.0f} MB rotated ({pools * case.pool_bytes / 1e6:.0f} MB > L2): every step reads cold KV",
+                **({"host_cores_per_rank": len(cores)} if cores else {}),
             },
             "pct_of_hbm_peak": round(100 * value / (peak * world), 2),
             "roofline": {
                 "bound": "hbm", "achieved": round(achieved, 2), "peak": peak, "unit": "GB/s",
                 "frac": round(achieved / peak, 4),
-                "traffic": None if (args.strong or kv_range_mode) else NCU_TRAFFIC_BYTES_PER_LAUNCH.get((args.workload, path)),
+                "traffic": None if mode != "batch" else ncu_traffic(args.workload, short_kernel),
                 "kernel": kernel_name, "us_per_launch": round(ms_kernel * 1e3, 3), "peak_source": peak_kind,
-                "algorithmic_bytes_per_launch": kv_bytes,
+                "algorithmic_bytes_per_launch": case.kv_bytes,
             },
+            "isolated": {"us_per_layer_step": round(res["ms_isolated"] * 1e3, 3),
+                         "what": "an unrelated ordinary kernel between steps (its own time subtracted): no overlap of a "
+                                 "step's prologue with the previous step's tail"},
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "us_per_layer_step": round(ms_e2e * 1e3, 3)},
-            "gpu_launches": int(launches),
-            "timing": "K steps replayed from CUDA graphs, CUDA events around the replays; eager launch loop beside it",
+            "gpu_launches": int(res["launches_per_step"] * args.steps),
+            "timing": "K steps replayed from CUDA graphs, CUDA events around the replays, median of `repeats` runs; eager launch loop beside it",
             "us_per_layer_step_eager_launch": round(ms_eager * 1e3, 3),
             "clocks": clocks.summary(),
         }
+        if "ms_exchange" in res:
+            line["exchange_and_merge_us"] = round(res["ms_exchange"] * 1e3, 3)
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
+    case.release()
+    del case
+
+    # -------- the other configurations (N = 1) / the two sharded forms (N > 1)
+    extra_steps = max(40, min(args.steps, 200))
+    if not args.no_per_config and not kv16 and args.workload == DEFAULT_WORKLOAD and mode == "batch":
+        if world == 1:
+            per_config = {}
+            for name in ALL_WORKLOADS:
+                if name == args.workload:
+                    continue
+                c = Case(args, name, dev, 0, 1, "kv-range" if name == "llama3-8b-long-b4" else "batch")
+                r = c.measure(extra_steps, 5, 3, check=True, isolated=name != "llama3-8b-long-b4")
+                per_config[name] = short_report(c, r, peak, c.kv_bytes, 1)
+                c.release()
+                del c
+            line["per_config"] = per_config
+        else:
+            sharded = {}
+            for name, smode in (("qwen2.5-7b-b256", "strong"), ("llama3-8b-long-b4", "kv-range")):
+                c = Case(args, name, dev, rank, world, smode)
+                r = c.measure(extra_steps, 5, 3, check=smode == "strong", isolated=False)
+                tb = torch.tensor([float(c.kv_bytes)], device=dev, dtype=torch.float64)
+                dist.all_reduce(tb)
+                ok = torch.tensor([1.0 if r.get("correct") in (True, None) else 0.0], device=dev)
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+                rep = short_report(c, r, peak, float(tb.item()), world) if rank == 0 else None
+                c.release()
+                del c
+                # the one-GPU figure of the same workload, measured in this run on rank 0 alone
+                one = None
+                if rank == 0:
+                    c1 = Case(args, name, dev, 0, 1, "kv-range" if smode == "kv-range" else "batch")
+                    r1 = c1.measure(extra_steps, 5, 1, check=False, isolated=False)
+                    one = r1["ms_step"] * 1e3
+                    c1.release()
+                    del c1
+                dist.barrier()
+                if rank == 0:
+                    if smode == "strong":
+                        rep["correct"] = bool(ok.item() > 0.5)
+                    rep["one_gpu_us_per_layer_step"] = round(one, 3)
+                    rep["speedup_over_one_gpu"] = round(one / rep["us_per_layer_step"], 3)
+                    rep["sharding"] = ("sequences split over the ranks by tokens (longest first), no communication"
+                                       if smode == "strong" else
+                                       "KV range of every sequence split over the ranks; packed (o, m, l) all-gathered, merged on every rank")
+                    sharded[name] = rep
+            if rank == 0:
+                line["sharded"] = sharded
+    if rank == 0:
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

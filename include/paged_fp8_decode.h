@@ -198,8 +198,12 @@ int64_t pfd_balanced_workspace_rows(int32_t num_q_heads, int32_t num_kv_heads);
  * library carries that array until the process exits.  Inputs and outputs are still the
  * caller's.  The call is refused with PFD_ERR_UNSUPPORTED when
  *   batch * num_q_heads * ceil((max_seq_len - kv_start) / split_size) * (head_dim + 2) * 4
- * exceeds the array (a larger split_size shrinks the need).  No cudaMalloc, cudaFree or other
- * allocating routine is called, on the first call or later.
+ * exceeds the array (a larger split_size shrinks the need; a request whose longest sequence fits
+ * one split writes its rows directly, touches no scratch and is never refused for size).  It
+ * always runs the fixed-split grid, so it takes a block table only (page_indptr is refused) and
+ * ignores `plan`; PFD_FLAG_PARTIAL_ONLY is refused, since the partials would stay inside the
+ * library.  No cudaMalloc, cudaFree or other allocating routine is called, on the first call or
+ * later.
  *
  * The first call on each device looks up the array's device address (cudaGetSymbolAddress)
  * with the caller's current device, which must be the device of `args->stream`; make that

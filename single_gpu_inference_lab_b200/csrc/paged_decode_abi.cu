@@ -315,6 +315,8 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
   {
     // Few rows mean few, long sequences whose pieces are many: four warps then share a row,
     // which also puts more loads in flight per SM.  Either way 64 registers, 8 CTAs per SM.
+    // (CTAs of a single warp and row, all resident beside the chunk kernel, were measured
+    // slower: 21.8 against 19.9 us per step on the batch-64 configuration.)
     const int rows = a.batch * a.num_q_heads;
     const bool wide = rows <= 8 * sms;
     cudaLaunchConfig_t cfg{};
@@ -746,16 +748,33 @@ int pfd_paged_decode_fp8_e4m3_split_out_noalloc(const pfd_decode_args* args) {
   if (a.batch < 0 || a.num_q_heads <= 0 || a.head_dim <= 0 || a.split_size < 16 || a.kv_start < 0 ||
       a.max_seq_len < 0)
     return fail(PFD_ERR_INVALID, "invalid geometry");
+  if (a.page_indptr != nullptr)
+    return fail(PFD_ERR_UNSUPPORTED,
+                "the allocation-free entry point takes a block table: page_indptr addressing needs the balanced "
+                "kernel, which this entry point never runs");
+  if (a.flags & PFD_FLAG_PARTIAL_ONLY)
+    return fail(PFD_ERR_UNSUPPORTED,
+                "PFD_FLAG_PARTIAL_ONLY makes no sense here: the partials would stay in the library's own array");
+  a.plan = nullptr;
   const int64_t span = a.max_seq_len > a.kv_start ? a.max_seq_len - a.kv_start : 0;
   int64_t splits = (span + a.split_size - 1) / a.split_size;
   if (splits < 1) splits = 1;
   const int64_t rows = (int64_t)a.batch * a.num_q_heads * splits;
   const int64_t need = rows * (a.head_dim + 2) * (int64_t)sizeof(float);
-  if (need > (int64_t)PFD_NOALLOC_SCRATCH_BYTES)
+  // With a single split every work item writes its final rows itself and the array is not touched.
+  const bool touches_scratch = splits > 1 || (a.flags & PFD_FLAG_NO_DIRECT_OUT);
+  if (touches_scratch && need > (int64_t)PFD_NOALLOC_SCRATCH_BYTES)
     return fail(PFD_ERR_UNSUPPORTED,
                 "request needs %lld bytes of split-KV scratch but the built-in array holds %u; "
                 "raise split_size or use the entry point that takes a workspace",
                 (long long)need, PFD_NOALLOC_SCRATCH_BYTES);
+  if (!touches_scratch) {  // no partials: run as the ordinary entry point does without a workspace
+    a.partial_output = nullptr;
+    a.partial_max = a.partial_sum = nullptr;
+    a.workspace_splits = 0;
+    a.flags |= PFD_FLAG_FIXED_SPLITS;
+    return pfd_paged_decode_fp8_e4m3_split_out(&a);
+  }
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));

@@ -35,15 +35,14 @@ struct ChunkParams {
   int32_t* plan;       // device plan written by plan_decode_kernel, or nullptr
 };
 
-// How the work is cut.  Cost is counted in pages: sequence b owns the cost range that starts at
-// 2 * (pairs before b) + piece_cost * b, first piece_cost units for taking the sequence up
-// (query fetch, state reset, output rows), then one unit per page, two per page pair (the
-// second unit of a last pair that holds a single page stands for nothing).  The cost axis is
-// cut into `groups` contiguous chunks whose lengths differ by at most one unit, and a page
-// belongs to the chunk that holds its unit: a chunk boundary may fall between the two pages of a
-// pair, which then both neighbours step through, each loading and attending its own page only.
-// Tiny workloads use fewer groups so that no chunk is shorter than kMinChunkCost units (a chunk
-// inside a sequence is never empty).
+// How the work is cut.  Cost is counted in half page pairs: sequence b owns the cost range that
+// starts at 2 * (pairs before b) + piece_cost * b, first piece_cost units for taking the
+// sequence up (query fetch, state reset, output rows), then two units per page pair.  The cost
+// axis is cut into `groups` contiguous chunks whose lengths differ by at most one unit, and a
+// page pair belongs to the chunk that holds its first unit.  Tiny workloads use fewer groups so
+// that no chunk is shorter than kMinChunkCost units (a chunk inside a sequence is never empty).
+// (Cutting at page granularity, a pair shared by two chunks that each attend one of its pages,
+// balances bytes better but was measured slower: the shared pairs cost both chunks a step.)
 constexpr int kMinChunkCost = 8;
 struct Chunking {
   int base, rem, groups, piece_cost;
@@ -70,11 +69,6 @@ struct Chunking {
 __device__ __forceinline__ int pairs_of(int len, int kv_start) {
   const int pages = len > kv_start ? (len + kPage - 1) / kPage - kv_start / kPage : 0;
   return (pages + 1) >> 1;
-}
-
-// Pages of such a sequence (its cost units that stand for data).
-__device__ __forceinline__ int pages_of(int len, int kv_start) {
-  return len > kv_start ? (len + kPage - 1) / kPage - kv_start / kPage : 0;
 }
 
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
@@ -467,7 +461,7 @@ __device__ __forceinline__ int64_t chunk_slot_row(int grp, int which, int num_q_
 //   [0, 16)            header (kPlan* indices below)
 //   [16, 16 + B + 1)   pairs before sequence b
 //   [.., + B)          sequence lengths
-//   groups_off         per group kPlanGroupWords words: P0, P1, split flags, 1 reserved, 32 page ids
+//   groups_off         per group kPlanGroupWords words: P0, P1, 2 reserved, 32 page ids
 //   counters_off       B * Hkv arrival counters (page pairs consumed), zero between launches
 constexpr int kPlanMagic = 0x70666431;
 constexpr int kPlanHeaderWords = 16;
@@ -499,47 +493,38 @@ struct PairList {
     }
     return lo_b;
   }
-  // The chunk boundary at cost position c: returns the pairs whose first unit lies before c;
-  // *split is set when the last of them has its second page at c, i.e. the boundary falls inside
-  // that pair (its second page belongs to the chunk that starts at c).
-  __device__ __forceinline__ int boundary(const Chunking& chunks, int c, bool* split) const {
+  // Pairs whose first cost unit lies before cost position c.
+  __device__ __forceinline__ int pairs_before(const Chunking& chunks, int c) const {
     const int total = prefix[B];
-    *split = false;
     if (c >= 2 * total + chunks.piece_cost * B) return total;
     int lo_b = 0, hi_b = B;  // largest b whose cost range starts at or before c
     while (hi_b - lo_b > 1) {
       const int mid = (lo_b + hi_b) >> 1;
       if (2 * prefix[mid] + chunks.piece_cost * mid <= c) lo_b = mid; else hi_b = mid;
     }
-    const int off = c - chunks.first_unit(prefix[lo_b], lo_b);  // units into the pages of lo_b
-    *split = off > 0 && (off & 1) && off < pages_of(lens[lo_b], kv_start);
+    const int off = c - chunks.first_unit(prefix[lo_b], lo_b);  // units into the pairs of lo_b
     return prefix[lo_b] + min(max((off + 1) >> 1, 0), prefix[lo_b + 1] - prefix[lo_b]);
   }
 };
 
-// The pairs a chunk steps through, [P0, P1) of the flattened pair list, and whether its first
-// (last) pair is shared with the chunk in front (behind): then only the pair's second (first)
-// page is this chunk's.
+// The pairs a chunk steps through: [P0, P1) of the flattened pair list.
 struct ChunkRange {
   int P0, P1;
-  bool head_split, tail_split;
 };
 __device__ __forceinline__ ChunkRange chunk_range(const PairList& list, const Chunking& chunks, int grp) {
   ChunkRange r;
   const int total = list.prefix[list.B];
   if (grp >= chunks.groups) {
     r.P0 = r.P1 = total;
-    r.head_split = r.tail_split = false;
     return r;
   }
-  const int before = list.boundary(chunks, chunks.start_of(grp), &r.head_split);
-  r.P0 = before - (r.head_split ? 1 : 0);
-  r.P1 = list.boundary(chunks, chunks.start_of(grp + 1), &r.tail_split);
+  r.P0 = list.pairs_before(chunks, chunks.start_of(grp));
+  r.P1 = list.pairs_before(chunks, chunks.start_of(grp + 1));
   return r;
 }
 
 // Page ids of 16 consecutive pairs of a chunk, one page per lane (lane 2t + u holds page u of
-// pair P0 + base_t + t, -1 if there is none or it is the neighbouring chunk's).
+// pair P0 + base_t + t, -1 if there is none).
 __device__ __forceinline__ int32_t fetch_ids(const PairList& list, const KernelParams& p, const ChunkRange& cr,
                                              int base_t, int lane) {
   int32_t phys = -1;
@@ -547,8 +532,7 @@ __device__ __forceinline__ int32_t fetch_ids(const PairList& list, const KernelP
   if (g < cr.P1) {
     const int b = list.seq_of(g);
     const int page = list.page_first + 2 * (g - list.prefix[b]) + (lane & 1);
-    const bool theirs = (cr.head_split && g == cr.P0 && !(lane & 1)) || (cr.tail_split && g == cr.P1 - 1 && (lane & 1));
-    if (!theirs && page <= (list.lens[b] - 1) / kPage)
+    if (page <= (list.lens[b] - 1) / kPage)
       phys = p.page_indptr ? __ldg(p.block_table + __ldg(p.page_indptr + b) + page)
                            : page_of(p.block_table, p.bt_stride_b, b, page);
   }
@@ -649,7 +633,7 @@ __global__ void __launch_bounds__(1024) plan_decode_kernel(const PlanParams pp) 
     const ChunkRange cr = chunk_range(list, chunks, grp);
     const int32_t id = fetch_ids(list, kp, cr, 0, lane);
     int32_t* gw = plan + plan_groups_off(B) + (int64_t)grp * kPlanGroupWords;
-    if (lane == 0) { gw[0] = cr.P0; gw[1] = cr.P1; gw[2] = (cr.head_split ? 1 : 0) | (cr.tail_split ? 2 : 0); gw[3] = 0; }
+    if (lane == 0) { gw[0] = cr.P0; gw[1] = cr.P1; gw[2] = 0; gw[3] = 0; }
     gw[4 + lane] = id;
   }
 }
@@ -855,16 +839,14 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
     const int32_t* gw = cp.plan + plan_groups_off(B) + (int64_t)min(grp, num_groups - 1) * kPlanGroupWords;
     const int4 h0 = __ldg(reinterpret_cast<const int4*>(cp.plan));      // magic, batch, kv_start, kv heads
     const int4 h1 = __ldg(reinterpret_cast<const int4*>(cp.plan) + 1);  // groups, piece cost, total, indptr
-    const int4 g0 = __ldg(reinterpret_cast<const int4*>(gw));  // P0, P1, split flags, -
+    const int2 g0 = __ldg(reinterpret_cast<const int2*>(gw));  // P0, P1
     cr.P0 = g0.x;
     cr.P1 = g0.y;
-    cr.head_split = (g0.z & 1) != 0;
-    cr.tail_split = (g0.z & 2) != 0;
     ids_cur = __ldg(gw + 4 + lane);
     plan_ok = h0.x == kPlanMagic && h0.y == B && h0.z == p.kv_start && h0.w == hkv && h1.x == num_groups &&
               h1.y == cp.piece_cost && h1.w == (p.page_indptr != nullptr ? 1 : 0);
     total = h1.z;
-    if (grp >= num_groups || !plan_ok) { cr.P0 = cr.P1 = total; cr.head_split = cr.tail_split = false; ids_cur = -1; }
+    if (grp >= num_groups || !plan_ok) { cr.P0 = cr.P1 = total; ids_cur = -1; }
     // prefix sum and lengths into shared memory; used only after the barrier further down
     for (int x = threadIdx.x; x < 2 * B + 1; x += NT) prefix[x] = __ldg(cp.plan + kPlanHeaderWords + x);
   } else {
@@ -887,8 +869,8 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
     if (lane == 0) {
       const uint32_t bar = my_bars + 8 * (t % NSTAGE);
       const uint32_t dst = my_ring + (t % NSTAGE) * kStage;
-      const bool has0 = phys0 >= 0, has1 = phys1 >= 0;  // a page of a shared pair may be the neighbour's
-      mbar_expect_tx(bar, ((has0 ? 1 : 0) + (has1 ? 1 : 0)) * (kStage / 2));
+      const bool two = phys1 >= 0;
+      mbar_expect_tx(bar, two ? kStage : kStage / 2);
       const int c1 = tp.head_is_dim1 ? kvh : 0;
       const int c2 = tp.head_is_dim1 ? 0 : kvh;
       const uint64_t pol = l2_policy_evict_first();
@@ -906,11 +888,9 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
           else tma_load_tile(to, map, bar, c1, c2, phys);
         }
       };
-      if (has0) {
-        load(dst, &tmap_k, phys0);
-        load(dst + 2 * kTile, &tmap_v, phys0);
-      }
-      if (has1) {
+      load(dst, &tmap_k, phys0);
+      load(dst + 2 * kTile, &tmap_v, phys0);
+      if (two) {
         load(dst + kTile, &tmap_k, phys1);
         load(dst + 3 * kTile, &tmap_v, phys1);
       }
@@ -985,9 +965,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       load_q(qn, nxt.b);
     }
     const int seq_len = lens[cur.b];
-    // every page of the sequence is this chunk's: no piece, the final rows are written here
-    const bool whole = cur.start >= P0 && cur.start + cur.np <= P1 && !(cr.head_split && cur.start == P0) &&
-                       !(cr.tail_split && cur.start + cur.np == P1);
+    const bool whole = cur.start >= P0 && cur.start + cur.np <= P1;
     bal_reset<1>(st);
 #pragma unroll 1
     for (; g < e; ++g, ++t) {
@@ -996,12 +974,8 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       if (t == 0) mark_phase_at(tp, W, 3, lane == 0);  // first data landed
       if (t == n / 2) mark_phase_at(tp, W, 6, lane == 0);  // half of the chunk consumed
       const int tok0 = (page_first + 2 * (g - cur.start)) * kPage;
-      // tokens attended in this step: the sequence's, minus the page of a shared pair that is the
-      // neighbouring chunk's (not loaded: whatever the stage holds there is masked like a tail)
-      const int lo = (cr.head_split && g == P0) ? max(p.kv_start, tok0 + kPage) : p.kv_start;
-      const int hi = (cr.tail_split && g == P1 - 1) ? min(seq_len, tok0 + kPage) : seq_len;
-      if constexpr (KV16) kv16_step<QBF16>(st, my_ring + s * kStage, qb, scale_log2, tok0, lo, hi, lane);
-      else bal_step<1>(st, my_ring + s * kStage, k_off, v_off, qb, scale_log2, tok0, lo, hi, i, j);
+      if constexpr (KV16) kv16_step<QBF16>(st, my_ring + s * kStage, qb, scale_log2, tok0, p.kv_start, seq_len, lane);
+      else bal_step<1>(st, my_ring + s * kStage, k_off, v_off, qb, scale_log2, tok0, p.kv_start, seq_len, i, j);
       // all reads of the stage fed MMAs above: hand it back to TMA for the chunk's pair t + NSTAGE
       __syncwarp();
       const int tn = t + NSTAGE;
@@ -1092,17 +1066,14 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       }
     }
     if constexpr (FUSED) if (!whole) {
-      // Publish the piece, then count this warp's pages of the sequence in: the warp that
+      // Publish the piece, then count this warp's pairs of the sequence in: the warp that
       // completes the count finds every other piece in L2 and writes the final rows.
       __threadfence();
       __syncwarp();
-      const int seq_pages = pages_of(seq_len, p.kv_start);
-      const int page_a = 2 * (piece_first - cur.start) + ((cr.head_split && piece_first == P0) ? 1 : 0);
-      const int page_e = min(2 * (e - cur.start), seq_pages) - ((cr.tail_split && e == P1) ? 1 : 0);
-      const int mine = page_e - page_a;
+      const int mine = e - piece_first;
       int32_t* counter = cp.plan + plan_counters_off(B, num_groups) + (int64_t)cur.b * hkv + kvh;
 #ifdef PFD_BOUNDS_CHECK
-      if (cur.b < 0 || cur.b >= B || mine <= 0 || mine > seq_pages) {
+      if (cur.b < 0 || cur.b >= B || mine <= 0 || mine > cur.np) {
         mark_value_at(tp, 2 * cp.num_warps + 3, 0, lane == 0, ((unsigned long long)(unsigned)cur.b << 32) | (unsigned)mine);
         mark_value_at(tp, 2 * cp.num_warps + 3, 1, lane == 0, ((unsigned long long)(unsigned)cur.np << 32) | (unsigned)W);
       }
@@ -1110,7 +1081,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
       int before = 0;
       if (lane == 0) before = atomicAdd(counter, mine);
       before = __shfl_sync(0xffffffffu, before, 0);
-      if (before + mine == seq_pages) {
+      if (before + mine == cur.np) {
         __threadfence();
         mark_phase_at(tp, cp.num_warps + W, 0, lane == 0);  // merge begins
         MergeJob job;
@@ -1125,7 +1096,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
         job.hq0 = kvh * p.group;
         job.group = p.group;
         job.w_first = chunks.chunk_of(s0);
-        job.ns = chunks.chunk_of(s0 + seq_pages - 1) - job.w_first + 1;
+        job.ns = chunks.chunk_of(s0 + 2 * (cur.np - 1)) - job.w_first + 1;
         job.which0 = s0 > chunks.start_of(job.w_first) ? 1 : 0;
         job.b = cur.b;
 #ifdef PFD_BOUNDS_CHECK
@@ -1167,21 +1138,25 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
   pdl_launch_dependents();
   mark_phase_at(tp, cp.num_warps + blockIdx.x, 5, threadIdx.x == 0);  // merge CTA resident
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int row = WPR == 1 ? blockIdx.x * 4 + warp : blockIdx.x;
+  const int row = WPR == 1 ? blockIdx.x * (blockDim.x >> 5) + warp : blockIdx.x;  // WPR == 1: one row per warp of the CTA
   const int part = WPR == 1 ? 0 : warp;
-  // Every exit path waits for the chunk kernel first: a dependent grid that completed early would
-  // let the next kernel of the stream start while the chunk kernel is still writing.
-  if (row >= cp.batch * p.num_q_heads) { pdl_wait(); return; }  // WPR == 1 only: whole warps, no barrier below
+  // This grid must not complete before the chunk kernel has (the next kernel of the stream would
+  // start while the chunk kernel is still writing): CTAs with nothing to do leave at once, which
+  // frees their slots for the rows that have, but the last CTA of the grid always waits.
+  const bool keeper = blockIdx.x == gridDim.x - 1;
+  if (row >= cp.batch * p.num_q_heads) {  // WPR == 1 only: whole warps, no barrier below
+    if (keeper) pdl_wait();
+    return;
+  }
   const int b = row / p.num_q_heads, hq = row % p.num_q_heads;
   // seq_lens is an input of the whole step, not a result of the chunk kernel: the chunking is
   // read from the plan, or recomputed here, while that kernel is still running.
-  int below = 0, all = 0, np = 0, seq_pages = 0;
+  int below = 0, all = 0, np = 0;
   if (cp.plan != nullptr) {
     const int32_t* pre = cp.plan + kPlanHeaderWords;
     below = __ldg(pre + b);
     np = __ldg(pre + b + 1) - below;
     all = __ldg(pre + cp.batch);
-    seq_pages = pages_of(__ldg(pre + cp.batch + 1 + b), p.kv_start);
   } else {
     for (int x = lane; x < cp.batch; x += 32) {
       const int n = pairs_of(__ldg(p.seq_lens + x), p.kv_start);
@@ -1193,15 +1168,16 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
       all += __shfl_xor_sync(0xffffffffu, all, off);
       below += __shfl_xor_sync(0xffffffffu, below, off);
     }
-    const int len = __ldg(p.seq_lens + b);
-    np = pairs_of(len, p.kv_start);
-    seq_pages = pages_of(len, p.kv_start);
+    np = pairs_of(__ldg(p.seq_lens + b), p.kv_start);
   }
   const Chunking chunks(all, cp.batch, max(cp.num_warps / p.num_kv_heads, 1), cp.piece_cost);
   const int s0 = chunks.first_unit(below, b);
   const int w_first = np > 0 ? chunks.chunk_of(s0) : 0;
-  const int ns = np > 0 ? chunks.chunk_of(s0 + seq_pages - 1) - w_first + 1 : 0;
-  if (ns == 1) { pdl_wait(); return; }  // written by the chunk kernel (the whole CTA returns: one row per CTA if WPR == 4)
+  const int ns = np > 0 ? chunks.chunk_of(s0 + 2 * (np - 1)) - w_first + 1 : 0;
+  if (ns == 1) {  // written by the chunk kernel (the whole CTA returns: one row per CTA if WPR == 4)
+    if (keeper) pdl_wait();
+    return;
+  }
   float acc[E] = {0.f, 0.f, 0.f, 0.f};
   float big = -INFINITY, den = 0.f;
   // pieces k0, k0 + WPR, ... (K of them) in one round trip, folded into (acc, big, den)

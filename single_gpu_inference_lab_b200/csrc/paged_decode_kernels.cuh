@@ -548,11 +548,14 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   return t;
 }
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, unsigned long long limit_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // the common case costs nothing but polls: the clock is first read after 64 of them
+#pragma unroll 1
+  for (int k = 0; k < 64; ++k)
+    if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_timer_ns();
   for (uint32_t round = 0; round < kSpinLimit; ++round) {
 #pragma unroll 1
-    for (int k = 0; k < 8; ++k)
+    for (int k = 0; k < 32; ++k)
       if (mbar_try_wait(bar, parity)) return true;
     if (global_timer_ns() - t0 > limit_ns) return false;
   }
@@ -885,9 +888,14 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
   const int row = WPR == 1 ? blockIdx.x * 4 + warp : blockIdx.x;
   const int part = WPR == 1 ? 0 : warp;
   const int lane = threadIdx.x & 31;
-  // Every exit path waits for the partial kernel first: a dependent grid that completed early
-  // would let the next kernel of the stream start while the partial kernel is still writing.
-  if (row >= batch * p.num_q_heads) { pdl_wait(); return; }  // WPR == 1 only: whole warps, no barrier below
+  // This grid must not complete before the partial kernel has (the next kernel of the stream
+  // would start while the partial kernel is still writing): warps with nothing to do leave at
+  // once, but the last CTA of the grid always waits.
+  const bool keeper = blockIdx.x == gridDim.x - 1;
+  if (row >= batch * p.num_q_heads) {  // WPR == 1 only: whole warps, no barrier below
+    if (keeper) pdl_wait();
+    return;
+  }
   const int b = row / p.num_q_heads, hq = row % p.num_q_heads;
   const int seq_len = p.seq_lens[b];
   const int live = seq_len - p.kv_start;
@@ -897,8 +905,11 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
 #pragma unroll
   for (int e = 0; e < E; ++e) acc[e] = 0.f;
   float big = -INFINITY, den = 0.f;
+  if (ns == 1 && p.direct_out) {  // written by the partial kernel (with WPR == 4 the whole CTA returns)
+    if (keeper) pdl_wait();
+    return;
+  }
   pdl_wait();  // the partial kernel's stores are complete and visible from here on
-  if (ns == 1 && p.direct_out) return;  // written by the partial kernel (with WPR == 4 the whole CTA returns)
   if (ns > 0) {
     const int64_t base = (int64_t)b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h;
     // One pass with a running maximum; eight splits per round trip, their maxima, sums and data

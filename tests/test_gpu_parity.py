@@ -436,6 +436,20 @@ def test_linearity_in_v_scale_and_scale_folding(cabi):
     assert torch.equal((a.float() * 2).to(torch.bfloat16).view(torch.int16), b.view(torch.int16))
 
 
+def test_a_wait_that_nothing_satisfies_runs_out_and_sets_the_status_word(cabi):
+    """Every device-side wait is bounded in time.  The self-test kernel arms a barrier for bytes
+    that no copy delivers: the wait gives up after the limit, the kernel finishes, the error word
+    reads 1 once and then 0 again, and the next decode call runs as usual."""
+    assert cabi.device_status() == 0
+    for limit_ns in (200_000, 3_000_000):
+        waited = cabi.selftest_bounded_wait(limit_ns)
+        assert limit_ns <= waited < limit_ns + 2_000_000, (limit_ns, waited)
+        assert cabi.device_status() == 1
+        assert cabi.device_status() == 0
+    w = make_inputs("qwen2.5-coder-3b-b64", seed=12, batch=4, shrink=0.25)
+    assert_within_gate(run(cabi, w.to(DEV), 128), expected(w), "decode after an expired wait")
+
+
 # ---------------------------------------------------------------- dispatcher op (torch.ops) surface
 def test_torch_op_reference_signature_and_wrapper_module(built_libs, golden):
     from single_gpu_inference_lab_b200 import l20_paged_decode, l20_paged_split_kv
