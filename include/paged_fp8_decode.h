@@ -80,6 +80,37 @@ extern "C" {
  * clipped to [0, seq_lens[b]).  partial_max is in natural-log units, partial_output is the
  * un-normalised sum of p*v (v already scaled), as in the reference kernels.
  */
+/*
+ * KV-range exchange between the GPUs of one node (no counterpart in the reference, which is
+ * single-GPU).  Every rank holds a KV range of every sequence; its decode call yields packed
+ * (o, m, l) rows for that range, which every rank needs for the final merge.  With `exchange`
+ * set in pfd_decode_args the kernels that finish those rows store them straight into slot
+ * `rank` of EVERY rank's receive buffer (plain stores through peer mappings over NVLink), and
+ * the warp that stores the step's last row releases the step's flag in every rank's flag array.
+ * pfd_exchange_merge() then waits (bounded) for the `world` flags in this rank's own array and
+ * merges this rank's own receive buffer: no collective call, no remote load.
+ *
+ *   recv[p]   rank p's receive buffer, f32 [2][world][batch * num_q_heads][head_dim + 2], as
+ *             mapped in THIS process (recv[rank] is local memory, the others peer memory)
+ *   flags[p]  rank p's flag words, int32 [2][world], zero before the first step
+ *   step      tag of this call: positive, increasing by one per call on every rank alike; its
+ *             lowest bit selects the half of the buffers, so that a rank one step ahead never
+ *             overwrites what a slower rank still merges
+ *   row_counter  one local int32, zero between calls
+ * Allocate with pfd_exchange_alloc() / map the peers' with pfd_exchange_open() (or any other way
+ * that yields peer-accessible device memory).  Needs the balanced kernel + merge kernel (head_dim
+ * 128, FP8 caches, at most 8 query heads per kv head, no PFD_FLAG_SINGLE_LAUNCH / FIXED_SPLITS);
+ * other calls are refused.  world <= 8.
+ */
+typedef struct pfd_exchange {
+  int32_t world, rank;
+  int32_t step;
+  int32_t reserved;
+  float* recv[8];
+  int32_t* flags[8];
+  int32_t* row_counter;
+} pfd_exchange;
+
 typedef struct pfd_decode_args {
   uint32_t struct_size; /* sizeof(pfd_decode_args): lets the library reject a stale caller */
   uint32_t flags;
@@ -137,6 +168,10 @@ typedef struct pfd_decode_args {
    * read their work split from it (and PFD_FLAG_SINGLE_LAUNCH becomes available).  NULL, or a
    * call that does not run the balanced kernel: ignored. */
   void* plan;
+
+  /* Optional: push the packed (o, m, l) rows of this call to every rank (see pfd_exchange).
+   * packed_output and output are then ignored; the result comes from pfd_exchange_merge(). */
+  const pfd_exchange* exchange;
 } pfd_decode_args;
 
 /*
@@ -245,6 +280,32 @@ int pfd_merge_packed(const float* packed, int32_t num_parts, int64_t rows, int32
                      void* output, int32_t out_dtype, void* stream);
 
 /*
+ * Receiving side of a KV-range exchange step: one kernel on `stream` (enqueue it behind the decode
+ * call of the same step) that waits until all `world` ranks have released the step's flag in this
+ * rank's flag array -- at most the wait limit (pfd_set_wait_limit_ns); on expiry device status 3
+ * is set, nothing is merged and the kernel ends -- and then LSE-merges the `world` packed partials
+ * of every row from this rank's receive buffer into output [rows, head_dim] of `out_dtype`.
+ * Same maths as pfd_merge_packed.
+ */
+int pfd_exchange_merge(const pfd_exchange* exchange, int64_t rows, int32_t head_dim, void* output,
+                       int32_t out_dtype, void* stream);
+
+/*
+ * Memory for one rank's side of the exchange: cudaMalloc of `bytes` (zero-filled), with the
+ * 64-byte CUDA IPC handle that the other ranks' processes turn into a peer mapping with
+ * pfd_exchange_open().  pfd_exchange_bytes() is what recv + flags + row counter of one rank need;
+ * the flags start at pfd_exchange_flags_offset() bytes, the row counter 256 bytes behind them.
+ * These four allocate / map / free device memory (the decode entry points never do).
+ */
+typedef struct pfd_ipc_handle { unsigned char bytes[64]; } pfd_ipc_handle;
+int64_t pfd_exchange_bytes(int32_t world, int64_t rows, int32_t head_dim);
+int64_t pfd_exchange_flags_offset(int32_t world, int64_t rows, int32_t head_dim);
+int pfd_exchange_alloc(int64_t bytes, void** ptr, pfd_ipc_handle* handle);
+int pfd_exchange_open(const pfd_ipc_handle* handle, void** peer_ptr);
+int pfd_exchange_close(void* peer_ptr);
+int pfd_exchange_free(void* ptr);
+
+/*
  * Debug / parity entry: writes, for every (sequence, token < max_seq_len), the cache slot
  * index page*16 + token%16 that the kernels' address function resolves (-1 beyond the
  * sequence) into slots[batch, max_seq_len] (int64).  Counterpart of the gather
@@ -257,7 +318,8 @@ int pfd_resolve_slots(const int32_t* block_table, int64_t bt_stride_b, const int
 /*
  * Synchronises with the current device and reads (then clears) the error word the kernels set
  * when a bounded wait gave up: 0 = none, 1 = a TMA copy did not complete in time (the step's
- * output is then undefined), 2 = args->plan was made for other inputs (nothing was written).
+ * output is then undefined), 2 = args->plan was made for other inputs (nothing was written),
+ * 3 = a rank's flag of a KV-range exchange step did not arrive in time (nothing was merged).
  * The kernels never trap and never spin without a limit.
  */
 int pfd_device_status(int32_t* status);

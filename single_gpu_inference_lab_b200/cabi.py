@@ -33,6 +33,13 @@ EXPORTS = (
     "pfd_balanced_workspace_rows",
     "pfd_plan_bytes",
     "pfd_plan_decode",
+    "pfd_exchange_merge",
+    "pfd_exchange_bytes",
+    "pfd_exchange_flags_offset",
+    "pfd_exchange_alloc",
+    "pfd_exchange_open",
+    "pfd_exchange_close",
+    "pfd_exchange_free",
     "pfd_device_status",
     "pfd_set_wait_limit_ns",
     "pfd_selftest_bounded_wait",
@@ -41,6 +48,24 @@ EXPORTS = (
     "pfd_last_error",
     "pfd_abi_version",
 )
+
+
+class Exchange(C.Structure):
+    """Mirror of ``pfd_exchange``: where the ranks of a KV-range exchange receive."""
+
+    _fields_ = [
+        ("world", C.c_int32),
+        ("rank", C.c_int32),
+        ("step", C.c_int32),
+        ("reserved", C.c_int32),
+        ("recv", C.c_void_p * 8),
+        ("flags", C.c_void_p * 8),
+        ("row_counter", C.c_void_p),
+    ]
+
+
+class IpcHandle(C.Structure):
+    _fields_ = [("bytes", C.c_ubyte * 64)]
 
 
 class DecodeArgs(C.Structure):
@@ -93,6 +118,7 @@ class DecodeArgs(C.Structure):
         ("stream", C.c_void_p),
         ("page_indptr", C.c_void_p),
         ("plan", C.c_void_p),
+        ("exchange", C.POINTER(Exchange)),
     ]
 
 
@@ -145,11 +171,12 @@ def _stream(t: torch.Tensor) -> int:
 def decode_args(
     query, key_cache, value_cache, block_table, seq_lens, *, k_scale, v_scale, max_seq_len,
     split_size, output=None, packed_output=None, workspace=None, kv_start=0, sm_scale=0.0, flags=0,
-    page_indptr=None, plan=None,
+    page_indptr=None, plan=None, exchange=None,
 ) -> DecodeArgs:
     """Fill ``pfd_decode_args`` from torch tensors (device buffers).  With ``page_indptr``
     (int32 ``[B + 1]``) ``block_table`` is the flat list of page ids it indexes.  ``plan`` is the
-    buffer ``plan_decode`` filled for the same inputs."""
+    buffer ``plan_decode`` filled for the same inputs.  ``exchange`` is an ``Exchange`` whose
+    ranks receive this call's packed rows instead of ``output`` / ``packed_output``."""
     a = DecodeArgs()
     a.struct_size = C.sizeof(DecodeArgs)
     a.flags = flags
@@ -193,6 +220,8 @@ def decode_args(
         a.packed_output = packed_output.data_ptr()
     if plan is not None:
         a.plan = plan.data_ptr()
+    if exchange is not None:
+        a.exchange = C.pointer(exchange)  # the pointer object keeps `exchange` alive with `a`
     a.stream = _stream(query)
     return a
 
@@ -276,6 +305,67 @@ def merge_packed(packed: torch.Tensor, output: torch.Tensor) -> None:
     with torch.cuda.device(packed.device):
         _check(load().pfd_merge_packed(packed.data_ptr(), parts, batch * heads, dp2 - 2, output.data_ptr(),
                                        _dtype_code(output.dtype), _stream(packed)))
+
+
+def exchange_geometry(world: int, rows: int, head_dim: int) -> tuple[int, int]:
+    """(bytes of one rank's exchange memory, byte offset of its flag words); the row counter
+    sits 256 bytes behind the flags (``pfd_exchange_bytes`` / ``pfd_exchange_flags_offset``)."""
+    lib = load()
+    for fn in (lib.pfd_exchange_bytes, lib.pfd_exchange_flags_offset):
+        fn.argtypes = [C.c_int32, C.c_int64, C.c_int32]
+        fn.restype = C.c_int64
+    total = int(lib.pfd_exchange_bytes(world, rows, head_dim))
+    if total < 0:
+        raise RuntimeError(lib.pfd_last_error().decode())
+    return total, int(lib.pfd_exchange_flags_offset(world, rows, head_dim))
+
+
+def exchange_alloc(nbytes: int) -> tuple[int, bytes]:
+    """``pfd_exchange_alloc`` on the current device: (device pointer, 64-byte IPC handle)."""
+    lib = load()
+    lib.pfd_exchange_alloc.argtypes = [C.c_int64, C.POINTER(C.c_void_p), C.POINTER(IpcHandle)]
+    lib.pfd_exchange_alloc.restype = C.c_int
+    ptr, handle = C.c_void_p(), IpcHandle()
+    _check(lib.pfd_exchange_alloc(int(nbytes), C.byref(ptr), C.byref(handle)))
+    return int(ptr.value), bytes(handle.bytes)
+
+
+def exchange_open(handle: bytes) -> int:
+    """``pfd_exchange_open``: map another process's exchange memory; returns the peer pointer."""
+    lib = load()
+    lib.pfd_exchange_open.argtypes = [C.POINTER(IpcHandle), C.POINTER(C.c_void_p)]
+    lib.pfd_exchange_open.restype = C.c_int
+    h = IpcHandle()
+    C.memmove(h.bytes, handle, 64)
+    ptr = C.c_void_p()
+    _check(lib.pfd_exchange_open(C.byref(h), C.byref(ptr)))
+    return int(ptr.value)
+
+
+def exchange_close(ptr: int) -> None:
+    lib = load()
+    lib.pfd_exchange_close.argtypes = [C.c_void_p]
+    lib.pfd_exchange_close.restype = C.c_int
+    _check(lib.pfd_exchange_close(C.c_void_p(ptr)))
+
+
+def exchange_free(ptr: int) -> None:
+    lib = load()
+    lib.pfd_exchange_free.argtypes = [C.c_void_p]
+    lib.pfd_exchange_free.restype = C.c_int
+    _check(lib.pfd_exchange_free(C.c_void_p(ptr)))
+
+
+def exchange_merge(exchange: Exchange, output: torch.Tensor) -> None:
+    """``pfd_exchange_merge``: bounded wait for every rank's flag of ``exchange.step``, then the
+    LSE merge of this rank's receive buffer into ``output [B, Hq, D]``."""
+    lib = load()
+    lib.pfd_exchange_merge.argtypes = [C.POINTER(Exchange), C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]
+    lib.pfd_exchange_merge.restype = C.c_int
+    rows = output.shape[0] * output.shape[1]
+    with torch.cuda.device(output.device):
+        _check(lib.pfd_exchange_merge(C.byref(exchange), rows, output.shape[2], output.data_ptr(),
+                                      _dtype_code(output.dtype), _stream(output)))
 
 
 def resolve_slots(block_table: torch.Tensor, seq_lens: torch.Tensor, max_seq_len: int) -> torch.Tensor:

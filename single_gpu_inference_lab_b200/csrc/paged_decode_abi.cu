@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -428,6 +429,22 @@ pfd::KernelParams fill_params(const pfd_decode_args& a, int group, bool direct_o
   kp.slot_offset = slot_offset;
   kp.early_metadata = (a.flags & PFD_FLAG_EARLY_METADATA) ? 1 : 0;
   kp.kv_evict_first = 1;
+  if (a.exchange != nullptr) {
+    const pfd_exchange& x = *a.exchange;
+    kp.xch_world = x.world;
+    kp.xch_rank = x.rank;
+    kp.xch_half = x.step & 1;
+    kp.xch_step = x.step;
+    kp.xch_rows = a.batch * a.num_q_heads;
+    for (int r = 0; r < x.world && r < 8; ++r) {
+      kp.xch_recv[r] = x.recv[r];
+      kp.xch_flags[r] = x.flags[r];
+    }
+    kp.xch_counter = x.row_counter;
+    // packed mode; kernels that know nothing of the exchange would at least fill the local slot
+    kp.packed_output = x.recv[x.rank] + ((int64_t)kp.xch_half * x.world + x.rank) * kp.xch_rows * (a.head_dim + 2);
+    kp.output = nullptr;
+  }
 #ifdef PFD_BOUNDS_CHECK
   kp.dbg_ws_rows = (int64_t)a.batch * a.num_q_heads * a.workspace_splits;
   kp.dbg_batch = a.batch;
@@ -460,7 +477,23 @@ int decode_impl(const pfd_decode_args* args, int slot_offset) {
   if (a.batch == 0) return PFD_OK;
   if (!a.query || !a.key_cache || !a.value_cache || !a.block_table || !a.seq_lens)
     return fail(PFD_ERR_INVALID, "NULL operand");
-  if (!a.output && !a.packed_output) return fail(PFD_ERR_INVALID, "no output given");
+  if (!a.output && !a.packed_output && !a.exchange) return fail(PFD_ERR_INVALID, "no output given");
+  if (a.exchange != nullptr) {
+    const pfd_exchange& x = *a.exchange;
+    if (x.world < 1 || x.world > 8 || x.rank < 0 || x.rank >= x.world || x.step < 1 || !x.row_counter)
+      return fail(PFD_ERR_INVALID, "exchange: world 1..8, 0 <= rank < world, step >= 1 and a row counter are needed");
+    for (int r = 0; r < x.world; ++r)
+      if (!x.recv[r] || !x.flags[r]) return fail(PFD_ERR_INVALID, "exchange: recv / flags pointer of rank %d is NULL", r);
+    if (slot_offset != 0 || (a.flags & (PFD_FLAG_SINGLE_LAUNCH | PFD_FLAG_PARTIAL_ONLY)))
+      return fail(PFD_ERR_UNSUPPORTED, "exchange: not with the shared-prefix pass, PFD_FLAG_SINGLE_LAUNCH or PFD_FLAG_PARTIAL_ONLY");
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    if (int rc = sm_count_of(dev, &sms)) return rc;
+    if (!balanced_eligible(a, group, 0, sms))
+      return fail(PFD_ERR_UNSUPPORTED,
+                  "exchange: needs the balanced kernel (head_dim 128, at most 8 query heads per KV head, TMA-describable "
+                  "cache, dense f32 workspace of pfd_balanced_workspace_rows() rows, no fixed-split flags)");
+  }
   if (a.q_stride_h % 4 || a.q_stride_b % 4 || (reinterpret_cast<uintptr_t>(a.query) & 7u))
     return fail(PFD_ERR_UNSUPPORTED, "query rows must be 8-byte aligned");
   if (a.output && (a.o_stride_h % 4 || a.o_stride_b % 4 || (reinterpret_cast<uintptr_t>(a.output) & 7u)))
@@ -615,6 +648,7 @@ int pfd_paged_decode_kv16_split_out(const pfd_decode_args* args) {
   if (int rc = validate_kv16(args, &cap, &sms, true)) return rc;
   const pfd_decode_args& a = *args;
   if (a.batch == 0) return PFD_OK;
+  if (a.exchange != nullptr) return fail(PFD_ERR_UNSUPPORTED, "exchange: FP8 caches only");
   const int group = a.num_q_heads / a.num_kv_heads;
   const pfd::KernelParams kp = fill_params(a, group, !(a.flags & PFD_FLAG_NO_DIRECT_OUT), 0);
   cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
@@ -715,6 +749,7 @@ int pfd_shared_prefix_decode_fp8_e4m3(const pfd_decode_args* args, int32_t prefi
   a.flags |= PFD_FLAG_FIXED_SPLITS | PFD_FLAG_NO_DIRECT_OUT;
   a.flags &= ~(uint32_t)PFD_FLAG_PARTIAL_ONLY;
   a.plan = nullptr;
+  if (a.exchange != nullptr) return fail(PFD_ERR_UNSUPPORTED, "exchange: not with the shared-prefix pass");
   {
     const int span = a.max_seq_len - prefix_len;
     const int ns = span > 0 ? (span + a.split_size - 1) / a.split_size : 1;
@@ -756,6 +791,7 @@ int pfd_paged_decode_fp8_e4m3_split_out_noalloc(const pfd_decode_args* args) {
     return fail(PFD_ERR_UNSUPPORTED,
                 "PFD_FLAG_PARTIAL_ONLY makes no sense here: the partials would stay in the library's own array");
   a.plan = nullptr;
+  if (a.exchange != nullptr) return fail(PFD_ERR_UNSUPPORTED, "exchange: not with the allocation-free entry point");
   const int64_t span = a.max_seq_len > a.kv_start ? a.max_seq_len - a.kv_start : 0;
   int64_t splits = (span + a.split_size - 1) / a.split_size;
   if (splits < 1) splits = 1;
@@ -936,6 +972,90 @@ int pfd_merge_packed(const float* packed, int32_t num_parts, int64_t rows, int32
   else
     pfd::merge_packed_kernel<64><<<blocks, 128, 0, s>>>(packed, num_parts, rows, output, out_dtype);
   return check_launch("merge_packed kernel");
+}
+
+int64_t pfd_exchange_flags_offset(int32_t world, int64_t rows, int32_t head_dim) {
+  if (world < 1 || world > 8 || rows < 0 || head_dim <= 0) return fail(PFD_ERR_INVALID, "invalid exchange geometry");
+  const int64_t recv = 2LL * world * rows * (head_dim + 2) * (int64_t)sizeof(float);
+  return (recv + 255) / 256 * 256;
+}
+
+int64_t pfd_exchange_bytes(int32_t world, int64_t rows, int32_t head_dim) {
+  const int64_t off = pfd_exchange_flags_offset(world, rows, head_dim);
+  return off < 0 ? off : off + 512;  // flags [2][world] in the first 256 bytes, the row counter in the next
+}
+
+int pfd_exchange_alloc(int64_t bytes, void** ptr, pfd_ipc_handle* handle) {
+  if (bytes <= 0 || ptr == nullptr || handle == nullptr) return fail(PFD_ERR_INVALID, "invalid argument");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, static_cast<size_t>(bytes));
+  if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaMalloc of the exchange buffer failed: %s", cudaGetErrorString(e));
+  e = cudaMemset(p, 0, static_cast<size_t>(bytes));
+  cudaIpcMemHandle_t h;
+  if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    return fail(PFD_ERR_CUDA, "preparing the exchange buffer failed: %s", cudaGetErrorString(e));
+  }
+  static_assert(sizeof(cudaIpcMemHandle_t) == sizeof(pfd_ipc_handle), "IPC handle size");
+  memcpy(handle->bytes, &h, sizeof h);
+  *ptr = p;
+  return PFD_OK;
+}
+
+int pfd_exchange_open(const pfd_ipc_handle* handle, void** peer_ptr) {
+  if (handle == nullptr || peer_ptr == nullptr) return fail(PFD_ERR_INVALID, "invalid argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle->bytes, sizeof h);
+  void* p = nullptr;
+  const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaIpcOpenMemHandle failed: %s", cudaGetErrorString(e));
+  *peer_ptr = p;
+  return PFD_OK;
+}
+
+int pfd_exchange_close(void* peer_ptr) {
+  if (peer_ptr == nullptr) return PFD_OK;
+  const cudaError_t e = cudaIpcCloseMemHandle(peer_ptr);
+  return e == cudaSuccess ? PFD_OK : fail(PFD_ERR_CUDA, "cudaIpcCloseMemHandle failed: %s", cudaGetErrorString(e));
+}
+
+int pfd_exchange_free(void* ptr) {
+  if (ptr == nullptr) return PFD_OK;
+  const cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? PFD_OK : fail(PFD_ERR_CUDA, "cudaFree failed: %s", cudaGetErrorString(e));
+}
+
+int pfd_exchange_merge(const pfd_exchange* exchange, int64_t rows, int32_t head_dim, void* output,
+                       int32_t out_dtype, void* stream) {
+  if (exchange == nullptr || output == nullptr) return fail(PFD_ERR_INVALID, "NULL operand");
+  const pfd_exchange& x = *exchange;
+  if (x.world < 1 || x.world > 8 || x.rank < 0 || x.rank >= x.world || x.step < 1)
+    return fail(PFD_ERR_INVALID, "exchange: world 1..8, 0 <= rank < world and step >= 1 are needed");
+  if (!x.recv[x.rank] || !x.flags[x.rank]) return fail(PFD_ERR_INVALID, "exchange: this rank's recv / flags pointer is NULL");
+  if (head_dim != 128) return fail(PFD_ERR_UNSUPPORTED, "exchange: head_dim must be 128");
+  if (out_dtype < PFD_DTYPE_F32 || out_dtype > PFD_DTYPE_BF16)
+    return fail(PFD_ERR_INVALID, "output dtype must be f32, f16 or bf16");
+  if (rows <= 0) return rows == 0 ? PFD_OK : fail(PFD_ERR_INVALID, "negative row count");
+  int32_t* status = nullptr;
+  if (int rc = status_pointer(&status)) return rc;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>((rows + 3) / 4));
+  cfg.blockDim = dim3(128);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const float* recv = x.recv[x.rank];
+  const int32_t* flags = x.flags[x.rank];
+  const int world = x.world, half = x.step & 1, step = x.step;
+  const unsigned long long limit = g_wait_limit_ns.load(std::memory_order_relaxed);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, pfd::exchange_merge_kernel<128>, recv, flags, world, half, step, rows,
+                                           output, (int)out_dtype, status, limit);
+  if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "exchange merge kernel launch failed: %s", cudaGetErrorString(e));
+  return check_launch("exchange merge kernel");
 }
 
 int pfd_resolve_slots(const int32_t* block_table, int64_t bt_stride_b, const int32_t* seq_lens,

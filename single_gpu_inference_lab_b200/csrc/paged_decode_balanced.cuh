@@ -256,10 +256,12 @@ __device__ __forceinline__ void store_row16(const KernelParams& p, int b, int hq
                                             float m_nat, float l, bool write_ml) {
   // 16 consecutive head-dim values of one (sequence, q head) row: final output or packed form
   if (p.packed_output != nullptr) {
-    float* dst = p.packed_output + ((int64_t)b * p.num_q_heads + hq) * 130 + d0;
+    for (int dest = 0; dest < packed_dests(p); ++dest) {
+      float* dst = packed_row(p, dest, (int64_t)b * p.num_q_heads + hq) + d0;
 #pragma unroll
-    for (int t = 0; t < 16; t += 2) *reinterpret_cast<float2*>(dst + t) = make_float2(v[t], v[t + 1]);
-    if (write_ml) { dst[128 - d0] = m_nat; dst[129 - d0] = l; }
+      for (int t = 0; t < 16; t += 2) *reinterpret_cast<float2*>(dst + t) = make_float2(v[t], v[t + 1]);
+      if (write_ml) { dst[128 - d0] = m_nat; dst[129 - d0] = l; }
+    }
   } else {
     const float inv = 1.f / l;
     uint32_t w[8];
@@ -1065,6 +1067,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
         }
       }
     }
+    if (whole && p.packed_output != nullptr) packed_rows_done(p, p.group, lane);
     if constexpr (FUSED) if (!whole) {
       // Publish the piece, then count this warp's pairs of the sequence in: the warp that
       // completes the count finds every other piece in L2 and writes the final rows.
@@ -1251,10 +1254,13 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
     big = m_all;
   }
   if (p.packed_output != nullptr) {
-    float* dst = p.packed_output + (int64_t)row * (D + 2);
-    *reinterpret_cast<float2*>(dst + lane * E) = make_float2(acc[0], acc[1]);
-    *reinterpret_cast<float2*>(dst + lane * E + 2) = make_float2(acc[2], acc[3]);
-    if (lane == 0) { dst[D] = big; dst[D + 1] = den; }
+    for (int dest = 0; dest < packed_dests(p); ++dest) {
+      float* dst = packed_row(p, dest, row);
+      *reinterpret_cast<float2*>(dst + lane * E) = make_float2(acc[0], acc[1]);
+      *reinterpret_cast<float2*>(dst + lane * E + 2) = make_float2(acc[2], acc[3]);
+      if (lane == 0) { dst[D] = big; dst[D + 1] = den; }
+    }
+    packed_rows_done(p, 1, lane);
     return;
   }
   mark_phase_at(tp, cp.num_warps + blockIdx.x, 7, threadIdx.x == 0);  // merged

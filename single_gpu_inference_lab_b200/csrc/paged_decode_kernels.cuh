@@ -58,6 +58,14 @@ struct KernelParams {
   int32_t slot_offset; // workspace slots [0, slot_offset) are filled by another kernel (dense prefix pass)
   int32_t early_metadata;  // 1: seq_lens and block_table may be read before the preceding kernel has completed
   int32_t kv_evict_first;  // 1: K/V tiles are loaded with the L2 evict-first hint
+  // KV-range exchange (xch_world > 0): the packed (o, m, l) rows of this rank go, instead of to
+  // packed_output, into slot xch_rank of every rank's receive buffer [2][world][rows][D + 2]
+  // (half xch_half), with plain stores over NVLink; the warp that stores the last row releases
+  // the step's flag in every rank's flag array [2][world].
+  int32_t xch_world, xch_rank, xch_half, xch_step, xch_rows;
+  float* xch_recv[8];
+  int32_t* xch_flags[8];
+  int32_t* xch_counter;    // local: rows stored so far in this step, zero between steps
 #ifdef PFD_BOUNDS_CHECK
   int64_t dbg_ws_rows;     // self-checking builds: rows of the workspace, sequences of the batch
   int32_t dbg_batch;
@@ -70,6 +78,39 @@ struct KernelParams {
 // has completed and its memory is visible.  Both are no-ops for an ordinary launch.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// ---- KV-range exchange: where packed rows go, and the hand-over to the other ranks ----------
+__device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
+  int32_t v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Number of copies of a packed row, and where copy `dest` of row `row` (of D + 2 = 130 floats) goes.
+__device__ __forceinline__ int packed_dests(const KernelParams& p) { return p.xch_world > 0 ? p.xch_world : 1; }
+__device__ __forceinline__ float* packed_row(const KernelParams& p, int dest, int64_t row) {
+  if (p.xch_world == 0) return p.packed_output + row * 130;
+  return p.xch_recv[dest] + (((int64_t)p.xch_half * p.xch_world + p.xch_rank) * p.xch_rows + row) * 130;
+}
+// A warp has stored `rows` packed rows in every destination.  With an exchange: make them visible
+// system-wide, count them, and let the warp that completes the step's rows release the flags.
+// Nobody waits here; the receiving side's wait is in exchange_merge_kernel.
+__device__ __forceinline__ void packed_rows_done(const KernelParams& p, int rows, int lane) {
+  if (p.xch_world == 0) return;
+  __threadfence_system();
+  __syncwarp();
+  if (lane == 0) {
+    const int before = atomicAdd(p.xch_counter, rows);
+    if (before + rows == p.xch_rows) {
+      atomicExch(p.xch_counter, 0);  // ready for the next step
+      __threadfence_system();
+      for (int d = 0; d < p.xch_world; ++d)
+        st_release_sys(p.xch_flags[d] + p.xch_half * p.xch_world + p.xch_rank, p.xch_step);
+    }
+  }
+}
 
 // The one address function every kernel uses for "which cache slot holds token t of
 // sequence b".  Returns the physical page; the slot is page * 16 + t % 16.
@@ -1015,6 +1056,69 @@ merge_packed_kernel(const float* __restrict__ packed, int parts, int64_t rows, v
     den += src[D + 1] * c;
 #pragma unroll
     for (int e = 0; e < E; ++e) acc[e] += c * src[lane * E + e];
+  }
+  const float inv = den > 0.f ? 1.f / den : 0.f;
+#pragma unroll
+  for (int e = 0; e < E; ++e) {
+    const float v = acc[e] * inv;
+    const int64_t idx = row * D + lane * E + e;
+    if (out_dtype == 0) reinterpret_cast<float*>(output)[idx] = v;
+    else if (out_dtype == 1) reinterpret_cast<__half*>(output)[idx] = __float2half_rn(v);
+    else reinterpret_cast<__nv_bfloat16*>(output)[idx] = __float2bfloat16_rn(v);
+  }
+}
+
+constexpr int kErrPeerTimeout = 3;
+
+// Receiving side of the KV-range exchange: waits until every rank's flag of this step has arrived
+// in this rank's flag array (the other GPUs' kernels release them; this GPU's own kernels have
+// completed by then, the grid being their programmatic dependent), then merges the `world` packed
+// partials of each row from this rank's receive buffer.  The wait is bounded in time: when it
+// runs out the error word is set, nothing is merged and the kernel ends.  One warp per row.
+template <int D>
+__global__ void __launch_bounds__(128)
+exchange_merge_kernel(const float* __restrict__ recv, const int32_t* __restrict__ flags, int world, int half,
+                      int step, int64_t rows, void* output, int out_dtype, int32_t* status,
+                      unsigned long long wait_limit_ns) {
+  pdl_wait();  // this GPU's own rows and flag are in place: from here on only other GPUs are waited for
+  __shared__ int sh_ok;
+  if (threadIdx.x == 0) sh_ok = 1;
+  __syncthreads();
+  if ((int)threadIdx.x < world) {
+    const int32_t* f = flags + half * world + threadIdx.x;
+    bool ok = ld_acquire_sys(f) == step;
+    if (!ok) {
+      const unsigned long long t0 = global_timer_ns();
+      for (uint32_t spin = 0; spin < kSpinLimit && !ok; ++spin) {
+        ok = ld_acquire_sys(f) == step;
+        if (!ok && global_timer_ns() - t0 > wait_limit_ns) break;
+      }
+    }
+    if (!ok) { sh_ok = 0; atomicExch(status, kErrPeerTimeout); }
+  }
+  __syncthreads();
+  if (!sh_ok) return;
+  __threadfence_system();
+  const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  constexpr int E = D / 32;
+  const float* base = recv + (int64_t)half * world * rows * (D + 2);
+  float big = -INFINITY;
+  for (int s = lane; s < world; s += 32) big = fmaxf(big, __ldcg(base + ((int64_t)s * rows + row) * (D + 2) + D));
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
+  float acc[E];
+#pragma unroll
+  for (int e = 0; e < E; ++e) acc[e] = 0.f;
+  float den = 0.f;
+  for (int s = 0; s < world; ++s) {
+    const float* src = base + ((int64_t)s * rows + row) * (D + 2);
+    const float m = __ldcg(src + D);
+    const float c = (m == -INFINITY) ? 0.f : expf(m - big);
+    den += __ldcg(src + D + 1) * c;
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] += c * __ldcg(src + lane * E + e);
   }
   const float inv = den > 0.f ? 1.f / den : 0.f;
 #pragma unroll

@@ -7,10 +7,15 @@ below are the natural shardings of its operator:
   rows, query rows and output rows of its sequences.  No data-path communication at all.
   ``lpt_partition`` balances *tokens*, not sequence counts.
 * **KV-range sharding** -- every sequence's pages are dealt out in contiguous page ranges, one
-  range per rank; each rank runs the ordinary operator on its range with ``packed_output``
-  (``o`` un-normalised, ``m``, ``l``), the ranks exchange those ``[B, Hq, D + 2]`` fp32 records
-  with one ``all_gather_into_tensor`` and every rank applies the same LSE merge the single-GPU
-  split-KV path uses (reference maths: integrations/vllm/l20_paged_split_kv.py:459-488).
+  range per rank; each rank runs the ordinary operator on its range, which yields packed
+  ``[B, Hq, D + 2]`` fp32 records (``o`` un-normalised, ``m``, ``l``), every rank needs every
+  rank's records and applies the same LSE merge the single-GPU split-KV path uses (reference
+  maths: integrations/vllm/l20_paged_split_kv.py:459-488).  Two forms of the exchange:
+  ``KvRangeExchange`` -- the decode kernels store their rows straight into every rank's receive
+  buffer over NVLink and release a step-tagged flag, the merge kernel waits (bounded) for the
+  flags: no collective call; and ``kv_range_decode`` -- ``packed_output`` plus one
+  ``all_gather_into_tensor``, the fallback where peer mappings are not to be had (and on CPU
+  ranks in tests).
 
 Nothing here falls back to a CPU implementation: the default compute callbacks are the CUDA
 operator; tests on CPU ranks inject their own.
@@ -140,3 +145,113 @@ def kv_range_decode(
     # concatenation along dim 0 is the layout every backend accepts; [world*B,...] == [world,B,...]
     dist.all_gather_into_tensor(gather_buffer.view(-1, *packed.shape[1:]), packed, group=group)
     return merge_fn(gather_buffer, local.query)
+
+
+class KvRangeExchange:
+    """Receive buffers, flags and peer mappings of the in-kernel KV-range exchange
+    (``pfd_exchange`` of include/paged_fp8_decode.h) for a fixed ``[B, Hq, D]`` step shape.
+
+    ``KvRangeExchange.create`` is the multi-process form: every rank allocates its own memory,
+    the ranks swap CUDA IPC handles over the process group (host side, once) and map each
+    other's.  ``KvRangeExchange.emulate`` builds all ranks' objects inside ONE process on one
+    device, for tests that issue the ranks' calls one after another on one stream.
+    """
+
+    def __init__(self, rank: int, world: int, rows: int, head_dim: int, bases: list[int], owned: int,
+                 opened: list[int], device: torch.device):
+        from . import cabi
+
+        self.rank, self.world, self.rows, self.head_dim = rank, world, rows, head_dim
+        self.device = device
+        self._owned, self._opened = owned, opened
+        _, flags_off = cabi.exchange_geometry(world, rows, head_dim)
+        x = cabi.Exchange()
+        x.world, x.rank, x.step = world, rank, 0
+        for r in range(world):
+            x.recv[r] = bases[r]
+            x.flags[r] = bases[r] + flags_off
+        x.row_counter = bases[rank] + flags_off + 256
+        self.struct = x
+        self.step = 0
+
+    @classmethod
+    def create(cls, batch: int, num_q_heads: int, head_dim: int, device, group=None) -> "KvRangeExchange":
+        from . import cabi
+
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        rows = batch * num_q_heads
+        nbytes, _ = cabi.exchange_geometry(world, rows, head_dim)
+        with torch.cuda.device(device):
+            base, handle = cabi.exchange_alloc(nbytes)
+            handles: list = [None] * world
+            dist.all_gather_object(handles, handle, group=group)
+            bases, opened = [], []
+            for r in range(world):
+                if r == rank:
+                    bases.append(base)
+                else:
+                    bases.append(cabi.exchange_open(handles[r]))
+                    opened.append(bases[-1])
+        return cls(rank, world, rows, head_dim, bases, base, opened, torch.device(device))
+
+    @classmethod
+    def emulate(cls, world: int, batch: int, num_q_heads: int, head_dim: int, device) -> list["KvRangeExchange"]:
+        from . import cabi
+
+        rows = batch * num_q_heads
+        nbytes, _ = cabi.exchange_geometry(world, rows, head_dim)
+        with torch.cuda.device(device):
+            bases = [cabi.exchange_alloc(nbytes)[0] for _ in range(world)]
+        return [cls(r, world, rows, head_dim, bases, bases[r], [], torch.device(device)) for r in range(world)]
+
+    def next_step(self) -> int:
+        """Advance the step tag (every rank calls this once per decode step, in step)."""
+        self.step += 1
+        self.struct.step = self.step
+        return self.step
+
+    def decode(self, local: PagedDecodeInputs, *, split_size: int, workspace, plan=None, flags: int = 0) -> None:
+        """This rank's range through the operator; its packed rows go to every rank."""
+        from . import cabi
+
+        cabi.paged_decode_fp8_e4m3_split_out(
+            local.query, local.key_cache, local.value_cache, local.block_table, local.seq_lens,
+            k_scale=local.k_scale, v_scale=local.v_scale, max_seq_len=local.max_seq_len, split_size=split_size,
+            workspace=workspace, plan=plan, flags=flags, exchange=self.struct,
+        )
+
+    def merge(self, output: torch.Tensor) -> torch.Tensor:
+        """Wait (bounded) for every rank's rows of the current step and merge them into ``output``."""
+        from . import cabi
+
+        cabi.exchange_merge(self.struct, output)
+        return output
+
+    def close(self) -> None:
+        from . import cabi
+
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize()
+            for p in self._opened:
+                cabi.exchange_close(p)
+            self._opened = []
+            if self._owned:
+                cabi.exchange_free(self._owned)
+                self._owned = 0
+
+
+def kv_range_decode_exchange(
+    local: PagedDecodeInputs, exchange: KvRangeExchange, *, split_size: int = 2048, workspace=None, plan=None,
+    flags: int = 0, output: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """One decode step of a KV-range-sharded batch with the exchange inside the kernels: two calls,
+    no collective.  Every rank must call it once per step.  Returns ``[B, Hq, D]``."""
+    from .l20_paged_split_kv import allocate_l20_paged_split_kv_workspace
+
+    if workspace is None:
+        workspace = allocate_l20_paged_split_kv_workspace(local.query, max(local.max_seq_len, 1), split_size=split_size)
+    if output is None:
+        output = torch.empty_like(local.query)
+    exchange.next_step()
+    exchange.decode(local, split_size=split_size, workspace=workspace, plan=plan, flags=flags)
+    return exchange.merge(output)
