@@ -75,6 +75,10 @@ def parse_args():
     p.add_argument("--kv-dtype", choices=["fp8", "bf16", "fp16"], default="fp8",
                    help="fp8: the e4m3 path (headline); bf16 / fp16: the non-quantised sibling operator, "
                         "caches and query in that type (single GPU, batch-sharded or weak scaling only)")
+    p.add_argument("--exchange", choices=("peer", "nccl"), default="peer",
+                   help="KV-range mode on several GPUs: 'peer' = the decode kernels store their packed rows into "
+                        "every rank's receive buffer and the merge kernel waits for flags (the all-gather form is "
+                        "measured beside it); 'nccl' = packed_output + all_gather_into_tensor + merge only")
     p.add_argument("--graph-collective", action="store_true",
                    help="KV-range mode on several GPUs: replay the step, exchange included, from a CUDA graph "
                         "instead of launching every step eagerly")
@@ -349,12 +353,17 @@ class Case:
             if args.single_launch:
                 self.flags |= cabi.PFD_FLAG_SINGLE_LAUNCH
         kvr = mode == "kv-range"
+        # KV-range mode on several GPUs: the decode kernels store their packed rows straight into
+        # every rank's receive buffer ("peer"); the all-gather form is measured beside it.
+        self.xch = None
+        if kvr and world > 1 and args.exchange == "peer":
+            self.xch = sharding.KvRangeExchange.create(self.batch, self.hq, self.d, dev)
         self.packed = torch.empty(self.batch, self.hq, self.d + 2, device=dev) if kvr else None
         self.gathered = torch.empty(world, self.batch, self.hq, self.d + 2, device=dev) if kvr else None
         self.filler = torch.zeros(1 << 14, device=dev)
 
     # -- the timed call
-    def step(self, i: int, flags=None, exchange: bool = True):
+    def step(self, i: int, flags=None, exchange: bool = True, peer: bool = True):
         import torch.distributed as dist
 
         cabi, w = self.cabi, self.w
@@ -372,6 +381,13 @@ class Case:
                 workspace=self.ws)
             return
         kvr = self.mode == "kv-range"
+        if kvr and self.xch is not None and peer and exchange and not (flags & cabi.PFD_FLAG_PARTIAL_ONLY):
+            cabi.paged_decode_fp8_e4m3_split_out(
+                w.query, kc, vc, w.block_table, w.seq_lens, k_scale=w.k_scale, v_scale=w.v_scale,
+                max_seq_len=w.max_seq_len, split_size=self.split, workspace=self.ws, flags=flags, plan=self.plan,
+                exchange=self.xch.struct)
+            cabi.exchange_merge(self.xch.struct, self.out)
+            return
         cabi.paged_decode_fp8_e4m3_split_out(
             w.query, kc, vc, w.block_table, w.seq_lens, k_scale=w.k_scale, v_scale=w.v_scale,
             max_seq_len=w.max_seq_len, split_size=self.split, output=None if kvr else self.out,
@@ -383,6 +399,10 @@ class Case:
             else:
                 self.gathered[0].copy_(self.packed)
             cabi.merge_packed(self.gathered, self.out)
+
+    def step_allgather(self, i: int):
+        """KV-range mode: the step with the packed partials exchanged by one all-gather."""
+        self.step(i, peer=False)
 
     def exchange_only(self, i: int):
         """KV-range mode: the exchange of the packed partials and the merge, without the kernel."""
@@ -448,7 +468,7 @@ class Case:
                     for i in range(count):
                         fn(i)
                 graphs.append(g)
-        torch.cuda.synchronize()
+        self.barrier()  # ranks whose kernels wait for one another start their replays together
         graphs[0].replay()
         runs = []
         for _ in range(repeats):
@@ -487,7 +507,7 @@ class Case:
         self.step(0)
         res["launches_per_step"] = cabi.launch_count() - before
         res["path"] = cabi.last_path()
-        ms_step, runs = self.timed_graph(self.step, steps, repeats, collective=kvr)
+        ms_step, runs = self.timed_graph(self.step, steps, repeats, collective=kvr and self.xch is None)
         res["ms_step"], res["runs_us"] = ms_step, [round(r * 1e3, 3) for r in runs]
         single = self.shared_prefix or res["launches_per_step"] == 1
         if single:
@@ -496,10 +516,15 @@ class Case:
             res["ms_kernel"], _ = self.timed_graph(
                 lambda i: self.step(i, self.flags | cabi.PFD_FLAG_PARTIAL_ONLY, exchange=False), steps, 1)
         if isolated:
-            res["ms_isolated"], _ = self.timed_graph(self.isolated_step, steps, 1, collective=kvr)
+            res["ms_isolated"], _ = self.timed_graph(self.isolated_step, steps, 1, collective=kvr and self.xch is None)
             ms_fill, _ = self.timed_graph(lambda i: self.filler.add_(1.0), steps, 1)
             res["ms_isolated"] = max(res["ms_isolated"] - ms_fill, 0.0)
-        if kvr:
+        if kvr and self.xch is not None:
+            res["ms_exchange"] = max(ms_step - res["ms_kernel"], 0.0)
+            res["ms_step_allgather"], _ = self.timed_graph(self.step_allgather, steps, 1, collective=True)
+            res["ms_exchange_allgather"], _ = self.timed_graph(self.exchange_only, steps, 1, collective=True)
+            res["exchange_status"] = cabi.device_status()
+        elif kvr:
             res["ms_exchange"], _ = self.timed_graph(self.exchange_only, steps, 1, collective=True)
         return res
 
@@ -509,6 +534,10 @@ class Case:
         return KERNEL_NAMES.get(path, "?")
 
     def release(self):
+        if self.xch is not None:
+            self.barrier()  # no rank still stores into another's buffer
+            self.xch.close()
+            self.xch = None
         del self.kcs, self.vcs, self.ws, self.w
         torch.cuda.empty_cache()
 
@@ -531,6 +560,13 @@ def short_report(case: Case, res: dict, peak: float, world_bytes: float, world: 
         out["correct"], out["max_abs_error"], out["checked"] = res["correct"], res["max_abs_error"], res["checked"]
     if "ms_exchange" in res:
         out["exchange_and_merge_us"] = round(res["ms_exchange"] * 1e3, 3)
+    if "ms_step_allgather" in res:
+        out["exchange"] = ("inside the kernels: packed rows stored to every rank over NVLink, step-tagged flags, bounded "
+                           "flag wait in the merge kernel; exchange_and_merge_us = step - decode kernels alone")
+        out["exchange_status"] = res["exchange_status"]
+        out["allgather_form"] = {"us_per_layer_step": round(res["ms_step_allgather"] * 1e3, 3),
+                                 "exchange_and_merge_us": round(res["ms_exchange_allgather"] * 1e3, 3),
+                                 "what": "packed_output + one NCCL all_gather_into_tensor + merge kernel, launched eagerly"}
     return out
 
 
@@ -599,7 +635,9 @@ def main() -> int:
         if mode == "kv-range":
             local = w.__class__(**{**w.__dict__, "query": dq, "block_table": dtable, "seq_lens": dlens,
                                    "key_cache": kc, "value_cache": vc})
-            if world > 1:
+            if world > 1 and case.xch is not None:
+                res = sharding.kv_range_decode_exchange(local, case.xch, split_size=split, workspace=ws, output=case.out)
+            elif world > 1:
                 res = sharding.kv_range_decode(local, split_size=split, gather_buffer=case.gathered, workspace=ws,
                                                packed_buffer=case.packed)
             else:
@@ -676,7 +714,9 @@ def main() -> int:
                 **({"shared_prefix_tokens": w.prefix_len,
                     "unique_kv_bytes_per_step": int(w.prefix_len + (w.seq_lens - w.prefix_len).sum().item()) * case.hkv * case.d * 2,
                     "prefix_pass": "dense tcgen05 (TMEM accumulators), 128 rows x 256 tokens per CTA"} if case.shared_prefix else {}),
-                "parallelism": ("kv-range split, packed partials exchanged (all-gather), merged on every rank" if mode == "kv-range" else
+                "parallelism": (("kv-range split; packed partials stored to every rank by the decode kernels (peer stores + flags), merged on every rank"
+                                 if args.exchange == "peer" else
+                                 "kv-range split, packed partials exchanged (all-gather), merged on every rank") if mode == "kv-range" else
                                 ("one batch sharded by sequence (token-balanced), no collective" if mode == "strong"
                                  else "the same batch on every GPU, no collective")) if world > 1 else "single GPU",
                 "l2": f"{pools} KV pools of {case.pool_bytes / 1e6:.0f} MB rotated ({pools * case.pool_bytes / 1e6:.0f} MB > L2): every step reads cold KV",
@@ -702,6 +742,10 @@ def main() -> int:
         }
         if "ms_exchange" in res:
             line["exchange_and_merge_us"] = round(res["ms_exchange"] * 1e3, 3)
+        if "ms_step_allgather" in res:
+            line["exchange_status"] = res["exchange_status"]
+            line["allgather_form"] = {"us_per_layer_step": round(res["ms_step_allgather"] * 1e3, 3),
+                                      "exchange_and_merge_us": round(res["ms_exchange_allgather"] * 1e3, 3)}
         if cpu_baseline is not None:
             line["cpu_baseline"] = cpu_baseline
     case.release()
@@ -749,7 +793,7 @@ def main() -> int:
                     rep["speedup_over_one_gpu"] = round(one / rep["us_per_layer_step"], 3)
                     rep["sharding"] = ("sequences split over the ranks by tokens (longest first), no communication"
                                        if smode == "strong" else
-                                       "KV range of every sequence split over the ranks; packed (o, m, l) all-gathered, merged on every rank")
+                                       "KV range of every sequence split over the ranks; packed (o, m, l) rows exchanged, merged on every rank")
                     sharded[name] = rep
             if rank == 0:
                 line["sharded"] = sharded

@@ -85,30 +85,32 @@ extern "C" {
  * single-GPU).  Every rank holds a KV range of every sequence; its decode call yields packed
  * (o, m, l) rows for that range, which every rank needs for the final merge.  With `exchange`
  * set in pfd_decode_args the kernels that finish those rows store them straight into slot
- * `rank` of EVERY rank's receive buffer (plain stores through peer mappings over NVLink), and
- * the warp that stores the step's last row releases the step's flag in every rank's flag array.
- * pfd_exchange_merge() then waits (bounded) for the `world` flags in this rank's own array and
- * merges this rank's own receive buffer: no collective call, no remote load.
+ * `rank` of EVERY rank's receive buffer (plain stores through peer mappings over NVLink).  Each
+ * 8-byte word of a row holds an f32 value in its low half and the step's tag in its high half
+ * and arrives whole, so the receiver needs no flag: pfd_exchange_merge() polls (bounded) the
+ * words of this rank's own buffer, row by row, until they carry the tag, and merges them.  No
+ * collective call, no fence, no remote load.
  *
- *   recv[p]   rank p's receive buffer, f32 [2][world][batch * num_q_heads][head_dim + 2], as
- *             mapped in THIS process (recv[rank] is local memory, the others peer memory)
- *   flags[p]  rank p's flag words, int32 [2][world], zero before the first step
- *   step      tag of this call: positive, increasing by one per call on every rank alike; its
- *             lowest bit selects the half of the buffers, so that a rank one step ahead never
- *             overwrites what a slower rank still merges
- *   row_counter  one local int32, zero between calls
+ *   recv[p]   rank p's receive buffer, 8-byte words [2][world][batch * num_q_heads][PFD_XCH_ROW]
+ *             (a row: o[head_dim], m, l), as mapped in THIS process (recv[rank] is local memory,
+ *             the others peer memory); zero before the first step
+ *   control   two local 32-bit words, zero before the first step: steps completed, merge CTAs done
+ * The step's tag lives on the device (control[0] + 1, wrapping), so that a step captured in a
+ * CUDA graph can be replayed: pfd_exchange_merge()'s kernel advances it, succeed or not, and
+ * every rank must therefore run exactly one decode call (at most) and one pfd_exchange_merge()
+ * per step.  The tag's lowest bit selects the half of the buffer, so that a rank one step ahead
+ * never overwrites what a slower rank still merges; no rank can get further ahead than that,
+ * because its next merge waits for the slower rank's rows.
  * Allocate with pfd_exchange_alloc() / map the peers' with pfd_exchange_open() (or any other way
  * that yields peer-accessible device memory).  Needs the balanced kernel + merge kernel (head_dim
  * 128, FP8 caches, at most 8 query heads per kv head, no PFD_FLAG_SINGLE_LAUNCH / FIXED_SPLITS);
  * other calls are refused.  world <= 8.
  */
+#define PFD_XCH_ROW 130
 typedef struct pfd_exchange {
   int32_t world, rank;
-  int32_t step;
-  int32_t reserved;
-  float* recv[8];
-  int32_t* flags[8];
-  int32_t* row_counter;
+  void* recv[8];
+  void* control;
 } pfd_exchange;
 
 typedef struct pfd_decode_args {
@@ -281,10 +283,10 @@ int pfd_merge_packed(const float* packed, int32_t num_parts, int64_t rows, int32
 
 /*
  * Receiving side of a KV-range exchange step: one kernel on `stream` (enqueue it behind the decode
- * call of the same step) that waits until all `world` ranks have released the step's flag in this
- * rank's flag array -- at most the wait limit (pfd_set_wait_limit_ns); on expiry device status 3
- * is set, nothing is merged and the kernel ends -- and then LSE-merges the `world` packed partials
- * of every row from this rank's receive buffer into output [rows, head_dim] of `out_dtype`.
+ * call of the same step), one warp per row, that waits until the words of all `world` ranks' copies
+ * of the row in this rank's receive buffer carry the step's tag -- at most the wait limit
+ * (pfd_set_wait_limit_ns); on expiry device status 3 is set and the row is left alone -- and then
+ * LSE-merges the `world` packed partials of the row into output [rows, head_dim] of `out_dtype`.
  * Same maths as pfd_merge_packed.
  */
 int pfd_exchange_merge(const pfd_exchange* exchange, int64_t rows, int32_t head_dim, void* output,
@@ -293,13 +295,13 @@ int pfd_exchange_merge(const pfd_exchange* exchange, int64_t rows, int32_t head_
 /*
  * Memory for one rank's side of the exchange: cudaMalloc of `bytes` (zero-filled), with the
  * 64-byte CUDA IPC handle that the other ranks' processes turn into a peer mapping with
- * pfd_exchange_open().  pfd_exchange_bytes() is what recv + flags + row counter of one rank need;
- * the flags start at pfd_exchange_flags_offset() bytes, the row counter 256 bytes behind them.
+ * pfd_exchange_open().  pfd_exchange_bytes() is what the receive buffer + control words of one
+ * rank need; the control words start at pfd_exchange_control_offset() bytes.
  * These four allocate / map / free device memory (the decode entry points never do).
  */
 typedef struct pfd_ipc_handle { unsigned char bytes[64]; } pfd_ipc_handle;
 int64_t pfd_exchange_bytes(int32_t world, int64_t rows, int32_t head_dim);
-int64_t pfd_exchange_flags_offset(int32_t world, int64_t rows, int32_t head_dim);
+int64_t pfd_exchange_control_offset(int32_t world, int64_t rows, int32_t head_dim);
 int pfd_exchange_alloc(int64_t bytes, void** ptr, pfd_ipc_handle* handle);
 int pfd_exchange_open(const pfd_ipc_handle* handle, void** peer_ptr);
 int pfd_exchange_close(void* peer_ptr);
@@ -319,7 +321,7 @@ int pfd_resolve_slots(const int32_t* block_table, int64_t bt_stride_b, const int
  * Synchronises with the current device and reads (then clears) the error word the kernels set
  * when a bounded wait gave up: 0 = none, 1 = a TMA copy did not complete in time (the step's
  * output is then undefined), 2 = args->plan was made for other inputs (nothing was written),
- * 3 = a rank's flag of a KV-range exchange step did not arrive in time (nothing was merged).
+ * 3 = a rank's rows of a KV-range exchange step did not arrive in time (those rows were not merged).
  * The kernels never trap and never spin without a limit.
  */
 int pfd_device_status(int32_t* status);

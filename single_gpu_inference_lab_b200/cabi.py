@@ -35,7 +35,7 @@ EXPORTS = (
     "pfd_plan_decode",
     "pfd_exchange_merge",
     "pfd_exchange_bytes",
-    "pfd_exchange_flags_offset",
+    "pfd_exchange_control_offset",
     "pfd_exchange_alloc",
     "pfd_exchange_open",
     "pfd_exchange_close",
@@ -56,11 +56,8 @@ class Exchange(C.Structure):
     _fields_ = [
         ("world", C.c_int32),
         ("rank", C.c_int32),
-        ("step", C.c_int32),
-        ("reserved", C.c_int32),
         ("recv", C.c_void_p * 8),
-        ("flags", C.c_void_p * 8),
-        ("row_counter", C.c_void_p),
+        ("control", C.c_void_p),
     ]
 
 
@@ -308,16 +305,16 @@ def merge_packed(packed: torch.Tensor, output: torch.Tensor) -> None:
 
 
 def exchange_geometry(world: int, rows: int, head_dim: int) -> tuple[int, int]:
-    """(bytes of one rank's exchange memory, byte offset of its flag words); the row counter
-    sits 256 bytes behind the flags (``pfd_exchange_bytes`` / ``pfd_exchange_flags_offset``)."""
+    """(bytes of one rank's exchange memory, byte offset of its control words)
+    (``pfd_exchange_bytes`` / ``pfd_exchange_control_offset``)."""
     lib = load()
-    for fn in (lib.pfd_exchange_bytes, lib.pfd_exchange_flags_offset):
+    for fn in (lib.pfd_exchange_bytes, lib.pfd_exchange_control_offset):
         fn.argtypes = [C.c_int32, C.c_int64, C.c_int32]
         fn.restype = C.c_int64
     total = int(lib.pfd_exchange_bytes(world, rows, head_dim))
     if total < 0:
         raise RuntimeError(lib.pfd_last_error().decode())
-    return total, int(lib.pfd_exchange_flags_offset(world, rows, head_dim))
+    return total, int(lib.pfd_exchange_control_offset(world, rows, head_dim))
 
 
 def exchange_alloc(nbytes: int) -> tuple[int, bytes]:
@@ -357,8 +354,8 @@ def exchange_free(ptr: int) -> None:
 
 
 def exchange_merge(exchange: Exchange, output: torch.Tensor) -> None:
-    """``pfd_exchange_merge``: bounded wait for every rank's flag of ``exchange.step``, then the
-    LSE merge of this rank's receive buffer into ``output [B, Hq, D]``."""
+    """``pfd_exchange_merge``: bounded wait, row by row, for every rank's rows of the running step,
+    then the LSE merge of this rank's receive buffer into ``output [B, Hq, D]``."""
     lib = load()
     lib.pfd_exchange_merge.argtypes = [C.POINTER(Exchange), C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p]
     lib.pfd_exchange_merge.restype = C.c_int

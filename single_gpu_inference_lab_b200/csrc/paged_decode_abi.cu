@@ -433,16 +433,10 @@ pfd::KernelParams fill_params(const pfd_decode_args& a, int group, bool direct_o
     const pfd_exchange& x = *a.exchange;
     kp.xch_world = x.world;
     kp.xch_rank = x.rank;
-    kp.xch_half = x.step & 1;
-    kp.xch_step = x.step;
     kp.xch_rows = a.batch * a.num_q_heads;
-    for (int r = 0; r < x.world && r < 8; ++r) {
-      kp.xch_recv[r] = x.recv[r];
-      kp.xch_flags[r] = x.flags[r];
-    }
-    kp.xch_counter = x.row_counter;
-    // packed mode; kernels that know nothing of the exchange would at least fill the local slot
-    kp.packed_output = x.recv[x.rank] + ((int64_t)kp.xch_half * x.world + x.rank) * kp.xch_rows * (a.head_dim + 2);
+    for (int r = 0; r < x.world && r < 8; ++r) kp.xch_recv[r] = static_cast<unsigned long long*>(x.recv[r]);
+    kp.xch_control = static_cast<uint32_t*>(x.control);
+    kp.packed_output = static_cast<float*>(x.recv[x.rank]);  // non-NULL selects the packed form; the kernels address through xch_recv
     kp.output = nullptr;
   }
 #ifdef PFD_BOUNDS_CHECK
@@ -480,10 +474,10 @@ int decode_impl(const pfd_decode_args* args, int slot_offset) {
   if (!a.output && !a.packed_output && !a.exchange) return fail(PFD_ERR_INVALID, "no output given");
   if (a.exchange != nullptr) {
     const pfd_exchange& x = *a.exchange;
-    if (x.world < 1 || x.world > 8 || x.rank < 0 || x.rank >= x.world || x.step < 1 || !x.row_counter)
-      return fail(PFD_ERR_INVALID, "exchange: world 1..8, 0 <= rank < world, step >= 1 and a row counter are needed");
+    if (x.world < 1 || x.world > 8 || x.rank < 0 || x.rank >= x.world || !x.control)
+      return fail(PFD_ERR_INVALID, "exchange: world 1..8, 0 <= rank < world and the control words are needed");
     for (int r = 0; r < x.world; ++r)
-      if (!x.recv[r] || !x.flags[r]) return fail(PFD_ERR_INVALID, "exchange: recv / flags pointer of rank %d is NULL", r);
+      if (!x.recv[r]) return fail(PFD_ERR_INVALID, "exchange: recv pointer of rank %d is NULL", r);
     if (slot_offset != 0 || (a.flags & (PFD_FLAG_SINGLE_LAUNCH | PFD_FLAG_PARTIAL_ONLY)))
       return fail(PFD_ERR_UNSUPPORTED, "exchange: not with the shared-prefix pass, PFD_FLAG_SINGLE_LAUNCH or PFD_FLAG_PARTIAL_ONLY");
     int dev = 0, sms = 0;
@@ -974,15 +968,16 @@ int pfd_merge_packed(const float* packed, int32_t num_parts, int64_t rows, int32
   return check_launch("merge_packed kernel");
 }
 
-int64_t pfd_exchange_flags_offset(int32_t world, int64_t rows, int32_t head_dim) {
-  if (world < 1 || world > 8 || rows < 0 || head_dim <= 0) return fail(PFD_ERR_INVALID, "invalid exchange geometry");
-  const int64_t recv = 2LL * world * rows * (head_dim + 2) * (int64_t)sizeof(float);
+int64_t pfd_exchange_control_offset(int32_t world, int64_t rows, int32_t head_dim) {
+  if (world < 1 || world > 8 || rows < 0 || head_dim != 128) return fail(PFD_ERR_INVALID, "invalid exchange geometry");
+  static_assert(PFD_XCH_ROW == pfd::kXchRow, "row layout");
+  const int64_t recv = 2LL * world * rows * PFD_XCH_ROW * 8;
   return (recv + 255) / 256 * 256;
 }
 
 int64_t pfd_exchange_bytes(int32_t world, int64_t rows, int32_t head_dim) {
-  const int64_t off = pfd_exchange_flags_offset(world, rows, head_dim);
-  return off < 0 ? off : off + 512;  // flags [2][world] in the first 256 bytes, the row counter in the next
+  const int64_t off = pfd_exchange_control_offset(world, rows, head_dim);
+  return off < 0 ? off : off + 256;
 }
 
 int pfd_exchange_alloc(int64_t bytes, void** ptr, pfd_ipc_handle* handle) {
@@ -1030,15 +1025,17 @@ int pfd_exchange_merge(const pfd_exchange* exchange, int64_t rows, int32_t head_
                        int32_t out_dtype, void* stream) {
   if (exchange == nullptr || output == nullptr) return fail(PFD_ERR_INVALID, "NULL operand");
   const pfd_exchange& x = *exchange;
-  if (x.world < 1 || x.world > 8 || x.rank < 0 || x.rank >= x.world || x.step < 1)
-    return fail(PFD_ERR_INVALID, "exchange: world 1..8, 0 <= rank < world and step >= 1 are needed");
-  if (!x.recv[x.rank] || !x.flags[x.rank]) return fail(PFD_ERR_INVALID, "exchange: this rank's recv / flags pointer is NULL");
+  if (x.world < 1 || x.world > 8 || x.rank < 0 || x.rank >= x.world || !x.control)
+    return fail(PFD_ERR_INVALID, "exchange: world 1..8, 0 <= rank < world and the control words are needed");
+  if (!x.recv[x.rank]) return fail(PFD_ERR_INVALID, "exchange: this rank's recv pointer is NULL");
   if (head_dim != 128) return fail(PFD_ERR_UNSUPPORTED, "exchange: head_dim must be 128");
   if (out_dtype < PFD_DTYPE_F32 || out_dtype > PFD_DTYPE_BF16)
     return fail(PFD_ERR_INVALID, "output dtype must be f32, f16 or bf16");
   if (rows <= 0) return rows == 0 ? PFD_OK : fail(PFD_ERR_INVALID, "negative row count");
-  int32_t* status = nullptr;
-  if (int rc = status_pointer(&status)) return rc;
+  pfd::TmaParams tp{};
+  if (int rc = status_pointer(&tp.status)) return rc;
+  tp.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
+  tp.phase_times = g_phase_times;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(static_cast<unsigned>((rows + 3) / 4));
   cfg.blockDim = dim3(128);
@@ -1048,12 +1045,11 @@ int pfd_exchange_merge(const pfd_exchange* exchange, int64_t rows, int32_t head_
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const float* recv = x.recv[x.rank];
-  const int32_t* flags = x.flags[x.rank];
-  const int world = x.world, half = x.step & 1, step = x.step;
-  const unsigned long long limit = g_wait_limit_ns.load(std::memory_order_relaxed);
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, pfd::exchange_merge_kernel<128>, recv, flags, world, half, step, rows,
-                                           output, (int)out_dtype, status, limit);
+  const unsigned long long* recv = static_cast<const unsigned long long*>(x.recv[x.rank]);
+  uint32_t* control = static_cast<uint32_t*>(x.control);
+  const int world = x.world;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, pfd::exchange_merge_kernel<128>, recv, control, world, rows,
+                                           output, (int)out_dtype, tp);
   if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "exchange merge kernel launch failed: %s", cudaGetErrorString(e));
   return check_launch("exchange merge kernel");
 }

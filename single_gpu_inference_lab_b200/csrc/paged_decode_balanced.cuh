@@ -253,15 +253,21 @@ __device__ __forceinline__ void bal_step(BalState<NH>& st, uint32_t stage, const
 
 template <bool QBF16>
 __device__ __forceinline__ void store_row16(const KernelParams& p, int b, int hq, int d0, const float (&v)[16],
-                                            float m_nat, float l, bool write_ml) {
-  // 16 consecutive head-dim values of one (sequence, q head) row: final output or packed form
-  if (p.packed_output != nullptr) {
-    for (int dest = 0; dest < packed_dests(p); ++dest) {
-      float* dst = packed_row(p, dest, (int64_t)b * p.num_q_heads + hq) + d0;
+                                            float m_nat, float l, bool write_ml, uint32_t xstep) {
+  // 16 consecutive head-dim values of one (sequence, q head) row: final output, packed form, or
+  // tagged words into every rank's receive buffer
+  if (p.xch_world > 0) {
+    for (int dest = 0; dest < p.xch_world; ++dest) {
+      unsigned long long* dst = xch_row(p, dest, (int64_t)b * p.num_q_heads + hq, xstep);
 #pragma unroll
-      for (int t = 0; t < 16; t += 2) *reinterpret_cast<float2*>(dst + t) = make_float2(v[t], v[t + 1]);
-      if (write_ml) { dst[128 - d0] = m_nat; dst[129 - d0] = l; }
+      for (int t = 0; t < 16; t += 2) xch_store2(dst + d0 + t, v[t], v[t + 1], xstep);
+      if (write_ml) xch_store2(dst + 128, m_nat, l, xstep);
     }
+  } else if (p.packed_output != nullptr) {
+    float* dst = p.packed_output + ((int64_t)b * p.num_q_heads + hq) * 130 + d0;
+#pragma unroll
+    for (int t = 0; t < 16; t += 2) *reinterpret_cast<float2*>(dst + t) = make_float2(v[t], v[t + 1]);
+    if (write_ml) { dst[128 - d0] = m_nat; dst[129 - d0] = l; }
   } else {
     const float inv = 1.f / l;
     uint32_t w[8];
@@ -900,6 +906,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
   };
   __syncwarp();
   if (p.early_metadata) pdl_wait();
+  const uint32_t xstep = exchange_step(p);  // behind the wait: the previous step's merge advances it
 #pragma unroll
   for (int t = 0; t < NSTAGE; ++t)
     if (t < n) fire(t, ids_cur, 0);
@@ -1054,7 +1061,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
           v[2 * mt + 1] = st.o[0][mt][2 + c] * vs;
         }
         if (whole) {
-          store_row16<QBF16>(p, cur.b, hq, 16 * i, v, st.m[0][c] * kLn2, lsum[c], i == 0);
+          store_row16<QBF16>(p, cur.b, hq, 16 * i, v, st.m[0][c] * kLn2, lsum[c], i == 0, xstep);
         } else {
           const int64_t r = chunk_slot_row(grp, which, p.num_q_heads, hq);
           float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.partial_output) + r * D + 16 * i);
@@ -1067,7 +1074,6 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
         }
       }
     }
-    if (whole && p.packed_output != nullptr) packed_rows_done(p, p.group, lane);
     if constexpr (FUSED) if (!whole) {
       // Publish the piece, then count this warp's pairs of the sequence in: the warp that
       // completes the count finds every other piece in L2 and writes the final rows.
@@ -1227,6 +1233,7 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
     big = m_new;
   };
   pdl_wait();  // the chunk kernel's stores are complete and visible from here on
+  const uint32_t xstep = exchange_step(p);  // issued here, needed only when the row is stored
   mark_phase_at(tp, cp.num_warps + blockIdx.x, 6, threadIdx.x == 0);  // chunk kernel complete
   if (WPR == 1 && ns <= 4) {
     if (ns > 0) round(std::integral_constant<int, 4>{}, 0);
@@ -1253,14 +1260,21 @@ paged_decode_chunk_merge_kernel(const KernelParams p, const TmaParams tp, const 
     }
     big = m_all;
   }
-  if (p.packed_output != nullptr) {
-    for (int dest = 0; dest < packed_dests(p); ++dest) {
-      float* dst = packed_row(p, dest, row);
-      *reinterpret_cast<float2*>(dst + lane * E) = make_float2(acc[0], acc[1]);
-      *reinterpret_cast<float2*>(dst + lane * E + 2) = make_float2(acc[2], acc[3]);
-      if (lane == 0) { dst[D] = big; dst[D + 1] = den; }
+  if (p.xch_world > 0) {
+    for (int dest = 0; dest < p.xch_world; ++dest) {
+      unsigned long long* dst = xch_row(p, dest, row, xstep);
+      xch_store2(dst + lane * E, acc[0], acc[1], xstep);
+      xch_store2(dst + lane * E + 2, acc[2], acc[3], xstep);
+      if (lane == 0) xch_store2(dst + D, big, den, xstep);
     }
-    packed_rows_done(p, 1, lane);
+    mark_phase_at(tp, cp.num_warps + blockIdx.x, 7, threadIdx.x == 0);  // merged and sent
+    return;
+  }
+  if (p.packed_output != nullptr) {
+    float* dst = p.packed_output + (int64_t)row * (D + 2);
+    *reinterpret_cast<float2*>(dst + lane * E) = make_float2(acc[0], acc[1]);
+    *reinterpret_cast<float2*>(dst + lane * E + 2) = make_float2(acc[2], acc[3]);
+    if (lane == 0) { dst[D] = big; dst[D + 1] = den; }
     return;
   }
   mark_phase_at(tp, cp.num_warps + blockIdx.x, 7, threadIdx.x == 0);  // merged

@@ -59,13 +59,16 @@ struct KernelParams {
   int32_t early_metadata;  // 1: seq_lens and block_table may be read before the preceding kernel has completed
   int32_t kv_evict_first;  // 1: K/V tiles are loaded with the L2 evict-first hint
   // KV-range exchange (xch_world > 0): the packed (o, m, l) rows of this rank go, instead of to
-  // packed_output, into slot xch_rank of every rank's receive buffer [2][world][rows][D + 2]
-  // (half xch_half), with plain stores over NVLink; the warp that stores the last row releases
-  // the step's flag in every rank's flag array [2][world].
-  int32_t xch_world, xch_rank, xch_half, xch_step, xch_rows;
-  float* xch_recv[8];
-  int32_t* xch_flags[8];
-  int32_t* xch_counter;    // local: rows stored so far in this step, zero between steps
+  // packed_output, into slot xch_rank of every rank's receive buffer [2][world][rows][kXchRow]
+  // (8-byte words) with plain stores over NVLink.  Every word carries its value in the low and
+  // the step's tag in the high half, and an aligned 8-byte store arrives whole: the receiver
+  // polls the words themselves, so no fence, flag or counter is needed (the low-latency
+  // protocol of collective libraries).  The step's tag is device-resident (a replayed CUDA
+  // graph carries no per-step arguments): xch_control[0] counts the completed steps, the tag is
+  // that count + 1 and its lowest bit picks the half of the buffers.
+  int32_t xch_world, xch_rank, xch_rows;
+  unsigned long long* xch_recv[8];
+  uint32_t* xch_control;   // local: [0] steps completed, [1] merge CTAs done
 #ifdef PFD_BOUNDS_CHECK
   int64_t dbg_ws_rows;     // self-checking builds: rows of the workspace, sequences of the batch
   int32_t dbg_batch;
@@ -80,36 +83,30 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ---- KV-range exchange: where packed rows go, and the hand-over to the other ranks ----------
-__device__ __forceinline__ void st_release_sys(int32_t* p, int32_t v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// A row of a receive buffer: o[128], m, l, one tagged 8-byte word each.
+constexpr int kXchRow = 130;
+__device__ __forceinline__ unsigned long long xch_word(float v, uint32_t tag) {
+  return (unsigned long long)__float_as_uint(v) | ((unsigned long long)tag << 32);
 }
-__device__ __forceinline__ int32_t ld_acquire_sys(const int32_t* p) {
-  int32_t v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
+__device__ __forceinline__ void xch_store2(unsigned long long* p, float a, float b, uint32_t tag) {
+  asm volatile("st.relaxed.sys.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(xch_word(a, tag)), "l"(xch_word(b, tag))
+               : "memory");
 }
-// Number of copies of a packed row, and where copy `dest` of row `row` (of D + 2 = 130 floats) goes.
-__device__ __forceinline__ int packed_dests(const KernelParams& p) { return p.xch_world > 0 ? p.xch_world : 1; }
-__device__ __forceinline__ float* packed_row(const KernelParams& p, int dest, int64_t row) {
-  if (p.xch_world == 0) return p.packed_output + row * 130;
-  return p.xch_recv[dest] + (((int64_t)p.xch_half * p.xch_world + p.xch_rank) * p.xch_rows + row) * 130;
+// Two tagged words; false while either has not arrived.
+__device__ __forceinline__ bool xch_load2(const unsigned long long* p, uint32_t tag, float& a, float& b) {
+  unsigned long long x, y;
+  asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(x), "=l"(y) : "l"(p) : "memory");
+  a = __uint_as_float((uint32_t)x);
+  b = __uint_as_float((uint32_t)y);
+  return (uint32_t)(x >> 32) == tag && (uint32_t)(y >> 32) == tag;
 }
-// A warp has stored `rows` packed rows in every destination.  With an exchange: make them visible
-// system-wide, count them, and let the warp that completes the step's rows release the flags.
-// Nobody waits here; the receiving side's wait is in exchange_merge_kernel.
-__device__ __forceinline__ void packed_rows_done(const KernelParams& p, int rows, int lane) {
-  if (p.xch_world == 0) return;
-  __threadfence_system();
-  __syncwarp();
-  if (lane == 0) {
-    const int before = atomicAdd(p.xch_counter, rows);
-    if (before + rows == p.xch_rows) {
-      atomicExch(p.xch_counter, 0);  // ready for the next step
-      __threadfence_system();
-      for (int d = 0; d < p.xch_world; ++d)
-        st_release_sys(p.xch_flags[d] + p.xch_half * p.xch_world + p.xch_rank, p.xch_step);
-    }
-  }
+// Tag of the exchange step this grid belongs to (0 without an exchange).  Read it after the
+// grid's programmatic-dependency wait: the previous step's merge kernel advances the count.
+__device__ __forceinline__ uint32_t exchange_step(const KernelParams& p) {
+  return p.xch_world > 0 ? __ldcg(p.xch_control) + 1u : 0u;
+}
+__device__ __forceinline__ unsigned long long* xch_row(const KernelParams& p, int dest, int64_t row, uint32_t step) {
+  return p.xch_recv[dest] + (((int64_t)(step & 1u) * p.xch_world + p.xch_rank) * p.xch_rows + row) * kXchRow;
 }
 
 // The one address function every kernel uses for "which cache slot holds token t of
@@ -602,7 +599,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
   return false;
 }
-// 4-D tiled TMA load of one (page, kv head) tile: no multicast, CTA-local destination.
+// 4-D tiled TMA load of one (page, kv head) tile: CTA-local destination, every CTA issues its own copies.
 __device__ __forceinline__ void tma_load_tile(uint32_t dst, const void* tmap, uint32_t bar, int c1,
                                               int c2, int c3) {
   asm volatile(
@@ -1070,64 +1067,84 @@ merge_packed_kernel(const float* __restrict__ packed, int parts, int64_t rows, v
 
 constexpr int kErrPeerTimeout = 3;
 
-// Receiving side of the KV-range exchange: waits until every rank's flag of this step has arrived
-// in this rank's flag array (the other GPUs' kernels release them; this GPU's own kernels have
-// completed by then, the grid being their programmatic dependent), then merges the `world` packed
-// partials of each row from this rank's receive buffer.  The wait is bounded in time: when it
-// runs out the error word is set, nothing is merged and the kernel ends.  One warp per row.
+// Receiving side of the KV-range exchange, one warp per row: the warp polls rank s's copy of the
+// row in this rank's receive buffer until every word it needs carries this step's tag (the other
+// GPUs' kernels store them; this GPU's own kernels have completed by then, the grid being their
+// programmatic dependent), folds it into the running LSE merge and goes on to rank s + 1.  The
+// wait is bounded in time: when it runs out the error word is set and the row is left alone.
+// Either way the CTA that finishes last advances the count of completed steps.
 template <int D>
 __global__ void __launch_bounds__(128)
-exchange_merge_kernel(const float* __restrict__ recv, const int32_t* __restrict__ flags, int world, int half,
-                      int step, int64_t rows, void* output, int out_dtype, int32_t* status,
-                      unsigned long long wait_limit_ns) {
-  pdl_wait();  // this GPU's own rows and flag are in place: from here on only other GPUs are waited for
-  __shared__ int sh_ok;
-  if (threadIdx.x == 0) sh_ok = 1;
-  __syncthreads();
-  if ((int)threadIdx.x < world) {
-    const int32_t* f = flags + half * world + threadIdx.x;
-    bool ok = ld_acquire_sys(f) == step;
-    if (!ok) {
-      const unsigned long long t0 = global_timer_ns();
-      for (uint32_t spin = 0; spin < kSpinLimit && !ok; ++spin) {
-        ok = ld_acquire_sys(f) == step;
-        if (!ok && global_timer_ns() - t0 > wait_limit_ns) break;
-      }
-    }
-    if (!ok) { sh_ok = 0; atomicExch(status, kErrPeerTimeout); }
-  }
-  __syncthreads();
-  if (!sh_ok) return;
-  __threadfence_system();
+exchange_merge_kernel(const unsigned long long* __restrict__ recv, uint32_t* control, int world, int64_t rows,
+                      void* output, int out_dtype, TmaParams tp) {
+  static_assert(D == 128, "row layout");
+  constexpr int kStampBase = 148 * 8 + 4096;  // rows of the stamp buffer (tuning builds only)
+  mark_phase_at(tp, kStampBase + blockIdx.x, 0, threadIdx.x == 0);
+  // The next kernel in the stream may be set up while this one waits for the other GPUs; whatever
+  // it does before its own dependency wait touches nothing this grid reads or writes.
+  pdl_launch_dependents();
+  pdl_wait();  // this GPU's own rows are in place: from here on only other GPUs are waited for
+  mark_phase_at(tp, kStampBase + blockIdx.x, 1, threadIdx.x == 0);
+  const uint32_t step = __ldcg(control) + 1u;
   const int64_t row = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (row >= rows) return;
-  constexpr int E = D / 32;
-  const float* base = recv + (int64_t)half * world * rows * (D + 2);
-  float big = -INFINITY;
-  for (int s = lane; s < world; s += 32) big = fmaxf(big, __ldcg(base + ((int64_t)s * rows + row) * (D + 2) + D));
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, off));
-  float acc[E];
-#pragma unroll
-  for (int e = 0; e < E; ++e) acc[e] = 0.f;
-  float den = 0.f;
-  for (int s = 0; s < world; ++s) {
-    const float* src = base + ((int64_t)s * rows + row) * (D + 2);
-    const float m = __ldcg(src + D);
-    const float c = (m == -INFINITY) ? 0.f : expf(m - big);
-    den += __ldcg(src + D + 1) * c;
-#pragma unroll
-    for (int e = 0; e < E; ++e) acc[e] += c * __ldcg(src + lane * E + e);
+  if (row < rows) {
+    const unsigned long long* base = recv + ((int64_t)(step & 1u) * world * rows + row) * kXchRow;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    float big = -INFINITY, den = 0.f;
+    bool complete = true;
+    unsigned long long t0 = 0;
+    for (int s = 0; s < world && complete; ++s) {
+      const unsigned long long* src = base + (int64_t)s * rows * kXchRow;
+      float4 x;
+      float m, l;
+      bool here = false;
+      for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+        bool ok = xch_load2(src + lane * 4, step, x.x, x.y);
+        ok = xch_load2(src + lane * 4 + 2, step, x.z, x.w) && ok;
+        ok = xch_load2(src + D, step, m, l) && ok;
+        here = __all_sync(0xffffffffu, ok);
+        if (here) break;
+        const unsigned long long now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        if (__any_sync(0xffffffffu, now - t0 > tp.wait_limit_ns)) break;
+      }
+      if (!here) { complete = false; break; }
+      const float m_new = fmaxf(big, m);
+      const float c_old = (big == -INFINITY) ? 0.f : expf(big - m_new);
+      const float c = (m == -INFINITY) ? 0.f : expf(m - m_new);
+      den = den * c_old + l * c;
+      acc.x = acc.x * c_old + c * x.x; acc.y = acc.y * c_old + c * x.y;
+      acc.z = acc.z * c_old + c * x.z; acc.w = acc.w * c_old + c * x.w;
+      big = m_new;
+    }
+    if (complete) {
+      mark_phase_at(tp, kStampBase + blockIdx.x, 2, threadIdx.x == 0);
+      const float inv = den > 0.f ? 1.f / den : 0.f;
+      acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv;
+      const int64_t idx = row * D + lane * 4;
+      if (out_dtype == 0) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(output) + idx) = acc;
+      } else if (out_dtype == 1) {
+        const uint2 v = make_uint2(pack_f16x2(acc.x, acc.y), pack_f16x2(acc.z, acc.w));
+        *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(output) + idx) = v;
+      } else {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+        const uint2 v = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(output) + idx) = v;
+      }
+    } else if (lane == 0) {
+      atomicExch(tp.status, kErrPeerTimeout);
+    }
   }
-  const float inv = den > 0.f ? 1.f / den : 0.f;
-#pragma unroll
-  for (int e = 0; e < E; ++e) {
-    const float v = acc[e] * inv;
-    const int64_t idx = row * D + lane * E + e;
-    if (out_dtype == 0) reinterpret_cast<float*>(output)[idx] = v;
-    else if (out_dtype == 1) reinterpret_cast<__half*>(output)[idx] = __float2half_rn(v);
-    else reinterpret_cast<__nv_bfloat16*>(output)[idx] = __float2bfloat16_rn(v);
+  // every warp of the grid has read the step count above; the last CTA to get here advances it
+  __syncthreads();
+  mark_phase_at(tp, kStampBase + blockIdx.x, 3, threadIdx.x == 0);
+  if (threadIdx.x == 0) {
+    if (atomicAdd(control + 1, 1u) == gridDim.x - 1) {
+      atomicExch(control + 1, 0u);
+      atomicAdd(control, 1u);
+    }
   }
 }
 

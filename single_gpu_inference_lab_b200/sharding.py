@@ -12,8 +12,8 @@ below are the natural shardings of its operator:
   rank's records and applies the same LSE merge the single-GPU split-KV path uses (reference
   maths: integrations/vllm/l20_paged_split_kv.py:459-488).  Two forms of the exchange:
   ``KvRangeExchange`` -- the decode kernels store their rows straight into every rank's receive
-  buffer over NVLink and release a step-tagged flag, the merge kernel waits (bounded) for the
-  flags: no collective call; and ``kv_range_decode`` -- ``packed_output`` plus one
+  buffer over NVLink and tag each row with the step, the merge kernel waits (bounded) for the
+  tags: no collective call; and ``kv_range_decode`` -- ``packed_output`` plus one
   ``all_gather_into_tensor``, the fallback where peer mappings are not to be had (and on CPU
   ranks in tests).
 
@@ -148,7 +148,7 @@ def kv_range_decode(
 
 
 class KvRangeExchange:
-    """Receive buffers, flags and peer mappings of the in-kernel KV-range exchange
+    """Receive buffers and peer mappings of the in-kernel KV-range exchange
     (``pfd_exchange`` of include/paged_fp8_decode.h) for a fixed ``[B, Hq, D]`` step shape.
 
     ``KvRangeExchange.create`` is the multi-process form: every rank allocates its own memory,
@@ -164,15 +164,13 @@ class KvRangeExchange:
         self.rank, self.world, self.rows, self.head_dim = rank, world, rows, head_dim
         self.device = device
         self._owned, self._opened = owned, opened
-        _, flags_off = cabi.exchange_geometry(world, rows, head_dim)
+        _, control_off = cabi.exchange_geometry(world, rows, head_dim)
         x = cabi.Exchange()
-        x.world, x.rank, x.step = world, rank, 0
+        x.world, x.rank = world, rank
         for r in range(world):
             x.recv[r] = bases[r]
-            x.flags[r] = bases[r] + flags_off
-        x.row_counter = bases[rank] + flags_off + 256
+        x.control = bases[rank] + control_off
         self.struct = x
-        self.step = 0
 
     @classmethod
     def create(cls, batch: int, num_q_heads: int, head_dim: int, device, group=None) -> "KvRangeExchange":
@@ -203,12 +201,6 @@ class KvRangeExchange:
         with torch.cuda.device(device):
             bases = [cabi.exchange_alloc(nbytes)[0] for _ in range(world)]
         return [cls(r, world, rows, head_dim, bases, bases[r], [], torch.device(device)) for r in range(world)]
-
-    def next_step(self) -> int:
-        """Advance the step tag (every rank calls this once per decode step, in step)."""
-        self.step += 1
-        self.struct.step = self.step
-        return self.step
 
     def decode(self, local: PagedDecodeInputs, *, split_size: int, workspace, plan=None, flags: int = 0) -> None:
         """This rank's range through the operator; its packed rows go to every rank."""
@@ -245,13 +237,14 @@ def kv_range_decode_exchange(
     flags: int = 0, output: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """One decode step of a KV-range-sharded batch with the exchange inside the kernels: two calls,
-    no collective.  Every rank must call it once per step.  Returns ``[B, Hq, D]``."""
+    no collective, nothing per step on the host (the step count lives on the device, so the pair
+    can be captured in a CUDA graph and replayed).  Every rank must call it once per step.
+    Returns ``[B, Hq, D]``."""
     from .l20_paged_split_kv import allocate_l20_paged_split_kv_workspace
 
     if workspace is None:
         workspace = allocate_l20_paged_split_kv_workspace(local.query, max(local.max_seq_len, 1), split_size=split_size)
     if output is None:
         output = torch.empty_like(local.query)
-    exchange.next_step()
     exchange.decode(local, split_size=split_size, workspace=workspace, plan=plan, flags=flags)
     return exchange.merge(output)

@@ -55,8 +55,6 @@ def test_exchange_matches_oracle_over_several_steps(built_libs, world, flags, pl
     try:
         for step in range(4):  # both halves of the buffers twice, the row counter reset three times
             outs = [torch.full_like(l.query, float("nan")) for l in locals_]
-            for x in ranks:
-                x.next_step()
             for x, l, ws, plan in zip(ranks, locals_, wss, plans):
                 x.decode(l, split_size=split, workspace=ws, plan=plan, flags=flags)
             for x, o in zip(ranks, outs):
@@ -93,8 +91,6 @@ def test_exchange_with_uneven_lengths_and_empty_ranges(built_libs):
     try:
         for step in range(3):
             outs = [torch.full_like(l.query, float("nan")) for l in locals_]
-            for x in ranks:
-                x.next_step()
             for x, l in zip(ranks, locals_):
                 x.decode(l, split_size=128, workspace=_workspace(l, 128), flags=EARLY)
             for x, o in zip(ranks, outs):
@@ -102,6 +98,44 @@ def test_exchange_with_uneven_lengths_and_empty_ranges(built_libs):
             assert cabi.device_status() == 0
             for r, o in enumerate(outs):
                 assert_within_gate(o, exp, f"step {step} rank {r}")
+    finally:
+        for x in ranks:
+            x.close()
+
+
+def test_exchange_steps_replayed_from_a_cuda_graph(built_libs):
+    """The step's tag is device-resident: one captured step (every rank's decode, every rank's
+    merge) is right on every replay, fresh KV each time."""
+    from single_gpu_inference_lab_b200 import cabi
+
+    cabi.load()
+    w, exp, locals_, ranks = _setup(2, "llama3-8b-long-b4", seed=6, batch=2, shrink=1 / 32)
+    split = 256
+    wss = [_workspace(l, split) for l in locals_]
+    outs = [torch.empty_like(l.query) for l in locals_]
+    try:
+        def one_step():
+            for x, l, ws in zip(ranks, locals_, wss):
+                x.decode(l, split_size=split, workspace=ws, flags=EARLY)
+            for x, o in zip(ranks, outs):
+                x.merge(o)
+
+        one_step()  # an odd number of eager steps first: replays then begin on the other half
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side), torch.cuda.graph(g, stream=side):
+            one_step()
+            one_step()
+            one_step()
+        for replay in range(4):
+            for o in outs:
+                o.fill_(float("nan"))
+            g.replay()
+            torch.cuda.synchronize()
+            assert cabi.device_status() == 0
+            for r, o in enumerate(outs):
+                assert_within_gate(o, exp, f"replay {replay} rank {r}")
     finally:
         for x in ranks:
             x.close()
@@ -116,9 +150,10 @@ def test_exchange_refusals(built_libs):
     ws = _workspace(l, 128)
     common = dict(k_scale=l.k_scale, v_scale=l.v_scale, max_seq_len=l.max_seq_len, split_size=128, workspace=ws)
     try:
-        with pytest.raises(RuntimeError, match="step >= 1"):
-            cabi.paged_decode_fp8_e4m3_split_out(l.query, l.key_cache, l.value_cache, l.block_table, l.seq_lens, exchange=x.struct, **common)
-        x.next_step()
+        broken = cabi.Exchange.from_buffer_copy(x.struct)
+        broken.control = None
+        with pytest.raises(RuntimeError, match="control words"):
+            cabi.paged_decode_fp8_e4m3_split_out(l.query, l.key_cache, l.value_cache, l.block_table, l.seq_lens, exchange=broken, **common)
         with pytest.raises(RuntimeError, match="exchange: needs the balanced kernel"):
             cabi.paged_decode_fp8_e4m3_split_out(l.query, l.key_cache, l.value_cache, l.block_table, l.seq_lens, exchange=x.struct,
                                                  flags=cabi.PFD_FLAG_FIXED_SPLITS, **common)
@@ -141,14 +176,11 @@ def test_a_rank_that_does_not_publish_ends_the_wait_with_a_status(built_libs):
 
     def step(skip=None):
         outs = [torch.full_like(l.query, 7.0) for l in locals_]
-        for x in ranks:
-            x.next_step()
         for r, (x, l, ws) in enumerate(zip(ranks, locals_, wss)):
             if r != skip:
                 x.decode(l, split_size=split, workspace=ws)
-        for r, (x, o) in enumerate(zip(ranks, outs)):
-            if r != skip:
-                x.merge(o)
+        for x, o in zip(ranks, outs):
+            x.merge(o)  # every rank, or the ranks' step counts part
         return outs
 
     try:
@@ -159,7 +191,7 @@ def test_a_rank_that_does_not_publish_ends_the_wait_with_a_status(built_libs):
         try:
             outs = step(skip=1)  # rank 1 is not asked to store: its flag never arrives
             assert cabi.device_status() == 3
-            assert bool((outs[0] == 7.0).all()), "nothing is merged when a flag is missing"
+            assert all(bool((o == 7.0).all()) for o in outs), "nothing is merged when a flag is missing"
             assert cabi.device_status() == 0, "reading the status clears it"
         finally:
             cabi.set_wait_limit_ns(200_000_000)  # the library's default

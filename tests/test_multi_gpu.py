@@ -105,7 +105,6 @@ for step in range(6):
 # the failure: rank 1 is not asked to store in this step, so its flag arrives nowhere
 torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
 cabi.set_wait_limit_ns(50_000_000)
-x.next_step()
 out = torch.full_like(local.query, 7.0)
 if rank != 1:
     x.decode(local, split_size=split, workspace=ws)
