@@ -612,8 +612,9 @@ def main() -> int:
 
     q_bytes, t_bytes, l_bytes = q.numel() * q.element_size(), w.block_table.numel() * 4, w.seq_lens.numel() * 4
     off_t, off_l = aligned(q_bytes), aligned(q_bytes) + aligned(t_bytes)
+    # two sets of buffers: the inputs of step i + 1 cross PCIe on a copy stream while step i computes
     host_in = torch.empty(off_l + aligned(l_bytes), dtype=torch.uint8).pin_memory()
-    dev_in = torch.empty_like(host_in, device=dev)
+    dev_ins = [torch.empty_like(host_in, device=dev) for _ in range(2)]
 
     def views(buf):
         return (buf[:q_bytes].view(q.dtype).view(q.shape),
@@ -622,15 +623,17 @@ def main() -> int:
 
     hq_v, ht_v, hl_v = views(host_in)
     hq_v.copy_(q.cpu()); ht_v.copy_(w.block_table.cpu()); hl_v.copy_(w.seq_lens.cpu())
-    dq, dtable, dlens = views(dev_in)
-    host_out = torch.empty(q.shape, dtype=q.dtype).pin_memory()
+    dev_views = [views(b) for b in dev_ins]
+    host_outs = [torch.empty(q.shape, dtype=q.dtype).pin_memory() for _ in range(2)]
     h2d = q_bytes + t_bytes + l_bytes
-    d2h = host_out.numel() * host_out.element_size()
+    d2h = host_outs[0].numel() * host_outs[0].element_size()
     stream = torch.cuda.current_stream()
+    copy_stream = torch.cuda.Stream()
+    in_ready = [torch.cuda.Event() for _ in range(2)]
+    out_ready = [torch.cuda.Event() for _ in range(2)]
     split, pools, ws = case.split, case.pools, case.ws
 
-    def e2e_step(i: int):
-        dev_in.copy_(host_in, non_blocking=True)
+    def e2e_call(i: int, dq, dtable, dlens):
         kc, vc = case.kcs[i % pools], case.vcs[i % pools]
         if mode == "kv-range":
             local = w.__class__(**{**w.__dict__, "query": dq, "block_table": dtable, "seq_lens": dlens,
@@ -655,15 +658,53 @@ def main() -> int:
             res = l20_paged_split_kv.l20_paged_split_kv_attention_fp8(
                 dq, kc, vc, dtable, dlens, k_scale=w.k_scale, v_scale=w.v_scale,
                 max_seq_len=w.max_seq_len, split_size=split, workspace=ws)
-        host_out.copy_(res, non_blocking=True)
+        return res
+
+    def e2e_serial_step(i: int):
+        """Copy in, compute, copy out, wait: nothing of one step overlaps the next."""
+        dev_ins[0].copy_(host_in, non_blocking=True)
+        host_outs[0].copy_(e2e_call(i, *dev_views[0]), non_blocking=True)
         stream.synchronize()  # the host consumes the step's result
+
+    def stage_inputs(slot: int):
+        """Host-to-device copy of one step's inputs, on the copy stream."""
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(out_ready[slot])  # the step that last read this buffer is done
+            dev_ins[slot].copy_(host_in, non_blocking=True)
+            in_ready[slot].record(copy_stream)
+
+    counter = [0]
+
+    def e2e_step(_i: int):
+        """Every step has its own copy in, call, copy out and host read of its result, but the
+        steps overlap as in an engine that schedules asynchronously: the inputs of step i + 1
+        cross PCIe on the copy stream while step i computes, and the host reads the result of
+        step i - 1 (waits for its copy out) after it has enqueued step i."""
+        i = counter[0]
+        counter[0] += 1
+        slot = i & 1
+        stream.wait_event(in_ready[slot])
+        host_outs[slot].copy_(e2e_call(i, *dev_views[slot]), non_blocking=True)
+        out_ready[slot].record(stream)
+        stage_inputs(slot ^ 1)
+        if i > 0:
+            out_ready[slot ^ 1].synchronize()  # the host consumes the previous step's result
+
+    def e2e_drain():
+        out_ready[(counter[0] - 1) & 1].synchronize()
 
     # -------- the headline workload, under clock sampling
     with ClockSampler(local_rank) as clocks:
         res = case.measure(args.steps, args.warmup, args.repeats, check=True)
         for i in range(3):
+            e2e_serial_step(i)
+        ms_e2e_serial = case.timed_eager(e2e_serial_step, args.steps)
+        stage_inputs(0)
+        for i in range(4):
             e2e_step(i)
-        ms_e2e = case.timed_eager(e2e_step, args.steps)
+        e2e_drain()
+        ms_e2e = case.timed_eager(e2e_step, args.steps)  # (the barrier behind the K steps waits for the last result)
+        torch.cuda.synchronize()
         ms_eager = case.timed_eager(case.step, args.steps)
 
     total_bytes = torch.tensor([float(case.kv_bytes)], device=dev, dtype=torch.float64)
@@ -734,7 +775,11 @@ def main() -> int:
                          "what": "an unrelated ordinary kernel between steps (its own time subtracted): no overlap of a "
                                  "step's prologue with the previous step's tail"},
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "us_per_layer_step": round(ms_e2e * 1e3, 3)},
+                    "us_per_layer_step": round(ms_e2e * 1e3, 3),
+                    "pipeline": "two buffers, asynchronous scheduling: step i + 1's inputs are copied in on a second stream "
+                                "while step i computes, and the host reads step i - 1's result after enqueueing step i; "
+                                "every step has its own copy in, call, copy out and host read",
+                    "serial_us_per_layer_step": round(ms_e2e_serial * 1e3, 3)},
             "gpu_launches": int(res["launches_per_step"] * args.steps),
             "timing": "K steps replayed from CUDA graphs, CUDA events around the replays, median of `repeats` runs; eager launch loop beside it",
             "us_per_layer_step_eager_launch": round(ms_eager * 1e3, 3),

@@ -285,7 +285,7 @@ int pfd_merge_packed(const float* packed, int32_t num_parts, int64_t rows, int32
  * Receiving side of a KV-range exchange step: one kernel on `stream` (enqueue it behind the decode
  * call of the same step), one warp per row, that waits until the words of all `world` ranks' copies
  * of the row in this rank's receive buffer carry the step's tag -- at most the wait limit
- * (pfd_set_wait_limit_ns); on expiry device status 3 is set and the row is left alone -- and then
+ * (pfd_set_wait_limit_ns); on expiry device status 4 is set and the row is left alone -- and then
  * LSE-merges the `world` packed partials of the row into output [rows, head_dim] of `out_dtype`.
  * Same maths as pfd_merge_packed.
  */
@@ -308,6 +308,48 @@ int pfd_exchange_close(void* peer_ptr);
 int pfd_exchange_free(void* ptr);
 
 /*
+ * Shared-prefix groups of a decode batch, found on the device (three small kernels on `stream`,
+ * no host copy): requests whose first `prefix length` tokens sit in the same pages.  Same key and
+ * the same filters as the reference's host-side find_l20_shared_prefix_groups
+ * (integrations/vllm/l20_shared_prefix_decode_dispatch.py:41-76): (prefix length, chain of the
+ * prefix's block ids); prefixes shorter than min_prefix_len and groups of fewer than min_batch
+ * requests are dropped; groups are numbered by their first member, members ascend.  The prefix
+ * length of row b is prefix_lengths[b] (device int32), or uniform_prefix_len when that is NULL
+ * and this positive, or else floor(min(seq_lens) / 16) * 16 (the candidate of the reference's
+ * trace_l20_shared_prefix_decode_candidate, :245-315).  Unlike the reference, which dispatches
+ * only when one group spans the batch, any number of groups (up to max_groups; later ones are
+ * left out) plus requests in no group come out.
+ *
+ * `groups` (device, pfd_prefix_groups_bytes() bytes) as int32 words: [0] magic, [1] batch,
+ * [2] max_groups, [3] number of groups, [4] rows in groups, [5..7] 0, then row_prefix_len[batch]
+ * (0 = in no group), row_group[batch] (-1 = none), group_offsets[max_groups + 1],
+ * group_prefix_len[max_groups], group_rows[batch] (group g's requests are
+ * group_rows[group_offsets[g] .. group_offsets[g + 1])), then scratch.  batch <= 2048.
+ */
+int64_t pfd_prefix_groups_bytes(int32_t batch, int32_t max_groups);
+int pfd_group_shared_prefixes(const int32_t* block_table, int64_t bt_stride_b, int32_t bt_cols,
+                              const int32_t* prefix_lengths, int32_t uniform_prefix_len, const int32_t* seq_lens,
+                              int32_t batch, int32_t min_batch, int32_t min_prefix_len, int32_t max_groups,
+                              void* groups, int64_t groups_bytes, void* stream);
+
+/*
+ * Decode step of a batch with any number of shared-prefix groups (and requests in none), all
+ * decided on the device: `groups` is the buffer pfd_group_shared_prefixes() filled for this batch
+ * (same batch size, same max_groups; made once per model step, read by every layer's call).  The
+ * dense tensor-core pass runs per group over the group's request list, the split-KV pass covers
+ * every request from the end of its group's prefix (from token 0 for a request in no group), one
+ * merge.  A prefix is used up to a multiple of 16 tokens and up to min(max_prefix_len,
+ * max_seq_len); what lies beyond goes through the split-KV pass, so any bound is safe and a
+ * tight one saves idle CTAs.  Every member of a group must be at least as long as the group's
+ * prefix.  The workspace needs ceil(min(max_prefix_len, max_seq_len) / 256) +
+ * ceil(max_seq_len / split_size) slots on its split axis.  The reference has no counterpart: its
+ * dispatch stops at one group spanning the batch
+ * (integrations/vllm/l20_shared_prefix_decode_dispatch.py:122-159).
+ */
+int pfd_shared_prefix_decode_grouped_fp8_e4m3(const pfd_decode_args* args, const void* groups, int32_t max_groups,
+                                              int32_t max_prefix_len);
+
+/*
  * Debug / parity entry: writes, for every (sequence, token < max_seq_len), the cache slot
  * index page*16 + token%16 that the kernels' address function resolves (-1 beyond the
  * sequence) into slots[batch, max_seq_len] (int64).  Counterpart of the gather
@@ -321,7 +363,8 @@ int pfd_resolve_slots(const int32_t* block_table, int64_t bt_stride_b, const int
  * Synchronises with the current device and reads (then clears) the error word the kernels set
  * when a bounded wait gave up: 0 = none, 1 = a TMA copy did not complete in time (the step's
  * output is then undefined), 2 = args->plan was made for other inputs (nothing was written),
- * 3 = a rank's rows of a KV-range exchange step did not arrive in time (those rows were not merged).
+ * 3 = the tensor cores of the dense shared-prefix pass did not complete in time (output undefined),
+ * 4 = a rank's rows of a KV-range exchange step did not arrive in time (those rows were not merged).
  * The kernels never trap and never spin without a limit.
  */
 int pfd_device_status(int32_t* status);

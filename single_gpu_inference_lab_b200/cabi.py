@@ -27,6 +27,9 @@ EXPORTS = (
     "pfd_paged_decode_fp8_e4m3_split_out_noalloc",
     "pfd_paged_decode_kv16_split_out",
     "pfd_shared_prefix_decode_fp8_e4m3",
+    "pfd_shared_prefix_decode_grouped_fp8_e4m3",
+    "pfd_group_shared_prefixes",
+    "pfd_prefix_groups_bytes",
     "pfd_merge_packed",
     "pfd_resolve_slots",
     "pfd_rope_quant_append",
@@ -280,6 +283,44 @@ def shared_prefix_decode_fp8_e4m3(query, key_cache, value_cache, block_table, se
     lib.pfd_shared_prefix_decode_fp8_e4m3.restype = C.c_int
     with torch.cuda.device(query.device):
         _check(lib.pfd_shared_prefix_decode_fp8_e4m3(C.byref(args), int(prefix_len)))
+
+
+def group_shared_prefixes(block_table, *, prefix_lengths=None, uniform_prefix_len=0, seq_lens=None, min_batch=8,
+                          min_prefix_len=4096, max_groups=None) -> tuple[torch.Tensor, int]:
+    """``pfd_group_shared_prefixes``: (int32 groups buffer on the device, its max_groups)."""
+    lib = load()
+    lib.pfd_prefix_groups_bytes.argtypes = [C.c_int32, C.c_int32]
+    lib.pfd_prefix_groups_bytes.restype = C.c_int64
+    batch = block_table.shape[0]
+    if max_groups is None:
+        max_groups = max(1, batch // max(1, min_batch))
+    nbytes = int(lib.pfd_prefix_groups_bytes(batch, max_groups))
+    if nbytes < 0:
+        raise RuntimeError(lib.pfd_last_error().decode())
+    lib.pfd_group_shared_prefixes.argtypes = [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_int32,
+                                              C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_int64, C.c_void_p]
+    lib.pfd_group_shared_prefixes.restype = C.c_int
+    with torch.cuda.device(block_table.device):
+        groups = torch.empty(nbytes // 4, dtype=torch.int32, device=block_table.device)
+        _check(lib.pfd_group_shared_prefixes(
+            block_table.data_ptr(), block_table.stride(0), block_table.shape[1],
+            None if prefix_lengths is None else prefix_lengths.data_ptr(), int(uniform_prefix_len),
+            None if seq_lens is None else seq_lens.data_ptr(), batch, int(min_batch), int(min_prefix_len), int(max_groups),
+            groups.data_ptr(), nbytes, _stream(block_table)))
+    return groups, max_groups
+
+
+def shared_prefix_decode_grouped_fp8_e4m3(query, key_cache, value_cache, block_table, seq_lens, *, groups, max_groups,
+                                          max_prefix_len=None, **kw) -> None:
+    """One layer-step through ``pfd_shared_prefix_decode_grouped_fp8_e4m3``: any number of
+    shared-prefix groups plus requests in none, as the groups buffer on the device says."""
+    args = decode_args(query, key_cache, value_cache, block_table, seq_lens, **kw)
+    lib = load()
+    lib.pfd_shared_prefix_decode_grouped_fp8_e4m3.argtypes = [C.POINTER(DecodeArgs), C.c_void_p, C.c_int32, C.c_int32]
+    lib.pfd_shared_prefix_decode_grouped_fp8_e4m3.restype = C.c_int
+    bound = args.max_seq_len if max_prefix_len is None else int(max_prefix_len)
+    with torch.cuda.device(query.device):
+        _check(lib.pfd_shared_prefix_decode_grouped_fp8_e4m3(C.byref(args), groups.data_ptr(), int(max_groups), bound))
 
 
 NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024

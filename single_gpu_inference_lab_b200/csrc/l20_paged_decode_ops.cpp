@@ -6,7 +6,7 @@
 //       :153-155 (pybind export of the same launcher)
 // and adds "paged_decode_fp8_e4m3_split_out_v2" (per-kv-head scale tensors, explicit softmax
 // scale, kv_start, optional packed (o, m, l) output, PFD_FLAG_* bits, an optional plan),
-// "plan_decode", "merge_packed_partials" and "resolve_slots".  Every op only unpacks tensors
+// "plan_decode", "group_shared_prefixes", "merge_packed_partials" and "resolve_slots".  Every op only unpacks tensors
 // into the C ABI of libpaged_fp8_decode.so
 // (include/paged_fp8_decode.h); there is no computation here and no fallback.
 #include <ATen/cuda/CUDAContext.h>
@@ -36,7 +36,9 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
                 double sm_scale, int64_t max_seq_len, int64_t split_size, int64_t kv_start,
                 int64_t flags, const c10::optional<at::Tensor>& plan = c10::nullopt,
                 int64_t prefix_len = 0, bool kv16 = false,
-                const c10::optional<at::Tensor>& page_indptr = c10::nullopt, bool plan_only = false) {
+                const c10::optional<at::Tensor>& page_indptr = c10::nullopt, bool plan_only = false,
+                const c10::optional<at::Tensor>& groups = c10::nullopt, int64_t max_groups = 0,
+                int64_t max_prefix_len = 0) {
   TORCH_CHECK(query.is_cuda(), "query must be CUDA");
   TORCH_CHECK(query.scalar_type() == at::kHalf || query.scalar_type() == at::kBFloat16,
               "query must be FP16 or BF16");
@@ -169,6 +171,15 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
     TORCH_CHECK(pfd_plan_decode(&a, kv16 ? 2 : 1, a.plan, plan->numel() * 4) == PFD_OK, pfd_last_error());
     return;
   }
+  if (groups.has_value()) {
+    TORCH_CHECK(groups->is_cuda() && groups->scalar_type() == at::kInt && groups->is_contiguous() &&
+                    groups->numel() * 4 >= pfd_prefix_groups_bytes(a.batch, static_cast<int32_t>(max_groups)),
+                "groups must be the int32 CUDA buffer group_shared_prefixes filled for this batch and max_groups");
+    TORCH_CHECK(pfd_shared_prefix_decode_grouped_fp8_e4m3(&a, groups->data_ptr<int32_t>(), static_cast<int32_t>(max_groups),
+                                                          static_cast<int32_t>(max_prefix_len)) == PFD_OK,
+                pfd_last_error());
+    return;
+  }
   const int rc = kv16             ? pfd_paged_decode_kv16_split_out(&a)
                  : prefix_len > 0 ? pfd_shared_prefix_decode_fp8_e4m3(&a, static_cast<int32_t>(prefix_len))
                                   : pfd_paged_decode_fp8_e4m3_split_out(&a);
@@ -286,6 +297,17 @@ void shared_prefix_decode_fp8_e4m3(at::Tensor query, at::Tensor key_cache, at::T
              c10::nullopt, prefix_len);
 }
 
+void shared_prefix_decode_grouped_fp8_e4m3(at::Tensor query, at::Tensor key_cache, at::Tensor value_cache,
+                                           at::Tensor block_table, at::Tensor seq_lens, at::Tensor partial_output,
+                                           at::Tensor partial_max, at::Tensor partial_sum, at::Tensor output,
+                                           at::Tensor k_scale, at::Tensor v_scale, double sm_scale,
+                                           int64_t max_seq_len, int64_t split_size, at::Tensor groups,
+                                           int64_t max_groups, int64_t max_prefix_len) {
+  run_decode(query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max, partial_sum,
+             output, c10::nullopt, 1.0, 1.0, k_scale, v_scale, sm_scale, max_seq_len, split_size, 0, 0,
+             c10::nullopt, 0, false, c10::nullopt, false, groups, max_groups, max_prefix_len);
+}
+
 // Rotary embedding of the new tokens' query and key (in place) + append of key / value to the
 // paged cache; argument list of the reference's l20_rope_and_cache
 // (integrations/vllm/l20_rope_kv.py:256-266) plus the scales an FP8 cache needs.
@@ -386,6 +408,44 @@ void resolve_slots(at::Tensor block_table, at::Tensor seq_lens, at::Tensor slots
   TORCH_CHECK(rc == PFD_OK, pfd_last_error());
 }
 
+int64_t prefix_groups_bytes(int64_t batch, int64_t max_groups) {
+  const int64_t n = pfd_prefix_groups_bytes(static_cast<int32_t>(batch), static_cast<int32_t>(max_groups));
+  TORCH_CHECK(n >= 0, pfd_last_error());
+  return n;
+}
+
+void group_shared_prefixes(at::Tensor block_table, c10::optional<at::Tensor> prefix_lengths, int64_t uniform_prefix_len,
+                           c10::optional<at::Tensor> seq_lens, int64_t min_batch, int64_t min_prefix_len,
+                           int64_t max_groups, at::Tensor groups) {
+  TORCH_CHECK(block_table.is_cuda() && block_table.scalar_type() == at::kInt && block_table.dim() == 2 &&
+                  block_table.stride(1) == 1,
+              "int32 block table");
+  const int64_t batch = block_table.size(0);
+  const int32_t* lengths = nullptr;
+  const int32_t* lens = nullptr;
+  if (prefix_lengths.has_value()) {
+    TORCH_CHECK(prefix_lengths->is_cuda() && prefix_lengths->scalar_type() == at::kInt &&
+                    prefix_lengths->is_contiguous() && prefix_lengths->numel() == batch,
+                "prefix_lengths must be int32 CUDA with one entry per request");
+    lengths = prefix_lengths->data_ptr<int32_t>();
+  }
+  if (seq_lens.has_value()) {
+    TORCH_CHECK(seq_lens->is_cuda() && seq_lens->scalar_type() == at::kInt && seq_lens->is_contiguous() &&
+                    seq_lens->numel() == batch,
+                "int32 sequence lengths");
+    lens = seq_lens->data_ptr<int32_t>();
+  }
+  TORCH_CHECK(groups.is_cuda() && groups.scalar_type() == at::kInt && groups.is_contiguous(),
+              "groups must be a contiguous int32 CUDA tensor");
+  const at::cuda::CUDAGuard guard(block_table.device());
+  const int rc = pfd_group_shared_prefixes(
+      block_table.data_ptr<int32_t>(), block_table.stride(0), static_cast<int32_t>(block_table.size(1)), lengths,
+      static_cast<int32_t>(uniform_prefix_len), lens, static_cast<int32_t>(batch), static_cast<int32_t>(min_batch),
+      static_cast<int32_t>(min_prefix_len), static_cast<int32_t>(max_groups), groups.data_ptr<int32_t>(),
+      groups.numel() * 4, at::cuda::getCurrentCUDAStream().stream());
+  TORCH_CHECK(rc == PFD_OK, pfd_last_error());
+}
+
 }  // namespace
 
 TORCH_LIBRARY(l20_stack, module) {
@@ -434,12 +494,22 @@ TORCH_LIBRARY(l20_stack, module) {
       "Tensor(a!) partial_output, Tensor(b!) partial_max, Tensor(c!) partial_sum, Tensor(d!) output, "
       "Tensor k_scale, Tensor v_scale, float sm_scale, int max_seq_len, int split_size, int prefix_len) -> ()");
   module.def(
+      "shared_prefix_decode_grouped_fp8_e4m3("
+      "Tensor query, Tensor key_cache, Tensor value_cache, Tensor block_table, Tensor seq_lens, "
+      "Tensor(a!) partial_output, Tensor(b!) partial_max, Tensor(c!) partial_sum, Tensor(d!) output, "
+      "Tensor k_scale, Tensor v_scale, float sm_scale, int max_seq_len, int split_size, Tensor groups, "
+      "int max_groups, int max_prefix_len) -> ()");
+  module.def(
       "rope_and_cache(Tensor(a!) query, Tensor(b!) key, Tensor value, Tensor positions, Tensor cos_sin_cache, "
       "bool is_neox, Tensor(c!) key_cache, Tensor(d!) value_cache, Tensor slot_mapping, "
       "Tensor? k_scale, Tensor? v_scale) -> ()");
   module.def("plan_bytes(int batch, int num_kv_heads) -> int", &plan_bytes);
   module.def("merge_packed_partials(Tensor packed, Tensor(a!) output) -> ()");
   module.def("resolve_slots(Tensor block_table, Tensor seq_lens, Tensor(a!) slots) -> ()");
+  module.def("prefix_groups_bytes(int batch, int max_groups) -> int", &prefix_groups_bytes);
+  module.def(
+      "group_shared_prefixes(Tensor block_table, Tensor? prefix_lengths, int uniform_prefix_len, Tensor? seq_lens, "
+      "int min_batch, int min_prefix_len, int max_groups, Tensor(a!) groups) -> ()");
 }
 
 TORCH_LIBRARY_IMPL(l20_stack, CUDA, module) {
@@ -453,6 +523,8 @@ TORCH_LIBRARY_IMPL(l20_stack, CUDA, module) {
   module.impl("rope_and_cache", &rope_and_cache);
   module.impl("merge_packed_partials", &merge_packed_partials);
   module.impl("resolve_slots", &resolve_slots);
+  module.impl("shared_prefix_decode_grouped_fp8_e4m3", &shared_prefix_decode_grouped_fp8_e4m3);
+  module.impl("group_shared_prefixes", &group_shared_prefixes);
 }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, module) {

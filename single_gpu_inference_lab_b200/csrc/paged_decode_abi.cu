@@ -16,6 +16,7 @@
 #include "shared_prefix_dense.cuh"
 #include "paged_decode_kernels.cuh"
 #include "rope_kv_append.cuh"
+#include "shared_prefix_groups.cuh"
 
 namespace {
 
@@ -53,22 +54,59 @@ constexpr int kMaxDevices = 64;
 // for the symbol; each device's address is looked up once with cudaGetSymbolAddress.
 static __device__ int g_device_status;
 std::mutex g_state_mutex;
-int32_t* g_status_ptr[kMaxDevices] = {nullptr};
 
-int status_pointer(int32_t** out) {
+// What a call needs to know about its device, looked up once per device.  Every entry point
+// begins with enter_call(): one cudaGetDevice, then a lock-free read of this table; the helpers
+// below take the device of the call in progress from t_device.
+struct DeviceState {
+  int dev = -1;
+  int sms = 0;
+  int32_t* status = nullptr;
+};
+DeviceState g_device_state[kMaxDevices];
+std::atomic<bool> g_device_ready[kMaxDevices];
+thread_local const DeviceState* t_device = nullptr;
+
+int enter_call() {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
   if (dev < 0 || dev >= kMaxDevices) return fail(PFD_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
-  std::lock_guard<std::mutex> lock(g_state_mutex);
-  if (g_status_ptr[dev] == nullptr) {
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_device_status);
-    if (e != cudaSuccess || p == nullptr)
-      return fail(PFD_ERR_CUDA, "cudaGetSymbolAddress(status) failed: %s", cudaGetErrorString(e));
-    g_status_ptr[dev] = static_cast<int32_t*>(p);
+  if (!g_device_ready[dev].load(std::memory_order_acquire)) {
+    std::lock_guard<std::mutex> lock(g_state_mutex);
+    if (!g_device_ready[dev].load(std::memory_order_relaxed)) {
+      DeviceState& d = g_device_state[dev];
+      e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaDeviceGetAttribute failed: %s", cudaGetErrorString(e));
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_device_status);
+      if (e != cudaSuccess || p == nullptr)
+        return fail(PFD_ERR_CUDA, "cudaGetSymbolAddress(status) failed: %s", cudaGetErrorString(e));
+      d.status = static_cast<int32_t*>(p);
+      d.dev = dev;
+      g_device_ready[dev].store(true, std::memory_order_release);
+    }
   }
-  *out = g_status_ptr[dev];
+  t_device = &g_device_state[dev];
+  return PFD_OK;
+}
+
+int status_pointer(int32_t** out) {
+  *out = t_device->status;
+  return PFD_OK;
+}
+
+// First launch of a kernel that needs more than the default dynamic shared memory, per device.
+template <typename Kernel>
+int configure_smem(std::atomic<bool>* done, Kernel kernel, int smem) {
+  std::atomic<bool>& flag = done[t_device->dev];
+  if (flag.load(std::memory_order_acquire)) return PFD_OK;
+  std::lock_guard<std::mutex> lock(g_state_mutex);
+  if (!flag.load(std::memory_order_relaxed)) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
+    flag.store(true, std::memory_order_release);
+  }
   return PFD_OK;
 }
 
@@ -95,8 +133,23 @@ struct MapEntry {
   MapKey key;
   CUtensorMap map;
 };
-std::vector<MapEntry> g_maps;
+std::vector<MapEntry> g_maps;  // every map encoded so far (under g_state_mutex)
 EncodeTiledFn g_encode = nullptr;
+// Hit path: a direct-mapped table per thread, indexed by a hash of the cache's base address; no
+// lock, one key comparison, one 128-byte copy.  A model's layers each have their own K and V
+// cache, so a serving thread cycles through a few dozen entries.
+constexpr int kMapSlots = 256;
+struct MapSlot {
+  bool used = false;
+  MapEntry entry;
+};
+thread_local MapSlot t_map_slots[kMapSlots];
+inline unsigned map_slot_of(const void* base, int32_t elem_bytes) {
+  uint64_t x = reinterpret_cast<uintptr_t>(base) >> 8;
+  x ^= x >> 17;
+  x *= 0x9E3779B97F4A7C15ull;
+  return (unsigned)((x >> 40) + (unsigned)elem_bytes) % kMapSlots;
+}
 
 bool head_is_dim1(int64_t stride_token, int64_t stride_head) { return stride_head <= stride_token; }
 
@@ -111,12 +164,17 @@ bool head_is_dim1(int64_t stride_token, int64_t stride_head) { return stride_hea
 // elements = 128 bytes, so that the 128-byte swizzle still applies.)
 int get_tensor_map(const void* base, int64_t stride_page, int64_t stride_token, int64_t stride_head,
                    int64_t num_pages, int32_t heads, int32_t promotion, CUtensorMap* out, int32_t elem_bytes = 1) {
-  int dev = 0;
-  cudaGetDevice(&dev);
-  const MapKey key{dev, base, stride_page, stride_token, stride_head, num_pages, heads, promotion, elem_bytes};
+  const MapKey key{t_device->dev, base, stride_page, stride_token, stride_head, num_pages, heads, promotion, elem_bytes};
+  MapSlot& slot = t_map_slots[map_slot_of(base, elem_bytes)];
+  if (slot.used && slot.entry.key == key) {
+    *out = slot.entry.map;
+    return PFD_OK;
+  }
   std::lock_guard<std::mutex> lock(g_state_mutex);
   for (const MapEntry& e : g_maps)
     if (e.key == key) {
+      slot.entry = e;
+      slot.used = true;
       *out = e.map;
       return PFD_OK;
     }
@@ -148,8 +206,10 @@ int get_tensor_map(const void* base, int64_t stride_page, int64_t stride_token, 
                               box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, promo,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(PFD_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  if (g_maps.size() >= 256) g_maps.erase(g_maps.begin());
+  if (g_maps.size() >= 1024) g_maps.erase(g_maps.begin());
   g_maps.push_back(entry);
+  slot.entry = entry;
+  slot.used = true;
   *out = entry.map;
   return PFD_OK;
 }
@@ -177,14 +237,8 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
   tp.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   auto kernel = pfd::paged_decode_fp8_partial_tma_kernel<QBF16, kWarps, kStages>;
   constexpr int smem = 1024 + kWarps * kStages * 8192 + kWarps * kStages * 8 + 2 * kWarps * 16 * 4;
-  static bool configured[kMaxDevices] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (!configured[dev]) {
-    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
-    configured[dev] = true;
-  }
+  static std::atomic<bool> configured[kMaxDevices];
+  if (int rc = configure_smem(configured, kernel, smem)) return rc;
   {
     // Programmatic dependent launch.  Behind the dense prefix pass: independent work, it runs
     // beside that pass.  Otherwise: the CTAs may become resident while the preceding kernel of
@@ -217,21 +271,6 @@ constexpr int kChunkStages16 = 2;
 constexpr int kChunkWarps16 = 6;
 constexpr int kChunkPieceCost = 2;  // half page pairs charged for starting a sequence
 
-int sm_count_of(int dev, int* out) {
-  static int sm_count[kMaxDevices] = {0};
-  if (dev < 0 || dev >= kMaxDevices) return fail(PFD_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
-  std::lock_guard<std::mutex> lock(g_state_mutex);
-  if (sm_count[dev] == 0) {
-    const cudaError_t e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaDeviceGetAttribute failed: %s", cudaGetErrorString(e));
-  }
-  *out = sm_count[dev];
-  return PFD_OK;
-}
-
-// The balanced path treats the workspace as a flat array of (o, m, l) rows: two slots of
-// num_q_heads rows for each group of num_kv_heads warps.  It needs a dense f32 workspace of
-// that capacity; a call that does not qualify runs on the fixed-split grid instead.
 bool balanced_eligible(const pfd_decode_args& a, int group, int slot_offset, int sms) {
   if (a.flags & (PFD_FLAG_FIXED_SPLITS | PFD_FLAG_NO_TMA | PFD_FLAG_NO_DIRECT_OUT)) return false;
   if (slot_offset != 0) return false;  // slots in front belong to the dense prefix pass
@@ -279,17 +318,8 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
   // ring + mbarriers + scan scratch + prefix[B + 1] + lens[B], sized for the largest batch
   constexpr int smem = 1024 + kWarpsT * kStagesT * 8192 * kElem + kWarpsT * kStagesT * 8 +
                        kWarpsT * 4 + (2 * kChunkMaxBatch + 1) * 4 + 16;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  static bool configured[kMaxDevices][2] = {};  // one array per instantiation of this template
-  {
-    std::lock_guard<std::mutex> lock(g_state_mutex);
-    if (!configured[dev][fused ? 1 : 0]) {
-      const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-      if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
-      configured[dev][fused ? 1 : 0] = true;
-    }
-  }
+  static std::atomic<bool> configured[2][kMaxDevices];  // one array per instantiation of this template
+  if (int rc = configure_smem(configured[fused ? 1 : 0], kernel, smem)) return rc;
   pfd::ChunkParams cp{};
   cp.batch = a.batch;
   cp.num_warps = balanced_num_warps(sms, kWarpsT, a.num_kv_heads, max_groups);
@@ -339,9 +369,7 @@ template <int D, bool QBF16>
 int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num_splits) {
   cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
   if (D == 128) {
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    if (int rc = sm_count_of(dev, &sms)) return rc;
+    const int sms = t_device->sms;
     if (balanced_eligible(a, kp.group, kp.slot_offset, sms)) return launch_balanced<QBF16, kChunkStages, kChunkWarps>(a, kp, sms, stream);
   }
   if (a.page_indptr != nullptr)
@@ -362,9 +390,7 @@ int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num
     // programmatic dependent launch: the merge grid is scheduled while the partial grid drains
     cudaLaunchConfig_t cfg{};
     // few rows and more than eight slots per row: four warps share a row (one round trip instead of several)
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    if (int rc = sm_count_of(dev, &sms)) return rc;
+    const int sms = t_device->sms;
     const bool wide = rows <= 8 * sms && num_splits + kp.slot_offset > 8;
     cfg.gridDim = dim3(wide ? rows : (rows + 3) / 4);
     cfg.blockDim = dim3(128);
@@ -397,7 +423,8 @@ int64_t pfd_launch_count(void) { return g_launches.load(std::memory_order_relaxe
 }  // extern "C"
 
 namespace {
-pfd::KernelParams fill_params(const pfd_decode_args& a, int group, bool direct_ok, int slot_offset) {
+pfd::KernelParams fill_params(const pfd_decode_args& a, int group, bool direct_ok, int slot_offset,
+                              const int32_t* row_kv_start = nullptr, int row_kv_cap = 0) {
   pfd::KernelParams kp{};
   kp.query = a.query;
   kp.key_cache = static_cast<const uint8_t*>(a.key_cache);
@@ -427,6 +454,8 @@ pfd::KernelParams fill_params(const pfd_decode_args& a, int group, bool direct_o
   kp.direct_out = direct_ok ? 1 : 0;
   kp.bt_cols = (a.max_seq_len + pfd::kPage - 1) / pfd::kPage;  // rows are at least this wide
   kp.slot_offset = slot_offset;
+  kp.row_kv_start = row_kv_start;
+  kp.row_kv_cap = row_kv_cap;
   kp.early_metadata = (a.flags & PFD_FLAG_EARLY_METADATA) ? 1 : 0;
   kp.kv_evict_first = 1;
   if (a.exchange != nullptr) {
@@ -448,7 +477,7 @@ pfd::KernelParams fill_params(const pfd_decode_args& a, int group, bool direct_o
 
 // slot_offset > 0: workspace slots [0, slot_offset) are filled by the dense prefix pass; the
 // split-KV kernels then write behind them and the merge kernel covers both.
-int decode_impl(const pfd_decode_args* args, int slot_offset) {
+int decode_impl(const pfd_decode_args* args, int slot_offset, const int32_t* row_kv_start = nullptr, int row_kv_cap = 0) {
   if (args == nullptr) return fail(PFD_ERR_INVALID, "args is NULL");
   if (args->struct_size != sizeof(pfd_decode_args))
     return fail(PFD_ERR_INVALID, "pfd_decode_args size mismatch: caller %u, library %zu",
@@ -480,9 +509,8 @@ int decode_impl(const pfd_decode_args* args, int slot_offset) {
       if (!x.recv[r]) return fail(PFD_ERR_INVALID, "exchange: recv pointer of rank %d is NULL", r);
     if (slot_offset != 0 || (a.flags & (PFD_FLAG_SINGLE_LAUNCH | PFD_FLAG_PARTIAL_ONLY)))
       return fail(PFD_ERR_UNSUPPORTED, "exchange: not with the shared-prefix pass, PFD_FLAG_SINGLE_LAUNCH or PFD_FLAG_PARTIAL_ONLY");
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    if (int rc = sm_count_of(dev, &sms)) return rc;
+    if (int rc = enter_call()) return rc;
+    const int sms = t_device->sms;
     if (!balanced_eligible(a, group, 0, sms))
       return fail(PFD_ERR_UNSUPPORTED,
                   "exchange: needs the balanced kernel (head_dim 128, at most 8 query heads per KV head, TMA-describable "
@@ -512,7 +540,8 @@ int decode_impl(const pfd_decode_args* args, int slot_offset) {
       return fail(PFD_ERR_UNSUPPORTED, "partial_output must be 16-byte aligned");
   }
 
-  const pfd::KernelParams kp = fill_params(a, group, direct_ok, slot_offset);
+  if (int rc = enter_call()) return rc;  // (argument errors above are reported without a device)
+  const pfd::KernelParams kp = fill_params(a, group, direct_ok, slot_offset, row_kv_start, row_kv_cap);
 
   const bool bf16 = a.query_dtype == PFD_DTYPE_BF16;
   if (a.head_dim == 128)
@@ -521,7 +550,8 @@ int decode_impl(const pfd_decode_args* args, int slot_offset) {
 }
 
 template <bool QBF16>
-int launch_prefix(const pfd_decode_args& a, int prefix_len, int chunks) {
+int launch_prefix(const pfd_decode_args& a, int prefix_len, int chunks, const int32_t* groups = nullptr,
+                  int max_groups = 0) {
   pfd::KernelParams kp{};
   kp.query = a.query;
   kp.key_cache = static_cast<const uint8_t*>(a.key_cache);
@@ -546,22 +576,20 @@ int launch_prefix(const pfd_decode_args& a, int prefix_len, int chunks) {
   pfd::PrefixParams pp{};
   pp.prefix_len = prefix_len;
   pp.batch = a.batch;
+  pp.groups = groups;
+  pp.groups_batch = a.batch;
+  pp.max_groups = max_groups;
   if (int rc = status_pointer(&pp.status)) return rc;
   pp.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   pp.phase_times = g_phase_times;
   auto kernel = pfd::shared_prefix_dense_kernel<QBF16>;
   constexpr int smem = 1024 + 160 * 1024 + 32 + 2 * 4 * 128 * 4;
-  static bool configured[kMaxDevices] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= kMaxDevices) return fail(PFD_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
-  if (!configured[dev]) {
-    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
-    configured[dev] = true;
-  }
+  static std::atomic<bool> configured[kMaxDevices];
+  if (int rc = configure_smem(configured, kernel, smem)) return rc;
   const int rows = a.batch * kp.group;
-  const dim3 grid(chunks, (rows + pfd::kPrefixRows - 1) / pfd::kPrefixRows, a.num_kv_heads);
+  // grouped: every group's last 128-row tile may be ragged, hence one more tile slot per group
+  const dim3 grid = groups == nullptr ? dim3(chunks, (rows + pfd::kPrefixRows - 1) / pfd::kPrefixRows, a.num_kv_heads)
+                                      : dim3(rows / pfd::kPrefixRows + max_groups, chunks, a.num_kv_heads);
   kernel<<<grid, 512, smem, static_cast<cudaStream_t>(a.stream)>>>(kp, pp);
   return check_launch("shared-prefix dense kernel");
 }
@@ -626,9 +654,8 @@ int validate_kv16(const pfd_decode_args* args, int* cap, int* sms_out, bool need
     const int64_t rows = (int64_t)a.batch * a.num_q_heads * a.workspace_splits;
     groups = rows / (2LL * a.num_q_heads);
   }
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (int rc = sm_count_of(dev, sms_out)) return rc;
+  if (int rc = enter_call()) return rc;
+  *sms_out = t_device->sms;
   if (a.num_kv_heads > kChunkWarps16 * *sms_out / 2) return fail(PFD_ERR_UNSUPPORTED, "too many KV heads");
   *cap = (int)std::min<int64_t>(std::max<int64_t>(groups, 1), 1 << 20);
   return PFD_OK;
@@ -654,9 +681,8 @@ int pfd_paged_decode_kv16_split_out(const pfd_decode_args* args) {
 int64_t pfd_plan_bytes(int32_t batch, int32_t num_kv_heads) {
   if (batch < 0 || batch > kChunkMaxBatch || num_kv_heads <= 0)
     return fail(PFD_ERR_INVALID, "batch must be 0 .. %d and num_kv_heads positive", kChunkMaxBatch);
-  int dev = 0, sms = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaGetDevice failed");
-  if (int rc = sm_count_of(dev, &sms)) return rc;
+  if (int rc = enter_call()) return rc;
+  const int sms = t_device->sms;
   const int max_groups = std::max(sms * kChunkWarps / num_kv_heads, 1);
   return 4 * pfd::plan_words(batch, max_groups, num_kv_heads);
 }
@@ -682,9 +708,8 @@ int pfd_plan_decode(const pfd_decode_args* args, int32_t cache_elem_bytes, void*
     if (a.kv_start < 0) return fail(PFD_ERR_INVALID, "negative length");
     if (a.batch == 0) return PFD_OK;
     if (!a.block_table || !a.seq_lens) return fail(PFD_ERR_INVALID, "NULL operand");
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    if (int rc = sm_count_of(dev, &sms)) return rc;
+    if (int rc = enter_call()) return rc;
+    const int sms = t_device->sms;
     if (a.page_size != pfd::kPage || !balanced_eligible(a, a.num_q_heads / a.num_kv_heads, 0, sms))
       return fail(PFD_ERR_UNSUPPORTED,
                   "no plan: this call does not run the balanced kernel (head_dim 128, at most 8 query heads per KV "
@@ -752,6 +777,7 @@ int pfd_shared_prefix_decode_fp8_e4m3(const pfd_decode_args* args, int32_t prefi
       return fail(PFD_ERR_INVALID, "partial output workspace has wrong shape: the shared-prefix pass needs %d slots",
                   chunks + ns);
   }
+  if (int rc = enter_call()) return rc;
   if (int rc = bf16 ? launch_prefix<true>(a, prefix_len, chunks) : launch_prefix<false>(a, prefix_len, chunks)) return rc;
   return decode_impl(&a, chunks);
 }
@@ -767,6 +793,50 @@ namespace {
 std::mutex g_noalloc_mutex;
 void* g_noalloc_ptr[kMaxDevices] = {nullptr};
 }  // namespace
+
+int pfd_shared_prefix_decode_grouped_fp8_e4m3(const pfd_decode_args* args, const void* groups, int32_t max_groups,
+                                              int32_t max_prefix_len) {
+  if (args == nullptr) return fail(PFD_ERR_INVALID, "args is NULL");
+  if (args->struct_size != sizeof(pfd_decode_args))
+    return fail(PFD_ERR_INVALID, "pfd_decode_args size mismatch: caller %u, library %zu", args->struct_size,
+                sizeof(pfd_decode_args));
+  pfd_decode_args a = *args;
+  if (groups == nullptr || max_groups < 1) return fail(PFD_ERR_INVALID, "a groups buffer and its max_groups are needed");
+  if (a.head_dim != 128 || a.page_size != pfd::kPage)
+    return fail(PFD_ERR_UNSUPPORTED, "the shared-prefix pass needs head_dim 128 and page_size 16");
+  if (max_prefix_len < 0) return fail(PFD_ERR_INVALID, "negative length");
+  if (a.kv_start != 0) return fail(PFD_ERR_INVALID, "kv_start must be 0 for the shared-prefix pass");
+  if (a.page_indptr != nullptr) return fail(PFD_ERR_UNSUPPORTED, "the shared-prefix pass needs a block table");
+  if (a.exchange != nullptr) return fail(PFD_ERR_UNSUPPORTED, "exchange: not with the shared-prefix pass");
+  if (a.batch <= 0) return a.batch == 0 ? PFD_OK : fail(PFD_ERR_INVALID, "invalid query");
+  if (a.batch > pfd::kGroupsMaxBatch) return fail(PFD_ERR_UNSUPPORTED, "at most %d sequences per call", pfd::kGroupsMaxBatch);
+  if (a.num_kv_heads <= 0 || a.num_q_heads % a.num_kv_heads != 0 || a.num_q_heads / a.num_kv_heads > 16)
+    return fail(PFD_ERR_INVALID, "Q heads must be divisible by KV heads (at most 16 per KV head)");
+  if (!a.partial_output || !a.partial_max || !a.partial_sum || a.partial_dtype != PFD_DTYPE_F32)
+    return fail(PFD_ERR_INVALID, "the shared-prefix pass needs an f32 partial workspace");
+  if (!a.query || !a.key_cache || !a.value_cache || !a.block_table || !a.seq_lens)
+    return fail(PFD_ERR_INVALID, "NULL operand");
+  if ((reinterpret_cast<uintptr_t>(a.query) & 15u) || a.q_stride_h % 8 || a.q_stride_b % 8)
+    return fail(PFD_ERR_UNSUPPORTED, "query rows must be 16-byte aligned for the shared-prefix pass");
+  const bool bf16 = a.query_dtype == PFD_DTYPE_BF16;
+  if (!bf16 && a.query_dtype != PFD_DTYPE_F16) return fail(PFD_ERR_INVALID, "query must be FP16 or BF16");
+  if (a.split_size < 16 || a.split_size % 16) return fail(PFD_ERR_INVALID, "split_size must be a multiple of 16");
+  const int cap = std::min(max_prefix_len, a.max_seq_len) & ~15;  // no group's prefix pass reaches further
+  const int chunks = (cap + pfd::kPrefixChunk - 1) / pfd::kPrefixChunk;
+  const int ns = std::max((a.max_seq_len + a.split_size - 1) / a.split_size, 1);  // a request in no group attends from 0
+  if (a.workspace_splits < chunks + ns)
+    return fail(PFD_ERR_INVALID, "partial output workspace has wrong shape: the grouped shared-prefix pass needs %d slots",
+                chunks + ns);
+  a.flags |= PFD_FLAG_FIXED_SPLITS | PFD_FLAG_NO_DIRECT_OUT;
+  a.flags &= ~(uint32_t)PFD_FLAG_PARTIAL_ONLY;
+  a.plan = nullptr;
+  if (int rc = enter_call()) return rc;
+  const int32_t* g = static_cast<const int32_t*>(groups);
+  if (chunks > 0)
+    if (int rc = bf16 ? launch_prefix<true>(a, cap, chunks, g, max_groups) : launch_prefix<false>(a, cap, chunks, g, max_groups))
+      return rc;
+  return decode_impl(&a, chunks, g + pfd::groups_row_prefix_off(), cap);
+}
 
 int pfd_paged_decode_fp8_e4m3_split_out_noalloc(const pfd_decode_args* args) {
   if (args == nullptr) return fail(PFD_ERR_INVALID, "args is NULL");
@@ -886,9 +956,8 @@ int pfd_last_path(void) { return g_last_path; }
 int64_t pfd_balanced_workspace_rows(int32_t num_q_heads, int32_t num_kv_heads) {
   if (num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads)
     return fail(PFD_ERR_INVALID, "Q heads must be divisible by KV heads");
-  int dev = 0, sms = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaGetDevice failed");
-  if (int rc = sm_count_of(dev, &sms)) return rc;
+  if (int rc = enter_call()) return rc;
+  const int sms = t_device->sms;
   return 2LL * (sms * kChunkWarps / num_kv_heads) * num_q_heads;
 }
 
@@ -910,6 +979,7 @@ int pfd_set_wait_limit_ns(uint64_t limit_ns) {
 int pfd_selftest_bounded_wait(uint64_t limit_ns, uint64_t* waited_ns, void* stream) {
   if (limit_ns == 0 || limit_ns > 1000ull * 1000 * 1000)
     return fail(PFD_ERR_INVALID, "limit_ns must be between 1 ns and 1 s");
+  if (int rc = enter_call()) return rc;
   int32_t* status = nullptr;
   if (int rc = status_pointer(&status)) return rc;
   unsigned long long* dev_waited = nullptr;
@@ -937,6 +1007,7 @@ int pfd_selftest_bounded_wait(uint64_t limit_ns, uint64_t* waited_ns, void* stre
 
 int pfd_device_status(int32_t* status) {
   if (status == nullptr) return fail(PFD_ERR_INVALID, "status is NULL");
+  if (int rc = enter_call()) return rc;
   int32_t* p = nullptr;
   if (int rc = status_pointer(&p)) return rc;
   cudaError_t e = cudaDeviceSynchronize();  // kernels on non-blocking streams included
@@ -1032,6 +1103,7 @@ int pfd_exchange_merge(const pfd_exchange* exchange, int64_t rows, int32_t head_
   if (out_dtype < PFD_DTYPE_F32 || out_dtype > PFD_DTYPE_BF16)
     return fail(PFD_ERR_INVALID, "output dtype must be f32, f16 or bf16");
   if (rows <= 0) return rows == 0 ? PFD_OK : fail(PFD_ERR_INVALID, "negative row count");
+  if (int rc = enter_call()) return rc;
   pfd::TmaParams tp{};
   if (int rc = status_pointer(&tp.status)) return rc;
   tp.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
@@ -1052,6 +1124,49 @@ int pfd_exchange_merge(const pfd_exchange* exchange, int64_t rows, int32_t head_
                                            output, (int)out_dtype, tp);
   if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "exchange merge kernel launch failed: %s", cudaGetErrorString(e));
   return check_launch("exchange merge kernel");
+}
+
+int64_t pfd_prefix_groups_bytes(int32_t batch, int32_t max_groups) {
+  if (batch < 0 || batch > pfd::kGroupsMaxBatch || max_groups < 1)
+    return fail(PFD_ERR_INVALID, "batch must be 0 .. %d and max_groups positive", pfd::kGroupsMaxBatch);
+  return 4 * pfd::groups_words(batch, max_groups);
+}
+
+int pfd_group_shared_prefixes(const int32_t* block_table, int64_t bt_stride_b, int32_t bt_cols,
+                              const int32_t* prefix_lengths, int32_t uniform_prefix_len, const int32_t* seq_lens,
+                              int32_t batch, int32_t min_batch, int32_t min_prefix_len, int32_t max_groups,
+                              void* groups, int64_t groups_bytes, void* stream) {
+  if (batch < 0 || batch > pfd::kGroupsMaxBatch)
+    return fail(PFD_ERR_UNSUPPORTED, "at most %d sequences per call", pfd::kGroupsMaxBatch);
+  if (min_batch < 1 || min_prefix_len < 0 || max_groups < 1 || bt_cols < 0 || uniform_prefix_len < 0)
+    return fail(PFD_ERR_INVALID, "min_batch and max_groups must be positive, lengths non-negative");
+  if (groups == nullptr || groups_bytes < 4 * pfd::groups_words(batch, max_groups))
+    return fail(PFD_ERR_INVALID, "groups buffer holds %lld bytes, this call needs %lld (pfd_prefix_groups_bytes)",
+                (long long)groups_bytes, (long long)(4 * pfd::groups_words(batch, max_groups)));
+  if (batch > 0 && block_table == nullptr) return fail(PFD_ERR_INVALID, "NULL operand");
+  if (prefix_lengths == nullptr && uniform_prefix_len == 0 && seq_lens == nullptr)
+    return fail(PFD_ERR_INVALID, "give prefix_lengths, a uniform prefix length, or seq_lens to derive one from");
+  pfd::GroupParams gp{};
+  gp.block_table = block_table;
+  gp.bt_stride_b = bt_stride_b;
+  gp.bt_cols = bt_cols;
+  gp.prefix_lengths = prefix_lengths;
+  gp.uniform_prefix_len = uniform_prefix_len;
+  gp.seq_lens = seq_lens;
+  gp.batch = batch;
+  gp.min_batch = min_batch;
+  gp.min_prefix_len = min_prefix_len;
+  gp.max_groups = max_groups;
+  gp.groups = static_cast<int32_t*>(groups);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (batch > 0) {
+    pfd::prefix_hash_kernel<<<batch, 256, 0, s>>>(gp);
+    if (int rc = check_launch("prefix hash kernel")) return rc;
+    pfd::prefix_match_kernel<<<batch, 256, 0, s>>>(gp);
+    if (int rc = check_launch("prefix match kernel")) return rc;
+  }
+  pfd::prefix_finish_kernel<<<1, 1024, 0, s>>>(gp);
+  return check_launch("prefix finish kernel");
 }
 
 int pfd_resolve_slots(const int32_t* block_table, int64_t bt_stride_b, const int32_t* seq_lens,

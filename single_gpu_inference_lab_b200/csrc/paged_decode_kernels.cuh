@@ -56,6 +56,10 @@ struct KernelParams {
   int32_t direct_out;  // 1: a sequence with a single split writes its final result itself
   int32_t bt_cols;     // width of a block-table row
   int32_t slot_offset; // workspace slots [0, slot_offset) are filled by another kernel (dense prefix pass)
+  // Grouped shared-prefix decode: row b attends from token row_kv_start[b] & ~15 on (the prefix of
+  // its group, 0 for a request in no group) and owns ceil(that / 256) of the slots in front.
+  const int32_t* row_kv_start;
+  int32_t row_kv_cap;  // upper bound applied to row_kv_start (a multiple of 16): the slots in front cover no more
   int32_t early_metadata;  // 1: seq_lens and block_table may be read before the preceding kernel has completed
   int32_t kv_evict_first;  // 1: K/V tiles are loaded with the L2 evict-first hint
   // KV-range exchange (xch_world > 0): the packed (o, m, l) rows of this rank go, instead of to
@@ -111,6 +115,11 @@ __device__ __forceinline__ unsigned long long* xch_row(const KernelParams& p, in
 
 // The one address function every kernel uses for "which cache slot holds token t of
 // sequence b".  Returns the physical page; the slot is page * 16 + t % 16.
+// First token the split-KV kernels attend for sequence b.
+__device__ __forceinline__ int kv_start_of(const KernelParams& p, int b) {
+  return p.row_kv_start != nullptr ? min(__ldg(p.row_kv_start + b) & ~15, p.row_kv_cap) : p.kv_start;
+}
+
 __device__ __forceinline__ int32_t page_of(const int32_t* __restrict__ block_table,
                                            int64_t bt_stride_b, int b, int logical_page) {
   return __ldg(block_table + (int64_t)b * bt_stride_b + logical_page);
@@ -504,14 +513,15 @@ paged_decode_fp8_partial_ldg_kernel(const KernelParams p) {
   pdl_launch_dependents();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int seq_len = p.seq_lens[b];
-  const int lo = p.kv_start + split * p.split_size;
+  const int kv0 = kv_start_of(p, b);
+  const int lo = kv0 + split * p.split_size;
   const int hi = min(lo + p.split_size, seq_len);
   if (lo >= hi) {  // the merge kernel derives the live split count from seq_len
     pdl_wait();
     if (split == 0 && gridDim.x == 1 && p.direct_out) write_empty_rows<D>(p, b, kvh);
     return;
   }
-  const int nsplits_seq = (seq_len - p.kv_start + p.split_size - 1) / p.split_size;
+  const int nsplits_seq = (seq_len - kv0 + p.split_size - 1) / p.split_size;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
 
   __shared__ float sm_m[NWARPS * 16];
@@ -738,7 +748,8 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   if (p.slot_offset == 0 && !p.early_metadata) pdl_wait();
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
-  const int lo = p.kv_start + split * p.split_size;
+  const int kv0 = kv_start_of(p, b);
+  const int lo = kv0 + split * p.split_size;
 
   // Page ids of this warp's first 16 page pairs, one page per lane, fetched before the
   // sequence length is known (the block-table row is bt_cols wide, so this stays inside it).
@@ -758,7 +769,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
     return;
   }
   if (p.slot_offset == 0 && p.early_metadata) pdl_wait();
-  const int nsplits_seq = (seq_len - p.kv_start + p.split_size - 1) / p.split_size;
+  const int nsplits_seq = (seq_len - kv0 + p.split_size - 1) / p.split_size;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -936,8 +947,12 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
   }
   const int b = row / p.num_q_heads, hq = row % p.num_q_heads;
   const int seq_len = p.seq_lens[b];
-  const int live = seq_len - p.kv_start;
-  const int ns = (live > 0 ? (live + p.split_size - 1) / p.split_size : 0) + p.slot_offset;
+  const int kv0 = kv_start_of(p, b);
+  const int live = seq_len - kv0;
+  // slots in front of the splits: all slot_offset of them, or (grouped) those of this row's prefix
+  const int pre = p.row_kv_start != nullptr ? (kv0 + 255) / 256 : p.slot_offset;
+  const int skip = p.slot_offset - pre;  // unused slots between the row's prefix chunks and its splits
+  const int ns = (live > 0 ? (live + p.split_size - 1) / p.split_size : 0) + pre;
   constexpr int E = D / 32;  // elements per lane
   float acc[E];
 #pragma unroll
@@ -957,7 +972,8 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         const bool on = s0 + u * WPR < ns;
-        const int64_t pidx = base + (int64_t)(on ? s0 + u * WPR : 0) * p.partial_stride_s;
+        const int k = on ? s0 + u * WPR : 0;  // (an idle lane re-reads the row's first live slot: finite data, weight 0)
+        const int64_t pidx = base + (int64_t)(k < pre ? k : k + skip) * p.partial_stride_s;
         mv[u] = on ? p.partial_max[pidx] : -INFINITY;
         lv[u] = on ? p.partial_sum[pidx] : 0.f;
         if (p.partial_dtype == 0) {
@@ -1065,7 +1081,7 @@ merge_packed_kernel(const float* __restrict__ packed, int parts, int64_t rows, v
   }
 }
 
-constexpr int kErrPeerTimeout = 3;
+constexpr int kErrPeerTimeout = 4;
 
 // Receiving side of the KV-range exchange, one warp per row: the warp polls rank s's copy of the
 // row in this rank's receive buffer until every word it needs carries this step's tag (the other

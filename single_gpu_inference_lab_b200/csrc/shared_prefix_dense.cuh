@@ -22,6 +22,7 @@
 #pragma once
 
 #include "paged_decode_kernels.cuh"
+#include "shared_prefix_groups.cuh"
 
 namespace pfd {
 
@@ -147,6 +148,11 @@ __device__ __forceinline__ void sts_u16(uint32_t addr, uint32_t v) {
 struct PrefixParams {
   int32_t prefix_len;   // tokens shared by every request (multiple of 16)
   int32_t batch;
+  // Grouped form: the groups buffer of the grouping kernels (shared_prefix_groups.cuh) and its
+  // geometry.  grid = (slots for (group, 128-row tile) pairs, prefix chunks, kv heads); a CTA
+  // whose slot or chunk lies beyond what the device-side table holds leaves at once.
+  const int32_t* groups;
+  int32_t groups_batch, max_groups;
   int32_t* status;
   unsigned long long wait_limit_ns;  // after this long a wait for the tensor cores gives up and sets the error word
   unsigned long long* phase_times;  // [grid][8] nanosecond stamps; read only in builds with PFD_PHASE_STAMPS
@@ -166,7 +172,8 @@ __device__ __forceinline__ void prefix_mark(const PrefixParams& pp, int k) {
 #endif
 }
 
-// grid = (prefix chunks, 128-row tiles, kv heads), block = 512 threads, 1 CTA per SM.
+// grid = (prefix chunks, 128-row tiles, kv heads), block = 512 threads, 1 CTA per SM
+// (grouped form: see PrefixParams).
 // Warp w works on TMEM lanes (= rows) 32 * (w % 4) .. +31, the only ones it may address, and on
 // column group w / 4 of whatever is being read: with 16 warps the staging, the softmax and the
 // stores around the two MMAs are spread over all four schedulers four warps deep.
@@ -177,12 +184,35 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   constexpr uint32_t kQBytes = kPrefixRows * D * 2;         // 32 KiB: 2 k-blocks of [128][64]
   constexpr uint32_t kKBytes = kPrefixChunk * D * 2;        // 64 KiB: 2 k-blocks of [256][64]; later P: 4 x [128][64]; later O rows
   constexpr uint32_t kVBytes = D * kPrefixChunk * 2;        // 64 KiB: 2 d-blocks of [256 tokens][64]
-  const int chunk = blockIdx.x, mtile = blockIdx.y, kvh = blockIdx.z;
+  int chunk = blockIdx.x, mtile = blockIdx.y;
+  const int kvh = blockIdx.z;
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
   const int qd = warp & 3, cg = warp >> 2;  // TMEM lane quarter, column group
   const int row = 32 * qd + lane;           // this thread's (request, head) row of the tile
   pdl_launch_dependents();
   prefix_mark(pp, 0);
+  // Which requests, which prefix: the whole batch and pp.prefix_len, or one group of the table.
+  int prefix_len = pp.prefix_len, n_req = pp.batch, page_row = 0;
+  const int32_t* req_list = nullptr;  // request index of the group's i-th member
+  if (pp.groups != nullptr) {
+    const int B = pp.groups_batch, G = pp.max_groups;
+    const int32_t* offs = pp.groups + groups_offsets_off(B);
+    const int n_groups = min(__ldg(pp.groups + 3), G);
+    int slot = blockIdx.x, g = 0;
+    for (; g < n_groups; ++g) {
+      const int tiles = ((__ldg(offs + g + 1) - __ldg(offs + g)) * p.group + kPrefixRows - 1) / kPrefixRows;
+      if (slot < tiles) break;
+      slot -= tiles;
+    }
+    if (g >= n_groups) return;
+    mtile = slot;
+    chunk = blockIdx.y;
+    prefix_len = min(__ldg(pp.groups + groups_prefix_off(B, G) + g) & ~15, pp.prefix_len);  // (pp.prefix_len: the cap)
+    if (chunk * kPrefixChunk >= prefix_len) return;
+    req_list = pp.groups + groups_rows_off(B, G) + __ldg(offs + g);
+    n_req = __ldg(offs + g + 1) - __ldg(offs + g);
+    page_row = __ldg(req_list);  // any member's block-table row names the prefix pages
+  }
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -201,7 +231,7 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   if (warp == 0) tmem_alloc(tslot, 512);
 
   const int tok_lo = chunk * kPrefixChunk;
-  const int tok_hi = min(tok_lo + kPrefixChunk, pp.prefix_len);
+  const int tok_hi = min(tok_lo + kPrefixChunk, prefix_len);
 
   // ---- K and V chunk: thread t stages half a token row (64 head-dim elements) of token t / 2
   const int tr = t >> 1, dh = t & 1;
@@ -210,7 +240,7 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
     const int tok = tok_lo + tr;
     const bool live = tok < tok_hi;
     int64_t phys = 0;
-    if (live) phys = page_of(p.block_table, p.bt_stride_b, 0, tok / kPage);
+    if (live) phys = page_of(p.block_table, p.bt_stride_b, page_row, tok / kPage);
     const uint8_t* krow = p.key_cache + phys * p.k_stride_page + (int64_t)(tok % kPage) * p.k_stride_token + (int64_t)kvh * p.k_stride_head;
     const uint8_t* vrow = p.value_cache + phys * p.v_stride_page + (int64_t)(tok % kPage) * p.v_stride_token + (int64_t)kvh * p.v_stride_head;
 #pragma unroll
@@ -224,8 +254,9 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   }
   // ---- Q tile: thread (row, cg) stages 32 of the row's 128 elements
   const int row_g = mtile * kPrefixRows + row;
-  const int b = row_g / p.group, head = row_g % p.group;
-  const bool row_live = b < pp.batch;
+  const int head = row_g % p.group;
+  const bool row_live = row_g / p.group < n_req;
+  const int b = !row_live ? 0 : (req_list != nullptr ? __ldg(req_list + row_g / p.group) : row_g / p.group);
   {
     const uint16_t* q = reinterpret_cast<const uint16_t*>(p.query) + (int64_t)(row_live ? b : 0) * p.q_stride_b +
                         (int64_t)(kvh * p.group + head) * p.q_stride_h;
@@ -365,8 +396,9 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
     for (int r = 0; r < 8; ++r) {
       const int orow = warp * 8 + r;
       const int rg = mtile * kPrefixRows + orow;
-      const int rb = rg / p.group, rh = rg % p.group;
-      if (rb >= pp.batch) break;
+      const int rh = rg % p.group;
+      if (rg / p.group >= n_req) break;
+      const int rb = req_list != nullptr ? __ldg(req_list + rg / p.group) : rg / p.group;
       const uint4 x = lds_16(sk + orow * 512 + ((lane ^ (orow & 31)) << 4));
       const int64_t pidx = (int64_t)rb * p.partial_stride_b + (int64_t)(kvh * p.group + rh) * p.partial_stride_h +
                            (int64_t)chunk * p.partial_stride_s;

@@ -251,6 +251,92 @@ def shared_prefix_decode_fp8_e4m3(
     return output
 
 
+def shared_prefix_decode_grouped_fp8_e4m3(
+    query: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_table: torch.Tensor,
+    seq_lens: torch.Tensor,
+    partial_output: torch.Tensor,
+    partial_max: torch.Tensor,
+    partial_sum: torch.Tensor,
+    output: torch.Tensor,
+    k_scale: torch.Tensor,
+    v_scale: torch.Tensor,
+    max_seq_len: int,
+    split_size: int,
+    groups: "PrefixGroups",
+    *,
+    max_prefix_len: Optional[int] = None,
+    sm_scale: float = 0.0,
+) -> torch.Tensor:
+    """Decode step of a batch with any number of shared-prefix groups plus requests in none
+    (``groups`` from ``group_shared_prefixes``, read on the device): dense tcgen05 pass per group,
+    split-KV pass from each request's own start, one merge.  The workspace needs
+    ``ceil(min(max_prefix_len, max_seq_len) / 256) + ceil(max_seq_len / split_size)`` slots."""
+    torch.ops.l20_stack.shared_prefix_decode_grouped_fp8_e4m3(
+        query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max, partial_sum, output,
+        k_scale, v_scale, float(sm_scale), max_seq_len, split_size, groups.buffer, groups.max_groups,
+        int(max_seq_len if max_prefix_len is None else max_prefix_len),
+    )
+    return output
+
+
+class PrefixGroups:
+    """Device-resident result of ``group_shared_prefixes`` (layout of ``pfd_group_shared_prefixes``
+    in include/paged_fp8_decode.h).  The views below alias the buffer; reading them on the host
+    (``to_lists``) is for tests and traces, the decode path consumes the buffer on the device."""
+
+    HEADER = 8
+
+    def __init__(self, buffer: torch.Tensor, batch: int, max_groups: int):
+        self.buffer, self.batch, self.max_groups = buffer, batch, max_groups
+        b, g, h = batch, max_groups, self.HEADER
+        self.row_prefix_len = buffer[h:h + b]
+        self.row_group = buffer[h + b:h + 2 * b]
+        self.group_offsets = buffer[h + 2 * b:h + 2 * b + g + 1]
+        self.group_prefix_len = buffer[h + 2 * b + g + 1:h + 2 * b + 2 * g + 1]
+        self.group_rows = buffer[h + 2 * b + 2 * g + 1:h + 3 * b + 2 * g + 1]
+
+    def to_lists(self) -> list[list[int]]:
+        """The groups as lists of request indices (one device-to-host copy of the small buffer)."""
+        host = self.buffer[: self.HEADER + 3 * self.batch + 2 * self.max_groups + 1].cpu()
+        view = PrefixGroups(host, self.batch, self.max_groups)
+        n = int(host[3])
+        off = view.group_offsets.tolist()
+        rows = view.group_rows.tolist()
+        return [rows[off[g]:off[g + 1]] for g in range(n)]
+
+
+def group_shared_prefixes(
+    block_table: torch.Tensor,
+    *,
+    prefix_lengths: Optional[torch.Tensor] = None,
+    uniform_prefix_len: int = 0,
+    seq_lens: Optional[torch.Tensor] = None,
+    min_batch: int = 8,
+    min_prefix_len: int = 4096,
+    max_groups: Optional[int] = None,
+    buffer: Optional[torch.Tensor] = None,
+) -> PrefixGroups:
+    """Shared-prefix groups of a decode batch, found on the device without a host copy: same key
+    and filters as the reference's ``find_l20_shared_prefix_groups``
+    (integrations/vllm/l20_shared_prefix_decode_dispatch.py:41-76), any number of groups.  The
+    prefix length of a request comes from ``prefix_lengths`` (int32, device), else from
+    ``uniform_prefix_len``, else from ``seq_lens`` as ``floor(min / 16) * 16``."""
+    batch = block_table.shape[0]
+    if max_groups is None:
+        max_groups = max(1, batch // max(1, min_batch))
+    if buffer is None:
+        words = torch.ops.l20_stack.prefix_groups_bytes(batch, max_groups) // 4
+        buffer = torch.empty(words, dtype=torch.int32, device=block_table.device)
+    torch.ops.l20_stack.group_shared_prefixes(
+        block_table, prefix_lengths, int(uniform_prefix_len), seq_lens, int(min_batch), int(min_prefix_len),
+        int(max_groups), buffer,
+    )
+    return PrefixGroups(buffer, batch, max_groups)
+
+
 def merge_packed_partials(packed: torch.Tensor, output: torch.Tensor) -> torch.Tensor:
     """LSE-merge ``[parts, B, Hq, D + 2]`` packed partials into ``output [B, Hq, D]``."""
     torch.ops.l20_stack.merge_packed_partials(packed, output)
@@ -311,6 +397,14 @@ def _register_fake() -> None:
 
     @torch.library.register_fake("l20_stack::merge_packed_partials")
     def _merge_packed_partials_fake(packed, output):
+        return None
+
+    @torch.library.register_fake("l20_stack::shared_prefix_decode_grouped_fp8_e4m3")
+    def _shared_prefix_decode_grouped_fake(*args):
+        return None
+
+    @torch.library.register_fake("l20_stack::group_shared_prefixes")
+    def _group_shared_prefixes_fake(*args):
         return None
 
     @torch.library.register_fake("l20_stack::resolve_slots")

@@ -16,107 +16,135 @@ from __future__ import annotations
 import json
 import os
 import time
-from collections import defaultdict
-from pathlib import Path
-from typing import Sequence
+from typing import Optional, Sequence
 
 import torch
 
-PREFIX_CHUNK = 256  # prefix tokens per CTA of the dense pass
+PREFIX_CHUNK = 256  # prefix tokens per work item of the dense pass
+_SWITCH = "VLLM_ENABLE_L20_SHARED_PREFIX_DECODE"
+_TRACE = "VLLM_L20_SHARED_PREFIX_DECODE_TRACE"
 
 
 def l20_shared_prefix_decode_enabled() -> bool:
-    return os.getenv("VLLM_ENABLE_L20_SHARED_PREFIX_DECODE", "0") == "1"
+    """The reference's opt-in switch (l20_shared_prefix_decode_dispatch.py:18-19)."""
+    return os.environ.get(_SWITCH, "0") == "1"
 
 
 def l20_shared_prefix_trace(event: str, **fields) -> None:
-    path = os.getenv("VLLM_L20_SHARED_PREFIX_DECODE_TRACE")
-    if not path:
+    """Append one JSON line ``{"event", "ts", **fields}`` to the file the trace switch names, as
+    the reference's trace does (:22-31); a trace that cannot be written is dropped silently."""
+    target = os.environ.get(_TRACE)
+    if not target:
         return
-    payload = {"event": event, "ts": time.time(), **fields}
+    record = dict(fields, event=event, ts=time.time())
     try:
-        with Path(path).open("a", encoding="utf-8") as trace_file:
-            trace_file.write(json.dumps(payload, sort_keys=True) + "\n")
+        with open(target, "a", encoding="utf-8") as sink:
+            print(json.dumps(record, sort_keys=True), file=sink)
     except OSError:
-        return
+        pass
 
 
-def _to_int_list(values: torch.Tensor | Sequence[int]) -> list[int]:
+def _lengths_on_host(values) -> list[int]:
     if isinstance(values, torch.Tensor):
-        return [int(item) for item in values.detach().cpu().tolist()]
-    return [int(item) for item in values]
+        values = values.detach().to("cpu").tolist()
+    return list(map(int, values))
 
 
-def shared_prefix_block_key(
-    block_table_row: torch.Tensor, prefix_length: int, *, page_size: int = 16
-) -> tuple[int, tuple[int, ...]]:
-    pages = (int(prefix_length) + page_size - 1) // page_size
-    blocks = block_table_row[:pages].detach().cpu().tolist()
-    return int(prefix_length), tuple(int(block) for block in blocks)
+def shared_prefix_block_key(block_table_row: torch.Tensor, prefix_length: int, *, page_size: int = 16):
+    """The grouping key of one request: its prefix length and the block ids that hold the prefix."""
+    n_pages = -(-int(prefix_length) // page_size)
+    return int(prefix_length), tuple(map(int, block_table_row[:n_pages].detach().to("cpu").tolist()))
 
 
 def find_l20_shared_prefix_groups(
     block_tables: torch.Tensor,
-    prefix_lengths: torch.Tensor | Sequence[int],
+    prefix_lengths,
     *,
     min_batch: int = 8,
     min_prefix_length: int = 4096,
     page_size: int = 16,
 ) -> list[list[int]]:
-    """Group request indices by identical prefix length and block chain."""
+    """Requests with the same prefix length whose prefixes sit in the same blocks, as lists of
+    request indices (groups ordered by first member, groups below ``min_batch`` and prefixes below
+    ``min_prefix_length`` left out): the reference function of the same name (:41-76).
+
+    A block table on the GPU is grouped there (``group_shared_prefixes``: hash, verify, number --
+    the table itself never leaves the device, only the small result is read back for this
+    list-returning interface); a table in host memory is grouped with ``torch.unique`` over the
+    prefix columns, one call per distinct prefix length."""
     if block_tables.ndim != 2:
         raise ValueError("block_tables must have shape [B, max_pages]")
-    lengths = _to_int_list(prefix_lengths)
-    if len(lengths) != block_tables.shape[0]:
+    lengths = _lengths_on_host(prefix_lengths)
+    batch = block_tables.shape[0]
+    if len(lengths) != batch:
         raise ValueError("prefix_lengths must have one entry per request")
-    table = block_tables.detach().cpu()  # one copy for the whole batch
-    groups: dict[tuple[int, tuple[int, ...]], list[int]] = defaultdict(list)
-    for index, prefix_length in enumerate(lengths):
-        if prefix_length < min_prefix_length:
-            continue
-        groups[shared_prefix_block_key(table[index], prefix_length, page_size=page_size)].append(index)
-    return [indices for indices in groups.values() if len(indices) >= min_batch]
+    if block_tables.is_cuda and page_size == 16 and block_tables.dtype == torch.int32 and batch <= 2048:
+        from . import l20_paged_decode as ops
+
+        found = ops.group_shared_prefixes(
+            block_tables, prefix_lengths=torch.tensor(lengths, dtype=torch.int32, device=block_tables.device),
+            min_batch=min_batch, min_prefix_len=max(int(min_prefix_length), 1), max_groups=max(batch, 1),
+        )
+        return found.to_lists()
+    table = block_tables.detach().to("cpu")
+    by_first_member: dict[int, list[int]] = {}
+    for length in sorted(set(x for x in lengths if x >= min_prefix_length)):
+        members = torch.tensor([i for i, x in enumerate(lengths) if x == length], dtype=torch.long)
+        n_pages = -(-length // page_size)
+        _, klass = torch.unique(table[members, :n_pages], dim=0, return_inverse=True)
+        for k in klass.unique().tolist():
+            rows = members[klass == k].tolist()
+            if len(rows) >= min_batch:
+                by_first_member[rows[0]] = rows
+    return [by_first_member[first] for first in sorted(by_first_member)]
+
+
+def _why_not(query, key_cache, block_tables, prefix_lengths, page_size, min_batch, min_prefix_length) -> Optional[str]:
+    """None when the conservative single-group dispatch applies, else the first reason it does not
+    (the conditions of the reference's gate, :122-159, with sm_100 and an e4m3 cache in place of
+    its sm_89 / unquantised ones)."""
+    if not l20_shared_prefix_decode_enabled():
+        return "switch"
+    if not (torch.cuda.is_available() and query.is_cuda):
+        return "device"
+    if torch.cuda.get_device_capability(query.device) != (10, 0):
+        return "arch"
+    if torch.cuda.is_current_stream_capturing():
+        return "capturing"  # this gate reads the grouping result on the host
+    if query.dtype not in (torch.float16, torch.bfloat16) or key_cache.dtype != torch.float8_e4m3fn:
+        return "dtype"
+    shapes_ok = (
+        query.ndim == 3 and key_cache.ndim == 4 and block_tables.ndim == 2
+        and block_tables.shape[0] == query.shape[0]
+        and query.shape[-1] == 128 and key_cache.shape[-1] == 128
+        and key_cache.shape[1] == page_size == 16
+    )
+    if not shapes_ok:
+        return "shape"
+    if query.shape[0] < min_batch:
+        return "batch"
+    lengths = _lengths_on_host(prefix_lengths)
+    if not lengths or lengths[0] % page_size:
+        return "prefix_alignment"
+    groups = find_l20_shared_prefix_groups(
+        block_tables, lengths, min_batch=min_batch, min_prefix_length=min_prefix_length, page_size=page_size
+    )
+    if len(groups) != 1 or len(groups[0]) != query.shape[0]:
+        return "groups"
+    return None
 
 
 def should_dispatch_l20_shared_prefix_paged_decode(
     query: torch.Tensor,
     key_cache: torch.Tensor,
     block_tables: torch.Tensor,
-    prefix_lengths: torch.Tensor | Sequence[int],
+    prefix_lengths,
     *,
     page_size: int = 16,
     min_batch: int = 8,
     min_prefix_length: int = 4096,
 ) -> bool:
-    if not l20_shared_prefix_decode_enabled():
-        return False
-    if not torch.cuda.is_available() or not query.is_cuda:
-        return False
-    if torch.cuda.get_device_capability(query.device) != (10, 0):
-        return False
-    if torch.cuda.is_current_stream_capturing():
-        return False  # the grouping below copies the block table to the host
-    if query.dtype not in (torch.float16, torch.bfloat16):
-        return False
-    if key_cache.dtype != torch.float8_e4m3fn:
-        return False
-    if query.ndim != 3 or key_cache.ndim != 4:
-        return False
-    if block_tables.ndim != 2 or block_tables.shape[0] != query.shape[0]:
-        return False
-    if query.shape[0] < min_batch:
-        return False
-    if query.shape[-1] != 128 or key_cache.shape[-1] != 128:
-        return False
-    if key_cache.shape[1] != page_size or page_size != 16:
-        return False
-    lengths = _to_int_list(prefix_lengths)
-    if not lengths or lengths[0] % page_size:
-        return False
-    groups = find_l20_shared_prefix_groups(
-        block_tables, lengths, min_batch=min_batch, min_prefix_length=min_prefix_length, page_size=page_size
-    )
-    return len(groups) == 1 and len(groups[0]) == query.shape[0]
+    return _why_not(query, key_cache, block_tables, prefix_lengths, page_size, min_batch, min_prefix_length) is None
 
 
 def allocate_shared_prefix_workspace(query: torch.Tensor, max_seq_len: int, prefix_length: int, *, suffix_split_size: int = 512):
@@ -196,7 +224,7 @@ def maybe_l20_shared_prefix_paged_decode(
         query, key_cache, block_tables, prefix_lengths, page_size=page_size
     ):
         return None
-    prefix_length = _to_int_list(prefix_lengths)[0]
+    prefix_length = _lengths_on_host(prefix_lengths)[0]
     out = shared_paged_prefix_paged_suffix_gqa_decode_attention_fp8(
         query, key_cache, value_cache, block_tables, seq_lens, prefix_length, k_scale=k_scale, v_scale=v_scale,
         max_seq_len=max_seq_len, suffix_split_size=suffix_split_size, workspace=workspace,

@@ -5,7 +5,7 @@ decode kernels store their packed rows into every "rank's" receive buffer and re
 flags; the exchange merge kernel checks the flags and merges.  Held against the CPU oracle.
 
 The expiry case: a rank that is not asked to store never releases its flag; the other ranks'
-merge kernels give up after the wait limit, set device status 3 and leave their output alone, and
+merge kernels give up after the wait limit, set device status 4 and leave their output alone, and
 the next complete step is right again.
 """
 
@@ -190,7 +190,7 @@ def test_a_rank_that_does_not_publish_ends_the_wait_with_a_status(built_libs):
         cabi.set_wait_limit_ns(2_000_000)  # 2 ms
         try:
             outs = step(skip=1)  # rank 1 is not asked to store: its flag never arrives
-            assert cabi.device_status() == 3
+            assert cabi.device_status() == 4
             assert all(bool((o == 7.0).all()) for o in outs), "nothing is merged when a flag is missing"
             assert cabi.device_status() == 0, "reading the status clears it"
         finally:

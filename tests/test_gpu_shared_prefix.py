@@ -122,3 +122,157 @@ def test_dispatch_module_end_to_end(built_libs, monkeypatch):
     other = g.block_table.clone()
     other[5, 0] = other[6, 1]
     assert not d.should_dispatch_l20_shared_prefix_paged_decode(g.query, g.key_cache, other, prefix, min_prefix_length=1024)
+
+
+def _random_grouped_table(gen, batch, cols, n_groups, prefix_pages, loners):
+    """A block table in which `n_groups` sets of rows share their first pages (each set its own
+    chain and prefix length), `loners` rows share nothing, and everything is shuffled."""
+    table = torch.randint(0, 1 << 20, (batch, cols), generator=gen, dtype=torch.int32)
+    lengths = torch.zeros(batch, dtype=torch.int32)
+    order = torch.randperm(batch, generator=gen).tolist()
+    free = order[loners:]
+    per = len(free) // max(n_groups, 1)
+    for g in range(n_groups):
+        rows = free[g * per:(g + 1) * per] if g < n_groups - 1 else free[g * per:]
+        pages = prefix_pages[g % len(prefix_pages)]
+        chain = torch.randint(0, 1 << 20, (pages,), generator=gen, dtype=torch.int32)
+        for r in rows:
+            table[r, :pages] = chain
+            lengths[r] = pages * 16
+    for r in order[:loners]:
+        lengths[r] = prefix_pages[0] * 16  # same length as a group, different chain
+    return table, lengths
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_device_grouping_equals_the_oracle_on_random_tables(built_libs, seed):
+    from single_gpu_inference_lab_b200 import l20_paged_decode as ops
+
+    gen = torch.Generator().manual_seed(100 + seed)
+    batch = [8, 37, 64, 200, 513, 2048][seed]
+    cols = [40, 64, 300, 128, 96, 48][seed]
+    n_groups = [1, 3, 4, 7, 20, 60][seed]
+    pages = [[8], [4, 9, 30], [256, 17], [64], [5, 6, 7, 90], [16, 33]][seed]
+    table, lengths = _random_grouped_table(gen, batch, cols, n_groups, pages, loners=batch // 5)
+    if seed == 2:  # near misses: one block of the chain differs, at its start, middle and end
+        grouped = [r for r in range(batch) if lengths[r] == 256 * 16][:3]
+        for r, col in zip(grouped, (0, 128, 255)):
+            table[r, col] += 1
+    if seed == 3:  # the same chain under two prefix lengths is two groups
+        same = [r for r in range(batch) if lengths[r] > 0][:40]
+        for r in same[:20]:
+            table[r] = table[same[0]]
+            lengths[r] = 64 * 16
+        for r in same[20:]:
+            table[r] = table[same[0]]
+            lengths[r] = 32 * 16
+    for min_batch, min_prefix in ((1, 16), (2, 64), (8, 16), (8, 4096)):
+        want = oracle.find_shared_prefix_groups(table, lengths, min_batch=min_batch, min_prefix_length=min_prefix)
+        found = ops.group_shared_prefixes(table.to(DEV), prefix_lengths=lengths.to(DEV), min_batch=min_batch,
+                                          min_prefix_len=min_prefix, max_groups=batch)
+        torch.cuda.synchronize()
+        assert found.to_lists() == want, (seed, min_batch, min_prefix)
+        row_group = found.row_group.cpu().tolist()
+        row_prefix = found.row_prefix_len.cpu().tolist()
+        for gi, rows in enumerate(want):
+            assert all(row_group[r] == gi and row_prefix[r] == int(lengths[r]) for r in rows)
+        in_groups = {r for rows in want for r in rows}
+        assert all(row_group[r] == -1 and row_prefix[r] == 0 for r in range(batch) if r not in in_groups)
+
+
+def test_device_grouping_derives_the_candidate_prefix_and_caps_the_groups(built_libs):
+    from single_gpu_inference_lab_b200 import l20_paged_decode as ops
+    from single_gpu_inference_lab_b200 import l20_shared_prefix_decode_dispatch as d
+
+    w = make_inputs("shared-prefix-b64", seed=4, batch=24, shrink=0.25)  # prefix 1024, private suffixes
+    g = w.to(DEV)
+    cand = (int(w.seq_lens.min()) // 16) * 16
+    want = oracle.find_shared_prefix_groups(w.block_table, [cand] * 24, min_batch=8, min_prefix_length=512)
+    found = ops.group_shared_prefixes(g.block_table, seq_lens=g.seq_lens, min_batch=8, min_prefix_len=512)
+    assert found.to_lists() == want
+    uniform = ops.group_shared_prefixes(g.block_table, uniform_prefix_len=w.prefix_len, min_batch=8, min_prefix_len=512)
+    assert uniform.to_lists() == [list(range(24))]
+    # the list-returning mirror of the reference function runs the same kernels for a CUDA table
+    assert d.find_l20_shared_prefix_groups(g.block_table, [w.prefix_len] * 24, min_batch=8, min_prefix_length=512) == [list(range(24))]
+    # capacity: with room for one group only the first (by first member) comes out
+    table = w.block_table.clone()
+    table[12:, 0] += 7  # rows 12.. form a second group
+    both = oracle.find_shared_prefix_groups(table, [w.prefix_len] * 24, min_batch=8, min_prefix_length=512)
+    assert len(both) == 2
+    capped = ops.group_shared_prefixes(table.to(DEV), uniform_prefix_len=w.prefix_len, min_batch=8, min_prefix_len=512, max_groups=1)
+    assert capped.to_lists() == both[:1]
+    assert capped.row_group.cpu().tolist()[12:] == [-1] * 12
+
+
+def _mixed_batch(seed, prefix_a, prefix_b):
+    """24 requests: rows 0-9 share a prefix of `prefix_a` tokens, rows 10-17 another of `prefix_b`
+    tokens in other pages, rows 18-23 share nothing."""
+    w = make_inputs("shared-prefix-b64", seed=seed, batch=24, shrink=0.25)  # every row: the same 1024-token prefix
+    gen = torch.Generator().manual_seed(seed)
+    table = w.block_table.clone()
+    pages = w.key_cache.shape[0]
+    chain_b = torch.randperm(pages, generator=gen)[: -(-prefix_b // 16)].to(torch.int32)
+    for r in range(10, 18):
+        table[r, : chain_b.numel()] = chain_b
+    for r in range(18, 24):
+        table[r, :64] = torch.randperm(pages, generator=gen)[:64].to(torch.int32)
+    lengths = torch.tensor([prefix_a] * 10 + [prefix_b] * 8 + [prefix_a] * 6, dtype=torch.int32)
+    w.block_table = table
+    w.seq_lens = torch.maximum(w.seq_lens, lengths + 1)
+    w.max_seq_len = int(w.seq_lens.max())
+    return w, lengths
+
+
+@pytest.mark.parametrize("prefix_a,prefix_b,bound,min_batch", [
+    (1024, 512, None, 8),     # two groups + six requests in none
+    (1024, 528, None, 8),     # a prefix that ends inside a 256-token chunk
+    (1000, 520, None, 8),     # lengths that are no multiple of 16: used up to the page boundary
+    (1024, 512, 768, 8),      # a bound below the longer prefix: the rest goes through the split-KV pass
+    (1024, 512, None, 16),    # no group is large enough: everything through the split-KV pass
+    (1024, 512, 0, 8),        # a bound of zero: no dense pass at all
+])
+def test_grouped_decode_of_a_mixed_batch_matches_the_oracle(cabi, prefix_a, prefix_b, bound, min_batch):
+    w, lengths = _mixed_batch(11, prefix_a, prefix_b)
+    exp = oracle.reference(w.query, w.key_cache, w.value_cache, w.block_table.long(), w.seq_lens, w.k_scale, w.v_scale)
+    g = w.to(DEV)
+    groups, max_groups = cabi.group_shared_prefixes(g.block_table, prefix_lengths=lengths.to(DEV), min_batch=min_batch, min_prefix_len=256)
+    split = 128
+    cap = w.max_seq_len if bound is None else min(bound, w.max_seq_len)
+    slots = -(-cap // 256) + -(-w.max_seq_len // split)
+    b, hq, d = g.query.shape
+    ws = (
+        torch.full((b, hq, slots, d), float("nan"), device=DEV),
+        torch.full((b, hq, slots), float("nan"), device=DEV),
+        torch.full((b, hq, slots), float("nan"), device=DEV),
+    )
+    for step in range(2):  # the same groups buffer serves every layer of a model step
+        out = torch.full_like(g.query, float("nan"))
+        cabi.shared_prefix_decode_grouped_fp8_e4m3(
+            g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens, groups=groups, max_groups=max_groups,
+            max_prefix_len=bound, k_scale=g.k_scale, v_scale=g.v_scale, max_seq_len=w.max_seq_len, split_size=split,
+            output=out, workspace=ws)
+        torch.cuda.synchronize()
+        assert cabi.device_status() == 0
+        assert_within_gate(out, exp, f"grouped decode step {step}")
+
+
+def test_grouped_decode_through_the_dispatcher_and_its_workspace_check(built_libs):
+    from single_gpu_inference_lab_b200 import l20_paged_decode as ops
+
+    w, lengths = _mixed_batch(12, 1024, 512)
+    exp = oracle.reference(w.query, w.key_cache, w.value_cache, w.block_table.long(), w.seq_lens, w.k_scale, w.v_scale)
+    g = w.to(DEV)
+    found = ops.group_shared_prefixes(g.block_table, prefix_lengths=lengths.to(DEV), min_batch=8, min_prefix_len=256)
+    assert found.to_lists() == [list(range(10)), list(range(10, 18))]
+    b, hq, d = g.query.shape
+    slots = -(-w.max_seq_len // 256) + -(-w.max_seq_len // 128)
+    ws = (torch.empty(b, hq, slots, d, device=DEV), torch.empty(b, hq, slots, device=DEV), torch.empty(b, hq, slots, device=DEV))
+    out = torch.empty_like(g.query)
+    ops.shared_prefix_decode_grouped_fp8_e4m3(g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens, *ws, out,
+                                              g.k_scale, g.v_scale, w.max_seq_len, 128, found)
+    torch.cuda.synchronize()
+    assert_within_gate(out, exp, "grouped decode through torch.ops")
+    small = tuple(t[:, :, : slots - 1].contiguous() for t in ws)
+    with pytest.raises(RuntimeError, match="needs"):
+        ops.shared_prefix_decode_grouped_fp8_e4m3(g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens, *small, out,
+                                                  g.k_scale, g.v_scale, w.max_seq_len, 128, found)

@@ -124,7 +124,7 @@ print(f"RANK{{rank}} exchange_ok={{ok}} max_abs={{worst:.2e}} missing_status={{s
 torch.cuda.synchronize(); dist.barrier()
 x.close()
 dist.destroy_process_group()
-sys.exit(0 if ok and after and status == 3 and untouched else 1)
+sys.exit(0 if ok and after and status == 4 and untouched else 1)
 """
 
 
@@ -143,4 +143,4 @@ def test_in_kernel_exchange_on_two_gpus_and_a_rank_that_does_not_publish(tmp_pat
     assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
     for r in (0, 1):
         assert f"RANK{r} exchange_ok=True" in proc.stdout, proc.stdout[-2000:]
-        assert f"missing_status=3 untouched=True after_ok=True" in proc.stdout
+        assert f"missing_status=4 untouched=True after_ok=True" in proc.stdout
