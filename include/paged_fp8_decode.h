@@ -315,10 +315,14 @@ int pfd_exchange_free(void* ptr);
  * prefix's block ids); prefixes shorter than min_prefix_len and groups of fewer than min_batch
  * requests are dropped; groups are numbered by their first member, members ascend.  The prefix
  * length of row b is prefix_lengths[b] (device int32), or uniform_prefix_len when that is NULL
- * and this positive, or else floor(min(seq_lens) / 16) * 16 (the candidate of the reference's
- * trace_l20_shared_prefix_decode_candidate, :245-315).  Unlike the reference, which dispatches
- * only when one group spans the batch, any number of groups (up to max_groups; later ones are
- * left out) plus requests in no group come out.
+ * and this positive.  With neither, the prefixes are DISCOVERED from the table and seq_lens: rows
+ * are keyed on their first ceil(min_prefix_len / 16) pages, and a group's prefix is as long as all
+ * its members agree with its first member, in whole pages that every member has filled.  (The
+ * reference's trace_l20_shared_prefix_decode_candidate, :245-315, tries the one candidate
+ * floor(min(seq_lens) / 16) * 16, which finds nothing once the requests have private suffixes of
+ * a page or more.)  Unlike the reference, which dispatches only when one group spans the batch,
+ * any number of groups (up to max_groups; later ones are left out) plus requests in no group come
+ * out.
  *
  * `groups` (device, pfd_prefix_groups_bytes() bytes) as int32 words: [0] magic, [1] batch,
  * [2] max_groups, [3] number of groups, [4] rows in groups, [5..7] 0, then row_prefix_len[batch]

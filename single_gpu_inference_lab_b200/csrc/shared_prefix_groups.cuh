@@ -12,6 +12,12 @@
 //                           chain (verified element by element, so a hash collision costs a
 //                           second look, never a wrong group) becomes the row's representative
 //   3. prefix_finish_kernel one CTA: numbers the groups, lays out their row lists
+//
+// Without given prefix lengths the kernels DISCOVER them: rows are keyed on their first
+// ceil(min_prefix_len / 16) pages, and a group's prefix is then as long as all of its members
+// agree with the representative, in whole pages every member has filled (the reference's trace,
+// :245-315, tries one candidate length, floor(min(seq_lens) / 16) * 16, which misses every batch
+// whose requests have grown private suffixes of a page or more).
 #pragma once
 
 #include <cstdint>
@@ -28,7 +34,7 @@ constexpr int kGroupsHeader = 8;  // magic, batch, max_groups, num_groups, group
 //   group_offsets[G+1] group g's rows are group_rows[group_offsets[g] .. group_offsets[g + 1])
 //   group_prefix_len[G]
 //   group_rows[B]
-//   scratch: rep[B], count[B], hash[2 B]
+//   scratch: rep[B], count[B], lcp[B], hash[2 B]
 __host__ __device__ inline int64_t groups_row_prefix_off() { return kGroupsHeader; }
 __host__ __device__ inline int64_t groups_row_group_off(int B) { return kGroupsHeader + (int64_t)B; }
 __host__ __device__ inline int64_t groups_offsets_off(int B) { return kGroupsHeader + 2LL * B; }
@@ -36,7 +42,8 @@ __host__ __device__ inline int64_t groups_prefix_off(int B, int G) { return grou
 __host__ __device__ inline int64_t groups_rows_off(int B, int G) { return groups_prefix_off(B, G) + G; }
 __host__ __device__ inline int64_t groups_rep_off(int B, int G) { return groups_rows_off(B, G) + B; }
 __host__ __device__ inline int64_t groups_count_off(int B, int G) { return groups_rep_off(B, G) + B; }
-__host__ __device__ inline int64_t groups_hash_off(int B, int G) { return (groups_count_off(B, G) + B + 1) & ~1LL; }
+__host__ __device__ inline int64_t groups_lcp_off(int B, int G) { return groups_count_off(B, G) + B; }
+__host__ __device__ inline int64_t groups_hash_off(int B, int G) { return (groups_lcp_off(B, G) + B + 1) & ~1LL; }
 __host__ __device__ inline int64_t groups_words(int B, int G) { return groups_hash_off(B, G) + 2LL * B; }
 
 struct GroupParams {
@@ -45,7 +52,7 @@ struct GroupParams {
   int32_t bt_cols;
   const int32_t* prefix_lengths;  // per row, or NULL
   int32_t uniform_prefix_len;     // used when prefix_lengths is NULL and this is > 0
-  const int32_t* seq_lens;        // else: every row's candidate is floor(min(seq_lens) / 16) * 16
+  const int32_t* seq_lens;        // else: discover the prefixes (see above); needs the sequence lengths
   int32_t batch, min_batch, min_prefix_len, max_groups;
   int32_t* groups;
 };
@@ -57,35 +64,28 @@ __device__ __forceinline__ uint64_t mix64(uint64_t x) {
   return x;
 }
 
-// Prefix length the grouping uses for row r (0 = the row takes no part).
-__device__ __forceinline__ int group_prefix_len_of(const GroupParams& gp, int r, int derived) {
-  int len = gp.prefix_lengths != nullptr ? gp.prefix_lengths[r] : (gp.uniform_prefix_len > 0 ? gp.uniform_prefix_len : derived);
+__device__ __forceinline__ bool groups_discover(const GroupParams& gp) {
+  return gp.prefix_lengths == nullptr && gp.uniform_prefix_len <= 0;
+}
+
+// Length of the chain row r is keyed on (0 = the row takes no part).
+__device__ __forceinline__ int group_key_len_of(const GroupParams& gp, int r) {
+  int len;
+  if (groups_discover(gp)) {
+    len = (max(gp.min_prefix_len, 16) + 15) / 16 * 16;
+    if (gp.seq_lens[r] < len) return 0;
+  } else {
+    len = gp.prefix_lengths != nullptr ? gp.prefix_lengths[r] : gp.uniform_prefix_len;
+  }
   if (len < gp.min_prefix_len || len <= 0) return 0;
   if ((len + 15) / 16 > gp.bt_cols) return 0;  // a prefix the block table cannot hold
   return len;
 }
 
-// min over seq_lens, floored to whole pages (every thread of the CTA gets it)
-__device__ __forceinline__ int derived_candidate(const GroupParams& gp, int* sh) {
-  if (gp.prefix_lengths != nullptr || gp.uniform_prefix_len > 0 || gp.seq_lens == nullptr) return 0;
-  int m = 0x7fffffff;
-  for (int i = threadIdx.x; i < gp.batch; i += blockDim.x) m = min(m, gp.seq_lens[i]);
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) m = min(m, __shfl_xor_sync(0xffffffffu, m, off));
-  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = m;
-  __syncthreads();
-  m = 0x7fffffff;
-  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) m = min(m, sh[i]);
-  __syncthreads();
-  return m == 0x7fffffff ? 0 : (m / 16) * 16;
-}
-
 __global__ void __launch_bounds__(256) prefix_hash_kernel(const GroupParams gp) {
-  __shared__ int sh_i[8];
   __shared__ unsigned long long sh_h[8];
   const int r = blockIdx.x, B = gp.batch, G = gp.max_groups;
-  const int derived = derived_candidate(gp, sh_i);
-  const int len = group_prefix_len_of(gp, r, derived);
+  const int len = group_key_len_of(gp, r);
   const int pages = (len + 15) / 16;
   const int32_t* row = gp.block_table + (int64_t)r * gp.bt_stride_b;
   unsigned long long h = 0;
@@ -104,6 +104,8 @@ __global__ void __launch_bounds__(256) prefix_hash_kernel(const GroupParams gp) 
     g[groups_hash_off(B, G) + 2 * r + 1] = (int32_t)(uint32_t)(h >> 32);
     g[groups_count_off(B, G) + r] = 0;
     g[groups_row_prefix_off() + r] = len;  // provisional: the finish kernel clears rows left without a group
+    // discovery: whole pages this row has filled (and its table can name) bound its group's prefix
+    g[groups_lcp_off(B, G) + r] = groups_discover(gp) ? min(gp.seq_lens[r] / 16, gp.bt_cols) : (len + 15) / 16;
     if (r == 0) {
       g[0] = kGroupsMagic; g[1] = B; g[2] = G; g[3] = 0; g[4] = 0; g[5] = g[6] = g[7] = 0;
     }
@@ -151,6 +153,17 @@ __global__ void __launch_bounds__(256) prefix_match_kernel(const GroupParams gp)
     __syncthreads();
     if (equal) { found = cand; break; }
     start = cand + 1;
+  }
+  if (groups_discover(gp) && found != r) {
+    // how far beyond the key pages this row agrees with its representative
+    const int32_t* other = gp.block_table + (int64_t)found * gp.bt_stride_b;
+    const int limit = min(min(gp.seq_lens[r], gp.seq_lens[found]) / 16, gp.bt_cols);
+    int first_diff = limit;
+    for (int i = pages + threadIdx.x; i < limit; i += blockDim.x)
+      if (mine[i] != other[i]) { first_diff = i; break; }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) first_diff = min(first_diff, __shfl_xor_sync(0xffffffffu, first_diff, off));
+    if ((threadIdx.x & 31) == 0) atomicMin(g + groups_lcp_off(B, G) + found, first_diff);
   }
   if (threadIdx.x == 0) {
     rep[r] = found;
@@ -223,7 +236,8 @@ __global__ void __launch_bounds__(1024) prefix_finish_kernel(const GroupParams g
       sh_off[r] = obase + (k == 1 ? cnt[0] : 0);
       if (sh_gid[r] >= 0) {
         g[groups_offsets_off(B) + sh_gid[r]] = sh_off[r];
-        g[groups_prefix_off(B, G) + sh_gid[r]] = g[groups_row_prefix_off() + r];
+        g[groups_prefix_off(B, G) + sh_gid[r]] =
+            groups_discover(gp) ? 16 * g[groups_lcp_off(B, G) + r] : g[groups_row_prefix_off() + r];
       }
     }
   }
@@ -248,6 +262,7 @@ __global__ void __launch_bounds__(1024) prefix_finish_kernel(const GroupParams g
     for (int i = rp; i < r; ++i) rank += sh_rep[i] == rp;
     g[groups_row_group_off(B) + r] = gid;
     g[groups_rows_off(B, G) + sh_off[rp] + rank] = r;
+    if (groups_discover(gp)) g[groups_row_prefix_off() + r] = 16 * g[groups_lcp_off(B, G) + rp];
   }
 }
 

@@ -35,7 +35,14 @@ What differs from the reference installer, because vLLM on sm_100 differs from v
 * it imports what its text uses (``os``, ``json``), which the reference text assumes;
 * FlashInfer asks for the HND cache layout on sm_100, so the hook hands the operator a
   ``[pages, 16, Hkv, D]`` *view* of either layout (the kernels take strides);
-* it copies the operator's two modules and two shared libraries next to each other into
+* what depends on the step's block table and lengths alone -- the balanced kernel's work split
+  (plan), the shared-prefix groups, the workspace -- is made once per model step by the first
+  layer and kept on the step's ``FIDecode`` (``l20_decode_step.py``), not once per layer;
+* with ``VLLM_ENABLE_L20_SHARED_PREFIX_DECODE=1`` (the reference's switch, which there only
+  traces candidates: install_l20_shared_prefix_decode.py:92-110) a step whose batch has
+  shared-prefix groups runs the grouped shared-prefix operator, and
+  ``VLLM_L20_SHARED_PREFIX_DECODE_TRACE`` gets the candidate and run records;
+* it copies the operator's modules and two shared libraries next to each other into
   ``vllm/v1/attention/ops/`` (the reference copies one Triton module).
 """
 
@@ -51,6 +58,8 @@ BACKUP_SUFFIX = ".py.l20-fp8-paged-backup"
 COPIED = (
     "l20_paged_split_kv.py",
     "l20_paged_decode.py",
+    "l20_decode_step.py",
+    "l20_shared_prefix_decode_dispatch.py",
     "l20_paged_decode_ops.so",
     "libpaged_fp8_decode.so",
 )
@@ -93,6 +102,7 @@ FIDECODE_NEW = '''class FIDecode:
     block_tables: torch.Tensor | None = None
     seq_lens: torch.Tensor | None = None
     max_seq_len: int = 0
+    l20_step: object | None = None  # what the first layer of a step computes for all of them
 '''
 
 CONSTRUCT_OLD = "attn_metadata.decode = FIDecode(wrapper=decode_wrapper)"
@@ -195,8 +205,11 @@ CALL_NEW = """                else:
                             int(l20_fp8_max_seq),
                         )
                     if l20_fp8_enabled or l20_kv16_enabled:
+                        from vllm.v1.attention.ops.l20_decode_step import (
+                            l20_decode_step,
+                            l20_grouped_decode,
+                        )
                         from vllm.v1.attention.ops.l20_paged_split_kv import (
-                            allocate_l20_paged_split_kv_workspace,
                             l20_paged_split_kv_attention,
                             l20_paged_split_kv_attention_fp8,
                         )
@@ -218,22 +231,35 @@ CALL_NEW = """                else:
                                 value_cache,
                             )
                         key_cache, value_cache = l20_views[1], l20_views[2]
-                        l20_fp8_shape = (
-                            l20_fp8_batch,
-                            decode_query.shape[1],
-                            (l20_fp8_max_seq + 511) // 512,
-                            decode_query.dtype,
+                        # once per model step, by its first layer: the work split (plan), the
+                        # shared-prefix groups, and one workspace for all layers
+                        l20_step = l20_decode_step(
+                            attn_metadata.decode,
+                            decode_query,
+                            key_cache,
+                            value_cache,
+                            attn_metadata.decode.block_tables,
+                            attn_metadata.decode.seq_lens,
+                            l20_fp8_max_seq,
+                            split_size=512,
+                            fp8=bool(l20_fp8_enabled),
                         )
-                        if getattr(self, "_l20_fp8_workspace_shape", None) != l20_fp8_shape:
-                            self._l20_fp8_workspace = (
-                                allocate_l20_paged_split_kv_workspace(
-                                    decode_query,
-                                    l20_fp8_max_seq,
-                                    split_size=512,
-                                )
-                            )
-                            self._l20_fp8_workspace_shape = l20_fp8_shape
-                    if l20_fp8_enabled:
+                    if l20_fp8_enabled and l20_step.groups is not None:
+                        # VLLM_ENABLE_L20_SHARED_PREFIX_DECODE=1 and this step has shared-prefix groups
+                        l20_grouped_decode(
+                            l20_step,
+                            decode_query,
+                            key_cache,
+                            value_cache,
+                            attn_metadata.decode.block_tables,
+                            attn_metadata.decode.seq_lens,
+                            layer._k_scale_float,
+                            layer._v_scale_float,
+                            l20_fp8_max_seq,
+                            out_decode.view_as(decode_query),
+                            split_size=512,
+                        )
+                    elif l20_fp8_enabled:
                         l20_paged_split_kv_attention_fp8(
                             decode_query,
                             key_cache,
@@ -245,8 +271,9 @@ CALL_NEW = """                else:
                             max_seq_len=l20_fp8_max_seq,
                             split_size=512,
                             output=out_decode.view_as(decode_query),
-                            workspace=self._l20_fp8_workspace,
+                            workspace=l20_step.workspace,
                             metadata_stable=True,  # built once per model step
+                            plan=l20_step.plan,
                         )
                         trace_path = l20_static["fp8_trace"]
                         if trace_path:
@@ -272,9 +299,11 @@ CALL_NEW = """                else:
                             attn_metadata.decode.block_tables,
                             attn_metadata.decode.seq_lens,
                             split_size=512,
-                            workspace=self._l20_fp8_workspace,
+                            workspace=l20_step.workspace,
                             max_seq_len=l20_fp8_max_seq,
                             output=out_decode.view_as(decode_query),
+                            metadata_stable=True,
+                            plan=l20_step.plan,
                         )
                         trace_path = l20_static["kv16_trace"]
                         if trace_path:

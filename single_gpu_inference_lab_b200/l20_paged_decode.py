@@ -323,7 +323,9 @@ def group_shared_prefixes(
     and filters as the reference's ``find_l20_shared_prefix_groups``
     (integrations/vllm/l20_shared_prefix_decode_dispatch.py:41-76), any number of groups.  The
     prefix length of a request comes from ``prefix_lengths`` (int32, device), else from
-    ``uniform_prefix_len``, else from ``seq_lens`` as ``floor(min / 16) * 16``."""
+    ``uniform_prefix_len``; with neither the prefixes are discovered from the table and
+    ``seq_lens``: requests that agree on their first ``min_prefix_len`` tokens' pages form a group
+    whose prefix is as long as all of them agree, in whole filled pages."""
     batch = block_table.shape[0]
     if max_groups is None:
         max_groups = max(1, batch // max(1, min_batch))

@@ -180,16 +180,31 @@ def test_device_grouping_equals_the_oracle_on_random_tables(built_libs, seed):
         assert all(row_group[r] == -1 and row_prefix[r] == 0 for r in range(batch) if r not in in_groups)
 
 
-def test_device_grouping_derives_the_candidate_prefix_and_caps_the_groups(built_libs):
+def test_device_grouping_discovers_the_prefixes_and_caps_the_groups(built_libs):
     from single_gpu_inference_lab_b200 import l20_paged_decode as ops
     from single_gpu_inference_lab_b200 import l20_shared_prefix_decode_dispatch as d
 
-    w = make_inputs("shared-prefix-b64", seed=4, batch=24, shrink=0.25)  # prefix 1024, private suffixes
+    w = make_inputs("shared-prefix-b64", seed=4, batch=24, shrink=0.25)  # prefix 1024, private suffixes of 0..8 pages
     g = w.to(DEV)
-    cand = (int(w.seq_lens.min()) // 16) * 16
-    want = oracle.find_shared_prefix_groups(w.block_table, [cand] * 24, min_batch=8, min_prefix_length=512)
+    # discovery: keyed on the first 512 tokens' pages, extended as far as every member agrees
     found = ops.group_shared_prefixes(g.block_table, seq_lens=g.seq_lens, min_batch=8, min_prefix_len=512)
-    assert found.to_lists() == want
+    assert found.to_lists() == [list(range(24))]
+    assert found.group_prefix_len.cpu().tolist()[0] == 1024
+    assert found.row_prefix_len.cpu().tolist() == [1024] * 24
+    # a member that leaves the common chain early shortens the group's prefix to where it leaves
+    table = w.block_table.clone()
+    table[5, 40] += 3  # page 40 = tokens 640..655
+    found = ops.group_shared_prefixes(table.to(DEV), seq_lens=g.seq_lens, min_batch=8, min_prefix_len=512)
+    assert found.to_lists() == [list(range(24))] and found.group_prefix_len.cpu().tolist()[0] == 640
+    # ... and one that differs inside the key pages is no member
+    table[7, 3] += 1
+    found = ops.group_shared_prefixes(table.to(DEV), seq_lens=g.seq_lens, min_batch=8, min_prefix_len=512)
+    assert found.to_lists() == [[r for r in range(24) if r != 7]] and found.row_group.cpu().tolist()[7] == -1
+    # a short member bounds the prefix by the whole pages it has filled
+    lens = g.seq_lens.clone()
+    lens[2] = 700
+    found = ops.group_shared_prefixes(g.block_table, seq_lens=lens, min_batch=8, min_prefix_len=512)
+    assert found.group_prefix_len.cpu().tolist()[0] == 688
     uniform = ops.group_shared_prefixes(g.block_table, uniform_prefix_len=w.prefix_len, min_batch=8, min_prefix_len=512)
     assert uniform.to_lists() == [list(range(24))]
     # the list-returning mirror of the reference function runs the same kernels for a CUDA table

@@ -40,7 +40,11 @@ def test_install_is_idempotent_compiles_and_uninstalls(tmp_path, built_libs, cap
         "VLLM_L20_FP8_PAGED_FORCE",
         "VLLM_L20_FP8_PAGED_TRACE",
         "should_use_l20_paged_fp8_split_kv",
-        "allocate_l20_paged_split_kv_workspace",
+        "l20_decode_step(",
+        "l20_grouped_decode(",
+        "plan=l20_step.plan",
+        "workspace=l20_step.workspace",
+        "l20_step: object | None = None",
         "l20_paged_split_kv_attention_fp8",
         "is_quantized_kv_cache(self.kv_cache_dtype)",
         "DeviceCapability(10, 0)",
