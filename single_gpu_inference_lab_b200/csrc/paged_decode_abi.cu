@@ -946,6 +946,22 @@ int pfd_rope_quant_append(const pfd_rope_args* args) {
   p.cos_sin_f32 = a.cos_sin_dtype == PFD_DTYPE_F32 ? 1 : 0;
   p.cache_fp8 = a.cache_dtype == PFD_DTYPE_E4M3 ? 1 : 0;
   cudaStream_t stream = static_cast<cudaStream_t>(a.stream);
+  // The vectorised kernel: NeoX pairs over the whole head, rows and caches 16-byte aligned.
+  const auto al = [](const void* ptr, int64_t bytes) { return (reinterpret_cast<uintptr_t>(ptr) & (uintptr_t)(bytes - 1)) == 0; };
+  const auto m8 = [](int64_t x) { return x % 8 == 0; };
+  const int cache_elem = p.cache_fp8 ? 1 : 2;
+  const bool vec = p.is_neox && a.rotary_dim == a.head_dim && a.head_dim % 16 == 0 &&
+                   al(a.query, 16) && al(a.key, 16) && al(a.value, 16) && al(a.cos_sin_cache, 16) &&
+                   m8(a.q_stride_t) && m8(a.q_stride_h) && m8(a.k_stride_t) && m8(a.k_stride_h) && m8(a.v_stride_t) &&
+                   m8(a.v_stride_h) && (p.cos_sin_f32 ? a.cos_sin_stride % 4 == 0 : m8(a.cos_sin_stride)) &&
+                   al(a.key_cache, 8 * cache_elem) && al(a.value_cache, 8 * cache_elem) && m8(a.kc_stride_block) &&
+                   m8(a.kc_stride_token) && m8(a.kc_stride_head) && m8(a.vc_stride_block) && m8(a.vc_stride_token) &&
+                   m8(a.vc_stride_head);
+  if (vec) {
+    if (a.query_dtype == PFD_DTYPE_BF16) pfd::rope_quant_append_vec_kernel<true><<<a.num_tokens, 256, 0, stream>>>(p);
+    else pfd::rope_quant_append_vec_kernel<false><<<a.num_tokens, 256, 0, stream>>>(p);
+    return check_launch("rope + append kernel (vectorised)");
+  }
   if (a.query_dtype == PFD_DTYPE_BF16) pfd::rope_quant_append_kernel<true><<<a.num_tokens, 256, 0, stream>>>(p);
   else pfd::rope_quant_append_kernel<false><<<a.num_tokens, 256, 0, stream>>>(p);
   return check_launch("rope + append kernel");

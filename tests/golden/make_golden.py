@@ -106,7 +106,11 @@ def smoke_recipe(ref, batch: int, context: int, q_heads: int, kv_heads: int):
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--reference-root", default=os.environ.get("REFERENCE_ROOT"), required="REFERENCE_ROOT" not in os.environ)
+    parser.add_argument("--only-paged-rope", action="store_true",
+                        help="add the paged producer cases to the existing file, leave the rest as it is")
     args = parser.parse_args()
+    if args.only_paged_rope:
+        return update_paged_rope_only(args.reference_root)
     ref = load_reference(Path(args.reference_root))
     golden: dict = {"torch": torch.__version__, "cases": {}, "smoke": {}}
 
@@ -168,8 +172,59 @@ def main() -> int:
                                     dtype=str(dtype).replace("torch.", ""), key_cache=kc.clone(), value_cache=vc.clone())
         print("rope", name)
 
+    add_paged_rope_cases(golden, rope)
     torch.save(golden, HERE / "paged_decode_golden.pt")
     print("wrote", HERE / "paged_decode_golden.pt")
+    return 0
+
+
+PAGED_ROPE_CASES = [("s5-t23-h2-d128-r128-bf16", 5, 23, 2, 128, 128, torch.bfloat16),
+                    ("s3-t40-h4-d128-r64-fp16", 3, 40, 4, 128, 64, torch.float16),
+                    ("s8-t8-h8-d64-r64-bf16", 8, 8, 8, 64, 64, torch.bfloat16)]
+
+
+def paged_rope_inputs(name, seqs, tokens, hkv, d, rot, dtype):
+    """Seeded inputs of one paged case (the test regenerates them from the same recipe): new
+    tokens of `seqs` sequences at arbitrary positions, written through a block table into a
+    [blocks, 16, Hkv, D] cache."""
+    gen = torch.Generator().manual_seed(43)
+    k = torch.randn(tokens, hkv, d, generator=gen).to(dtype)
+    v = torch.randn(tokens, hkv, d, generator=gen).to(dtype)
+    angle = torch.rand(tokens, rot // 2, generator=gen) * 6.2831853
+    max_blocks = 6
+    table = torch.randperm(seqs * max_blocks, generator=gen).reshape(seqs, max_blocks)
+    # distinct (sequence, position) pairs, so that no two tokens write the same slot
+    flat = torch.randperm(seqs * max_blocks * 16, generator=gen)[:tokens]
+    sequence_ids, positions = flat // (max_blocks * 16), flat % (max_blocks * 16)
+    return k, v, torch.cos(angle), torch.sin(angle), sequence_ids, positions, table
+
+
+def add_paged_rope_cases(golden, rope):
+    """paged_rope_kv_reference of src/l20_stack/ops/triton_rope_kv.py:176-205."""
+    golden["rope_paged"] = {}
+    for case in PAGED_ROPE_CASES:
+        name, seqs, tokens, hkv, d, rot, dtype = case
+        k, v, cos, sin, sequence_ids, positions, table = paged_rope_inputs(*case)
+        kc = torch.zeros(table.numel(), 16, hkv, d, dtype=dtype)
+        vc = torch.zeros_like(kc)
+        kc, vc = rope.paged_rope_kv_reference(k, v, cos, sin, sequence_ids, positions, table, kc, vc)
+        # the rows the reference wrote, plus digests of the whole caches (everything else stays zero)
+        blocks, offsets = table[sequence_ids, positions // 16], positions % 16
+        golden["rope_paged"][name] = dict(seqs=seqs, tokens=tokens, kv_heads=hkv, head_dim=d, rotary_dim=rot,
+                                          dtype=str(dtype).replace("torch.", ""),
+                                          key_rows=kc[blocks, offsets].clone(), value_rows=vc[blocks, offsets].clone(),
+                                          key_cache_sha256=digest(kc), value_cache_sha256=digest(vc))
+        print("rope paged", name)
+
+
+def update_paged_rope_only(reference_root: str) -> int:
+    """Add the paged producer cases to the committed file without regenerating the rest."""
+    sys.path.insert(0, str(Path(reference_root) / "src"))
+    rope = importlib.import_module("l20_stack.ops.triton_rope_kv")
+    golden = torch.load(HERE / "paged_decode_golden.pt", weights_only=False)
+    add_paged_rope_cases(golden, rope)
+    torch.save(golden, HERE / "paged_decode_golden.pt")
+    print("updated", HERE / "paged_decode_golden.pt")
     return 0
 
 

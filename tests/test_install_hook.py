@@ -123,3 +123,44 @@ def test_live_check_overlay_leaves_the_installed_package_alone(tmp_path):
     (dst / "v1/attention/ops/new.py").write_text("new\n")
     assert (real / "v1/attention/backends/flashinfer.py").read_text() == "stock\n"
     assert not (real / "v1/attention/ops/new.py").exists()
+
+
+def test_rope_hook_installs_compiles_and_uninstalls(tmp_path, built_libs, capsys):
+    """The producer hook at the reference's call site (integrations/vllm/install_l20_rope_kv.py):
+    config guard relaxed for CUDA, the two backend methods added with the sm_100 / FP8 gate."""
+    from single_gpu_inference_lab_b200 import install_l20_rope_kv as rope_installer
+
+    root = _fake_tree(tmp_path)
+    spec = importlib.util.find_spec("vllm")
+    real_config = Path(list(spec.submodule_search_locations)[0]) / "config/compilation.py"
+    if not real_config.exists():
+        pytest.skip("this vLLM has no config/compilation.py")
+    (root / "vllm/config").mkdir(parents=True)
+    shutil.copy2(real_config, root / "vllm/config/compilation.py")
+    backend = root / "vllm/v1/attention/backends/flashinfer.py"
+    config = root / "vllm/config/compilation.py"
+    originals = backend.read_text(), config.read_text()
+    assert rope_installer.main(["--vllm-source-dir", str(root)]) == 0
+    capsys.readouterr()
+    patched_backend, patched_config = backend.read_text(), config.read_text()
+    ast.parse(patched_backend)
+    ast.parse(patched_config)
+    for needle in (
+        "from vllm.v1.attention.ops.l20_rope_kv import l20_rope_and_cache",
+        "def fused_rope_kvcache_supported(self):",
+        "capability.to_int() == 100",
+        "is_quantized_kv_cache(self.kv_cache_dtype)",
+        "def do_rope_and_kv_cache_update(",
+        "k_scale=layer._k_scale if l20_fp8 else None",
+    ):
+        assert needle in patched_backend, needle
+    assert "and not current_platform.is_cuda()" in patched_config
+    for name in rope_installer.COPIED:
+        assert (root / "vllm/v1/attention/ops" / name).exists(), name
+    assert rope_installer.main(["--vllm-source-dir", str(root)]) == 0  # idempotent
+    assert backend.read_text() == patched_backend and config.read_text() == patched_config
+    # both hooks together: the decode hook patches the same backend file
+    assert installer.main(["--vllm-source-dir", str(root)]) == 0
+    ast.parse(backend.read_text())
+    assert rope_installer.main(["--vllm-source-dir", str(root), "--uninstall"]) == 0
+    assert (backend.read_text(), config.read_text()) == originals

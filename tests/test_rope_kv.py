@@ -40,6 +40,59 @@ def test_oracle_reproduces_reference_rope_kv_outputs_bit_for_bit(golden):
         assert torch.equal(vc2[:, 0].view(torch.int16), case["value_cache"].view(torch.int16)), name
 
 
+def paged_golden_inputs(case):
+    """The seeded inputs tests/golden/make_golden.py fed to the reference's paged_rope_kv_reference
+    (src/l20_stack/ops/triton_rope_kv.py:176-205): same recipe as paged_rope_inputs there."""
+    seqs, tokens, hkv, d, rot = case["seqs"], case["tokens"], case["kv_heads"], case["head_dim"], case["rotary_dim"]
+    dtype = getattr(torch, case["dtype"])
+    gen = torch.Generator().manual_seed(43)
+    k = torch.randn(tokens, hkv, d, generator=gen).to(dtype)
+    v = torch.randn(tokens, hkv, d, generator=gen).to(dtype)
+    angle = torch.rand(tokens, rot // 2, generator=gen) * 6.2831853
+    max_blocks = 6
+    table = torch.randperm(seqs * max_blocks, generator=gen).reshape(seqs, max_blocks)
+    flat = torch.randperm(seqs * max_blocks * 16, generator=gen)[:tokens]
+    sequence_ids, positions = flat // (max_blocks * 16), flat % (max_blocks * 16)
+    # what an engine hands the operator: the slot of every token, resolved through the block table
+    slots = table[sequence_ids, positions // 16] * 16 + positions % 16
+    cos_sin = torch.cat([torch.cos(angle), torch.sin(angle)], dim=1)  # one row per token, indexed by token number
+    return k, v, cos_sin, slots, table.numel(), dtype
+
+
+def check_against_paged_golden(case, kc, vc, slots, name):
+    from helpers import digest
+
+    assert torch.equal(kc[slots // 16, slots % 16].view(torch.int16), case["key_rows"].view(torch.int16)), name
+    assert torch.equal(vc[slots // 16, slots % 16].view(torch.int16), case["value_rows"].view(torch.int16)), name
+    assert digest(kc) == case["key_cache_sha256"] and digest(vc) == case["value_cache_sha256"], name
+
+
+def test_oracle_reproduces_reference_paged_rope_kv_outputs_bit_for_bit(golden):
+    for name, case in golden["rope_paged"].items():
+        k, v, cos_sin, slots, blocks, dtype = paged_golden_inputs(case)
+        tokens, hkv, d = k.shape
+        kc = torch.zeros(blocks, 16, hkv, d, dtype=dtype)
+        _, _, kc2, vc2 = oracle.rope_and_cache(torch.zeros(tokens, hkv, d, dtype=dtype), k, v, torch.arange(tokens), cos_sin,
+                                               True, kc, torch.zeros_like(kc), slots)
+        check_against_paged_golden(case, kc2, vc2, slots, name)
+
+
+@pytest.mark.gpu
+def test_kernel_reproduces_reference_paged_rope_kv_outputs_bit_for_bit(built_libs, golden):
+    from single_gpu_inference_lab_b200 import l20_rope_kv
+
+    for name, case in golden["rope_paged"].items():
+        k, v, cos_sin, slots, blocks, dtype = paged_golden_inputs(case)
+        tokens, hkv, d = k.shape
+        kc = torch.zeros(blocks, 16, hkv, d, dtype=dtype, device=DEV)
+        vc = torch.zeros_like(kc)
+        q = torch.zeros(tokens, hkv, d, dtype=dtype, device=DEV)
+        l20_rope_kv.l20_rope_and_cache(q, k.to(DEV), v.to(DEV), torch.arange(tokens, device=DEV), cos_sin.to(DEV), True,
+                                       kc, vc, slots.to(DEV))
+        torch.cuda.synchronize()
+        check_against_paged_golden(case, kc.cpu(), vc.cpu(), slots, name)
+
+
 def make_step(seed, tokens, hq, hkv, d, rot, dtype, cache_dtype, table_dtype, block_size=16):
     gen = torch.Generator().manual_seed(seed)
     q = torch.randn(tokens, hq, d, generator=gen).to(dtype)
@@ -75,6 +128,8 @@ def test_kernel_matches_oracle_bit_for_bit(built_libs, is_neox, cache):
         (5, 28, 4, 128, 64, torch.float16, torch.float16),
         (256, 14, 2, 64, 64, torch.bfloat16, torch.bfloat16),
         (1, 32, 8, 128, 32, torch.float16, torch.float32),
+        (33, 8, 8, 128, 128, torch.float16, torch.float16),  # the vectorised kernel in fp16 with an fp16 table
+        (700, 16, 2, 128, 128, torch.bfloat16, torch.float32),
     ]):
         cache_dtype = torch.float8_e4m3fn if cache == "fp8" else dtype
         q, k, v, pos, cs, kc, vc, slots, ks, vs = make_step(seed, tokens, hq, hkv, d, rot, dtype, cache_dtype, table_dtype)
