@@ -93,6 +93,12 @@ def parse_args():
                    help="with the plan: combine the pieces of cut sequences inside the balanced kernel (PFD_FLAG_SINGLE_LAUNCH)")
     p.add_argument("--no-plan", action="store_true",
                    help="do not plan the step: every call derives its work split itself")
+    p.add_argument("--producer-step", action="store_true",
+                   help="time the step in front of decode attention instead (rotary embedding + FP8 quantise + paged "
+                        "KV append, l20_rope_and_cache) and print its own JSON line")
+    p.add_argument("--grouped-prefix", action="store_true",
+                   help="shared-prefix-b64 only: find the groups on the device (once, as per model step) and run the "
+                        "grouped shared-prefix entry instead of the single-group one")
     p.add_argument("--strong", action="store_true",
                    help="N > 1: shard ONE batch by sequence over the ranks (token-balanced) instead of one batch per rank")
     return p.parse_args()
@@ -341,6 +347,17 @@ class Case:
 
             self.spd = spd
             self.ws = spd.allocate_shared_prefix_workspace(q, w.max_seq_len, w.prefix_len, suffix_split_size=self.split)
+        # --grouped-prefix: the groups are discovered on the device from the block table and the
+        # lengths (once, as an engine does per model step); every timed layer-step reads them
+        self.groups = None
+        if self.shared_prefix and args.grouped_prefix:
+            self.groups, self.max_groups = cabi.group_shared_prefixes(w.block_table, seq_lens=w.seq_lens, min_batch=8,
+                                                                      min_prefix_len=1024, max_groups=4)
+            self.prefix_bound = (w.prefix_len + 255) // 256 * 256  # an engine knows how long its cached prefixes can be
+            slots = self.prefix_bound // 256 + -(-w.max_seq_len // self.split)
+            self.ws = (torch.empty(self.batch, self.hq, slots, self.d, device=dev), torch.empty(self.batch, self.hq, slots, device=dev),
+                       torch.empty(self.batch, self.hq, slots, device=dev), torch.empty_like(q))
+            torch.cuda.synchronize()
         self.out = self.ws[3]
         self.flags = args.flags
         # The plan of the model step: block table and lengths are the same for every layer, so the
@@ -373,6 +390,12 @@ class Case:
             cabi.paged_decode_kv16_split_out(
                 w.query, kc, vc, w.block_table, w.seq_lens, max_seq_len=w.max_seq_len,
                 split_size=self.split, output=self.out, workspace=self.ws, flags=flags, plan=self.plan)
+            return
+        if self.groups is not None:
+            cabi.shared_prefix_decode_grouped_fp8_e4m3(
+                w.query, kc, vc, w.block_table, w.seq_lens, groups=self.groups, max_groups=self.max_groups,
+                max_prefix_len=self.prefix_bound, k_scale=w.k_scale, v_scale=w.v_scale, max_seq_len=w.max_seq_len,
+                split_size=self.split, output=self.out, workspace=self.ws)
             return
         if self.shared_prefix:
             cabi.shared_prefix_decode_fp8_e4m3(
@@ -570,8 +593,69 @@ def short_report(case: Case, res: dict, peak: float, world_bytes: float, world: 
     return out
 
 
+def run_producer_step(args) -> int:
+    """The producer step alone: T new tokens (one per request of a decode step, or a prefill
+    chunk), qwen2.5-coder-3b geometry, FP8 caches with per-head scales.  Bytes moved per token:
+    q, k read and written back, v read, cos / sin rows read, k and v written as e4m3."""
+    from single_gpu_inference_lab_b200 import l20_rope_kv
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hq, hkv, d = 16, 2, 128
+    gen = torch.Generator(device="cpu").manual_seed(0)
+    rows = []
+    for tokens in (64, 256, 1024, 4096, 16384):
+        q = torch.randn(tokens, hq, d, generator=gen).to(torch.bfloat16).to(dev)
+        k = torch.randn(tokens, hkv, d, generator=gen).to(torch.bfloat16).to(dev)
+        v = torch.randn(tokens, hkv, d, generator=gen).to(torch.bfloat16).to(dev)
+        angle = torch.rand(8192, d // 2, generator=gen) * 6.2831853
+        cos_sin = torch.cat([torch.cos(angle), torch.sin(angle)], dim=1).to(dev)
+        pos = torch.randint(0, 8192, (tokens,), generator=gen).to(dev)
+        blocks = tokens // 16 + 64
+        slots = torch.randperm(blocks * 16, generator=gen)[:tokens].to(dev)
+        kc = torch.zeros(blocks, 16, hkv, d, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+        vc = torch.zeros_like(kc)
+        ks = torch.full((hkv,), 0.01, device=dev)
+        vs = torch.full((hkv,), 0.01, device=dev)
+
+        def call():
+            l20_rope_kv.l20_rope_and_cache(q, k, v, pos, cos_sin, True, kc, vc, slots, k_scale=ks, v_scale=vs)
+
+        for _ in range(5):
+            call()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side), torch.cuda.graph(g, stream=side):
+            for _ in range(20):
+                call()
+        torch.cuda.synchronize()
+        g.replay()
+        runs = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            runs.append(e0.elapsed_time(e1) / 20 * 1e3)
+        us = statistics.median(runs)
+        nbytes = tokens * ((hq + hkv) * d * 2 * 2 + hkv * d * 2 + d * 4 + 2 * hkv * d)
+        rows.append({"tokens": tokens, "us_per_call": round(us, 3), "bytes_per_call": nbytes,
+                     "gbs": round(nbytes / (us * 1e-6) / 1e9, 1)})
+    peak, peak_kind = measured_peak()
+    print(json.dumps({"metric": "rope_quant_append_us", "unit": "us", "geometry": {"q_heads": hq, "kv_heads": hkv, "head_dim": d},
+                      "dtype": "bf16 q/k/v, fp32 cos/sin table, e4m3 caches, per-head scales", "kernel": "rope_quant_append_vec_kernel",
+                      "timing": "20 calls per CUDA graph replay, CUDA events, median of 5; operands of the larger sizes exceed L2",
+                      "hbm_peak_gbs": peak, "peak_source": peak_kind, "rows": rows}))
+    return 0
+
+
 def main() -> int:
     args = parse_args()
+    if args.producer_step:
+        return run_producer_step(args)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -650,6 +734,15 @@ def main() -> int:
         elif case.kv16 is not None:
             res = l20_paged_split_kv.l20_paged_split_kv_attention(
                 dq, kc, vc, dtable, dlens, split_size=split, workspace=ws, max_seq_len=w.max_seq_len)
+        elif case.groups is not None:
+            # the step's own block table and lengths arrive with the step: group them, then decode
+            from single_gpu_inference_lab_b200 import l20_paged_decode as ops
+
+            found = ops.group_shared_prefixes(dtable, seq_lens=dlens, min_batch=8, min_prefix_len=1024,
+                                              max_groups=case.max_groups, buffer=case.groups)
+            res = ops.shared_prefix_decode_grouped_fp8_e4m3(
+                dq, kc, vc, dtable, dlens, ws[0], ws[1], ws[2], ws[3], w.k_scale, w.v_scale, w.max_seq_len, split, found,
+                max_prefix_len=case.prefix_bound)
         elif case.shared_prefix:
             res = case.spd.shared_paged_prefix_paged_suffix_gqa_decode_attention_fp8(
                 dq, kc, vc, dtable, dlens, w.prefix_len, k_scale=w.k_scale, v_scale=w.v_scale,
@@ -754,7 +847,10 @@ def main() -> int:
                 "kv_bytes_per_step_per_gpu": case.kv_bytes,
                 **({"shared_prefix_tokens": w.prefix_len,
                     "unique_kv_bytes_per_step": int(w.prefix_len + (w.seq_lens - w.prefix_len).sum().item()) * case.hkv * case.d * 2,
-                    "prefix_pass": "dense tcgen05 (TMEM accumulators), 128 rows x 256 tokens per CTA"} if case.shared_prefix else {}),
+                    "prefix_pass": "dense tcgen05 (TMEM accumulators), 128 rows x 256 tokens per CTA",
+                    "groups": ("found on the device from the block table and the lengths (prefix lengths discovered), "
+                               "grouped entry point") if case.groups is not None else "one group given by the caller"}
+                   if case.shared_prefix else {}),
                 "parallelism": (("kv-range split; packed partials stored to every rank by the decode kernels (peer stores + flags), merged on every rank"
                                  if args.exchange == "peer" else
                                  "kv-range split, packed partials exchanged (all-gather), merged on every rank") if mode == "kv-range" else

@@ -589,7 +589,7 @@ int launch_prefix(const pfd_decode_args& a, int prefix_len, int chunks, const in
   const int rows = a.batch * kp.group;
   // grouped: every group's last 128-row tile may be ragged, hence one more tile slot per group
   const dim3 grid = groups == nullptr ? dim3(chunks, (rows + pfd::kPrefixRows - 1) / pfd::kPrefixRows, a.num_kv_heads)
-                                      : dim3(rows / pfd::kPrefixRows + max_groups, chunks, a.num_kv_heads);
+                                      : dim3(chunks * a.num_kv_heads, rows / pfd::kPrefixRows + max_groups, 1);
   kernel<<<grid, 512, smem, static_cast<cudaStream_t>(a.stream)>>>(kp, pp);
   return check_launch("shared-prefix dense kernel");
 }

@@ -149,8 +149,9 @@ struct PrefixParams {
   int32_t prefix_len;   // tokens shared by every request (multiple of 16)
   int32_t batch;
   // Grouped form: the groups buffer of the grouping kernels (shared_prefix_groups.cuh) and its
-  // geometry.  grid = (slots for (group, 128-row tile) pairs, prefix chunks, kv heads); a CTA
-  // whose slot or chunk lies beyond what the device-side table holds leaves at once.
+  // geometry.  grid = (prefix chunks x kv heads, slots for (group, 128-row tile) pairs): the
+  // slots that exist come first in launch order, so CTAs whose slot or chunk lies beyond what the
+  // device-side table holds (they leave at once) queue behind the working ones, not among them.
   const int32_t* groups;
   int32_t groups_batch, max_groups;
   int32_t* status;
@@ -185,7 +186,7 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   constexpr uint32_t kKBytes = kPrefixChunk * D * 2;        // 64 KiB: 2 k-blocks of [256][64]; later P: 4 x [128][64]; later O rows
   constexpr uint32_t kVBytes = D * kPrefixChunk * 2;        // 64 KiB: 2 d-blocks of [256 tokens][64]
   int chunk = blockIdx.x, mtile = blockIdx.y;
-  const int kvh = blockIdx.z;
+  int kvh = blockIdx.z;
   const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
   const int qd = warp & 3, cg = warp >> 2;  // TMEM lane quarter, column group
   const int row = 32 * qd + lane;           // this thread's (request, head) row of the tile
@@ -198,7 +199,7 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
     const int B = pp.groups_batch, G = pp.max_groups;
     const int32_t* offs = pp.groups + groups_offsets_off(B);
     const int n_groups = min(__ldg(pp.groups + 3), G);
-    int slot = blockIdx.x, g = 0;
+    int slot = blockIdx.y, g = 0;
     for (; g < n_groups; ++g) {
       const int tiles = ((__ldg(offs + g + 1) - __ldg(offs + g)) * p.group + kPrefixRows - 1) / kPrefixRows;
       if (slot < tiles) break;
@@ -206,7 +207,8 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
     }
     if (g >= n_groups) return;
     mtile = slot;
-    chunk = blockIdx.y;
+    chunk = blockIdx.x / p.num_kv_heads;
+    kvh = blockIdx.x % p.num_kv_heads;
     prefix_len = min(__ldg(pp.groups + groups_prefix_off(B, G) + g) & ~15, pp.prefix_len);  // (pp.prefix_len: the cap)
     if (chunk * kPrefixChunk >= prefix_len) return;
     req_list = pp.groups + groups_rows_off(B, G) + __ldg(offs + g);

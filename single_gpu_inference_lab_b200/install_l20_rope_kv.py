@@ -21,6 +21,7 @@ What differs from the reference:
 * the Triton attention backend is left alone (the reference patches it too, :123-229): on sm_100
   an FP8 cache runs on the FlashInfer backend.
 
+``VLLM_L20_ROPE_KV_TRACE=<path>`` appends one JSON line per call of the operator.
 ``--uninstall`` restores the backups (``*.l20-rope-backup``).  ``--vllm-source-dir`` points at a
 vLLM checkout instead of the installed package.
 """
@@ -97,6 +98,13 @@ METHODS = '''
             k_scale=layer._k_scale if l20_fp8 else None,
             v_scale=layer._v_scale if l20_fp8 else None,
         )
+        l20_trace = __import__("os").environ.get("VLLM_L20_ROPE_KV_TRACE")
+        if l20_trace:
+            with open(l20_trace, "a", encoding="utf-8") as l20_sink:
+                l20_sink.write(
+                    '{"event": "l20_rope_kv_run", "tokens": %d, "fp8_cache": %s}\\n'
+                    % (int(query.shape[0]), "true" if l20_fp8 else "false")
+                )
 '''
 
 

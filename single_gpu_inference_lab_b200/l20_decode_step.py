@@ -31,6 +31,7 @@ import torch
 
 MIN_GROUP_BATCH = 8
 MIN_PREFIX_TOKENS = 4096
+MAX_GROUPS = 4
 PREFIX_CHUNK = 256
 
 
@@ -95,7 +96,8 @@ def l20_decode_step(meta, query, key_cache, value_cache, block_tables, seq_lens,
     capturing = torch.cuda.is_current_stream_capturing()
     if fp8 and sw["shared_prefix"] and head_dim == 128 and MIN_GROUP_BATCH <= batch <= 2048 and max_seq_len >= MIN_PREFIX_TOKENS \
             and (not capturing or sw["shared_prefix_force"]):
-        max_groups = max(1, batch // MIN_GROUP_BATCH)
+        # every group the buffer has room for costs idle CTAs in each layer's dense pass: room for a few
+        max_groups = max(1, min(batch // MIN_GROUP_BATCH, MAX_GROUPS))
         groups_buffer = _persistent(("groups", query.device, batch, max_groups), lambda: torch.empty(
             torch.ops.l20_stack.prefix_groups_bytes(batch, max_groups) // 4, dtype=torch.int32, device=query.device))
         groups = ops.group_shared_prefixes(block_tables, seq_lens=seq_lens, min_batch=MIN_GROUP_BATCH,

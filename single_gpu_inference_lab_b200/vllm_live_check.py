@@ -49,6 +49,8 @@ llm = LLM(model=os.environ["LIVE_MODEL"], load_format="dummy", skip_tokenizer_in
           kv_cache_dtype=os.environ["LIVE_KV"], block_size=16, dtype="bfloat16",
           max_model_len=int(os.environ.get("LIVE_MAX_LEN", "4096")), max_num_seqs=int(os.environ.get("LIVE_BATCH", "64")),
           gpu_memory_utilization=float(os.environ.get("LIVE_MEM", "0.3")), seed=0, enable_prefix_caching=False,
+          **({"compilation_config": {"pass_config": {"fuse_rope_kvcache": True}}}
+             if os.environ.get("LIVE_ROPE_FUSION", "0") == "1" else {}),
           attention_config={"backend": "FLASHINFER",
                             **({} if os.environ.get("LIVE_TRTLLM_AUTO", "0") == "1" else {"use_trtllm_attention": False})})
 
@@ -170,10 +172,17 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--stock-auto", action="store_true",
                         help="with --ab: a third engine with use_trtllm_attention left to vLLM's own choice")
     parser.add_argument("--log-uniform", action="store_true", help="with --ab: prompt lengths log-uniform in [16, prompt-len]")
+    parser.add_argument("--rope-hook", action="store_true",
+                        help="also install the producer hook (install_l20_rope_kv.py) and switch vLLM's "
+                             "fuse_rope_kvcache pass on in the hooked engine: rotary embedding + KV append then run "
+                             "through l20_rope_and_cache, decode through the decode hook; implies --cuda-graphs "
+                             "(the pass belongs to vLLM's compilation)")
     parser.add_argument("--cuda-graphs", action="store_true",
                         help="let vLLM compile and record CUDA graphs (both engines), and keep the hook on while "
                              "it records (VLLM_L20_PAGED_CUDAGRAPH=1); hook hits are then counted at recording time")
     args = parser.parse_args(argv)
+    if args.rope_hook:
+        args.cuda_graphs = True
 
     spec = importlib.util.find_spec("vllm")  # located, not imported
     if spec is None or not spec.submodule_search_locations:
@@ -182,11 +191,16 @@ def main(argv: list[str] | None = None) -> int:
     work.mkdir(parents=True, exist_ok=True)
     if (work / "vllm_src").exists():
         shutil.rmtree(work / "vllm_src")
-    overlay(Path(list(spec.submodule_search_locations)[0]), work / "vllm_src" / "vllm", COPIED_PATHS)
+    copied = COPIED_PATHS + (("config/compilation.py",) if args.rope_hook else ())
+    overlay(Path(list(spec.submodule_search_locations)[0]), work / "vllm_src" / "vllm", copied)
     sys.path.insert(0, str(PKG.parent))
     from single_gpu_inference_lab_b200 import install_l20_fp8_paged_decode as installer
 
     installer.main(["--vllm-source-dir", str(work / "vllm_src")])
+    if args.rope_hook:
+        from single_gpu_inference_lab_b200 import install_l20_rope_kv as rope_installer
+
+        rope_installer.main(["--vllm-source-dir", str(work / "vllm_src")])
     if args.ab:
         write_model_config(work / "model", args.layers, args.q_heads, args.kv_heads, args.intermediate)
     else:
@@ -228,6 +242,10 @@ def main(argv: list[str] | None = None) -> int:
     )
     if args.cuda_graphs:
         switches["VLLM_L20_PAGED_CUDAGRAPH"] = "1"
+    rope_trace = work / f"rope_trace_{kv}.jsonl"
+    rope_trace.unlink(missing_ok=True)
+    if args.rope_hook:
+        switches.update(LIVE_ROPE_FUSION="1", VLLM_L20_ROPE_KV_TRACE=str(rope_trace))
     hooked = run_engine(work, kv, {**graphs, **switches}, work / f"{kv}_hook.log")
 
     hits = [json.loads(line) for line in trace.read_text().splitlines()] if trace.exists() else []
@@ -245,6 +263,7 @@ def main(argv: list[str] | None = None) -> int:
         "kv_cache_dtype": kv, "mode": "cuda graphs" if args.cuda_graphs else "eager", "hook_hits": len(hits),
         "hook_hits_beyond_warmup": sum(1 for h in hits if h["max_seq_len"] > 64),
         "generated_steps_compared": compared, "same_token": agree, "max_abs_logprob_diff": worst,
+        **({"rope_hook_hits": sum(1 for _ in rope_trace.open()) if rope_trace.exists() else 0} if args.rope_hook else {}),
         "workdir": str(work),
     }))
     return 0 if hits and agree >= compared * 0.8 else 1
