@@ -16,8 +16,8 @@ What differs from the reference:
   ``kv_cache_dtype == "auto"`` (:86, :182) because its operator refuses quantised caches
   (integrations/vllm/l20_rope_kv.py:273-274); this operator quantises with the layer's
   ``_k_scale`` / ``_v_scale``, the scales the decode operator dequantises with;
-* FlashInfer keeps the cache in the HND layout on sm_100: the operator gets logical
-  ``[blocks, 16, Hkv, D]`` views of either layout (it takes strides);
+* FlashInfer keeps the cache in the HND layout on sm_100 and hands the method a logical
+  ``[blocks, 2, 16, Hkv, D]`` tensor whose strides carry that layout: the operator takes strides;
 * the Triton attention backend is left alone (the reference patches it too, :123-229): on sm_100
   an FP8 cache runs on the FlashInfer backend.
 
@@ -76,9 +76,11 @@ METHODS = '''
         kv_cache: torch.Tensor,
         layer_slot_mapping: torch.Tensor,
     ) -> None:
-        # logical [blocks, 16, Hkv, D] views of the layer's cache, whichever layout it is kept in
+        # logical [blocks, 16, Hkv, D] views of the layer's cache: vLLM hands this method the cache
+        # in that shape whatever the physical layout (the strides carry it); a tensor that comes
+        # head-major instead is turned into the same view
         key_cache, value_cache = kv_cache[:, 0], kv_cache[:, 1]
-        if get_kv_cache_layout() == "HND":
+        if key_cache.shape[2] != key.shape[1] and key_cache.shape[1] == key.shape[1]:
             key_cache = key_cache.permute(0, 2, 1, 3)
             value_cache = value_cache.permute(0, 2, 1, 3)
         l20_fp8 = is_quantized_kv_cache(self.kv_cache_dtype)

@@ -49,7 +49,7 @@ llm = LLM(model=os.environ["LIVE_MODEL"], load_format="dummy", skip_tokenizer_in
           kv_cache_dtype=os.environ["LIVE_KV"], block_size=16, dtype="bfloat16",
           max_model_len=int(os.environ.get("LIVE_MAX_LEN", "4096")), max_num_seqs=int(os.environ.get("LIVE_BATCH", "64")),
           gpu_memory_utilization=float(os.environ.get("LIVE_MEM", "0.3")), seed=0, enable_prefix_caching=False,
-          **({"compilation_config": {"pass_config": {"fuse_rope_kvcache": True}}}
+          **({"compilation_config": {"pass_config": {"fuse_rope_kvcache": True}, "splitting_ops": []}}  # (the pass wants an unsplit graph)
              if os.environ.get("LIVE_ROPE_FUSION", "0") == "1" else {}),
           attention_config={"backend": "FLASHINFER",
                             **({} if os.environ.get("LIVE_TRTLLM_AUTO", "0") == "1" else {"use_trtllm_attention": False})})
