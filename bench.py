@@ -77,7 +77,7 @@ def parse_args():
                         "caches and query in that type (single GPU, batch-sharded or weak scaling only)")
     p.add_argument("--exchange", choices=("peer", "nccl"), default="peer",
                    help="KV-range mode on several GPUs: 'peer' = the decode kernels store their packed rows into "
-                        "every rank's receive buffer and the merge kernel waits for flags (the all-gather form is "
+                        "every rank's receive buffer and the merge kernel waits for them (the all-gather form is "
                         "measured beside it); 'nccl' = packed_output + all_gather_into_tensor + merge only")
     p.add_argument("--graph-collective", action="store_true",
                    help="KV-range mode on several GPUs: replay the step, exchange included, from a CUDA graph "
@@ -584,8 +584,8 @@ def short_report(case: Case, res: dict, peak: float, world_bytes: float, world: 
     if "ms_exchange" in res:
         out["exchange_and_merge_us"] = round(res["ms_exchange"] * 1e3, 3)
     if "ms_step_allgather" in res:
-        out["exchange"] = ("inside the kernels: packed rows stored to every rank over NVLink, step-tagged flags, bounded "
-                           "flag wait in the merge kernel; exchange_and_merge_us = step - decode kernels alone")
+        out["exchange"] = ("inside the kernels: rows stored to every rank over NVLink as tagged 8-byte words, bounded "
+                           "wait for them in the merge kernel; exchange_and_merge_us = step - decode kernels alone")
         out["exchange_status"] = res["exchange_status"]
         out["allgather_form"] = {"us_per_layer_step": round(res["ms_step_allgather"] * 1e3, 3),
                                  "exchange_and_merge_us": round(res["ms_exchange_allgather"] * 1e3, 3),
@@ -851,7 +851,7 @@ def main() -> int:
                     "groups": ("found on the device from the block table and the lengths (prefix lengths discovered), "
                                "grouped entry point") if case.groups is not None else "one group given by the caller"}
                    if case.shared_prefix else {}),
-                "parallelism": (("kv-range split; packed partials stored to every rank by the decode kernels (peer stores + flags), merged on every rank"
+                "parallelism": (("kv-range split; packed partials stored to every rank by the decode kernels (peer stores of tagged words), merged on every rank"
                                  if args.exchange == "peer" else
                                  "kv-range split, packed partials exchanged (all-gather), merged on every rank") if mode == "kv-range" else
                                 ("one batch sharded by sequence (token-balanced), no collective" if mode == "strong"
