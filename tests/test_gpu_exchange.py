@@ -202,3 +202,43 @@ def test_a_rank_that_does_not_publish_ends_the_wait_with_a_status(built_libs):
     finally:
         for x in ranks:
             x.close()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_exchange_on_random_batches(built_libs, seed):
+    """Random worlds, batches, head geometries and lengths (some shorter than a rank's range start),
+    plan and early-metadata flag at random; three steps each."""
+    from single_gpu_inference_lab_b200 import cabi, sharding
+
+    cabi.load()
+    gen = torch.Generator().manual_seed(900 + seed)
+    world = [2, 3, 4, 5, 7, 8][seed]
+    name = ["qwen2.5-coder-3b-b64", "qwen2.5-7b-b256", "llama3-8b-long-b4"][seed % 3]
+    batch = int(torch.randint(1, 20, (1,), generator=gen))
+    w = make_inputs(name, seed=seed, batch=batch, shrink=[0.3, 0.1, 1 / 64][seed % 3])
+    lens = w.seq_lens.clone()
+    for i in range(0, batch, 3):
+        lens[i] = int(torch.randint(1, int(w.max_seq_len) + 1, (1,), generator=gen))
+    w.seq_lens = lens
+    exp = oracle.reference(w.query, w.key_cache, w.value_cache, w.block_table.long(), w.seq_lens, w.k_scale, w.v_scale)
+    locals_ = [sharding.shard_kv_range(w, r, world).to(DEV) for r in range(world)]
+    b, hq, d = w.query.shape
+    ranks = sharding.KvRangeExchange.emulate(world, b, hq, d, DEV)
+    split = 128
+    flags = EARLY if seed % 2 else 0
+    try:
+        wss = [_workspace(l, split) for l in locals_]
+        plans = [cabi.plan_decode(l.query, l.key_cache, l.value_cache, l.block_table, l.seq_lens, max_seq_len=l.max_seq_len,
+                                  split_size=split, workspace=ws) if seed % 3 == 0 else None for l, ws in zip(locals_, wss)]
+        for step in range(3):
+            outs = [torch.full_like(l.query, float("nan")) for l in locals_]
+            for x, l, ws, plan in zip(ranks, locals_, wss, plans):
+                x.decode(l, split_size=split, workspace=ws, plan=plan, flags=flags)
+            for x, o in zip(ranks, outs):
+                x.merge(o)
+            assert cabi.device_status() == 0
+            for r, o in enumerate(outs):
+                assert_within_gate(o, exp, f"seed {seed} world {world} step {step} rank {r}")
+    finally:
+        for x in ranks:
+            x.close()

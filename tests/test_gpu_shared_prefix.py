@@ -291,3 +291,52 @@ def test_grouped_decode_through_the_dispatcher_and_its_workspace_check(built_lib
     with pytest.raises(RuntimeError, match="needs"):
         ops.shared_prefix_decode_grouped_fp8_e4m3(g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens, *small, out,
                                                   g.k_scale, g.v_scale, w.max_seq_len, 128, found)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_grouped_decode_on_random_batches_matches_the_oracle(cabi, seed):
+    """Random batches: 1-4 groups of random sizes and prefix lengths (discovered on the device from
+    the table and the lengths), requests in no group, random suffixes, both head geometries."""
+    gen = torch.Generator().manual_seed(500 + seed)
+    hq, hkv = [(16, 2), (28, 4), (8, 8), (32, 8)][seed % 4]
+    batch = int(torch.randint(9, 70, (1,), generator=gen))
+    n_groups = int(torch.randint(1, 5, (1,), generator=gen))
+    pages = 4096
+    d = 128
+    key = torch.randn(pages, 16, hkv, d, generator=gen)
+    value = torch.randn(pages, 16, hkv, d, generator=gen)
+    from single_gpu_inference_lab_b200.workloads import quantize_per_head
+
+    kc, ks = quantize_per_head(key)
+    vc, vs = quantize_per_head(value)
+    cols = 80
+    table = torch.randint(0, pages, (batch, cols), generator=gen, dtype=torch.int32)
+    lens = torch.randint(1, cols * 16 + 1, (batch,), generator=gen, dtype=torch.int32)
+    order = torch.randperm(batch, generator=gen).tolist()
+    per = max(batch // (n_groups + 1), 1)
+    expect_groups = 0
+    for g in range(n_groups):
+        rows = order[g * per:(g + 1) * per]
+        prefix_pages = int(torch.randint(17, 60, (1,), generator=gen))  # 272 .. 944 tokens, min_prefix_len is 256
+        chain = torch.randint(0, pages, (prefix_pages,), generator=gen, dtype=torch.int32)
+        for r in rows:
+            table[r, :prefix_pages] = chain
+            lens[r] = int(torch.randint(prefix_pages * 16, cols * 16 + 1, (1,), generator=gen))
+        expect_groups += len(rows) >= 8
+    q = torch.randn(batch, hq, d, generator=gen).to(torch.bfloat16)
+    exp = oracle.reference(q, kc, vc, table.long(), lens, ks, vs)
+    dev = lambda t: t.to(DEV)
+    gq, gkc, gvc, gt, gl, gks, gvs = map(dev, (q, kc, vc, table, lens, ks, vs))
+    groups, max_groups = cabi.group_shared_prefixes(gt, seq_lens=gl, min_batch=8, min_prefix_len=256, max_groups=4)
+    max_len = int(lens.max())
+    split = 256
+    slots = -(-max_len // 256) + -(-max_len // split)
+    ws = (torch.full((batch, hq, slots, d), float("nan"), device=DEV), torch.full((batch, hq, slots), float("nan"), device=DEV),
+          torch.full((batch, hq, slots), float("nan"), device=DEV))
+    out = torch.full_like(gq, float("nan"))
+    cabi.shared_prefix_decode_grouped_fp8_e4m3(gq, gkc, gvc, gt, gl, groups=groups, max_groups=max_groups, k_scale=gks, v_scale=gvs,
+                                               max_seq_len=max_len, split_size=split, output=out, workspace=ws)
+    torch.cuda.synchronize()
+    assert cabi.device_status() == 0
+    assert int(groups[3]) >= expect_groups  # (chance agreement of random pages aside, at least the planted groups)
+    assert_within_gate(out, exp, f"random grouped batch {seed}: batch {batch}, {n_groups} planted groups, {hq}/{hkv} heads")
