@@ -55,6 +55,17 @@ extern "C" {
  */
 
 /*
+ * Stream order.  Every kernel of a call is launched with programmatic stream serialisation: it may
+ * become resident while the kernel in front of it in the stream drains, but it reads and writes
+ * nothing before that kernel has completed -- except, under PFD_FLAG_EARLY_METADATA, seq_lens,
+ * block_table and the plan.  The last kernel of a call completes only after every kernel of the
+ * call has (whatever rows it had to merge itself), so whoever enqueues work behind a call, with or
+ * without programmatic launch attributes, finds the call's output complete.  Nothing is allocated,
+ * nothing synchronises with the host; the entry points that take a workspace are captured in CUDA
+ * graphs by this repository's tests.
+ */
+
+/*
  * Operands of one decode-attention layer-step.
  *
  * Replaces the argument list of
