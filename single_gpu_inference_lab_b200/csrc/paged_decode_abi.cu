@@ -269,7 +269,9 @@ constexpr int kChunkMaxBatch = 2048;
 // 16-bit caches: a stage of two pages is 16 KiB, six warps x two stages fill the same 192 KiB.
 constexpr int kChunkStages16 = 2;
 constexpr int kChunkWarps16 = 6;
-constexpr int kChunkPieceCost = 2;  // half page pairs charged for starting a sequence
+// Half page pairs charged for starting a sequence.  Measured on the batch-256 configuration
+// (us per step): 0 -> 53.9, 1 -> 44.2, 2 -> 43.0, 3 -> 43.3, 4 -> 44.0; the batch-64 one does not care.
+constexpr int kChunkPieceCost = 2;
 
 bool balanced_eligible(const pfd_decode_args& a, int group, int slot_offset, int sms) {
   if (a.flags & (PFD_FLAG_FIXED_SPLITS | PFD_FLAG_NO_TMA | PFD_FLAG_NO_DIRECT_OUT)) return false;
@@ -345,11 +347,15 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
   if (fused || (a.flags & PFD_FLAG_PARTIAL_ONLY)) return PFD_OK;
   {
     // Few rows mean few, long sequences whose pieces are many: four warps then share a row,
-    // which also puts more loads in flight per SM.  Either way 64 registers, 8 CTAs per SM.
+    // which also puts more loads in flight per SM (64 registers, 8 CTAs per SM).  Many rows: one
+    // warp per row, up to 16 pieces requested in one round trip (128 registers, 4 CTAs per SM):
+    // most rows of a large batch have nothing to merge and leave at once, and the few long
+    // sequences that were cut into a dozen pieces set the tail -- 44.9 -> 43.0 us per step on the
+    // batch-256 configuration against 8 pieces per round at 8 CTAs per SM.
     // (CTAs of a single warp and row, all resident beside the chunk kernel, were measured
     // slower: 21.8 against 19.9 us per step on the batch-64 configuration.)
     const int rows = a.batch * a.num_q_heads;
-    const bool wide = rows <= 8 * sms;
+    const bool wide = rows <= 8 * sms;  // (one warp per row on the batch-64 configuration: 21.0 against 19.9 us)
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(wide ? rows : (rows + 3) / 4);
     cfg.blockDim = dim3(128);
@@ -359,7 +365,7 @@ int launch_balanced(const pfd_decode_args& a, const pfd::KernelParams& kp, int s
     cfg.numAttrs = 1;
     const cudaError_t e =
         wide ? cudaLaunchKernelEx(&cfg, pfd::paged_decode_chunk_merge_kernel<QBF16, 4, 4, 8>, kp, tp, cp)
-             : cudaLaunchKernelEx(&cfg, pfd::paged_decode_chunk_merge_kernel<QBF16, 1, 8, 8>, kp, tp, cp);
+             : cudaLaunchKernelEx(&cfg, pfd::paged_decode_chunk_merge_kernel<QBF16, 1, 16, 4>, kp, tp, cp);
     if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "balanced merge kernel launch failed: %s", cudaGetErrorString(e));
   }
   return check_launch("balanced merge kernel");
