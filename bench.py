@@ -340,7 +340,9 @@ class Case:
         self.vcs = [w.value_cache] + [w.value_cache.clone() for _ in range(self.pools - 1)]
         self.shared_prefix = w.prefix_len > 0 and not args.no_shared_prefix and self.d == 128 and kv16 is None
         if self.shared_prefix and not args.split_size:
-            self.split = 512
+            from single_gpu_inference_lab_b200.l20_shared_prefix_decode_dispatch import choose_suffix_split_size
+
+            self.split = choose_suffix_split_size(self.batch, self.hkv, w.max_seq_len - w.prefix_len)
         self.ws = l20_paged_split_kv.allocate_l20_paged_split_kv_workspace(q, w.max_seq_len, split_size=self.split)
         if self.shared_prefix:
             from single_gpu_inference_lab_b200 import l20_shared_prefix_decode_dispatch as spd
@@ -352,9 +354,11 @@ class Case:
         self.groups = None
         if self.shared_prefix and args.grouped_prefix:
             self.groups, self.max_groups = cabi.group_shared_prefixes(w.block_table, seq_lens=w.seq_lens, min_batch=8,
-                                                                      min_prefix_len=1024, max_groups=4)
+                                                                      min_prefix_len=4096, max_groups=4)
             self.prefix_bound = (w.prefix_len + 255) // 256 * 256  # an engine knows how long its cached prefixes can be
-            slots = self.prefix_bound // 256 + -(-w.max_seq_len // self.split)
+            self.suffix_bound = max(w.max_seq_len - 4096, 16)  # true for any group the grouping call above can find
+            self.split = choose_suffix_split_size(self.batch, self.hkv, self.suffix_bound) if not args.split_size else self.split
+            slots = self.prefix_bound // 256 + -(-self.suffix_bound // self.split)
             self.ws = (torch.empty(self.batch, self.hq, slots, self.d, device=dev), torch.empty(self.batch, self.hq, slots, device=dev),
                        torch.empty(self.batch, self.hq, slots, device=dev), torch.empty_like(q))
             torch.cuda.synchronize()
@@ -394,7 +398,8 @@ class Case:
         if self.groups is not None:
             cabi.shared_prefix_decode_grouped_fp8_e4m3(
                 w.query, kc, vc, w.block_table, w.seq_lens, groups=self.groups, max_groups=self.max_groups,
-                max_prefix_len=self.prefix_bound, k_scale=w.k_scale, v_scale=w.v_scale, max_seq_len=w.max_seq_len,
+                max_prefix_len=self.prefix_bound, max_suffix_len=self.suffix_bound, k_scale=w.k_scale, v_scale=w.v_scale,
+                max_seq_len=w.max_seq_len,
                 split_size=self.split, output=self.out, workspace=self.ws)
             return
         if self.shared_prefix:
@@ -738,11 +743,11 @@ def main() -> int:
             # the step's own block table and lengths arrive with the step: group them, then decode
             from single_gpu_inference_lab_b200 import l20_paged_decode as ops
 
-            found = ops.group_shared_prefixes(dtable, seq_lens=dlens, min_batch=8, min_prefix_len=1024,
+            found = ops.group_shared_prefixes(dtable, seq_lens=dlens, min_batch=8, min_prefix_len=4096,
                                               max_groups=case.max_groups, buffer=case.groups)
             res = ops.shared_prefix_decode_grouped_fp8_e4m3(
                 dq, kc, vc, dtable, dlens, ws[0], ws[1], ws[2], ws[3], w.k_scale, w.v_scale, w.max_seq_len, split, found,
-                max_prefix_len=case.prefix_bound)
+                max_prefix_len=case.prefix_bound, max_suffix_len=case.suffix_bound)
         elif case.shared_prefix:
             res = case.spd.shared_paged_prefix_paged_suffix_gqa_decode_attention_fp8(
                 dq, kc, vc, dtable, dlens, w.prefix_len, k_scale=w.k_scale, v_scale=w.v_scale,

@@ -356,13 +356,18 @@ int pfd_group_shared_prefixes(const int32_t* block_table, int64_t bt_stride_b, i
  * merge.  A prefix is used up to a multiple of 16 tokens and up to min(max_prefix_len,
  * max_seq_len); what lies beyond goes through the split-KV pass, so any bound is safe and a
  * tight one saves idle CTAs.  Every member of a group must be at least as long as the group's
- * prefix.  The workspace needs ceil(min(max_prefix_len, max_seq_len) / 256) +
- * ceil(max_seq_len / split_size) slots on its split axis.  The reference has no counterpart: its
+ * prefix.  max_suffix_len bounds what a request IN a group has behind its prefix (0 = unknown: the
+ * whole context); the split-KV grid is sized for it, ceil(max_suffix_len / split_size) splits, and
+ * a request in no group covers its whole context with as many, longer, splits.  A member whose
+ * suffix exceeds the bound would be attended only up to it (device status 5 reports it): give a true bound (max_seq_len minus
+ * the smallest prefix a group can have, i.e. the min_prefix_len of the grouping call).  The
+ * workspace needs ceil(min(max_prefix_len, max_seq_len) / 256) +
+ * ceil(min(max_suffix_len or max_seq_len, max_seq_len) / split_size) slots on its split axis.  The reference has no counterpart: its
  * dispatch stops at one group spanning the batch
  * (integrations/vllm/l20_shared_prefix_decode_dispatch.py:122-159).
  */
 int pfd_shared_prefix_decode_grouped_fp8_e4m3(const pfd_decode_args* args, const void* groups, int32_t max_groups,
-                                              int32_t max_prefix_len);
+                                              int32_t max_prefix_len, int32_t max_suffix_len);
 
 /*
  * Debug / parity entry: writes, for every (sequence, token < max_seq_len), the cache slot
@@ -379,7 +384,8 @@ int pfd_resolve_slots(const int32_t* block_table, int64_t bt_stride_b, const int
  * when a bounded wait gave up: 0 = none, 1 = a TMA copy did not complete in time (the step's
  * output is then undefined), 2 = args->plan was made for other inputs (nothing was written),
  * 3 = the tensor cores of the dense shared-prefix pass did not complete in time (output undefined),
- * 4 = a rank's rows of a KV-range exchange step did not arrive in time (those rows were not merged).
+ * 4 = a rank's rows of a KV-range exchange step did not arrive in time (those rows were not merged),
+ * 5 = grouped shared-prefix decode: a request's suffix is longer than max_suffix_len (its output is wrong).
  * The kernels never trap and never spin without a limit.
  */
 int pfd_device_status(int32_t* status);

@@ -311,16 +311,17 @@ def group_shared_prefixes(block_table, *, prefix_lengths=None, uniform_prefix_le
 
 
 def shared_prefix_decode_grouped_fp8_e4m3(query, key_cache, value_cache, block_table, seq_lens, *, groups, max_groups,
-                                          max_prefix_len=None, **kw) -> None:
+                                          max_prefix_len=None, max_suffix_len=None, **kw) -> None:
     """One layer-step through ``pfd_shared_prefix_decode_grouped_fp8_e4m3``: any number of
     shared-prefix groups plus requests in none, as the groups buffer on the device says."""
     args = decode_args(query, key_cache, value_cache, block_table, seq_lens, **kw)
     lib = load()
-    lib.pfd_shared_prefix_decode_grouped_fp8_e4m3.argtypes = [C.POINTER(DecodeArgs), C.c_void_p, C.c_int32, C.c_int32]
+    lib.pfd_shared_prefix_decode_grouped_fp8_e4m3.argtypes = [C.POINTER(DecodeArgs), C.c_void_p, C.c_int32, C.c_int32, C.c_int32]
     lib.pfd_shared_prefix_decode_grouped_fp8_e4m3.restype = C.c_int
     bound = args.max_seq_len if max_prefix_len is None else int(max_prefix_len)
     with torch.cuda.device(query.device):
-        _check(lib.pfd_shared_prefix_decode_grouped_fp8_e4m3(C.byref(args), groups.data_ptr(), int(max_groups), bound))
+        _check(lib.pfd_shared_prefix_decode_grouped_fp8_e4m3(C.byref(args), groups.data_ptr(), int(max_groups), bound,
+                                                             int(max_suffix_len or 0)))
 
 
 NOALLOC_SCRATCH_BYTES = 8 * 1024 * 1024

@@ -38,7 +38,7 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
                 int64_t prefix_len = 0, bool kv16 = false,
                 const c10::optional<at::Tensor>& page_indptr = c10::nullopt, bool plan_only = false,
                 const c10::optional<at::Tensor>& groups = c10::nullopt, int64_t max_groups = 0,
-                int64_t max_prefix_len = 0) {
+                int64_t max_prefix_len = 0, int64_t max_suffix_len = 0) {
   TORCH_CHECK(query.is_cuda(), "query must be CUDA");
   TORCH_CHECK(query.scalar_type() == at::kHalf || query.scalar_type() == at::kBFloat16,
               "query must be FP16 or BF16");
@@ -176,7 +176,8 @@ void run_decode(const at::Tensor& query, const at::Tensor& key_cache, const at::
                     groups->numel() * 4 >= pfd_prefix_groups_bytes(a.batch, static_cast<int32_t>(max_groups)),
                 "groups must be the int32 CUDA buffer group_shared_prefixes filled for this batch and max_groups");
     TORCH_CHECK(pfd_shared_prefix_decode_grouped_fp8_e4m3(&a, groups->data_ptr<int32_t>(), static_cast<int32_t>(max_groups),
-                                                          static_cast<int32_t>(max_prefix_len)) == PFD_OK,
+                                                          static_cast<int32_t>(max_prefix_len),
+                                                          static_cast<int32_t>(max_suffix_len)) == PFD_OK,
                 pfd_last_error());
     return;
   }
@@ -302,10 +303,10 @@ void shared_prefix_decode_grouped_fp8_e4m3(at::Tensor query, at::Tensor key_cach
                                            at::Tensor partial_max, at::Tensor partial_sum, at::Tensor output,
                                            at::Tensor k_scale, at::Tensor v_scale, double sm_scale,
                                            int64_t max_seq_len, int64_t split_size, at::Tensor groups,
-                                           int64_t max_groups, int64_t max_prefix_len) {
+                                           int64_t max_groups, int64_t max_prefix_len, int64_t max_suffix_len) {
   run_decode(query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max, partial_sum,
              output, c10::nullopt, 1.0, 1.0, k_scale, v_scale, sm_scale, max_seq_len, split_size, 0, 0,
-             c10::nullopt, 0, false, c10::nullopt, false, groups, max_groups, max_prefix_len);
+             c10::nullopt, 0, false, c10::nullopt, false, groups, max_groups, max_prefix_len, max_suffix_len);
 }
 
 // Rotary embedding of the new tokens' query and key (in place) + append of key / value to the
@@ -498,7 +499,7 @@ TORCH_LIBRARY(l20_stack, module) {
       "Tensor query, Tensor key_cache, Tensor value_cache, Tensor block_table, Tensor seq_lens, "
       "Tensor(a!) partial_output, Tensor(b!) partial_max, Tensor(c!) partial_sum, Tensor(d!) output, "
       "Tensor k_scale, Tensor v_scale, float sm_scale, int max_seq_len, int split_size, Tensor groups, "
-      "int max_groups, int max_prefix_len) -> ()");
+      "int max_groups, int max_prefix_len, int max_suffix_len) -> ()");
   module.def(
       "rope_and_cache(Tensor(a!) query, Tensor(b!) key, Tensor value, Tensor positions, Tensor cos_sin_cache, "
       "bool is_neox, Tensor(c!) key_cache, Tensor(d!) value_cache, Tensor slot_mapping, "

@@ -429,8 +429,17 @@ int64_t pfd_launch_count(void) { return g_launches.load(std::memory_order_relaxe
 }  // extern "C"
 
 namespace {
+// What the grouped shared-prefix entry adds to a split-KV pass: per-request attend starts read on
+// the device, their cap, the split size of requests in no group, and the grid's split count.
+struct GroupedRows {
+  const int32_t* row_kv_start = nullptr;
+  int row_kv_cap = 0;
+  int split_size_loner = 0;
+  int num_splits = 0;
+};
+
 pfd::KernelParams fill_params(const pfd_decode_args& a, int group, bool direct_ok, int slot_offset,
-                              const int32_t* row_kv_start = nullptr, int row_kv_cap = 0) {
+                              const GroupedRows* grouped = nullptr) {
   pfd::KernelParams kp{};
   kp.query = a.query;
   kp.key_cache = static_cast<const uint8_t*>(a.key_cache);
@@ -460,8 +469,11 @@ pfd::KernelParams fill_params(const pfd_decode_args& a, int group, bool direct_o
   kp.direct_out = direct_ok ? 1 : 0;
   kp.bt_cols = (a.max_seq_len + pfd::kPage - 1) / pfd::kPage;  // rows are at least this wide
   kp.slot_offset = slot_offset;
-  kp.row_kv_start = row_kv_start;
-  kp.row_kv_cap = row_kv_cap;
+  if (grouped != nullptr) {
+    kp.row_kv_start = grouped->row_kv_start;
+    kp.row_kv_cap = grouped->row_kv_cap;
+    kp.split_size_loner = grouped->split_size_loner;
+  }
   kp.early_metadata = (a.flags & PFD_FLAG_EARLY_METADATA) ? 1 : 0;
   kp.kv_evict_first = 1;
   if (a.exchange != nullptr) {
@@ -483,7 +495,7 @@ pfd::KernelParams fill_params(const pfd_decode_args& a, int group, bool direct_o
 
 // slot_offset > 0: workspace slots [0, slot_offset) are filled by the dense prefix pass; the
 // split-KV kernels then write behind them and the merge kernel covers both.
-int decode_impl(const pfd_decode_args* args, int slot_offset, const int32_t* row_kv_start = nullptr, int row_kv_cap = 0) {
+int decode_impl(const pfd_decode_args* args, int slot_offset, const GroupedRows* grouped = nullptr) {
   if (args == nullptr) return fail(PFD_ERR_INVALID, "args is NULL");
   if (args->struct_size != sizeof(pfd_decode_args))
     return fail(PFD_ERR_INVALID, "pfd_decode_args size mismatch: caller %u, library %zu",
@@ -533,6 +545,7 @@ int decode_impl(const pfd_decode_args* args, int slot_offset, const int32_t* row
 
   const int span = a.max_seq_len > a.kv_start ? a.max_seq_len - a.kv_start : 0;
   int num_splits = (span + a.split_size - 1) / a.split_size;
+  if (grouped != nullptr) num_splits = grouped->num_splits;
   if (num_splits < 1) num_splits = 1;
   const bool direct_ok = !(a.flags & PFD_FLAG_NO_DIRECT_OUT) && slot_offset == 0;
   if (num_splits > 1 || !direct_ok) {
@@ -547,7 +560,7 @@ int decode_impl(const pfd_decode_args* args, int slot_offset, const int32_t* row
   }
 
   if (int rc = enter_call()) return rc;  // (argument errors above are reported without a device)
-  const pfd::KernelParams kp = fill_params(a, group, direct_ok, slot_offset, row_kv_start, row_kv_cap);
+  const pfd::KernelParams kp = fill_params(a, group, direct_ok, slot_offset, grouped);
 
   const bool bf16 = a.query_dtype == PFD_DTYPE_BF16;
   if (a.head_dim == 128)
@@ -801,7 +814,7 @@ void* g_noalloc_ptr[kMaxDevices] = {nullptr};
 }  // namespace
 
 int pfd_shared_prefix_decode_grouped_fp8_e4m3(const pfd_decode_args* args, const void* groups, int32_t max_groups,
-                                              int32_t max_prefix_len) {
+                                              int32_t max_prefix_len, int32_t max_suffix_len) {
   if (args == nullptr) return fail(PFD_ERR_INVALID, "args is NULL");
   if (args->struct_size != sizeof(pfd_decode_args))
     return fail(PFD_ERR_INVALID, "pfd_decode_args size mismatch: caller %u, library %zu", args->struct_size,
@@ -810,7 +823,7 @@ int pfd_shared_prefix_decode_grouped_fp8_e4m3(const pfd_decode_args* args, const
   if (groups == nullptr || max_groups < 1) return fail(PFD_ERR_INVALID, "a groups buffer and its max_groups are needed");
   if (a.head_dim != 128 || a.page_size != pfd::kPage)
     return fail(PFD_ERR_UNSUPPORTED, "the shared-prefix pass needs head_dim 128 and page_size 16");
-  if (max_prefix_len < 0) return fail(PFD_ERR_INVALID, "negative length");
+  if (max_prefix_len < 0 || max_suffix_len < 0) return fail(PFD_ERR_INVALID, "negative length");
   if (a.kv_start != 0) return fail(PFD_ERR_INVALID, "kv_start must be 0 for the shared-prefix pass");
   if (a.page_indptr != nullptr) return fail(PFD_ERR_UNSUPPORTED, "the shared-prefix pass needs a block table");
   if (a.exchange != nullptr) return fail(PFD_ERR_UNSUPPORTED, "exchange: not with the shared-prefix pass");
@@ -829,7 +842,11 @@ int pfd_shared_prefix_decode_grouped_fp8_e4m3(const pfd_decode_args* args, const
   if (a.split_size < 16 || a.split_size % 16) return fail(PFD_ERR_INVALID, "split_size must be a multiple of 16");
   const int cap = std::min(max_prefix_len, a.max_seq_len) & ~15;  // no group's prefix pass reaches further
   const int chunks = (cap + pfd::kPrefixChunk - 1) / pfd::kPrefixChunk;
-  const int ns = std::max((a.max_seq_len + a.split_size - 1) / a.split_size, 1);  // a request in no group attends from 0
+  // Requests in groups have at most max_suffix_len tokens behind their prefix (0 = unknown: the
+  // whole context); a request in no group attends from 0 and gets the same number of splits, longer ones.
+  const int suffix = max_suffix_len > 0 ? std::min(max_suffix_len, a.max_seq_len) : a.max_seq_len;
+  const int ns = std::max((suffix + a.split_size - 1) / a.split_size, 1);
+  const int split_loner = std::max(((a.max_seq_len + ns - 1) / ns + 15) / 16 * 16, a.split_size);
   if (a.workspace_splits < chunks + ns)
     return fail(PFD_ERR_INVALID, "partial output workspace has wrong shape: the grouped shared-prefix pass needs %d slots",
                 chunks + ns);
@@ -841,7 +858,12 @@ int pfd_shared_prefix_decode_grouped_fp8_e4m3(const pfd_decode_args* args, const
   if (chunks > 0)
     if (int rc = bf16 ? launch_prefix<true>(a, cap, chunks, g, max_groups) : launch_prefix<false>(a, cap, chunks, g, max_groups))
       return rc;
-  return decode_impl(&a, chunks, g + pfd::groups_row_prefix_off(), cap);
+  GroupedRows rows;
+  rows.row_kv_start = g + pfd::groups_row_prefix_off();
+  rows.row_kv_cap = cap;
+  rows.split_size_loner = split_loner;
+  rows.num_splits = ns;
+  return decode_impl(&a, chunks, &rows);
 }
 
 int pfd_paged_decode_fp8_e4m3_split_out_noalloc(const pfd_decode_args* args) {
@@ -988,6 +1010,7 @@ int64_t pfd_balanced_workspace_rows(int32_t num_q_heads, int32_t num_kv_heads) {
 // set, the kernels store %globaltimer stamps of their phases there.  Not part of the shipped ABI.
 int pfd_debug_phase_times(void* device_buffer) {
   g_phase_times = static_cast<unsigned long long*>(device_buffer);
+  cudaMemcpyToSymbol(pfd::g_dbg_stamps, &g_phase_times, sizeof g_phase_times);
   return PFD_OK;
 }
 #endif

@@ -60,6 +60,7 @@ struct KernelParams {
   // its group, 0 for a request in no group) and owns ceil(that / 256) of the slots in front.
   const int32_t* row_kv_start;
   int32_t row_kv_cap;  // upper bound applied to row_kv_start (a multiple of 16): the slots in front cover no more
+  int32_t split_size_loner;  // grouped decode: split size of a request in no group (it attends from 0); 0 = split_size
   int32_t early_metadata;  // 1: seq_lens and block_table may be read before the preceding kernel has completed
   int32_t kv_evict_first;  // 1: K/V tiles are loaded with the L2 evict-first hint
   // KV-range exchange (xch_world > 0): the packed (o, m, l) rows of this rank go, instead of to
@@ -118,6 +119,12 @@ __device__ __forceinline__ unsigned long long* xch_row(const KernelParams& p, in
 // First token the split-KV kernels attend for sequence b.
 __device__ __forceinline__ int kv_start_of(const KernelParams& p, int b) {
   return p.row_kv_start != nullptr ? min(__ldg(p.row_kv_start + b) & ~15, p.row_kv_cap) : p.kv_start;
+}
+
+// Split size of sequence b, whose first attended token is kv0: in a grouped decode a request in
+// no group has the whole context to cover with the same number of splits as the others' suffixes.
+__device__ __forceinline__ int split_size_of(const KernelParams& p, int kv0) {
+  return (p.row_kv_start != nullptr && kv0 == 0 && p.split_size_loner > 0) ? p.split_size_loner : p.split_size;
 }
 
 __device__ __forceinline__ int32_t page_of(const int32_t* __restrict__ block_table,
@@ -514,14 +521,15 @@ paged_decode_fp8_partial_ldg_kernel(const KernelParams p) {
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int seq_len = p.seq_lens[b];
   const int kv0 = kv_start_of(p, b);
-  const int lo = kv0 + split * p.split_size;
-  const int hi = min(lo + p.split_size, seq_len);
+  const int split_sz = split_size_of(p, kv0);
+  const int lo = kv0 + split * split_sz;
+  const int hi = min(lo + split_sz, seq_len);
   if (lo >= hi) {  // the merge kernel derives the live split count from seq_len
     pdl_wait();
     if (split == 0 && gridDim.x == 1 && p.direct_out) write_empty_rows<D>(p, b, kvh);
     return;
   }
-  const int nsplits_seq = (seq_len - kv0 + p.split_size - 1) / p.split_size;
+  const int nsplits_seq = (seq_len - kv0 + split_sz - 1) / split_sz;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
 
   __shared__ float sm_m[NWARPS * 16];
@@ -693,6 +701,21 @@ __device__ __forceinline__ void mark_value_at(const TmaParams& tp, int slot, int
   (void)tp; (void)slot; (void)k; (void)leader; (void)v;
 #endif
 }
+// Tuning builds only: marks of kernels that carry no TmaParams (slot rows of the same buffer).
+#ifdef PFD_PHASE_STAMPS
+__device__ unsigned long long* g_dbg_stamps = nullptr;
+#endif
+__device__ __forceinline__ void dbg_mark(int slot, int k, bool leader) {
+#ifdef PFD_PHASE_STAMPS
+  if (g_dbg_stamps != nullptr && leader) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_dbg_stamps[(size_t)slot * 8 + k] = t;
+  }
+#else
+  (void)slot; (void)k; (void)leader;
+#endif
+}
 __device__ __forceinline__ unsigned sm_id() {
   unsigned r;
   asm volatile("mov.u32 %0, %%smid;" : "=r"(r));
@@ -700,6 +723,7 @@ __device__ __forceinline__ unsigned sm_id() {
 }
 
 constexpr int kErrTmaTimeout = 1;
+constexpr int kErrSuffixBound = 5;  // grouped decode: a request's suffix exceeds the caller's bound
 
 __global__ void bounded_wait_selftest_kernel(int32_t* status, unsigned long long limit_ns, unsigned long long* waited_ns) {
   __shared__ __align__(8) unsigned long long bar_storage;
@@ -736,6 +760,8 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   constexpr uint32_t kTileBytes = kPage * D;  // 2 KiB
   constexpr uint32_t kStageBytes = 4 * kTileBytes;
   pdl_launch_dependents();
+  const int dbg_slot = 1024 + blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);  // tuning builds only
+  dbg_mark(dbg_slot, 0, threadIdx.x == 0);
   if (threadIdx.x == 0) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_k)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmap_v)) : "memory");
@@ -749,7 +775,8 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, i = lane >> 2, j = lane & 3;
   const int kv0 = kv_start_of(p, b);
-  const int lo = kv0 + split * p.split_size;
+  const int split_sz = split_size_of(p, kv0);
+  const int lo = kv0 + split * split_sz;
 
   // Page ids of this warp's first 16 page pairs, one page per lane, fetched before the
   // sequence length is known (the block-table row is bt_cols wide, so this stays inside it).
@@ -762,14 +789,19 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
     if (pg < p.bt_cols) ids = page_of(p.block_table, p.bt_stride_b, b, pg);
   }
   const int seq_len = p.seq_lens[b];
-  const int hi = min(lo + p.split_size, seq_len);
+  const int hi = min(lo + split_sz, seq_len);
+  // grouped decode: the grid was sized from the caller's bound on the suffixes; a request that
+  // needs more splits than the grid has would lose its tail silently, so it is reported instead
+  if (p.row_kv_start != nullptr && split == 0 && kvh == 0 && threadIdx.x == 0 &&
+      seq_len - kv0 > (int)gridDim.x * split_sz)
+    atomicExch(tp.status, kErrSuffixBound);
   if (lo >= hi) {
     pdl_wait();
     if (split == 0 && gridDim.x == 1 && p.direct_out) write_empty_rows<D>(p, b, kvh);
     return;
   }
   if (p.slot_offset == 0 && p.early_metadata) pdl_wait();
-  const int nsplits_seq = (seq_len - kv0 + p.split_size - 1) / p.split_size;
+  const int nsplits_seq = (seq_len - kv0 + split_sz - 1) / split_sz;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t ring = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -918,10 +950,12 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   }
   __syncthreads();  // every warp is done with its ring: sm_o may alias it
   cta_merge_and_store<D, QBF16, NWARPS>(st, p, b, kvh, split, nsplits_seq, vs, sm_m, sm_l, sm_o);
+  dbg_mark(dbg_slot, 1, threadIdx.x == 0);
   // When this grid was launched as a programmatic dependent of the dense prefix pass (it never
   // reads that pass's results, so it starts right away), it must not complete before that pass:
   // the merge kernel behind it waits for *this* grid only.  A no-op for an ordinary launch.
   pdl_wait();
+  dbg_mark(dbg_slot, 2, threadIdx.x == 0);
 }
 
 // LSE merge over the live splits of each (sequence, q head).  WPR = 1: one warp per row, four
@@ -933,6 +967,7 @@ __global__ void __launch_bounds__(128)
 paged_decode_merge_kernel(const KernelParams p, int batch) {
   static_assert(WPR == 1 || WPR == 4, "one or four warps per row");
   pdl_launch_dependents();
+  dbg_mark(4096 + blockIdx.x, 0, threadIdx.x == 0);
   const int warp = threadIdx.x >> 5;
   const int row = WPR == 1 ? blockIdx.x * 4 + warp : blockIdx.x;
   const int part = WPR == 1 ? 0 : warp;
@@ -952,7 +987,8 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
   // slots in front of the splits: all slot_offset of them, or (grouped) those of this row's prefix
   const int pre = p.row_kv_start != nullptr ? (kv0 + 255) / 256 : p.slot_offset;
   const int skip = p.slot_offset - pre;  // unused slots between the row's prefix chunks and its splits
-  const int ns = (live > 0 ? (live + p.split_size - 1) / p.split_size : 0) + pre;
+  const int split_sz = split_size_of(p, kv0);
+  const int ns = (live > 0 ? (live + split_sz - 1) / split_sz : 0) + pre;
   constexpr int E = D / 32;  // elements per lane
   float acc[E];
 #pragma unroll
@@ -963,6 +999,7 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
     return;
   }
   pdl_wait();  // the partial kernel's stores are complete and visible from here on
+  dbg_mark(4096 + blockIdx.x, 1, threadIdx.x == 0);
   if (ns > 0) {
     const int64_t base = (int64_t)b * p.partial_stride_b + (int64_t)hq * p.partial_stride_h;
     // One pass with a running maximum; eight splits per round trip, their maxima, sums and data
@@ -1035,6 +1072,7 @@ paged_decode_merge_kernel(const KernelParams p, int batch) {
     if (lane == 0) { dst[D] = big; dst[D + 1] = den; }
     return;
   }
+  dbg_mark(4096 + blockIdx.x, 2, threadIdx.x == 0);
   const float inv = ns > 0 ? 1.f / den : 0.f;
   const int64_t oidx = (int64_t)b * p.o_stride_b + (int64_t)hq * p.o_stride_h + lane * E;
 #pragma unroll

@@ -41,6 +41,8 @@ class DecodeStep:
     plan: Optional[torch.Tensor] = None
     groups: object = None              # PrefixGroups when this step takes the grouped path
     prefix_workspace: Optional[tuple] = None
+    suffix_split: int = 512            # split size of the grouped path's split-KV pass
+    max_suffix: int = 0                # what a request in a group can have behind its prefix
     group_sizes: Optional[list] = None
 
 
@@ -119,7 +121,12 @@ def l20_decode_step(meta, query, key_cache, value_cache, block_tables, seq_lens,
                 )
                 step.group_sizes = sizes
         if take:
-            slots = -(-max_seq_len // PREFIX_CHUNK) + -(-max_seq_len // split_size)
+            from .l20_shared_prefix_decode_dispatch import choose_suffix_split_size
+
+            # grouped requests attend at most max_seq_len - MIN_PREFIX_TOKENS tokens behind their prefix
+            step.max_suffix = max(max_seq_len - MIN_PREFIX_TOKENS, 16)
+            step.suffix_split = choose_suffix_split_size(batch, kv_heads, step.max_suffix)
+            slots = -(-max_seq_len // PREFIX_CHUNK) + -(-step.max_suffix // step.suffix_split)
             step.groups = groups
             step.prefix_workspace = _persistent(("pws", query.device, batch, q_heads, slots), lambda: (
                 torch.empty(batch, q_heads, slots, head_dim, device=query.device, dtype=torch.float32),
@@ -150,7 +157,8 @@ def l20_grouped_decode(step: DecodeStep, query, key_cache, value_cache, block_ta
 
     po, pm, ps = step.prefix_workspace
     ops.shared_prefix_decode_grouped_fp8_e4m3(query, key_cache, value_cache, block_tables, seq_lens, po, pm, ps, output,
-                                              vec(k_scale), vec(v_scale), max_seq_len, split_size, step.groups)
+                                              vec(k_scale), vec(v_scale), max_seq_len, step.suffix_split, step.groups,
+                                              max_suffix_len=step.max_suffix)
     sw = _switches()
     if sw["trace"]:
         from .l20_shared_prefix_decode_dispatch import l20_shared_prefix_trace

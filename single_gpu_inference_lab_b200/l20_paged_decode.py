@@ -268,16 +268,21 @@ def shared_prefix_decode_grouped_fp8_e4m3(
     groups: "PrefixGroups",
     *,
     max_prefix_len: Optional[int] = None,
+    max_suffix_len: Optional[int] = None,
     sm_scale: float = 0.0,
 ) -> torch.Tensor:
     """Decode step of a batch with any number of shared-prefix groups plus requests in none
     (``groups`` from ``group_shared_prefixes``, read on the device): dense tcgen05 pass per group,
-    split-KV pass from each request's own start, one merge.  The workspace needs
-    ``ceil(min(max_prefix_len, max_seq_len) / 256) + ceil(max_seq_len / split_size)`` slots."""
+    split-KV pass from each request's own start, one merge.  ``max_suffix_len`` bounds what a
+    request in a group has behind its prefix (``max_seq_len`` minus the grouping's
+    ``min_prefix_len`` is always a true bound; ``None`` = the whole context): the split-KV grid is
+    sized for it and requests in no group get as many, longer, splits.  The workspace needs
+    ``ceil(min(max_prefix_len, max_seq_len) / 256) + ceil(min(max_suffix_len, max_seq_len) /
+    split_size)`` slots."""
     torch.ops.l20_stack.shared_prefix_decode_grouped_fp8_e4m3(
         query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max, partial_sum, output,
         k_scale, v_scale, float(sm_scale), max_seq_len, split_size, groups.buffer, groups.max_groups,
-        int(max_seq_len if max_prefix_len is None else max_prefix_len),
+        int(max_seq_len if max_prefix_len is None else max_prefix_len), int(max_suffix_len or 0),
     )
     return output
 

@@ -147,6 +147,21 @@ def should_dispatch_l20_shared_prefix_paged_decode(
     return _why_not(query, key_cache, block_tables, prefix_lengths, page_size, min_batch, min_prefix_length) is None
 
 
+def choose_suffix_split_size(batch: int, num_kv_heads: int, max_suffix_len: int, *, resident_ctas: int = 444) -> int:
+    """Split size of the suffix pass behind the dense prefix pass.  The suffix kernel's work items
+    are (request, kv head, split); private suffixes are short, so with the reference's constant
+    512 (install hook, :117) a work item is one latency chain of a few page pairs and there are too
+    few of them: the pass then lasts as long as the dense pass it follows (10 us on the batch of
+    64 with suffixes up to 512 tokens).  As many equal splits per request as make about one wave
+    of resident CTAs (3 per SM on 148 SMs) is the measured optimum there, in us per step:
+    512 -> 24.7, 256 -> 21.9, 192 -> 21.2, 160 -> 21.0, 144 -> 21.1, 128 -> 20.1, 112 -> 20.5, 64 -> 22.8."""
+    if max_suffix_len <= 0:
+        return 64
+    splits = max(1, -(-int(resident_ctas) // max(int(batch) * int(num_kv_heads), 1)))
+    size = -(-(-(-int(max_suffix_len) // splits)) // 16) * 16
+    return int(min(512, max(64, size)))
+
+
 def allocate_shared_prefix_workspace(query: torch.Tensor, max_seq_len: int, prefix_length: int, *, suffix_split_size: int = 512):
     """``(partial_output, partial_max, partial_sum, output)`` with one slot per 256-token prefix
     chunk plus one per suffix split."""
@@ -172,7 +187,7 @@ def shared_paged_prefix_paged_suffix_gqa_decode_attention_fp8(
     k_scale: torch.Tensor | float,
     v_scale: torch.Tensor | float,
     max_seq_len: int | None = None,
-    suffix_split_size: int = 512,
+    suffix_split_size: int | None = 512,
     output: torch.Tensor | None = None,
     workspace=None,
 ) -> torch.Tensor:
@@ -184,6 +199,8 @@ def shared_paged_prefix_paged_suffix_gqa_decode_attention_fp8(
     if max_seq_len is None:
         max_seq_len = int(seq_lens.max().item())
     num_kv_heads = key_cache.shape[2]
+    if suffix_split_size is None:  # (the reference's default is the constant 512)
+        suffix_split_size = choose_suffix_split_size(query.shape[0], num_kv_heads, max_seq_len - int(prefix_length))
     if workspace is None:
         workspace = allocate_shared_prefix_workspace(query, max_seq_len, prefix_length, suffix_split_size=suffix_split_size)
     partial_output, partial_max, partial_sum, workspace_output = workspace[:4]
@@ -214,7 +231,7 @@ def maybe_l20_shared_prefix_paged_decode(
     k_scale: torch.Tensor | float,
     v_scale: torch.Tensor | float,
     page_size: int = 16,
-    suffix_split_size: int = 512,
+    suffix_split_size: int | None = None,
     max_seq_len: int | None = None,
     workspace=None,
 ):

@@ -340,3 +340,31 @@ def test_grouped_decode_on_random_batches_matches_the_oracle(cabi, seed):
     assert cabi.device_status() == 0
     assert int(groups[3]) >= expect_groups  # (chance agreement of random pages aside, at least the planted groups)
     assert_within_gate(out, exp, f"random grouped batch {seed}: batch {batch}, {n_groups} planted groups, {hq}/{hkv} heads")
+
+
+def test_grouped_decode_with_a_suffix_bound_and_its_violation(cabi):
+    """With a true bound on the grouped requests' suffixes the split-KV grid has few splits, and the
+    requests in no group cover their whole context with as many, longer, ones; a bound that a
+    grouped request exceeds is reported through the device status (5), not swallowed."""
+    w, lengths = _mixed_batch(13, 1024, 512)
+    exp = oracle.reference(w.query, w.key_cache, w.value_cache, w.block_table.long(), w.seq_lens, w.k_scale, w.v_scale)
+    g = w.to(DEV)
+    groups, max_groups = cabi.group_shared_prefixes(g.block_table, prefix_lengths=lengths.to(DEV), min_batch=8, min_prefix_len=256)
+    split = 64
+    bound = w.max_seq_len - 512  # group B's prefix is the shortest
+    slots = -(-w.max_seq_len // 256) + -(-bound // split)
+    b, hq, d = g.query.shape
+    ws = (torch.full((b, hq, slots, d), float("nan"), device=DEV), torch.full((b, hq, slots), float("nan"), device=DEV),
+          torch.full((b, hq, slots), float("nan"), device=DEV))
+    common = dict(groups=groups, max_groups=max_groups, k_scale=g.k_scale, v_scale=g.v_scale, max_seq_len=w.max_seq_len,
+                  split_size=split, workspace=ws)
+    out = torch.full_like(g.query, float("nan"))
+    cabi.shared_prefix_decode_grouped_fp8_e4m3(g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens, output=out,
+                                               max_suffix_len=bound, **common)
+    torch.cuda.synchronize()
+    assert cabi.device_status() == 0
+    assert_within_gate(out, exp, "grouped decode with a suffix bound")
+    cabi.shared_prefix_decode_grouped_fp8_e4m3(g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens, output=out,
+                                               max_suffix_len=64, **common)
+    torch.cuda.synchronize()
+    assert cabi.device_status() == 5
