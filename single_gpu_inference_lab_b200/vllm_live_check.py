@@ -48,7 +48,8 @@ llm = LLM(model=os.environ["LIVE_MODEL"], load_format="dummy", skip_tokenizer_in
           enforce_eager=os.environ.get("LIVE_GRAPHS", "0") != "1",
           kv_cache_dtype=os.environ["LIVE_KV"], block_size=16, dtype="bfloat16",
           max_model_len=int(os.environ.get("LIVE_MAX_LEN", "4096")), max_num_seqs=int(os.environ.get("LIVE_BATCH", "64")),
-          gpu_memory_utilization=float(os.environ.get("LIVE_MEM", "0.3")), seed=0, enable_prefix_caching=False,
+          gpu_memory_utilization=float(os.environ.get("LIVE_MEM", "0.3")), seed=0,
+          enable_prefix_caching=os.environ.get("LIVE_SHARED_PREFIX", "0") == "1",
           **({"compilation_config": {"pass_config": {"fuse_rope_kvcache": True}, "splitting_ops": []}}  # (the pass wants an unsplit graph)
              if os.environ.get("LIVE_ROPE_FUSION", "0") == "1" else {}),
           attention_config={"backend": "FLASHINFER",
@@ -90,7 +91,14 @@ if AB:
 
 llm.apply_model(reinit)
 rng = random.Random(0)
-prompts = [{"prompt_token_ids": [rng.randrange(10, 31000) for _ in range(rng.randrange(300, 1500))]} for _ in range(8)]
+if os.environ.get("LIVE_SHARED_PREFIX", "0") == "1":
+    # 16 requests behind one 4200-token prefix: a first request computes (and caches) the prefix's
+    # blocks, the others then start from the same physical blocks -- a shared-prefix decode batch
+    common = [rng.randrange(10, 31000) for _ in range(4200)]
+    llm.generate([{"prompt_token_ids": common}], SamplingParams(temperature=0.0, max_tokens=1, detokenize=False), use_tqdm=False)
+    prompts = [{"prompt_token_ids": common + [rng.randrange(10, 31000) for _ in range(rng.randrange(20, 200))]} for _ in range(16)]
+else:
+    prompts = [{"prompt_token_ids": [rng.randrange(10, 31000) for _ in range(rng.randrange(300, 1500))]} for _ in range(8)]
 params = SamplingParams(temperature=0.0, max_tokens=12, logprobs=3, detokenize=False, ignore_eos=True)
 t0 = time.time()
 outs = llm.generate(prompts, params)
@@ -157,6 +165,17 @@ def run_engine(work: Path, kv: str, extra_env: dict, log: Path) -> dict:
     raise RuntimeError(f"the engine run failed (exit code {proc.returncode}); see {log}")
 
 
+def shared_prefix_summary(trace: Path) -> dict:
+    """Counts of the shared-prefix trace: candidate records (one per model step), how many found a
+    group, the group sizes seen, and layer calls of the grouped operator."""
+    records = [json.loads(line) for line in trace.read_text().splitlines()] if trace.exists() else []
+    candidates = [r for r in records if r["event"] == "shared_prefix_decode_candidate"]
+    sizes = sorted({tuple(r.get("group_sizes") or ()) for r in candidates if r.get("eligible")})
+    return {"shared_prefix_steps": len(candidates), "shared_prefix_steps_with_groups": sum(1 for r in candidates if r.get("eligible")),
+            "shared_prefix_group_sizes": [list(s) for s in sizes],
+            "shared_prefix_layer_calls": sum(1 for r in records if r["event"] == "l20_shared_prefix_paged_decode_run")}
+
+
 def main(argv: list[str] | None = None) -> int:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     parser.add_argument("--kv-cache-dtype", choices=["fp8", "auto"], default="fp8")
@@ -177,6 +196,10 @@ def main(argv: list[str] | None = None) -> int:
                              "fuse_rope_kvcache pass on in the hooked engine: rotary embedding + KV append then run "
                              "through l20_rope_and_cache, decode through the decode hook; implies --cuda-graphs "
                              "(the pass belongs to vLLM's compilation)")
+    parser.add_argument("--shared-prefix", action="store_true",
+                        help="16 requests behind one cached 4200-token prefix (prefix caching on in both engines); the "
+                             "hooked engine also gets VLLM_ENABLE_L20_SHARED_PREFIX_DECODE=1, so its decode steps find "
+                             "the group on the device and run the grouped shared-prefix operator; eager mode")
     parser.add_argument("--cuda-graphs", action="store_true",
                         help="let vLLM compile and record CUDA graphs (both engines), and keep the hook on while "
                              "it records (VLLM_L20_PAGED_CUDAGRAPH=1); hook hits are then counted at recording time")
@@ -234,6 +257,10 @@ def main(argv: list[str] | None = None) -> int:
     trace = work / f"trace_{kv}.jsonl"
     trace.unlink(missing_ok=True)
     graphs = {"LIVE_GRAPHS": "1"} if args.cuda_graphs else {}
+    prefix_trace = work / f"prefix_trace_{kv}.jsonl"
+    prefix_trace.unlink(missing_ok=True)
+    if args.shared_prefix:
+        graphs.update(LIVE_SHARED_PREFIX="1", LIVE_MAX_LEN="8192", LIVE_MEM="0.4")
     stock = run_engine(work, kv, graphs, work / f"{kv}_stock.log")
     switches = (
         {"VLLM_ENABLE_L20_FP8_PAGED_DECODE": "1", "VLLM_L20_FP8_PAGED_FORCE": "1", "VLLM_L20_FP8_PAGED_TRACE": str(trace)}
@@ -246,6 +273,8 @@ def main(argv: list[str] | None = None) -> int:
     rope_trace.unlink(missing_ok=True)
     if args.rope_hook:
         switches.update(LIVE_ROPE_FUSION="1", VLLM_L20_ROPE_KV_TRACE=str(rope_trace))
+    if args.shared_prefix:
+        switches.update(VLLM_ENABLE_L20_SHARED_PREFIX_DECODE="1", VLLM_L20_SHARED_PREFIX_DECODE_TRACE=str(prefix_trace))
     hooked = run_engine(work, kv, {**graphs, **switches}, work / f"{kv}_hook.log")
 
     hits = [json.loads(line) for line in trace.read_text().splitlines()] if trace.exists() else []
@@ -264,6 +293,7 @@ def main(argv: list[str] | None = None) -> int:
         "hook_hits_beyond_warmup": sum(1 for h in hits if h["max_seq_len"] > 64),
         "generated_steps_compared": compared, "same_token": agree, "max_abs_logprob_diff": worst,
         **({"rope_hook_hits": sum(1 for _ in rope_trace.open()) if rope_trace.exists() else 0} if args.rope_hook else {}),
+        **(shared_prefix_summary(prefix_trace) if args.shared_prefix else {}),
         "workdir": str(work),
     }))
     return 0 if hits and agree >= compared * 0.8 else 1
