@@ -355,6 +355,8 @@ class Case:
         if self.shared_prefix and args.grouped_prefix:
             self.groups, self.max_groups = cabi.group_shared_prefixes(w.block_table, seq_lens=w.seq_lens, min_batch=8,
                                                                       min_prefix_len=4096, max_groups=4)
+            # one host read per model step, as the decode hook does: are all requests in groups?
+            self.group_flags = cabi.PFD_FLAG_ALL_IN_GROUPS if int(self.groups[4].item()) == self.batch else 0
             self.prefix_bound = (w.prefix_len + 255) // 256 * 256  # an engine knows how long its cached prefixes can be
             self.suffix_bound = max(w.max_seq_len - 4096, 16)  # true for any group the grouping call above can find
             self.split = choose_suffix_split_size(self.batch, self.hkv, self.suffix_bound) if not args.split_size else self.split
@@ -400,7 +402,7 @@ class Case:
                 w.query, kc, vc, w.block_table, w.seq_lens, groups=self.groups, max_groups=self.max_groups,
                 max_prefix_len=self.prefix_bound, max_suffix_len=self.suffix_bound, k_scale=w.k_scale, v_scale=w.v_scale,
                 max_seq_len=w.max_seq_len,
-                split_size=self.split, output=self.out, workspace=self.ws)
+                split_size=self.split, output=self.out, workspace=self.ws, flags=self.group_flags)
             return
         if self.shared_prefix:
             cabi.shared_prefix_decode_fp8_e4m3(
@@ -747,7 +749,8 @@ def main() -> int:
                                               max_groups=case.max_groups, buffer=case.groups)
             res = ops.shared_prefix_decode_grouped_fp8_e4m3(
                 dq, kc, vc, dtable, dlens, ws[0], ws[1], ws[2], ws[3], w.k_scale, w.v_scale, w.max_seq_len, split, found,
-                max_prefix_len=case.prefix_bound, max_suffix_len=case.suffix_bound)
+                max_prefix_len=case.prefix_bound, max_suffix_len=case.suffix_bound,
+                all_in_groups=int(found.buffer[4].item()) == dq.shape[0])
         elif case.shared_prefix:
             res = case.spd.shared_paged_prefix_paged_suffix_gqa_decode_attention_fp8(
                 dq, kc, vc, dtable, dlens, w.prefix_len, k_scale=w.k_scale, v_scale=w.v_scale,

@@ -46,6 +46,13 @@ extern "C" {
                                      sequences (the warp whose piece arrives last does it), so the
                                      step is one launch and no merge kernel follows; measured slower
                                      on B200 than the two launches, for callers that want one node  */
+#define PFD_FLAG_ALL_IN_GROUPS 128u /* grouped shared-prefix decode: the caller has read word 4 of the
+                                     groups buffer and it equals the batch, i.e. no request is outside
+                                     the groups.  The split-KV pass over the short suffixes may then
+                                     run as small CTAs beside the dense prefix pass instead of behind
+                                     it.  Only a hint about speed: with a request in no group after
+                                     all the result is the same, that request's share just takes
+                                     longer                                                         */
 /*
  * Kernel selection.  For head_dim 128, at most 8 query heads per kv head, a TMA-describable
  * cache and a dense f32 workspace of at least pfd_balanced_workspace_rows() rows the balanced
@@ -396,6 +403,17 @@ int pfd_device_status(int32_t* status);
  * lasts well under one.  Process-wide, read at launch.
  */
 int pfd_set_wait_limit_ns(uint64_t limit_ns);
+
+/*
+ * Tuning: which form the split-KV pass of the shared-prefix entry points takes.  -1 (default):
+ * chosen per call -- two-warp CTAs that run on the same SMs WHILE the dense prefix pass runs when
+ * that pass is one wave of CTAs that nearly fills the GPU and the suffixes are short next to the
+ * prefix work (and, with a groups table, PFD_FLAG_ALL_IN_GROUPS is set), else the ordinary
+ * eight-warp CTAs, which start on the SMs the dense pass leaves free and take the rest after it;
+ * 0: always the latter; 1: always the former.
+ * Process-wide, read at launch; results do not depend on it.
+ */
+int pfd_set_suffix_form(int32_t form);
 
 /*
  * Self-test of that mechanism (it allocates one pinned host word while it runs): a one-warp

@@ -21,6 +21,7 @@ PFD_FLAG_PARTIAL_ONLY = 4
 PFD_FLAG_FIXED_SPLITS = 8
 PFD_FLAG_EARLY_METADATA = 32
 PFD_FLAG_SINGLE_LAUNCH = 64
+PFD_FLAG_ALL_IN_GROUPS = 128
 
 EXPORTS = (
     "pfd_paged_decode_fp8_e4m3_split_out",
@@ -45,6 +46,7 @@ EXPORTS = (
     "pfd_exchange_free",
     "pfd_device_status",
     "pfd_set_wait_limit_ns",
+    "pfd_set_suffix_form",
     "pfd_selftest_bounded_wait",
     "pfd_last_path",
     "pfd_launch_count",
@@ -423,6 +425,15 @@ def device_status() -> int:
     lib.pfd_device_status.restype = C.c_int
     _check(lib.pfd_device_status(C.byref(value)))
     return int(value.value)
+
+
+def set_suffix_form(form: int) -> None:
+    """Tuning: form of the split-KV pass behind a dense prefix pass (``pfd_set_suffix_form``):
+    -1 chosen per call, 0 always after that pass, 1 always beside it."""
+    lib = load()
+    lib.pfd_set_suffix_form.argtypes = [C.c_int32]
+    lib.pfd_set_suffix_form.restype = C.c_int
+    _check(lib.pfd_set_suffix_form(int(form)))
 
 
 def set_wait_limit_ns(limit_ns: int) -> None:

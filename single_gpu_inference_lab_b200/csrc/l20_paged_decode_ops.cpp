@@ -303,10 +303,12 @@ void shared_prefix_decode_grouped_fp8_e4m3(at::Tensor query, at::Tensor key_cach
                                            at::Tensor partial_max, at::Tensor partial_sum, at::Tensor output,
                                            at::Tensor k_scale, at::Tensor v_scale, double sm_scale,
                                            int64_t max_seq_len, int64_t split_size, at::Tensor groups,
-                                           int64_t max_groups, int64_t max_prefix_len, int64_t max_suffix_len) {
+                                           int64_t max_groups, int64_t max_prefix_len, int64_t max_suffix_len,
+                                           bool all_in_groups) {
   run_decode(query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max, partial_sum,
-             output, c10::nullopt, 1.0, 1.0, k_scale, v_scale, sm_scale, max_seq_len, split_size, 0, 0,
-             c10::nullopt, 0, false, c10::nullopt, false, groups, max_groups, max_prefix_len, max_suffix_len);
+             output, c10::nullopt, 1.0, 1.0, k_scale, v_scale, sm_scale, max_seq_len, split_size, 0,
+             all_in_groups ? PFD_FLAG_ALL_IN_GROUPS : 0, c10::nullopt, 0, false, c10::nullopt, false, groups, max_groups,
+             max_prefix_len, max_suffix_len);
 }
 
 // Rotary embedding of the new tokens' query and key (in place) + append of key / value to the
@@ -499,7 +501,7 @@ TORCH_LIBRARY(l20_stack, module) {
       "Tensor query, Tensor key_cache, Tensor value_cache, Tensor block_table, Tensor seq_lens, "
       "Tensor(a!) partial_output, Tensor(b!) partial_max, Tensor(c!) partial_sum, Tensor(d!) output, "
       "Tensor k_scale, Tensor v_scale, float sm_scale, int max_seq_len, int split_size, Tensor groups, "
-      "int max_groups, int max_prefix_len, int max_suffix_len) -> ()");
+      "int max_groups, int max_prefix_len, int max_suffix_len, bool all_in_groups=False) -> ()");
   module.def(
       "rope_and_cache(Tensor(a!) query, Tensor(b!) key, Tensor value, Tensor positions, Tensor cos_sin_cache, "
       "bool is_neox, Tensor(c!) key_cache, Tensor(d!) value_cache, Tensor slot_mapping, "

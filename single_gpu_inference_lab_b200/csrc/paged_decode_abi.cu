@@ -97,13 +97,17 @@ int status_pointer(int32_t** out) {
 }
 
 // First launch of a kernel that needs more than the default dynamic shared memory, per device.
+// `whole_sm`: also ask for the largest shared-memory carve-out, so that a CTA of another kernel
+// can use what this one leaves over (the carve-out is otherwise sized for this kernel alone).
 template <typename Kernel>
-int configure_smem(std::atomic<bool>* done, Kernel kernel, int smem) {
+int configure_smem(std::atomic<bool>* done, Kernel kernel, int smem, bool whole_sm = false) {
   std::atomic<bool>& flag = done[t_device->dev];
   if (flag.load(std::memory_order_acquire)) return PFD_OK;
   std::lock_guard<std::mutex> lock(g_state_mutex);
   if (!flag.load(std::memory_order_relaxed)) {
-    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e == cudaSuccess && whole_sm)
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "cudaFuncSetAttribute failed: %s", cudaGetErrorString(e));
     flag.store(true, std::memory_order_release);
   }
@@ -222,7 +226,9 @@ bool tma_eligible(const pfd_decode_args& a) {
          head_is_dim1(a.k_stride_token, a.k_stride_head) == head_is_dim1(a.v_stride_token, a.v_stride_head);
 }
 
-template <bool QBF16>
+// kWarpsT = 2 behind the dense prefix pass: a CTA of two warps, 128 registers and 34 KB fits on an
+// SM beside a prefix CTA, so the two passes run side by side instead of one after the other.
+template <bool QBF16, int kWarpsT = kWarps>
 int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, dim3 grid, cudaStream_t stream) {
   CUtensorMap mk, mv;
   if (int rc = get_tensor_map(a.key_cache, a.k_stride_page, a.k_stride_token, a.k_stride_head, a.num_pages,
@@ -235,17 +241,17 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
   tp.head_is_dim1 = head_is_dim1(a.k_stride_token, a.k_stride_head) ? 1 : 0;
   if (int rc = status_pointer(&tp.status)) return rc;
   tp.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
-  auto kernel = pfd::paged_decode_fp8_partial_tma_kernel<QBF16, kWarps, kStages>;
-  constexpr int smem = 1024 + kWarps * kStages * 8192 + kWarps * kStages * 8 + 2 * kWarps * 16 * 4;
-  static std::atomic<bool> configured[kMaxDevices];
-  if (int rc = configure_smem(configured, kernel, smem)) return rc;
+  auto kernel = pfd::paged_decode_fp8_partial_tma_kernel<QBF16, kWarpsT, kStages>;
+  constexpr int smem = 1024 + kWarpsT * kStages * 8192 + kWarpsT * kStages * 8 + 2 * kWarpsT * 16 * 4;
+  static std::atomic<bool> configured[kMaxDevices];  // (one array per instantiation)
+  if (int rc = configure_smem(configured, kernel, smem, kWarpsT != kWarps)) return rc;
   {
     // Programmatic dependent launch.  Behind the dense prefix pass: independent work, it runs
     // beside that pass.  Otherwise: the CTAs may become resident while the preceding kernel of
     // the stream drains; the kernel waits for that kernel's completion before its first access.
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(kWarps * 32);
+    cfg.blockDim = dim3(kWarpsT * 32);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -257,6 +263,34 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
     if (e != cudaSuccess) return fail(PFD_ERR_CUDA, "partial kernel (TMA) launch failed: %s", cudaGetErrorString(e));
   }
   return check_launch("partial kernel (TMA)");
+}
+
+// Behind the dense prefix pass the split-KV pass has two forms.  Two-warp CTAs (166 registers,
+// 34 KB) fit BESIDE a CTA of the slim dense kernel -- one per SM there, six on an SM that pass
+// leaves free -- and run while it runs.  Otherwise the eight-warp CTAs of the ordinary pass are
+// launched behind the dense pass; as its programmatic dependents they already start on whatever
+// SMs that pass leaves free, so the small form only pays where it leaves few: when its grid is
+// one wave that nearly fills the GPU.  And two warps per CTA are few, so the suffixes must be
+// short next to the prefix work.  Measured in us per step (behind / beside), 16 query and 2 KV
+// heads, prefix 4096 unless noted, suffixes up to 511:
+//   batch 64 (128 dense CTAs), splits of 128: 19.6 / 18.4   splits of 256: 20.7 / 19.1
+//   batch 32 (64 CTAs): 15.6 / 16.5   batch 16: 15.3 / 15.7   batch 128 (256 CTAs): 35.2 / 35.7
+//   batch 256: 61.9 / 65.2   batch 64, prefix 3072 of the 4096 (suffixes up to 1535): 23.9 / 30.9
+// A request in no group attends its whole context in as many splits as the others their suffix,
+// which two warps would take several times longer over: with a groups table the small form
+// needs the caller's word that every request is in a group (PFD_FLAG_ALL_IN_GROUPS).
+std::atomic<int> g_suffix_form{-1};  // tuning: -1 choose, 0 always behind, 1 always beside
+bool suffix_beside_prefix(const pfd_decode_args& a, int prefix_chunks, int num_splits, bool groups_table) {
+  if (prefix_chunks <= 0 || a.head_dim != 128 || !tma_eligible(a)) return false;
+  const int forced = g_suffix_form.load(std::memory_order_relaxed);
+  if (forced >= 0) return forced == 1;
+  if (groups_table && !(a.flags & PFD_FLAG_ALL_IN_GROUPS)) return false;
+  const int group = a.num_q_heads / a.num_kv_heads;
+  const int64_t dense_ctas = (int64_t)prefix_chunks * a.num_kv_heads *
+                             (((int64_t)a.batch * group + pfd::kPrefixRows - 1) / pfd::kPrefixRows);
+  const int sms = t_device->sms;
+  if (dense_ctas > sms || 10 * dense_ctas < 7 * sms) return false;
+  return (int64_t)num_splits * a.num_kv_heads * a.batch * a.split_size <= 640 * dense_ctas;
 }
 
 // ---- balanced persistent kernel -------------------------------------------------------------
@@ -385,7 +419,10 @@ int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num
   const dim3 grid(num_splits, a.num_kv_heads, a.batch);
   if (D == 128 && tma_eligible(a)) {
     g_last_path = PFD_PATH_FIXED_TMA;
-    if (int rc = launch_partial_tma<QBF16>(a, kp, grid, stream)) return rc;
+    if (int rc = suffix_beside_prefix(a, kp.slot_offset, num_splits, kp.row_kv_start != nullptr)
+                     ? launch_partial_tma<QBF16, 2>(a, kp, grid, stream)
+                     : launch_partial_tma<QBF16>(a, kp, grid, stream))
+      return rc;
   } else {
     g_last_path = PFD_PATH_FIXED_LDG;
     pfd::paged_decode_fp8_partial_ldg_kernel<D, QBF16, kWarps><<<grid, kWarps * 32, 0, stream>>>(kp);
@@ -569,8 +606,8 @@ int decode_impl(const pfd_decode_args* args, int slot_offset, const GroupedRows*
 }
 
 template <bool QBF16>
-int launch_prefix(const pfd_decode_args& a, int prefix_len, int chunks, const int32_t* groups = nullptr,
-                  int max_groups = 0) {
+int launch_prefix(const pfd_decode_args& a, int prefix_len, int chunks, bool suffix_beside,
+                  const int32_t* groups = nullptr, int max_groups = 0) {
   pfd::KernelParams kp{};
   kp.query = a.query;
   kp.key_cache = static_cast<const uint8_t*>(a.key_cache);
@@ -601,14 +638,23 @@ int launch_prefix(const pfd_decode_args& a, int prefix_len, int chunks, const in
   if (int rc = status_pointer(&pp.status)) return rc;
   pp.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
   pp.phase_times = g_phase_times;
-  auto kernel = pfd::shared_prefix_dense_kernel<QBF16>;
+  // the slim instantiation (80 registers, whole-SM carve-out) leaves room for the suffix pass's
+  // two-warp CTAs on the same SM; it is 1 us slower by itself, so the other one runs otherwise
+  auto kernel = suffix_beside ? pfd::shared_prefix_dense_kernel<QBF16, true> : pfd::shared_prefix_dense_kernel<QBF16, false>;
   constexpr int smem = 1024 + 160 * 1024 + 32 + 2 * 4 * 128 * 4;
-  static std::atomic<bool> configured[kMaxDevices];
-  if (int rc = configure_smem(configured, kernel, smem)) return rc;
+  static std::atomic<bool> configured[2][kMaxDevices];
+  if (int rc = configure_smem(configured[suffix_beside ? 1 : 0], kernel, smem, suffix_beside)) return rc;
   const int rows = a.batch * kp.group;
-  // grouped: every group's last 128-row tile may be ragged, hence one more tile slot per group
-  const dim3 grid = groups == nullptr ? dim3(chunks, (rows + pfd::kPrefixRows - 1) / pfd::kPrefixRows, a.num_kv_heads)
-                                      : dim3(chunks * a.num_kv_heads, rows / pfd::kPrefixRows + max_groups, 1);
+  const int tiles = (rows + pfd::kPrefixRows - 1) / pfd::kPrefixRows;
+  // Grouped: every group's last 128-row tile may be ragged, so there can be up to one more tile
+  // per group than the rows fill.  The kernel's CTAs take tile slots in turns, so any grid is
+  // right; slots beyond `tiles` are added only while the grid stays within one CTA per SM, where
+  // a CTA that finds its slot empty costs nothing.  (Beyond that every idle CTA waits for a whole
+  // SM's shared memory, and the suffix pass, a programmatic dependent, starts only after the
+  // last of them: 6 us late with 128 idle CTAs on the batch of 64.)
+  const int spare = std::max(0, std::min(max_groups, t_device->sms / std::max(chunks * a.num_kv_heads, 1) - tiles));
+  const dim3 grid = groups == nullptr ? dim3(chunks, tiles, a.num_kv_heads)
+                                      : dim3(chunks * a.num_kv_heads, tiles + spare, 1);
   kernel<<<grid, 512, smem, static_cast<cudaStream_t>(a.stream)>>>(kp, pp);
   return check_launch("shared-prefix dense kernel");
 }
@@ -797,7 +843,10 @@ int pfd_shared_prefix_decode_fp8_e4m3(const pfd_decode_args* args, int32_t prefi
                   chunks + ns);
   }
   if (int rc = enter_call()) return rc;
-  if (int rc = bf16 ? launch_prefix<true>(a, prefix_len, chunks) : launch_prefix<false>(a, prefix_len, chunks)) return rc;
+  const int span = a.max_seq_len - prefix_len;
+  const bool beside = suffix_beside_prefix(a, chunks, span > 0 ? (span + a.split_size - 1) / a.split_size : 1, false);
+  if (int rc = bf16 ? launch_prefix<true>(a, prefix_len, chunks, beside) : launch_prefix<false>(a, prefix_len, chunks, beside))
+    return rc;
   return decode_impl(&a, chunks);
 }
 
@@ -855,8 +904,10 @@ int pfd_shared_prefix_decode_grouped_fp8_e4m3(const pfd_decode_args* args, const
   a.plan = nullptr;
   if (int rc = enter_call()) return rc;
   const int32_t* g = static_cast<const int32_t*>(groups);
+  const bool beside = suffix_beside_prefix(a, chunks, ns, true);
   if (chunks > 0)
-    if (int rc = bf16 ? launch_prefix<true>(a, cap, chunks, g, max_groups) : launch_prefix<false>(a, cap, chunks, g, max_groups))
+    if (int rc = bf16 ? launch_prefix<true>(a, cap, chunks, beside, g, max_groups)
+                      : launch_prefix<false>(a, cap, chunks, beside, g, max_groups))
       return rc;
   GroupedRows rows;
   rows.row_kv_start = g + pfd::groups_row_prefix_off();
@@ -1014,6 +1065,12 @@ int pfd_debug_phase_times(void* device_buffer) {
   return PFD_OK;
 }
 #endif
+
+int pfd_set_suffix_form(int32_t form) {
+  if (form < -1 || form > 1) return fail(PFD_ERR_INVALID, "form must be -1, 0 or 1");
+  g_suffix_form.store(form, std::memory_order_relaxed);
+  return PFD_OK;
+}
 
 int pfd_set_wait_limit_ns(uint64_t limit_ns) {
   if (limit_ns == 0) return fail(PFD_ERR_INVALID, "the wait limit must be positive");

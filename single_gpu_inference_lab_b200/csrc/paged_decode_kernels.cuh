@@ -711,6 +711,7 @@ __device__ __forceinline__ void dbg_mark(int slot, int k, bool leader) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     g_dbg_stamps[(size_t)slot * 8 + k] = t;
+    if (k == 0) { unsigned r; asm volatile("mov.u32 %0, %%smid;" : "=r"(r)); g_dbg_stamps[(size_t)slot * 8 + 7] = r + 1; }
   }
 #else
   (void)slot; (void)k; (void)leader;
@@ -752,7 +753,7 @@ __global__ void bounded_wait_selftest_kernel(int32_t* status, unsigned long long
 // step give four independent QK^T accumulator chains and halve the per-token cost of the
 // softmax bookkeeping (shuffles, rescale).
 template <bool QBF16, int NWARPS, int NSTAGE>
-__global__ void __launch_bounds__(NWARPS * 32)
+__global__ void __launch_bounds__(NWARPS * 32, NWARPS == 2 ? 6 : 1)  // two warps: at most 128 registers (see the dense prefix pass)
 paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
                                     const __grid_constant__ CUtensorMap tmap_k,
                                     const __grid_constant__ CUtensorMap tmap_v) {
@@ -795,8 +796,12 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   if (p.row_kv_start != nullptr && split == 0 && kvh == 0 && threadIdx.x == 0 &&
       seq_len - kv0 > (int)gridDim.x * split_sz)
     atomicExch(tp.status, kErrSuffixBound);
+  // Behind the dense prefix pass (slot_offset > 0) this grid reads nothing of that pass, but it must
+  // not COMPLETE before it: the merge kernel waits for this grid only.  One CTA that waits before
+  // it exits is enough for that, and the others give their place on the SM to the next CTA.
+  const bool waits_at_exit = p.slot_offset == 0 || (blockIdx.x | blockIdx.y | blockIdx.z) == 0;
   if (lo >= hi) {
-    pdl_wait();
+    if (waits_at_exit) pdl_wait();
     if (split == 0 && gridDim.x == 1 && p.direct_out) write_empty_rows<D>(p, b, kvh);
     return;
   }
@@ -951,10 +956,8 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
   __syncthreads();  // every warp is done with its ring: sm_o may alias it
   cta_merge_and_store<D, QBF16, NWARPS>(st, p, b, kvh, split, nsplits_seq, vs, sm_m, sm_l, sm_o);
   dbg_mark(dbg_slot, 1, threadIdx.x == 0);
-  // When this grid was launched as a programmatic dependent of the dense prefix pass (it never
-  // reads that pass's results, so it starts right away), it must not complete before that pass:
-  // the merge kernel behind it waits for *this* grid only.  A no-op for an ordinary launch.
-  pdl_wait();
+  // (see waits_at_exit; a no-op for an ordinary launch, which has waited before its first access)
+  if (waits_at_exit) pdl_wait();
   dbg_mark(dbg_slot, 2, threadIdx.x == 0);
 }
 

@@ -167,6 +167,7 @@ __device__ __forceinline__ void prefix_mark(const PrefixParams& pp, int k) {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     const size_t cta = blockIdx.x + gridDim.x * (blockIdx.y + (size_t)gridDim.y * blockIdx.z);
     pp.phase_times[cta * 8 + k] = t;
+    if (k == 0) { unsigned r; asm volatile("mov.u32 %0, %%smid;" : "=r"(r)); pp.phase_times[cta * 8 + 7] = r + 1; }
   }
 #else
   (void)pp; (void)k;
@@ -178,8 +179,15 @@ __device__ __forceinline__ void prefix_mark(const PrefixParams& pp, int k) {
 // Warp w works on TMEM lanes (= rows) 32 * (w % 4) .. +31, the only ones it may address, and on
 // column group w / 4 of whatever is being read: with 16 warps the staging, the softmax and the
 // stores around the two MMAs are spread over all four schedulers four warps deep.
-template <bool QBF16>
-__global__ void __launch_bounds__(512, 1)
+// SLIM caps the kernel at 80 registers per thread (126 otherwise; the cap costs about 1 us of the
+// pass).  Registers are handed out per SM sub-partition (16 K each): four warps of this CTA at 80
+// registers leave 6144 there, one warp of up to 192 registers -- the two-warp instantiation of
+// the suffix kernel uses 166 -- and with the largest shared-memory carve-out the 34 KB of such a
+// CTA fit beside the 166 KB of this one: the suffix pass then runs on the same SMs WHILE this
+// pass runs instead of after it.  (At 126 registers nothing above 32 registers per thread fits
+// beside this CTA; without the carve-out request nothing at all, whatever the registers.)
+template <bool QBF16, bool SLIM>
+__global__ void __maxnreg__(SLIM ? 80 : 128)
 shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   constexpr int D = 128;
   constexpr uint32_t kQBytes = kPrefixRows * D * 2;         // 32 KiB: 2 k-blocks of [128][64]
@@ -192,29 +200,6 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   const int row = 32 * qd + lane;           // this thread's (request, head) row of the tile
   pdl_launch_dependents();
   prefix_mark(pp, 0);
-  // Which requests, which prefix: the whole batch and pp.prefix_len, or one group of the table.
-  int prefix_len = pp.prefix_len, n_req = pp.batch, page_row = 0;
-  const int32_t* req_list = nullptr;  // request index of the group's i-th member
-  if (pp.groups != nullptr) {
-    const int B = pp.groups_batch, G = pp.max_groups;
-    const int32_t* offs = pp.groups + groups_offsets_off(B);
-    const int n_groups = min(__ldg(pp.groups + 3), G);
-    int slot = blockIdx.y, g = 0;
-    for (; g < n_groups; ++g) {
-      const int tiles = ((__ldg(offs + g + 1) - __ldg(offs + g)) * p.group + kPrefixRows - 1) / kPrefixRows;
-      if (slot < tiles) break;
-      slot -= tiles;
-    }
-    if (g >= n_groups) return;
-    mtile = slot;
-    chunk = blockIdx.x / p.num_kv_heads;
-    kvh = blockIdx.x % p.num_kv_heads;
-    prefix_len = min(__ldg(pp.groups + groups_prefix_off(B, G) + g) & ~15, pp.prefix_len);  // (pp.prefix_len: the cap)
-    if (chunk * kPrefixChunk >= prefix_len) return;
-    req_list = pp.groups + groups_rows_off(B, G) + __ldg(offs + g);
-    n_req = __ldg(offs + g + 1) - __ldg(offs + g);
-    page_row = __ldg(req_list);  // any member's block-table row names the prefix pages
-  }
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -225,192 +210,256 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
   volatile uint32_t* tslot_ptr = reinterpret_cast<volatile uint32_t*>(gen + kQBytes + kKBytes + kVBytes + 16);
   float* red = reinterpret_cast<float*>(gen + kQBytes + kKBytes + kVBytes + 32);  // [2][4][128] row partials
 
-  if (t == 0) {
-    mbar_init(bars, 1);
-    mbar_init(bars + 8, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 0) tmem_alloc(tslot, 512);
-
-  const int tok_lo = chunk * kPrefixChunk;
-  const int tok_hi = min(tok_lo + kPrefixChunk, prefix_len);
-
-  // ---- K and V chunk: thread t stages half a token row (64 head-dim elements) of token t / 2
-  const int tr = t >> 1, dh = t & 1;
-  uint4 kin[4], vin[4];
-  {
-    const int tok = tok_lo + tr;
-    const bool live = tok < tok_hi;
-    int64_t phys = 0;
-    if (live) phys = page_of(p.block_table, p.bt_stride_b, page_row, tok / kPage);
-    const uint8_t* krow = p.key_cache + phys * p.k_stride_page + (int64_t)(tok % kPage) * p.k_stride_token + (int64_t)kvh * p.k_stride_head;
-    const uint8_t* vrow = p.value_cache + phys * p.v_stride_page + (int64_t)(tok % kPage) * p.v_stride_token + (int64_t)kvh * p.v_stride_head;
+  // Grouped form: the grid has as many tile slots as the rows of the batch fill; the groups'
+  // ragged last tiles can make a few more, which the CTAs of the first slots take in a second
+  // turn (tiles done so far = `turns`, the parity the two mbarriers are waited on).  The other
+  // form has one tile per CTA.
+  int turns = 0;
+  uint32_t tmem = 0;
+  bool ok = true;
+  for (int slot0 = blockIdx.y;; slot0 += gridDim.y) {
+    // Which requests, which prefix: the whole batch and pp.prefix_len, or one group of the table.
+    int prefix_len = pp.prefix_len, n_req = pp.batch, page_row = 0;
+    const int32_t* req_list = nullptr;  // request index of the group's i-th member
+    if (pp.groups == nullptr) {
+      if (turns > 0) break;
+    } else {
+      const int B = pp.groups_batch, G = pp.max_groups;
+      const int32_t* offs = pp.groups + groups_offsets_off(B);
+      // Group of tile slot `slot0`.  Up to 8 groups: all offsets and prefix lengths are fetched at
+      // once (offsets of unused groups equal the total, i.e. no tiles), so the lookup costs one
+      // round trip to L2 instead of one per dependent step.
+      constexpr int kFast = 8;
+      int slot = slot0, g = 0, first = 0, members = 0, group_prefix = 0;
+      if (G <= kFast) {
+        int o[kFast + 1], pl[kFast];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      kin[c] = vin[c] = make_uint4(0u, 0u, 0u, 0u);
-      if (live) {
-        kin[c] = __ldg(reinterpret_cast<const uint4*>(krow) + 4 * dh + c);
-        vin[c] = __ldg(reinterpret_cast<const uint4*>(vrow) + 4 * dh + c);
+        for (int i = 0; i <= kFast; ++i) o[i] = __ldg(offs + min(i, G));
+#pragma unroll
+        for (int i = 0; i < kFast; ++i) pl[i] = __ldg(pp.groups + groups_prefix_off(B, G) + min(i, G - 1));
+        bool found = false;
+#pragma unroll
+        for (int i = 0; i < kFast; ++i) {
+          const int tiles = ((o[i + 1] - o[i]) * p.group + kPrefixRows - 1) / kPrefixRows;
+          if (!found && slot < tiles) { found = true; g = i; first = o[i]; members = o[i + 1] - o[i]; group_prefix = pl[i]; }
+          if (!found) slot -= tiles;
+        }
+        if (!found) break;
+      } else {
+        const int n_groups = min(__ldg(pp.groups + 3), G);
+        for (; g < n_groups; ++g) {
+          const int tiles = ((__ldg(offs + g + 1) - __ldg(offs + g)) * p.group + kPrefixRows - 1) / kPrefixRows;
+          if (slot < tiles) break;
+          slot -= tiles;
+        }
+        if (g >= n_groups) break;
+        first = __ldg(offs + g);
+        members = __ldg(offs + g + 1) - first;
+        group_prefix = __ldg(pp.groups + groups_prefix_off(B, G) + g);
       }
+      mtile = slot;
+      chunk = blockIdx.x / p.num_kv_heads;
+      kvh = blockIdx.x % p.num_kv_heads;
+      prefix_len = min(group_prefix & ~15, pp.prefix_len);  // (pp.prefix_len: the cap)
+      if (chunk * kPrefixChunk >= prefix_len) continue;
+      req_list = pp.groups + groups_rows_off(B, G) + first;
+      n_req = members;
+      page_row = __ldg(req_list);  // any member's block-table row names the prefix pages
     }
-  }
-  // ---- Q tile: thread (row, cg) stages 32 of the row's 128 elements
-  const int row_g = mtile * kPrefixRows + row;
-  const int head = row_g % p.group;
-  const bool row_live = row_g / p.group < n_req;
-  const int b = !row_live ? 0 : (req_list != nullptr ? __ldg(req_list + row_g / p.group) : row_g / p.group);
-  {
-    const uint16_t* q = reinterpret_cast<const uint16_t*>(p.query) + (int64_t)(row_live ? b : 0) * p.q_stride_b +
-                        (int64_t)(kvh * p.group + head) * p.q_stride_h;
+
+    if (turns == 0) {
+      if (t == 0) {
+        mbar_init(bars, 1);
+        mbar_init(bars + 8, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+      }
+      if (warp == 0) tmem_alloc(tslot, 512);
+    }
+    const uint32_t parity = turns & 1;
+    const int tok_lo = chunk * kPrefixChunk;
+    const int tok_hi = min(tok_lo + kPrefixChunk, prefix_len);
+
+    // ---- K and V chunk: thread t stages half a token row (64 head-dim elements) of token t / 2
+    const int tr = t >> 1, dh = t & 1;
+    uint4 kin[4], vin[4];
+    {
+      const int tok = tok_lo + tr;
+      const bool live = tok < tok_hi;
+      int64_t phys = 0;
+      if (live) phys = page_of(p.block_table, p.bt_stride_b, page_row, tok / kPage);
+      const uint8_t* krow = p.key_cache + phys * p.k_stride_page + (int64_t)(tok % kPage) * p.k_stride_token + (int64_t)kvh * p.k_stride_head;
+      const uint8_t* vrow = p.value_cache + phys * p.v_stride_page + (int64_t)(tok % kPage) * p.v_stride_token + (int64_t)kvh * p.v_stride_head;
 #pragma unroll
-    for (int cc = 0; cc < 4; ++cc) {
-      const int c = 4 * cg + cc;
-      uint4 x = make_uint4(0u, 0u, 0u, 0u);
-      if (row_live) x = __ldg(reinterpret_cast<const uint4*>(q) + c);
-      if constexpr (QBF16) {
-        uint32_t* w = reinterpret_cast<uint32_t*>(&x);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
-          w[e] = pack_f16x2(__bfloat162float(v.x), __bfloat162float(v.y));
+      for (int c = 0; c < 4; ++c) {
+        kin[c] = vin[c] = make_uint4(0u, 0u, 0u, 0u);
+        if (live) {
+          kin[c] = __ldg(reinterpret_cast<const uint4*>(krow) + 4 * dh + c);
+          vin[c] = __ldg(reinterpret_cast<const uint4*>(vrow) + 4 * dh + c);
         }
       }
-      sts_16(sq + (c >> 3) * (kPrefixRows * 128) + sw128_chunk(row, c & 7), x);
     }
-  }
+    // ---- Q tile: thread (row, cg) stages 32 of the row's 128 elements
+    const int row_g = mtile * kPrefixRows + row;
+    const int head = row_g % p.group;
+    const bool row_live = row_g / p.group < n_req;
+    const int b = !row_live ? 0 : (req_list != nullptr ? __ldg(req_list + row_g / p.group) : row_g / p.group);
+    {
+      const uint16_t* q = reinterpret_cast<const uint16_t*>(p.query) + (int64_t)(row_live ? b : 0) * p.q_stride_b +
+                          (int64_t)(kvh * p.group + head) * p.q_stride_h;
 #pragma unroll
-  for (int cc = 0; cc < 4; ++cc) {  // 16 bytes = 16 head-dim elements at a time
-    const int c = 4 * dh + cc;
-    uint4 lo, hi;
-    cvt16_e4m3_f16(kin[cc], lo, hi);
-    // K: row = token, k = d; elements 16c .. 16c+15 are chunks 2c, 2c+1 of k-block (c / 4)
-    const uint32_t kb = sk + (c >> 2) * (kPrefixChunk * 128);
-    sts_16(kb + sw128_chunk(tr, (2 * c) & 7), lo);
-    sts_16(kb + sw128_chunk(tr, (2 * c + 1) & 7), hi);
-    // V: the same token-major rows (two blocks of 64 head-dim elements); the second MMA reads
-    // them as an MN-major operand, so no transposition is needed
-    cvt16_e4m3_f16(vin[cc], lo, hi);
-    const uint32_t vb = sv + (c >> 2) * (kPrefixChunk * 128);
-    sts_16(vb + sw128_chunk(tr, (2 * c) & 7), lo);
-    sts_16(vb + sw128_chunk(tr, (2 * c + 1) & 7), hi);
-  }
-  // generic-proxy writes -> visible to the tensor core's (async proxy) reads
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = *tslot_ptr;
-  prefix_mark(pp, 1);  // operands staged
-
-  // ---- S = Q K^T : M 128, N 256, K 128 = 2 k-blocks x 4 slices of 16
-  if (t == 0) {
-    const uint32_t idesc = umma_idesc_f16(128, 256);
+      for (int cc = 0; cc < 4; ++cc) {
+        const int c = 4 * cg + cc;
+        uint4 x = make_uint4(0u, 0u, 0u, 0u);
+        if (row_live) x = __ldg(reinterpret_cast<const uint4*>(q) + c);
+        if constexpr (QBF16) {
+          uint32_t* w = reinterpret_cast<uint32_t*>(&x);
 #pragma unroll
-    for (int kb = 0; kb < 2; ++kb)
-#pragma unroll
-      for (int s = 0; s < 4; ++s)
-        umma_f16(tmem, umma_desc_k_sw128(sq + kb * (kPrefixRows * 128) + 32 * s),
-                 umma_desc_k_sw128(sk + kb * (kPrefixChunk * 128) + 32 * s), idesc, (kb | s) ? 1u : 0u);
-    umma_commit(bars);
-  }
-  bool ok = mbar_wait_bounded(bars, 0, pp.wait_limit_ns);
-  tc_fence_after_sync();
-  prefix_mark(pp, 2);  // S ready
-
-  // ---- softmax: thread (row, cg) holds the row's scores of tokens [64 cg, 64 cg + 64)
-  const float ks = p.k_scale_ph ? __ldg(p.k_scale_ph + kvh) : p.k_scale;
-  const float vs = p.v_scale_ph ? __ldg(p.v_scale_ph + kvh) : p.v_scale;
-  const float scale_log2 = ks * p.sm_scale * kLog2e;
-  const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);  // this warp's 32 TMEM lanes
-  const int n_live = tok_hi - tok_lo;
-  float sc[64];
-  {
-    uint32_t r0[32], r1[32];
-    tmem_ld32_nowait(lane_addr + 64 * cg, r0);
-    tmem_ld32_nowait(lane_addr + 64 * cg + 32, r1);
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int e = 0; e < 32; ++e) { sc[e] = __uint_as_float(r0[e]); sc[32 + e] = __uint_as_float(r1[e]); }
-  }
-  float mx = -INFINITY;
-#pragma unroll
-  for (int e = 0; e < 64; ++e)
-    if (64 * cg + e < n_live) mx = fmaxf(mx, sc[e]);
-  red[cg * 128 + row] = mx;
-  __syncthreads();
-  mx = fmaxf(fmaxf(red[row], red[128 + row]), fmaxf(red[256 + row], red[384 + row])) * scale_log2;  // scale > 0
-  float lsum = 0.f;
-#pragma unroll
-  for (int e8 = 0; e8 < 8; ++e8) {
-    uint4 out;
-    uint32_t* w = reinterpret_cast<uint32_t*>(&out);
-#pragma unroll
-    for (int e = 0; e < 8; e += 2) {
-      const int i0 = 8 * e8 + e;
-      const float p0 = (64 * cg + i0 < n_live) ? exp2f(sc[i0] * scale_log2 - mx) : 0.f;
-      const float p1 = (64 * cg + i0 + 1 < n_live) ? exp2f(sc[i0 + 1] * scale_log2 - mx) : 0.f;
-      lsum += p0 + p1;
-      w[e >> 1] = pack_f16x2(p0, p1);
+          for (int e = 0; e < 4; ++e) {
+            const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
+            w[e] = pack_f16x2(__bfloat162float(v.x), __bfloat162float(v.y));
+          }
+        }
+        sts_16(sq + (c >> 3) * (kPrefixRows * 128) + sw128_chunk(row, c & 7), x);
+      }
     }
-    // P: row = row, k = token 64 cg + 8 e8 ..: chunk e8 of k-block cg
-    sts_16(sk + cg * (kPrefixRows * 128) + sw128_chunk(row, e8), out);
-  }
-  red[512 + cg * 128 + row] = lsum;
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  lsum = red[512 + row] + red[640 + row] + red[768 + row] + red[896 + row];
-
-  prefix_mark(pp, 3);  // P written
-  // ---- O = P V : M 128, N 128, K 256 = 16 slices of 16 tokens.  A = P (K-major: 4 k-blocks of
-  // 64 tokens), B = V (MN-major: 16 tokens = two 1 KiB atoms, d blocks 32 KiB apart)
-  if (t == 0) {
-    const uint32_t idesc = umma_idesc_f16(128, 128, true);
 #pragma unroll
-    for (int s = 0; s < 16; ++s)
-      umma_f16(tmem + 256, umma_desc_k_sw128(sk + (s >> 2) * (kPrefixRows * 128) + 32 * (s & 3)),
-               umma_desc_mn_sw128(sv + 2048 * s, kPrefixChunk * 128), idesc, s ? 1u : 0u);
-    umma_commit(bars + 8);
-  }
-  ok = mbar_wait_bounded(bars + 8, 0, pp.wait_limit_ns) && ok;
-  tc_fence_after_sync();
-  prefix_mark(pp, 4);  // O ready
-
-  // ---- (o, m, l) of the rows into slot `chunk` of the workspace.  Thread (row, cg) parks
-  // columns [32 cg, +32) of its row in shared memory (16-byte chunks XOR-swizzled by the row);
-  // then every warp writes whole rows, 32 lanes x 16 bytes = one contiguous 512-byte row per store.
-  {
-    float v[32];
-    tmem_ld32(lane_addr + 256 + 32 * cg, v);
-#pragma unroll
-    for (int c = 0; c < 8; ++c)
-      sts_16(sk + row * 512 + (((8 * cg + c) ^ (row & 31)) << 4),
-             make_uint4(__float_as_uint(v[4 * c] * vs), __float_as_uint(v[4 * c + 1] * vs),
-                        __float_as_uint(v[4 * c + 2] * vs), __float_as_uint(v[4 * c + 3] * vs)));
-    if (row_live && cg == 0) {
-      const int64_t pidx = (int64_t)b * p.partial_stride_b + (int64_t)(kvh * p.group + head) * p.partial_stride_h +
-                           (int64_t)chunk * p.partial_stride_s;
-      p.partial_max[pidx] = mx * kLn2;
-      p.partial_sum[pidx] = lsum;
+    for (int cc = 0; cc < 4; ++cc) {  // 16 bytes = 16 head-dim elements at a time
+      const int c = 4 * dh + cc;
+      uint4 lo, hi;
+      cvt16_e4m3_f16(kin[cc], lo, hi);
+      // K: row = token, k = d; elements 16c .. 16c+15 are chunks 2c, 2c+1 of k-block (c / 4)
+      const uint32_t kb = sk + (c >> 2) * (kPrefixChunk * 128);
+      sts_16(kb + sw128_chunk(tr, (2 * c) & 7), lo);
+      sts_16(kb + sw128_chunk(tr, (2 * c + 1) & 7), hi);
+      // V: the same token-major rows (two blocks of 64 head-dim elements); the second MMA reads
+      // them as an MN-major operand, so no transposition is needed
+      cvt16_e4m3_f16(vin[cc], lo, hi);
+      const uint32_t vb = sv + (c >> 2) * (kPrefixChunk * 128);
+      sts_16(vb + sw128_chunk(tr, (2 * c) & 7), lo);
+      sts_16(vb + sw128_chunk(tr, (2 * c + 1) & 7), hi);
     }
+    // generic-proxy writes -> visible to the tensor core's (async proxy) reads
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before_sync();
     __syncthreads();
-    for (int r = 0; r < 8; ++r) {
-      const int orow = warp * 8 + r;
-      const int rg = mtile * kPrefixRows + orow;
-      const int rh = rg % p.group;
-      if (rg / p.group >= n_req) break;
-      const int rb = req_list != nullptr ? __ldg(req_list + rg / p.group) : rg / p.group;
-      const uint4 x = lds_16(sk + orow * 512 + ((lane ^ (orow & 31)) << 4));
-      const int64_t pidx = (int64_t)rb * p.partial_stride_b + (int64_t)(kvh * p.group + rh) * p.partial_stride_h +
-                           (int64_t)chunk * p.partial_stride_s;
-      reinterpret_cast<uint4*>(reinterpret_cast<float*>(p.partial_output) + pidx * D)[lane] = x;
+    tc_fence_after_sync();
+    tmem = *tslot_ptr;
+    prefix_mark(pp, 1);  // operands staged
+
+    // ---- S = Q K^T : M 128, N 256, K 128 = 2 k-blocks x 4 slices of 16
+    if (t == 0) {
+      const uint32_t idesc = umma_idesc_f16(128, 256);
+#pragma unroll
+      for (int kb = 0; kb < 2; ++kb)
+#pragma unroll
+        for (int s = 0; s < 4; ++s)
+          umma_f16(tmem, umma_desc_k_sw128(sq + kb * (kPrefixRows * 128) + 32 * s),
+                   umma_desc_k_sw128(sk + kb * (kPrefixChunk * 128) + 32 * s), idesc, (kb | s) ? 1u : 0u);
+      umma_commit(bars);
     }
+    ok = mbar_wait_bounded(bars, parity, pp.wait_limit_ns) && ok;
+    tc_fence_after_sync();
+    prefix_mark(pp, 2);  // S ready
+
+    // ---- softmax: thread (row, cg) holds the row's scores of tokens [64 cg, 64 cg + 64)
+    const float ks = p.k_scale_ph ? __ldg(p.k_scale_ph + kvh) : p.k_scale;
+    const float vs = p.v_scale_ph ? __ldg(p.v_scale_ph + kvh) : p.v_scale;
+    const float scale_log2 = ks * p.sm_scale * kLog2e;
+    const uint32_t lane_addr = tmem + ((uint32_t)(qd * 32) << 16);  // this warp's 32 TMEM lanes
+    const int n_live = tok_hi - tok_lo;
+    float sc[64];
+    {
+      uint32_t r0[32], r1[32];
+      tmem_ld32_nowait(lane_addr + 64 * cg, r0);
+      tmem_ld32_nowait(lane_addr + 64 * cg + 32, r1);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int e = 0; e < 32; ++e) { sc[e] = __uint_as_float(r0[e]); sc[32 + e] = __uint_as_float(r1[e]); }
+    }
+    float mx = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < 64; ++e)
+      if (64 * cg + e < n_live) mx = fmaxf(mx, sc[e]);
+    red[cg * 128 + row] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(red[row], red[128 + row]), fmaxf(red[256 + row], red[384 + row])) * scale_log2;  // scale > 0
+    float lsum = 0.f;
+#pragma unroll
+    for (int e8 = 0; e8 < 8; ++e8) {
+      uint4 out;
+      uint32_t* w = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+      for (int e = 0; e < 8; e += 2) {
+        const int i0 = 8 * e8 + e;
+        const float p0 = (64 * cg + i0 < n_live) ? exp2f(sc[i0] * scale_log2 - mx) : 0.f;
+        const float p1 = (64 * cg + i0 + 1 < n_live) ? exp2f(sc[i0 + 1] * scale_log2 - mx) : 0.f;
+        lsum += p0 + p1;
+        w[e >> 1] = pack_f16x2(p0, p1);
+      }
+      // P: row = row, k = token 64 cg + 8 e8 ..: chunk e8 of k-block cg
+      sts_16(sk + cg * (kPrefixRows * 128) + sw128_chunk(row, e8), out);
+    }
+    red[512 + cg * 128 + row] = lsum;
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    lsum = red[512 + row] + red[640 + row] + red[768 + row] + red[896 + row];
+
+    prefix_mark(pp, 3);  // P written
+    // ---- O = P V : M 128, N 128, K 256 = 16 slices of 16 tokens.  A = P (K-major: 4 k-blocks of
+    // 64 tokens), B = V (MN-major: 16 tokens = two 1 KiB atoms, d blocks 32 KiB apart)
+    if (t == 0) {
+      const uint32_t idesc = umma_idesc_f16(128, 128, true);
+#pragma unroll
+      for (int s = 0; s < 16; ++s)
+        umma_f16(tmem + 256, umma_desc_k_sw128(sk + (s >> 2) * (kPrefixRows * 128) + 32 * (s & 3)),
+                 umma_desc_mn_sw128(sv + 2048 * s, kPrefixChunk * 128), idesc, s ? 1u : 0u);
+      umma_commit(bars + 8);
+    }
+    ok = mbar_wait_bounded(bars + 8, parity, pp.wait_limit_ns) && ok;
+    tc_fence_after_sync();
+    prefix_mark(pp, 4);  // O ready
+
+    // ---- (o, m, l) of the rows into slot `chunk` of the workspace.  Thread (row, cg) parks
+    // columns [32 cg, +32) of its row in shared memory (16-byte chunks XOR-swizzled by the row);
+    // then every warp writes whole rows, 32 lanes x 16 bytes = one contiguous 512-byte row per store.
+    {
+      float v[32];
+      tmem_ld32(lane_addr + 256 + 32 * cg, v);
+#pragma unroll
+      for (int c = 0; c < 8; ++c)
+        sts_16(sk + row * 512 + (((8 * cg + c) ^ (row & 31)) << 4),
+               make_uint4(__float_as_uint(v[4 * c] * vs), __float_as_uint(v[4 * c + 1] * vs),
+                          __float_as_uint(v[4 * c + 2] * vs), __float_as_uint(v[4 * c + 3] * vs)));
+      if (row_live && cg == 0) {
+        const int64_t pidx = (int64_t)b * p.partial_stride_b + (int64_t)(kvh * p.group + head) * p.partial_stride_h +
+                             (int64_t)chunk * p.partial_stride_s;
+        p.partial_max[pidx] = mx * kLn2;
+        p.partial_sum[pidx] = lsum;
+      }
+      __syncthreads();
+      for (int r = 0; r < 8; ++r) {
+        const int orow = warp * 8 + r;
+        const int rg = mtile * kPrefixRows + orow;
+        const int rh = rg % p.group;
+        if (rg / p.group >= n_req) break;
+        const int rb = req_list != nullptr ? __ldg(req_list + rg / p.group) : rg / p.group;
+        const uint4 x = lds_16(sk + orow * 512 + ((lane ^ (orow & 31)) << 4));
+        const int64_t pidx = (int64_t)rb * p.partial_stride_b + (int64_t)(kvh * p.group + rh) * p.partial_stride_h +
+                             (int64_t)chunk * p.partial_stride_s;
+        reinterpret_cast<uint4*>(reinterpret_cast<float*>(p.partial_output) + pidx * D)[lane] = x;
+      }
+    }
+    prefix_mark(pp, 5);  // stored
+    ++turns;
+    // the next tile's staging overwrites what the stores above read, and its MMAs the accumulators
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
   }
-  prefix_mark(pp, 5);  // stored
+  if (turns == 0) return;
   if (!ok && t == 0) atomicExch(pp.status, kErrUmmaTimeout);
-  tc_fence_before_sync();
-  __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 512);
 }
 

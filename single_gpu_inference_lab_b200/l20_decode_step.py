@@ -44,6 +44,7 @@ class DecodeStep:
     suffix_split: int = 512            # split size of the grouped path's split-KV pass
     max_suffix: int = 0                # what a request in a group can have behind its prefix
     group_sizes: Optional[list] = None
+    all_in_groups: bool = False        # no request of the step is outside the groups (read on the host)
 
 
 _BUFFERS: dict = {}
@@ -107,8 +108,9 @@ def l20_decode_step(meta, query, key_cache, value_cache, block_tables, seq_lens,
         take = sw["shared_prefix_force"]
         if not capturing:
             sizes = [len(g) for g in groups.to_lists()] if sw["trace"] else None
-            found = len(sizes) if sizes is not None else int(groups.buffer[3].item())  # the one host read of the step
+            found, grouped = groups.buffer[3:5].tolist()  # the one host read of the step: groups, requests in them
             take = take or found > 0
+            step.all_in_groups = grouped == batch
             if sw["trace"]:
                 from .l20_shared_prefix_decode_dispatch import l20_shared_prefix_trace
 
@@ -158,7 +160,7 @@ def l20_grouped_decode(step: DecodeStep, query, key_cache, value_cache, block_ta
     po, pm, ps = step.prefix_workspace
     ops.shared_prefix_decode_grouped_fp8_e4m3(query, key_cache, value_cache, block_tables, seq_lens, po, pm, ps, output,
                                               vec(k_scale), vec(v_scale), max_seq_len, step.suffix_split, step.groups,
-                                              max_suffix_len=step.max_suffix)
+                                              max_suffix_len=step.max_suffix, all_in_groups=step.all_in_groups)
     sw = _switches()
     if sw["trace"]:
         from .l20_shared_prefix_decode_dispatch import l20_shared_prefix_trace

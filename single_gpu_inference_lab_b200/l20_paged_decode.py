@@ -270,6 +270,7 @@ def shared_prefix_decode_grouped_fp8_e4m3(
     max_prefix_len: Optional[int] = None,
     max_suffix_len: Optional[int] = None,
     sm_scale: float = 0.0,
+    all_in_groups: bool = False,
 ) -> torch.Tensor:
     """Decode step of a batch with any number of shared-prefix groups plus requests in none
     (``groups`` from ``group_shared_prefixes``, read on the device): dense tcgen05 pass per group,
@@ -278,11 +279,13 @@ def shared_prefix_decode_grouped_fp8_e4m3(
     ``min_prefix_len`` is always a true bound; ``None`` = the whole context): the split-KV grid is
     sized for it and requests in no group get as many, longer, splits.  The workspace needs
     ``ceil(min(max_prefix_len, max_seq_len) / 256) + ceil(min(max_suffix_len, max_seq_len) /
-    split_size)`` slots."""
+    split_size)`` slots.  ``all_in_groups`` (``PFD_FLAG_ALL_IN_GROUPS``): the caller has read
+    ``groups.buffer[4]`` and it equals the batch; the split-KV pass may then run beside the dense
+    pass instead of behind it (a hint about speed only)."""
     torch.ops.l20_stack.shared_prefix_decode_grouped_fp8_e4m3(
         query, key_cache, value_cache, block_table, seq_lens, partial_output, partial_max, partial_sum, output,
         k_scale, v_scale, float(sm_scale), max_seq_len, split_size, groups.buffer, groups.max_groups,
-        int(max_seq_len if max_prefix_len is None else max_prefix_len), int(max_suffix_len or 0),
+        int(max_seq_len if max_prefix_len is None else max_prefix_len), int(max_suffix_len or 0), bool(all_in_groups),
     )
     return output
 

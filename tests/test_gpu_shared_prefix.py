@@ -368,3 +368,86 @@ def test_grouped_decode_with_a_suffix_bound_and_its_violation(cabi):
                                                max_suffix_len=64, **common)
     torch.cuda.synchronize()
     assert cabi.device_status() == 5
+
+
+@pytest.fixture
+def suffix_form(cabi):
+    """Forces one of the two forms of the split-KV pass behind the dense pass; restores the choice."""
+    yield cabi.set_suffix_form
+    cabi.set_suffix_form(-1)
+
+
+@pytest.mark.parametrize("form", [0, 1])
+def test_both_forms_of_the_suffix_pass_match_the_oracle(cabi, suffix_form, form):
+    """The split-KV pass over the suffixes runs either after the dense prefix pass (eight-warp
+    CTAs) or beside it (two-warp CTAs, of which only one waits for the dense pass before the grid
+    completes): same results, whichever the library would choose by itself."""
+    suffix_form(form)
+    for batch, shrink, splits in ((20, 0.25, (64, 128, 512)), (64, 1.0, (128, 192))):
+        w = make_inputs("shared-prefix-b64", seed=3, batch=batch, shrink=shrink)
+        exp = oracle.reference(w.query, w.key_cache, w.value_cache, w.block_table.long(), w.seq_lens, w.k_scale, w.v_scale)
+        for split in splits:
+            for rep in range(2):
+                out, _, _ = run_shared(cabi, w, split)
+                assert_within_gate(out, exp, f"form={form} batch={batch} split={split} rep={rep}")
+    w, lengths = _mixed_batch(14, 1024, 512)
+    exp = oracle.reference(w.query, w.key_cache, w.value_cache, w.block_table.long(), w.seq_lens, w.k_scale, w.v_scale)
+    g = w.to(DEV)
+    groups, max_groups = cabi.group_shared_prefixes(g.block_table, prefix_lengths=lengths.to(DEV), min_batch=8, min_prefix_len=256)
+    slots = -(-w.max_seq_len // 256) + -(-w.max_seq_len // 128)
+    b, hq, d = g.query.shape
+    ws = (torch.full((b, hq, slots, d), float("nan"), device=DEV), torch.full((b, hq, slots), float("nan"), device=DEV),
+          torch.full((b, hq, slots), float("nan"), device=DEV))
+    out = torch.full_like(g.query, float("nan"))
+    cabi.shared_prefix_decode_grouped_fp8_e4m3(
+        g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens, groups=groups, max_groups=max_groups,
+        k_scale=g.k_scale, v_scale=g.v_scale, max_seq_len=w.max_seq_len, split_size=128, output=out, workspace=ws)
+    torch.cuda.synchronize()
+    assert cabi.device_status() == 0
+    assert_within_gate(out, exp, f"form={form}: mixed batch (requests in no group attend from token 0)")
+
+
+def _full_size_batch_in_three_groups(seed):
+    """64 requests behind 4096-token prefixes: three groups of 17 (136 rows of 8 heads each: one
+    full 128-row tile and a ragged one) and 13 requests that share nothing."""
+    w = make_inputs("shared-prefix-b64", seed=seed, batch=64)
+    gen = torch.Generator().manual_seed(seed)
+    pages = w.key_cache.shape[0]
+    table = w.block_table.clone()
+    prefix_pages = w.prefix_len // 16
+    for first in (17, 34):
+        chain = torch.randint(0, pages, (prefix_pages,), generator=gen, dtype=torch.int32)
+        table[first:first + 17, :prefix_pages] = chain
+    for r in range(51, 64):
+        table[r, :prefix_pages] = torch.randint(0, pages, (prefix_pages,), generator=gen, dtype=torch.int32)
+    w.block_table = table
+    return w
+
+
+@pytest.mark.parametrize("hint", [False, True])
+def test_grouped_decode_with_more_tiles_than_tile_slots(cabi, hint):
+    """At full size the dense pass's grid is one CTA per SM wide and gets no spare tile slots:
+    three groups with a ragged tile each make six tiles for four slots, so CTAs take a second tile
+    in turn.  With the all-in-groups hint set although 13 requests are in no group (a caller's
+    mistake) the result is still right."""
+    w = _full_size_batch_in_three_groups(21)
+    exp = oracle.reference(w.query, w.key_cache, w.value_cache, w.block_table.long(), w.seq_lens, w.k_scale, w.v_scale)
+    g = w.to(DEV)
+    groups, max_groups = cabi.group_shared_prefixes(g.block_table, seq_lens=g.seq_lens, min_batch=8, min_prefix_len=4096, max_groups=4)
+    torch.cuda.synchronize()
+    assert groups[3:5].tolist() == [3, 51]
+    split = 128
+    bound = w.max_seq_len - 4096
+    slots = w.prefix_len // 256 + -(-bound // split)
+    b, hq, d = g.query.shape
+    ws = (torch.full((b, hq, slots, d), float("nan"), device=DEV), torch.full((b, hq, slots), float("nan"), device=DEV),
+          torch.full((b, hq, slots), float("nan"), device=DEV))
+    for step in range(2):
+        out = torch.full_like(g.query, float("nan"))
+        cabi.shared_prefix_decode_grouped_fp8_e4m3(
+            g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens, groups=groups, max_groups=max_groups,
+            max_prefix_len=w.prefix_len, max_suffix_len=bound, k_scale=g.k_scale, v_scale=g.v_scale, max_seq_len=w.max_seq_len,
+            split_size=split, output=out, workspace=ws, flags=cabi.PFD_FLAG_ALL_IN_GROUPS if hint else 0)
+        torch.cuda.synchronize()
+        assert cabi.device_status() == 0
+        assert_within_gate(out, exp, f"three groups of 17, hint={hint}, step {step}")
