@@ -226,8 +226,8 @@ bool tma_eligible(const pfd_decode_args& a) {
          head_is_dim1(a.k_stride_token, a.k_stride_head) == head_is_dim1(a.v_stride_token, a.v_stride_head);
 }
 
-// kWarpsT = 2 behind the dense prefix pass: a CTA of two warps, 128 registers and 34 KB fits on an
-// SM beside a prefix CTA, so the two passes run side by side instead of one after the other.
+// kWarpsT = 2 beside the dense prefix pass: a CTA of two warps, 166 registers and 34 KB fits on an
+// SM next to a CTA of the slim prefix kernel (see suffix_beside_prefix).
 template <bool QBF16, int kWarpsT = kWarps>
 int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, dim3 grid, cudaStream_t stream) {
   CUtensorMap mk, mv;
