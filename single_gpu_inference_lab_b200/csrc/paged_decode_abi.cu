@@ -228,7 +228,7 @@ bool tma_eligible(const pfd_decode_args& a) {
 
 // kWarpsT = 2 beside the dense prefix pass: a CTA of two warps, 166 registers and 34 KB fits on an
 // SM next to a CTA of the slim prefix kernel (see suffix_beside_prefix).
-template <bool QBF16, int kWarpsT = kWarps>
+template <bool QBF16, int kWarpsT = kWarps, int kStagesT = kStages>
 int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, dim3 grid, cudaStream_t stream) {
   CUtensorMap mk, mv;
   if (int rc = get_tensor_map(a.key_cache, a.k_stride_page, a.k_stride_token, a.k_stride_head, a.num_pages,
@@ -241,8 +241,8 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
   tp.head_is_dim1 = head_is_dim1(a.k_stride_token, a.k_stride_head) ? 1 : 0;
   if (int rc = status_pointer(&tp.status)) return rc;
   tp.wait_limit_ns = g_wait_limit_ns.load(std::memory_order_relaxed);
-  auto kernel = pfd::paged_decode_fp8_partial_tma_kernel<QBF16, kWarpsT, kStages>;
-  constexpr int smem = 1024 + kWarpsT * kStages * 8192 + kWarpsT * kStages * 8 + 2 * kWarpsT * 16 * 4;
+  auto kernel = pfd::paged_decode_fp8_partial_tma_kernel<QBF16, kWarpsT, kStagesT>;
+  constexpr int smem = 1024 + kWarpsT * kStagesT * 8192 + kWarpsT * kStagesT * 8 + 2 * kWarpsT * 16 * 4;
   static std::atomic<bool> configured[kMaxDevices];  // (one array per instantiation)
   if (int rc = configure_smem(configured, kernel, smem, kWarpsT != kWarps)) return rc;
   {
@@ -420,7 +420,7 @@ int launch_decode(const pfd_decode_args& a, const pfd::KernelParams& kp, int num
   if (D == 128 && tma_eligible(a)) {
     g_last_path = PFD_PATH_FIXED_TMA;
     if (int rc = suffix_beside_prefix(a, kp.slot_offset, num_splits, kp.row_kv_start != nullptr)
-                     ? launch_partial_tma<QBF16, 2>(a, kp, grid, stream)
+                     ? launch_partial_tma<QBF16, 2, 1>(a, kp, grid, stream)
                      : launch_partial_tma<QBF16>(a, kp, grid, stream))
       return rc;
   } else {

@@ -806,6 +806,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
     return;
   }
   if (p.slot_offset == 0 && p.early_metadata) pdl_wait();
+  dbg_mark(dbg_slot, 6, threadIdx.x == 0);  // sequence length known
   const int nsplits_seq = (seq_len - kv0 + split_sz - 1) / split_sz;
 
   extern __shared__ uint8_t smem_raw[];
@@ -863,6 +864,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
     const int32_t phys1 = __shfl_sync(0xffffffffu, ids, (2 * t + 1) & 31);
     if (lane == 0 && t < n_pairs) issue(t, phys0, phys1);
   }
+  dbg_mark(dbg_slot, 3, threadIdx.x == 0);  // first copies issued
 
   uint32_t qa[D / 16][4];
   load_q_frags<D, QBF16>(qa, p, b, kvh, i, j);
@@ -895,6 +897,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
     const int s = t % NSTAGE;
     const uint32_t parity = (t / NSTAGE) & 1;
     if (!mbar_wait_bounded(my_bars + 8 * s, parity, tp.wait_limit_ns)) { ok = false; break; }
+    if (t == 0) dbg_mark(dbg_slot, 4, threadIdx.x == 0);  // first pair arrived
     const uint32_t stage = my_ring + s * kStageBytes;
     const int tok0 = my_page(t, 0) * kPage;
     // the second page of the last pair may not exist: its (stale) bytes are masked like any
@@ -943,6 +946,7 @@ paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
       }
     }
   }
+  dbg_mark(dbg_slot, 5, threadIdx.x == 0);  // pairs consumed
   if (!ok) {
     // Record the failure, then give this warp's copies still in flight a bounded chance to
     // land before the ring is reused by the merge below.
