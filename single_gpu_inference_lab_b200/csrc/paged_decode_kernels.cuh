@@ -753,7 +753,7 @@ __global__ void bounded_wait_selftest_kernel(int32_t* status, unsigned long long
 // step give four independent QK^T accumulator chains and halve the per-token cost of the
 // softmax bookkeeping (shuffles, rescale).
 template <bool QBF16, int NWARPS, int NSTAGE>
-__global__ void __launch_bounds__(NWARPS * 32, NWARPS == 2 ? 6 : 1)  // two warps: six CTAs per SM, i.e. at most 168 registers
+__global__ void __launch_bounds__(NWARPS * 32, NWARPS <= 12 ? 12 / NWARPS : 1)  // twelve warps per SM: at most 168 registers
 paged_decode_fp8_partial_tma_kernel(const KernelParams p, const TmaParams tp,
                                     const __grid_constant__ CUtensorMap tmap_k,
                                     const __grid_constant__ CUtensorMap tmap_v) {

@@ -279,52 +279,61 @@ shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
     const int tok_lo = chunk * kPrefixChunk;
     const int tok_hi = min(tok_lo + kPrefixChunk, prefix_len);
 
-    // ---- K and V chunk: thread t stages half a token row (64 head-dim elements) of token t / 2
-    const int tr = t >> 1, dh = t & 1;
+    // ---- K and V chunk: warp w stages page w of the chunk (16 tokens); per load instruction its
+    // lanes cover four whole 128-byte token rows (lane = 8 * token + 16-byte group), so every
+    // sector that is fetched is used at once -- with the whole-SM shared-memory carve-out the L1
+    // is too small to keep half-used lines until the thread's next load comes back for them
+    const int e16 = lane & 7;
     uint4 kin[4], vin[4];
     {
-      const int tok = tok_lo + tr;
-      const bool live = tok < tok_hi;
+      const bool live = tok_lo + kPage * warp < tok_hi;  // (the prefix ends on a page boundary)
       int64_t phys = 0;
-      if (live) phys = page_of(p.block_table, p.bt_stride_b, page_row, tok / kPage);
-      const uint8_t* krow = p.key_cache + phys * p.k_stride_page + (int64_t)(tok % kPage) * p.k_stride_token + (int64_t)kvh * p.k_stride_head;
-      const uint8_t* vrow = p.value_cache + phys * p.v_stride_page + (int64_t)(tok % kPage) * p.v_stride_token + (int64_t)kvh * p.v_stride_head;
+      if (live) phys = page_of(p.block_table, p.bt_stride_b, page_row, tok_lo / kPage + warp);
+      const uint8_t* kpage = p.key_cache + phys * p.k_stride_page + (int64_t)kvh * p.k_stride_head;
+      const uint8_t* vpage = p.value_cache + phys * p.v_stride_page + (int64_t)kvh * p.v_stride_head;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
+        const int tp = 4 * c + (lane >> 3);  // token of the page
         kin[c] = vin[c] = make_uint4(0u, 0u, 0u, 0u);
         if (live) {
-          kin[c] = __ldg(reinterpret_cast<const uint4*>(krow) + 4 * dh + c);
-          vin[c] = __ldg(reinterpret_cast<const uint4*>(vrow) + 4 * dh + c);
+          kin[c] = __ldg(reinterpret_cast<const uint4*>(kpage + (int64_t)tp * p.k_stride_token) + e16);
+          vin[c] = __ldg(reinterpret_cast<const uint4*>(vpage + (int64_t)tp * p.v_stride_token) + e16);
         }
       }
     }
-    // ---- Q tile: thread (row, cg) stages 32 of the row's 128 elements
+    // ---- Q tile.  This thread's own row (TMEM lane) of the tile, for the softmax and the stores:
     const int row_g = mtile * kPrefixRows + row;
     const int head = row_g % p.group;
     const bool row_live = row_g / p.group < n_req;
     const int b = !row_live ? 0 : (req_list != nullptr ? __ldg(req_list + row_g / p.group) : row_g / p.group);
-    {
-      const uint16_t* q = reinterpret_cast<const uint16_t*>(p.query) + (int64_t)(row_live ? b : 0) * p.q_stride_b +
-                          (int64_t)(kvh * p.group + head) * p.q_stride_h;
+    // Staging: warp w takes rows 8w .. 8w+7, two whole 256-byte rows per load instruction
+    // (lane = 16 * row + 16-byte chunk), fully used sectors as for K and V.
 #pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        const int c = 4 * cg + cc;
-        uint4 x = make_uint4(0u, 0u, 0u, 0u);
-        if (row_live) x = __ldg(reinterpret_cast<const uint4*>(q) + c);
-        if constexpr (QBF16) {
-          uint32_t* w = reinterpret_cast<uint32_t*>(&x);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
-            w[e] = pack_f16x2(__bfloat162float(v.x), __bfloat162float(v.y));
-          }
-        }
-        sts_16(sq + (c >> 3) * (kPrefixRows * 128) + sw128_chunk(row, c & 7), x);
+    for (int it = 0; it < 4; ++it) {
+      const int r = 8 * warp + 2 * it + (lane >> 4), c = lane & 15;
+      const int rg = mtile * kPrefixRows + r;
+      const int req = rg / p.group;
+      uint4 x = make_uint4(0u, 0u, 0u, 0u);
+      if (req < n_req) {
+        const int rb = req_list != nullptr ? __ldg(req_list + req) : req;
+        const uint16_t* q = reinterpret_cast<const uint16_t*>(p.query) + (int64_t)rb * p.q_stride_b +
+                            (int64_t)(kvh * p.group + rg % p.group) * p.q_stride_h;
+        x = __ldg(reinterpret_cast<const uint4*>(q) + c);
       }
+      if constexpr (QBF16) {
+        uint32_t* w = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
+          w[e] = pack_f16x2(__bfloat162float(v.x), __bfloat162float(v.y));
+        }
+      }
+      sts_16(sq + (c >> 3) * (kPrefixRows * 128) + sw128_chunk(r, c & 7), x);
     }
 #pragma unroll
     for (int cc = 0; cc < 4; ++cc) {  // 16 bytes = 16 head-dim elements at a time
-      const int c = 4 * dh + cc;
+      const int tr = kPage * warp + 4 * cc + (lane >> 3);  // token row of the chunk
+      const int c = e16;
       uint4 lo, hi;
       cvt16_e4m3_f16(kin[cc], lo, hi);
       // K: row = token, k = d; elements 16c .. 16c+15 are chunks 2c, 2c+1 of k-block (c / 4)
