@@ -265,20 +265,24 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
   return check_launch("partial kernel (TMA)");
 }
 
-// Behind the dense prefix pass the split-KV pass has two forms.  Two-warp CTAs (166 registers,
-// 34 KB) fit BESIDE a CTA of the slim dense kernel -- one per SM there, six on an SM that pass
-// leaves free -- and run while it runs.  Otherwise the eight-warp CTAs of the ordinary pass are
-// launched behind the dense pass; as its programmatic dependents they already start on whatever
-// SMs that pass leaves free, so the small form only pays where it leaves few: when its grid is
-// one wave that nearly fills the GPU.  And two warps per CTA are few, so the suffixes must be
-// short next to the prefix work.  Measured in us per step (behind / beside), 16 query and 2 KV
-// heads, prefix 4096 unless noted, suffixes up to 511:
-//   batch 64 (128 dense CTAs), splits of 128: 19.6 / 18.4   splits of 256: 20.7 / 19.1
-//   batch 32 (64 CTAs): 15.6 / 16.5   batch 16: 15.3 / 15.7   batch 128 (256 CTAs): 35.2 / 35.7
-//   batch 256: 61.9 / 65.2   batch 64, prefix 3072 of the 4096 (suffixes up to 1535): 23.9 / 30.9
-// A request in no group attends its whole context in as many splits as the others their suffix,
-// which two warps would take several times longer over: with a groups table the small form
-// needs the caller's word that every request is in a group (PFD_FLAG_ALL_IN_GROUPS).
+// Behind the dense prefix pass the split-KV pass has two forms.  Two-warp CTAs with a one-stage
+// ring (165 registers, 18 KB) fit BESIDE a CTA of the slim dense kernel -- two per SM there, six
+// on an SM that pass leaves free -- and run while it runs.  Otherwise the ordinary four-warp CTAs
+// are launched behind the dense pass; as its programmatic dependents they already start on
+// whatever SMs that pass leaves free, so the small form pays where it leaves few, and two warps
+// with one copy in flight each are slow, so it pays while a CTA's share of a suffix is short.
+// Measured in us per step (behind / beside), 16 query and 2 KV heads, prefix 4096 unless noted,
+// suffixes up to 511 behind it:
+//   batch 64 (128 dense CTAs), splits of 128: 19.8 / 17.4   of 256: 21.7 / 19.2   of 512: 24.6 / 24.8
+//   batch 128 (256 CTAs), splits of 256: 35.6 / 34.2        batch 256 (512 CTAs), of 512: 61.7 / 65.5
+//   batch 32 (64 CTAs): 15.2 / 16.6                         batch 16 (32 CTAs): 14.9 / 15.5
+//   batch 64 with 3072 of the 4096 declared shared (96 CTAs, suffixes up to 1535, splits of 384): 23.8 / 21.9
+//   ... 2048 declared (64 CTAs, suffixes up to 2559), splits of 512: 26.0 / 27.5   of 256: 28.4 / 27.6
+//   batch 128 with 2048 declared (128 CTAs), splits of 512: 46.0 / 44.9
+// The rule below is drawn from that table.  A request in no group attends its whole context in
+// as many splits as the others their suffix, which two warps would take several times longer
+// over: with a groups table the small form needs the caller's word that every request is in a
+// group (PFD_FLAG_ALL_IN_GROUPS).
 std::atomic<int> g_suffix_form{-1};  // tuning: -1 choose, 0 always behind, 1 always beside
 bool suffix_beside_prefix(const pfd_decode_args& a, int prefix_chunks, int num_splits, bool groups_table) {
   if (prefix_chunks <= 0 || a.head_dim != 128 || !tma_eligible(a)) return false;
@@ -289,8 +293,9 @@ bool suffix_beside_prefix(const pfd_decode_args& a, int prefix_chunks, int num_s
   const int64_t dense_ctas = (int64_t)prefix_chunks * a.num_kv_heads *
                              (((int64_t)a.batch * group + pfd::kPrefixRows - 1) / pfd::kPrefixRows);
   const int sms = t_device->sms;
-  if (dense_ctas > sms || 10 * dense_ctas < 7 * sms) return false;
-  return (int64_t)num_splits * a.num_kv_heads * a.batch * a.split_size <= 640 * dense_ctas;
+  if (5 * dense_ctas < 3 * sms || dense_ctas > 2 * sms) return false;  // too few CTAs to fill the SMs, or many waves
+  if (a.split_size > 384 && dense_ctas > sms) return false;
+  return (int64_t)num_splits * a.num_kv_heads * a.batch * a.split_size <= 6144 * dense_ctas;
 }
 
 // ---- balanced persistent kernel -------------------------------------------------------------

@@ -148,13 +148,14 @@ def should_dispatch_l20_shared_prefix_paged_decode(
 
 
 def choose_suffix_split_size(batch: int, num_kv_heads: int, max_suffix_len: int, *, resident_ctas: int = 444) -> int:
-    """Split size of the suffix pass behind the dense prefix pass.  The suffix kernel's work items
-    are (request, kv head, split); private suffixes are short, so with the reference's constant
-    512 (install hook, :117) a work item is one latency chain of a few page pairs and there are too
-    few of them: the pass then lasts as long as the dense pass it follows (10 us on the batch of
-    64 with suffixes up to 512 tokens).  As many equal splits per request as make about one wave
-    of resident CTAs (3 per SM on 148 SMs) is the measured optimum there, in us per step:
-    512 -> 24.7, 256 -> 21.9, 192 -> 21.2, 160 -> 21.0, 144 -> 21.1, 128 -> 20.1, 112 -> 20.5, 64 -> 22.8."""
+    """Split size of the suffix pass of the shared-prefix operators.  The suffix kernel's work
+    items are (request, kv head, split); private suffixes are short, so with the reference's
+    constant 512 (install hook, :117) a work item is one latency chain of a few page pairs and
+    there are too few of them: the pass then lasts as long as the dense pass it accompanies (10 us
+    on the batch of 64 with suffixes up to 512 tokens).  As many equal splits per request as make
+    about one wave of resident CTAs (3 per SM on 148 SMs) is the measured optimum there, in us per
+    step: 512 -> 25.1, 256 -> 19.4, 192 -> 18.1, 160 -> 18.2, 128 -> 17.6, 96 -> 20.1, 64 -> 18.9
+    (multiples of 64 keep the CTA's two warps at whole page pairs each)."""
     if max_suffix_len <= 0:
         return 64
     splits = max(1, -(-int(resident_ctas) // max(int(batch) * int(num_kv_heads), 1)))
