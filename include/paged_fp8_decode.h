@@ -407,10 +407,9 @@ int pfd_set_wait_limit_ns(uint64_t limit_ns);
 /*
  * Tuning: which form the split-KV pass of the shared-prefix entry points takes.  -1 (default):
  * chosen per call -- two-warp CTAs that run on the same SMs WHILE the dense prefix pass runs when
- * that pass has CTAs for most of the SMs but not many waves of them and the suffixes are short
- * next to the prefix work (and, with a groups table, PFD_FLAG_ALL_IN_GROUPS is set), else the
- * ordinary four-warp CTAs, which start on the SMs the dense pass leaves free and take the rest
- * after it; 0: always the latter; 1: always the former.
+ * the SMs that pass leaves free could not absorb the suffix work meanwhile (and, with a groups
+ * table, PFD_FLAG_ALL_IN_GROUPS is set), else the ordinary four-warp CTAs, which start on those
+ * free SMs and take the rest after the pass; 0: always the latter; 1: always the former.
  * Process-wide, read at launch; results do not depend on it.
  */
 int pfd_set_suffix_form(int32_t form);

@@ -268,21 +268,24 @@ int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, di
 // Behind the dense prefix pass the split-KV pass has two forms.  Two-warp CTAs with a one-stage
 // ring (165 registers, 18 KB) fit BESIDE a CTA of the slim dense kernel -- two per SM there, six
 // on an SM that pass leaves free -- and run while it runs.  Otherwise the ordinary four-warp CTAs
-// are launched behind the dense pass; as its programmatic dependents they already start on
-// whatever SMs that pass leaves free, so the small form pays where it leaves few, and two warps
-// with one copy in flight each are slow, so it pays while a CTA's share of a suffix is short.
-// Measured in us per step (behind / beside), 16 query and 2 KV heads, prefix 4096 unless noted,
-// suffixes up to 511 behind it:
-//   batch 64 (128 dense CTAs), splits of 128: 19.8 / 17.4   of 256: 21.7 / 19.2   of 512: 24.6 / 24.8
-//   batch 128 (256 CTAs), splits of 256: 35.6 / 34.2        batch 256 (512 CTAs), of 512: 61.7 / 65.5
-//   batch 32 (64 CTAs): 15.2 / 16.6                         batch 16 (32 CTAs): 14.9 / 15.5
+// are launched behind the dense pass; as its programmatic dependents they start, three per SM, on
+// whatever SMs the last wave of that pass leaves free, and only what those SMs do not get done
+// while the wave runs is left for afterwards.  The small form costs the dense pass 1 us and its
+// CTAs are slow (two warps, one copy in flight each), so it is taken only when the free SMs
+// cannot absorb the suffix work.  Measured in us per step (behind / beside), 16 query and 2 KV
+// heads, prefix 4096 unless noted, suffixes up to 511 behind it (batch b = 2 b dense CTAs):
+//   batch 64, splits of 128: 19.8 / 17.4   of 256: 21.7 / 19.2   of 512: 24.6 / 24.8
+//   batch 16: 14.2 / 15.1   batch 32: 15.1 / 16.0   batch 48: 15.2 / 16.9   batch 96: 29.1 / 31.5
+//   batch 128, splits of 128: 34.3 / 35.6   of 256: 35.5 / 34.2      batch 256, of 256: 59.8 / 65.3   of 512: 61.7 / 65.5
 //   batch 64 with 3072 of the 4096 declared shared (96 CTAs, suffixes up to 1535, splits of 384): 23.8 / 21.9
 //   ... 2048 declared (64 CTAs, suffixes up to 2559), splits of 512: 26.0 / 27.5   of 256: 28.4 / 27.6
 //   batch 128 with 2048 declared (128 CTAs), splits of 512: 46.0 / 44.9
-// The rule below is drawn from that table.  A request in no group attends its whole context in
-// as many splits as the others their suffix, which two warps would take several times longer
-// over: with a groups table the small form needs the caller's word that every request is in a
-// group (PFD_FLAG_ALL_IN_GROUPS).
+// The estimate below (a dense wave lasts 10 us, a four-warp CTA 2 us + 1 us per page pair of each
+// warp, about 65 % of the grid has work; never with more than two dense waves, each of which
+// pays the slim kernel's 1 us) decides all of these but one as measured.  A request in
+// no group attends its whole context in as many splits as the others their suffix, which two
+// warps would take several times longer over: with a groups table the small form needs the
+// caller's word that every request is in a group (PFD_FLAG_ALL_IN_GROUPS).
 std::atomic<int> g_suffix_form{-1};  // tuning: -1 choose, 0 always behind, 1 always beside
 bool suffix_beside_prefix(const pfd_decode_args& a, int prefix_chunks, int num_splits, bool groups_table) {
   if (prefix_chunks <= 0 || a.head_dim != 128 || !tma_eligible(a)) return false;
@@ -292,10 +295,14 @@ bool suffix_beside_prefix(const pfd_decode_args& a, int prefix_chunks, int num_s
   const int group = a.num_q_heads / a.num_kv_heads;
   const int64_t dense_ctas = (int64_t)prefix_chunks * a.num_kv_heads *
                              (((int64_t)a.batch * group + pfd::kPrefixRows - 1) / pfd::kPrefixRows);
+  const int64_t grid_ctas = (int64_t)num_splits * a.num_kv_heads * a.batch;
+  if (grid_ctas * a.split_size > 6144 * dense_ctas) return false;  // suffixes far longer than the prefix
   const int sms = t_device->sms;
-  if (5 * dense_ctas < 3 * sms || dense_ctas > 2 * sms) return false;  // too few CTAs to fill the SMs, or many waves
-  if (a.split_size > 384 && dense_ctas > sms) return false;
-  return (int64_t)num_splits * a.num_kv_heads * a.batch * a.split_size <= 6144 * dense_ctas;
+  if (dense_ctas > 2 * sms) return false;
+  const int last_wave = dense_ctas % sms == 0 ? sms : static_cast<int>(dense_ctas % sms);
+  const double cta_us = 2.0 + (a.split_size + 127) / 128;
+  const double absorbed = 3.0 * (sms - last_wave) * (10.0 / cta_us);
+  return 0.65 * static_cast<double>(grid_ctas) > absorbed;
 }
 
 // ---- balanced persistent kernel -------------------------------------------------------------
