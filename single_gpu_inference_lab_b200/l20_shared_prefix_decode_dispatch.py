@@ -153,13 +153,17 @@ def choose_suffix_split_size(batch: int, num_kv_heads: int, max_suffix_len: int,
     constant 512 (install hook, :117) a work item is one latency chain of a few page pairs and
     there are too few of them: the pass then lasts as long as the dense pass it accompanies (10 us
     on the batch of 64 with suffixes up to 512 tokens).  As many equal splits per request as make
-    about one wave of resident CTAs (3 per SM on 148 SMs) is the measured optimum there, in us per
-    step: 512 -> 25.1, 256 -> 19.4, 192 -> 18.1, 160 -> 18.2, 128 -> 17.6, 96 -> 20.1, 64 -> 18.9
-    (multiples of 64 keep the CTA's two warps at whole page pairs each)."""
+    about one wave of resident CTAs (3 per SM on 148 SMs), but two to four of them, in multiples
+    of 64 tokens (whole page pairs for each warp of a CTA), is what the measurements ask for, in us
+    per step with suffixes up to 511 tokens behind a prefix of 4096:
+    batch 64: 512 -> 25.1, 256 -> 19.4, 192 -> 18.1, 160 -> 18.2, 128 -> 17.6, 96 -> 20.1, 64 -> 18.9;
+    batch 256: 512 -> 61.9, 256 -> 59.8, 128 -> 62.3;  batch 128: 512 -> 37.0, 256 -> 34.1, 128 -> 34.2;
+    batches 32 to 96: within 0.3 us from 128 to 512;  batch 16: 512 -> 14.0, 128 -> 14.4, 64 -> 14.5."""
     if max_suffix_len <= 0:
         return 64
-    splits = max(1, -(-int(resident_ctas) // max(int(batch) * int(num_kv_heads), 1)))
-    size = -(-(-(-int(max_suffix_len) // splits)) // 16) * 16
+    splits = -(-int(resident_ctas) // max(int(batch) * int(num_kv_heads), 1))
+    splits = min(4, max(2, splits))
+    size = -(-(-(-int(max_suffix_len) // splits)) // 64) * 64
     return int(min(512, max(64, size)))
 
 
