@@ -64,6 +64,26 @@ def test_argument_errors_are_reported_without_a_gpu(built_libs):
     assert lib.pfd_paged_decode_fp8_e4m3_split_out(ctypes.byref(a)) == -1
     assert b"split_size must be a multiple of 16" in lib.pfd_last_error()
     assert lib.pfd_launch_count() == 0
+    # the tuning switch of the shared-prefix suffix pass takes -1, 0 or 1 and needs no device
+    for form in (0, 1, -1):
+        cabi.set_suffix_form(form)
+    with pytest.raises(RuntimeError, match="form must be"):
+        cabi.set_suffix_form(2)
+
+
+def test_suffix_split_policy():
+    """Two to four splits per request, in multiples of 64 tokens, within [64, 512]."""
+    from single_gpu_inference_lab_b200.l20_shared_prefix_decode_dispatch import choose_suffix_split_size as choose
+
+    assert choose(64, 2, 511) == 128      # the batch-64 configuration: four splits
+    assert choose(256, 2, 511) == 256     # many requests: still two splits each
+    assert choose(8, 2, 511) == 128       # few requests: no more than four
+    assert choose(64, 2, 100) == 64 and choose(64, 2, 0) == 64
+    assert choose(64, 2, 8192) == 512     # long suffixes: the reference's constant is the cap
+    for batch in (1, 7, 64, 500):
+        for suffix in (1, 63, 64, 65, 700, 5000):
+            size = choose(batch, 4, suffix)
+            assert size % 64 == 0 and 64 <= size <= 512
 
 
 def test_dispatcher_library_registers_the_reference_schema(built_libs):
