@@ -226,8 +226,8 @@ bool tma_eligible(const pfd_decode_args& a) {
          head_is_dim1(a.k_stride_token, a.k_stride_head) == head_is_dim1(a.v_stride_token, a.v_stride_head);
 }
 
-// kWarpsT = 2 beside the dense prefix pass: a CTA of two warps, 166 registers and 34 KB fits on an
-// SM next to a CTA of the slim prefix kernel (see suffix_beside_prefix).
+// kWarpsT = 2, kStagesT = 1 beside the dense prefix pass: two CTAs of two warps, 165 registers
+// and 18 KB fit on an SM next to a CTA of the slim prefix kernel (see suffix_beside_prefix).
 template <bool QBF16, int kWarpsT = kWarps, int kStagesT = kStages>
 int launch_partial_tma(const pfd_decode_args& a, const pfd::KernelParams& kp, dim3 grid, cudaStream_t stream) {
   CUtensorMap mk, mv;

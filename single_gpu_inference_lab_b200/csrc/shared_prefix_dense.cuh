@@ -179,13 +179,13 @@ __device__ __forceinline__ void prefix_mark(const PrefixParams& pp, int k) {
 // Warp w works on TMEM lanes (= rows) 32 * (w % 4) .. +31, the only ones it may address, and on
 // column group w / 4 of whatever is being read: with 16 warps the staging, the softmax and the
 // stores around the two MMAs are spread over all four schedulers four warps deep.
-// SLIM caps the kernel at 80 registers per thread (126 otherwise; the cap costs about 1 us of the
+// SLIM caps the kernel at 80 registers per thread (128 otherwise; the cap costs about 1 us of the
 // pass).  Registers are handed out per SM sub-partition (16 K each): four warps of this CTA at 80
 // registers leave 6144 there, one warp of up to 192 registers -- the two-warp instantiation of
-// the suffix kernel uses 166 -- and with the largest shared-memory carve-out the 34 KB of such a
-// CTA fit beside the 166 KB of this one: the suffix pass then runs on the same SMs WHILE this
-// pass runs instead of after it.  (At 126 registers nothing above 32 registers per thread fits
-// beside this CTA; without the carve-out request nothing at all, whatever the registers.)
+// the suffix kernel uses 165 -- and with the largest shared-memory carve-out two 18 KB CTAs of
+// that kind fit beside the 166 KB of this one: the suffix pass then runs on the same SMs WHILE
+// this pass runs instead of after it.  (At 126 registers nothing above 32 registers per thread
+// fits beside this CTA; without the carve-out request nothing at all, whatever the registers.)
 template <bool QBF16, bool SLIM>
 __global__ void __maxnreg__(SLIM ? 80 : 128)
 shared_prefix_dense_kernel(const KernelParams p, const PrefixParams pp) {
