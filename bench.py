@@ -34,7 +34,9 @@ it.  Rank 0 prints ONE JSON line.
 With N > 1 the headline is one batch per GPU, the same batch (seed) on every rank, no data-path
 collective ("weak").  ``--strong`` / ``--workload llama3-8b-long-b4`` make a sharded form the
 headline instead.  ``--kv-dtype bf16|fp16`` times the non-quantised sibling operator; ``--flags``
-are the ``PFD_FLAG_*`` bits of the timed calls (default: early metadata reads).
+are the ``PFD_FLAG_*`` bits of the timed calls (default 32: early metadata reads; 288 adds early
+K/V streaming).  ``--with-producer`` adds ``with_producer``: the fused RoPE + FP8 append of each
+request's new token in front of every decode call, as in a model layer.
 """
 
 from __future__ import annotations
@@ -93,6 +95,9 @@ def parse_args():
                    help="with the plan: combine the pieces of cut sequences inside the balanced kernel (PFD_FLAG_SINGLE_LAUNCH)")
     p.add_argument("--no-plan", action="store_true",
                    help="do not plan the step: every call derives its work split itself")
+    p.add_argument("--with-producer", action="store_true",
+                   help="also time producer + decode: the fused RoPE + FP8 append of each request's new token in front of "
+                        "every decode call, as in a model layer (reported as `with_producer`)")
     p.add_argument("--producer-step", action="store_true",
                    help="time the step in front of decode attention instead (rotary embedding + FP8 quantise + paged "
                         "KV append, l20_rope_and_cache) and print its own JSON line")
@@ -558,6 +563,44 @@ class Case:
             res["ms_exchange"], _ = self.timed_graph(self.exchange_only, steps, 1, collective=True)
         return res
 
+    # -- producer + decode, as in a model layer: the new token of every request is rotated,
+    # quantised and appended by the kernel in front of the decode call
+    def init_producer(self):
+        w, dev = self.w, self.w.query.device
+        gen = torch.Generator(device="cpu").manual_seed(1)
+        mk = lambda heads: torch.randn(self.batch, heads, self.d, generator=gen).to(w.query.dtype).to(dev)
+        self.pq, self.pk, self.pv = mk(self.hq), mk(self.hkv), mk(self.hkv)
+        pos = (w.seq_lens.long() - 1).clamp_min(0)
+        self.ppos = pos.to(dev)
+        rows = torch.arange(self.batch, device=dev)
+        self.pslots = w.block_table[rows, (self.ppos // 16)].long() * 16 + self.ppos % 16
+        angle = torch.rand(int(pos.max()) + 1, self.d // 2, generator=gen) * 6.2831853
+        self.cos_sin = torch.cat([torch.cos(angle), torch.sin(angle)], dim=1).to(dev)
+
+    def producer(self, i: int):
+        from single_gpu_inference_lab_b200 import l20_rope_kv
+
+        w = self.w
+        l20_rope_kv.l20_rope_and_cache(self.pq, self.pk, self.pv, self.ppos, self.cos_sin, True, self.kcs[i % self.pools],
+                                       self.vcs[i % self.pools], self.pslots, k_scale=w.k_scale, v_scale=w.v_scale)
+
+    def measure_with_producer(self, steps: int, repeats: int) -> dict:
+        self.init_producer()
+
+        def both(i):
+            self.producer(i)
+            self.step(i)
+
+        for i in range(3):
+            both(i)
+        torch.cuda.synchronize()
+        ms_both, runs = self.timed_graph(both, steps, repeats)
+        ms_prod, _ = self.timed_graph(self.producer, steps, 1)
+        return {"us_per_layer_step": round(ms_both * 1e3, 3), "runs_us": [round(r * 1e3, 3) for r in runs],
+                "producer_alone_us": round(ms_prod * 1e3, 3), "status": self.cabi.device_status(),
+                "what": "fused RoPE + FP8 append of one new token per request (its last position), then the decode call; "
+                        "the decode call's flags are the run's"}
+
     def kernel_name(self, path: int) -> str:
         if self.shared_prefix:
             return "shared_prefix_dense_kernel + paged_decode_fp8_partial_tma_kernel + paged_decode_merge_kernel"
@@ -807,6 +850,9 @@ def main() -> int:
         ms_e2e = case.timed_eager(e2e_step, args.steps)  # (the barrier behind the K steps waits for the last result)
         torch.cuda.synchronize()
         ms_eager = case.timed_eager(case.step, args.steps)
+        with_producer = None
+        if args.with_producer and mode == "batch" and case.kv16 is None and not case.shared_prefix and world == 1:
+            with_producer = case.measure_with_producer(args.steps, 3)  # (last: it rewrites the pools' newest tokens)
 
     total_bytes = torch.tensor([float(case.kv_bytes)], device=dev, dtype=torch.float64)
     if world > 1:
@@ -884,6 +930,7 @@ def main() -> int:
                                 "while step i computes, and the host reads step i - 1's result after enqueueing step i; "
                                 "every step has its own copy in, call, copy out and host read",
                     "serial_us_per_layer_step": round(ms_e2e_serial * 1e3, 3)},
+            **({"with_producer": with_producer} if with_producer is not None else {}),
             "gpu_launches": int(res["launches_per_step"] * args.steps),
             "timing": "K steps replayed from CUDA graphs, CUDA events around the replays, median of `repeats` runs; eager launch loop beside it",
             "us_per_layer_step_eager_launch": round(ms_eager * 1e3, 3),

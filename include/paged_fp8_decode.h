@@ -53,6 +53,12 @@ extern "C" {
                                      it.  Only a hint about speed: with a request in no group after
                                      all the result is the same, that request's share just takes
                                      longer                                                         */
+#define PFD_FLAG_EARLY_KV 256u /* with PFD_FLAG_EARLY_METADATA and a plan: the caller also vouches that the
+                                kernel preceding this call in the stream writes K/V only into the LAST page of
+                                each sequence (a decode step's cache append writes one token, at position
+                                seq_len - 1) and nothing of the workspace: the balanced kernel then starts
+                                streaming every other page while that kernel drains and fetches the page pairs
+                                that end a sequence, and the queries, after it has completed                   */
 /*
  * Kernel selection.  For head_dim 128, at most 8 query heads per kv head, a TMA-describable
  * cache and a dense f32 workspace of at least pfd_balanced_workspace_rows() rows the balanced

@@ -22,6 +22,7 @@ PFD_FLAG_FIXED_SPLITS = 8
 PFD_FLAG_EARLY_METADATA = 32
 PFD_FLAG_SINGLE_LAUNCH = 64
 PFD_FLAG_ALL_IN_GROUPS = 128
+PFD_FLAG_EARLY_KV = 256
 
 EXPORTS = (
     "pfd_paged_decode_fp8_e4m3_split_out",

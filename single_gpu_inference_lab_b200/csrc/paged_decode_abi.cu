@@ -524,6 +524,7 @@ pfd::KernelParams fill_params(const pfd_decode_args& a, int group, bool direct_o
     kp.split_size_loner = grouped->split_size_loner;
   }
   kp.early_metadata = (a.flags & PFD_FLAG_EARLY_METADATA) ? 1 : 0;
+  kp.early_kv = (kp.early_metadata && (a.flags & PFD_FLAG_EARLY_KV)) ? 1 : 0;
   kp.kv_evict_first = 1;
   if (a.exchange != nullptr) {
     const pfd_exchange& x = *a.exchange;

@@ -469,7 +469,8 @@ __device__ __forceinline__ int64_t chunk_slot_row(int grp, int which, int num_q_
 //   [0, 16)            header (kPlan* indices below)
 //   [16, 16 + B + 1)   pairs before sequence b
 //   [.., + B)          sequence lengths
-//   groups_off         per group kPlanGroupWords words: P0, P1, 2 reserved, 32 page ids
+//   groups_off         per group kPlanGroupWords words: P0, P1, mask of those of its first 16 pairs
+//                      that end a sequence (hold its last page), 1 reserved, 32 page ids
 //   counters_off       B * Hkv arrival counters (page pairs consumed), zero between launches
 constexpr int kPlanMagic = 0x70666431;
 constexpr int kPlanHeaderWords = 16;
@@ -641,7 +642,12 @@ __global__ void __launch_bounds__(1024) plan_decode_kernel(const PlanParams pp) 
     const ChunkRange cr = chunk_range(list, chunks, grp);
     const int32_t id = fetch_ids(list, kp, cr, 0, lane);
     int32_t* gw = plan + plan_groups_off(B) + (int64_t)grp * kPlanGroupWords;
-    if (lane == 0) { gw[0] = cr.P0; gw[1] = cr.P1; gw[2] = 0; gw[3] = 0; }
+    // which of the group's first 16 pairs end their sequence: a decode step's cache append writes
+    // there and nowhere else, so these are the only pairs that must wait for it (early_kv)
+    const int gpair = cr.P0 + lane;
+    const bool last_of_seq = lane < 16 && gpair < cr.P1 && gpair + 1 == prefix[list.seq_of(gpair) + 1];
+    const unsigned ends = __ballot_sync(0xffffffffu, last_of_seq);
+    if (lane == 0) { gw[0] = cr.P0; gw[1] = cr.P1; gw[2] = (int32_t)ends; gw[3] = 0; }
     gw[4 + lane] = id;
   }
 }
@@ -840,6 +846,7 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
   int total;
   ChunkRange cr;
   int32_t ids_cur;
+  uint32_t seq_ends = 0xffffffffu;  // of the first pairs, those that hold a sequence's last page
   bool plan_ok = true;
   if (planned) {
     // one round trip: header, this group's range and the page ids of its first 16 pairs.  Every
@@ -847,9 +854,10 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
     const int32_t* gw = cp.plan + plan_groups_off(B) + (int64_t)min(grp, num_groups - 1) * kPlanGroupWords;
     const int4 h0 = __ldg(reinterpret_cast<const int4*>(cp.plan));      // magic, batch, kv_start, kv heads
     const int4 h1 = __ldg(reinterpret_cast<const int4*>(cp.plan) + 1);  // groups, piece cost, total, indptr
-    const int2 g0 = __ldg(reinterpret_cast<const int2*>(gw));  // P0, P1
+    const int4 g0 = __ldg(reinterpret_cast<const int4*>(gw));  // P0, P1, pairs that end a sequence
     cr.P0 = g0.x;
     cr.P1 = g0.y;
+    seq_ends = (uint32_t)g0.z;
     ids_cur = __ldg(gw + 4 + lane);
     plan_ok = h0.x == kPlanMagic && h0.y == B && h0.z == p.kv_start && h0.w == hkv && h1.x == num_groups &&
               h1.y == cp.piece_cost && h1.w == (p.page_indptr != nullptr ? 1 : 0);
@@ -905,11 +913,19 @@ paged_decode_fp8_chunk_kernel(const KernelParams p, const TmaParams tp, const Ch
     }
   };
   __syncwarp();
+  // early_kv: the preceding kernel writes K/V only into each sequence's last page, so the first
+  // copies go out before it has completed -- except pairs that hold such a page
+  const bool early_kv = planned && p.early_metadata && p.early_kv && plan_ok;
+  if (early_kv) {
+#pragma unroll
+    for (int t = 0; t < NSTAGE; ++t)
+      if (t < n && !((seq_ends >> t) & 1u)) fire(t, ids_cur, 0);
+  }
   if (p.early_metadata) pdl_wait();
   const uint32_t xstep = exchange_step(p);  // behind the wait: the previous step's merge advances it
 #pragma unroll
   for (int t = 0; t < NSTAGE; ++t)
-    if (t < n) fire(t, ids_cur, 0);
+    if (t < n && (!early_kv || ((seq_ends >> t) & 1u))) fire(t, ids_cur, 0);
   mark_phase_at(tp, W, 2, lane == 0);  // first copies issued
   if (planned) {
     __syncthreads();  // the last CTA-wide barrier: prefix and lens are in shared memory

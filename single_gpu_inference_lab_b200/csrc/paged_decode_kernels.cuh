@@ -62,6 +62,7 @@ struct KernelParams {
   int32_t row_kv_cap;  // upper bound applied to row_kv_start (a multiple of 16): the slots in front cover no more
   int32_t split_size_loner;  // grouped decode: split size of a request in no group (it attends from 0); 0 = split_size
   int32_t early_metadata;  // 1: seq_lens and block_table may be read before the preceding kernel has completed
+  int32_t early_kv;        // 1: so may K/V pages, except each sequence's last (balanced kernel with a plan)
   int32_t kv_evict_first;  // 1: K/V tiles are loaded with the L2 evict-first hint
   // KV-range exchange (xch_world > 0): the packed (o, m, l) rows of this rank go, instead of to
   // packed_output, into slot xch_rank of every rank's receive buffer [2][world][rows][kXchRow]

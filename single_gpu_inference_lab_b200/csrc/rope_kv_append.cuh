@@ -64,6 +64,9 @@ __device__ __forceinline__ uint8_t to_e4m3(float x, float scale) {
 
 template <bool BF16>
 __global__ void __launch_bounds__(256) rope_quant_append_kernel(const RopeParams p) {
+  // lets a kernel launched behind this one as a programmatic dependent become resident while this
+  // one runs (the decode kernels, which wait for its completion before they touch what it writes)
+  asm volatile("griddepcontrol.launch_dependents;");
   const int t = blockIdx.x;
   const int64_t pos = p.positions[t];
   const int64_t slot = p.slot_mapping[t];
@@ -182,6 +185,9 @@ __device__ __forceinline__ void store8_e4m3(void* cache, int64_t i, const Vec8& 
 
 template <bool BF16>
 __global__ void __launch_bounds__(256) rope_quant_append_vec_kernel(const RopeParams p) {
+  // lets a kernel launched behind this one as a programmatic dependent become resident while this
+  // one runs (the decode kernels, which wait for its completion before they touch what it writes)
+  asm volatile("griddepcontrol.launch_dependents;");
   const int t = blockIdx.x;
   const int64_t pos = p.positions[t];
   const int64_t slot = p.slot_mapping[t];

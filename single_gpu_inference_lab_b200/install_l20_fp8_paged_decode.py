@@ -150,6 +150,10 @@ CALL_NEW = """                else:
                             # the operator is capturable: VLLM_L20_PAGED_CUDAGRAPH=1 keeps the hook on
                             # while vLLM records its decode graphs (the reference always steps aside)
                             "graphs": l20_os.getenv("VLLM_L20_PAGED_CUDAGRAPH", "0") == "1",
+                            # the kernel in front of a decode call (the cache write, a prefill
+                            # kernel) writes K/V at most at the decode requests' last positions:
+                            # with VLLM_L20_PAGED_EARLY_KV=1 older pages are streamed while it drains
+                            "early_kv": l20_os.getenv("VLLM_L20_PAGED_EARLY_KV", "0") == "1",
                             "hnd": get_kv_cache_layout() == "HND",
                             "views": None,
                         }
@@ -273,6 +277,7 @@ CALL_NEW = """                else:
                             output=out_decode.view_as(decode_query),
                             workspace=l20_step.workspace,
                             metadata_stable=True,  # built once per model step
+                            kv_stable=l20_static["early_kv"],
                             plan=l20_step.plan,
                         )
                         trace_path = l20_static["fp8_trace"]
@@ -303,6 +308,7 @@ CALL_NEW = """                else:
                             max_seq_len=l20_fp8_max_seq,
                             output=out_decode.view_as(decode_query),
                             metadata_stable=True,
+                            kv_stable=l20_static["early_kv"],
                             plan=l20_step.plan,
                         )
                         trace_path = l20_static["kv16_trace"]

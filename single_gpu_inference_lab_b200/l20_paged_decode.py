@@ -23,6 +23,7 @@ FLAG_PARTIAL_ONLY = 4
 FLAG_FIXED_SPLITS = 8
 FLAG_EARLY_METADATA = 32
 FLAG_SINGLE_LAUNCH = 64
+FLAG_EARLY_KV = 256
 
 
 def load_library(path: Optional[Union[str, Path]] = None) -> None:

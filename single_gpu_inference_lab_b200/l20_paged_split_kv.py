@@ -161,6 +161,7 @@ def l20_paged_split_kv_attention_fp8(
     metadata_stable: bool = False,
     plan: torch.Tensor | None = None,
     single_launch: bool = False,
+    kv_stable: bool = False,
 ) -> torch.Tensor:
     """``metadata_stable=True`` (not in the reference) tells the operator that the kernel
     running before it on the stream does not write ``block_table``, ``seq_lens`` or ``plan`` --
@@ -169,7 +170,10 @@ def l20_paged_split_kv_attention_fp8(
     either) is the result of ``plan_l20_paged_split_kv`` for the same step: the kernels then read
     their work split instead of deriving it; ``single_launch`` (needs a plan) makes the balanced
     kernel combine the pieces of cut sequences itself, one launch instead of two
-    (``PFD_FLAG_SINGLE_LAUNCH``; the slower of the two on B200)."""
+    (``PFD_FLAG_SINGLE_LAUNCH``; the slower of the two on B200).  ``kv_stable=True`` (with
+    ``metadata_stable`` and a plan): that kernel also writes K/V only into the last page of each
+    sequence -- a decode step's cache append -- so every other page may be streamed while it
+    drains (``PFD_FLAG_EARLY_KV``)."""
     if not _on_required_gpu(query):
         raise RuntimeError("requires an SM100 GPU")
     if query.ndim != 3 or key_cache.ndim != 4 or value_cache.shape != key_cache.shape:
@@ -219,7 +223,8 @@ def l20_paged_split_kv_attention_fp8(
             query, key_cache, value_cache, block_table, seq_lens,
             partial_output, partial_max, partial_sum, output,
             as_vec(k_scale), as_vec(v_scale), max_seq_len, split_size,
-            flags=(ops.FLAG_EARLY_METADATA if metadata_stable else 0) | (ops.FLAG_SINGLE_LAUNCH if single_launch else 0),
+            flags=(ops.FLAG_EARLY_METADATA if metadata_stable else 0) | (ops.FLAG_SINGLE_LAUNCH if single_launch else 0)
+            | (ops.FLAG_EARLY_KV if kv_stable and metadata_stable else 0),
             plan=plan,
         )
         return output
@@ -244,9 +249,10 @@ def l20_paged_split_kv_attention(
     metadata_stable: bool = False,
     plan: torch.Tensor | None = None,
     single_launch: bool = False,
+    kv_stable: bool = False,
 ) -> torch.Tensor:
     """The non-quantised sibling (reference :491-594): K/V caches in the query's fp16 / bf16
-    type.  ``metadata_stable`` / ``plan`` / ``single_launch`` as for the FP8 wrapper.  ``page_granular`` / ``grouped_gqa`` of the reference select between its Triton kernel
+    type.  ``metadata_stable`` / ``plan`` / ``single_launch`` / ``kv_stable`` as for the FP8 wrapper.  ``page_granular`` / ``grouped_gqa`` of the reference select between its Triton kernel
     variants and have no counterpart here.  ``max_seq_len`` (not in the reference, which always
     reads it back from the device, :517) avoids that host synchronisation."""
     if not _on_required_gpu(query):
@@ -288,7 +294,8 @@ def l20_paged_split_kv_attention(
         return ops.paged_decode_split_out_v2(
             query, key_cache, value_cache, block_table, seq_lens,
             partial_output, partial_max, partial_sum, output, max_seq_len, split_size,
-            flags=(ops.FLAG_EARLY_METADATA if metadata_stable else 0) | (ops.FLAG_SINGLE_LAUNCH if single_launch else 0),
+            flags=(ops.FLAG_EARLY_METADATA if metadata_stable else 0) | (ops.FLAG_SINGLE_LAUNCH if single_launch else 0)
+            | (ops.FLAG_EARLY_KV if kv_stable and metadata_stable else 0),
             plan=plan,
         )
     return ops.paged_decode_split_out(

@@ -30,6 +30,7 @@ def cabi(built_libs):
 PATH_LDG, PATH_TMA, PATH_BALANCED, PATH_FUSED = 1, 2, 3, 5
 EARLY = 32  # PFD_FLAG_EARLY_METADATA: what the benchmark and the vLLM hook pass
 SINGLE = 64  # PFD_FLAG_SINGLE_LAUNCH: pieces combined inside the balanced kernel (needs a plan)
+EARLY_KV = 256  # PFD_FLAG_EARLY_KV: with EARLY and a plan, pages other than a sequence's last are streamed before the wait
 PLAN = 1 << 20  # not a library flag: the test helpers call pfd_plan_decode first and pass the plan
 FUSED = PLAN | SINGLE
 
@@ -106,7 +107,7 @@ def expected(w, **kw):
 @pytest.mark.parametrize(
     "name", ["cfg1-qwen0.5b-b8", "cfg2-coder3b-b4", "cfg3-qwen7b-b24", "cfg4-llama8b-b2", "cfg5-prefix-b8"]
 )
-@pytest.mark.parametrize("flags", [PLAN, FUSED, 8, 1, 0, PLAN | EARLY, FUSED | EARLY])
+@pytest.mark.parametrize("flags", [PLAN, FUSED, 8, 1, 0, PLAN | EARLY, FUSED | EARLY, PLAN | EARLY | EARLY_KV, FUSED | EARLY | EARLY_KV])
 def test_against_committed_reference_outputs(cabi, golden, name, flags):
     case = golden["cases"][name]
     w = make_inputs(case["workload"], seed=0, device="cpu", batch=case["batch"], shrink=case["shrink"])
@@ -143,7 +144,7 @@ def test_config1_full_size(cabi):
 def test_config2_full_size(cabi):
     w = make_inputs("qwen2.5-coder-3b-b64", seed=0)
     exp = expected(w)
-    for split, flags in ((256, PLAN), (512, 0), (896, 0), (512, 8), (1024, 1), (512, EARLY), (896, EARLY | 8), (256, EARLY | 1), (512, PLAN | EARLY), (512, FUSED), (256, FUSED | EARLY)):
+    for split, flags in ((256, PLAN), (512, 0), (896, 0), (512, 8), (1024, 1), (512, EARLY), (896, EARLY | 8), (256, EARLY | 1), (512, PLAN | EARLY), (512, FUSED), (256, FUSED | EARLY), (512, PLAN | EARLY | EARLY_KV), (256, EARLY | EARLY_KV)):
         assert_within_gate(run(cabi, w.to(DEV), split, flags=flags), exp, f"cfg2 split={split} flags={flags}")
 
 
@@ -151,7 +152,7 @@ def test_config3_full_size_log_uniform_lengths(cabi):
     w = make_inputs("qwen2.5-7b-b256", seed=0)
     assert int(w.seq_lens.min()) <= 4
     exp = expected(w)
-    for flags in (0, PLAN, FUSED, 8, EARLY, EARLY | 8, PLAN | EARLY, FUSED | EARLY):
+    for flags in (0, PLAN, FUSED, 8, EARLY, EARLY | 8, PLAN | EARLY, FUSED | EARLY, PLAN | EARLY | EARLY_KV):
         assert_within_gate(run(cabi, w.to(DEV), 512, flags=flags), exp, f"cfg3 flags={flags}")
 
 
@@ -165,7 +166,9 @@ def test_config4_long_context_sampled_rows_and_split_invariance(cabi):
     out_c = run(cabi, w, 16384)
     out_d = run(cabi, w, 2048, flags=EARLY)
     out_f = run(cabi, w, 2048, flags=PLAN | EARLY)
+    out_h = run(cabi, w, 2048, flags=PLAN | EARLY | EARLY_KV)
     assert_within_gate(out_f, out_a, "planned, early metadata vs not")
+    assert_within_gate(out_h, out_a, "planned, early metadata and early K/V vs not")
     out_g = run(cabi, w, 2048, flags=FUSED | EARLY)
     assert_within_gate(out_g, out_a, "pieces combined inside the balanced kernel vs the merge kernel")
     out_e = run(cabi, w, 1024, flags=EARLY | 8)

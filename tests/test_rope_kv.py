@@ -180,6 +180,38 @@ def test_append_then_decode_equals_the_oracles(built_libs):
     torch.cuda.synchronize()
     assert torch.equal(g.key_cache.cpu().view(torch.uint8), ekc.view(torch.uint8))
     assert_within_gate(out, exp, "append + decode")
+    # The same step with a plan and the caller's word that the kernel in front of the decode call
+    # writes K/V only at each sequence's last position (kv_stable): the balanced kernel may then
+    # fetch older pages before the append has completed, and must still see the new token.
+    w2 = make_inputs("qwen2.5-coder-3b-b64", seed=12, batch=64, shrink=0.5)
+    batch = w2.query.shape[0]
+    positions = (w2.seq_lens.long() - 1)
+    slots = w2.block_table[torch.arange(batch), positions // 16].long() * 16 + positions % 16
+    q = torch.randn(batch, hq, d, generator=gen).to(torch.bfloat16)
+    k = torch.randn(batch, hkv, d, generator=gen).to(torch.bfloat16)
+    v = torch.randn(batch, hkv, d, generator=gen).to(torch.bfloat16)
+    angle = torch.arange(int(positions.max()) + 1)[:, None] * (1e4 ** (-torch.arange(0, d, 2) / d))[None, :]
+    cos_sin = torch.cat([torch.cos(angle), torch.sin(angle)], dim=1).float()
+    eq, _, ekc, evc = oracle.rope_and_cache(q, k, v, positions, cos_sin, True, w2.key_cache, w2.value_cache, slots,
+                                            w2.k_scale, w2.v_scale)
+    exp = decode_oracle.reference(eq, ekc, evc, w2.block_table.long(), w2.seq_lens, w2.k_scale, w2.v_scale)
+    g = w2.to(DEV)
+    kc0, vc0 = g.key_cache.clone(), g.value_cache.clone()
+    ws = l20_paged_split_kv.allocate_l20_paged_split_kv_workspace(g.query, w2.max_seq_len, split_size=512)
+    plan = l20_paged_split_kv.plan_l20_paged_split_kv(g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens,
+                                                      max_seq_len=w2.max_seq_len, split_size=512, workspace=ws)
+    cs, pos, sl = cos_sin.to(DEV), positions.to(DEV), slots.to(DEV)
+    for rep in range(8):
+        g.key_cache.copy_(kc0)
+        g.value_cache.copy_(vc0)
+        gq, gk, gv = q.to(DEV), k.to(DEV), v.to(DEV)
+        l20_rope_kv.l20_rope_and_cache(gq, gk, gv, pos, cs, True, g.key_cache, g.value_cache, sl,
+                                       k_scale=g.k_scale, v_scale=g.v_scale)
+        out = l20_paged_split_kv.l20_paged_split_kv_attention_fp8(
+            gq, g.key_cache, g.value_cache, g.block_table, g.seq_lens, k_scale=g.k_scale, v_scale=g.v_scale,
+            max_seq_len=w2.max_seq_len, split_size=512, workspace=ws, plan=plan, metadata_stable=True, kv_stable=True)
+        torch.cuda.synchronize()
+        assert_within_gate(out, exp, f"append + planned decode with early K/V, repetition {rep}")
 
 
 def test_wrapper_argument_errors_without_a_gpu():
