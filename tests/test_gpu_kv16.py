@@ -86,6 +86,7 @@ def test_config2_and_config3_full_size(cabi, dtype):
         exp = expected(w)
         assert_within_gate(run(cabi, w.to(DEV)), exp, f"{name} {dtype}")
         assert_within_gate(run(cabi, w.to(DEV), planned=True, flags=32), exp, f"{name} {dtype} planned")
+        assert_within_gate(run(cabi, w.to(DEV), planned=True, flags=32 | 256), exp, f"{name} {dtype} planned, early K/V")
         assert_within_gate(run(cabi, w.to(DEV), planned="fused", flags=32), exp, f"{name} {dtype} fused")
 
 
