@@ -66,14 +66,29 @@ def test_a_step_with_shared_prefix_groups_takes_the_grouped_operator_and_is_trac
     for _layer in range(2):
         step = mod.l20_decode_step(meta, g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens, w.max_seq_len)
         assert step.groups is not None and step.group_sizes == [16]
+        assert step.all_in_groups and step.one_prefix == 4096  # one group spans the batch: the single-group operator runs
         out = mod.l20_grouped_decode(step, g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens, g.k_scale, g.v_scale,
                                      w.max_seq_len, torch.empty_like(g.query))
         torch.cuda.synchronize()
         assert_within_gate(out, exp, "grouped layer")
     records = [json.loads(line) for line in trace.read_text().splitlines()]
     assert [r["event"] for r in records] == ["shared_prefix_decode_candidate", "l20_shared_prefix_paged_decode_run",
-                                             "l20_shared_prefix_paged_decode_run"]
+                                             "l20_shared_prefix_paged_decode_run"]  # (read before the second batch below)
     assert records[0]["eligible"] is True and records[0]["group_sizes"] == [16] and records[0]["batch"] == 16
+    # two groups of eight: the grouped operator, with the word that no request is outside the groups
+    gen = torch.Generator().manual_seed(5)
+    pages = w.key_cache.shape[0]
+    w.block_table = w.block_table.clone()
+    w.block_table[8:, : w.prefix_len // 16] = torch.randint(0, pages, (w.prefix_len // 16,), generator=gen, dtype=torch.int32)
+    exp = oracle.reference(w.query, w.key_cache, w.value_cache, w.block_table.long(), w.seq_lens, w.k_scale, w.v_scale)
+    g = w.to(DEV)
+    meta = SimpleNamespace(l20_step=None)
+    step = mod.l20_decode_step(meta, g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens, w.max_seq_len)
+    assert step.group_sizes == [8, 8] and step.all_in_groups and step.one_prefix == 0
+    out = mod.l20_grouped_decode(step, g.query, g.key_cache, g.value_cache, g.block_table, g.seq_lens, g.k_scale, g.v_scale,
+                                 w.max_seq_len, torch.empty_like(g.query))
+    torch.cuda.synchronize()
+    assert_within_gate(out, exp, "two groups of eight")
     # a batch without groups: the step keeps to the ordinary operator
     other = make_inputs("qwen2.5-coder-3b-b64", seed=33, batch=16).to(DEV)
     meta = SimpleNamespace(l20_step=None)
