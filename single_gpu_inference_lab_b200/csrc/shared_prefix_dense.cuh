@@ -149,9 +149,9 @@ struct PrefixParams {
   int32_t prefix_len;   // tokens shared by every request (multiple of 16)
   int32_t batch;
   // Grouped form: the groups buffer of the grouping kernels (shared_prefix_groups.cuh) and its
-  // geometry.  grid = (prefix chunks x kv heads, slots for (group, 128-row tile) pairs): the
-  // slots that exist come first in launch order, so CTAs whose slot or chunk lies beyond what the
-  // device-side table holds (they leave at once) queue behind the working ones, not among them.
+  // geometry.  grid = (prefix chunks x kv heads, tile slots); the (group, 128-row tile) pairs of
+  // the device-side table are numbered in group order and the CTAs of a column take the numbers
+  // blockIdx.y, blockIdx.y + gridDim.y, ... in turns, so any number of slots covers the table.
   const int32_t* groups;
   int32_t groups_batch, max_groups;
   int32_t* status;
