@@ -14,6 +14,12 @@ hook's trace file says how often it ran.  Two ways to run it:
            ``--cuda-graphs`` vLLM's default graphs and the hook kept on while they are recorded
            (``VLLM_L20_PAGED_CUDAGRAPH=1``; the reference always steps aside under capture).
 
+           ``--dummy-weights`` makes this mode runnable on a host without model files: a Qwen2-shaped
+           model directory is written (``--layers``, ``--q-heads``, ``--kv-heads``, ``--intermediate``) with a
+           synthetic word-level tokenizer whose decode / encode round trip is exact, and the server
+           draws the weights (``--load-format dummy``).  Latencies are then those of the shape, the
+           generated text means nothing.
+
 ``dummy``  for a host without weights (this build's GPU boxes have no network): the in-process
            engine of ``vllm_live_check.py --ab`` -- a Qwen2-shaped model with re-drawn random
            weights -- once per cell; batch = concurrency, all prompts of the given length, decode
@@ -66,6 +72,31 @@ def build_overlay(work: Path) -> Path:
     return src
 
 
+def write_dummy_model(path: Path, *, layers: int, q_heads: int, kv_heads: int, intermediate: int, vocab: int = 32000) -> Path:
+    """A model directory a server can start from without any downloaded file: the config of a
+    Qwen2-shaped model and a word-level tokenizer over ``vocab`` made-up words (ids 0-3: unk, bos,
+    eos, pad; id i: the word "w<i>"), for which ``encode(decode(ids)) == ids`` -- the random
+    dataset of ``vllm bench serve`` builds its prompts by decoding random ids."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    from .vllm_live_check import write_model_config
+
+    write_model_config(path, layers=layers, q_heads=q_heads, kv_heads=kv_heads, intermediate=intermediate)
+    config = json.loads((path / "config.json").read_text())
+    config["vocab_size"] = vocab
+    (path / "config.json").write_text(json.dumps(config))
+    specials = ["<unk>", "<bos>", "<eos>", "<pad>"]
+    assert config["bos_token_id"] == 1 and config["eos_token_id"] == 2
+    words = {s: i for i, s in enumerate(specials)}
+    words.update({f"w{i}": i for i in range(len(specials), vocab)})
+    tok = Tokenizer(models.WordLevel(words, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    PreTrainedTokenizerFast(tokenizer_object=tok, unk_token="<unk>", bos_token="<bos>", eos_token="<eos>",
+                            pad_token="<pad>").save_pretrained(str(path))
+    return path
+
+
 def wait_for_server(port: int, proc: subprocess.Popen, log: Path, seconds: int = 900) -> None:
     deadline = time.time() + seconds
     while time.time() < deadline:
@@ -97,6 +128,8 @@ def run_serve_arm(args, src: Path, out: Path, hook_on: bool) -> dict:
              "--max-num-seqs", str(max(args.concurrencies)), "--max-model-len", str(args.max_model_len)]
     if not args.cuda_graphs:
         serve.append("--enforce-eager")
+    if args.dummy_weights:
+        serve += ["--load-format", "dummy"]
     log = out / "server.log"
     with log.open("w") as sink:
         server = subprocess.Popen(serve, env=env, stdout=sink, stderr=subprocess.STDOUT, start_new_session=True)
@@ -171,7 +204,12 @@ def main(argv: list[str] | None = None) -> int:
     parser.add_argument("--num-prompts", type=int, default=int(os.environ.get("NUM_PROMPTS", "32")))
     parser.add_argument("--output-tokens", type=int, default=int(os.environ.get("OUTPUT_TOKENS", "32")))
     parser.add_argument("--max-model-len", type=int, default=int(os.environ.get("MAX_MODEL_LEN", "8192")))
-    parser.add_argument("--layers", type=int, default=36, help="dummy: layers of the random-weight model")
+    parser.add_argument("--layers", type=int, default=36, help="dummy, serve --dummy-weights: layers of the random-weight model")
+    parser.add_argument("--dummy-weights", action="store_true",
+                        help="serve: write a Qwen2-shaped model directory with a synthetic tokenizer and let the server draw the weights")
+    parser.add_argument("--q-heads", type=int, default=16)
+    parser.add_argument("--kv-heads", type=int, default=2)
+    parser.add_argument("--intermediate", type=int, default=4096)
     parser.add_argument("--cuda-graphs", action="store_true")
     args = parser.parse_args(argv)
     out = Path(args.output_dir).resolve()
@@ -181,8 +219,12 @@ def main(argv: list[str] | None = None) -> int:
     if args.mode == "dummy":
         summary["cells"] = run_dummy_cells(args, out)
     else:
+        if args.dummy_weights:
+            args.model = str(write_dummy_model(out / "model", layers=args.layers, q_heads=args.q_heads,
+                                               kv_heads=args.kv_heads, intermediate=args.intermediate))
+            summary["weights"] = "dummy"
         if not args.model:
-            parser.error("serve needs --model")
+            parser.error("serve needs --model or --dummy-weights")
         src = build_overlay(out)
         off = run_serve_arm(args, src, out / "hook-off", hook_on=False)
         on = run_serve_arm(args, src, out / "hook-on", hook_on=True)
